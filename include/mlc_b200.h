@@ -1,0 +1,186 @@
+/*
+ * mlc_b200.h - C ABI of the B200-native paged-attention path.
+ *
+ * Drop-in boundary for MLcompiler's paged flash-attention decode kernel, its
+ * paged KV writers/readers and the host objects that feed them. MLcompiler has
+ * no FFI layer: the surface being replaced is the member-function set of the
+ * singleton mlc::runtime::MetalExecutor (compiler/runtime/metal_runtime.hpp)
+ * plus the paged-KV classes (compiler/runtime/paged_kv.hpp) and the scheduler
+ * interface (compiler/runtime/scheduler.hpp, batched_executor.hpp). Each entry
+ * point below names the declaration it stands in for.
+ *
+ * Conventions
+ *   - Plain C: opaque handles, raw pointers, sizes. No C++/torch types.
+ *   - "device pointer" = CUDA global memory of the context's GPU (from
+ *     mlc_alloc, cudaMalloc, or a torch tensor's data_ptr()).
+ *   - "host array" = ordinary host memory; it is copied during the call and
+ *     never retained (same contract as the reference's std::vector arguments,
+ *     metal_runtime.mm:7101-7107).
+ *   - Every function returning int returns an mlc_status; MLC_OK == 0.
+ *     The reference returns bool: ok <=> MLC_OK.
+ *   - encode_* calls are asynchronous on the context's stream and require an
+ *     open pass (mlc_pass_begin), like the reference's encode* members which
+ *     need an open forward-pass command buffer (metal_runtime.mm:7090).
+ *     run_* calls validate their arguments, launch and wait.
+ *   - A context is single-threaded by contract (paged_kv.hpp:25-27).
+ *   - There is no CPU fallback anywhere behind this header: without a CUDA
+ *     device mlc_ctx_create fails with MLC_ERR_NO_DEVICE.
+ */
+#ifndef MLC_B200_H
+#define MLC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mlc_status {
+    MLC_OK = 0,
+    MLC_ERR_INVALID_ARG = 1,   /* the cases for which the reference returns false */
+    MLC_ERR_NO_OPEN_PASS = 2,  /* encode_* without mlc_pass_begin (mm:7090, 7178) */
+    MLC_ERR_CUDA = 3,          /* a CUDA runtime/driver call failed; see mlc_last_error */
+    MLC_ERR_BOUNDS = 4,        /* page id / slot / length check failed (added checks) */
+    MLC_ERR_UNSUPPORTED = 5,   /* shape outside what the kernels cover (head_dim > 256) */
+    MLC_ERR_NO_DEVICE = 6,
+    MLC_ERR_OOM = 7,
+    MLC_ERR_DEVICE_FLAG = 8    /* a kernel recorded an error word; see mlc_device_error_word */
+} mlc_status;
+
+typedef enum mlc_dtype { MLC_F32 = 0, MLC_F16 = 1 } mlc_dtype;
+
+/* Bits of the device-written error word (never a trap, never a hang). */
+#define MLC_DEVERR_WAIT_TIMEOUT 0x1u  /* a bounded mbarrier wait ran out */
+#define MLC_DEVERR_BAD_PAGE 0x2u      /* page id >= capacity seen by a checking kernel */
+#define MLC_DEVERR_BAD_SLOT 0x4u      /* slot >= page_size seen by a checking kernel */
+
+typedef struct mlc_ctx mlc_ctx;
+
+/* ---- context: replaces MetalExecutor::Instance() (metal_runtime.mm:5774) ------
+ * One context per GPU. `stream` is a cudaStream_t to enqueue on, or NULL to let
+ * the context create its own non-blocking stream. */
+int mlc_ctx_create(int device, void* stream, mlc_ctx** out);
+void mlc_ctx_destroy(mlc_ctx* ctx);
+/* isAvailable() (metal_runtime.hpp:26): 1 when the context owns a usable device. */
+int mlc_ctx_available(const mlc_ctx* ctx);
+/* Text of the most recent failure on this context (valid until the next call). */
+const char* mlc_last_error(const mlc_ctx* ctx);
+/* Reads and clears the device error word (synchronises the stream first). */
+int mlc_device_error_word(mlc_ctx* ctx, uint32_t* word);
+/* The stream the context enqueues on (cudaStream_t). */
+void* mlc_ctx_stream(const mlc_ctx* ctx);
+/* Number of kernels this context has launched since creation. */
+uint64_t mlc_ctx_launch_count(const mlc_ctx* ctx);
+
+/* ---- buffers: allocateScratchBuffer / releaseScratchBuffer / uploadToBuffer /
+ * downloadFromBuffer (metal_runtime.hpp:693-696) and getOrAllocCachedBuffer
+ * (metal_runtime.hpp:703). upload/download are synchronous. */
+void* mlc_alloc(mlc_ctx* ctx, size_t bytes);
+void mlc_free(mlc_ctx* ctx, void* buffer);
+int mlc_upload(mlc_ctx* ctx, void* buffer, const void* src, size_t bytes, size_t dst_offset);
+int mlc_download(mlc_ctx* ctx, const void* buffer, void* dst, size_t bytes, size_t src_offset);
+void* mlc_cached_buffer(mlc_ctx* ctx, const char* name, size_t bytes);
+/* Size of the mlc_alloc / mlc_cached_buffer allocation that starts at `buffer`,
+ * or 0 if the pointer is not one of the context's own. */
+size_t mlc_buffer_bytes(const mlc_ctx* ctx, const void* buffer);
+
+/* ---- pass bracketing: beginForwardPassCB / hasForwardPassCB / flushForwardPassCB
+ * (metal_runtime.hpp:181-183). flush waits for the stream and reports
+ * MLC_ERR_DEVICE_FLAG if a kernel of the pass recorded an error word. */
+int mlc_pass_begin(mlc_ctx* ctx);
+int mlc_pass_is_open(const mlc_ctx* ctx);
+int mlc_pass_flush(mlc_ctx* ctx);
+
+/* ---- KV writers / readers ------------------------------------------------------
+ * Page layout everywhere: [page_size_tokens, n_kv_heads, head_dim] token-major,
+ * page i at element offset i * page_size_tokens * n_kv_heads * head_dim
+ * (paged_kv.hpp:101-105).
+ *
+ * capacity_pages: number of pages `page_storage` holds, used for the added
+ * bounds checks; pass 0 when unknown (then, like the reference, ids are not
+ * checked - except that buffers obtained from mlc_alloc are still checked
+ * against their recorded size). */
+
+/* scatterKVPagedBatched (metal_runtime.hpp:680-687; kernel
+ * scatter_kv_paged_batched_f16, metal_runtime.mm:405-424): one new fp16 row per
+ * request. src: device fp16 [batch, n_kv_heads, head_dim]; page_ids / slots_in_page:
+ * host u32 [batch]. Synchronous. */
+int mlc_run_scatter_kv_paged_batched_f16(mlc_ctx* ctx, void* page_storage,
+                                         const uint32_t* page_ids, const uint32_t* slots_in_page,
+                                         size_t page_size_tokens, size_t n_kv_heads,
+                                         size_t head_dim, size_t batch, const void* src,
+                                         size_t capacity_pages);
+/* encodeScatterKVPagedBatched (metal_runtime.hpp:526-533). Asynchronous. */
+int mlc_encode_scatter_kv_paged_batched_f16(mlc_ctx* ctx, void* page_storage,
+                                            const uint32_t* page_ids,
+                                            const uint32_t* slots_in_page,
+                                            size_t page_size_tokens, size_t n_kv_heads,
+                                            size_t head_dim, size_t batch, const void* src,
+                                            size_t capacity_pages);
+/* K and V rows of one layer in ONE launch (the reference issues two dispatches,
+ * batched_walker.cpp:304-309). Asynchronous. */
+int mlc_encode_scatter_kv_pair_paged_batched_f16(mlc_ctx* ctx, void* k_page_storage,
+                                                 void* v_page_storage, const uint32_t* page_ids,
+                                                 const uint32_t* slots_in_page,
+                                                 size_t page_size_tokens, size_t n_kv_heads,
+                                                 size_t head_dim, size_t batch, const void* k_src,
+                                                 const void* v_src, size_t capacity_pages);
+/* scatterKVPaged (metal_runtime.hpp:666-674; kernels scatter_kv_paged_f16/_f32,
+ * metal_runtime.mm:468-512): multi-token scatter of one request. src: device
+ * [n_kv_heads, tokens, head_dim]; page_table: host u32 [n_page_table]. Synchronous. */
+int mlc_run_scatter_kv_paged(mlc_ctx* ctx, void* page_storage, const uint32_t* page_table,
+                             size_t n_page_table, size_t page_size_tokens, size_t n_kv_heads,
+                             size_t head_dim, size_t tokens, size_t start_slot, const void* src,
+                             size_t dtype_bytes, size_t capacity_pages);
+/* gatherKVPages (metal_runtime.hpp:619-626; kernels gather_kv_pages_f16/_f32,
+ * metal_runtime.mm:328-370): paged -> contiguous [n_kv_heads, num_tokens, head_dim]. */
+int mlc_run_gather_kv_pages(mlc_ctx* ctx, const void* page_storage, const uint32_t* page_table,
+                            size_t n_page_table, size_t page_size_tokens, size_t n_kv_heads,
+                            size_t head_dim, size_t num_tokens, void* dst, size_t dtype_bytes,
+                            size_t capacity_pages);
+
+/* ---- paged flash-attention decode ------------------------------------------------
+ * O[r,h,:] = softmax_s(scale * Q[r,h,:].K[r,s,kv_h,:] + mask) . V[r,s,kv_h,:],
+ * s in [0, seq_lens[r]), kv_h = h * kv_heads / num_heads, mask = -inf where
+ * apply_causal and s > q_positions[r]; seq_lens[r] == 0 or a fully masked row
+ * gives zeros (kernel paged_flash_attention, metal_runtime.mm:2216-2335).
+ *
+ *   q, o            device [batch, num_heads, head_dim], fp32 (the reference's
+ *                   type, metal_runtime.hpp:632-636) or fp16, per q_dtype / o_dtype
+ *   k_pages,v_pages device fp16 paged pools
+ *   page_tables_flat, page_table_offsets[batch+1], seq_lens[batch],
+ *   q_positions[batch]   host u32 arrays
+ *   scale           multiplies the scores; the reference hard-codes
+ *                   1/sqrt(head_dim) (metal_runtime.mm:7133) - pass a value <= 0
+ *                   to get exactly that.
+ */
+/* runPagedFlashAttention (metal_runtime.hpp:645-658). Validates as
+ * metal_runtime.mm:7742-7750, launches, waits. */
+int mlc_run_paged_flash_attention(mlc_ctx* ctx, const void* q, const void* k_pages,
+                                  const void* v_pages, void* o,
+                                  const uint32_t* page_tables_flat, size_t n_page_tables_flat,
+                                  const uint32_t* page_table_offsets, const uint32_t* seq_lens,
+                                  const uint32_t* q_positions, size_t batch, size_t num_heads,
+                                  size_t kv_heads, size_t head_dim, size_t page_size_tokens,
+                                  int apply_causal, float scale, int q_dtype, int o_dtype,
+                                  size_t capacity_pages);
+/* encodePagedFlashAttention (metal_runtime.hpp:510-523). Asynchronous. */
+int mlc_encode_paged_flash_attention(mlc_ctx* ctx, const void* q, const void* k_pages,
+                                     const void* v_pages, void* o,
+                                     const uint32_t* page_tables_flat, size_t n_page_tables_flat,
+                                     const uint32_t* page_table_offsets, const uint32_t* seq_lens,
+                                     const uint32_t* q_positions, size_t batch, size_t num_heads,
+                                     size_t kv_heads, size_t head_dim, size_t page_size_tokens,
+                                     int apply_causal, float scale, int q_dtype, int o_dtype,
+                                     size_t capacity_pages);
+
+/* Selects the kernel family used by the attention entry points of this context:
+ * 0 = automatic (TMA + tensor-core split-KV kernel when the shape allows it,
+ * otherwise the general kernel), 1 = always the general kernel. Both are CUDA. */
+int mlc_ctx_set_attention_kernel(mlc_ctx* ctx, int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLC_B200_H */

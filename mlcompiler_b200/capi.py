@@ -1,0 +1,273 @@
+"""ctypes binding of include/mlc_b200.h plus a thin `Executor` whose methods carry
+the names and argument order of the reference's MetalExecutor members
+(compiler/runtime/metal_runtime.hpp:510-533, 619-703), so that tests written
+against it read like the reference's own tests.
+
+Device buffers are passed as integers (addresses), `torch.Tensor`s (their
+data_ptr() is taken) or anything with a `data_ptr()`; host arrays as anything
+numpy can view as uint32.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+_PKG = Path(__file__).resolve().parent
+_LIB = None
+
+MLC_F32, MLC_F16 = 0, 1
+STATUS = {0: "MLC_OK", 1: "MLC_ERR_INVALID_ARG", 2: "MLC_ERR_NO_OPEN_PASS", 3: "MLC_ERR_CUDA",
+          4: "MLC_ERR_BOUNDS", 5: "MLC_ERR_UNSUPPORTED", 6: "MLC_ERR_NO_DEVICE", 7: "MLC_ERR_OOM",
+          8: "MLC_ERR_DEVICE_FLAG"}
+
+
+class MlcError(RuntimeError):
+    def __init__(self, status: int, message: str = ""):
+        self.status = status
+        super().__init__(f"{STATUS.get(status, status)}: {message}")
+
+
+def library_path() -> Path:
+    return _PKG / "libmlc_b200.so"
+
+
+_u32p = C.POINTER(C.c_uint32)
+_vp, _sz, _i, _f = C.c_void_p, C.c_size_t, C.c_int, C.c_float
+
+_PROTOTYPES = {
+    "mlc_ctx_create": (_i, [_i, _vp, C.POINTER(_vp)]),
+    "mlc_ctx_destroy": (None, [_vp]),
+    "mlc_ctx_available": (_i, [_vp]),
+    "mlc_last_error": (C.c_char_p, [_vp]),
+    "mlc_device_error_word": (_i, [_vp, _u32p]),
+    "mlc_ctx_stream": (_vp, [_vp]),
+    "mlc_ctx_launch_count": (C.c_uint64, [_vp]),
+    "mlc_ctx_set_attention_kernel": (_i, [_vp, _i]),
+    "mlc_alloc": (_vp, [_vp, _sz]),
+    "mlc_free": (None, [_vp, _vp]),
+    "mlc_upload": (_i, [_vp, _vp, _vp, _sz, _sz]),
+    "mlc_download": (_i, [_vp, _vp, _vp, _sz, _sz]),
+    "mlc_cached_buffer": (_vp, [_vp, C.c_char_p, _sz]),
+    "mlc_buffer_bytes": (_sz, [_vp, _vp]),
+    "mlc_pass_begin": (_i, [_vp]),
+    "mlc_pass_is_open": (_i, [_vp]),
+    "mlc_pass_flush": (_i, [_vp]),
+    "mlc_run_scatter_kv_paged_batched_f16": (_i, [_vp, _vp, _u32p, _u32p, _sz, _sz, _sz, _sz, _vp, _sz]),
+    "mlc_encode_scatter_kv_paged_batched_f16": (_i, [_vp, _vp, _u32p, _u32p, _sz, _sz, _sz, _sz, _vp, _sz]),
+    "mlc_encode_scatter_kv_pair_paged_batched_f16": (_i, [_vp, _vp, _vp, _u32p, _u32p, _sz, _sz, _sz, _sz, _vp, _vp, _sz]),
+    "mlc_run_scatter_kv_paged": (_i, [_vp, _vp, _u32p, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _sz, _sz]),
+    "mlc_run_gather_kv_pages": (_i, [_vp, _vp, _u32p, _sz, _sz, _sz, _sz, _sz, _vp, _sz, _sz]),
+    "mlc_run_paged_flash_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p,
+                                           _sz, _sz, _sz, _sz, _sz, _i, _f, _i, _i, _sz]),
+    "mlc_encode_paged_flash_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p,
+                                              _sz, _sz, _sz, _sz, _sz, _i, _f, _i, _i, _sz]),
+}
+
+
+def load_library(build_if_missing: bool = False):
+    """Loads libmlc_b200.so. There is no fallback: a missing library is an error."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not path.exists():
+        if not build_if_missing:
+            raise ImportError(
+                f"{path} is missing: build the CUDA extension first "
+                "(python -m mlcompiler_b200.build, or __graft_entry__.build())")
+        from . import build as _build
+        _build.build()
+    lib = C.CDLL(str(path))
+    for name, (res, args) in _PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib
+
+
+def _ptr(x) -> int:
+    if x is None:
+        return 0
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    raise TypeError(f"not a device buffer: {type(x)}")
+
+
+def _u32(a):
+    arr = np.ascontiguousarray(np.asarray(a, dtype=np.uint32))
+    return arr, arr.ctypes.data_as(_u32p)
+
+
+class Executor:
+    """One context on one GPU; replaces MetalExecutor::Instance()."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._lib = load_library()
+        h = _vp()
+        st = self._lib.mlc_ctx_create(device, _vp(stream) if stream else None, C.byref(h))
+        if st != 0:
+            raise MlcError(st, "mlc_ctx_create failed (is a CUDA device present?)")
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.mlc_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- status ---------------------------------------------------------------
+    @property
+    def handle(self):
+        return self._h
+
+    def last_error(self) -> str:
+        return (self._lib.mlc_last_error(self._h) or b"").decode()
+
+    def status(self, st: int) -> bool:
+        """bool view of a status code, like the reference's bool returns."""
+        self.last_status = st
+        return st == 0
+
+    def check(self, st: int):
+        if st != 0:
+            raise MlcError(st, self.last_error())
+
+    def isAvailable(self) -> bool:
+        return bool(self._lib.mlc_ctx_available(self._h))
+
+    def deviceErrorWord(self) -> int:
+        w = C.c_uint32(0)
+        self.check(self._lib.mlc_device_error_word(self._h, C.byref(w)))
+        return w.value
+
+    def launchCount(self) -> int:
+        return int(self._lib.mlc_ctx_launch_count(self._h))
+
+    def stream(self) -> int:
+        return int(self._lib.mlc_ctx_stream(self._h) or 0)
+
+    def setAttentionKernel(self, which: int):
+        self.check(self._lib.mlc_ctx_set_attention_kernel(self._h, which))
+
+    # -- buffers (metal_runtime.hpp:693-703) --------------------------------------
+    def allocateScratchBuffer(self, nbytes: int) -> int:
+        return int(self._lib.mlc_alloc(self._h, nbytes) or 0)
+
+    def releaseScratchBuffer(self, buf: int):
+        self._lib.mlc_free(self._h, _vp(buf))
+
+    def uploadToBuffer(self, buf, src: np.ndarray, dst_offset: int = 0):
+        src = np.ascontiguousarray(src)
+        self.check(self._lib.mlc_upload(self._h, _vp(_ptr(buf)), src.ctypes.data_as(_vp), src.nbytes, dst_offset))
+
+    def downloadFromBuffer(self, buf, dst: np.ndarray, src_offset: int = 0):
+        assert dst.flags["C_CONTIGUOUS"]
+        self.check(self._lib.mlc_download(self._h, _vp(_ptr(buf)), dst.ctypes.data_as(_vp), dst.nbytes, src_offset))
+
+    def getOrAllocCachedBuffer(self, name: str, nbytes: int) -> int:
+        return int(self._lib.mlc_cached_buffer(self._h, name.encode(), nbytes) or 0)
+
+    def bufferBytes(self, buf) -> int:
+        return int(self._lib.mlc_buffer_bytes(self._h, _vp(_ptr(buf))))
+
+    # -- pass bracketing (metal_runtime.hpp:181-183) --------------------------------
+    def beginForwardPassCB(self) -> bool:
+        return self.status(self._lib.mlc_pass_begin(self._h))
+
+    def hasForwardPassCB(self) -> bool:
+        return bool(self._lib.mlc_pass_is_open(self._h))
+
+    def flushForwardPassCB(self) -> bool:
+        return self.status(self._lib.mlc_pass_flush(self._h))
+
+    # -- KV writers / readers ----------------------------------------------------------
+    def scatterKVPagedBatched(self, page_storage, page_ids, slots_in_page, page_size_tokens, n_kv_heads,
+                              head_dim, batch, src, capacity_pages: int = 0) -> bool:
+        ids, pids = _u32(page_ids)
+        sl, pslots = _u32(slots_in_page)
+        if ids.size != batch or sl.size != batch:  # metal_runtime.mm:7243
+            return self.status(1)
+        return self.status(self._lib.mlc_run_scatter_kv_paged_batched_f16(
+            self._h, _vp(_ptr(page_storage)), pids, pslots, page_size_tokens, n_kv_heads, head_dim, batch,
+            _vp(_ptr(src)), capacity_pages))
+
+    def encodeScatterKVPagedBatched(self, page_storage, page_ids, slots_in_page, page_size_tokens,
+                                    n_kv_heads, head_dim, batch, src, capacity_pages: int = 0) -> bool:
+        ids, pids = _u32(page_ids)
+        sl, pslots = _u32(slots_in_page)
+        if ids.size != batch or sl.size != batch:
+            return self.status(1)
+        return self.status(self._lib.mlc_encode_scatter_kv_paged_batched_f16(
+            self._h, _vp(_ptr(page_storage)), pids, pslots, page_size_tokens, n_kv_heads, head_dim, batch,
+            _vp(_ptr(src)), capacity_pages))
+
+    def encodeScatterKVPairPagedBatched(self, k_storage, v_storage, page_ids, slots_in_page,
+                                        page_size_tokens, n_kv_heads, head_dim, batch, k_src, v_src,
+                                        capacity_pages: int = 0) -> bool:
+        ids, pids = _u32(page_ids)
+        sl, pslots = _u32(slots_in_page)
+        if ids.size != batch or sl.size != batch:
+            return self.status(1)
+        return self.status(self._lib.mlc_encode_scatter_kv_pair_paged_batched_f16(
+            self._h, _vp(_ptr(k_storage)), _vp(_ptr(v_storage)), pids, pslots, page_size_tokens,
+            n_kv_heads, head_dim, batch, _vp(_ptr(k_src)), _vp(_ptr(v_src)), capacity_pages))
+
+    def scatterKVPaged(self, page_storage, page_table, page_size_tokens, n_kv_heads, head_dim, tokens,
+                       start_slot, src, dtype_bytes, capacity_pages: int = 0) -> bool:
+        pt, ppt = _u32(page_table)
+        return self.status(self._lib.mlc_run_scatter_kv_paged(
+            self._h, _vp(_ptr(page_storage)), ppt, pt.size, page_size_tokens, n_kv_heads, head_dim, tokens,
+            start_slot, _vp(_ptr(src)), dtype_bytes, capacity_pages))
+
+    def gatherKVPages(self, page_storage, page_table, page_size_tokens, n_kv_heads, head_dim, num_tokens,
+                      dst, dtype_bytes, capacity_pages: int = 0) -> bool:
+        pt, ppt = _u32(page_table)
+        return self.status(self._lib.mlc_run_gather_kv_pages(
+            self._h, _vp(_ptr(page_storage)), ppt, pt.size, page_size_tokens, n_kv_heads, head_dim,
+            num_tokens, _vp(_ptr(dst)), dtype_bytes, capacity_pages))
+
+    # -- attention ---------------------------------------------------------------------
+    def _attention(self, fn, q, k_pages, v_pages, o, page_tables_flat, page_table_offsets, seq_lens,
+                   q_positions, batch, num_heads, kv_heads, head_dim, page_size_tokens, apply_causal,
+                   scale, q_dtype, o_dtype, capacity_pages) -> bool:
+        flat, pflat = _u32(page_tables_flat)
+        off, poff = _u32(page_table_offsets)
+        sl, psl = _u32(seq_lens)
+        qp, pqp = _u32(q_positions)
+        # metal_runtime.mm:7746-7748: vector-size rules a raw-pointer ABI cannot see
+        if off.size != batch + 1 or sl.size != batch or qp.size != batch:
+            return self.status(1)
+        return self.status(fn(self._h, _vp(_ptr(q)), _vp(_ptr(k_pages)), _vp(_ptr(v_pages)), _vp(_ptr(o)),
+                              pflat, flat.size, poff, psl, pqp, batch, num_heads, kv_heads, head_dim,
+                              page_size_tokens, 1 if apply_causal else 0, float(scale), q_dtype, o_dtype,
+                              capacity_pages))
+
+    def runPagedFlashAttention(self, q, k_pages, v_pages, o, page_tables_flat, page_table_offsets, seq_lens,
+                               q_positions, batch, num_heads, kv_heads, head_dim, page_size_tokens,
+                               apply_causal, scale: float = 0.0, q_dtype: int = MLC_F32,
+                               o_dtype: int = MLC_F32, capacity_pages: int = 0) -> bool:
+        return self._attention(self._lib.mlc_run_paged_flash_attention, q, k_pages, v_pages, o,
+                               page_tables_flat, page_table_offsets, seq_lens, q_positions, batch, num_heads,
+                               kv_heads, head_dim, page_size_tokens, apply_causal, scale, q_dtype, o_dtype,
+                               capacity_pages)
+
+    def encodePagedFlashAttention(self, q, k_pages, v_pages, o, page_tables_flat, page_table_offsets,
+                                  seq_lens, q_positions, batch, num_heads, kv_heads, head_dim,
+                                  page_size_tokens, apply_causal, scale: float = 0.0,
+                                  q_dtype: int = MLC_F32, o_dtype: int = MLC_F32,
+                                  capacity_pages: int = 0) -> bool:
+        return self._attention(self._lib.mlc_encode_paged_flash_attention, q, k_pages, v_pages, o,
+                               page_tables_flat, page_table_offsets, seq_lens, q_positions, batch, num_heads,
+                               kv_heads, head_dim, page_size_tokens, apply_causal, scale, q_dtype, o_dtype,
+                               capacity_pages)

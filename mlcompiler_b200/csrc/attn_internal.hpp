@@ -1,0 +1,64 @@
+// Shared declarations of the attention entry points and their two kernel families.
+#pragma once
+
+#include "ctx.hpp"
+
+namespace mlcb {
+
+// One attention call after validation (host arrays already checked).
+struct AttnArgs {
+    const void* q = nullptr;
+    const void* k_pages = nullptr;
+    const void* v_pages = nullptr;
+    void* o = nullptr;
+    size_t batch = 0, H = 0, KVH = 0, D = 0, P = 0;
+    size_t capacity = 0;  // pages in the pool, 0 = unknown
+    float scale = 0.f;
+    int q_dtype = MLC_F32, o_dtype = MLC_F32;
+    // Split-KV partial output (un-normalised o + (m, l) per row) instead of O.
+    float* o_partial = nullptr;
+    float* ml_partial = nullptr;
+};
+
+// ---- work plan of the TMA / tensor-core kernel ----------------------------------
+// The kernel is persistent: CTA c owns a contiguous range of "tiles" in the order
+// (request, head block, tile), a tile being kTileTokens consecutive tokens of one
+// request for the kDecodeWarps KV heads of one head block. A maximal run of tiles
+// with the same (request, head block) inside a CTA's range is a piece.
+static constexpr int kDecodeWarps = 4;   // KV heads per head block = warps per CTA
+static constexpr int kTileTokens = 32;   // tokens per pipeline stage
+
+struct PieceDesc {
+    uint32_t req;
+    uint32_t tile_begin;      // first tile of the piece, in tiles from the request's token 0
+    uint32_t n_tiles;
+    uint32_t part_slot;       // workspace slot this piece writes when n_parts > 1
+    uint32_t seg_first_slot;  // first workspace slot of the (request, head block) segment
+    uint32_t seg;             // segment index: arrival counters seg*kDecodeWarps + warp
+    uint16_t n_parts;         // pieces the segment is split into (1: write O directly)
+    uint16_t hb;              // head block: KV heads hb*kDecodeWarps ...
+    uint16_t last_valid;      // valid tokens in the piece's last tile, 1..kTileTokens
+    uint16_t pad;
+};
+static_assert(sizeof(PieceDesc) == 32, "PieceDesc is read as two 16-byte vectors");
+
+struct DecodePlanView {            // device addresses inside one plan blob
+    const uint32_t* cta_counts;    // [n_cta][2] = {pieces, tiles}
+    const PieceDesc* pieces;       // [n_cta][max_pieces]
+    const uint32_t* tile_pages;    // [n_cta][max_tiles] page id of every tile
+    const uint32_t* pt_flat;       // copies of the caller's tables (general kernel, checks)
+    const uint32_t* pt_off;
+    const uint32_t* eff_len;       // tokens each request attends to
+    const uint32_t* zero_rows;     // requests with eff_len == 0 (their O rows are zero-filled)
+    uint32_t n_cta = 0, max_pieces = 0, max_tiles = 0, n_zero = 0;
+    uint32_t n_slots = 0, n_segs = 0;
+};
+
+int launch_attention_general(mlc_ctx* ctx, const AttnArgs& a, const uint32_t* d_pt_flat,
+                             const uint32_t* d_pt_off, const uint32_t* d_eff_len);
+
+// True when the TMA / tensor-core kernel covers this shape and these pointers.
+bool decode_tma_supported(const mlc_ctx* ctx, const AttnArgs& a);
+int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan);
+
+}  // namespace mlcb

@@ -1,0 +1,103 @@
+// Internal definition of the per-GPU context behind the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/mlc_b200.h"
+
+namespace mlcb {
+
+// Pinned-host + device staging area for the small u32 host arrays every call
+// carries (page tables, lengths, positions). Regions handed out between two
+// resets never overlap, so an async H2D copy can still be in flight while the
+// next call fills its own region.
+struct StageChunk {
+    uint8_t* host = nullptr;
+    uint8_t* dev = nullptr;
+    size_t cap = 0;
+    size_t used = 0;
+};
+
+struct AttnPlanCache;  // attn_api.cu
+struct TensorMapCache; // attn_decode_tma.cu
+
+}  // namespace mlcb
+
+struct mlc_ctx {
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    bool pass_open = false;
+    int sm_count = 0;
+    int force_general = 0;
+    uint64_t launches = 0;
+    std::string last_error;
+    std::unordered_map<const void*, size_t> allocs;
+    std::unordered_map<std::string, std::pair<void*, size_t>> cached;
+    std::vector<mlcb::StageChunk> stage;
+    uint32_t* d_err = nullptr;  // device error word
+    // split-KV workspace (partials + arrival counters), grown on demand
+    void* d_work = nullptr;
+    size_t work_bytes = 0;
+    uint32_t* d_counters = nullptr;
+    size_t n_counters = 0;
+    size_t decode_smem_set[4] = {0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
+    mlcb::AttnPlanCache* plan_cache = nullptr;
+    mlcb::TensorMapCache* tmap_cache = nullptr;
+
+    int fail(int status, const char* fmt, ...) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof(buf), fmt, ap);
+        va_end(ap);
+        last_error = buf;
+        return status;
+    }
+};
+
+namespace mlcb {
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+#define MLCB_CUDA(ctx, expr)                                                              \
+    do {                                                                                  \
+        cudaError_t _e = (expr);                                                          \
+        if (_e != cudaSuccess)                                                            \
+            return (ctx)->fail(MLC_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+// Copies `bytes` of host memory into the staging area and enqueues the H2D copy
+// on the context's stream; returns the device address (256-byte aligned) or null.
+void* stage_to_device(mlc_ctx* ctx, const void* host, size_t bytes);
+// Reserves a staging region and returns both addresses; the caller fills `*host`
+// and then calls stage_commit for the same region.
+bool stage_reserve(mlc_ctx* ctx, size_t bytes, void** host, void** dev);
+bool stage_commit(mlc_ctx* ctx, void* host, void* dev, size_t bytes);
+void stage_reset(mlc_ctx* ctx);
+// Grows the split-KV workspace / counters (synchronises when it has to reallocate).
+int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters);
+// Number of pages a pool pointer can hold given the caller's claim (0 = unknown)
+// and the context's own allocation registry.
+size_t resolve_capacity(const mlc_ctx* ctx, const void* pool, size_t claimed, size_t page_bytes);
+void destroy_plan_cache(mlc_ctx* ctx);
+void destroy_tmap_cache(mlc_ctx* ctx);
+
+}  // namespace mlcb

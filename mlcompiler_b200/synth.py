@@ -1,0 +1,127 @@
+"""Seeded synthetic workloads with the shapes of the benchmark configurations.
+
+The reference measures on no public dataset; these inputs stand in for its
+TinyLlama runs (tools/paged_flash_bench.cpp:29-34 uses the same head shape).
+Values are N(0,1) rounded once to fp16; the fp16 bit patterns are the ground
+truth for the CPU oracle and the GPU alike. Page tables are disjoint slices of
+one seeded permutation of the pool, so they are non-contiguous and unordered.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+SHAPE_A = dict(H=32, KVH=4, D=64)    # TinyLlama head shape
+SHAPE_B = dict(H=32, KVH=8, D=128)   # wider GQA shape
+
+
+@dataclass
+class PagedCase:
+    N: int
+    H: int
+    KVH: int
+    D: int
+    P: int
+    capacity: int
+    seq_lens: np.ndarray          # tokens per request AFTER the new token is written
+    pt_flat: np.ndarray
+    pt_off: np.ndarray
+    q_pos: np.ndarray
+    page_ids: np.ndarray          # where the step's new K/V row goes: (page, slot) per request
+    slots: np.ndarray
+    scale: float
+    q: np.ndarray | None = None       # float16 [N, H, D]
+    k_new: np.ndarray | None = None   # float16 [N, KVH, D]
+    v_new: np.ndarray | None = None
+    k_pool: np.ndarray | None = None  # float16 [capacity, P, KVH, D]
+    v_pool: np.ndarray | None = None
+    meta: dict = field(default_factory=dict)
+
+    @property
+    def kv_bytes(self) -> int:
+        """Algorithmic KV bytes one attention pass reads: sum_r 2*S_r*KVH*D*2."""
+        return int(self.seq_lens.astype(np.int64).sum()) * 2 * self.KVH * self.D * 2
+
+    def tokens_of(self, r: int, pool: np.ndarray) -> np.ndarray:
+        """De-paged rows [S_r, KVH, D] of request r in logical token order."""
+        S = int(self.seq_lens[r])
+        pages = self.pt_flat[self.pt_off[r]:self.pt_off[r + 1]]
+        rows = pool[pages].reshape(-1, self.KVH, self.D)
+        return rows[:S]
+
+
+def make_tables(seq_lens, P: int, rng: np.random.Generator, slack: float = 0.10, capacity: int | None = None):
+    seq_lens = np.asarray(seq_lens, dtype=np.uint32)
+    pages = (seq_lens.astype(np.int64) + P - 1) // P
+    total = int(pages.sum())
+    if capacity is None:
+        capacity = max(int(np.ceil(total * (1.0 + slack))), 1)
+    assert capacity >= total
+    perm = rng.permutation(capacity).astype(np.uint32)
+    pt_off = np.zeros(len(seq_lens) + 1, np.uint32)
+    pt_off[1:] = np.cumsum(pages)
+    pt_flat = perm[:total].copy()
+    return pt_flat, pt_off, capacity
+
+
+def make_case(seed: int, seq_lens, H: int, KVH: int, D: int, P: int = 64, capacity: int | None = None,
+              fill: bool = True, scale: float | None = None, q_pos=None) -> PagedCase:
+    rng = np.random.default_rng(seed)
+    seq_lens = np.asarray(seq_lens, dtype=np.uint32)
+    N = len(seq_lens)
+    pt_flat, pt_off, capacity = make_tables(seq_lens, P, rng, capacity=capacity)
+    page_ids = np.zeros(N, np.uint32)
+    slots = np.zeros(N, np.uint32)
+    for r in range(N):
+        S = int(seq_lens[r])
+        if S:
+            page_ids[r] = pt_flat[pt_off[r] + (S - 1) // P]
+            slots[r] = (S - 1) % P
+    if q_pos is None:
+        q_pos = np.where(seq_lens > 0, seq_lens - 1, 0).astype(np.uint32)
+    case = PagedCase(N=N, H=H, KVH=KVH, D=D, P=P, capacity=capacity, seq_lens=seq_lens, pt_flat=pt_flat,
+                     pt_off=pt_off, q_pos=np.asarray(q_pos, np.uint32), page_ids=page_ids, slots=slots,
+                     scale=float(scale if scale is not None else 1.0 / np.sqrt(np.float32(D))))
+    if fill:
+        case.q = rng.standard_normal((N, H, D), dtype=np.float32).astype(np.float16)
+        case.k_new = rng.standard_normal((N, KVH, D), dtype=np.float32).astype(np.float16)
+        case.v_new = rng.standard_normal((N, KVH, D), dtype=np.float32).astype(np.float16)
+        case.k_pool = rng.standard_normal((capacity, P, KVH, D), dtype=np.float32).astype(np.float16)
+        case.v_pool = rng.standard_normal((capacity, P, KVH, D), dtype=np.float32).astype(np.float16)
+    return case
+
+
+def config_lengths(config: int, seed: int | None = None) -> np.ndarray:
+    """Context lengths of the numbered benchmark configurations (1-based)."""
+    rng = np.random.default_rng(0xBEEF + config if seed is None else seed)
+    if config == 1:
+        return np.array([512], np.uint32)
+    if config == 2:
+        return rng.integers(64, 2048, size=32, endpoint=True).astype(np.uint32)
+    if config == 3:
+        return np.full(4, 32768, np.uint32)
+    if config == 4:
+        return rng.integers(512, 8192, size=128, endpoint=True).astype(np.uint32)
+    raise ValueError(config)
+
+
+def config_case(config: int, fill: bool = True, seed: int | None = None) -> PagedCase:
+    shape = SHAPE_B if config == 4 else SHAPE_A
+    lens = config_lengths(config, seed)
+    cap = 64 if config == 1 else None
+    return make_case(0xBEEF + config if seed is None else seed, lens, P=64, capacity=cap, fill=fill, **shape)
+
+
+def shard_requests_by_kv_bytes(seq_lens, n_shards: int) -> list[list[int]]:
+    """Greedy longest-first bin packing of requests onto shards by KV bytes."""
+    order = np.argsort(-np.asarray(seq_lens, dtype=np.int64), kind="stable")
+    load = [0] * n_shards
+    out: list[list[int]] = [[] for _ in range(n_shards)]
+    for r in order:
+        i = int(np.argmin(load))
+        out[i].append(int(r))
+        load[i] += int(seq_lens[r])
+    for lst in out:
+        lst.sort()
+    return out

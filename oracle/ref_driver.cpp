@@ -1,0 +1,227 @@
+// Harness around MLcompiler's own executor-CPU attention path.
+//
+// TEST INFRASTRUCTURE ONLY: linked into oracle/_ref/libref_attention.so by
+// build_ref.py together with the reference's unmodified sources. The product
+// library never links or loads this file.
+//
+// The harness builds the graph the reference's own unit test builds
+// (tests/test_runtime.cpp:1659-1719): one CPU `Attention` node with inputs
+// q / k_in / v_in, state tensors kv_k / kv_v of shape {KVH, ctx, D} and output
+// attn_out. The state tensors carry metadata role="kv_cache", which makes
+// ExecutionContext::ensureStateTensor store their rows as fp16
+// (compiler/runtime/execution_context.cpp:132-176). ModelConfig.rotary_dim
+// stays 0, so RunAttentionCPU applies no RoPE
+// (compiler/runtime/attention_cpu.cpp:352-363).
+//
+// One step = setSequencePosition(pos), set q/k_in/v_in, ExecutionExecutor::run()
+// -> CpuExecutionBackend::execute (operator_backend.cpp:887) -> RunAttentionCPU
+// (attention_cpu.cpp:272): the new K/V row is written at `pos` through the
+// reference's fp16 row writer, then every head attends over [0, pos].
+
+#include "runtime/attention_cpu.hpp"
+#include "runtime/execution_context.hpp"
+#include "runtime/execution_executor.hpp"
+#include "runtime/execution_graph.hpp"
+#include "runtime/operator_backend.hpp"
+#include "runtime/quant_utils.hpp"
+#include "runtime/session.hpp"
+#include "runtime/float_convert.hpp"
+#include "runtime/paged_kv.hpp"
+#include "runtime/scheduler.hpp"
+
+#include <unistd.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace {
+
+using namespace mlc::runtime;
+
+// Smallest file Session accepts: GGUF magic, version 1, one F32 [3,2] tensor.
+std::string writeTinyGGUF() {
+    static std::atomic<int> counter{0};
+    std::string path = "/tmp/mlc_b200_oracle_" + std::to_string(getpid()) + "_" +
+                       std::to_string(counter++) + ".gguf";
+    std::ofstream f(path, std::ios::binary);
+    auto u32 = [&](uint32_t v) { f.write(reinterpret_cast<const char*>(&v), 4); };
+    auto u64 = [&](uint64_t v) { f.write(reinterpret_cast<const char*>(&v), 8); };
+    auto str = [&](const std::string& s) { u64(s.size()); f.write(s.data(), s.size()); };
+    u32(0x46554747); u32(1); u64(1); u64(0);
+    str("linear.weight"); u32(2); u64(2); u32(3); u32(2); u32(0); u64(256);
+    f.seekp(256, std::ios::beg);
+    float w[6] = {1, 2, 3, 0, 1, 0.5f};
+    f.write(reinterpret_cast<const char*>(w), sizeof(w));
+    return path;
+}
+
+struct RefAttention {
+    size_t H, KVH, D, ctx;
+    std::string gguf_path;
+    std::unique_ptr<Session> session;
+    ExecutionGraph graph;
+    std::unique_ptr<ExecutionContext> context;
+    std::unique_ptr<ExecutionExecutor> executor;
+
+    RefAttention(size_t h, size_t kvh, size_t d, size_t c) : H(h), KVH(kvh), D(d), ctx(c) {
+        gguf_path = writeTinyGGUF();
+        session = std::make_unique<Session>(gguf_path);
+        graph.addTensor("q", {static_cast<int64_t>(H * D)}, mlc::ir::DataType::F32);
+        graph.addTensor("k_in", {static_cast<int64_t>(KVH * D)}, mlc::ir::DataType::F32);
+        graph.addTensor("v_in", {static_cast<int64_t>(KVH * D)}, mlc::ir::DataType::F32);
+        std::vector<int64_t> cache_shape{static_cast<int64_t>(KVH), static_cast<int64_t>(ctx),
+                                         static_cast<int64_t>(D)};
+        for (const char* name : {"kv_k", "kv_v"}) {
+            auto& t = graph.addTensor(name, cache_shape, mlc::ir::DataType::F32);
+            t.is_state = true;
+            t.metadata["role"] = "kv_cache";
+        }
+        graph.addTensor("attn_out", {static_cast<int64_t>(H * D)}, mlc::ir::DataType::F32);
+        auto& attn = graph.addNode("attention", ExecOpType::Attention, {"q", "k_in", "v_in"},
+                                   {"attn_out", "kv_k", "kv_v"}, BackendKind::CPU);
+        attn.attributes["heads"] = static_cast<float>(H);
+        attn.attributes["kv_heads"] = static_cast<float>(KVH);
+        attn.attributes["head_dim"] = static_cast<float>(D);
+        attn.annotations["kv_cache_k"] = "kv_k";
+        attn.annotations["kv_cache_v"] = "kv_v";
+        context = std::make_unique<ExecutionContext>(*session, &graph);
+        executor = std::make_unique<ExecutionExecutor>(graph, nullptr, context.get());
+    }
+    ~RefAttention() { ::unlink(gguf_path.c_str()); }
+};
+
+}  // namespace
+
+extern "C" {
+
+void* ref_attn_create(size_t heads, size_t kv_heads, size_t head_dim, size_t context_length) {
+    try {
+        return new RefAttention(heads, kv_heads, head_dim, context_length);
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ref_attn_create: %s\n", e.what());
+        return nullptr;
+    }
+}
+
+void ref_attn_destroy(void* h) { delete static_cast<RefAttention*>(h); }
+
+// Storage dtype the reference chose for the cache rows (1 == GGML F16 expected).
+int ref_attn_cache_dtype(void* h) {
+    auto* r = static_cast<RefAttention*>(h);
+    TensorStorage* s = r->context->tensorStorage("kv_k");
+    return s ? static_cast<int>(s->dtype) : -1;
+}
+
+// Pre-load `n` history rows, given token-major as fp32 [n][KVH][D], through the
+// reference's own row writer (quantizeRowFrom, quant_utils.cpp:120-131), into the
+// reference cache layout [KVH][ctx][D].
+int ref_attn_load_history(void* h, const float* k_hist, const float* v_hist, size_t n) {
+    auto* r = static_cast<RefAttention*>(h);
+    TensorStorage* ks = r->context->tensorStorage("kv_k");
+    TensorStorage* vs = r->context->tensorStorage("kv_v");
+    if (!ks || !vs || n > r->ctx) return -1;
+    for (size_t t = 0; t < n; ++t) {
+        for (size_t kv = 0; kv < r->KVH; ++kv) {
+            size_t row = kv * r->ctx + t;
+            const float* ksrc = k_hist + (t * r->KVH + kv) * r->D;
+            const float* vsrc = v_hist + (t * r->KVH + kv) * r->D;
+            quantizeRowFrom(ksrc, ks->dtype, r->D, ks->quant_version,
+                            ks->raw_data.data() + row * ks->row_stride_bytes);
+            quantizeRowFrom(vsrc, vs->dtype, r->D, vs->quant_version,
+                            vs->raw_data.data() + row * vs->row_stride_bytes);
+        }
+    }
+    return 0;
+}
+
+// One decode step through ExecutionExecutor::run(). q fp32 [H*D]; k_new / v_new
+// fp32 [KVH*D] are written at `position`; out fp32 [H*D].
+int ref_attn_decode(void* h, size_t position, const float* q, const float* k_new,
+                    const float* v_new, float* out) {
+    auto* r = static_cast<RefAttention*>(h);
+    r->context->setSequencePosition(position);
+    r->context->setTensor("q", std::vector<float>(q, q + r->H * r->D));
+    r->context->setTensor("k_in", std::vector<float>(k_new, k_new + r->KVH * r->D));
+    r->context->setTensor("v_in", std::vector<float>(v_new, v_new + r->KVH * r->D));
+    auto res = r->executor->run();
+    if (!res.success) return -1;
+    const auto* o = r->context->getTensor("attn_out");
+    if (!o || o->size() != r->H * r->D) return -2;
+    std::memcpy(out, o->data(), o->size() * sizeof(float));
+    return 0;
+}
+
+// Same step, calling RunAttentionCPU directly (no graph walk) - used for timing.
+int ref_attn_decode_direct(void* h, size_t position, const float* q, const float* k_new,
+                           const float* v_new, float* out) {
+    auto* r = static_cast<RefAttention*>(h);
+    r->context->setSequencePosition(position);
+    std::vector<float> qv(q, q + r->H * r->D), kv(k_new, k_new + r->KVH * r->D),
+        vv(v_new, v_new + r->KVH * r->D);
+    auto res = RunAttentionCPU(r->graph.nodes().front(), r->context.get(), qv, kv, vv);
+    if (!res.success) return -1;
+    const auto* o = r->context->getTensor("attn_out");
+    if (!o || o->size() != r->H * r->D) return -2;
+    std::memcpy(out, o->data(), o->size() * sizeof(float));
+    return 0;
+}
+
+// Raw fp16 bits of one cache row (kv_head, position) of K (which=0) or V (which=1).
+int ref_attn_read_cache_row(void* h, int which, size_t kv_head, size_t position, uint16_t* dst) {
+    auto* r = static_cast<RefAttention*>(h);
+    TensorStorage* s = r->context->tensorStorage(which == 0 ? "kv_k" : "kv_v");
+    if (!s || s->row_stride_bytes != r->D * 2) return -1;
+    size_t row = kv_head * r->ctx + position;
+    std::memcpy(dst, s->raw_data.data() + row * s->row_stride_bytes, r->D * 2);
+    return 0;
+}
+
+// fp16 <-> fp32 through the reference's scalar converters (float_convert.hpp:14-76).
+float ref_fp16_to_float(uint16_t h) { return fp16ToFloat(h); }
+uint16_t ref_float_to_fp16(float v) { return floatToFp16(v); }
+
+// ---- PagePool / RequestKVState (compiler/runtime/paged_kv.cpp:10-81) ----------
+void* ref_pool_create(uint32_t capacity) { return new PagePool(capacity); }
+void ref_pool_destroy(void* p) { delete static_cast<PagePool*>(p); }
+int ref_pool_allocate(void* p, uint32_t* id) {
+    auto r = static_cast<PagePool*>(p)->allocate();
+    if (!r) return 0;
+    *id = *r;
+    return 1;
+}
+void ref_pool_release(void* p, uint32_t id) { static_cast<PagePool*>(p)->release(id); }
+size_t ref_pool_in_use(void* p) { return static_cast<PagePool*>(p)->pages_in_use(); }
+size_t ref_pool_free(void* p) { return static_cast<PagePool*>(p)->pages_free(); }
+
+void* ref_kvstate_create(uint32_t page_size) {
+    auto* s = new RequestKVState();
+    s->page_size_tokens = page_size;
+    return s;
+}
+void ref_kvstate_destroy(void* s) { delete static_cast<RequestKVState*>(s); }
+int ref_kvstate_extend(void* s, void* pool, uint32_t* page, uint32_t* slot) {
+    auto r = static_cast<RequestKVState*>(s)->extend_one_token(*static_cast<PagePool*>(pool));
+    if (!r) return 0;
+    *page = r->first;
+    *slot = r->second;
+    return 1;
+}
+int ref_kvstate_reserve(void* s, void* pool, size_t tokens) {
+    return static_cast<RequestKVState*>(s)->reserve(*static_cast<PagePool*>(pool), tokens) ? 1 : 0;
+}
+size_t ref_kvstate_pages(void* s, uint32_t* out, size_t cap) {
+    auto* st = static_cast<RequestKVState*>(s);
+    for (size_t i = 0; i < st->page_table.size() && i < cap; ++i) out[i] = st->page_table[i];
+    return st->page_table.size();
+}
+size_t ref_kvstate_total(void* s) { return static_cast<RequestKVState*>(s)->total_tokens(); }
+void ref_kvstate_release(void* s, void* pool) {
+    static_cast<RequestKVState*>(s)->release_all(*static_cast<PagePool*>(pool));
+}
+
+}  // extern "C"
