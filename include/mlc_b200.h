@@ -179,6 +179,63 @@ int mlc_encode_paged_flash_attention(mlc_ctx* ctx, const void* q, const void* k_
  * 0 = automatic (TMA + tensor-core split-KV kernel when the shape allows it,
  * otherwise the general kernel), 1 = always the general kernel. Both are CUDA. */
 int mlc_ctx_set_attention_kernel(mlc_ctx* ctx, int which);
+/* Which family the most recent attention call used: 0 none yet, 1 general, 2 TMA. */
+int mlc_ctx_last_attention_kernel(const mlc_ctx* ctx);
+
+/* ---- device-resident plans --------------------------------------------------------
+ * The reference rebuilds and re-uploads page_tables_flat / offsets / seq_lens /
+ * q_positions for every layer of a pass although they are identical across layers
+ * (compiler/runtime/batched_walker.cpp:316-325, metal_runtime.mm:7092-7107). A plan
+ * holds one pass's tables - and, optionally, the (page, slot) each request's new
+ * K/V row goes to (batched_walker.cpp:127-142) - on the device, so the per-layer
+ * calls carry no host arrays. The host-array entry points above build and cache
+ * such plans internally. */
+typedef struct mlc_attn_plan mlc_attn_plan;
+int mlc_attn_plan_create(mlc_ctx* ctx, const uint32_t* page_tables_flat, size_t n_page_tables_flat,
+                         const uint32_t* page_table_offsets, const uint32_t* seq_lens,
+                         const uint32_t* q_positions, const uint32_t* page_ids /* may be NULL */,
+                         const uint32_t* slots_in_page /* may be NULL */, size_t batch,
+                         size_t num_heads, size_t kv_heads, size_t head_dim,
+                         size_t page_size_tokens, int apply_causal, size_t capacity_pages,
+                         mlc_attn_plan** out);
+void mlc_attn_plan_destroy(mlc_ctx* ctx, mlc_attn_plan* plan);
+/* encodePagedFlashAttention (metal_runtime.hpp:510-523) with the tables taken from `plan`. */
+int mlc_encode_paged_flash_attention_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
+                                             const void* k_pages, const void* v_pages, void* o,
+                                             float scale, int q_dtype, int o_dtype);
+/* The two encodeScatterKVPagedBatched calls of a layer (batched_walker.cpp:304-309) as
+ * one launch, page ids and slots taken from `plan`. */
+int mlc_encode_scatter_kv_pair_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, void* k_page_storage,
+                                       void* v_page_storage, const void* k_src, const void* v_src);
+
+/* ---- split-KV across GPUs (no counterpart in the reference: it has one device) -------
+ * A rank that holds only a slice of every request's pages computes, over its
+ * slice, the un-normalised state of the online softmax instead of O:
+ *   o_partial  fp32 [batch, num_heads, head_dim] = sum_s exp(score_s - m) V_s
+ *   ml_partial fp32 [batch, num_heads, 2]        = (m, l), m in natural-log units
+ * After the ranks' partials have been gathered (NCCL), mlc_encode_lse_combine
+ * merges `parts` of them laid out [parts, rows, head_dim] / [parts, rows, 2]:
+ *   m* = max_k m_k, w_k = exp(m_k - m*), O = sum_k o_k w_k / sum_k l_k w_k
+ * - between partials, the rule the reference kernel applies between tiles
+ * (metal_runtime.mm:2304-2329). */
+int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
+                                               const void* k_pages, const void* v_pages,
+                                               float* o_partial, float* ml_partial, float scale,
+                                               int q_dtype);
+int mlc_encode_lse_combine(mlc_ctx* ctx, const float* o_parts, const float* ml_parts, size_t parts,
+                           size_t rows, size_t head_dim, void* out, int o_dtype);
+
+/* ---- CUDA-graph bracketing of a pass --------------------------------------------------
+ * Records the planned encode_* calls issued between begin and end into a CUDA graph
+ * that replays them with one launch (the reference pays one command-buffer commit
+ * per pass, metal_runtime.mm:6030-6033). Only the *_planned entry points and
+ * mlc_encode_lse_combine may be called while capturing; run the same sequence once
+ * outside a capture first so that workspaces exist. */
+typedef struct mlc_graph mlc_graph;
+int mlc_graph_begin_capture(mlc_ctx* ctx);
+int mlc_graph_end_capture(mlc_ctx* ctx, mlc_graph** out);
+int mlc_graph_launch(mlc_ctx* ctx, mlc_graph* graph);
+void mlc_graph_destroy(mlc_ctx* ctx, mlc_graph* graph);
 
 #ifdef __cplusplus
 }

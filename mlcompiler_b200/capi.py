@@ -63,6 +63,18 @@ _PROTOTYPES = {
                                            _sz, _sz, _sz, _sz, _sz, _i, _f, _i, _i, _sz]),
     "mlc_encode_paged_flash_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p,
                                               _sz, _sz, _sz, _sz, _sz, _i, _f, _i, _i, _sz]),
+    "mlc_ctx_last_attention_kernel": (_i, [_vp]),
+    "mlc_attn_plan_create": (_i, [_vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p, _u32p, _sz, _sz, _sz, _sz, _sz,
+                                  _i, _sz, C.POINTER(_vp)]),
+    "mlc_attn_plan_destroy": (None, [_vp, _vp]),
+    "mlc_encode_paged_flash_attention_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
+    "mlc_encode_scatter_kv_pair_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "mlc_encode_paged_attention_partial_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i]),
+    "mlc_encode_lse_combine": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _i]),
+    "mlc_graph_begin_capture": (_i, [_vp]),
+    "mlc_graph_end_capture": (_i, [_vp, C.POINTER(_vp)]),
+    "mlc_graph_launch": (_i, [_vp, _vp]),
+    "mlc_graph_destroy": (None, [_vp, _vp]),
 }
 
 
@@ -271,3 +283,92 @@ class Executor:
                                page_tables_flat, page_table_offsets, seq_lens, q_positions, batch, num_heads,
                                kv_heads, head_dim, page_size_tokens, apply_causal, scale, q_dtype, o_dtype,
                                capacity_pages)
+
+    def lastAttentionKernel(self) -> int:
+        return int(self._lib.mlc_ctx_last_attention_kernel(self._h))
+
+    # -- device-resident plans -------------------------------------------------------
+    def createPlan(self, page_tables_flat, page_table_offsets, seq_lens, q_positions, batch, num_heads,
+                   kv_heads, head_dim, page_size_tokens, apply_causal=True, capacity_pages=0,
+                   page_ids=None, slots_in_page=None) -> "Plan":
+        flat, pflat = _u32(page_tables_flat)
+        off, poff = _u32(page_table_offsets)
+        sl, psl = _u32(seq_lens)
+        qp, pqp = _u32(q_positions)
+        if off.size != batch + 1 or sl.size != batch or qp.size != batch:
+            raise MlcError(1, "table sizes do not match batch")
+        pids = pslots = None
+        if page_ids is not None:
+            ids, pids = _u32(page_ids)
+            sls, pslots = _u32(slots_in_page)
+            if ids.size != batch or sls.size != batch:
+                raise MlcError(1, "page_ids / slots_in_page sizes do not match batch")
+        h = _vp()
+        self.check(self._lib.mlc_attn_plan_create(self._h, pflat, flat.size, poff, psl, pqp, pids, pslots, batch,
+                                                  num_heads, kv_heads, head_dim, page_size_tokens,
+                                                  1 if apply_causal else 0, capacity_pages, C.byref(h)))
+        return Plan(self, h)
+
+    def encodePagedFlashAttentionPlanned(self, plan, q, k_pages, v_pages, o, scale=0.0, q_dtype=MLC_F32,
+                                         o_dtype=MLC_F32) -> bool:
+        return self.status(self._lib.mlc_encode_paged_flash_attention_planned(
+            self._h, plan.handle, _vp(_ptr(q)), _vp(_ptr(k_pages)), _vp(_ptr(v_pages)), _vp(_ptr(o)),
+            float(scale), q_dtype, o_dtype))
+
+    def encodeScatterKVPairPlanned(self, plan, k_storage, v_storage, k_src, v_src) -> bool:
+        return self.status(self._lib.mlc_encode_scatter_kv_pair_planned(
+            self._h, plan.handle, _vp(_ptr(k_storage)), _vp(_ptr(v_storage)), _vp(_ptr(k_src)), _vp(_ptr(v_src))))
+
+    def encodePagedAttentionPartialPlanned(self, plan, q, k_pages, v_pages, o_partial, ml_partial, scale=0.0,
+                                           q_dtype=MLC_F32) -> bool:
+        return self.status(self._lib.mlc_encode_paged_attention_partial_planned(
+            self._h, plan.handle, _vp(_ptr(q)), _vp(_ptr(k_pages)), _vp(_ptr(v_pages)), _vp(_ptr(o_partial)),
+            _vp(_ptr(ml_partial)), float(scale), q_dtype))
+
+    def encodeLseCombine(self, o_parts, ml_parts, parts, rows, head_dim, out, o_dtype=MLC_F32) -> bool:
+        return self.status(self._lib.mlc_encode_lse_combine(
+            self._h, _vp(_ptr(o_parts)), _vp(_ptr(ml_parts)), parts, rows, head_dim, _vp(_ptr(out)), o_dtype))
+
+    # -- CUDA graphs -------------------------------------------------------------------
+    def beginCapture(self) -> bool:
+        return self.status(self._lib.mlc_graph_begin_capture(self._h))
+
+    def endCapture(self) -> "Graph":
+        h = _vp()
+        self.check(self._lib.mlc_graph_end_capture(self._h, C.byref(h)))
+        return Graph(self, h)
+
+
+class Plan:
+    def __init__(self, ex: Executor, handle):
+        self._ex, self.handle = ex, handle
+
+    def destroy(self):
+        if self.handle and self._ex._h:
+            self._ex._lib.mlc_attn_plan_destroy(self._ex._h, self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class Graph:
+    def __init__(self, ex: Executor, handle):
+        self._ex, self.handle = ex, handle
+
+    def launch(self):
+        self._ex.check(self._ex._lib.mlc_graph_launch(self._ex._h, self.handle))
+
+    def destroy(self):
+        if self.handle and self._ex._h:
+            self._ex._lib.mlc_graph_destroy(self._ex._h, self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass

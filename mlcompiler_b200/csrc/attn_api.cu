@@ -17,44 +17,53 @@
 
 namespace mlcb {
 
-namespace {
-
 struct PlanKey {
     size_t batch = 0, H = 0, KVH = 0, D = 0, P = 0, capacity = 0, n_flat = 0;
     int causal = 0;
-    bool tma = false;
     bool operator==(const PlanKey& o) const {
         return batch == o.batch && H == o.H && KVH == o.KVH && D == o.D && P == o.P &&
-               capacity == o.capacity && n_flat == o.n_flat && causal == o.causal && tma == o.tma;
+               capacity == o.capacity && n_flat == o.n_flat && causal == o.causal;
     }
 };
 
-struct PlanEntry {
-    PlanKey key;
+}  // namespace mlcb
+
+// A device-resident work plan for one set of page tables. Created explicitly by
+// mlc_attn_plan_create, or implicitly (and cached) by the entry points that take
+// host arrays.
+struct mlc_attn_plan {
+    mlcb::PlanKey key;
     std::vector<uint32_t> tables;  // pt_flat | pt_off | seq_lens | q_pos as passed by the caller
     uint8_t* host = nullptr;       // pinned image of the device blob
     uint8_t* dev = nullptr;
     size_t cap = 0;
     cudaEvent_t uploaded = nullptr;
-    DecodePlanView view;
+    mlcb::DecodePlanView view;
+    const uint32_t* d_page_ids = nullptr;  // this step's (page, slot) per request, when given
+    const uint32_t* d_slots = nullptr;
     uint64_t stamp = 0;
 };
 
-}  // namespace
+namespace mlcb {
 
 struct AttnPlanCache {
     static constexpr int kEntries = 4;
-    PlanEntry e[kEntries];
+    mlc_attn_plan e[kEntries];
     uint64_t clock = 0;
 };
 
+static void release_plan_buffers(mlc_attn_plan& p) {
+    if (p.host) cudaFreeHost(p.host);
+    if (p.dev) cudaFree(p.dev);
+    if (p.uploaded) cudaEventDestroy(p.uploaded);
+    p.host = p.dev = nullptr;
+    p.uploaded = nullptr;
+    p.cap = 0;
+}
+
 void destroy_plan_cache(mlc_ctx* ctx) {
     if (!ctx->plan_cache) return;
-    for (auto& p : ctx->plan_cache->e) {
-        if (p.host) cudaFreeHost(p.host);
-        if (p.dev) cudaFree(p.dev);
-        if (p.uploaded) cudaEventDestroy(p.uploaded);
-    }
+    for (auto& p : ctx->plan_cache->e) release_plan_buffers(p);
     delete ctx->plan_cache;
     ctx->plan_cache = nullptr;
 }
@@ -69,8 +78,11 @@ int env_int(const char* name, int dflt) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Builds the plan image for one set of tables into `p` and uploads it.
-int build_plan(mlc_ctx* ctx, PlanEntry& p, const uint32_t* pt_flat, const uint32_t* pt_off,
-               const uint32_t* seq_lens, const uint32_t* q_pos) {
+int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const uint32_t* pt_off,
+               const uint32_t* seq_lens, const uint32_t* q_pos, const uint32_t* page_ids,
+               const uint32_t* slots) {
+    if (ctx->capturing)
+        return ctx->fail(MLC_ERR_UNSUPPORTED, "new page tables inside a graph capture: create the plan before capturing");
     const PlanKey& k = p.key;
     const size_t N = k.batch;
     std::vector<uint32_t> eff(N), zero_rows;
@@ -82,11 +94,11 @@ int build_plan(mlc_ctx* ctx, PlanEntry& p, const uint32_t* pt_flat, const uint32
         if (S == 0) zero_rows.push_back(static_cast<uint32_t>(r));
     }
 
-    std::vector<uint32_t> counts;
     std::vector<std::vector<PieceDesc>> cta_pieces;
     std::vector<std::vector<uint32_t>> cta_tiles;
     uint32_t n_cta = 0, max_pieces = 1, max_tiles = 1, n_slots = 0, n_segs = 0;
-    if (k.tma) {
+    const bool tma = decode_tma_shape_supported(k.H, k.KVH, k.D, k.P, k.capacity);
+    if (tma) {
         const uint32_t TOK = kTileTokens;
         const uint32_t n_hb = static_cast<uint32_t>((k.KVH + kDecodeWarps - 1) / kDecodeWarps);
         uint64_t total = 0;
@@ -158,6 +170,8 @@ int build_plan(mlc_ctx* ctx, PlanEntry& p, const uint32_t* pt_flat, const uint32
     const size_t off_ptoff = off;    off = align_up(off + (N + 1) * 4, 16);
     const size_t off_eff = off;      off = align_up(off + N * 4, 16);
     const size_t off_zero = off;     off = align_up(off + zero_rows.size() * 4, 16);
+    const size_t off_ids = off;      off = align_up(off + (page_ids ? N * 4 : 0), 16);
+    const size_t off_slots = off;    off = align_up(off + (slots ? N * 4 : 0), 16);
     const size_t bytes = std::max<size_t>(off, 16);
 
     if (p.uploaded) MLCB_CUDA(ctx, cudaEventSynchronize(p.uploaded));
@@ -185,10 +199,12 @@ int build_plan(mlc_ctx* ctx, PlanEntry& p, const uint32_t* pt_flat, const uint32
         std::copy(cta_pieces[i].begin(), cta_pieces[i].end(), pieces_h + size_t(i) * max_pieces);
         std::copy(cta_tiles[i].begin(), cta_tiles[i].end(), tiles_h + size_t(i) * max_tiles);
     }
-    std::memcpy(p.host + off_flat, pt_flat, k.n_flat * 4);
+    if (k.n_flat) std::memcpy(p.host + off_flat, pt_flat, k.n_flat * 4);
     std::memcpy(p.host + off_ptoff, pt_off, (N + 1) * 4);
     std::memcpy(p.host + off_eff, eff.data(), N * 4);
     if (!zero_rows.empty()) std::memcpy(p.host + off_zero, zero_rows.data(), zero_rows.size() * 4);
+    if (page_ids) std::memcpy(p.host + off_ids, page_ids, N * 4);
+    if (slots) std::memcpy(p.host + off_slots, slots, N * 4);
     MLCB_CUDA(ctx, cudaMemcpyAsync(p.dev, p.host, bytes, cudaMemcpyHostToDevice, ctx->stream));
     MLCB_CUDA(ctx, cudaEventRecord(p.uploaded, ctx->stream));
 
@@ -200,104 +216,125 @@ int build_plan(mlc_ctx* ctx, PlanEntry& p, const uint32_t* pt_flat, const uint32
     v.pt_off = reinterpret_cast<const uint32_t*>(p.dev + off_ptoff);
     v.eff_len = reinterpret_cast<const uint32_t*>(p.dev + off_eff);
     v.zero_rows = reinterpret_cast<const uint32_t*>(p.dev + off_zero);
+    v.has_tma = tma;
     v.n_cta = n_cta;
     v.max_pieces = max_pieces;
     v.max_tiles = max_tiles;
     v.n_zero = static_cast<uint32_t>(zero_rows.size());
     v.n_slots = n_slots;
     v.n_segs = n_segs;
+    p.d_page_ids = page_ids ? reinterpret_cast<const uint32_t*>(p.dev + off_ids) : nullptr;
+    p.d_slots = slots ? reinterpret_cast<const uint32_t*>(p.dev + off_slots) : nullptr;
     return MLC_OK;
 }
 
-int get_plan(mlc_ctx* ctx, const PlanKey& key, const uint32_t* pt_flat, const uint32_t* pt_off,
-             const uint32_t* seq_lens, const uint32_t* q_pos, const DecodePlanView** out) {
+// Argument rules shared by every entry point that takes the host tables.
+int validate_tables(mlc_ctx* ctx, PlanKey& key, const void* k_pages, const uint32_t* pt_flat, size_t n_flat,
+                    const uint32_t* pt_off, const uint32_t* seq_lens, const uint32_t* q_pos,
+                    size_t capacity_pages) {
+    // metal_runtime.mm:7742-7750
+    if (key.batch == 0 || key.H == 0 || key.D == 0 || key.P == 0) return ctx->fail(MLC_ERR_INVALID_ARG, "zero dimension");
+    if (key.KVH == 0 || key.H % key.KVH != 0) return ctx->fail(MLC_ERR_INVALID_ARG, "num_heads must be a multiple of kv_heads");
+    if (!pt_off || !seq_lens || !q_pos || (!pt_flat && n_flat)) return ctx->fail(MLC_ERR_INVALID_ARG, "null table");
+    if (n_flat < pt_off[key.batch]) return ctx->fail(MLC_ERR_INVALID_ARG, "page_tables_flat shorter than the last offset");
+    if (key.D > 256) return ctx->fail(MLC_ERR_UNSUPPORTED, "head_dim > 256");
+    if (key.batch * key.H >= (size_t(1) << 31)) return ctx->fail(MLC_ERR_UNSUPPORTED, "batch * heads too large");
+    // checks the reference does not make
+    key.capacity = resolve_capacity(ctx, k_pages, capacity_pages, key.P * key.KVH * key.D * 2);
+    key.n_flat = pt_off[key.batch];
+    for (size_t r = 0; r < key.batch; ++r) {
+        if (pt_off[r + 1] < pt_off[r]) return ctx->fail(MLC_ERR_BOUNDS, "page_table_offsets not monotone at %zu", r);
+        uint64_t room = static_cast<uint64_t>(pt_off[r + 1] - pt_off[r]) * key.P;
+        if (seq_lens[r] > room)
+            return ctx->fail(MLC_ERR_BOUNDS, "seq_lens[%zu]=%u exceeds its %u pages", r, seq_lens[r], pt_off[r + 1] - pt_off[r]);
+    }
+    if (key.capacity)
+        for (size_t i = 0; i < key.n_flat; ++i)
+            if (pt_flat[i] >= key.capacity)
+                return ctx->fail(MLC_ERR_BOUNDS, "page_tables_flat[%zu]=%u >= capacity %zu", i, pt_flat[i], key.capacity);
+    return MLC_OK;
+}
+
+int get_cached_plan(mlc_ctx* ctx, const PlanKey& key, const uint32_t* pt_flat, const uint32_t* pt_off,
+                    const uint32_t* seq_lens, const uint32_t* q_pos, mlc_attn_plan** out) {
     if (!ctx->plan_cache) ctx->plan_cache = new AttnPlanCache();
     AttnPlanCache& pc = *ctx->plan_cache;
     const size_t N = key.batch;
     const size_t words = key.n_flat + (N + 1) + N + N;
-    PlanEntry* victim = &pc.e[0];
+    mlc_attn_plan* victim = &pc.e[0];
     for (auto& p : pc.e) {
         if (p.stamp && p.key == key && p.tables.size() == words) {
             const uint32_t* t = p.tables.data();
-            if (!std::memcmp(t, pt_flat, key.n_flat * 4) &&
+            if ((key.n_flat == 0 || !std::memcmp(t, pt_flat, key.n_flat * 4)) &&
                 !std::memcmp(t + key.n_flat, pt_off, (N + 1) * 4) &&
                 !std::memcmp(t + key.n_flat + N + 1, seq_lens, N * 4) &&
                 !std::memcmp(t + key.n_flat + 2 * N + 1, q_pos, N * 4)) {
                 p.stamp = ++pc.clock;
-                *out = &p.view;
+                *out = &p;
                 return MLC_OK;
             }
         }
         if (p.stamp < victim->stamp) victim = &p;
     }
-    PlanEntry& p = *victim;
+    mlc_attn_plan& p = *victim;
     p.key = key;
     p.tables.resize(words);
-    std::memcpy(p.tables.data(), pt_flat, key.n_flat * 4);
+    if (key.n_flat) std::memcpy(p.tables.data(), pt_flat, key.n_flat * 4);
     std::memcpy(p.tables.data() + key.n_flat, pt_off, (N + 1) * 4);
     std::memcpy(p.tables.data() + key.n_flat + N + 1, seq_lens, N * 4);
     std::memcpy(p.tables.data() + key.n_flat + 2 * N + 1, q_pos, N * 4);
     p.stamp = 0;
-    int st = build_plan(ctx, p, pt_flat, pt_off, seq_lens, q_pos);
+    int st = build_plan(ctx, p, pt_flat, pt_off, seq_lens, q_pos, nullptr, nullptr);
     if (st != MLC_OK) return st;
     p.stamp = ++pc.clock;
-    *out = &p.view;
+    *out = &p;
     return MLC_OK;
+}
+
+int finish_sync(mlc_ctx* ctx, const char* what) {
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return ctx->fail(MLC_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+    uint32_t word = 0;
+    MLCB_CUDA(ctx, cudaMemcpy(&word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
+    if (word) {
+        cudaMemset(ctx->d_err, 0, 4);
+        return ctx->fail(MLC_ERR_DEVICE_FLAG, "%s recorded error word 0x%x", what, word);
+    }
+    return MLC_OK;
+}
+
+// Launches attention for a validated call through `plan`.
+int launch_with_plan(mlc_ctx* ctx, AttnArgs a, const mlc_attn_plan& plan) {
+    const PlanKey& k = plan.key;
+    if (!a.q || !a.k_pages || !a.v_pages || (!a.o && !a.o_partial)) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    if ((a.q_dtype != MLC_F32 && a.q_dtype != MLC_F16) || (a.o_dtype != MLC_F32 && a.o_dtype != MLC_F16))
+        return ctx->fail(MLC_ERR_INVALID_ARG, "dtype must be MLC_F32 or MLC_F16");
+    if (a.o_partial && !a.ml_partial) return ctx->fail(MLC_ERR_INVALID_ARG, "partial output needs both buffers");
+    a.batch = k.batch; a.H = k.H; a.KVH = k.KVH; a.D = k.D; a.P = k.P; a.capacity = k.capacity;
+    if (a.scale <= 0.f) a.scale = 1.0f / std::sqrt(static_cast<float>(a.D));  // mm:7133
+    if (plan.view.has_tma && !ctx->force_general && decode_tma_pointers_supported(a)) {
+        ctx->last_attention_kernel = 2;
+        return launch_attention_decode_tma(ctx, a, plan.view);
+    }
+    ctx->last_attention_kernel = 1;
+    return launch_attention_general(ctx, a, plan.view.pt_flat, plan.view.pt_off, plan.view.eff_len);
 }
 
 int attention_impl(mlc_ctx* ctx, bool sync, AttnArgs a, const uint32_t* pt_flat, size_t n_flat,
                    const uint32_t* pt_off, const uint32_t* seq_lens, const uint32_t* q_pos,
                    int causal, size_t capacity_pages) {
     if (!ctx) return MLC_ERR_INVALID_ARG;
-    // metal_runtime.mm:7742-7750
-    if (!a.q || !a.k_pages || !a.v_pages || (!a.o && !a.o_partial))
-        return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
-    if (a.batch == 0 || a.H == 0 || a.D == 0 || a.P == 0) return ctx->fail(MLC_ERR_INVALID_ARG, "zero dimension");
-    if (a.KVH == 0 || a.H % a.KVH != 0) return ctx->fail(MLC_ERR_INVALID_ARG, "num_heads must be a multiple of kv_heads");
-    if (!pt_off || !seq_lens || !q_pos || (!pt_flat && n_flat)) return ctx->fail(MLC_ERR_INVALID_ARG, "null table");
-    if (n_flat < pt_off[a.batch]) return ctx->fail(MLC_ERR_INVALID_ARG, "page_tables_flat shorter than the last offset");
-    if (a.D > 256) return ctx->fail(MLC_ERR_UNSUPPORTED, "head_dim > 256");
-    if ((a.q_dtype != MLC_F32 && a.q_dtype != MLC_F16) || (a.o_dtype != MLC_F32 && a.o_dtype != MLC_F16))
-        return ctx->fail(MLC_ERR_INVALID_ARG, "dtype must be MLC_F32 or MLC_F16");
-    if (!sync && !ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
-    if (a.batch * a.H >= (size_t(1) << 31)) return ctx->fail(MLC_ERR_UNSUPPORTED, "batch * heads too large");
-    // checks the reference does not make
-    a.capacity = resolve_capacity(ctx, a.k_pages, capacity_pages, a.P * a.KVH * a.D * 2);
-    for (size_t r = 0; r < a.batch; ++r) {
-        if (pt_off[r + 1] < pt_off[r]) return ctx->fail(MLC_ERR_BOUNDS, "page_table_offsets not monotone at %zu", r);
-        uint64_t room = static_cast<uint64_t>(pt_off[r + 1] - pt_off[r]) * a.P;
-        if (seq_lens[r] > room)
-            return ctx->fail(MLC_ERR_BOUNDS, "seq_lens[%zu]=%u exceeds its %u pages", r, seq_lens[r], pt_off[r + 1] - pt_off[r]);
-    }
-    if (a.capacity)
-        for (size_t i = 0; i < pt_off[a.batch]; ++i)
-            if (pt_flat[i] >= a.capacity)
-                return ctx->fail(MLC_ERR_BOUNDS, "page_tables_flat[%zu]=%u >= capacity %zu", i, pt_flat[i], a.capacity);
-    if (a.scale <= 0.f) a.scale = 1.0f / std::sqrt(static_cast<float>(a.D));  // mm:7133
-
-    DeviceGuard guard(ctx->device);
+    if (!a.q || !a.k_pages || !a.v_pages || (!a.o && !a.o_partial)) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
     PlanKey key;
-    key.batch = a.batch; key.H = a.H; key.KVH = a.KVH; key.D = a.D; key.P = a.P;
-    key.capacity = a.capacity; key.n_flat = pt_off[a.batch]; key.causal = causal ? 1 : 0;
-    key.tma = !ctx->force_general && decode_tma_supported(ctx, a);
-    const DecodePlanView* plan = nullptr;
-    int st = get_plan(ctx, key, pt_flat, pt_off, seq_lens, q_pos, &plan);
+    key.batch = a.batch; key.H = a.H; key.KVH = a.KVH; key.D = a.D; key.P = a.P; key.causal = causal ? 1 : 0;
+    int st = validate_tables(ctx, key, a.k_pages, pt_flat, n_flat, pt_off, seq_lens, q_pos, capacity_pages);
     if (st != MLC_OK) return st;
-    if (key.tma) st = launch_attention_decode_tma(ctx, a, *plan);
-    else if (a.o_partial) return ctx->fail(MLC_ERR_UNSUPPORTED, "partial output needs the split-KV kernel's shapes");
-    else st = launch_attention_general(ctx, a, plan->pt_flat, plan->pt_off, plan->eff_len);
-    if (st != MLC_OK) return st;
-    if (sync) {
-        cudaError_t e = cudaStreamSynchronize(ctx->stream);
-        if (e != cudaSuccess) return ctx->fail(MLC_ERR_CUDA, "attention failed: %s", cudaGetErrorString(e));
-        uint32_t word = 0;
-        MLCB_CUDA(ctx, cudaMemcpy(&word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
-        if (word) {
-            cudaMemset(ctx->d_err, 0, 4);
-            return ctx->fail(MLC_ERR_DEVICE_FLAG, "attention kernel recorded error word 0x%x", word);
-        }
-    }
-    return MLC_OK;
+    if (!sync && !ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    DeviceGuard guard(ctx->device);
+    mlc_attn_plan* plan = nullptr;
+    if ((st = get_cached_plan(ctx, key, pt_flat, pt_off, seq_lens, q_pos, &plan)) != MLC_OK) return st;
+    if ((st = launch_with_plan(ctx, a, *plan)) != MLC_OK) return st;
+    return sync ? finish_sync(ctx, "attention") : MLC_OK;
 }
 
 }  // namespace
@@ -336,6 +373,90 @@ int mlc_encode_paged_flash_attention(mlc_ctx* ctx, const void* q, const void* k_
     a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
     return attention_impl(ctx, false, a, page_tables_flat, n_page_tables_flat, page_table_offsets,
                           seq_lens, q_positions, apply_causal, capacity_pages);
+}
+
+int mlc_ctx_last_attention_kernel(const mlc_ctx* ctx) { return ctx ? ctx->last_attention_kernel : 0; }
+
+int mlc_attn_plan_create(mlc_ctx* ctx, const uint32_t* page_tables_flat, size_t n_page_tables_flat,
+                         const uint32_t* page_table_offsets, const uint32_t* seq_lens,
+                         const uint32_t* q_positions, const uint32_t* page_ids,
+                         const uint32_t* slots_in_page, size_t batch, size_t num_heads,
+                         size_t kv_heads, size_t head_dim, size_t page_size_tokens, int apply_causal,
+                         size_t capacity_pages, mlc_attn_plan** out) {
+    if (!ctx || !out) return MLC_ERR_INVALID_ARG;
+    *out = nullptr;
+    if ((page_ids == nullptr) != (slots_in_page == nullptr)) return ctx->fail(MLC_ERR_INVALID_ARG, "page_ids and slots_in_page go together");
+    PlanKey key;
+    key.batch = batch; key.H = num_heads; key.KVH = kv_heads; key.D = head_dim; key.P = page_size_tokens;
+    key.causal = apply_causal ? 1 : 0;
+    int st = validate_tables(ctx, key, nullptr, page_tables_flat, n_page_tables_flat, page_table_offsets,
+                             seq_lens, q_positions, capacity_pages);
+    if (st != MLC_OK) return st;
+    if (page_ids)
+        for (size_t r = 0; r < batch; ++r) {
+            if (key.capacity && page_ids[r] >= key.capacity)
+                return ctx->fail(MLC_ERR_BOUNDS, "page_ids[%zu]=%u >= capacity %zu", r, page_ids[r], key.capacity);
+            if (slots_in_page[r] >= page_size_tokens)
+                return ctx->fail(MLC_ERR_BOUNDS, "slots_in_page[%zu]=%u >= page size", r, slots_in_page[r]);
+        }
+    DeviceGuard guard(ctx->device);
+    auto* p = new mlc_attn_plan();
+    p->key = key;
+    st = build_plan(ctx, *p, page_tables_flat, page_table_offsets, seq_lens, q_positions, page_ids, slots_in_page);
+    if (st != MLC_OK) {
+        release_plan_buffers(*p);
+        delete p;
+        return st;
+    }
+    *out = p;
+    return MLC_OK;
+}
+
+void mlc_attn_plan_destroy(mlc_ctx* ctx, mlc_attn_plan* plan) {
+    if (!ctx || !plan) return;
+    DeviceGuard guard(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    release_plan_buffers(*plan);
+    delete plan;
+}
+
+int mlc_encode_paged_flash_attention_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
+                                             const void* k_pages, const void* v_pages, void* o,
+                                             float scale, int q_dtype, int o_dtype) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    DeviceGuard guard(ctx->device);
+    AttnArgs a;
+    a.q = q; a.k_pages = k_pages; a.v_pages = v_pages; a.o = o;
+    a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
+    return launch_with_plan(ctx, a, *plan);
+}
+
+int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
+                                               const void* k_pages, const void* v_pages,
+                                               float* o_partial, float* ml_partial, float scale,
+                                               int q_dtype) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (!o_partial || !ml_partial) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    DeviceGuard guard(ctx->device);
+    AttnArgs a;
+    a.q = q; a.k_pages = k_pages; a.v_pages = v_pages;
+    a.o_partial = o_partial; a.ml_partial = ml_partial;
+    a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = MLC_F32;
+    return launch_with_plan(ctx, a, *plan);
+}
+
+int mlc_encode_scatter_kv_pair_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, void* k_page_storage,
+                                       void* v_page_storage, const void* k_src, const void* v_src) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (!plan->d_page_ids) return ctx->fail(MLC_ERR_INVALID_ARG, "the plan was created without page_ids / slots_in_page");
+    if (!k_page_storage || !v_page_storage || !k_src || !v_src) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    DeviceGuard guard(ctx->device);
+    const PlanKey& k = plan->key;
+    return launch_scatter_rows_device_tables(ctx, k_page_storage, v_page_storage, plan->d_page_ids,
+                                             plan->d_slots, k.P, k.KVH, k.D, k.batch, k_src, v_src, k.capacity);
 }
 
 }  // extern "C"

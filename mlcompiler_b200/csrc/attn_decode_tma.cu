@@ -555,13 +555,16 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 // ------------------------------------------------------------------------------
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-bool decode_tma_supported(const mlc_ctx* ctx, const AttnArgs& a) {
-    (void)ctx;
-    if (a.D != 64 && a.D != 128) return false;
-    if (a.P % kTileTokens != 0 || a.P / kTileTokens > 8) return false;
-    if (a.H / a.KVH > 16) return false;
-    if ((a.KVH + kDecodeWarps - 1) / kDecodeWarps > 16) return false;
-    if (a.capacity == 0 || a.capacity > (size_t(1) << 25)) return false;
+bool decode_tma_shape_supported(size_t H, size_t KVH, size_t D, size_t P, size_t capacity) {
+    if (D != 64 && D != 128) return false;
+    if (P % kTileTokens != 0 || P / kTileTokens > 8) return false;
+    if (KVH == 0 || H / KVH > 16) return false;
+    if ((KVH + kDecodeWarps - 1) / kDecodeWarps > 16) return false;
+    if (capacity == 0 || capacity > (size_t(1) << 25)) return false;
+    return true;
+}
+
+bool decode_tma_pointers_supported(const AttnArgs& a) {
     if (!aligned(a.k_pages, 16) || !aligned(a.v_pages, 16)) return false;
     if (!aligned(a.q, a.q_dtype == MLC_F32 ? 8 : 4)) return false;
     if (a.o && !aligned(a.o, a.o_dtype == MLC_F32 ? 8 : 4)) return false;

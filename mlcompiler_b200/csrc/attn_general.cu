@@ -37,7 +37,8 @@ paged_attention_general_kernel(const QT* __restrict__ q, const __half* __restric
                                const uint32_t* __restrict__ pt_off,
                                const uint32_t* __restrict__ eff_len,  // tokens each request attends to
                                uint32_t H, uint32_t KVH, uint32_t D, uint32_t P, float scale,
-                               uint32_t capacity, uint32_t* __restrict__ err) {
+                               uint32_t capacity, uint32_t* __restrict__ err,
+                               float* __restrict__ o_partial, float* __restrict__ ml_partial) {
     const uint32_t req = blockIdx.x / H, head = blockIdx.x % H;
     const uint32_t kv_h = static_cast<uint32_t>((static_cast<uint64_t>(head) * KVH) / H);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,10 +101,18 @@ paged_attention_general_kernel(const QT* __restrict__ q, const __half* __restric
         lsum += s_l[w] * wgt[w];
     }
     float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
+    if (o_partial && threadIdx.x == 0) {  // split-KV partial: un-normalised o plus (m, l)
+        ml_partial[(static_cast<size_t>(req) * H + head) * 2] = mstar;
+        ml_partial[(static_cast<size_t>(req) * H + head) * 2 + 1] = lsum;
+    }
     for (uint32_t d = threadIdx.x; d < D; d += blockDim.x) {
         float v = 0.0f;
 #pragma unroll
         for (int w = 0; w < kGenWarps; ++w) v += s_o[w][d] * wgt[w];
+        if (o_partial) {
+            o_partial[row + d] = v;
+            continue;
+        }
         v *= inv;
         if constexpr (sizeof(OT) == 4) o[row + d] = v;
         else o[row + d] = __float2half_rn(v);
@@ -120,7 +129,7 @@ int launch_attention_general(mlc_ctx* ctx, const AttnArgs& a, const uint32_t* d_
     paged_attention_general_kernel<QT, OT><<<grid, block, 0, ctx->stream>>>(                       \
         static_cast<const QT*>(a.q), kp, vp, static_cast<OT*>(a.o), d_pt_flat, d_pt_off, d_eff_len, \
         static_cast<uint32_t>(a.H), static_cast<uint32_t>(a.KVH), static_cast<uint32_t>(a.D),       \
-        static_cast<uint32_t>(a.P), a.scale, cap32, ctx->d_err)
+        static_cast<uint32_t>(a.P), a.scale, cap32, ctx->d_err, a.o_partial, a.ml_partial)
     if (a.q_dtype == MLC_F32 && a.o_dtype == MLC_F32) MLCB_GEN_LAUNCH(float, float);
     else if (a.q_dtype == MLC_F32) MLCB_GEN_LAUNCH(float, __half);
     else if (a.o_dtype == MLC_F32) MLCB_GEN_LAUNCH(__half, float);

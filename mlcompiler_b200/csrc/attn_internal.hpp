@@ -50,6 +50,7 @@ struct DecodePlanView {            // device addresses inside one plan blob
     const uint32_t* pt_off;
     const uint32_t* eff_len;       // tokens each request attends to
     const uint32_t* zero_rows;     // requests with eff_len == 0 (their O rows are zero-filled)
+    bool has_tma = false;          // the per-CTA tile lists above were built
     uint32_t n_cta = 0, max_pieces = 0, max_tiles = 0, n_zero = 0;
     uint32_t n_slots = 0, n_segs = 0;
 };
@@ -57,8 +58,13 @@ struct DecodePlanView {            // device addresses inside one plan blob
 int launch_attention_general(mlc_ctx* ctx, const AttnArgs& a, const uint32_t* d_pt_flat,
                              const uint32_t* d_pt_off, const uint32_t* d_eff_len);
 
-// True when the TMA / tensor-core kernel covers this shape and these pointers.
-bool decode_tma_supported(const mlc_ctx* ctx, const AttnArgs& a);
+// True when the TMA / tensor-core kernel covers this shape / these pointers.
+bool decode_tma_shape_supported(size_t H, size_t KVH, size_t D, size_t P, size_t capacity);
+bool decode_tma_pointers_supported(const AttnArgs& a);
+// One launch writing this step's K and V rows; page ids and slots already on the device.
+int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, const uint32_t* d_ids,
+                                      const uint32_t* d_slots, size_t P, size_t KVH, size_t D,
+                                      size_t batch, const void* k_src, const void* v_src, size_t capacity);
 int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan);
 
 }  // namespace mlcb

@@ -66,6 +66,8 @@ void stage_reset(mlc_ctx* ctx) {
 }
 
 int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters) {
+    if ((bytes > ctx->work_bytes || counters > ctx->n_counters) && ctx->capturing)
+        return ctx->fail(MLC_ERR_UNSUPPORTED, "workspace must grow: run the step once outside the capture first");
     if (bytes > ctx->work_bytes) {
         MLCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         if (ctx->d_work) cudaFree(ctx->d_work);

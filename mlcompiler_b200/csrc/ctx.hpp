@@ -35,8 +35,11 @@ struct mlc_ctx {
     cudaStream_t stream = nullptr;
     bool own_stream = false;
     bool pass_open = false;
+    bool capturing = false;          // between mlc_graph_begin_capture and mlc_graph_end_capture
+    uint64_t launches_at_capture = 0;
     int sm_count = 0;
     int force_general = 0;
+    int last_attention_kernel = 0;  // 0 none yet, 1 general, 2 TMA / tensor-core
     uint64_t launches = 0;
     std::string last_error;
     std::unordered_map<const void*, size_t> allocs;

@@ -13,7 +13,7 @@
 // 64-bit; an element-wise kernel covers everything else. Page ids and slots are
 // checked on the host when the pool capacity is known and again in the kernel,
 // which records an error word and skips the access instead of faulting.
-#include "ctx.hpp"
+#include "attn_internal.hpp"
 
 namespace mlcb {
 
@@ -65,37 +65,11 @@ __global__ void paged_tokens_kernel(Vec* __restrict__ pool, Vec* __restrict__ fl
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-static int scatter_batched_impl(mlc_ctx* ctx, bool sync, void* k_pool, void* v_pool,
-                                const uint32_t* page_ids, const uint32_t* slots, size_t P,
-                                size_t KVH, size_t D, size_t batch, const void* k_src,
-                                const void* v_src, size_t capacity_pages) {
-    if (!ctx) return MLC_ERR_INVALID_ARG;
-    // metal_runtime.mm:7241-7243 (sync form); the encode form has no checks in the
-    // reference beyond the open pass, the same rules are applied to both here.
-    if (!k_pool || !k_src || !page_ids || !slots) return ctx->fail(MLC_ERR_INVALID_ARG, "null argument");
-    if ((v_pool == nullptr) != (v_src == nullptr)) return ctx->fail(MLC_ERR_INVALID_ARG, "V pool/src mismatch");
-    if (batch == 0 || KVH == 0 || D == 0 || P == 0) return ctx->fail(MLC_ERR_INVALID_ARG, "zero dimension");
-    if (!sync && !ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
-    if (batch * KVH * D >= (size_t(1) << 32)) return ctx->fail(MLC_ERR_UNSUPPORTED, "batch too large");
-    DeviceGuard guard(ctx->device);
-    size_t row_bytes = KVH * D * 2;
-    size_t cap = resolve_capacity(ctx, k_pool, capacity_pages, P * row_bytes);
-    for (size_t r = 0; r < batch; ++r) {
-        if (cap && page_ids[r] >= cap)
-            return ctx->fail(MLC_ERR_BOUNDS, "page_ids[%zu]=%u >= capacity %zu", r, page_ids[r], cap);
-        if (slots[r] >= P)
-            return ctx->fail(MLC_ERR_BOUNDS, "slots_in_page[%zu]=%u >= page size %zu", r, slots[r], P);
-    }
-    uint32_t cap32 = cap ? static_cast<uint32_t>(cap) : 0xFFFFFFFFu;
-    // one staging region: ids then slots
-    void *h = nullptr, *d = nullptr;
-    if (!stage_reserve(ctx, batch * 8, &h, &d)) return MLC_ERR_OOM;
-    memcpy(h, page_ids, batch * 4);
-    memcpy(static_cast<char*>(h) + batch * 4, slots, batch * 4);
-    if (!stage_commit(ctx, h, d, batch * 8)) return MLC_ERR_CUDA;
-    const uint32_t* d_ids = static_cast<const uint32_t*>(d);
-    const uint32_t* d_slots = d_ids + batch;
-
+int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, const uint32_t* d_ids,
+                                      const uint32_t* d_slots, size_t P, size_t KVH, size_t D,
+                                      size_t batch, const void* k_src, const void* v_src, size_t capacity) {
+    const size_t row_bytes = KVH * D * 2;
+    const uint32_t cap32 = capacity ? static_cast<uint32_t>(capacity) : 0xFFFFFFFFu;
     bool vec = row_bytes % 16 == 0 && aligned16(k_pool) && aligned16(k_src) &&
                (!v_pool || (aligned16(v_pool) && aligned16(v_src)));
     dim3 grid(1, v_pool ? 2 : 1);
@@ -117,6 +91,44 @@ static int scatter_batched_impl(mlc_ctx* ctx, bool sync, void* k_pool, void* v_p
     }
     ++ctx->launches;
     MLCB_CUDA(ctx, cudaGetLastError());
+    return MLC_OK;
+}
+
+static int scatter_batched_impl(mlc_ctx* ctx, bool sync, void* k_pool, void* v_pool,
+                                const uint32_t* page_ids, const uint32_t* slots, size_t P,
+                                size_t KVH, size_t D, size_t batch, const void* k_src,
+                                const void* v_src, size_t capacity_pages) {
+    if (!ctx) return MLC_ERR_INVALID_ARG;
+    // metal_runtime.mm:7241-7243 (sync form); the encode form has no checks in the
+    // reference beyond the open pass, the same rules are applied to both here.
+    if (!k_pool || !k_src || !page_ids || !slots) return ctx->fail(MLC_ERR_INVALID_ARG, "null argument");
+    if ((v_pool == nullptr) != (v_src == nullptr)) return ctx->fail(MLC_ERR_INVALID_ARG, "V pool/src mismatch");
+    if (batch == 0 || KVH == 0 || D == 0 || P == 0) return ctx->fail(MLC_ERR_INVALID_ARG, "zero dimension");
+    if (!sync && !ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (batch * KVH * D >= (size_t(1) << 32)) return ctx->fail(MLC_ERR_UNSUPPORTED, "batch too large");
+    if (ctx->capturing)
+        return ctx->fail(MLC_ERR_UNSUPPORTED, "host page ids inside a graph capture: use the planned scatter");
+    DeviceGuard guard(ctx->device);
+    size_t row_bytes = KVH * D * 2;
+    size_t cap = resolve_capacity(ctx, k_pool, capacity_pages, P * row_bytes);
+    for (size_t r = 0; r < batch; ++r) {
+        if (cap && page_ids[r] >= cap)
+            return ctx->fail(MLC_ERR_BOUNDS, "page_ids[%zu]=%u >= capacity %zu", r, page_ids[r], cap);
+        if (slots[r] >= P)
+            return ctx->fail(MLC_ERR_BOUNDS, "slots_in_page[%zu]=%u >= page size %zu", r, slots[r], P);
+    }
+    // one staging region: ids then slots
+    void *h = nullptr, *d = nullptr;
+    if (!stage_reserve(ctx, batch * 8, &h, &d)) return MLC_ERR_OOM;
+    memcpy(h, page_ids, batch * 4);
+    memcpy(static_cast<char*>(h) + batch * 4, slots, batch * 4);
+    if (!stage_commit(ctx, h, d, batch * 8)) return MLC_ERR_CUDA;
+    const uint32_t* d_ids = static_cast<const uint32_t*>(d);
+    const uint32_t* d_slots = d_ids + batch;
+
+    int st = launch_scatter_rows_device_tables(ctx, k_pool, v_pool, d_ids, d_slots, P, KVH, D, batch, k_src,
+                                               v_src, cap);
+    if (st != MLC_OK) return st;
     if (sync) {
         cudaError_t e = cudaStreamSynchronize(ctx->stream);
         if (!ctx->pass_open) stage_reset(ctx);
