@@ -72,6 +72,14 @@ int mlc_device_error_word(mlc_ctx* ctx, uint32_t* word);
 void* mlc_ctx_stream(const mlc_ctx* ctx);
 /* Number of kernels this context has launched since creation. */
 uint64_t mlc_ctx_launch_count(const mlc_ctx* ctx);
+/* Profiling aid (the reference's are env-gated wall-clock tables,
+ * compiler/runtime/batched_walker.cpp:100-125): with MLC_B200_TRACE=1 in the
+ * environment when the context is created, every warp of the split-KV attention
+ * kernel records 8 %globaltimer stamps (entry, copies issued, first tile landed,
+ * first piece computed, partial published, merge done, merge started, exit). Copies
+ * the stamps of the most recent launch (previous = 0) or of the one before it
+ * (previous = 1) as [ctas][4][8] u64 nanoseconds; returns the number of CTAs. */
+uint32_t mlc_ctx_read_trace(mlc_ctx* ctx, unsigned long long* out, size_t max_words, int previous);
 
 /* ---- buffers: allocateScratchBuffer / releaseScratchBuffer / uploadToBuffer /
  * downloadFromBuffer (metal_runtime.hpp:693-696) and getOrAllocCachedBuffer
@@ -207,6 +215,26 @@ int mlc_encode_paged_flash_attention_planned(mlc_ctx* ctx, const mlc_attn_plan* 
  * one launch, page ids and slots taken from `plan`. */
 int mlc_encode_scatter_kv_pair_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, void* k_page_storage,
                                        void* v_page_storage, const void* k_src, const void* v_src);
+
+/* One layer of a decode step in ONE launch: what the reference's walker issues as two
+ * encodeScatterKVPagedBatched calls followed by encodePagedFlashAttention
+ * (batched_walker.cpp:299-331). The attention kernel writes each request's new K/V
+ * row (k_new / v_new: device fp16 [batch, kv_heads, head_dim]) to the (page, slot) the
+ * plan was created with and attends over the pool including that row. Requirements
+ * for the single-launch form (otherwise the call transparently issues the scatter
+ * and the attention as two launches): the plan was created with page_ids /
+ * slots_in_page pointing at token seq_lens[r]-1 of every request and q_positions[r]
+ * == seq_lens[r]-1, as in a decode step.
+ * Stream-order contract of the single-launch form: the kernel is launched with
+ * programmatic stream serialisation and starts fetching K/V pages while earlier work
+ * on the stream is still finishing; Q, k_new and v_new are read only after that work
+ * has completed. Therefore pool rows OTHER than this step's new rows must not be
+ * written by work that is still in flight on the stream when this call is enqueued
+ * (they were written by earlier steps; a pass_flush / stream sync between steps, or
+ * any non-overlapping kernel in between, satisfies this). */
+int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
+                                         const void* k_new, const void* v_new, void* k_pages,
+                                         void* v_pages, void* o, float scale, int q_dtype, int o_dtype);
 
 /* ---- split-KV across GPUs (no counterpart in the reference: it has one device) -------
  * A rank that holds only a slice of every request's pages computes, over its

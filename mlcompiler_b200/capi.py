@@ -64,11 +64,13 @@ _PROTOTYPES = {
     "mlc_encode_paged_flash_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p,
                                               _sz, _sz, _sz, _sz, _sz, _i, _f, _i, _i, _sz]),
     "mlc_ctx_last_attention_kernel": (_i, [_vp]),
+    "mlc_ctx_read_trace": (C.c_uint32, [_vp, C.POINTER(C.c_uint64), _sz, _i]),
     "mlc_attn_plan_create": (_i, [_vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p, _u32p, _sz, _sz, _sz, _sz, _sz,
                                   _i, _sz, C.POINTER(_vp)]),
     "mlc_attn_plan_destroy": (None, [_vp, _vp]),
     "mlc_encode_paged_flash_attention_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_scatter_kv_pair_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "mlc_encode_paged_decode_step_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_paged_attention_partial_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i]),
     "mlc_encode_lse_combine": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _i]),
     "mlc_graph_begin_capture": (_i, [_vp]),
@@ -284,6 +286,14 @@ class Executor:
                                kv_heads, head_dim, page_size_tokens, apply_causal, scale, q_dtype, o_dtype,
                                capacity_pages)
 
+    def readTrace(self, previous: bool = False) -> np.ndarray:
+        """[ctas, 4, 8] uint64 nanosecond stamps of the last traced decode launch
+        (or, with previous=True, of the launch before it)."""
+        buf = np.zeros(1 << 15, np.uint64)
+        n = self._lib.mlc_ctx_read_trace(self._h, buf.ctypes.data_as(C.POINTER(C.c_uint64)), buf.size,
+                                         1 if previous else 0)
+        return buf[: n * 32].reshape(n, 4, 8)
+
     def lastAttentionKernel(self) -> int:
         return int(self._lib.mlc_ctx_last_attention_kernel(self._h))
 
@@ -314,6 +324,12 @@ class Executor:
         return self.status(self._lib.mlc_encode_paged_flash_attention_planned(
             self._h, plan.handle, _vp(_ptr(q)), _vp(_ptr(k_pages)), _vp(_ptr(v_pages)), _vp(_ptr(o)),
             float(scale), q_dtype, o_dtype))
+
+    def encodePagedDecodeStepPlanned(self, plan, q, k_new, v_new, k_pages, v_pages, o, scale=0.0,
+                                     q_dtype=MLC_F32, o_dtype=MLC_F32) -> bool:
+        return self.status(self._lib.mlc_encode_paged_decode_step_planned(
+            self._h, plan.handle, _vp(_ptr(q)), _vp(_ptr(k_new)), _vp(_ptr(v_new)), _vp(_ptr(k_pages)),
+            _vp(_ptr(v_pages)), _vp(_ptr(o)), float(scale), q_dtype, o_dtype))
 
     def encodeScatterKVPairPlanned(self, plan, k_storage, v_storage, k_src, v_src) -> bool:
         return self.status(self._lib.mlc_encode_scatter_kv_pair_planned(

@@ -14,6 +14,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <queue>
 
 namespace mlcb {
 
@@ -96,14 +97,27 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
 
     std::vector<std::vector<PieceDesc>> cta_pieces;
     std::vector<std::vector<uint32_t>> cta_tiles;
-    uint32_t n_cta = 0, max_pieces = 1, max_tiles = 1, n_slots = 0, n_segs = 0;
+    uint32_t n_cta = 0, max_pieces = 1, max_tiles = 1, n_slots = 0, n_segs = 0, stages = 3;
+    // A decode step can fuse the row write into attention when the newest token of every
+    // request (position seq_len - 1, where page_ids / slots must point) is attended to.
+    bool fusable = page_ids != nullptr;
+    for (size_t r = 0; r < N && fusable; ++r) {
+        const uint32_t S = seq_lens[r];
+        fusable = S > 0 && eff[r] == S && page_ids[r] == pt_flat[pt_off[r] + (S - 1) / k.P] &&
+                  slots[r] == (S - 1) % k.P;
+    }
     const bool tma = decode_tma_shape_supported(k.H, k.KVH, k.D, k.P, k.capacity);
+    std::vector<SegDesc> segs;
     if (tma) {
         const uint32_t TOK = kTileTokens;
         const uint32_t n_hb = static_cast<uint32_t>((k.KVH + kDecodeWarps - 1) / kDecodeWarps);
         uint64_t total = 0;
         for (size_t r = 0; r < N; ++r) total += static_cast<uint64_t>((eff[r] + TOK - 1) / TOK) * n_hb;
-        int per_sm = env_int("MLC_B200_DECODE_CTAS_PER_SM", k.D <= 64 ? 2 : 1);
+        // One CTA per SM and ~100 KiB of ring per CTA where possible: a decode-step kernel
+        // and its programmatic successor can then share an SM.
+        int per_sm = env_int("MLC_B200_DECODE_CTAS_PER_SM", 1);
+        stages = static_cast<uint32_t>(std::min<int>(decode_tma_max_stages(k.H, k.KVH, k.D),
+                                                     std::max(1, env_int("MLC_B200_DECODE_STAGES", 3))));
         uint64_t max_cta = static_cast<uint64_t>(ctx->sm_count) * std::max(per_sm, 1);
         int min_tiles = std::max(env_int("MLC_B200_DECODE_MIN_TILES", 1), 1);
         n_cta = static_cast<uint32_t>(std::max<uint64_t>(1, std::min<uint64_t>(max_cta, total / min_tiles)));
@@ -128,14 +142,15 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                     d.n_tiles = take;
                     d.last_valid = static_cast<uint16_t>(
                         (t + take == tiles_r) ? eff[r] - (tiles_r - 1) * TOK : TOK);
+                    d.flags = (fusable && t + take == tiles_r) ? 1u : 0u;
                     seg_pieces.emplace_back(c, static_cast<uint32_t>(cta_pieces[c].size()));
                     cta_pieces[c].push_back(d);
                     for (uint32_t i = 0; i < take; ++i) {
-                        // tile word: page id | sub-tile within the page << 25 | head block << 28
                         uint64_t tok0 = static_cast<uint64_t>(t + i) * TOK;
                         uint32_t page = pt_flat[pt_off[r] + tok0 / k.P];
                         uint32_t sub = static_cast<uint32_t>((tok0 % k.P) / TOK);
-                        cta_tiles[c].push_back(page | (sub << 25) | (hb << 28));
+                        uint32_t fresh = (fusable && t + i + 1 == tiles_r) ? kTileFreshBit : 0u;
+                        cta_tiles[c].push_back(page | (sub << kTileSubShift) | (hb << kTileHbShift) | fresh);
                     }
                     t += take;
                     g += take;
@@ -150,6 +165,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                     d.part_slot = first_slot + static_cast<uint32_t>(i);
                 }
                 if (parts > 1) {
+                    segs.push_back({static_cast<uint32_t>(r), hb, first_slot, parts});
                     n_slots += parts;
                     ++n_segs;
                 }
@@ -164,12 +180,14 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     // ---- lay the image out
     size_t off = 0;
     const size_t off_counts = off;   off = align_up(off + size_t(n_cta) * 8, 16);
-    const size_t off_pieces = off;   off = align_up(off + size_t(n_cta) * max_pieces * sizeof(PieceDesc), 16);
-    const size_t off_tiles = off;    off = align_up(off + size_t(n_cta) * max_tiles * 4, 16);
+    // +512 / +128 bytes: the kernel prologue reads 16 descriptors and 32 tile words per CTA unconditionally
+    const size_t off_pieces = off;   off = align_up(off + size_t(n_cta) * max_pieces * sizeof(PieceDesc) + 512, 16);
+    const size_t off_tiles = off;    off = align_up(off + size_t(n_cta) * max_tiles * 4 + 128, 16);
     const size_t off_flat = off;     off = align_up(off + k.n_flat * 4, 16);
     const size_t off_ptoff = off;    off = align_up(off + (N + 1) * 4, 16);
     const size_t off_eff = off;      off = align_up(off + N * 4, 16);
     const size_t off_zero = off;     off = align_up(off + zero_rows.size() * 4, 16);
+    const size_t off_segs = off;     off = align_up(off + segs.size() * sizeof(SegDesc), 16);
     const size_t off_ids = off;      off = align_up(off + (page_ids ? N * 4 : 0), 16);
     const size_t off_slots = off;    off = align_up(off + (slots ? N * 4 : 0), 16);
     const size_t bytes = std::max<size_t>(off, 16);
@@ -203,6 +221,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     std::memcpy(p.host + off_ptoff, pt_off, (N + 1) * 4);
     std::memcpy(p.host + off_eff, eff.data(), N * 4);
     if (!zero_rows.empty()) std::memcpy(p.host + off_zero, zero_rows.data(), zero_rows.size() * 4);
+    if (!segs.empty()) std::memcpy(p.host + off_segs, segs.data(), segs.size() * sizeof(SegDesc));
     if (page_ids) std::memcpy(p.host + off_ids, page_ids, N * 4);
     if (slots) std::memcpy(p.host + off_slots, slots, N * 4);
     MLCB_CUDA(ctx, cudaMemcpyAsync(p.dev, p.host, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -216,7 +235,10 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     v.pt_off = reinterpret_cast<const uint32_t*>(p.dev + off_ptoff);
     v.eff_len = reinterpret_cast<const uint32_t*>(p.dev + off_eff);
     v.zero_rows = reinterpret_cast<const uint32_t*>(p.dev + off_zero);
+    v.seg_desc = reinterpret_cast<const SegDesc*>(p.dev + off_segs);
     v.has_tma = tma;
+    v.step_fusable = tma && fusable;
+    v.stages = stages;
     v.n_cta = n_cta;
     v.max_pieces = max_pieces;
     v.max_tiles = max_tiles;
@@ -444,6 +466,29 @@ int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan
     a.q = q; a.k_pages = k_pages; a.v_pages = v_pages;
     a.o_partial = o_partial; a.ml_partial = ml_partial;
     a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = MLC_F32;
+    return launch_with_plan(ctx, a, *plan);
+}
+
+int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
+                                         const void* k_new, const void* v_new, void* k_pages,
+                                         void* v_pages, void* o, float scale, int q_dtype, int o_dtype) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (!plan->d_page_ids) return ctx->fail(MLC_ERR_INVALID_ARG, "the plan was created without page_ids / slots_in_page");
+    if (!k_new || !v_new || !k_pages || !v_pages) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    DeviceGuard guard(ctx->device);
+    AttnArgs a;
+    a.q = q; a.k_pages = k_pages; a.v_pages = v_pages; a.o = o;
+    a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
+    a.k_new = k_new; a.v_new = v_new;
+    const PlanKey& k = plan->key;
+    if (plan->view.step_fusable && !ctx->force_general && decode_tma_pointers_supported(a))
+        return launch_with_plan(ctx, a, *plan);
+    // not fusable (odd shape, causal cut before the newest token, unaligned buffers): two launches
+    int st = launch_scatter_rows_device_tables(ctx, k_pages, v_pages, plan->d_page_ids, plan->d_slots, k.P,
+                                               k.KVH, k.D, k.batch, k_new, v_new, k.capacity);
+    if (st != MLC_OK) return st;
+    a.k_new = a.v_new = nullptr;
     return launch_with_plan(ctx, a, *plan);
 }
 

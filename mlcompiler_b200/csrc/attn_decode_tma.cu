@@ -21,15 +21,33 @@
 //   reductions through threadgroup memory   accumulate) for Q.K^T and P.V; row max
 //                                           and row sum by quad shuffles
 //
+// The four warps of a CTA work on the four KV heads of one head block over the same
+// tiles, so together they read whole token rows (KVH*D contiguous halfs) of a page at
+// about the same time. That matters: fetching one head's 128-byte slices alone
+// (512-byte stride) was measured at roughly half the DRAM throughput of the dense
+// pattern on B200.
+//
 // G = 8 means 4 FMA per KV byte; at HBM speed that is more than half of the
 // SM's fp32 FMA rate before any fp16->fp32 conversion, so the dots go through the
 // tensor cores and the kernel stays bandwidth-bound. tcgen05/TMEM is not used
 // here: a decode tile has 8 (or 4) query rows against the 64-row minimum of a
 // tcgen05 MMA, and the accumulators fit in registers.
 //
-// Partials of a (request, KV head) that is split over several CTAs go to a
-// workspace as un-normalised (o, m, l); the warp that arrives last (an atomic
-// counter, no waiting) merges them with the log-sum-exp rule and writes O.
+// A (request, head block) that spans several CTAs leaves one un-normalised partial
+// (o, m, l) per piece in a workspace - plain stores, no fence, no counter - and a
+// second small kernel, chained to the first by programmatic dependent launch, merges
+// them with the log-sum-exp rule and writes O. The kernel boundary is the only
+// synchronisation between the two.
+//
+// Decode-step variant (`step` launches): the kernel also writes the step's new K/V
+// row of every request into the pool - the reference's two
+// scatter_kv_paged_batched_f16 dispatches (metal_runtime.mm:405-424) - and uses the
+// row from its source buffer, so no separate scatter launch has to finish first. It is
+// launched with programmatic stream serialisation: everything that depends only on
+// the plan and on K/V rows written by earlier steps (plan reads, barrier set-up, the
+// first ring-full of TMA copies) runs before griddepcontrol.wait, i.e. while the
+// previous kernels in the stream are still draining; Q and the new rows are read
+// after it.
 //
 // Nothing here spins on another CTA. The only waits are mbarrier waits on this
 // warp's own TMA copies; they are bounded, and on expiry the warp records
@@ -71,12 +89,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 // Map over one pool viewed as [capacity][P][KVH][D] halfs; box = 64 halfs of one
 // KV head for kTileTokens consecutive slots of one page, 128-byte swizzled.
-static int get_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, const CUtensorMap** out) {
+static int get_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, CUtensorMap* out) {
     if (!ctx->tmap_cache) ctx->tmap_cache = new TensorMapCache();
     TensorMapCache& tc = *ctx->tmap_cache;
     for (auto& e : tc.entries)
         if (e.pool == pool && e.D == a.D && e.KVH == a.KVH && e.P == a.P && e.capacity == a.capacity) {
-            *out = &e.map;
+            *out = e.map;
             return MLC_OK;
         }
     if (!tc.encode_fn) {
@@ -97,7 +115,7 @@ static int get_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, con
     if (r != CUDA_SUCCESS) return ctx->fail(MLC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
     if (tc.entries.size() >= 256) tc.entries.erase(tc.entries.begin());
     tc.entries.push_back(e);
-    *out = &tc.entries.back().map;
+    *out = e.map;
     return MLC_OK;
 }
 
@@ -113,16 +131,23 @@ struct DecodeParams {
     const PieceDesc* pieces;
     const uint32_t* tile_pages;
     const uint32_t* zero_rows;
+    const SegDesc* seg_desc;
     float* work_o;      // split-KV workspace: o fragments
     float* work_ml;     // split-KV workspace: (m, l) per lane
-    uint32_t* counters;
     uint32_t* err;
+    // decode-step variant: the step's new rows (fp16 [batch, KVH, D]) and the pools they go to
+    const __half* k_new;
+    const __half* v_new;
+    __half* k_pool;
+    __half* v_pool;
     uint32_t max_pieces, max_tiles, n_zero;
-    uint32_t H, KVH, G;
+    uint32_t H, KVH, G, P;
     uint32_t stages;
-    uint32_t sub_per_page;  // P / kTileTokens
-    float scale_log2;       // scale * log2(e)
+    float scale_log2;   // scale * log2(e)
     int q_f32, o_f32;
+    int step;           // 1: decode-step variant (fused row write, early start)
+    int pdl;            // 1: launched with programmatic stream serialisation
+    unsigned long long* trace;  // optional [cta][warp][8] %globaltimer stamps (MLC_B200_TRACE)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -180,22 +205,52 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ float2 ld_cg_f2(const float2* p) {
-    float2 v;
-    asm volatile("ld.global.cg.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ float4 ld_cg_f4(const float4* p) {
-    float4 v;
-    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-}
 
-// Tile entry: page id in bits 0..24, sub-tile within the page in 25..27, head block in 28..31.
-static constexpr uint32_t kTilePageMask = (1u << 25) - 1;
+// Writes the rows of one (request, KV head) from accumulator fragments: either O
+// (normalised, fp32 or fp16) or the caller-visible partial (un-normalised o, (m, l)).
+template <int D, bool G16>
+__device__ __forceinline__ void write_rows(const DecodeParams& prm, uint32_t req, uint32_t head, uint32_t lane,
+                                           const float (&o_acc)[D / 8][4], const float (&m_run)[2],
+                                           const float (&l_run)[2]) {
+    constexpr int NT_O = D / 8;
+    constexpr int ROWSETS = G16 ? 2 : 1;
+    const uint32_t qrow = lane >> 2, qcol = (lane & 3) * 2;
+#pragma unroll
+    for (int rs = 0; rs < ROWSETS; ++rs) {
+        const uint32_t row = qrow + 8 * rs;
+        if (row >= prm.G) continue;
+        const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
+        if (prm.o_partial) {
+            float* dst = prm.o_partial + hrow * D;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8 + qcol) = make_float2(o_acc[n][2 * rs], o_acc[n][2 * rs + 1]);
+            if ((lane & 3) == 0) {
+                // natural-log units for the caller: m_nat = m_2 * ln 2
+                prm.ml_partial[hrow * 2] = m_run[rs] * 0.6931471805599453f;
+                prm.ml_partial[hrow * 2 + 1] = l_run[rs];
+            }
+        } else {
+            const float inv = l_run[rs] > 0.f ? 1.0f / l_run[rs] : 0.f;
+            if (prm.o_f32) {
+                float* dst = static_cast<float*>(prm.o) + hrow * D;
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n)
+                    *reinterpret_cast<float2*>(dst + n * 8 + qcol) =
+                        make_float2(o_acc[n][2 * rs] * inv, o_acc[n][2 * rs + 1] * inv);
+            } else {
+                __half* dst = static_cast<__half*>(prm.o) + hrow * D;
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n)
+                    *reinterpret_cast<__half2*>(dst + n * 8 + qcol) =
+                        __floats2half2_rn(o_acc[n][2 * rs] * inv, o_acc[n][2 * rs + 1] * inv);
+            }
+        }
+    }
+}
 
 // ------------------------------------------------------------------------------
-// the kernel
+// the attention kernel
 // ------------------------------------------------------------------------------
 template <int D, bool G16>
 __global__ void __launch_bounds__(kDecodeWarps * 32)
@@ -219,6 +274,87 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t ring = smem_base + warp * stages * kStageBytes;
 
+    // The three plan reads of the prologue are independent of one another, so they
+    // cost one memory round trip together: the CTA's counts, its first 32 tile words
+    // (one per lane) and its first 16 piece descriptors (half a descriptor per lane).
+    // The planner pads both arrays so that these reads stay inside the plan image.
+    const uint32_t* my_tiles = prm.tile_pages + static_cast<size_t>(cta) * prm.max_tiles;
+    const PieceDesc* my_pieces = prm.pieces + static_cast<size_t>(cta) * prm.max_pieces;
+    const uint2 counts = __ldg(reinterpret_cast<const uint2*>(prm.cta_counts) + cta);
+    uint32_t win_base = 0;
+    uint32_t win = __ldg(my_tiles + lane);
+    const uint4 desc_half = __ldg(reinterpret_cast<const uint4*>(my_pieces) + lane);
+    const uint32_t n_pieces = counts.x, n_tiles = counts.y;
+    auto stamp = [&](int i) {
+        if (prm.trace && lane == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            prm.trace[(static_cast<size_t>(cta) * kDecodeWarps + warp) * 8 + i] = t;
+        }
+    };
+    stamp(0);
+
+    if (lane == 0) {
+        for (uint32_t s = 0; s < stages; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    auto tile_entry = [&](uint32_t j) -> uint32_t {
+        if (j - win_base >= 32u) {  // uniform across the warp
+            win_base = j & ~31u;
+            win = (win_base + lane < n_tiles) ? __ldg(my_tiles + win_base + lane) : 0u;
+        }
+        return __shfl_sync(0xffffffffu, win, j - win_base);
+    };
+    // Ring position counters of this warp. They count only tiles of head blocks in
+    // which this warp owns a KV head, in the (identical) order of issue and use.
+    uint32_t iss = 0, con = 0;
+    // Issues the TMA copies of the tile word `e` into the next ring stage.
+    auto issue_word = [&](uint32_t e) {
+        const uint32_t head = ((e >> kTileHbShift) & kTileHbMask) * kDecodeWarps + warp;
+        if (head >= prm.KVH) return;  // this warp has no KV head in that head block
+        const uint32_t s = iss % stages;
+        ++iss;
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&bars[warp][s]);
+            const uint32_t dst = ring + s * kStageBytes;
+            const int page = static_cast<int>(e & kTilePageMask);
+            const int slot0 = static_cast<int>(((e >> kTileSubShift) & 7u) * TOK);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(bar, kStageBytes);
+#pragma unroll
+            for (int sub = 0; sub < SUBS; ++sub) {
+                tma_load_4d(dst + sub * (TOK * 128), &tmK, bar, sub * 64, static_cast<int>(head), slot0, page);
+                tma_load_4d(dst + kTileBytes + sub * (TOK * 128), &tmV, bar, sub * 64, static_cast<int>(head), slot0, page);
+            }
+        }
+    };
+
+    // Prefetches run ahead over piece boundaries; they need nothing but the tile list.
+    // In a decode step, tiles that hold a row written in this step ("fresh" tiles: the
+    // ones containing the new token) are not fetched before griddepcontrol.wait;
+    // everything older may be.
+    uint32_t next_issue = 0;  // next CTA-local tile to fetch
+    const uint32_t window = n_tiles < stages ? n_tiles : stages;
+    if (prm.pdl) {
+        if (prm.step) {
+            while (next_issue < window) {
+                const uint32_t e = tile_entry(next_issue);
+                if (e & kTileFreshBit) break;
+                issue_word(e);
+                ++next_issue;
+            }
+        }
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    while (next_issue < window) {
+        issue_word(tile_entry(next_issue));
+        ++next_issue;
+    }
+    stamp(1);
+
     // Requests that attend to nothing: their O rows are zeros (mm:2254-2257).
     for (uint32_t i = cta; i < prm.n_zero; i += gridDim.x) {
         const uint32_t r = prm.zero_rows[i];
@@ -235,73 +371,37 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
     }
 
-    const uint32_t n_pieces = prm.cta_counts[2 * cta];
-    const uint32_t n_tiles = prm.cta_counts[2 * cta + 1];
-    if (n_tiles == 0) return;
-    const uint32_t* my_tiles = prm.tile_pages + static_cast<size_t>(cta) * prm.max_tiles;
-    const PieceDesc* my_pieces = prm.pieces + static_cast<size_t>(cta) * prm.max_pieces;
-
-    if (lane == 0) {
-        for (uint32_t s = 0; s < stages; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncwarp();
-
-    // Window of 32 tile entries held one per lane.
-    uint32_t win_base = 0;
-    uint32_t win = (lane < n_tiles) ? __ldg(my_tiles + lane) : 0u;
-
-    auto tile_entry = [&](uint32_t j) -> uint32_t {
-        if (j - win_base >= 32u) {  // uniform across the warp
-            win_base = j & ~31u;
-            win = (win_base + lane < n_tiles) ? __ldg(my_tiles + win_base + lane) : 0u;
-        }
-        return __shfl_sync(0xffffffffu, win, j - win_base);
-    };
-    // Ring position counters of this warp. They count only tiles of head blocks in
-    // which this warp owns a KV head, in the (identical) order of issue and use.
-    uint32_t iss = 0, con = 0;
-    // Issues the TMA copies of CTA-local tile j into the next ring stage.
-    auto issue = [&](uint32_t j) {
-        const uint32_t e = tile_entry(j);
-        const uint32_t head = (e >> 28) * kDecodeWarps + warp;
-        if (head >= prm.KVH) return;  // this warp has no KV head in that head block
-        const uint32_t s = iss % stages;
-        ++iss;
-        if (lane == 0) {
-            const uint32_t bar = smem_u32(&bars[warp][s]);
-            const uint32_t dst = ring + s * kStageBytes;
-            const int page = static_cast<int>(e & kTilePageMask);
-            const int slot0 = static_cast<int>(((e >> 25) & 7u) * TOK);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(bar, kStageBytes);
-#pragma unroll
-            for (int sub = 0; sub < SUBS; ++sub) {
-                tma_load_4d(dst + sub * (TOK * 128), &tmK, bar, sub * 64, static_cast<int>(head), slot0, page);
-                tma_load_4d(dst + kTileBytes + sub * (TOK * 128), &tmV, bar, sub * 64, static_cast<int>(head), slot0, page);
-            }
-        }
-    };
-
-    // Prefetches run ahead over piece boundaries; they need nothing but the tile list.
-    const uint32_t prologue = n_tiles < stages ? n_tiles : stages;
-    for (uint32_t j = 0; j < prologue; ++j) issue(j);
-
     const uint32_t qrow = lane >> 2, qcol = (lane & 3) * 2;
     uint32_t j = 0;  // CTA-local tile counter (consume side)
     bool dead = false;
 
     for (uint32_t pi = 0; pi < n_pieces && !dead; ++pi) {
-        const uint4 d0 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi));
-        const uint4 d1 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi) + 1);
+        uint4 d0, d1;
+        if (pi < 16u) {  // prefetched in the prologue: lane 2i holds the first half of piece i
+            d0.x = __shfl_sync(0xffffffffu, desc_half.x, 2 * pi);
+            d0.y = __shfl_sync(0xffffffffu, desc_half.y, 2 * pi);
+            d0.z = __shfl_sync(0xffffffffu, desc_half.z, 2 * pi);
+            d0.w = __shfl_sync(0xffffffffu, desc_half.w, 2 * pi);
+            d1.x = __shfl_sync(0xffffffffu, desc_half.x, 2 * pi + 1);
+            d1.y = __shfl_sync(0xffffffffu, desc_half.y, 2 * pi + 1);
+            d1.z = __shfl_sync(0xffffffffu, desc_half.z, 2 * pi + 1);
+            d1.w = __shfl_sync(0xffffffffu, desc_half.w, 2 * pi + 1);
+        } else {
+            d0 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi));
+            d1 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi) + 1);
+        }
         const uint32_t req = d0.x, piece_tiles = d0.z, part_slot = d0.w;
-        const uint32_t seg_first_slot = d1.x, seg = d1.y;
         const uint32_t n_parts = d1.z & 0xffffu, hb = d1.z >> 16;
         const uint32_t last_valid = d1.w & 0xffffu;
+        const bool fresh_piece = prm.step && ((d1.w >> 16) & 1u);  // its last tile holds the new token
         const uint32_t head = hb * kDecodeWarps + warp;
         if (head >= prm.KVH) {  // keep the tile counter and the prefetch stream in step
-            for (uint32_t t = 0; t < piece_tiles; ++t, ++j)
-                if (j + stages < n_tiles) issue(j + stages);
+            for (uint32_t t = 0; t < piece_tiles; ++t, ++j) {
+                if (next_issue < n_tiles) {
+                    issue_word(tile_entry(next_issue));
+                    ++next_issue;
+                }
+            }
             continue;
         }
 
@@ -332,6 +432,17 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
             }
         }
+        // ---- decode step: this step's new K/V row of (request, head), one 16-byte chunk per
+        // lane (lanes [0, D/8) hold K, lanes [16, 16 + D/8) hold V). It is written to the pool
+        // here and patched over the fresh tile's copy in shared memory below.
+        uint4 new_row = make_uint4(0u, 0u, 0u, 0u);
+        constexpr uint32_t kRowChunks = D / 8;
+        const bool row_lane = (lane & 15u) < kRowChunks;
+        if (fresh_piece && row_lane) {
+            const __half* src = (lane < 16u ? prm.k_new : prm.v_new) +
+                                (static_cast<size_t>(req) * prm.KVH + head) * D + (lane & 15u) * 8;
+            new_row = *reinterpret_cast<const uint4*>(src);
+        }
 
         float o_acc[NT_O][4];
 #pragma unroll
@@ -348,8 +459,29 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 dead = true;
                 break;
             }
+            if (j == 0) stamp(2);
             const uint32_t sK = ring + s * kStageBytes, sV = sK + kTileBytes;
-            const uint32_t nv = (t + 1 == piece_tiles) ? last_valid : TOK;
+            const bool last_tile = t + 1 == piece_tiles;
+            const uint32_t nv = last_tile ? last_valid : TOK;
+
+            if (fresh_piece && last_tile) {
+                // The new token is the last valid row of this tile; its pool address follows
+                // from the tile word (page, sub-tile).
+                const uint32_t rowi = nv - 1;
+                const uint32_t e = __ldg(my_tiles + j);
+                if (row_lane) {
+                    const uint32_t chunk = lane & 15u;
+                    const uint32_t addr = (lane < 16u ? sK : sV) + (chunk >> 3) * (TOK * 128) + rowi * 128 +
+                                          (((chunk & 7) ^ (rowi & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(new_row.x), "r"(new_row.y),
+                                 "r"(new_row.z), "r"(new_row.w) : "memory");
+                    const size_t prow = (static_cast<size_t>(e & kTilePageMask) * prm.P +
+                                         ((e >> kTileSubShift) & 7u) * TOK + rowi) * prm.KVH + head;
+                    __half* dstp = (lane < 16u ? prm.k_pool : prm.v_pool) + prow * D + chunk * 8;
+                    *reinterpret_cast<uint4*>(dstp) = new_row;
+                }
+                __syncwarp();
+            }
 
             // ---- S = Q.K^T (fp32)
             float sc[NT_S][4];
@@ -433,9 +565,13 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
             }
             __syncwarp();
-            if (j + stages < n_tiles) issue(j + stages);
+            if (next_issue < n_tiles) {
+                issue_word(tile_entry(next_issue));
+                ++next_issue;
+            }
         }
         if (dead) break;
+        if (pi == 0) stamp(3);
 
         // ---- end of piece: row sums over the quad
 #pragma unroll
@@ -445,7 +581,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
 
         if (n_parts > 1) {
-            // un-normalised partial -> workspace, fragment order (coalesced)
+            // un-normalised partial -> workspace, fragment order (coalesced). The merge kernel
+            // that follows in the stream reads it; the kernel boundary orders the two.
             const size_t unit = static_cast<size_t>(part_slot) * kDecodeWarps + warp;
             if (G16) {
                 float4* wo = reinterpret_cast<float4*>(prm.work_o) + unit * NT_O * 32;
@@ -460,94 +597,88 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 for (int n = 0; n < NT_O; ++n) wo[n * 32 + lane] = make_float2(o_acc[n][0], o_acc[n][1]);
                 reinterpret_cast<float2*>(prm.work_ml)[unit * 32 + lane] = make_float2(m_run[0], l_run[0]);
             }
-            __threadfence();
-            __syncwarp();
-            uint32_t old = 0;
-            if (lane == 0) old = atomicAdd(prm.counters + seg * kDecodeWarps + warp, 1u);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old != n_parts - 1) continue;  // someone else will merge
-            __threadfence();
-            // ---- last arrival: merge all partials of (request, head)
-            float mstar[2] = {-INFINITY, -INFINITY};
-            for (uint32_t k = 0; k < n_parts; ++k) {
-                const size_t u = static_cast<size_t>(seg_first_slot + k) * kDecodeWarps + warp;
-                if (G16) {
-                    const float4 ml = ld_cg_f4(reinterpret_cast<const float4*>(prm.work_ml) + u * 32 + lane);
-                    mstar[0] = fmaxf(mstar[0], ml.x);
-                    mstar[1] = fmaxf(mstar[1], ml.z);
-                } else {
-                    const float2 ml = ld_cg_f2(reinterpret_cast<const float2*>(prm.work_ml) + u * 32 + lane);
-                    mstar[0] = fmaxf(mstar[0], ml.x);
-                }
-            }
-#pragma unroll
-            for (int n = 0; n < NT_O; ++n) o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f;
-            l_run[0] = l_run[1] = 0.f;
-            for (uint32_t k = 0; k < n_parts; ++k) {
-                const size_t u = static_cast<size_t>(seg_first_slot + k) * kDecodeWarps + warp;
-                if (G16) {
-                    const float4 ml = ld_cg_f4(reinterpret_cast<const float4*>(prm.work_ml) + u * 32 + lane);
-                    const float w0 = ex2(ml.x - mstar[0]), w1 = ex2(ml.z - mstar[1]);
-                    l_run[0] += ml.y * w0;
-                    l_run[1] += ml.w * w1;
-                    const float4* wo = reinterpret_cast<const float4*>(prm.work_o) + u * NT_O * 32;
-#pragma unroll
-                    for (int n = 0; n < NT_O; ++n) {
-                        const float4 v = ld_cg_f4(wo + n * 32 + lane);
-                        o_acc[n][0] += v.x * w0; o_acc[n][1] += v.y * w0;
-                        o_acc[n][2] += v.z * w1; o_acc[n][3] += v.w * w1;
-                    }
-                } else {
-                    const float2 ml = ld_cg_f2(reinterpret_cast<const float2*>(prm.work_ml) + u * 32 + lane);
-                    const float w0 = ex2(ml.x - mstar[0]);
-                    l_run[0] += ml.y * w0;
-                    const float2* wo = reinterpret_cast<const float2*>(prm.work_o) + u * NT_O * 32;
-#pragma unroll
-                    for (int n = 0; n < NT_O; ++n) {
-                        const float2 v = ld_cg_f2(wo + n * 32 + lane);
-                        o_acc[n][0] += v.x * w0; o_acc[n][1] += v.y * w0;
-                    }
-                }
-            }
-            m_run[0] = mstar[0];
-            m_run[1] = mstar[1];
-            if (lane == 0) prm.counters[seg * kDecodeWarps + warp] = 0u;  // ready for the next launch
+            if (pi == 0) stamp(4);
+        } else {
+            write_rows<D, G16>(prm, req, head, lane, o_acc, m_run, l_run);
         }
+        if (pi + 1 == n_pieces) stamp(7);
+    }
+}
 
-        // ---- write the rows of this (request, KV head)
+// ------------------------------------------------------------------------------
+// the merge kernel: one CTA per split (request, head block), one warp per KV head
+// ------------------------------------------------------------------------------
+template <int D, bool G16>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+paged_decode_merge_kernel(const DecodeParams prm) {
+    constexpr int NT_O = D / 8;
+    constexpr int ROWSETS = G16 ? 2 : 1;
+    constexpr int FR = G16 ? 4 : 2;  // floats per lane per output n-tile
+    constexpr int BATCH = (NT_O * FR) <= 16 ? 12 : ((NT_O * FR) <= 32 ? 6 : 3);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // The segment descriptor is plan data: read it while the attention kernel still runs.
+    // Then let the next kernel in the stream start its own prologue, and wait until the
+    // attention kernel that produced the partials has completed.
+    const uint4 sdw = __ldg(reinterpret_cast<const uint4*>(prm.seg_desc) + blockIdx.x);
+    SegDesc sd;
+    sd.req = sdw.x; sd.hb = sdw.y; sd.first_slot = sdw.z; sd.n_parts = sdw.w;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t head = sd.hb * kDecodeWarps + warp;
+    if (head >= prm.KVH) return;
+
+    float o_acc[NT_O][4];
 #pragma unroll
-        for (int rs = 0; rs < ROWSETS; ++rs) {
-            const uint32_t row = qrow + 8 * rs;
-            if (row >= prm.G) continue;
-            const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
-            if (prm.o_partial) {
-                float* dst = prm.o_partial + hrow * D;
+    for (int n = 0; n < NT_O; ++n) o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // One pass with a running maximum; the loads of a batch of partials are all issued
+    // before any of them is used, so a batch costs a single L2 round trip.
+    for (uint32_t k0 = 0; k0 < sd.n_parts; k0 += BATCH) {
+        float mlb[BATCH][FR];
+        float ob[BATCH][NT_O][FR];
 #pragma unroll
-                for (int n = 0; n < NT_O; ++n)
-                    *reinterpret_cast<float2*>(dst + n * 8 + qcol) = make_float2(o_acc[n][2 * rs], o_acc[n][2 * rs + 1]);
-                if ((lane & 3) == 0) {
-                    // natural-log units for the caller: m_nat = m_2 * ln 2
-                    prm.ml_partial[hrow * 2] = m_run[rs] * 0.6931471805599453f;
-                    prm.ml_partial[hrow * 2 + 1] = l_run[rs];
+        for (int bi = 0; bi < BATCH; ++bi) {
+            const uint32_t k = (k0 + bi < sd.n_parts) ? k0 + bi : sd.n_parts - 1;
+            const size_t u = static_cast<size_t>(sd.first_slot + k) * kDecodeWarps + warp;
+            if (G16) {
+                const float4 ml = reinterpret_cast<const float4*>(prm.work_ml)[u * 32 + lane];
+                mlb[bi][0] = ml.x; mlb[bi][1] = ml.y; mlb[bi][FR - 2] = ml.z; mlb[bi][FR - 1] = ml.w;
+                const float4* wo = reinterpret_cast<const float4*>(prm.work_o) + u * NT_O * 32;
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n) {
+                    const float4 v = wo[n * 32 + lane];
+                    ob[bi][n][0] = v.x; ob[bi][n][1] = v.y; ob[bi][n][FR - 2] = v.z; ob[bi][n][FR - 1] = v.w;
                 }
             } else {
-                const float inv = l_run[rs] > 0.f ? 1.0f / l_run[rs] : 0.f;
-                if (prm.o_f32) {
-                    float* dst = static_cast<float*>(prm.o) + hrow * D;
+                const float2 ml = reinterpret_cast<const float2*>(prm.work_ml)[u * 32 + lane];
+                mlb[bi][0] = ml.x; mlb[bi][1] = ml.y;
+                const float2* wo = reinterpret_cast<const float2*>(prm.work_o) + u * NT_O * 32;
 #pragma unroll
-                    for (int n = 0; n < NT_O; ++n)
-                        *reinterpret_cast<float2*>(dst + n * 8 + qcol) =
-                            make_float2(o_acc[n][2 * rs] * inv, o_acc[n][2 * rs + 1] * inv);
-                } else {
-                    __half* dst = static_cast<__half*>(prm.o) + hrow * D;
+                for (int n = 0; n < NT_O; ++n) {
+                    const float2 v = wo[n * 32 + lane];
+                    ob[bi][n][0] = v.x; ob[bi][n][1] = v.y;
+                }
+            }
+        }
 #pragma unroll
-                    for (int n = 0; n < NT_O; ++n)
-                        *reinterpret_cast<__half2*>(dst + n * 8 + qcol) =
-                            __floats2half2_rn(o_acc[n][2 * rs] * inv, o_acc[n][2 * rs + 1] * inv);
+        for (int bi = 0; bi < BATCH; ++bi) {
+            if (k0 + bi >= sd.n_parts) break;
+#pragma unroll
+            for (int rs = 0; rs < ROWSETS; ++rs) {
+                const float mk = mlb[bi][2 * rs], lk = mlb[bi][2 * rs + 1];  // mk is finite
+                const float m_new = fmaxf(m_run[rs], mk);
+                const float a = ex2(m_run[rs] - m_new), w = ex2(mk - m_new);
+                l_run[rs] = l_run[rs] * a + lk * w;
+                m_run[rs] = m_new;
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n) {
+                    o_acc[n][2 * rs] = o_acc[n][2 * rs] * a + ob[bi][n][2 * rs] * w;
+                    o_acc[n][2 * rs + 1] = o_acc[n][2 * rs + 1] * a + ob[bi][n][2 * rs + 1] * w;
                 }
             }
         }
     }
+    write_rows<D, G16>(prm, sd.req, head, lane, o_acc, m_run, l_run);
 }
 
 // ------------------------------------------------------------------------------
@@ -559,8 +690,8 @@ bool decode_tma_shape_supported(size_t H, size_t KVH, size_t D, size_t P, size_t
     if (D != 64 && D != 128) return false;
     if (P % kTileTokens != 0 || P / kTileTokens > 8) return false;
     if (KVH == 0 || H / KVH > 16) return false;
-    if ((KVH + kDecodeWarps - 1) / kDecodeWarps > 16) return false;
-    if (capacity == 0 || capacity > (size_t(1) << 25)) return false;
+    if ((KVH + kDecodeWarps - 1) / kDecodeWarps > kTileHbMask + 1) return false;
+    if (capacity == 0 || capacity > kTilePageMask + size_t(1)) return false;
     return true;
 }
 
@@ -569,39 +700,73 @@ bool decode_tma_pointers_supported(const AttnArgs& a) {
     if (!aligned(a.q, a.q_dtype == MLC_F32 ? 8 : 4)) return false;
     if (a.o && !aligned(a.o, a.o_dtype == MLC_F32 ? 8 : 4)) return false;
     if (a.o_partial && (!aligned(a.o_partial, 8) || !a.ml_partial)) return false;
+    if (a.k_new && (!aligned(a.k_new, 16) || !aligned(a.v_new, 16))) return false;
     return true;
 }
 
+// Deepest TMA ring that fits in the SM's shared memory.
+uint32_t decode_tma_max_stages(size_t H, size_t KVH, size_t D) {
+    (void)H; (void)KVH;
+    const size_t stage = static_cast<size_t>(kDecodeWarps) * 2 * kTileTokens * D * 2;
+    const size_t avail = 227 * 1024 - 2048;
+    return static_cast<uint32_t>(std::min<size_t>(8, avail / stage));
+}
+
 template <int D, bool G16>
-static int launch_t(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan, const DecodeParams& prm,
-                    const CUtensorMap* mk, const CUtensorMap* mv, uint32_t stages) {
-    const size_t smem = static_cast<size_t>(kDecodeWarps) * stages * (2 * kTileTokens * D * 2) + 1024;
+static int launch_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams& prm, const CUtensorMap& mk,
+                    const CUtensorMap& mv) {
+    const size_t smem = static_cast<size_t>(kDecodeWarps) * plan.stages * (2 * kTileTokens * D * 2) + 1024;
     size_t& configured = ctx->decode_smem_set[(D == 128 ? 2 : 0) + (G16 ? 1 : 0)];
     if (smem > configured) {
         MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_decode_tma_kernel<D, G16>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
-    (void)a;
-    paged_decode_tma_kernel<D, G16><<<plan.n_cta, kDecodeWarps * 32, smem, ctx->stream>>>(*mk, *mv, prm);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(plan.n_cta);
+    cfg.blockDim = dim3(kDecodeWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = prm.pdl ? 1 : 0;
+    MLCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<D, G16>, mk, mv, prm));
     ++ctx->launches;
-    MLCB_CUDA(ctx, cudaGetLastError());
+    if (plan.n_segs) {
+        // the merge is always chained programmatically: before its wait it touches nothing
+        cudaLaunchConfig_t mc{};
+        mc.gridDim = dim3(plan.n_segs);
+        mc.blockDim = dim3(kDecodeWarps * 32);
+        mc.dynamicSmemBytes = 0;
+        mc.stream = ctx->stream;
+        mc.attrs = attr;
+        mc.numAttrs = 1;
+        MLCB_CUDA(ctx, cudaLaunchKernelEx(&mc, paged_decode_merge_kernel<D, G16>, prm));
+        ++ctx->launches;
+    }
     return MLC_OK;
 }
 
 int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan) {
     const uint32_t G = static_cast<uint32_t>(a.H / a.KVH);
     const bool g16 = G > 8;
+    const bool step = a.k_new != nullptr;
     const size_t frag_floats = (g16 ? 4 : 2) * 32 * (a.D / 8);  // per (slot, warp)
     const size_t ml_floats = (g16 ? 4 : 2) * 32;
     const size_t units = static_cast<size_t>(plan.n_slots) * kDecodeWarps;
-    const size_t o_bytes = units * frag_floats * 4, ml_bytes = units * ml_floats * 4;
-    int st = ensure_workspace(ctx, o_bytes + ml_bytes + 256, static_cast<size_t>(plan.n_segs) * kDecodeWarps + 1);
+    const size_t o_bytes = ((units * frag_floats * 4 + 255) / 256) * 256;
+    const size_t ml_bytes = ((units * ml_floats * 4 + 255) / 256) * 256;
+    // Two copies of the workspace, used alternately: with programmatic dependent launch
+    // the next attention kernel may publish partials while this one's merge still reads.
+    int st = ensure_workspace(ctx, 2 * (o_bytes + ml_bytes) + 512, 0);
     if (st != MLC_OK) return st;
-    const CUtensorMap *mk = nullptr, *mv = nullptr;
+    CUtensorMap mk, mv;
     if ((st = get_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
-    CUtensorMap mk_copy = *mk;  // the cache may grow while the second map is made
     if ((st = get_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
+    const uint32_t parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
+    char* work = static_cast<char*>(ctx->d_work) + parity * (ctx->work_bytes / 2 / 256 * 256);
 
     DecodeParams prm{};
     prm.q = a.q;
@@ -612,29 +777,36 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     prm.pieces = plan.pieces;
     prm.tile_pages = plan.tile_pages;
     prm.zero_rows = plan.zero_rows;
-    prm.work_o = static_cast<float*>(ctx->d_work);
-    prm.work_ml = reinterpret_cast<float*>(static_cast<char*>(ctx->d_work) + ((o_bytes + 255) / 256) * 256);
-    prm.counters = ctx->d_counters;
+    prm.seg_desc = plan.seg_desc;
+    prm.work_o = reinterpret_cast<float*>(work);
+    prm.work_ml = reinterpret_cast<float*>(work + o_bytes);
     prm.err = ctx->d_err;
+    prm.k_new = static_cast<const __half*>(a.k_new);
+    prm.v_new = static_cast<const __half*>(a.v_new);
+    prm.k_pool = static_cast<__half*>(const_cast<void*>(a.k_pages));
+    prm.v_pool = static_cast<__half*>(const_cast<void*>(a.v_pages));
     prm.max_pieces = plan.max_pieces;
     prm.max_tiles = plan.max_tiles;
     prm.n_zero = plan.n_zero;
     prm.H = static_cast<uint32_t>(a.H);
     prm.KVH = static_cast<uint32_t>(a.KVH);
     prm.G = G;
-    prm.sub_per_page = static_cast<uint32_t>(a.P / kTileTokens);
+    prm.P = static_cast<uint32_t>(a.P);
     prm.scale_log2 = a.scale * 1.4426950408889634f;
     prm.q_f32 = a.q_dtype == MLC_F32;
     prm.o_f32 = a.o_dtype == MLC_F32;
-    const char* env = std::getenv("MLC_B200_DECODE_STAGES");
-    uint32_t stages = env && *env ? static_cast<uint32_t>(std::atoi(env)) : 3u;
-    if (stages < 1) stages = 1;
-    if (stages > 8) stages = 8;
-    prm.stages = stages;
-    if (a.D == 64) return g16 ? launch_t<64, true>(ctx, a, plan, prm, &mk_copy, mv, stages)
-                              : launch_t<64, false>(ctx, a, plan, prm, &mk_copy, mv, stages);
-    return g16 ? launch_t<128, true>(ctx, a, plan, prm, &mk_copy, mv, stages)
-               : launch_t<128, false>(ctx, a, plan, prm, &mk_copy, mv, stages);
+    prm.step = step ? 1 : 0;
+    // Every attention launch is allowed to start early: before its wait it reads only the
+    // plan (and, in a decode step, K/V rows of earlier steps).
+    prm.pdl = 1;
+    prm.stages = plan.stages;
+    // traces of consecutive launches alternate between the two halves of the buffer
+    const size_t trace_need = static_cast<size_t>(plan.n_cta) * kDecodeWarps * 8;
+    prm.trace = ctx->d_trace && trace_need <= ctx->trace_words / 2 ? ctx->d_trace + parity * (ctx->trace_words / 2) : nullptr;
+    ctx->trace_ctas = prm.trace ? plan.n_cta : 0;
+    ctx->trace_parity = parity;
+    if (a.D == 64) return g16 ? launch_t<64, true>(ctx, plan, prm, mk, mv) : launch_t<64, false>(ctx, plan, prm, mk, mv);
+    return g16 ? launch_t<128, true>(ctx, plan, prm, mk, mv) : launch_t<128, false>(ctx, plan, prm, mk, mv);
 }
 
 }  // namespace mlcb

@@ -18,15 +18,27 @@ struct AttnArgs {
     // Split-KV partial output (un-normalised o + (m, l) per row) instead of O.
     float* o_partial = nullptr;
     float* ml_partial = nullptr;
+    // Decode step: this step's new rows, fp16 [batch, KVH, D]; written into the pools by
+    // the attention kernel itself (the pools are then written to, not only read).
+    const void* k_new = nullptr;
+    const void* v_new = nullptr;
 };
 
 // ---- work plan of the TMA / tensor-core kernel ----------------------------------
 // The kernel is persistent: CTA c owns a contiguous range of "tiles" in the order
 // (request, head block, tile), a tile being kTileTokens consecutive tokens of one
 // request for the kDecodeWarps KV heads of one head block. A maximal run of tiles
-// with the same (request, head block) inside a CTA's range is a piece.
+// with the same (request, head block) inside a CTA's range is a piece; a (request,
+// head block) whose tiles span several CTAs is a split segment, whose pieces are
+// merged by a second, tiny kernel.
 static constexpr int kDecodeWarps = 4;   // KV heads per head block = warps per CTA
 static constexpr int kTileTokens = 32;   // tokens per pipeline stage
+// Tile word: page id | sub-tile within the page | head block | "holds this step's new token".
+static constexpr uint32_t kTilePageMask = (1u << 22) - 1;
+static constexpr uint32_t kTileSubShift = 22;
+static constexpr uint32_t kTileHbShift = 25;
+static constexpr uint32_t kTileHbMask = 0x3Fu;
+static constexpr uint32_t kTileFreshBit = 1u << 31;
 
 struct PieceDesc {
     uint32_t req;
@@ -34,13 +46,17 @@ struct PieceDesc {
     uint32_t n_tiles;
     uint32_t part_slot;       // workspace slot this piece writes when n_parts > 1
     uint32_t seg_first_slot;  // first workspace slot of the (request, head block) segment
-    uint32_t seg;             // segment index: arrival counters seg*kDecodeWarps + warp
+    uint32_t seg;             // index of the split segment (0 when not split)
     uint16_t n_parts;         // pieces the segment is split into (1: write O directly)
     uint16_t hb;              // head block: KV heads hb*kDecodeWarps ...
     uint16_t last_valid;      // valid tokens in the piece's last tile, 1..kTileTokens
-    uint16_t pad;
+    uint16_t flags;           // bit 0: the piece's last tile ends with the request's newest token
 };
 static_assert(sizeof(PieceDesc) == 32, "PieceDesc is read as two 16-byte vectors");
+
+struct SegDesc {              // one split (request, head block): input of the merge kernel
+    uint32_t req, hb, first_slot, n_parts;
+};
 
 struct DecodePlanView {            // device addresses inside one plan blob
     const uint32_t* cta_counts;    // [n_cta][2] = {pieces, tiles}
@@ -50,7 +66,10 @@ struct DecodePlanView {            // device addresses inside one plan blob
     const uint32_t* pt_off;
     const uint32_t* eff_len;       // tokens each request attends to
     const uint32_t* zero_rows;     // requests with eff_len == 0 (their O rows are zero-filled)
+    const SegDesc* seg_desc;       // [n_segs] split segments
     bool has_tma = false;          // the per-CTA tile lists above were built
+    bool step_fusable = false;     // every request's newest token is the last one it attends to
+    uint32_t stages = 3;           // ring depth the plan was cut for
     uint32_t n_cta = 0, max_pieces = 0, max_tiles = 0, n_zero = 0;
     uint32_t n_slots = 0, n_segs = 0;
 };
@@ -61,6 +80,8 @@ int launch_attention_general(mlc_ctx* ctx, const AttnArgs& a, const uint32_t* d_
 // True when the TMA / tensor-core kernel covers this shape / these pointers.
 bool decode_tma_shape_supported(size_t H, size_t KVH, size_t D, size_t P, size_t capacity);
 bool decode_tma_pointers_supported(const AttnArgs& a);
+// Deepest TMA ring that fits in shared memory next to the kernel's merge buffers.
+uint32_t decode_tma_max_stages(size_t H, size_t KVH, size_t D);
 // One launch writing this step's K and V rows; page ids and slots already on the device.
 int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, const uint32_t* d_ids,
                                       const uint32_t* d_slots, size_t P, size_t KVH, size_t D,

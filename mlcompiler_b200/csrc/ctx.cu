@@ -7,6 +7,7 @@
 // CUDA stream.
 #include "ctx.hpp"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace mlcb {
@@ -139,8 +140,26 @@ int mlc_ctx_create(int device, void* stream, mlc_ctx** out) {
         delete ctx;
         return MLC_ERR_CUDA;
     }
+    if (const char* t = std::getenv("MLC_B200_TRACE"); t && *t == '1') {
+        ctx->trace_words = size_t(1) << 16;
+        if (cudaMalloc(reinterpret_cast<void**>(&ctx->d_trace), ctx->trace_words * 8) != cudaSuccess) ctx->d_trace = nullptr;
+        else cudaMemset(ctx->d_trace, 0, ctx->trace_words * 8);
+    }
     *out = ctx;
     return MLC_OK;
+}
+
+// Copies the phase stamps of the last traced decode launch: [ctas][4 warps][8] u64
+// nanosecond timestamps. Returns the number of CTAs, 0 when tracing is off.
+uint32_t mlc_ctx_read_trace(mlc_ctx* ctx, unsigned long long* out, size_t max_words, int previous) {
+    if (!ctx || !ctx->d_trace || !out) return 0;
+    DeviceGuard guard(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    size_t words = static_cast<size_t>(ctx->trace_ctas) * 32;
+    if (words > max_words) words = max_words;
+    const uint32_t half = previous ? 1u - ctx->trace_parity : ctx->trace_parity;
+    cudaMemcpy(out, ctx->d_trace + half * (ctx->trace_words / 2), words * 8, cudaMemcpyDeviceToHost);
+    return ctx->trace_ctas;
 }
 
 void mlc_ctx_destroy(mlc_ctx* ctx) {
@@ -157,6 +176,7 @@ void mlc_ctx_destroy(mlc_ctx* ctx) {
     if (ctx->d_work) cudaFree(ctx->d_work);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
     if (ctx->d_err) cudaFree(ctx->d_err);
+    if (ctx->d_trace) cudaFree(ctx->d_trace);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }

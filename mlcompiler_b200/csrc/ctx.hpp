@@ -41,6 +41,7 @@ struct mlc_ctx {
     int force_general = 0;
     int last_attention_kernel = 0;  // 0 none yet, 1 general, 2 TMA / tensor-core
     uint64_t launches = 0;
+    uint64_t decode_launches = 0;   // selects the workspace copy of the split-KV kernel
     std::string last_error;
     std::unordered_map<const void*, size_t> allocs;
     std::unordered_map<std::string, std::pair<void*, size_t>> cached;
@@ -52,6 +53,11 @@ struct mlc_ctx {
     uint32_t* d_counters = nullptr;
     size_t n_counters = 0;
     size_t decode_smem_set[4] = {0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
+    // optional per-warp phase stamps of the last decode launch (env MLC_B200_TRACE=1)
+    unsigned long long* d_trace = nullptr;
+    size_t trace_words = 0;
+    uint32_t trace_ctas = 0;
+    uint32_t trace_parity = 0;  // which half of d_trace the most recent launch wrote
     mlcb::AttnPlanCache* plan_cache = nullptr;
     mlcb::TensorMapCache* tmap_cache = nullptr;
 
