@@ -236,6 +236,32 @@ int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
                                          const void* k_new, const void* v_new, void* k_pages,
                                          void* v_pages, void* o, float scale, int q_dtype, int o_dtype);
 
+/* Planned attention that allocates nothing (no counterpart in the reference, whose
+ * kernel never splits a sequence and so needs no scratch). For callers that must not
+ * allocate device memory when they call: a server that has given the whole GPU to its
+ * own memory pool (a later cudaMalloc would fail or fragment it), or a decode loop that
+ * cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply. Same
+ * arguments and result as mlc_encode_paged_flash_attention_planned, but the split-KV
+ * scratch is a fixed 8 MiB array inside the library (mlc_static_scratch_bytes(); every
+ * GPU that loads the library holds it until exit) instead of the context's growing
+ * workspace; the call makes no cudaMalloc / cudaFree and no host allocation.
+ *   - Limit: a batch whose split requests need more than 4 MiB of partials (about 450
+ *     request pieces at head_dim 64) is rejected with MLC_ERR_UNSUPPORTED and a message
+ *     naming the sizes; use the regular entry point for it. The plan itself is created
+ *     beforehand with mlc_attn_plan_create, which does allocate.
+ *   - The first call on a device resolves the array's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture.
+ *   - All calls on a GPU share the array. Nothing in it has to start at zero (every
+ *     partial is fully written before it is read), but two such calls that overlap on
+ *     the GPU - different contexts or streams of the same device - race on it.
+ *     Consecutive calls on one context are safe: they alternate between its two halves
+ *     and are stream-ordered. */
+size_t mlc_static_scratch_bytes(void);
+int mlc_encode_paged_flash_attention_planned_static(mlc_ctx* ctx, const mlc_attn_plan* plan,
+                                                    const void* q, const void* k_pages,
+                                                    const void* v_pages, void* o, float scale,
+                                                    int q_dtype, int o_dtype);
+
 /* ---- split-KV across GPUs (no counterpart in the reference: it has one device) -------
  * A rank that holds only a slice of every request's pages computes, over its
  * slice, the un-normalised state of the online softmax instead of O:

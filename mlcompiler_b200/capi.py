@@ -70,6 +70,8 @@ _PROTOTYPES = {
     "mlc_attn_plan_destroy": (None, [_vp, _vp]),
     "mlc_encode_paged_flash_attention_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_scatter_kv_pair_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "mlc_static_scratch_bytes": (_sz, []),
+    "mlc_encode_paged_flash_attention_planned_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_paged_decode_step_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_paged_attention_partial_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i]),
     "mlc_encode_lse_combine": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _i]),
@@ -330,6 +332,17 @@ class Executor:
         return self.status(self._lib.mlc_encode_paged_decode_step_planned(
             self._h, plan.handle, _vp(_ptr(q)), _vp(_ptr(k_new)), _vp(_ptr(v_new)), _vp(_ptr(k_pages)),
             _vp(_ptr(v_pages)), _vp(_ptr(o)), float(scale), q_dtype, o_dtype))
+
+    def encodePagedFlashAttentionPlannedStatic(self, plan, q, k_pages, v_pages, o, scale=0.0, q_dtype=MLC_F32,
+                                               o_dtype=MLC_F32) -> bool:
+        """Same as encodePagedFlashAttentionPlanned, but allocates nothing: the split-KV
+        scratch is the library's fixed 8 MiB array (see include/mlc_b200.h for the limits)."""
+        return self.status(self._lib.mlc_encode_paged_flash_attention_planned_static(
+            self._h, plan.handle, _vp(_ptr(q)), _vp(_ptr(k_pages)), _vp(_ptr(v_pages)), _vp(_ptr(o)),
+            float(scale), q_dtype, o_dtype))
+
+    def staticScratchBytes(self) -> int:
+        return int(self._lib.mlc_static_scratch_bytes())
 
     def encodeScatterKVPairPlanned(self, plan, k_storage, v_storage, k_src, v_src) -> bool:
         return self.status(self._lib.mlc_encode_scatter_kv_pair_planned(

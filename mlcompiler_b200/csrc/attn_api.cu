@@ -360,6 +360,11 @@ int attention_impl(mlc_ctx* ctx, bool sync, AttnArgs a, const uint32_t* pt_flat,
 }
 
 }  // namespace
+
+int launch_attention_with_plan(mlc_ctx* ctx, AttnArgs a, const mlc_attn_plan* plan) {
+    return launch_with_plan(ctx, a, *plan);
+}
+
 }  // namespace mlcb
 
 using namespace mlcb;

@@ -89,6 +89,26 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 // Map over one pool viewed as [capacity][P][KVH][D] halfs; box = 64 halfs of one
 // KV head for kTileTokens consecutive slots of one page, 128-byte swizzled.
+// Encodes the map for one pool; pure host arithmetic inside the driver, no allocation.
+static int encode_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, CUtensorMap* out) {
+    if (!ctx->tmap_encode_fn) {
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->tmap_encode_fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !ctx->tmap_encode_fn)
+            return ctx->fail(MLC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    }
+    cuuint64_t dims[4] = {a.D, a.KVH, a.P, a.capacity};
+    cuuint64_t strides[3] = {a.D * 2, a.KVH * a.D * 2, a.P * a.KVH * a.D * 2};
+    cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(kTileTokens), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode_fn)(
+        out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(pool), dims, strides, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ctx->fail(MLC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    return MLC_OK;
+}
+
 static int get_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, CUtensorMap* out) {
     if (!ctx->tmap_cache) ctx->tmap_cache = new TensorMapCache();
     TensorMapCache& tc = *ctx->tmap_cache;
@@ -97,22 +117,9 @@ static int get_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, CUt
             *out = e.map;
             return MLC_OK;
         }
-    if (!tc.encode_fn) {
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &tc.encode_fn, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess || !tc.encode_fn)
-            return ctx->fail(MLC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    }
     TensorMapCache::Entry e{pool, a.D, a.KVH, a.P, a.capacity, {}};
-    cuuint64_t dims[4] = {a.D, a.KVH, a.P, a.capacity};
-    cuuint64_t strides[3] = {a.D * 2, a.KVH * a.D * 2, a.P * a.KVH * a.D * 2};
-    cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(kTileTokens), 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = reinterpret_cast<EncodeTiledFn>(tc.encode_fn)(
-        &e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(pool), dims, strides, box, estr,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return ctx->fail(MLC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    int st = encode_tensor_map(ctx, pool, a, &e.map);
+    if (st != MLC_OK) return st;
     if (tc.entries.size() >= 256) tc.entries.erase(tc.entries.begin());
     tc.entries.push_back(e);
     *out = e.map;
@@ -760,13 +767,30 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     const size_t ml_bytes = ((units * ml_floats * 4 + 255) / 256) * 256;
     // Two copies of the workspace, used alternately: with programmatic dependent launch
     // the next attention kernel may publish partials while this one's merge still reads.
-    int st = ensure_workspace(ctx, 2 * (o_bytes + ml_bytes) + 512, 0);
-    if (st != MLC_OK) return st;
+    int st = MLC_OK;
     CUtensorMap mk, mv;
-    if ((st = get_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
-    if ((st = get_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
-    const uint32_t parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
-    char* work = static_cast<char*>(ctx->d_work) + parity * (ctx->work_bytes / 2 / 256 * 256);
+    char* work = nullptr;
+    uint32_t parity = 0;
+    if (a.ext_work) {
+        // Caller-provided workspace: nothing is allocated on this path, neither on the
+        // device nor (the tensor maps are encoded on the stack, uncached) on the host.
+        const size_t half = a.ext_work_bytes / 2 / 256 * 256;
+        if (o_bytes + ml_bytes > half)
+            return ctx->fail(MLC_ERR_UNSUPPORTED,
+                             "this batch needs %zu bytes of split-KV scratch per copy, the fixed scratch holds %zu",
+                             o_bytes + ml_bytes, half);
+        if ((st = encode_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
+        if ((st = encode_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
+        parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
+        work = static_cast<char*>(a.ext_work) + parity * half;
+    } else {
+        st = ensure_workspace(ctx, 2 * (o_bytes + ml_bytes) + 512, 0);
+        if (st != MLC_OK) return st;
+        if ((st = get_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
+        if ((st = get_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
+        parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
+        work = static_cast<char*>(ctx->d_work) + parity * (ctx->work_bytes / 2 / 256 * 256);
+    }
 
     DecodeParams prm{};
     prm.q = a.q;

@@ -3,6 +3,8 @@
 
 #include "ctx.hpp"
 
+struct mlc_attn_plan;
+
 namespace mlcb {
 
 // One attention call after validation (host arrays already checked).
@@ -22,6 +24,10 @@ struct AttnArgs {
     // the attention kernel itself (the pools are then written to, not only read).
     const void* k_new = nullptr;
     const void* v_new = nullptr;
+    // Caller-provided split-KV workspace (device memory) instead of the context's own;
+    // when set, the launch makes no device or host allocation at all.
+    void* ext_work = nullptr;
+    size_t ext_work_bytes = 0;
 };
 
 // ---- work plan of the TMA / tensor-core kernel ----------------------------------
@@ -87,5 +93,7 @@ int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, 
                                       const uint32_t* d_slots, size_t P, size_t KVH, size_t D,
                                       size_t batch, const void* k_src, const void* v_src, size_t capacity);
 int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan);
+// Launches attention for an already created plan (the plan's shape fields fill `a`).
+int launch_attention_with_plan(mlc_ctx* ctx, AttnArgs a, const mlc_attn_plan* plan);
 
 }  // namespace mlcb

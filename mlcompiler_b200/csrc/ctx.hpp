@@ -60,6 +60,7 @@ struct mlc_ctx {
     uint32_t trace_parity = 0;  // which half of d_trace the most recent launch wrote
     mlcb::AttnPlanCache* plan_cache = nullptr;
     mlcb::TensorMapCache* tmap_cache = nullptr;
+    void* tmap_encode_fn = nullptr;  // cuTensorMapEncodeTiled, resolved through the runtime
 
     int fail(int status, const char* fmt, ...) {
         char buf[512];
