@@ -291,6 +291,135 @@ int mlc_graph_end_capture(mlc_ctx* ctx, mlc_graph** out);
 int mlc_graph_launch(mlc_ctx* ctx, mlc_graph* graph);
 void mlc_graph_destroy(mlc_ctx* ctx, mlc_graph* graph);
 
+/* ======================================================================================
+ * Host-side objects (C++17 inside the library, like the reference's): page allocator,
+ * per-request page tables, per-layer paged storage, executor, scheduler.
+ * int-returning functions in this part return 1 for "ok / has value" and 0 for the
+ * reference's nullopt / false, unless they say mlc_status.
+ * ====================================================================================== */
+
+/* ---- PagePool (compiler/runtime/paged_kv.hpp:28-53, paged_kv.cpp:10-42): LIFO free list
+ * of page ids; a fresh pool hands out 0, 1, 2, ...; allocate_n is all-or-nothing. */
+typedef struct mlc_page_pool mlc_page_pool;
+mlc_page_pool* mlc_page_pool_create(uint32_t capacity);
+void mlc_page_pool_destroy(mlc_page_pool* pool);
+int mlc_page_pool_allocate(mlc_page_pool* pool, uint32_t* page_id);
+int mlc_page_pool_allocate_n(mlc_page_pool* pool, size_t n, uint32_t* out /* [n] */);
+/* release: the reference asserts on a bad id (paged_kv.cpp:37-42); this returns 0 and
+ * changes nothing. */
+int mlc_page_pool_release(mlc_page_pool* pool, uint32_t page_id);
+uint32_t mlc_page_pool_capacity(const mlc_page_pool* pool);
+size_t mlc_page_pool_in_use(const mlc_page_pool* pool);
+size_t mlc_page_pool_free(const mlc_page_pool* pool);
+
+/* ---- RequestKVState (paged_kv.hpp:65-97, paged_kv.cpp:44-81) */
+typedef struct mlc_kv_state mlc_kv_state;
+mlc_kv_state* mlc_kv_state_create(uint32_t request_id, uint32_t page_size_tokens);
+void mlc_kv_state_destroy(mlc_kv_state* state);
+int mlc_kv_state_reserve(mlc_kv_state* state, mlc_page_pool* pool, size_t target_tokens);
+int mlc_kv_state_extend_one_token(mlc_kv_state* state, mlc_page_pool* pool, uint32_t* page_id,
+                                  uint32_t* slot_in_page);
+int mlc_kv_state_locate(const mlc_kv_state* state, size_t pos, uint32_t* page_id, uint32_t* slot_in_page);
+void mlc_kv_state_release_all(mlc_kv_state* state, mlc_page_pool* pool);
+size_t mlc_kv_state_total_tokens(const mlc_kv_state* state);
+uint32_t mlc_kv_state_tokens_in_last_page(const mlc_kv_state* state);
+/* Copies up to `capacity` page ids; returns the table's length. */
+size_t mlc_kv_state_page_table(const mlc_kv_state* state, uint32_t* out, size_t capacity);
+
+/* ---- PagedKVStorage (paged_kv.hpp:109-145, paged_kv.cpp:83-127): one zero-filled K pool
+ * and one V pool of capacity_pages * page_bytes per layer, owned by the object. */
+typedef struct mlc_kv_storage mlc_kv_storage;
+mlc_kv_storage* mlc_kv_storage_create(mlc_ctx* ctx, uint32_t capacity_pages, uint32_t n_layers,
+                                      uint32_t page_size_tokens, uint32_t n_kv_heads, uint32_t head_dim,
+                                      uint32_t dtype_bytes);
+void mlc_kv_storage_destroy(mlc_kv_storage* storage);
+int mlc_kv_storage_initialize(mlc_kv_storage* storage);
+void* mlc_kv_storage_k_buffer(const mlc_kv_storage* storage, size_t layer);
+void* mlc_kv_storage_v_buffer(const mlc_kv_storage* storage, size_t layer);
+size_t mlc_kv_storage_page_bytes(const mlc_kv_storage* storage);
+
+/* ---- executors (compiler/runtime/batched_executor.hpp:33-57: RequestSlot,
+ * BatchedDecodeOutput, IBatchedExecutor) */
+typedef struct mlc_request_slot {
+    uint32_t request_id;
+    uint64_t input_token;
+    uint64_t sequence_position;
+} mlc_request_slot;
+typedef struct mlc_decode_row {      /* BatchedDecodeOutput::PerRequest */
+    uint32_t request_id;
+    int success;
+    const float* logits;             /* valid until the callback is entered again */
+    size_t n_logits;
+} mlc_decode_row;
+/* An IBatchedExecutor implemented by the caller (the seam the reference's scheduler tests
+ * mock, tests/test_scheduler.cpp:22-60). run_decode fills rows[0..n) and returns how many
+ * it filled; run_prefill returns the number of logits and points *logits at them. */
+typedef struct mlc_executor_callbacks {
+    void* user;
+    size_t (*run_decode)(void* user, const mlc_request_slot* slots, size_t n, mlc_decode_row* rows);
+    size_t (*run_prefill)(void* user, uint32_t request_id, const uint64_t* tokens, size_t n, const float** logits);
+    void (*release_request)(void* user, uint32_t request_id);
+} mlc_executor_callbacks;
+
+typedef struct mlc_executor mlc_executor;
+/* The paged-attention part of the reference's BatchedExecutor + BatchedWalker
+ * (batched_executor.cpp:29-65, 96-103, 445-467; batched_walker.cpp:127-149, 299-331):
+ * per-request page state, one batched pass = extend every request by one token, then per
+ * layer write the new K/V rows and run attention. The model around attention is out of
+ * scope: Q and the new K/V rows come from a deterministic hash of (seed, request, token,
+ * position, layer) - see mlc_hash_qkv_value - and the "logits" are the last layer's
+ * attention output, num_heads * head_dim floats per request. */
+mlc_executor* mlc_paged_executor_create(mlc_ctx* ctx, uint32_t num_heads, uint32_t kv_heads, uint32_t head_dim,
+                                        uint32_t n_layers, uint64_t qkv_seed);
+mlc_executor* mlc_callback_executor_create(const mlc_executor_callbacks* callbacks);
+void mlc_executor_destroy(mlc_executor* exec);
+/* attach_page_pool / attach_paged_storage (batched_executor.hpp:73, 90); mlc_status. */
+int mlc_executor_attach_page_pool(mlc_executor* exec, mlc_page_pool* pool, uint32_t page_size_tokens);
+int mlc_executor_attach_paged_storage(mlc_executor* exec, mlc_kv_storage* storage);
+/* 0 (default): one fused launch per layer; 1: the reference's order - scatter K, scatter V,
+ * attention with host tables per layer (batched_walker.cpp:299-331). mlc_status. */
+int mlc_executor_set_call_order(mlc_executor* exec, int reference_order);
+/* run_decode: returns the number of per-request results; success[i] and, for successful
+ * requests, logits[i * logits_stride ...] are filled. */
+size_t mlc_executor_run_decode(mlc_executor* exec, const mlc_request_slot* slots, size_t n, uint8_t* success,
+                               float* logits, size_t logits_stride);
+/* run_prefill: returns the number of logits (0 = failed). */
+size_t mlc_executor_run_prefill(mlc_executor* exec, uint32_t request_id, const uint64_t* tokens, size_t n,
+                                float* logits, size_t capacity);
+void mlc_executor_release_request(mlc_executor* exec, uint32_t request_id);
+size_t mlc_executor_live_request_count(const mlc_executor* exec);
+size_t mlc_executor_known_position(const mlc_executor* exec, uint32_t request_id);
+/* page_state() (batched_executor.hpp:77): copies the request's page ids, returns their count. */
+size_t mlc_executor_page_table(const mlc_executor* exec, uint32_t request_id, uint32_t* out, size_t capacity,
+                               size_t* total_tokens);
+/* Element `index` of tensor 0 (Q), 1 (K row) or 2 (V row) the paged executor feeds. */
+float mlc_hash_qkv_value(uint64_t seed, uint32_t request, uint64_t token, uint64_t position, uint32_t layer,
+                         uint32_t tensor, uint32_t index);
+
+/* ---- Scheduler (compiler/runtime/scheduler.hpp:27-104, scheduler.cpp:10-186) */
+typedef struct mlc_scheduler mlc_scheduler;
+typedef void (*mlc_token_callback)(void* user, uint32_t request_id, uint64_t token);
+mlc_scheduler* mlc_scheduler_create(mlc_executor* exec, size_t max_batch_size /* reference default 8 */);
+void mlc_scheduler_destroy(mlc_scheduler* sched);
+uint32_t mlc_scheduler_add_request(mlc_scheduler* sched, const uint64_t* prompt_tokens, size_t n,
+                                   size_t max_new_tokens /* reference default 100 */,
+                                   int64_t eos_token_id /* -1 disables */);
+void mlc_scheduler_set_token_callback(mlc_scheduler* sched, mlc_token_callback cb, void* user);
+int mlc_scheduler_tick(mlc_scheduler* sched);
+size_t mlc_scheduler_run_until_idle(mlc_scheduler* sched);
+int mlc_scheduler_empty(const mlc_scheduler* sched);
+size_t mlc_scheduler_queued_count(const mlc_scheduler* sched);
+size_t mlc_scheduler_active_count(const mlc_scheduler* sched);
+size_t mlc_scheduler_completed_count(const mlc_scheduler* sched);
+void mlc_scheduler_stats(const mlc_scheduler* sched, size_t* requests_completed, size_t* decode_steps,
+                         size_t* tokens_generated);
+/* drain_completed(): moves the completed requests into the handle and returns their count;
+ * mlc_scheduler_drained_request reads one of them (state: 0 Queued, 1 Prefilling, 2 Decoding,
+ * 3 Complete, 4 Failed). */
+size_t mlc_scheduler_drain_completed(mlc_scheduler* sched);
+int mlc_scheduler_drained_request(const mlc_scheduler* sched, size_t index, uint32_t* id, int* state,
+                                  size_t* n_generated, uint64_t* generated, size_t capacity);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,124 @@
+// Executor interface the scheduler drives, and the paged-attention executor behind it.
+//
+// RequestSlot / BatchedDecodeOutput / IBatchedExecutor carry the reference's names and
+// meaning (compiler/runtime/batched_executor.hpp:33-57). PagedAttentionExecutor is the
+// part of the reference's BatchedExecutor that belongs to the paged-attention path
+// (batched_executor.hpp:59-141, batched_executor.cpp:29-65, 96-103, 445-467): per-request
+// page state, pool / storage attachment, page release, decode routed to the batched
+// walker, prefill as a loop of single-token decode passes. The model around attention
+// (embeddings, mat-vecs, norms, logits) is out of this repository's scope: Q and the new
+// K/V rows of every layer come from an IQkvSource, and what the reference returns as
+// logits is here the attention output of the last layer.
+#pragma once
+
+#include <cstdint>
+#include <memory>
+#include <unordered_map>
+#include <vector>
+
+#include "paged_kv.hpp"
+
+struct mlc_ctx;
+struct mlc_attn_plan;
+
+namespace mlcb {
+namespace runtime {
+
+struct RequestSlot {
+    uint32_t request_id = 0;
+    uint64_t input_token = 0;
+    size_t sequence_position = 0;
+};
+
+struct BatchedDecodeOutput {
+    struct PerRequest {
+        uint32_t request_id = 0;
+        bool success = false;
+        std::vector<float> logits;  // empty on failure
+    };
+    std::vector<PerRequest> per_request;
+};
+
+class IBatchedExecutor {
+public:
+    virtual ~IBatchedExecutor() = default;
+    virtual BatchedDecodeOutput run_decode(const std::vector<RequestSlot>& slots) = 0;
+    virtual std::vector<float> run_prefill(uint32_t request_id, const std::vector<uint64_t>& tokens) = 0;
+    virtual void release_request(uint32_t request_id) = 0;
+};
+
+// Supplies, for one layer of one pass, what the projections before attention would:
+// q fp32 [N, H, D] and the new K / V rows as fp16 bits [N, KVH, D], on the host.
+class IQkvSource {
+public:
+    virtual ~IQkvSource() = default;
+    virtual void fill(uint32_t layer, const std::vector<RequestSlot>& slots, uint32_t H, uint32_t KVH, uint32_t D,
+                      float* q, uint16_t* k_new, uint16_t* v_new) = 0;
+};
+
+// Deterministic stand-in: every element is a hash of (seed, request, token, position,
+// layer, tensor, index) mapped onto the grid {-1024..1023}/1024, which fp16 holds exactly.
+class HashQkvSource : public IQkvSource {
+public:
+    explicit HashQkvSource(uint64_t seed) : seed_(seed) {}
+    void fill(uint32_t layer, const std::vector<RequestSlot>& slots, uint32_t H, uint32_t KVH, uint32_t D,
+              float* q, uint16_t* k_new, uint16_t* v_new) override;
+    static float value(uint64_t seed, uint32_t request, uint64_t token, uint64_t position, uint32_t layer,
+                       uint32_t tensor, uint32_t index);
+
+private:
+    uint64_t seed_;
+};
+
+class BatchedWalker;
+
+class PagedAttentionExecutor : public IBatchedExecutor {
+    friend class BatchedWalker;
+
+public:
+    enum class CallOrder {
+        Fused,      // one launch per layer: KV row write fused into attention
+        Reference,  // the reference walker's order: scatter K, scatter V, attention
+    };
+
+    PagedAttentionExecutor(mlc_ctx* ctx, uint32_t num_heads, uint32_t kv_heads, uint32_t head_dim,
+                           uint32_t n_layers, std::unique_ptr<IQkvSource> source);
+    ~PagedAttentionExecutor() override;
+
+    void attach_page_pool(PagePool* pool, uint32_t page_size_tokens = 64);
+    void attach_paged_storage(PagedKVStorage* storage) { storage_ = storage; }
+    void set_call_order(CallOrder o) { order_ = o; }
+    const RequestKVState* page_state(uint32_t request_id) const;
+
+    BatchedDecodeOutput run_decode(const std::vector<RequestSlot>& slots) override;
+    std::vector<float> run_prefill(uint32_t request_id, const std::vector<uint64_t>& tokens) override;
+    void release_request(uint32_t request_id) override;
+    void reset();
+
+    size_t known_position(uint32_t request_id) const;
+    size_t live_request_count() const { return requests_.size(); }
+    uint32_t num_heads() const { return H_; }
+    uint32_t kv_heads() const { return KVH_; }
+    uint32_t head_dim() const { return D_; }
+    uint32_t n_layers() const { return L_; }
+
+private:
+    struct PerRequest {
+        size_t next_position = 0;
+        std::unique_ptr<RequestKVState> page_state;
+    };
+    PerRequest& ensure_request(uint32_t request_id);
+
+    mlc_ctx* ctx_;
+    uint32_t H_, KVH_, D_, L_;
+    std::unique_ptr<IQkvSource> source_;
+    std::unordered_map<uint32_t, PerRequest> requests_;
+    PagePool* pool_ = nullptr;
+    uint32_t page_size_tokens_ = 64;
+    PagedKVStorage* storage_ = nullptr;
+    CallOrder order_ = CallOrder::Fused;
+    std::unique_ptr<BatchedWalker> walker_;
+};
+
+}  // namespace runtime
+}  // namespace mlcb

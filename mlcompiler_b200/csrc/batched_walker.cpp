@@ -1,0 +1,132 @@
+// See batched_walker.hpp.
+#include "batched_walker.hpp"
+
+#include <cmath>
+#include <cstring>
+
+#include "ctx.hpp"
+
+namespace mlcb {
+namespace runtime {
+
+BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
+    BatchedDecodeOutput out;
+    if (slots.empty()) return out;
+    PagedAttentionExecutor& ex = exec_;
+    mlc_ctx* ctx = ex.ctx_;
+    PagedKVStorage* storage = ex.storage_;
+    const size_t N = slots.size();
+    const uint32_t H = ex.H_, KVH = ex.KVH_, D = ex.D_, P = storage->page_size_tokens();
+    auto fail_all = [&]() {
+        out.per_request.clear();
+        for (const auto& s : slots) {
+            BatchedDecodeOutput::PerRequest p;
+            p.request_id = s.request_id;
+            out.per_request.push_back(std::move(p));
+        }
+        return out;
+    };
+
+    // One new token per request: extend the page tables. If the pool runs out, every slot of
+    // the pass is reported failed and the requests extended so far keep their extension,
+    // exactly as in the reference (batched_walker.cpp:127-149).
+    std::vector<PagedAttentionExecutor::PerRequest*> reqs(N, nullptr);
+    std::vector<uint32_t> page_ids(N), slot_ids(N);
+    for (size_t r = 0; r < N; ++r) {
+        reqs[r] = &ex.ensure_request(slots[r].request_id);
+        if (!reqs[r]->page_state) {
+            reqs[r]->page_state.reset(new RequestKVState());
+            reqs[r]->page_state->request_id = slots[r].request_id;
+            reqs[r]->page_state->page_size_tokens = ex.page_size_tokens_;
+        }
+        auto loc = reqs[r]->page_state->extend_one_token(*ex.pool_);
+        if (!loc) return fail_all();
+        page_ids[r] = loc->first;
+        slot_ids[r] = loc->second;
+    }
+
+    // Tables of the pass, built once (the reference rebuilds them per layer, 316-325):
+    // seq_lens count the new token, q_pos is the new token's own position.
+    std::vector<uint32_t> pt_flat, pt_off(N + 1, 0), seq_lens(N), q_pos(N);
+    for (size_t r = 0; r < N; ++r) {
+        pt_off[r] = static_cast<uint32_t>(pt_flat.size());
+        const auto& table = reqs[r]->page_state->page_table;
+        pt_flat.insert(pt_flat.end(), table.begin(), table.end());
+        seq_lens[r] = static_cast<uint32_t>(reqs[r]->page_state->total_tokens());
+        q_pos[r] = static_cast<uint32_t>(slots[r].sequence_position);
+    }
+    pt_off[N] = static_cast<uint32_t>(pt_flat.size());
+
+    // Name-keyed persistent device buffers, as the reference's walker keeps (163-180).
+    const size_t q_bytes = N * H * D * sizeof(float), kv_bytes = N * KVH * D * sizeof(uint16_t);
+    void* buf_q = mlc_cached_buffer(ctx, "walker_q", q_bytes * ex.L_);
+    void* buf_k = mlc_cached_buffer(ctx, "walker_kv_f16_k", kv_bytes * ex.L_);
+    void* buf_v = mlc_cached_buffer(ctx, "walker_kv_f16_v", kv_bytes * ex.L_);
+    void* buf_o = mlc_cached_buffer(ctx, "walker_attn_mix", q_bytes);
+    if (!buf_q || !buf_k || !buf_v || !buf_o) return fail_all();
+
+    q_host_.resize(N * H * D * ex.L_);
+    k_host_.resize(N * KVH * D * ex.L_);
+    v_host_.resize(N * KVH * D * ex.L_);
+    for (uint32_t layer = 0; layer < ex.L_; ++layer)
+        ex.source_->fill(layer, slots, H, KVH, D, q_host_.data() + static_cast<size_t>(layer) * N * H * D,
+                         k_host_.data() + static_cast<size_t>(layer) * N * KVH * D,
+                         v_host_.data() + static_cast<size_t>(layer) * N * KVH * D);
+    if (mlc_upload(ctx, buf_q, q_host_.data(), q_bytes * ex.L_, 0) != MLC_OK ||
+        mlc_upload(ctx, buf_k, k_host_.data(), kv_bytes * ex.L_, 0) != MLC_OK ||
+        mlc_upload(ctx, buf_v, v_host_.data(), kv_bytes * ex.L_, 0) != MLC_OK)
+        return fail_all();
+
+    const float scale = 1.0f / std::sqrt(static_cast<float>(D));
+    const size_t cap = storage->capacity_pages();
+    const bool fused = ex.order_ == PagedAttentionExecutor::CallOrder::Fused;
+    mlc_attn_plan* plan = nullptr;
+    if (fused && mlc_attn_plan_create(ctx, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
+                                      q_pos.data(), page_ids.data(), slot_ids.data(), N, H, KVH, D, P, 1, cap,
+                                      &plan) != MLC_OK)
+        return fail_all();
+
+    bool ok = mlc_pass_begin(ctx) == MLC_OK;
+    for (uint32_t layer = 0; ok && layer < ex.L_; ++layer) {
+        const char* q_l = static_cast<const char*>(buf_q) + static_cast<size_t>(layer) * q_bytes;
+        const char* k_l = static_cast<const char*>(buf_k) + static_cast<size_t>(layer) * kv_bytes;
+        const char* v_l = static_cast<const char*>(buf_v) + static_cast<size_t>(layer) * kv_bytes;
+        void* kp = storage->k_buffer(layer);
+        void* vp = storage->v_buffer(layer);
+        if (fused) {
+            ok = mlc_encode_paged_decode_step_planned(ctx, plan, q_l, k_l, v_l, kp, vp, buf_o, scale, MLC_F32,
+                                                      MLC_F32) == MLC_OK;
+        } else {
+            // the reference's call order (batched_walker.cpp:299-331)
+            ok = mlc_encode_scatter_kv_paged_batched_f16(ctx, kp, page_ids.data(), slot_ids.data(), P, KVH, D, N,
+                                                         k_l, cap) == MLC_OK &&
+                 mlc_encode_scatter_kv_paged_batched_f16(ctx, vp, page_ids.data(), slot_ids.data(), P, KVH, D, N,
+                                                         v_l, cap) == MLC_OK &&
+                 mlc_encode_paged_flash_attention(ctx, q_l, kp, vp, buf_o, pt_flat.data(), pt_flat.size(),
+                                                  pt_off.data(), seq_lens.data(), q_pos.data(), N, H, KVH, D, P, 1,
+                                                  scale, MLC_F32, MLC_F32, cap) == MLC_OK;
+        }
+    }
+    ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
+    if (plan) mlc_attn_plan_destroy(ctx, plan);
+    if (!ok) return fail_all();
+
+    // what the reference downloads as logits [N, vocab] (461-475) is the last layer's
+    // attention output [N, H*D] here
+    o_host_.resize(N * H * D);
+    if (mlc_download(ctx, buf_o, o_host_.data(), q_bytes, 0) != MLC_OK) return fail_all();
+    out.per_request.reserve(N);
+    for (size_t r = 0; r < N; ++r) {
+        BatchedDecodeOutput::PerRequest p;
+        p.request_id = slots[r].request_id;
+        p.success = true;
+        p.logits.assign(o_host_.begin() + static_cast<std::ptrdiff_t>(r * H * D),
+                        o_host_.begin() + static_cast<std::ptrdiff_t>((r + 1) * H * D));
+        reqs[r]->next_position = slots[r].sequence_position + 1;
+        out.per_request.push_back(std::move(p));
+    }
+    return out;
+}
+
+}  // namespace runtime
+}  // namespace mlcb

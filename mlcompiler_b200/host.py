@@ -1,0 +1,397 @@
+"""ctypes binding of the host-side objects of include/mlc_b200.h under the reference's
+class and method names (compiler/runtime/paged_kv.hpp, batched_executor.hpp,
+scheduler.hpp), so that the host-logic tests read like the reference's
+tests/test_paged_kv.cpp and tests/test_scheduler.cpp. None of these needs a GPU except
+PagedKVStorage.initialize and the paged executor's passes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from .capi import load_library
+
+_vp, _sz, _u32, _u64, _i = C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint64, C.c_int
+_u32p, _u64p, _fp, _szp = C.POINTER(C.c_uint32), C.POINTER(C.c_uint64), C.POINTER(C.c_float), C.POINTER(C.c_size_t)
+
+
+class RequestSlotC(C.Structure):
+    _fields_ = [("request_id", _u32), ("input_token", _u64), ("sequence_position", _u64)]
+
+
+class DecodeRowC(C.Structure):
+    _fields_ = [("request_id", _u32), ("success", _i), ("logits", _fp), ("n_logits", _sz)]
+
+
+RUN_DECODE_CB = C.CFUNCTYPE(_sz, _vp, C.POINTER(RequestSlotC), _sz, C.POINTER(DecodeRowC))
+RUN_PREFILL_CB = C.CFUNCTYPE(_sz, _vp, _u32, _u64p, _sz, C.POINTER(_fp))
+RELEASE_CB = C.CFUNCTYPE(None, _vp, _u32)
+TOKEN_CB = C.CFUNCTYPE(None, _vp, _u32, _u64)
+
+
+class ExecutorCallbacksC(C.Structure):
+    _fields_ = [("user", _vp), ("run_decode", RUN_DECODE_CB), ("run_prefill", RUN_PREFILL_CB),
+                ("release_request", RELEASE_CB)]
+
+
+_PROTOTYPES = {
+    "mlc_page_pool_create": (_vp, [_u32]),
+    "mlc_page_pool_destroy": (None, [_vp]),
+    "mlc_page_pool_allocate": (_i, [_vp, _u32p]),
+    "mlc_page_pool_allocate_n": (_i, [_vp, _sz, _u32p]),
+    "mlc_page_pool_release": (_i, [_vp, _u32]),
+    "mlc_page_pool_capacity": (_u32, [_vp]),
+    "mlc_page_pool_in_use": (_sz, [_vp]),
+    "mlc_page_pool_free": (_sz, [_vp]),
+    "mlc_kv_state_create": (_vp, [_u32, _u32]),
+    "mlc_kv_state_destroy": (None, [_vp]),
+    "mlc_kv_state_reserve": (_i, [_vp, _vp, _sz]),
+    "mlc_kv_state_extend_one_token": (_i, [_vp, _vp, _u32p, _u32p]),
+    "mlc_kv_state_locate": (_i, [_vp, _sz, _u32p, _u32p]),
+    "mlc_kv_state_release_all": (None, [_vp, _vp]),
+    "mlc_kv_state_total_tokens": (_sz, [_vp]),
+    "mlc_kv_state_tokens_in_last_page": (_u32, [_vp]),
+    "mlc_kv_state_page_table": (_sz, [_vp, _u32p, _sz]),
+    "mlc_kv_storage_create": (_vp, [_vp, _u32, _u32, _u32, _u32, _u32, _u32]),
+    "mlc_kv_storage_destroy": (None, [_vp]),
+    "mlc_kv_storage_initialize": (_i, [_vp]),
+    "mlc_kv_storage_k_buffer": (_vp, [_vp, _sz]),
+    "mlc_kv_storage_v_buffer": (_vp, [_vp, _sz]),
+    "mlc_kv_storage_page_bytes": (_sz, [_vp]),
+    "mlc_paged_executor_create": (_vp, [_vp, _u32, _u32, _u32, _u32, _u64]),
+    "mlc_callback_executor_create": (_vp, [C.POINTER(ExecutorCallbacksC)]),
+    "mlc_executor_destroy": (None, [_vp]),
+    "mlc_executor_attach_page_pool": (_i, [_vp, _vp, _u32]),
+    "mlc_executor_attach_paged_storage": (_i, [_vp, _vp]),
+    "mlc_executor_set_call_order": (_i, [_vp, _i]),
+    "mlc_executor_run_decode": (_sz, [_vp, C.POINTER(RequestSlotC), _sz, C.POINTER(C.c_uint8), _fp, _sz]),
+    "mlc_executor_run_prefill": (_sz, [_vp, _u32, _u64p, _sz, _fp, _sz]),
+    "mlc_executor_release_request": (None, [_vp, _u32]),
+    "mlc_executor_live_request_count": (_sz, [_vp]),
+    "mlc_executor_known_position": (_sz, [_vp, _u32]),
+    "mlc_executor_page_table": (_sz, [_vp, _u32, _u32p, _sz, _szp]),
+    "mlc_hash_qkv_value": (C.c_float, [_u64, _u32, _u64, _u64, _u32, _u32, _u32]),
+    "mlc_scheduler_create": (_vp, [_vp, _sz]),
+    "mlc_scheduler_destroy": (None, [_vp]),
+    "mlc_scheduler_add_request": (_u32, [_vp, _u64p, _sz, _sz, C.c_int64]),
+    "mlc_scheduler_set_token_callback": (None, [_vp, TOKEN_CB, _vp]),
+    "mlc_scheduler_tick": (_i, [_vp]),
+    "mlc_scheduler_run_until_idle": (_sz, [_vp]),
+    "mlc_scheduler_empty": (_i, [_vp]),
+    "mlc_scheduler_queued_count": (_sz, [_vp]),
+    "mlc_scheduler_active_count": (_sz, [_vp]),
+    "mlc_scheduler_completed_count": (_sz, [_vp]),
+    "mlc_scheduler_stats": (None, [_vp, _szp, _szp, _szp]),
+    "mlc_scheduler_drain_completed": (_sz, [_vp]),
+    "mlc_scheduler_drained_request": (_i, [_vp, _sz, _u32p, C.POINTER(_i), _szp, _u64p, _sz]),
+}
+
+_LIB = None
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        l = load_library()
+        for name, (res, args) in _PROTOTYPES.items():
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+        _LIB = l
+    return _LIB
+
+
+class PagePool:
+    def __init__(self, capacity: int):
+        self._h = _vp(lib().mlc_page_pool_create(capacity))
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _LIB is not None:
+            _LIB.mlc_page_pool_destroy(self._h)
+            self._h = None
+
+    def allocate(self):
+        """Page id, or None when the pool is exhausted (std::nullopt in the reference)."""
+        v = _u32(0)
+        return v.value if lib().mlc_page_pool_allocate(self._h, C.byref(v)) else None
+
+    def allocate_n(self, n: int, out: list) -> bool:
+        buf = (C.c_uint32 * max(n, 1))()
+        if not lib().mlc_page_pool_allocate_n(self._h, n, buf):
+            return False
+        out.extend(buf[i] for i in range(n))
+        return True
+
+    def release(self, page_id: int) -> bool:
+        return bool(lib().mlc_page_pool_release(self._h, page_id))
+
+    def capacity(self) -> int:
+        return lib().mlc_page_pool_capacity(self._h)
+
+    def pages_in_use(self) -> int:
+        return lib().mlc_page_pool_in_use(self._h)
+
+    def pages_free(self) -> int:
+        return lib().mlc_page_pool_free(self._h)
+
+
+class RequestKVState:
+    def __init__(self, page_size_tokens: int = 64, request_id: int = 0):
+        self._h = _vp(lib().mlc_kv_state_create(request_id, page_size_tokens))
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _LIB is not None:
+            _LIB.mlc_kv_state_destroy(self._h)
+            self._h = None
+
+    def reserve(self, pool: PagePool, target_tokens: int) -> bool:
+        return bool(lib().mlc_kv_state_reserve(self._h, pool._h, target_tokens))
+
+    def extend_one_token(self, pool: PagePool):
+        p, s = _u32(0), _u32(0)
+        ok = lib().mlc_kv_state_extend_one_token(self._h, pool._h, C.byref(p), C.byref(s))
+        return (p.value, s.value) if ok else None
+
+    def locate(self, pos: int):
+        p, s = _u32(0), _u32(0)
+        ok = lib().mlc_kv_state_locate(self._h, pos, C.byref(p), C.byref(s))
+        return (p.value, s.value) if ok else None
+
+    def release_all(self, pool: PagePool):
+        lib().mlc_kv_state_release_all(self._h, pool._h)
+
+    def total_tokens(self) -> int:
+        return lib().mlc_kv_state_total_tokens(self._h)
+
+    @property
+    def tokens_in_last_page(self) -> int:
+        return lib().mlc_kv_state_tokens_in_last_page(self._h)
+
+    @property
+    def page_table(self) -> list:
+        n = lib().mlc_kv_state_page_table(self._h, None, 0)
+        buf = (C.c_uint32 * max(n, 1))()
+        lib().mlc_kv_state_page_table(self._h, buf, n)
+        return [buf[i] for i in range(n)]
+
+
+class PagedKVStorage:
+    def __init__(self, executor, capacity_pages, n_layers, page_size_tokens, n_kv_heads, head_dim, dtype_bytes=2):
+        self._ex = executor
+        self._h = _vp(lib().mlc_kv_storage_create(executor.handle, capacity_pages, n_layers, page_size_tokens,
+                                                   n_kv_heads, head_dim, dtype_bytes))
+        self.capacity_pages, self.n_layers = capacity_pages, n_layers
+
+    def destroy(self):
+        if getattr(self, "_h", None) and _LIB is not None and self._ex._h:
+            _LIB.mlc_kv_storage_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+    def initialize(self) -> bool:
+        return bool(lib().mlc_kv_storage_initialize(self._h))
+
+    def k_buffer(self, layer: int) -> int:
+        return int(lib().mlc_kv_storage_k_buffer(self._h, layer) or 0)
+
+    def v_buffer(self, layer: int) -> int:
+        return int(lib().mlc_kv_storage_v_buffer(self._h, layer) or 0)
+
+    def page_bytes(self) -> int:
+        return lib().mlc_kv_storage_page_bytes(self._h)
+
+
+class _ExecutorBase:
+    _h = None
+
+    def destroy(self):
+        if self._h and _LIB is not None:
+            _LIB.mlc_executor_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class PagedAttentionExecutor(_ExecutorBase):
+    """The built-in executor: page state + batched walker over the CUDA kernels."""
+
+    def __init__(self, executor, num_heads, kv_heads, head_dim, n_layers, qkv_seed=0):
+        self._ctx = executor
+        self.H, self.KVH, self.D, self.L, self.seed = num_heads, kv_heads, head_dim, n_layers, qkv_seed
+        self._h = _vp(lib().mlc_paged_executor_create(executor.handle, num_heads, kv_heads, head_dim, n_layers, qkv_seed))
+        if not self._h:
+            raise ValueError("bad executor shape")
+
+    def attach_page_pool(self, pool: PagePool, page_size_tokens: int = 64):
+        self._pool = pool
+        assert lib().mlc_executor_attach_page_pool(self._h, pool._h, page_size_tokens) == 0
+
+    def attach_paged_storage(self, storage: PagedKVStorage):
+        self._storage = storage
+        assert lib().mlc_executor_attach_paged_storage(self._h, storage._h) == 0
+
+    def set_call_order(self, reference_order: bool):
+        assert lib().mlc_executor_set_call_order(self._h, 1 if reference_order else 0) == 0
+
+    def run_decode(self, slots):
+        """slots: [(request_id, input_token, sequence_position)] -> [(request_id, success, logits or None)]"""
+        n = len(slots)
+        arr = (RequestSlotC * max(n, 1))(*[RequestSlotC(*s) for s in slots])
+        success = (C.c_uint8 * max(n, 1))()
+        stride = self.H * self.D
+        logits = np.zeros((max(n, 1), stride), np.float32)
+        got = lib().mlc_executor_run_decode(self._h, arr, n, success, logits.ctypes.data_as(_fp), stride)
+        return [(slots[i][0], bool(success[i]), logits[i].copy() if success[i] else None) for i in range(got)]
+
+    def run_prefill(self, request_id, tokens):
+        toks = (C.c_uint64 * max(len(tokens), 1))(*tokens)
+        out = np.zeros(self.H * self.D, np.float32)
+        n = lib().mlc_executor_run_prefill(self._h, request_id, toks, len(tokens), out.ctypes.data_as(_fp), out.size)
+        return out[:n].copy()
+
+    def release_request(self, request_id):
+        lib().mlc_executor_release_request(self._h, request_id)
+
+    def live_request_count(self) -> int:
+        return lib().mlc_executor_live_request_count(self._h)
+
+    def known_position(self, request_id) -> int:
+        return lib().mlc_executor_known_position(self._h, request_id)
+
+    def page_state(self, request_id):
+        """(page_table, total_tokens) of a tracked request, or None."""
+        total = _sz(0)
+        n = lib().mlc_executor_page_table(self._h, request_id, None, 0, C.byref(total))
+        if n == 0:
+            return None
+        buf = (C.c_uint32 * n)()
+        lib().mlc_executor_page_table(self._h, request_id, buf, n, C.byref(total))
+        return [buf[i] for i in range(n)], total.value
+
+
+class CallbackExecutor(_ExecutorBase):
+    """An IBatchedExecutor implemented in Python. Subclass and override run_decode(slots) ->
+    [(request_id, success, logits)], run_prefill(request_id, tokens) -> logits, release_request(id)."""
+
+    def __init__(self):
+        self._keep = []
+
+        def _decode(user, slots, n, rows):
+            out = self.run_decode([(slots[i].request_id, slots[i].input_token, slots[i].sequence_position)
+                                   for i in range(n)])
+            self._keep = []
+            for i, (rid, ok, logits) in enumerate(out[:n]):
+                rows[i].request_id = rid
+                rows[i].success = 1 if ok else 0
+                if ok and logits is not None:
+                    a = np.ascontiguousarray(logits, dtype=np.float32)
+                    self._keep.append(a)
+                    rows[i].logits = a.ctypes.data_as(_fp)
+                    rows[i].n_logits = a.size
+                else:
+                    rows[i].logits = None
+                    rows[i].n_logits = 0
+            return min(len(out), n)
+
+        def _prefill(user, rid, tokens, n, logits_out):
+            a = np.ascontiguousarray(self.run_prefill(rid, [tokens[i] for i in range(n)]), dtype=np.float32)
+            self._keep_prefill = a
+            logits_out[0] = a.ctypes.data_as(_fp)
+            return a.size
+
+        def _release(user, rid):
+            self.release_request(rid)
+
+        self._cbs = ExecutorCallbacksC(None, RUN_DECODE_CB(_decode), RUN_PREFILL_CB(_prefill), RELEASE_CB(_release))
+        self._h = _vp(lib().mlc_callback_executor_create(C.byref(self._cbs)))
+
+
+class Scheduler:
+    QUEUED, PREFILLING, DECODING, COMPLETE, FAILED = range(5)
+
+    def __init__(self, executor, max_batch_size: int = 8):
+        self._exec = executor
+        self._h = _vp(lib().mlc_scheduler_create(executor._h, max_batch_size))
+        self._token_cb = None
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _LIB is not None:
+            _LIB.mlc_scheduler_destroy(self._h)
+            self._h = None
+
+    def add_request(self, prompt_tokens, max_new_tokens: int = 100, eos_token_id: int = -1) -> int:
+        toks = (C.c_uint64 * max(len(prompt_tokens), 1))(*prompt_tokens)
+        return lib().mlc_scheduler_add_request(self._h, toks, len(prompt_tokens), max_new_tokens, eos_token_id)
+
+    def set_token_callback(self, fn):
+        self._token_cb = TOKEN_CB(lambda user, rid, tok: fn(rid, tok))
+        lib().mlc_scheduler_set_token_callback(self._h, self._token_cb, None)
+
+    def tick(self) -> bool:
+        return bool(lib().mlc_scheduler_tick(self._h))
+
+    def run_until_idle(self) -> int:
+        return lib().mlc_scheduler_run_until_idle(self._h)
+
+    def empty(self) -> bool:
+        return bool(lib().mlc_scheduler_empty(self._h))
+
+    def queued_count(self) -> int:
+        return lib().mlc_scheduler_queued_count(self._h)
+
+    def active_count(self) -> int:
+        return lib().mlc_scheduler_active_count(self._h)
+
+    def completed_count(self) -> int:
+        return lib().mlc_scheduler_completed_count(self._h)
+
+    def stats(self) -> dict:
+        a, b, c = _sz(0), _sz(0), _sz(0)
+        lib().mlc_scheduler_stats(self._h, C.byref(a), C.byref(b), C.byref(c))
+        return {"total_requests_completed": a.value, "total_decode_steps": b.value, "total_tokens_generated": c.value}
+
+    def drain_completed(self) -> list:
+        n = lib().mlc_scheduler_drain_completed(self._h)
+        out = []
+        for i in range(n):
+            rid, state, ng = _u32(0), _i(0), _sz(0)
+            lib().mlc_scheduler_drained_request(self._h, i, C.byref(rid), C.byref(state), C.byref(ng), None, 0)
+            buf = (C.c_uint64 * max(ng.value, 1))()
+            lib().mlc_scheduler_drained_request(self._h, i, None, None, None, buf, ng.value)
+            out.append({"id": rid.value, "state": state.value, "generated_tokens": [buf[j] for j in range(ng.value)]})
+        return out
+
+
+def hash_qkv_value(seed, request, token, position, layer, tensor, index) -> float:
+    return float(lib().mlc_hash_qkv_value(seed, request, token, position, layer, tensor, index))
+
+
+def hash_qkv_tensor(seed, request, token, position, layer, tensor, n) -> np.ndarray:
+    """numpy restatement of the paged executor's Q/K/V stand-in (csrc/batched_executor.cpp):
+    n elements of tensor 0 (Q), 1 (K row) or 2 (V row)."""
+    M = np.uint64(0xFFFFFFFFFFFFFFFF)
+
+    def mix(x):
+        x = (x + np.uint64(0x9E3779B97F4A7C15)) & M
+        x = ((x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)) & M
+        x = ((x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)) & M
+        return x ^ (x >> np.uint64(31))
+
+    with np.errstate(over="ignore"):
+        h = mix(np.uint64(seed) ^ np.uint64(0xA24BAED4963EE407))
+        h = mix(h ^ np.uint64(request))
+        h = mix(h ^ np.uint64(token))
+        h = mix(h ^ np.uint64(position))
+        h = mix(h ^ np.uint64((layer << 8) | tensor))
+        hv = mix(h ^ np.arange(n, dtype=np.uint64))
+    v = ((hv >> np.uint64(20)) & np.uint64(0x7FF)).astype(np.int64) - 1024
+    return (v / 1024.0).astype(np.float32)
