@@ -38,8 +38,8 @@ def build_port(force: bool = False) -> Path:
 
 
 def build_ref():
-    from . import build_ref as _b
-    return _b.build(verbose=False)
+    import importlib
+    return importlib.import_module(__name__ + ".build_ref").build(verbose=False)
 
 
 _port = None
