@@ -44,9 +44,10 @@ UNIT = "GB/s"
 WORKLOAD = ("cfg2: 22-layer continuous-batching decode, 32 requests, H32/KVH4/D64, fp16 KV, 64-token pages, "
             "contexts U[64,2048], random page tables, pool = pages + 10%; per layer: scatter 1 new K/V row "
             "per request, then attention")
-# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch of this workload,
-# from the ncu capture summarised in profiles/decode_attention_cfg2.md (null until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch of this workload
+# (37.71 MB read + 3.6 KB written), from the ncu capture summarised in
+# profiles/decode_attention_cfg2.md; the algorithmic KV bytes of that launch are 37.00 MB.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 37_715_712
 
 
 def measured_peak_gbs():

@@ -187,7 +187,8 @@ int mlc_encode_paged_flash_attention(mlc_ctx* ctx, const void* q, const void* k_
  * 0 = automatic (TMA + tensor-core split-KV kernel when the shape allows it,
  * otherwise the general kernel), 1 = always the general kernel. Both are CUDA. */
 int mlc_ctx_set_attention_kernel(mlc_ctx* ctx, int which);
-/* Which family the most recent attention call used: 0 none yet, 1 general, 2 TMA. */
+/* Which family the most recent attention call used: 0 none yet, 1 general, 2 TMA decode,
+ * 3 tcgen05 chunked prefill. */
 int mlc_ctx_last_attention_kernel(const mlc_ctx* ctx);
 
 /* ---- device-resident plans --------------------------------------------------------
@@ -278,6 +279,35 @@ int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan
                                                int q_dtype);
 int mlc_encode_lse_combine(mlc_ctx* ctx, const float* o_parts, const float* ml_parts, size_t parts,
                            size_t rows, size_t head_dim, void* out, int o_dtype);
+
+/* ---- chunked (multi-token) causal paged attention ------------------------------------
+ * The reference runs a paged prefill as q_len single-token decode passes
+ * (compiler/runtime/batched_executor.cpp:450-467); these entry points compute the same
+ * result for all query tokens of all requests in one launch. Query i of request r sits
+ * at position q_start[r] + i and attends to kv_pos <= q_start[r] + i (the mask rule of
+ * metal_runtime.mm:2286, what compiler/runtime/operator_backend.cpp:906-968 computes for
+ * seq_len > 1). Requires q_start[r] + q_len[r] <= seq_lens[r]: the chunk's K/V rows are
+ * scattered into the pages first, the reference's order (batched_walker.cpp:299-331).
+ *   q, o   [sum_r q_len[r], num_heads, head_dim], request after request
+ *   tables as in mlc_encode_paged_flash_attention
+ * With fp16 q and o, head_dim 128 and 64-token pages the work runs on tcgen05 tensor
+ * cores (accumulators in tensor memory, operands staged by TMA); every other shape /
+ * dtype runs the any-shape kernel, one row per query token.
+ * mlc_ctx_last_attention_kernel reports 3 for the tcgen05 kernel. */
+int mlc_run_paged_prefill_attention(mlc_ctx* ctx, const void* q, const void* k_pages, const void* v_pages,
+                                    void* o, const uint32_t* page_tables_flat, size_t n_page_tables_flat,
+                                    const uint32_t* page_table_offsets, const uint32_t* seq_lens,
+                                    const uint32_t* q_start, const uint32_t* q_len, size_t batch,
+                                    size_t num_heads, size_t kv_heads, size_t head_dim,
+                                    size_t page_size_tokens, float scale, int q_dtype, int o_dtype,
+                                    size_t capacity_pages);
+int mlc_encode_paged_prefill_attention(mlc_ctx* ctx, const void* q, const void* k_pages, const void* v_pages,
+                                       void* o, const uint32_t* page_tables_flat, size_t n_page_tables_flat,
+                                       const uint32_t* page_table_offsets, const uint32_t* seq_lens,
+                                       const uint32_t* q_start, const uint32_t* q_len, size_t batch,
+                                       size_t num_heads, size_t kv_heads, size_t head_dim,
+                                       size_t page_size_tokens, float scale, int q_dtype, int o_dtype,
+                                       size_t capacity_pages);
 
 /* ---- CUDA-graph bracketing of a pass --------------------------------------------------
  * Records the planned encode_* calls issued between begin and end into a CUDA graph

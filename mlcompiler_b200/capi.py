@@ -63,6 +63,10 @@ _PROTOTYPES = {
                                            _sz, _sz, _sz, _sz, _sz, _i, _f, _i, _i, _sz]),
     "mlc_encode_paged_flash_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p,
                                               _sz, _sz, _sz, _sz, _sz, _i, _f, _i, _i, _sz]),
+    "mlc_run_paged_prefill_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p,
+                                             _sz, _sz, _sz, _sz, _sz, _f, _i, _i, _sz]),
+    "mlc_encode_paged_prefill_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p,
+                                                _sz, _sz, _sz, _sz, _sz, _f, _i, _i, _sz]),
     "mlc_ctx_last_attention_kernel": (_i, [_vp]),
     "mlc_ctx_read_trace": (C.c_uint32, [_vp, C.POINTER(C.c_uint64), _sz, _i]),
     "mlc_attn_plan_create": (_i, [_vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p, _u32p, _sz, _sz, _sz, _sz, _sz,
@@ -287,6 +291,38 @@ class Executor:
                                page_tables_flat, page_table_offsets, seq_lens, q_positions, batch, num_heads,
                                kv_heads, head_dim, page_size_tokens, apply_causal, scale, q_dtype, o_dtype,
                                capacity_pages)
+
+    def _prefill(self, fn, q, k_pages, v_pages, o, page_tables_flat, page_table_offsets, seq_lens, q_start,
+                 q_len, batch, num_heads, kv_heads, head_dim, page_size_tokens, scale, q_dtype, o_dtype,
+                 capacity_pages) -> bool:
+        flat, pflat = _u32(page_tables_flat)
+        off, poff = _u32(page_table_offsets)
+        sl, psl = _u32(seq_lens)
+        qs, pqs = _u32(q_start)
+        ql, pql = _u32(q_len)
+        if off.size != batch + 1 or sl.size != batch or qs.size != batch or ql.size != batch:
+            return self.status(1)
+        return self.status(fn(self._h, _vp(_ptr(q)), _vp(_ptr(k_pages)), _vp(_ptr(v_pages)), _vp(_ptr(o)),
+                              pflat, flat.size, poff, psl, pqs, pql, batch, num_heads, kv_heads, head_dim,
+                              page_size_tokens, float(scale), q_dtype, o_dtype, capacity_pages))
+
+    def runPagedPrefillAttention(self, q, k_pages, v_pages, o, page_tables_flat, page_table_offsets, seq_lens,
+                                 q_start, q_len, batch, num_heads, kv_heads, head_dim, page_size_tokens,
+                                 scale: float = 0.0, q_dtype: int = MLC_F16, o_dtype: int = MLC_F16,
+                                 capacity_pages: int = 0) -> bool:
+        """Chunked causal attention: query i of request r is at position q_start[r] + i.
+        q / o are [sum(q_len), num_heads, head_dim]."""
+        return self._prefill(self._lib.mlc_run_paged_prefill_attention, q, k_pages, v_pages, o, page_tables_flat,
+                             page_table_offsets, seq_lens, q_start, q_len, batch, num_heads, kv_heads, head_dim,
+                             page_size_tokens, scale, q_dtype, o_dtype, capacity_pages)
+
+    def encodePagedPrefillAttention(self, q, k_pages, v_pages, o, page_tables_flat, page_table_offsets, seq_lens,
+                                    q_start, q_len, batch, num_heads, kv_heads, head_dim, page_size_tokens,
+                                    scale: float = 0.0, q_dtype: int = MLC_F16, o_dtype: int = MLC_F16,
+                                    capacity_pages: int = 0) -> bool:
+        return self._prefill(self._lib.mlc_encode_paged_prefill_attention, q, k_pages, v_pages, o,
+                             page_tables_flat, page_table_offsets, seq_lens, q_start, q_len, batch, num_heads,
+                             kv_heads, head_dim, page_size_tokens, scale, q_dtype, o_dtype, capacity_pages)
 
     def readTrace(self, previous: bool = False) -> np.ndarray:
         """[ctas, 4, 8] uint64 nanosecond stamps of the last traced decode launch

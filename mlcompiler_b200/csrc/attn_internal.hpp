@@ -93,6 +93,14 @@ int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, 
                                       const uint32_t* d_slots, size_t P, size_t KVH, size_t D,
                                       size_t batch, const void* k_src, const void* v_src, size_t capacity);
 int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan);
+
+// Chunked causal prefill on tcgen05 (attn_prefill_tcgen05.cu): D = 128, 64-token pages, fp16 q / o.
+bool prefill_tcgen05_supported(size_t H, size_t KVH, size_t D, size_t P, size_t capacity);
+int launch_prefill_tcgen05(mlc_ctx* ctx, const void* q, const void* k_pages, const void* v_pages, void* o,
+                           const uint32_t* d_pt_flat, const uint32_t* d_pt_off, const uint32_t* d_seq_lens,
+                           const uint32_t* d_q_start, const uint32_t* d_q_len, const uint32_t* d_q_row0,
+                           size_t batch, size_t total_q, size_t max_q_len, size_t H, size_t KVH, size_t capacity,
+                           float scale);
 // Launches attention for an already created plan (the plan's shape fields fill `a`).
 int launch_attention_with_plan(mlc_ctx* ctx, AttnArgs a, const mlc_attn_plan* plan);
 

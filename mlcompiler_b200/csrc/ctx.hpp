@@ -53,6 +53,7 @@ struct mlc_ctx {
     uint32_t* d_counters = nullptr;
     size_t n_counters = 0;
     size_t decode_smem_set[4] = {0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
+    bool prefill_smem_set = false;             // same, for the chunked-prefill kernel
     // optional per-warp phase stamps of the last decode launch (env MLC_B200_TRACE=1)
     unsigned long long* d_trace = nullptr;
     size_t trace_words = 0;
