@@ -58,7 +58,7 @@ int prefill_impl(mlc_ctx* ctx, bool sync, const void* q, const void* k_pages, co
     const bool tc = q_dtype == MLC_F16 && o_dtype == MLC_F16 && prefill_tcgen05_supported(H, KVH, D, P, capacity) &&
                     (reinterpret_cast<uintptr_t>(q) % 16 == 0) && (reinterpret_cast<uintptr_t>(o) % 16 == 0) &&
                     (reinterpret_cast<uintptr_t>(k_pages) % 128 == 0) && (reinterpret_cast<uintptr_t>(v_pages) % 128 == 0) &&
-                    !ctx->force_general;
+                    scale > 0.f && !ctx->force_general;  // the kernel orders raw scores: needs scale > 0
     int st;
     if (tc) {
         // one staging region: pt_flat | pt_off | seq_lens | q_start | q_len | q_row0

@@ -44,7 +44,12 @@ constexpr uint32_t kSubBytesKV = kKvTile * 128;  // one 64-half-wide slab of a K
 constexpr uint32_t kQBytes = 2 * kSubBytesQ;     // 32 KiB
 constexpr uint32_t kKvBytes = 2 * kSubBytesKV;   // 16 KiB per tensor
 constexpr uint32_t kPBytes = kQTile * 128;       // 16 KiB
-constexpr uint32_t kSmemBytes = kQBytes + kStages * 2 * kKvBytes + kPBytes + 1024;
+constexpr uint32_t kTileBytes = kQBytes + kStages * 2 * kKvBytes + kPBytes;  // 112 KiB
+struct Bars {
+    uint64_t q, kv_full[kStages], kv_empty[kStages], s_full[2], s_free[2], p_full, pv_done;
+    uint32_t tmem_slot;
+};
+constexpr uint32_t kSmemBytes = kTileBytes + sizeof(Bars);
 constexpr uint32_t kTmemCols = 256;              // O: 128 columns, S: 2 x 64 columns
 constexpr uint32_t kTmemO = 0, kTmemS = 128;
 
@@ -166,13 +171,20 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t M, uint32_t N, uint32_
 
 }  // namespace
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                              const __grid_constant__ CUtensorMap tmV, const PrefillParams prm) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[kStages], bar_kv_empty[kStages], bar_s_full[2], bar_s_free[2],
-        bar_p_full, bar_pv_done;
-    __shared__ uint32_t tmem_base_slot;
+    // All shared memory is dynamic (tiles first, barriers behind them) so that two CTAs fit one SM.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    Bars& bars = *reinterpret_cast<Bars*>(smem_raw + kTileBytes);
+    uint64_t& bar_q = bars.q;
+    uint64_t(&bar_kv_full)[kStages] = bars.kv_full;
+    uint64_t(&bar_kv_empty)[kStages] = bars.kv_empty;
+    uint64_t(&bar_s_full)[2] = bars.s_full;
+    uint64_t(&bar_s_free)[2] = bars.s_free;
+    uint64_t& bar_p_full = bars.p_full;
+    uint64_t& bar_pv_done = bars.pv_done;
+    uint32_t& tmem_base_slot = bars.tmem_slot;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t req = blockIdx.z, head = blockIdx.y, qt = blockIdx.x;
@@ -187,7 +199,11 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     const uint32_t kv_end = min(seq_len, q_start + qt * kQTile + q_rows);
     const uint32_t n_tiles = (kv_end + kKvTile - 1) / kKvTile;
 
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t base = smem_u32(smem_raw);
+    if (base & 1023u) {  // the 128-byte swizzle needs 1024-byte aligned tiles; never expected
+        if (threadIdx.x == 0) atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
+        return;
+    }
     const uint32_t sQ = base;
     const uint32_t sKV = sQ + kQBytes;                       // stage s: K at sKV + s*2*kKvBytes, V right after K
     const uint32_t sP = sKV + kStages * 2 * kKvBytes;
@@ -294,6 +310,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
         const uint32_t row = threadIdx.x;                      // 0..127 = TMEM lane
         const uint32_t lane_base = (warp * 32u) << 16;
         const uint32_t q_pos = q_start + qt * kQTile + row;    // position of this row's query token
+        const uint32_t q_pos_warp = q_start + qt * kQTile + warp * 32u;  // smallest position in this warp
+        const float rescale_step = 8.0f / prm.scale_log2;      // 2^8 in units of the unscaled scores
         float m_ref = -INFINITY, l_sum = 0.f;                  // reference maximum of the O accumulator, row sum
         bool ok = true;
         for (uint32_t j = 0; j < n_tiles; ++j) {
@@ -313,22 +331,50 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             mbar_arrive(smem_u32(&bar_s_free[j & 1u]));
             // mask: causal (kv_pos > q_pos) and past the end of the sequence
             const uint32_t kv0 = j * kKvTile;
-            float tmax = -INFINITY;
+            // Scores stay unscaled (scale > 0 keeps their order); the scale is folded into the
+            // exponent's FMA below. Only a tile that crosses the diagonal of some row of this
+            // warp, or the end of the sequence, pays for the mask (warp-uniform test).
+            if (kv0 + kKvTile - 1 > q_pos_warp || kv0 + kKvTile > seq_len) {
+                const uint32_t lim = min(q_pos + 1, seq_len);  // first masked position
 #pragma unroll
-            for (int c = 0; c < kKvTile; ++c) {
-                const uint32_t pos = kv0 + c;
-                float v = __uint_as_float(sreg[c]) * prm.scale_log2;
-                v = (pos <= q_pos && pos < seq_len) ? v : -INFINITY;
-                sreg[c] = __float_as_uint(v);
-                tmax = fmaxf(tmax, v);
+                for (int c = 0; c < kKvTile; ++c)
+                    if (kv0 + c >= lim) sreg[c] = 0xff800000u;  // -inf
             }
-            const float m_new = fmaxf(m_ref, tmax);
+            float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < kKvTile; c += 4) {
+                t0 = fmaxf(t0, __uint_as_float(sreg[c]));
+                t1 = fmaxf(t1, __uint_as_float(sreg[c + 1]));
+                t2 = fmaxf(t2, __uint_as_float(sreg[c + 2]));
+                t3 = fmaxf(t3, __uint_as_float(sreg[c + 3]));
+            }
+            const float m_new = fmaxf(m_ref, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
             // Rescale O only when this row's maximum outgrew the reference by more than 2^8
             // (P stays <= 256 otherwise, well inside fp16). The vote keeps the warp together:
             // tcgen05.ld / .st are warp-wide.
-            const bool need = (m_new > m_ref + 8.0f) || (m_ref == -INFINITY && m_new > -INFINITY);
-            const float alpha = need ? ((m_ref == -INFINITY) ? 0.f : ex2(m_ref - m_new)) : 1.0f;
+            const bool need = (m_new > m_ref + rescale_step) || (m_ref == -INFINITY && m_new > -INFINITY);
+            const float alpha = need ? ((m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * prm.scale_log2)) : 1.0f;
             if (need) m_ref = m_new;
+            l_sum *= alpha;
+            // P = exp2((s - m_ref) * scale), fp16, computed while the previous P.V may still run, then
+            // stored into the swizzled A-operand tile: row `row`, 8 chunks of 16 bytes
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * prm.scale_log2;
+            float ps[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[32];
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i]), prm.scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i + 1]), prm.scale_log2, neg_m));
+                    ps[i] += p0 + p1;
+                    __half2 h = __floats2half2_rn(p0, p1);
+                    w[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                pk[ch * 4 + 0] = w[0]; pk[ch * 4 + 1] = w[1]; pk[ch * 4 + 2] = w[2]; pk[ch * 4 + 3] = w[3];
+            }
+            l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
             // the previous P.V must be done before P (shared memory) or O (TMEM) are touched
             if (j > 0) {
                 ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (j - 1) & 1u);
@@ -347,25 +393,12 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                 }
                 tmem_wait_st();
             }
-            l_sum *= alpha;
-            // P = exp2(s - m_ref), fp16, into the swizzled A-operand tile: row `row`, 8 chunks of 16 bytes
-            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float psum = 0.f;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
-                uint32_t w[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float p0 = ex2(__uint_as_float(sreg[ch * 8 + 2 * i]) - m_use);
-                    const float p1 = ex2(__uint_as_float(sreg[ch * 8 + 2 * i + 1]) - m_use);
-                    psum += p0 + p1;
-                    __half2 h = __floats2half2_rn(p0, p1);
-                    w[i] = *reinterpret_cast<uint32_t*>(&h);
-                }
                 const uint32_t addr = sP + row * 128 + ((ch ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(pk[ch * 4]), "r"(pk[ch * 4 + 1]),
+                             "r"(pk[ch * 4 + 2]), "r"(pk[ch * 4 + 3]) : "memory");
             }
-            l_sum += psum;
             // V rows past the end of the sequence may hold anything: zero them (last page only)
             if (kv0 + kKvTile > seq_len) {
                 const uint32_t sV = sKV + (j % kStages) * 2 * kKvBytes + kKvBytes;
