@@ -19,7 +19,7 @@
 //                same reference maximum)
 //   O[128x128] += P[128x64] . V[64x128]     tcgen05.mma, B = V tile as an MN-major operand
 // Warps 0-3: softmax / epilogue (warp w reads TMEM lanes 32w..32w+31), warp 4: MMA issue
-// (one elected lane) and TMEM allocation, warp 5: TMA producer. S is double-buffered in
+// (one elected lane) and TMEM allocation, warps 5 / 6: TMA producers of K / V. S is double-buffered in
 // TMEM so Q.K^T of page j+1 runs under the softmax of page j. No cluster, no multicast.
 // Every mbarrier wait is bounded; on expiry the CTA records MLC_DEVERR_WAIT_TIMEOUT,
 // frees its TMEM and returns.
@@ -46,7 +46,7 @@ constexpr uint32_t kKvBytes = 2 * kSubBytesKV;   // 16 KiB per tensor
 constexpr uint32_t kPBytes = kQTile * 128;       // 16 KiB
 constexpr uint32_t kTileBytes = kQBytes + kStages * 2 * kKvBytes + kPBytes;  // 112 KiB
 struct Bars {
-    uint64_t q, kv_full[kStages], kv_empty[kStages], s_full[2], s_free[2], p_full, pv_done;
+    uint64_t q, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2], p_full, pv_done;
     uint32_t tmem_slot;
 };
 constexpr uint32_t kSmemBytes = kTileBytes + sizeof(Bars);
@@ -171,15 +171,17 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t M, uint32_t N, uint32_
 
 }  // namespace
 
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(224, 2)
 paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                              const __grid_constant__ CUtensorMap tmV, const PrefillParams prm) {
     // All shared memory is dynamic (tiles first, barriers behind them) so that two CTAs fit one SM.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Bars& bars = *reinterpret_cast<Bars*>(smem_raw + kTileBytes);
     uint64_t& bar_q = bars.q;
-    uint64_t(&bar_kv_full)[kStages] = bars.kv_full;
-    uint64_t(&bar_kv_empty)[kStages] = bars.kv_empty;
+    uint64_t(&bar_k_full)[kStages] = bars.k_full;
+    uint64_t(&bar_k_empty)[kStages] = bars.k_empty;
+    uint64_t(&bar_v_full)[kStages] = bars.v_full;
+    uint64_t(&bar_v_empty)[kStages] = bars.v_empty;
     uint64_t(&bar_s_full)[2] = bars.s_full;
     uint64_t(&bar_s_free)[2] = bars.s_free;
     uint64_t& bar_p_full = bars.p_full;
@@ -187,7 +189,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     uint32_t& tmem_base_slot = bars.tmem_slot;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t req = blockIdx.z, head = blockIdx.y, qt = blockIdx.x;
+    // the last query tile of a chunk sees the most keys: launch the long CTAs first
+    const uint32_t req = blockIdx.z, head = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
     const uint32_t q_len = prm.q_len[req];
     if (qt * kQTile >= q_len) return;  // uniform over the CTA, before any barrier or TMEM use
     const uint32_t q_start = prm.q_start[req];
@@ -211,8 +214,10 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bar_q), 1);
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&bar_kv_full[s]), 1);
-            mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+            mbar_init(smem_u32(&bar_k_full[s]), 1);
+            mbar_init(smem_u32(&bar_k_empty[s]), 1);
+            mbar_init(smem_u32(&bar_v_full[s]), 1);
+            mbar_init(smem_u32(&bar_v_empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bar_s_full[b]), 1);
@@ -233,7 +238,9 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     };
 
     if (warp == 5) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer of Q and the K tiles ----------------
+        // A K stage is free again as soon as the Q.K^T that read it has completed, a V stage
+        // only after its P.V: the two streams have their own barriers and their own warp.
         if (lane == 0 && n_tiles > 0) {
             const uint32_t bq = smem_u32(&bar_q);
             mbar_expect_tx(bq, kQBytes);
@@ -242,16 +249,32 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             const uint32_t pt_base = prm.pt_off[req];
             for (uint32_t j = 0; j < n_tiles; ++j) {
                 const uint32_t s = j % kStages;
-                if (j >= kStages && !mbar_wait_bounded(smem_u32(&bar_kv_empty[s]), ((j / kStages) - 1) & 1u)) {
+                if (j >= kStages && !mbar_wait_bounded(smem_u32(&bar_k_empty[s]), ((j / kStages) - 1) & 1u)) {
                     give_up();
                     break;
                 }
                 const int page = static_cast<int>(prm.pt_flat[pt_base + j]);
-                const uint32_t bf = smem_u32(&bar_kv_full[s]);
-                const uint32_t dK = sKV + s * 2 * kKvBytes, dV = dK + kKvBytes;
-                mbar_expect_tx(bf, 2 * kKvBytes);
+                const uint32_t bf = smem_u32(&bar_k_full[s]);
+                const uint32_t dK = sKV + s * 2 * kKvBytes;
+                mbar_expect_tx(bf, kKvBytes);
                 tma_load_4d(dK, &tmK, bf, 0, static_cast<int>(kv_head), 0, page);
                 tma_load_4d(dK + kSubBytesKV, &tmK, bf, 64, static_cast<int>(kv_head), 0, page);
+            }
+        }
+    } else if (warp == 6) {
+        // ---------------- TMA producer of the V tiles ----------------
+        if (lane == 0 && n_tiles > 0) {
+            const uint32_t pt_base = prm.pt_off[req];
+            for (uint32_t j = 0; j < n_tiles; ++j) {
+                const uint32_t s = j % kStages;
+                if (j >= kStages && !mbar_wait_bounded(smem_u32(&bar_v_empty[s]), ((j / kStages) - 1) & 1u)) {
+                    give_up();
+                    break;
+                }
+                const int page = static_cast<int>(prm.pt_flat[pt_base + j]);
+                const uint32_t bf = smem_u32(&bar_v_full[s]);
+                const uint32_t dV = sKV + s * 2 * kKvBytes + kKvBytes;
+                mbar_expect_tx(bf, kKvBytes);
                 tma_load_4d(dV, &tmV, bf, 0, static_cast<int>(kv_head), 0, page);
                 tma_load_4d(dV + kSubBytesKV, &tmV, bf, 64, static_cast<int>(kv_head), 0, page);
             }
@@ -271,9 +294,10 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                     const uint32_t b = sK + (k >> 2) * kSubBytesKV + (k & 3) * 32;
                     tc_mma_f16(d, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, 16, 1024), idesc_qk, k > 0);
                 }
+                tc_commit(smem_u32(&bar_k_empty[s]));
                 tc_commit(smem_u32(&bar_s_full[j & 1u]));
             };
-            bool ok = mbar_wait_bounded(smem_u32(&bar_q), 0) && mbar_wait_bounded(smem_u32(&bar_kv_full[0]), 0);
+            bool ok = mbar_wait_bounded(smem_u32(&bar_q), 0) && mbar_wait_bounded(smem_u32(&bar_k_full[0]), 0);
             if (ok) {
                 tc_fence_after();
                 issue_qk(0);
@@ -281,17 +305,18 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
                 if (j + 1 < n_tiles) {  // Q.K^T of the next page runs under this page's softmax
                     const uint32_t s1 = (j + 1) % kStages;
-                    ok = mbar_wait_bounded(smem_u32(&bar_kv_full[s1]), ((j + 1) / kStages) & 1u);
+                    ok = mbar_wait_bounded(smem_u32(&bar_k_full[s1]), ((j + 1) / kStages) & 1u);
                     // S buffer (j+1)&1 was last used by page j-1: wait until its scores were read
                     if (ok && j >= 1) ok = mbar_wait_bounded(smem_u32(&bar_s_free[(j + 1) & 1u]), ((j - 1) >> 1) & 1u);
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk(j + 1);
                 }
-                ok = mbar_wait_bounded(smem_u32(&bar_p_full), j & 1u);
+                const uint32_t s = j % kStages;
+                ok = mbar_wait_bounded(smem_u32(&bar_v_full[s]), (j / kStages) & 1u) &&
+                     mbar_wait_bounded(smem_u32(&bar_p_full), j & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t s = j % kStages;
                 const uint32_t sV = sKV + s * 2 * kKvBytes + kKvBytes;
 #pragma unroll
                 for (int k = 0; k < kKvTile / 16; ++k) {  // 16 tokens per step
@@ -300,7 +325,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                     tc_mma_f16(tmem + kTmemO, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, kSubBytesKV, 1024),
                                idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                 }
-                tc_commit(smem_u32(&bar_kv_empty[s]));
+                tc_commit(smem_u32(&bar_v_empty[s]));
                 tc_commit(smem_u32(&bar_pv_done));
             }
             if (!ok) give_up();
@@ -401,6 +426,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             }
             // V rows past the end of the sequence may hold anything: zero them (last page only)
             if (kv0 + kKvTile > seq_len) {
+                ok = mbar_wait_bounded(smem_u32(&bar_v_full[j % kStages]), (j / kStages) & 1u);  // the tile has landed
+                if (!ok) break;
                 const uint32_t sV = sKV + (j % kStages) * 2 * kKvBytes + kKvBytes;
                 const uint32_t first = seq_len - kv0;  // 1..63
                 for (uint32_t i = threadIdx.x; i < (kKvTile - first) * 16; i += 128) {
@@ -521,7 +548,7 @@ int launch_prefill_tcgen05(mlc_ctx* ctx, const void* q, const void* k_pages, con
     prm.G = static_cast<uint32_t>(H / KVH);
     prm.scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(static_cast<unsigned>((max_q_len + kQTile - 1) / kQTile), static_cast<unsigned>(H), static_cast<unsigned>(batch));
-    paged_prefill_tcgen05_kernel<<<grid, 192, kSmemBytes, ctx->stream>>>(mq, mk, mv, prm);
+    paged_prefill_tcgen05_kernel<<<grid, 224, kSmemBytes, ctx->stream>>>(mq, mk, mv, prm);
     ++ctx->launches;
     MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
