@@ -13,11 +13,12 @@
 //   S[128x64]  = Q[128x128] . K^T           tcgen05.mma kind::f16, A and B from shared memory
 //                                           (K-major, 128-byte swizzle), fp32 accumulator in TMEM
 //   softmax    : thread t owns row t: tcgen05.ld its 64 scores, mask, running max / sum in fp32
-//                (base-2 exponentials), P rounded to fp16 and written back to shared memory as the
-//                next A operand; the O accumulator in TMEM is rescaled only when a row's maximum
+//                (base-2 exponentials), P rounded to fp16 and stored back into tensor memory over its
+//                own scores (tcgen05.st) as the next A operand - P never touches shared memory, whose
+//                bandwidth is what bounds this kernel; the O accumulator is rescaled only when a row's maximum
 //                has grown by more than 2^8 since the last rescale (exact: the final 1/l uses the
 //                same reference maximum)
-//   O[128x128] += P[128x64] . V[64x128]     tcgen05.mma, B = V tile as an MN-major operand
+//   O[128x128] += P[128x64] . V[64x128]     tcgen05.mma, A = P from TMEM, B = V tile as an MN-major operand
 // Warps 0-3: softmax / epilogue (warp w reads TMEM lanes 32w..32w+31), warp 4: MMA issue
 // (one elected lane) and TMEM allocation, warps 5 / 6: TMA producers of K / V. S is double-buffered in
 // TMEM so Q.K^T of page j+1 runs under the softmax of page j. No cluster, no multicast.
@@ -43,13 +44,16 @@ constexpr uint32_t kSubBytesQ = kQTile * 128;    // one 64-half-wide slab of the
 constexpr uint32_t kSubBytesKV = kKvTile * 128;  // one 64-half-wide slab of a K or V tile
 constexpr uint32_t kQBytes = 2 * kSubBytesQ;     // 32 KiB
 constexpr uint32_t kKvBytes = 2 * kSubBytesKV;   // 16 KiB per tensor
-constexpr uint32_t kPBytes = kQTile * 128;       // 16 KiB
-constexpr uint32_t kTileBytes = kQBytes + kStages * 2 * kKvBytes + kPBytes;  // 112 KiB
+constexpr uint32_t kTileBytes = kQBytes + kStages * 2 * kKvBytes;  // 96 KiB
 struct Bars {
-    uint64_t q, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2], p_full, pv_done;
+    uint64_t q, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], p_full[2], pv_done;
     uint32_t tmem_slot;
 };
+#ifdef MLCB_PREFILL_ONE_CTA  // experiment: pad the request so that only one CTA fits an SM
+constexpr uint32_t kSmemBytes = kTileBytes + sizeof(Bars) + 32768;
+#else
 constexpr uint32_t kSmemBytes = kTileBytes + sizeof(Bars);
+#endif
 constexpr uint32_t kTmemCols = 256;              // O: 128 columns, S: 2 x 64 columns
 constexpr uint32_t kTmemO = 0, kTmemS = 128;
 
@@ -88,7 +92,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 22); ++i)
+    // a poll that finds the phase open suspends for a few microseconds: 2^18 polls are about a second
+    for (uint32_t i = 0; i < (1u << 18); ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
@@ -101,6 +106,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -128,6 +142,15 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Same with the A operand read from tensor memory: lane = row, one 32-bit column = two
+// consecutive fp16 elements along K.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -169,7 +192,28 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t M, uint32_t N, uint32_
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+#ifdef MLCB_PREFILL_TRACE
+// Build-time profiling aid: SM-clock stamps of one CTA's softmax warp 0 and MMA lane, per tile.
+__device__ unsigned long long g_prefill_trace[64 * 16];
+__device__ unsigned int g_prefill_fail[16];  // [0] = 1 + linear id of the first CTA that timed out, [1 + warp] = where | tile << 8
+#define PF_STAMP(tile, slot)                                                                    \
+    do {                                                                                        \
+        if (trace_cta && (tile) < 64) g_prefill_trace[(tile) * 16 + (slot)] = clock64();        \
+    } while (0)
+#else
+#define PF_STAMP(tile, slot) do { } while (0)
+#endif
+
 }  // namespace
+
+#ifdef MLCB_PREFILL_TRACE
+extern "C" int mlc_debug_read_prefill_trace(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(g_prefill_trace)) == cudaSuccess ? 0 : 1;
+}
+extern "C" int mlc_debug_read_prefill_fail(unsigned int* out) {
+    return cudaMemcpyFromSymbol(out, g_prefill_fail, sizeof(g_prefill_fail)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 __global__ void __launch_bounds__(224, 2)
 paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -183,12 +227,11 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     uint64_t(&bar_v_full)[kStages] = bars.v_full;
     uint64_t(&bar_v_empty)[kStages] = bars.v_empty;
     uint64_t(&bar_s_full)[2] = bars.s_full;
-    uint64_t(&bar_s_free)[2] = bars.s_free;
-    uint64_t& bar_p_full = bars.p_full;
+    uint64_t(&bar_p_full)[2] = bars.p_full;
     uint64_t& bar_pv_done = bars.pv_done;
     uint32_t& tmem_base_slot = bars.tmem_slot;
 
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
     // the last query tile of a chunk sees the most keys: launch the long CTAs first
     const uint32_t req = blockIdx.z, head = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
     const uint32_t q_len = prm.q_len[req];
@@ -204,12 +247,11 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
 
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {  // the 128-byte swizzle needs 1024-byte aligned tiles; never expected
-        if (threadIdx.x == 0) atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
+        if (threadIdx.x == 0) atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT | (0x40u << 8));
         return;
     }
     const uint32_t sQ = base;
     const uint32_t sKV = sQ + kQBytes;                       // stage s: K at sKV + s*2*kKvBytes, V right after K
-    const uint32_t sP = sKV + kStages * 2 * kKvBytes;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bar_q), 1);
@@ -221,9 +263,12 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bar_s_full[b]), 1);
-            mbar_init(smem_u32(&bar_s_free[b]), 128);
+            // Two P barriers, like the two S buffers: the softmax warps may finish page j+1 (its
+            // scores were issued early) before the MMA warp has looked at page j's arrival; with one
+            // barrier that second completion would flip the phase parity back and the wait would
+            // never see page j.
+            mbar_init(smem_u32(&bar_p_full[b]), 128);
         }
-        mbar_init(smem_u32(&bar_p_full), 128);
         mbar_init(smem_u32(&bar_pv_done), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -233,8 +278,22 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
 
-    auto give_up = [&]() {
-        if (lane == 0) atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
+#ifdef MLCB_PREFILL_TRACE
+    const bool trace_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4);
+#endif
+    // A wait that ran out records the timeout bit plus where it gave up: bits 8-15 = which wait
+    // (0x1x MMA warp, 0x2x softmax, 0x3x producers), bits 16-31 = the page it was working on.
+    auto give_up = [&](uint32_t where, uint32_t tile) {
+#ifdef MLCB_PREFILL_TRACE
+        if (lane == 0) {
+            const unsigned int me = 1u + blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+            const unsigned int prev = atomicCAS(&g_prefill_fail[0], 0u, me);
+            if (prev == 0u || prev == me) g_prefill_fail[1 + warp] = where | (tile << 8) | 0x80000000u;
+        }
+#endif
+        // the first failure's detail wins; later ones only (re)set the timeout bit
+        if (lane == 0 && atomicCAS(prm.err, 0u, MLC_DEVERR_WAIT_TIMEOUT | (where << 8) | (tile << 16)) != 0u)
+            atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
     };
 
     if (warp == 5) {
@@ -250,7 +309,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             for (uint32_t j = 0; j < n_tiles; ++j) {
                 const uint32_t s = j % kStages;
                 if (j >= kStages && !mbar_wait_bounded(smem_u32(&bar_k_empty[s]), ((j / kStages) - 1) & 1u)) {
-                    give_up();
+                    give_up(0x30, j);
                     break;
                 }
                 const int page = static_cast<int>(prm.pt_flat[pt_base + j]);
@@ -268,7 +327,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             for (uint32_t j = 0; j < n_tiles; ++j) {
                 const uint32_t s = j % kStages;
                 if (j >= kStages && !mbar_wait_bounded(smem_u32(&bar_v_empty[s]), ((j / kStages) - 1) & 1u)) {
-                    give_up();
+                    give_up(0x31, j);
                     break;
                 }
                 const int page = static_cast<int>(prm.pt_flat[pt_base + j]);
@@ -280,55 +339,81 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             }
         }
     } else if (warp == 4) {
-        // ---------------- MMA issue (one lane) ----------------
-        if (lane == 0 && n_tiles > 0) {
+        // ---------------- MMA issue ----------------
+        // The whole warp walks the loop (waits, addresses and descriptors stay warp-uniform, so the
+        // compiler can keep them in uniform registers); one elected lane issues the instructions.
+        if (n_tiles > 0) {
             constexpr uint32_t idesc_qk = idesc_f16(kQTile, kKvTile, 0);    // S = Q.K^T : B = K tile, K-major
             constexpr uint32_t idesc_pv = idesc_f16(kQTile, kHeadDim, 1);   // O += P.V  : B = V tile, MN-major
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+            const uint32_t sQ_u = __shfl_sync(0xffffffffu, sQ, 0);
+            const uint64_t desc_k_major = smem_desc_sw128(0, 16, 1024);
+            const uint64_t desc_v = smem_desc_sw128(0, kSubBytesKV, 1024);
             auto issue_qk = [&](uint32_t j) {
                 const uint32_t s = j % kStages;
-                const uint32_t sK = sKV + s * 2 * kKvBytes;
-                const uint32_t d = tmem + kTmemS + (j & 1u) * kKvTile;
+                const uint32_t sK = sQ_u + kQBytes + s * 2 * kKvBytes;
+                const uint32_t d = tmem_u + kTmemS + (j & 1u) * kKvTile;
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < kHeadDim / 16; ++k) {  // 16 halfs = 32 bytes per step inside a 128-byte row
-                    const uint32_t a = sQ + (k >> 2) * kSubBytesQ + (k & 3) * 32;
-                    const uint32_t b = sK + (k >> 2) * kSubBytesKV + (k & 3) * 32;
-                    tc_mma_f16(d, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, 16, 1024), idesc_qk, k > 0);
+                    for (int k = 0; k < kHeadDim / 16; ++k) {  // 16 halfs = 32 bytes per step inside a 128-byte row
+                        const uint32_t a = sQ_u + (k >> 2) * kSubBytesQ + (k & 3) * 32;
+                        const uint32_t b = sK + (k >> 2) * kSubBytesKV + (k & 3) * 32;
+                        tc_mma_f16(d, desc_k_major | (a >> 4), desc_k_major | (b >> 4), idesc_qk, k > 0);
+                    }
+                    tc_commit(smem_u32(&bar_k_empty[s]));
+                    tc_commit(smem_u32(&bar_s_full[j & 1u]));
                 }
-                tc_commit(smem_u32(&bar_k_empty[s]));
-                tc_commit(smem_u32(&bar_s_full[j & 1u]));
+                __syncwarp();
             };
+            uint32_t where = 0x10, at = 0;
             bool ok = mbar_wait_bounded(smem_u32(&bar_q), 0) && mbar_wait_bounded(smem_u32(&bar_k_full[0]), 0);
+            ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 tc_fence_after();
                 issue_qk(0);
             }
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+                at = j;
                 if (j + 1 < n_tiles) {  // Q.K^T of the next page runs under this page's softmax
                     const uint32_t s1 = (j + 1) % kStages;
-                    ok = mbar_wait_bounded(smem_u32(&bar_k_full[s1]), ((j + 1) / kStages) & 1u);
-                    // S buffer (j+1)&1 was last used by page j-1: wait until its scores were read
-                    if (ok && j >= 1) ok = mbar_wait_bounded(smem_u32(&bar_s_free[(j + 1) & 1u]), ((j - 1) >> 1) & 1u);
+                    where = 0x11;
+                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_k_full[s1]), ((j + 1) / kStages) & 1u));
+                    // S buffer (j+1)&1 still holds P of page j-1 (P overwrites S in place): its P.V must be done
+                    if (ok && j >= 1) {
+                        where = 0x12;
+                        ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_pv_done), (j - 1) & 1u));
+                    }
                     if (!ok) break;
                     tc_fence_after();
+                    PF_STAMP(j, 8);
                     issue_qk(j + 1);
                 }
                 const uint32_t s = j % kStages;
-                ok = mbar_wait_bounded(smem_u32(&bar_v_full[s]), (j / kStages) & 1u) &&
-                     mbar_wait_bounded(smem_u32(&bar_p_full), j & 1u);
+                where = 0x13;
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_v_full[s]), (j / kStages) & 1u));
+                if (ok) {
+                    where = 0x14;
+                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_p_full[j & 1u]), (j >> 1) & 1u));
+                }
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sV = sKV + s * 2 * kKvBytes + kKvBytes;
+                PF_STAMP(j, 9);
+                const uint32_t sV = sQ_u + kQBytes + s * 2 * kKvBytes + kKvBytes;
+                const uint32_t pj = tmem_u + kTmemS + (j & 1u) * kKvTile;
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < kKvTile / 16; ++k) {  // 16 tokens per step
-                    const uint32_t a = sP + k * 32;                         // P: K-major rows of 128 bytes
-                    const uint32_t b = sV + k * 16 * 128;                   // V: 16 token rows further down
-                    tc_mma_f16(tmem + kTmemO, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, kSubBytesKV, 1024),
-                               idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < kKvTile / 16; ++k) {  // 16 tokens per step
+                        const uint32_t b = sV + k * 16 * 128;  // V: 16 token rows further down
+                        // P in TMEM: 16 fp16 = 8 columns per step
+                        tc_mma_f16_ts(tmem_u + kTmemO, pj + k * 8, desc_v | (b >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&bar_v_empty[s]));
+                    tc_commit(smem_u32(&bar_pv_done));
                 }
-                tc_commit(smem_u32(&bar_v_empty[s]));
-                tc_commit(smem_u32(&bar_pv_done));
+                __syncwarp();
+                PF_STAMP(j, 10);
             }
-            if (!ok) give_up();
+            if (!ok) give_up(where, at);
         }
     } else {
         // ---------------- softmax + epilogue: thread = query row ----------------
@@ -339,10 +424,14 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
         const float rescale_step = 8.0f / prm.scale_log2;      // 2^8 in units of the unscaled scores
         float m_ref = -INFINITY, l_sum = 0.f;                  // reference maximum of the O accumulator, row sum
         bool ok = true;
+        uint32_t where = 0x20, at = 0;
         for (uint32_t j = 0; j < n_tiles; ++j) {
+            at = j;
+            where = 0x20;
             ok = ok && mbar_wait_bounded(smem_u32(&bar_s_full[j & 1u]), (j >> 1) & 1u);
             if (!ok) break;
             tc_fence_after();
+            PF_STAMP(j, 0);
             uint32_t sreg[64];
             {
                 uint32_t lo[32], hi[32];
@@ -352,8 +441,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
 #pragma unroll
                 for (int i = 0; i < 32; ++i) { sreg[i] = lo[i]; sreg[32 + i] = hi[i]; }
             }
-            tc_fence_before();
-            mbar_arrive(smem_u32(&bar_s_free[j & 1u]));
+            PF_STAMP(j, 1);
             // mask: causal (kv_pos > q_pos) and past the end of the sequence
             const uint32_t kv0 = j * kKvTile;
             // Scores stay unscaled (scale > 0 keeps their order); the scale is folded into the
@@ -380,6 +468,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             const bool need = (m_new > m_ref + rescale_step) || (m_ref == -INFINITY && m_new > -INFINITY);
             const float alpha = need ? ((m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * prm.scale_log2)) : 1.0f;
             if (need) m_ref = m_new;
+            PF_STAMP(j, 2);
             l_sum *= alpha;
             // P = exp2((s - m_ref) * scale), fp16, computed while the previous P.V may still run, then
             // stored into the swizzled A-operand tile: row `row`, 8 chunks of 16 bytes
@@ -400,13 +489,14 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                 pk[ch * 4 + 0] = w[0]; pk[ch * 4 + 1] = w[1]; pk[ch * 4 + 2] = w[2]; pk[ch * 4 + 3] = w[3];
             }
             l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-            // the previous P.V must be done before P (shared memory) or O (TMEM) are touched
-            if (j > 0) {
+            PF_STAMP(j, 3);
+            PF_STAMP(j, 4);
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+                // O may only be touched once the previous P.V is done (warp-uniform branch)
+                where = 0x21;
                 ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (j - 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-            }
-            if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
                     uint32_t oreg[32];
@@ -418,14 +508,12 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                 }
                 tmem_wait_st();
             }
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                const uint32_t addr = sP + row * 128 + ((ch ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(pk[ch * 4]), "r"(pk[ch * 4 + 1]),
-                             "r"(pk[ch * 4 + 2]), "r"(pk[ch * 4 + 3]) : "memory");
-            }
+            // P overwrites the first 32 columns of this page's S buffer (own lane only, already read)
+            tmem_st32(tmem + lane_base + kTmemS + (j & 1u) * kKvTile, pk);
+            tmem_wait_st();
             // V rows past the end of the sequence may hold anything: zero them (last page only)
             if (kv0 + kKvTile > seq_len) {
+                where = 0x22;
                 ok = mbar_wait_bounded(smem_u32(&bar_v_full[j % kStages]), (j / kStages) & 1u);  // the tile has landed
                 if (!ok) break;
                 const uint32_t sV = sKV + (j % kStages) * 2 * kKvBytes + kKvBytes;
@@ -435,14 +523,18 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                     const uint32_t addr = sV + (c >> 3) * kSubBytesKV + r * 128 + ((c & 7) << 4);
                     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
-            mbar_arrive(smem_u32(&bar_p_full));
+            mbar_arrive(smem_u32(&bar_p_full[j & 1u]));
+            PF_STAMP(j, 5);
         }
-        if (ok && n_tiles > 0) ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 1) & 1u);
+        if (ok && n_tiles > 0) {
+            where = 0x23;
+            ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 1) & 1u);
+        }
         if (!ok) {
-            give_up();
+            give_up(where, at);
         } else {
             tc_fence_after();
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;

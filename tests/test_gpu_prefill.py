@@ -149,3 +149,27 @@ def test_prefill_rejects_chunk_past_the_sequence(ex):
                                      capi.MLC_F16, capi.MLC_F16, case.capacity)
     assert not ok
     assert "exceeds" in ex.last_error()
+
+
+def test_prefill_many_back_to_back_launches(ex):
+    """Several waves of CTAs per launch and launches queued back to back: the softmax warps get
+    a page ahead of the MMA warp here, which a single-phase P barrier once turned into a
+    lost wake-up (reported as MLC_DEVERR_WAIT_TIMEOUT, not a hang)."""
+    import torch
+    H, KVH, D, P = 32, 8, 128, 64
+    case = make_case(19, [2048] * 8, H=H, KVH=KVH, D=D, fill=False)
+    dev = torch.device("cuda:0")
+    kp = torch.randn((case.capacity, P, KVH, D), device=dev, dtype=torch.float16)
+    vp = torch.randn((case.capacity, P, KVH, D), device=dev, dtype=torch.float16)
+    q = torch.randn((8 * 512, H, D), device=dev, dtype=torch.float16)
+    o = torch.zeros_like(q)
+    qs, ql = np.full(8, 1536, np.uint32), np.full(8, 512, np.uint32)
+    torch.cuda.synchronize()
+    for _ in range(4):
+        assert ex.beginForwardPassCB()
+        for _ in range(25):
+            assert ex.encodePagedPrefillAttention(q, kp, vp, o, case.pt_flat, case.pt_off, case.seq_lens, qs, ql,
+                                                  8, H, KVH, D, P, case.scale, capi.MLC_F16, capi.MLC_F16,
+                                                  case.capacity), ex.last_error()
+        assert ex.flushForwardPassCB(), ex.last_error()
+    assert torch.isfinite(o.float()).all()
