@@ -280,6 +280,36 @@ int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan
 int mlc_encode_lse_combine(mlc_ctx* ctx, const float* o_parts, const float* ml_parts, size_t parts,
                            size_t rows, size_t head_dim, void* out, int o_dtype);
 
+/* ---- QKV split + rotary embedding + cast, the step that feeds the scatter -------------
+ * encodeQkvSplitRopeCast (metal_runtime.hpp:540-547; metal_runtime.mm:7915-8025: 3 x
+ * strided_copy_f32 + 2 x batched_rope + 2 x cast_f32_to_f16 in one encoder) as ONE launch.
+ *   qkv        device fp32 [batch, qkv_rows], row = [q_rows | k_rows | v_rows | ...]
+ *   q, k, v    device fp32 [batch, q_rows / k_rows / v_rows]  (Q and K rotated)
+ *   k_f16, v_f16 device fp16 copies of k, v (round to nearest even, like MSL half())
+ *   cos_table, sin_table device fp32 [batch, rotary_dim / 2], one row per request
+ *              (computeRotaryCoefficients, quantization.cpp:795-823; mlc_compute_rotary_coefficients)
+ * Rotation of adjacent pairs (2i, 2i+1), i < rotary_dim / 2, of every head:
+ *   y0 = x0*c - x1*s, y1 = x0*s + x1*c in fp32 without contraction (bit-exact against the CPU
+ *   restatement). rotary_dim = 0 applies no rotation. Needs an open pass. */
+int mlc_encode_qkv_split_rope_cast(mlc_ctx* ctx, const void* qkv, void* q, void* k, void* v, void* k_f16,
+                                   void* v_f16, const void* cos_table, const void* sin_table, size_t batch,
+                                   size_t num_heads, size_t kv_heads, size_t head_dim, size_t qkv_rows,
+                                   size_t q_rows, size_t k_rows, size_t v_rows, size_t rotary_dim);
+/* The same step fused with the two scatters that follow it in the walker
+ * (batched_walker.cpp:299-309): the rotated K row and the V row of request r are written as
+ * fp16 straight to (page_ids[r], slots_in_page[r]) of the pools held by `plan`, and Q is
+ * written as q_dtype (fp32 like the reference, or fp16 for the attention kernel). Replaces 9
+ * dispatches of the reference; no fp32 K/V and no fp16 staging buffers. Capturable. */
+int mlc_encode_qkv_split_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* qkv,
+                                              void* q_out, int q_dtype, void* k_page_storage,
+                                              void* v_page_storage, const void* cos_table,
+                                              const void* sin_table, size_t qkv_rows, size_t rotary_dim);
+/* computeRotaryCoefficients (quantization.cpp:795-823) on the host: cos/sin of
+ * position * freq_base^(-2i/rotary_dim) * freq_scale for i < rotary_dim / 2
+ * (freq_base <= 0 -> 10000, freq_scale == 0 -> 1, as in the reference). */
+int mlc_compute_rotary_coefficients(size_t position, size_t rotary_dim, float freq_base, float freq_scale,
+                                    float* cos_out, float* sin_out);
+
 /* ---- chunked (multi-token) causal paged attention ------------------------------------
  * The reference runs a paged prefill as q_len single-token decode passes
  * (compiler/runtime/batched_executor.cpp:450-467); these entry points compute the same

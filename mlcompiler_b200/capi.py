@@ -67,6 +67,10 @@ _PROTOTYPES = {
                                              _sz, _sz, _sz, _sz, _sz, _f, _i, _i, _sz]),
     "mlc_encode_paged_prefill_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p,
                                                 _sz, _sz, _sz, _sz, _sz, _f, _i, _i, _sz]),
+    "mlc_encode_qkv_split_rope_cast": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz,
+                                            _sz, _sz, _sz, _sz]),
+    "mlc_encode_qkv_split_rope_scatter_planned": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _sz, _sz]),
+    "mlc_compute_rotary_coefficients": (_i, [_sz, _sz, _f, _f, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mlc_ctx_last_attention_kernel": (_i, [_vp]),
     "mlc_ctx_read_trace": (C.c_uint32, [_vp, C.POINTER(C.c_uint64), _sz, _i]),
     "mlc_attn_plan_create": (_i, [_vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p, _u32p, _sz, _sz, _sz, _sz, _sz,
@@ -379,6 +383,29 @@ class Executor:
 
     def staticScratchBytes(self) -> int:
         return int(self._lib.mlc_static_scratch_bytes())
+
+    def encodeQkvSplitRopeCast(self, qkv_buf, q_buf, k_buf, v_buf, k_f16_buf, v_f16_buf, cos_buf, sin_buf, batch,
+                               num_heads, kv_heads, head_dim, qkv_rows, q_rows, k_rows, v_rows, rotary_dim) -> bool:
+        """metal_runtime.hpp:540-547, one launch instead of seven dispatches."""
+        return self.status(self._lib.mlc_encode_qkv_split_rope_cast(
+            self._h, _vp(_ptr(qkv_buf)), _vp(_ptr(q_buf)), _vp(_ptr(k_buf)), _vp(_ptr(v_buf)), _vp(_ptr(k_f16_buf)),
+            _vp(_ptr(v_f16_buf)), _vp(_ptr(cos_buf)), _vp(_ptr(sin_buf)), batch, num_heads, kv_heads, head_dim,
+            qkv_rows, q_rows, k_rows, v_rows, rotary_dim))
+
+    def encodeQkvSplitRopeScatterPlanned(self, plan, qkv_buf, q_out, q_dtype, k_storage, v_storage, cos_buf, sin_buf,
+                                         qkv_rows, rotary_dim) -> bool:
+        """Split + rotate + cast + scatter of the step's K/V rows into the pools, one launch."""
+        return self.status(self._lib.mlc_encode_qkv_split_rope_scatter_planned(
+            self._h, plan.handle, _vp(_ptr(qkv_buf)), _vp(_ptr(q_out)), q_dtype, _vp(_ptr(k_storage)),
+            _vp(_ptr(v_storage)), _vp(_ptr(cos_buf)), _vp(_ptr(sin_buf)), qkv_rows, rotary_dim))
+
+    def computeRotaryCoefficients(self, position, rotary_dim, freq_base=10000.0, freq_scale=1.0):
+        """quantization.cpp:795-823: (cos, sin) float32 [rotary_dim // 2]."""
+        c, s = np.zeros(rotary_dim // 2, np.float32), np.zeros(rotary_dim // 2, np.float32)
+        fp = C.POINTER(C.c_float)
+        self.check(self._lib.mlc_compute_rotary_coefficients(position, rotary_dim, float(freq_base), float(freq_scale),
+                                                             c.ctypes.data_as(fp), s.ctypes.data_as(fp)))
+        return c, s
 
     def encodeScatterKVPairPlanned(self, plan, k_storage, v_storage, k_src, v_src) -> bool:
         return self.status(self._lib.mlc_encode_scatter_kv_pair_planned(

@@ -9,6 +9,7 @@
 // tables (the reference's walker passes identical tables for each of its 22
 // layers, compiler/runtime/batched_walker.cpp:316-325).
 #include "attn_internal.hpp"
+#include "qkv_rope.hpp"
 
 #include <algorithm>
 #include <cmath>
@@ -507,6 +508,42 @@ int mlc_encode_scatter_kv_pair_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, 
     const PlanKey& k = plan->key;
     return launch_scatter_rows_device_tables(ctx, k_page_storage, v_page_storage, plan->d_page_ids,
                                              plan->d_slots, k.P, k.KVH, k.D, k.batch, k_src, v_src, k.capacity);
+}
+
+int mlc_encode_qkv_split_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* qkv,
+                                              void* q_out, int q_dtype, void* k_page_storage,
+                                              void* v_page_storage, const void* cos_table,
+                                              const void* sin_table, size_t qkv_rows, size_t rotary_dim) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (!plan->d_page_ids) return ctx->fail(MLC_ERR_INVALID_ARG, "the plan was created without page_ids / slots_in_page");
+    if (!q_out || !k_page_storage || !v_page_storage) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    if (q_dtype != MLC_F16 && q_dtype != MLC_F32) return ctx->fail(MLC_ERR_INVALID_ARG, "q dtype must be MLC_F16 or MLC_F32");
+    const PlanKey& k = plan->key;
+    int st = check_qkv_rope_args(ctx, qkv, cos_table, sin_table, k.batch, k.H, k.KVH, k.D, qkv_rows, k.H * k.D,
+                                 k.KVH * k.D, k.KVH * k.D, rotary_dim);
+    if (st != MLC_OK) return st;
+    DeviceGuard guard(ctx->device);
+    QkvRopeParams p{};
+    p.qkv = static_cast<const float*>(qkv);
+    if (q_dtype == MLC_F32) p.q = static_cast<float*>(q_out);
+    else p.q16 = static_cast<__half*>(q_out);
+    p.k_pool = static_cast<__half*>(k_page_storage);
+    p.v_pool = static_cast<__half*>(v_page_storage);
+    p.page_ids = plan->d_page_ids;
+    p.slots = plan->d_slots;
+    p.cos_t = static_cast<const float*>(cos_table);
+    p.sin_t = static_cast<const float*>(sin_table);
+    p.err = ctx->d_err;
+    p.batch = static_cast<uint32_t>(k.batch);
+    p.head_dim = static_cast<uint32_t>(k.D);
+    p.rotary_pairs = static_cast<uint32_t>(rotary_dim / 2);
+    p.qkv_rows = static_cast<uint32_t>(qkv_rows);
+    p.q_rows = static_cast<uint32_t>(k.H * k.D);
+    p.k_rows = p.v_rows = static_cast<uint32_t>(k.KVH * k.D);
+    p.page_tokens = static_cast<uint32_t>(k.P);
+    p.capacity = k.capacity ? static_cast<uint32_t>(k.capacity) : 0xFFFFFFFFu;
+    return launch_qkv_split_rope_cast(ctx, p);
 }
 
 }  // extern "C"

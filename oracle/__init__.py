@@ -258,3 +258,30 @@ def reference_decode(q, k_tokens, v_tokens, H, KVH, D, direct=False):
         return out
     finally:
         lib.ref_attn_destroy(h)
+
+
+def compute_rotary(position, rotary_dim, freq_base=10000.0, freq_scale=1.0):
+    """(cos, sin) float32 [rotary_dim // 2] of one position (quantization.cpp:795-823)."""
+    pairs = rotary_dim // 2
+    c, s = np.zeros(pairs, np.float32), np.zeros(pairs, np.float32)
+    port().orc_compute_rotary(C.c_size_t(position), C.c_size_t(rotary_dim), C.c_float(freq_base),
+                              C.c_float(freq_scale), _p(c, _fp), _p(s, _fp))
+    return c, s
+
+
+def qkv_split_rope_cast(qkv, cos_t, sin_t, H, KVH, D, rotary_dim):
+    """encodeQkvSplitRopeCast (metal_runtime.mm:7915-8025) on the CPU.
+    qkv float32 [batch, qkv_rows]; returns q, k, v (float32) and k16, v16 (uint16 fp16 bits)."""
+    qkv = _c(qkv, np.float32)
+    batch, qkv_rows = qkv.shape
+    q_rows, k_rows = H * D, KVH * D
+    cos_t, sin_t = _c(cos_t, np.float32), _c(sin_t, np.float32)
+    q = np.zeros((batch, q_rows), np.float32)
+    k = np.zeros((batch, k_rows), np.float32)
+    v = np.zeros((batch, k_rows), np.float32)
+    k16 = np.zeros((batch, k_rows), np.uint16)
+    v16 = np.zeros((batch, k_rows), np.uint16)
+    port().orc_qkv_split_rope_cast(_p(qkv, _fp), _p(q, _fp), _p(k, _fp), _p(v, _fp), _p(k16, _u16p),
+                                   _p(v16, _u16p), _p(cos_t, _fp), _p(sin_t, _fp), batch, H, KVH, D,
+                                   qkv_rows, q_rows, k_rows, k_rows, rotary_dim)
+    return q, k, v, k16, v16

@@ -399,3 +399,62 @@ int orc_kvstate_extend(orc_pool* pool, uint32_t page_size, uint32_t* pages, size
     *slot = (*tokens_in_last)++;
     return 1;
 }
+
+/* ------------------------------------------------------------------------ */
+/* QKV split + rotary embedding + cast (the step before the scatter)         */
+/* ------------------------------------------------------------------------ */
+
+/* computeRotaryCoefficients, compiler/runtime/quantization.cpp:795-823. */
+void orc_compute_rotary(size_t position, size_t rotary_dim, float freq_base, float freq_scale,
+                        float* cos_out, float* sin_out) {
+    if (rotary_dim < 2) return;
+    if (freq_base <= 0.0f) freq_base = 10000.0f;
+    if (freq_scale == 0.0f) freq_scale = 1.0f;
+    size_t pairs = rotary_dim / 2;
+    float pos = (float)position;
+    for (size_t i = 0; i < pairs; ++i) {
+        float exponent = (float)(2 * i) / (float)rotary_dim;
+        float inv_freq = powf(freq_base, -exponent);
+        float angle = pos * inv_freq * freq_scale;
+        cos_out[i] = cosf(angle);
+        sin_out[i] = sinf(angle);
+    }
+}
+
+/* batched_rope, metal_runtime.mm:287-314 (the CPU form is applyRotaryEmbedding,
+ * quantization.cpp:773-793): adjacent pairs (2i, 2i+1) of every head, one cos/sin row per
+ * request. data [batch, n_heads, head_dim], in place. */
+void orc_batched_rope(float* data, const float* cos_t, const float* sin_t, uint32_t batch,
+                      uint32_t n_heads, uint32_t head_dim, uint32_t rotary_dim) {
+    uint32_t pairs = rotary_dim / 2;
+    for (uint32_t r = 0; r < batch; ++r)
+        for (uint32_t h = 0; h < n_heads; ++h)
+            for (uint32_t i = 0; i < pairs; ++i) {
+                float* d = data + ((size_t)r * n_heads + h) * head_dim;
+                float c = cos_t[(size_t)r * pairs + i], s = sin_t[(size_t)r * pairs + i];
+                volatile float a0 = d[2 * i] * c, a1 = d[2 * i + 1] * s; /* volatile: no contraction */
+                volatile float b0 = d[2 * i] * s, b1 = d[2 * i + 1] * c;
+                d[2 * i] = a0 - a1;
+                d[2 * i + 1] = b0 + b1;
+            }
+}
+
+/* encodeQkvSplitRopeCast, metal_runtime.mm:7915-8025: strided_copy_f32 x3 (mm:447-457),
+ * batched_rope on Q and K, cast_f32_to_f16 on K and V (mm:459-466, round to nearest even). */
+void orc_qkv_split_rope_cast(const float* qkv, float* q, float* k, float* v, uint16_t* k16,
+                             uint16_t* v16, const float* cos_t, const float* sin_t, uint32_t batch,
+                             uint32_t num_heads, uint32_t kv_heads, uint32_t head_dim,
+                             uint32_t qkv_rows, uint32_t q_rows, uint32_t k_rows, uint32_t v_rows,
+                             uint32_t rotary_dim) {
+    for (uint32_t r = 0; r < batch; ++r) {
+        memcpy(q + (size_t)r * q_rows, qkv + (size_t)r * qkv_rows, (size_t)q_rows * 4);
+        memcpy(k + (size_t)r * k_rows, qkv + (size_t)r * qkv_rows + q_rows, (size_t)k_rows * 4);
+        memcpy(v + (size_t)r * v_rows, qkv + (size_t)r * qkv_rows + q_rows + k_rows, (size_t)v_rows * 4);
+    }
+    if (rotary_dim > 0) {
+        orc_batched_rope(q, cos_t, sin_t, batch, num_heads, head_dim, rotary_dim);
+        orc_batched_rope(k, cos_t, sin_t, batch, kv_heads, head_dim, rotary_dim);
+    }
+    orc_cast_f32_to_f16_rne(k, k16, (size_t)batch * k_rows);
+    orc_cast_f32_to_f16_rne(v, v16, (size_t)batch * v_rows);
+}

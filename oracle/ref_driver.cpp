@@ -24,6 +24,7 @@
 #include "runtime/execution_graph.hpp"
 #include "runtime/operator_backend.hpp"
 #include "runtime/quant_utils.hpp"
+#include "runtime/quantization.hpp"
 #include "runtime/session.hpp"
 #include "runtime/float_convert.hpp"
 #include "runtime/paged_kv.hpp"
@@ -222,6 +223,24 @@ size_t ref_kvstate_pages(void* s, uint32_t* out, size_t cap) {
 size_t ref_kvstate_total(void* s) { return static_cast<RequestKVState*>(s)->total_tokens(); }
 void ref_kvstate_release(void* s, void* pool) {
     static_cast<RequestKVState*>(s)->release_all(*static_cast<PagePool*>(pool));
+}
+
+// computeRotaryCoefficients / applyRotaryEmbedding (compiler/runtime/quantization.cpp:773-823),
+// the reference's own CPU code for the rotation batched_rope performs on the GPU.
+size_t ref_compute_rotary(size_t position, size_t rotary_dim, float freq_base, float freq_scale,
+                          float* cos_out, float* sin_out) {
+    std::vector<float> c, s;
+    computeRotaryCoefficients(position, rotary_dim, freq_base, freq_scale, c, s);
+    for (size_t i = 0; i < c.size(); ++i) {
+        cos_out[i] = c[i];
+        sin_out[i] = s[i];
+    }
+    return c.size();
+}
+void ref_apply_rotary(float* data, const float* cos_in, const float* sin_in, size_t pairs, size_t head_dim,
+                      size_t rotary_dim) {
+    std::vector<float> c(cos_in, cos_in + pairs), s(sin_in, sin_in + pairs);
+    applyRotaryEmbedding(data, c, s, head_dim, rotary_dim);
 }
 
 }  // extern "C"

@@ -60,6 +60,34 @@ def main():
     hs = np.arange(0, 65536, 7, dtype=np.uint16)
     out["fp16/h"] = hs
     out["fp16/f"] = np.array([lib.ref_fp16_to_float(int(h)) for h in hs], np.float32)
+    # the reference's rotary coefficients and rotation (quantization.cpp:773-823)
+    import ctypes as C
+    fp = C.POINTER(C.c_float)
+    lib.ref_compute_rotary.restype = C.c_size_t
+    lib.ref_compute_rotary.argtypes = [C.c_size_t, C.c_size_t, C.c_float, C.c_float, fp, fp]
+    lib.ref_apply_rotary.restype = None
+    lib.ref_apply_rotary.argtypes = [fp, fp, fp, C.c_size_t, C.c_size_t, C.c_size_t]
+    positions = np.array([0, 1, 2, 17, 511, 2047, 32767], np.int64)
+    for rd, base, scale in ((64, 10000.0, 1.0), (128, 500000.0, 1.0), (32, 0.0, 0.0), (64, 10000.0, 0.25)):
+        cos = np.zeros((len(positions), rd // 2), np.float32)
+        sin = np.zeros_like(cos)
+        for i, pos in enumerate(positions):
+            n = lib.ref_compute_rotary(int(pos), rd, base, scale, cos[i].ctypes.data_as(fp), sin[i].ctypes.data_as(fp))
+            assert n == rd // 2
+        key = f"rope/{rd}_{base:g}_{scale:g}"
+        out[key + "/cos"], out[key + "/sin"] = cos, sin
+    out["rope/positions"] = positions
+    # one rotated head per position: head_dim 64, rotary_dim 64 and a partial rotary_dim 32
+    x = rng.standard_normal((len(positions), 64)).astype(np.float32)
+    out["rope/x"] = x
+    for rd in (64, 32):
+        y = x.copy()
+        cs = out["rope/64_10000_1/cos"] if rd == 64 else out["rope/32_0_0/cos"]
+        sn = out["rope/64_10000_1/sin"] if rd == 64 else out["rope/32_0_0/sin"]
+        for i in range(len(positions)):
+            lib.ref_apply_rotary(y[i].ctypes.data_as(fp), np.ascontiguousarray(cs[i]).ctypes.data_as(fp),
+                                 np.ascontiguousarray(sn[i]).ctypes.data_as(fp), rd // 2, 64, rd)
+        out[f"rope/y{rd}"] = y
     path = Path(__file__).with_name("reference_attention.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path} ({path.stat().st_size / 1024:.0f} KiB)")
