@@ -339,6 +339,29 @@ int mlc_encode_paged_prefill_attention(mlc_ctx* ctx, const void* q, const void* 
                                        size_t page_size_tokens, float scale, int q_dtype, int o_dtype,
                                        size_t capacity_pages);
 
+/* ---- split-KV across GPUs without a collective library: peer-memory exchange + combine --
+ * One kernel per step and rank: it stores this rank's (o, m, l) partial into every rank's
+ * gather buffer over NVLink peer memory, publishes a per-rank flag, waits - bounded, about a
+ * second, then MLC_DEVERR_WAIT_TIMEOUT in the device error word and no output - until all
+ * ranks' partials of this step are in its own memory, and applies the combine rule of
+ * mlc_encode_lse_combine. No counterpart in the reference (one device). Set-up, once:
+ *   mlc_exchange_create   allocates this rank's gather buffer (cudaMalloc, zeroed)
+ *   mlc_exchange_handle   64-byte cudaIpc handle of it; exchange the handles of all ranks by any
+ *                         host channel (torch.distributed all_gather_object, a file, MPI ...)
+ *   mlc_exchange_attach   handles = [world][MLC_IPC_HANDLE_BYTES], own entry ignored
+ * Ranks are separate processes, one per GPU of one node; every rank must make the same sequence
+ * of mlc_encode_exchange_lse_combine calls; synchronise the ranks on the host between the last
+ * call's completion and mlc_exchange_destroy. Capturable in a CUDA graph (the step counter is
+ * kept on the device). world <= 16, rows <= max_rows, head_dim % 4 == 0. */
+#define MLC_IPC_HANDLE_BYTES 64
+typedef struct mlc_exchange mlc_exchange;
+int mlc_exchange_create(mlc_ctx* ctx, int rank, int world, size_t max_rows, size_t head_dim, mlc_exchange** out);
+int mlc_exchange_handle(mlc_ctx* ctx, mlc_exchange* ex, void* handle_out);
+int mlc_exchange_attach(mlc_ctx* ctx, mlc_exchange* ex, const void* handles);
+int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float* o_partial,
+                                    const float* ml_partial, size_t rows, void* out, int o_dtype);
+void mlc_exchange_destroy(mlc_ctx* ctx, mlc_exchange* ex);
+
 /* ---- CUDA-graph bracketing of a pass --------------------------------------------------
  * Records the planned encode_* calls issued between begin and end into a CUDA graph
  * that replays them with one launch (the reference pays one command-buffer commit

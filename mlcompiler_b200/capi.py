@@ -71,6 +71,11 @@ _PROTOTYPES = {
                                             _sz, _sz, _sz, _sz]),
     "mlc_encode_qkv_split_rope_scatter_planned": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _sz, _sz]),
     "mlc_compute_rotary_coefficients": (_i, [_sz, _sz, _f, _f, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "mlc_exchange_create": (_i, [_vp, _i, _i, _sz, _sz, C.POINTER(_vp)]),
+    "mlc_exchange_handle": (_i, [_vp, _vp, _vp]),
+    "mlc_exchange_attach": (_i, [_vp, _vp, _vp]),
+    "mlc_encode_exchange_lse_combine": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _i]),
+    "mlc_exchange_destroy": (None, [_vp, _vp]),
     "mlc_ctx_last_attention_kernel": (_i, [_vp]),
     "mlc_ctx_read_trace": (C.c_uint32, [_vp, C.POINTER(C.c_uint64), _sz, _i]),
     "mlc_attn_plan_create": (_i, [_vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p, _u32p, _sz, _sz, _sz, _sz, _sz,
@@ -445,6 +450,46 @@ class Plan:
             self.destroy()
         except Exception:
             pass
+
+
+class PeerExchange:
+    """Gather buffer of one rank for the peer-memory exchange + combine kernel."""
+    HANDLE_BYTES = 64
+
+    def __init__(self, ex: Executor, rank: int, world: int, max_rows: int, head_dim: int):
+        self._ex = ex
+        h = _vp()
+        ex.check(ex._lib.mlc_exchange_create(ex._h, rank, world, max_rows, head_dim, C.byref(h)))
+        self.handle, self.rank, self.world = h, rank, world
+
+    def ipc_handle(self) -> bytes:
+        buf = (C.c_ubyte * self.HANDLE_BYTES)()
+        self._ex.check(self._ex._lib.mlc_exchange_handle(self._ex._h, self.handle, C.cast(buf, _vp)))
+        return bytes(buf)
+
+    def attach(self, handles: list[bytes]):
+        assert len(handles) == self.world and all(len(h) == self.HANDLE_BYTES for h in handles)
+        blob = b"".join(handles)
+        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        self._ex.check(self._ex._lib.mlc_exchange_attach(self._ex._h, self.handle, C.cast(buf, _vp)))
+
+    def attach_with_torch_distributed(self, group=None):
+        """Exchanges the handles with torch.distributed.all_gather_object and attaches."""
+        import torch.distributed as dist
+        if self.world == 1:
+            return
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.ipc_handle(), group=group)
+        self.attach(handles)
+
+    def encodeLseCombine(self, o_partial, ml_partial, rows, out, o_dtype=MLC_F32) -> bool:
+        return self._ex.status(self._ex._lib.mlc_encode_exchange_lse_combine(
+            self._ex._h, self.handle, _vp(_ptr(o_partial)), _vp(_ptr(ml_partial)), rows, _vp(_ptr(out)), o_dtype))
+
+    def destroy(self):
+        if self.handle and self._ex._h:
+            self._ex._lib.mlc_exchange_destroy(self._ex._h, self.handle)
+        self.handle = None
 
 
 class Graph:
