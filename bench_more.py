@@ -133,6 +133,8 @@ def main():
     ap.add_argument("--workload", choices=["cfg3", "cfg4", "cfg5"], required=True)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="cfg3 on several GPUs: peer-memory exchange kernel (default) or NCCL all-gather + combine")
     args = ap.parse_args()
     if args.workload == "cfg5":
         return run_cfg5(args)
@@ -141,7 +143,7 @@ def main():
     import torch.distributed as dist
     from bench import measured_peak_gbs
     from mlcompiler_b200 import Executor, sharding, synth
-    from mlcompiler_b200.capi import MLC_F16, MLC_F32
+    from mlcompiler_b200.capi import MLC_F16, MLC_F32, PeerExchange
 
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     if world > 1:
@@ -186,12 +188,25 @@ def main():
             ml_part = torch.zeros((N, H, 2), device=dev, dtype=torch.float32)
             out = torch.zeros((N, H, D), device=dev, dtype=torch.float16)
         plan = ex.createPlan(flat_local, off, lens, np.zeros(N, np.uint32), N, H, KVH, D, P, False, cap)
+        use_peer = world > 1 and args.exchange == "peer"
+        xc = None
+        if use_peer:
+            xc = PeerExchange(ex, rank, world, N * H, D)
+            xc.attach_with_torch_distributed()
+        graphs = None
 
         def step(i):
+            if graphs is not None:
+                graphs[i % copies].launch()
+                return
             assert ex.beginForwardPassCB()
             if world == 1:
                 ok = ex.encodePagedFlashAttentionPlanned(plan, q, kp[i % copies], vp[i % copies], out, case.scale, MLC_F16, MLC_F16)
                 assert ok, ex.last_error()
+            elif use_peer:
+                ok = ex.encodePagedAttentionPartialPlanned(plan, q, kp[i % copies], vp[i % copies], o_part, ml_part, case.scale, MLC_F16)
+                assert ok, ex.last_error()
+                assert xc.encodeLseCombine(o_part, ml_part, N * H, out, MLC_F16), ex.last_error()
             else:
                 ok = ex.encodePagedAttentionPartialPlanned(plan, q, kp[i % copies], vp[i % copies], o_part, ml_part, case.scale, MLC_F16)
                 assert ok, ex.last_error()
@@ -204,6 +219,19 @@ def main():
             step(i)
         assert ex.flushForwardPassCB(), ex.last_error()
         barrier()
+        if world == 1 or use_peer:
+            # only this library's kernels in a step: replay them as CUDA graphs, one per pool copy
+            built = []
+            for c in range(copies):
+                assert ex.beginForwardPassCB()
+                assert ex.beginCapture()
+                step(c)
+                built.append(ex.endCapture())
+            graphs = built
+            for i in range(copies * 2):     # every rank replays the same sequence: the exchange stays in step
+                step(i)
+            assert ex.flushForwardPassCB(), ex.last_error()
+            barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = ex.launchCount()
         assert ex.beginForwardPassCB()
@@ -215,8 +243,10 @@ def main():
         launches = ex.launchCount() - l0
         sec = reduce(e0.elapsed_time(e1) * 1e-3, dist.ReduceOp.MAX if world > 1 else None) / args.steps
         total_bytes = case.kv_bytes
-        workload = "cfg3: 4 requests x 32768 tokens, H32/KVH4/D64, KV sequence split over ranks, NCCL all-gather of (o,m,l), LSE combine"
-        extra = {"parallelism": f"sequence-sharded x{world}", "pool_copies_rotated": copies,
+        how = ("one GPU" if world == 1 else "partials pushed to the peers' memory, flags, combine - one kernel" if use_peer
+               else "NCCL all-gather of (o,m,l), LSE combine")
+        workload = "cfg3: 4 requests x 32768 tokens, H32/KVH4/D64, KV sequence split over ranks, " + how
+        extra = {"parallelism": f"sequence-sharded x{world}", "pool_copies_rotated": copies, "cuda_graph": graphs is not None,
                  "gather_bytes_per_rank": int((o_part.numel() + ml_part.numel()) * 4) if world > 1 else 0}
         n_req = N
     else:
@@ -282,6 +312,10 @@ def main():
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "peak_source": kind, "note": "per GPU"},
             "gpu_launches": int(launches)}))
+    if world > 1:
+        dist.barrier()
+    if args.workload == "cfg3" and xc is not None:
+        xc.destroy()
     plan.destroy()
     ex.close()
     if world > 1:
