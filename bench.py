@@ -10,13 +10,15 @@ over per-layer pools sized to the total pages + 10 %. One step = for every layer
 write one new K/V row per request into the pool, then run attention.
 
 `value` is KV GB/s with everything resident in HBM: the step is replayed from a
-CUDA graph (22 kernels, one per layer: the KV row write is fused into the attention
-kernel and consecutive kernels overlap by programmatic dependent launch) and timed with CUDA events
-on the launching stream. `e2e` is the same metric through the reference-shaped
-host-array entry points with host buffers: every step copies Q and the new K/V
-rows from pinned host memory, passes page tables / lengths / positions as host
-arrays (they grow by one token per step, as in serving), and copies the attention
-output back. With N > 1 (torchrun, one rank per GPU) every rank runs its own
+CUDA graph (per layer one attention kernel with the KV row write fused in, plus its
+merge kernel for requests split over CTAs; consecutive kernels overlap by programmatic
+dependent launch) and timed with CUDA events on the launching stream. `e2e` is the
+same metric through the C ABI with host buffers, the call sequence a walker makes:
+every step copies Q and the new K/V rows from pinned host memory, hands the step's
+page tables / lengths / positions / (page, slot) pairs over as host arrays (they grow
+by one token per step, as in serving) with one in-place plan update, issues one fused
+scatter + attention call per layer, and copies the attention output back. With N > 1
+(torchrun, one rank per GPU) every rank runs its own
 32-request batch: request sharding, no collective on the data path (weak scaling).
 
 `--impl reference` times MLcompiler's own executor-CPU attention (compiled from
@@ -375,6 +377,11 @@ def run_gpu_arm(args):
     h2d = q_host.numel() * 2 + kn_host.numel() * 2 + vn_host.numel() * 2
     d2h = o_host.numel() * 2
 
+    # The call sequence INTEGRATION.md recommends to a walker: per step one in-place plan update with the
+    # step's host tables, then one fused scatter + attention call per layer; Q / new K / new V rows come
+    # from pinned host memory and O goes back to it inside the timed region.
+    e2e_plan = ex.createPlan(flat, off, lens, q_pos, N, H, KVH, D, P, True, cap, page_ids=ids, slots_in_page=slots)
+
     def e2e_step(step):
         lens_s, q_pos_s, ids_s, slots_s, flat_s, off_s = tables(step)
         with torch.cuda.stream(stream):
@@ -382,11 +389,10 @@ def run_gpu_arm(args):
             kn_all.copy_(kn_host, non_blocking=True)
             vn_all.copy_(vn_host, non_blocking=True)
         assert ex.beginForwardPassCB()
+        assert e2e_plan.update(flat_s, off_s, lens_s, q_pos_s, ids_s, slots_s), ex.last_error()
         for L in range(LAYERS):
-            ok = ex.encodeScatterKVPagedBatched(k_pools[L], ids_s, slots_s, P, KVH, D, N, kn_all[L], cap)
-            ok = ok and ex.encodeScatterKVPagedBatched(v_pools[L], ids_s, slots_s, P, KVH, D, N, vn_all[L], cap)
-            ok = ok and ex.encodePagedFlashAttention(q_all[L], k_pools[L], v_pools[L], o_all[L], flat_s, off_s, lens_s,
-                                                     q_pos_s, N, H, KVH, D, P, True, case.scale, MLC_F16, MLC_F16, cap)
+            ok = ex.encodePagedDecodeStepPlanned(e2e_plan, q_all[L], kn_all[L], vn_all[L], k_pools[L], v_pools[L],
+                                                 o_all[L], case.scale, MLC_F16, MLC_F16)
             assert ok, ex.last_error()
         with torch.cuda.stream(stream):
             o_host.copy_(o_all, non_blocking=True)
@@ -435,6 +441,7 @@ def run_gpu_arm(args):
     graph.destroy()
     graph_attn.destroy()
     plan.destroy()
+    e2e_plan.destroy()
     ex.close()
     if world > 1:
         dist.destroy_process_group()

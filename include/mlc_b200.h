@@ -208,6 +208,15 @@ int mlc_attn_plan_create(mlc_ctx* ctx, const uint32_t* page_tables_flat, size_t 
                          size_t page_size_tokens, int apply_causal, size_t capacity_pages,
                          mlc_attn_plan** out);
 void mlc_attn_plan_destroy(mlc_ctx* ctx, mlc_attn_plan* plan);
+/* The next decode step's tables into the same plan (same head shape, page size, causal flag and
+ * capacity; batch may change): what the walker's per-step table rebuild
+ * (batched_walker.cpp:127-149, 316-325) becomes. Reuses the plan's pinned and device buffers; the
+ * upload is ordered on the context's stream behind the kernels already enqueued with the old
+ * tables. Not inside a graph capture. */
+int mlc_attn_plan_update(mlc_ctx* ctx, mlc_attn_plan* plan, const uint32_t* page_tables_flat,
+                         size_t n_page_tables_flat, const uint32_t* page_table_offsets,
+                         const uint32_t* seq_lens, const uint32_t* q_positions, const uint32_t* page_ids,
+                         const uint32_t* slots_in_page, size_t batch);
 /* encodePagedFlashAttention (metal_runtime.hpp:510-523) with the tables taken from `plan`. */
 int mlc_encode_paged_flash_attention_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
                                              const void* k_pages, const void* v_pages, void* o,

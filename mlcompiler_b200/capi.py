@@ -81,6 +81,7 @@ _PROTOTYPES = {
     "mlc_attn_plan_create": (_i, [_vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p, _u32p, _sz, _sz, _sz, _sz, _sz,
                                   _i, _sz, C.POINTER(_vp)]),
     "mlc_attn_plan_destroy": (None, [_vp, _vp]),
+    "mlc_attn_plan_update": (_i, [_vp, _vp, _u32p, _sz, _u32p, _u32p, _u32p, _u32p, _u32p, _sz]),
     "mlc_encode_paged_flash_attention_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_scatter_kv_pair_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "mlc_static_scratch_bytes": (_sz, []),
@@ -439,6 +440,23 @@ class Executor:
 class Plan:
     def __init__(self, ex: Executor, handle):
         self._ex, self.handle = ex, handle
+
+    def update(self, page_tables_flat, page_table_offsets, seq_lens, q_positions, page_ids=None,
+               slots_in_page=None) -> bool:
+        """New tables (next decode step) into the same plan object; its buffers are reused."""
+        flat, pflat = _u32(page_tables_flat)
+        off, poff = _u32(page_table_offsets)
+        sl, psl = _u32(seq_lens)
+        qp, pqp = _u32(q_positions)
+        ids = sl_in = None
+        pids = pslots = None
+        if page_ids is not None:
+            ids, pids = _u32(page_ids)
+            sl_in, pslots = _u32(slots_in_page)
+        if off.size != sl.size + 1 or qp.size != sl.size:
+            return self._ex.status(1)
+        return self._ex.status(self._ex._lib.mlc_attn_plan_update(
+            self._ex._h, self.handle, pflat, flat.size, poff, psl, pqp, pids, pslots, sl.size))
 
     def destroy(self):
         if self.handle and self._ex._h:

@@ -440,6 +440,31 @@ int mlc_attn_plan_create(mlc_ctx* ctx, const uint32_t* page_tables_flat, size_t 
     return MLC_OK;
 }
 
+int mlc_attn_plan_update(mlc_ctx* ctx, mlc_attn_plan* plan, const uint32_t* page_tables_flat,
+                         size_t n_page_tables_flat, const uint32_t* page_table_offsets, const uint32_t* seq_lens,
+                         const uint32_t* q_positions, const uint32_t* page_ids, const uint32_t* slots_in_page,
+                         size_t batch) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if ((page_ids == nullptr) != (slots_in_page == nullptr)) return ctx->fail(MLC_ERR_INVALID_ARG, "page_ids and slots_in_page go together");
+    PlanKey key = plan->key;   // same shape, new tables
+    key.batch = batch;
+    int st = validate_tables(ctx, key, nullptr, page_tables_flat, n_page_tables_flat, page_table_offsets, seq_lens,
+                             q_positions, plan->key.capacity);
+    if (st != MLC_OK) return st;
+    if (page_ids)
+        for (size_t r = 0; r < batch; ++r) {
+            if (key.capacity && page_ids[r] >= key.capacity)
+                return ctx->fail(MLC_ERR_BOUNDS, "page_ids[%zu]=%u >= capacity %zu", r, page_ids[r], key.capacity);
+            if (slots_in_page[r] >= key.P)
+                return ctx->fail(MLC_ERR_BOUNDS, "slots_in_page[%zu]=%u >= page size", r, slots_in_page[r]);
+        }
+    DeviceGuard guard(ctx->device);
+    plan->key = key;
+    // the rebuild waits for the previous upload to have left the pinned staging copy; the device copy is
+    // overwritten in stream order, after the kernels already enqueued with the old tables
+    return build_plan(ctx, *plan, page_tables_flat, page_table_offsets, seq_lens, q_positions, page_ids, slots_in_page);
+}
+
 void mlc_attn_plan_destroy(mlc_ctx* ctx, mlc_attn_plan* plan) {
     if (!ctx || !plan) return;
     DeviceGuard guard(ctx->device);

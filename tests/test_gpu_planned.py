@@ -231,3 +231,57 @@ def test_split_kv_partials_and_combine(executor, oracle_mod, parts, shape):
         assert_attention_close(norm_got[live], norm_ref[live])
     for p in plans:
         p.destroy()
+
+
+def test_plan_update_follows_growing_requests(executor, oracle_mod):
+    """One plan object updated in place for consecutive decode steps (each request one token longer,
+    crossing page boundaries, one request finishing): every step equals the oracle's scatter + attention."""
+    import torch
+    H, KVH, D, P = 32, 4, 64, 64
+    lens0 = np.array([62, 127, 300, 64], np.uint32)
+    case = synth.make_case(41, lens0 + 4, H, KVH, D, P=P)          # tables with room for 4 more tokens
+    dev = torch.device("cuda:0")
+    kp = torch.from_numpy(case.k_pool.view(np.int16)).to(dev)
+    vp = torch.from_numpy(case.v_pool.view(np.int16)).to(dev)
+    kp_ref = case.k_pool.view(np.uint16).reshape(-1).copy()
+    vp_ref = case.v_pool.view(np.uint16).reshape(-1).copy()
+    rng = np.random.default_rng(9)
+    plan = None
+    for step in range(4):
+        alive = [0, 1, 2, 3] if step < 2 else [0, 2, 3]           # request 1 leaves after two steps
+        lens = (lens0[alive] + step + 1).astype(np.uint32)          # length after this step's token
+        off = np.zeros(len(alive) + 1, np.uint32)
+        flat = []
+        for i, r in enumerate(alive):
+            n_pages = (int(lens[i]) + P - 1) // P
+            flat.extend(case.pt_flat[case.pt_off[r]:case.pt_off[r] + n_pages].tolist())
+            off[i + 1] = len(flat)
+        flat = np.array(flat, np.uint32)
+        q_pos = lens - 1
+        ids = np.array([flat[off[i] + (int(lens[i]) - 1) // P] for i in range(len(alive))], np.uint32)
+        slots = ((lens - 1) % P).astype(np.uint32)
+        n = len(alive)
+        q = rng.standard_normal((n, H, D), dtype=np.float32).astype(np.float16)
+        kn = rng.standard_normal((n, KVH, D), dtype=np.float32).astype(np.float16)
+        vn = rng.standard_normal((n, KVH, D), dtype=np.float32).astype(np.float16)
+        if plan is None:
+            plan = executor.createPlan(flat, off, lens, q_pos, n, H, KVH, D, P, True, case.capacity,
+                                       page_ids=ids, slots_in_page=slots)
+        else:
+            assert plan.update(flat, off, lens, q_pos, ids, slots), executor.last_error()
+        up = lambda a: torch.from_numpy(a.view(np.int16)).to(dev)
+        o = torch.full((n, H, D), float("nan"), dtype=torch.float16, device=dev)
+        assert executor.beginForwardPassCB()
+        assert executor.encodePagedDecodeStepPlanned(plan, up(q), up(kn), up(vn), kp, vp, o, case.scale, MLC_F16,
+                                                     MLC_F16), executor.last_error()
+        assert executor.flushForwardPassCB(), executor.last_error()
+        oracle_mod.scatter_kv_paged_batched_f16(kn, kp_ref, ids, slots, P, KVH, D)
+        oracle_mod.scatter_kv_paged_batched_f16(vn, vp_ref, ids, slots, P, KVH, D)
+        want = oracle_mod.paged_attention(q.astype(np.float32), kp_ref.view(np.float16), vp_ref.view(np.float16), flat,
+                                          off, lens, q_pos, H, KVH, D, P, causal=True, scale=case.scale)
+        assert np.array_equal(kp.cpu().numpy().view(np.uint16).reshape(-1), kp_ref)
+        assert np.array_equal(vp.cpu().numpy().view(np.uint16).reshape(-1), vp_ref)
+        assert_attention_close(o.float().cpu().numpy(), want)
+    # rules: a table that does not fit its pages is rejected and the plan stays usable
+    assert not plan.update(flat, off, lens + 10000, q_pos, ids, slots)
+    plan.destroy()
