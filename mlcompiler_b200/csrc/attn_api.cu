@@ -320,7 +320,7 @@ int finish_sync(mlc_ctx* ctx, const char* what) {
     uint32_t word = 0;
     MLCB_CUDA(ctx, cudaMemcpy(&word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
     if (word) {
-        cudaMemset(ctx->d_err, 0, 4);
+        reset_after_device_error(ctx);
         return ctx->fail(MLC_ERR_DEVICE_FLAG, "%s recorded error word 0x%x", what, word);
     }
     return MLC_OK;

@@ -155,6 +155,9 @@ struct DecodeParams {
     int step;           // 1: decode-step variant (fused row write, early start)
     int pdl;            // 1: launched with programmatic stream serialisation
     unsigned long long* trace;  // optional [cta][warp][8] %globaltimer stamps (MLC_B200_TRACE)
+    // In-kernel merge: one arrival counter per (split segment, warp); null = a merge kernel follows.
+    uint32_t* seg_counters;
+    uint32_t n_segs;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -260,6 +263,9 @@ __device__ __forceinline__ void write_rows(const DecodeParams& prm, uint32_t req
 // ------------------------------------------------------------------------------
 // the attention kernel
 // ------------------------------------------------------------------------------
+template <int D, bool G16, bool CG>
+__device__ __forceinline__ void merge_segment(const DecodeParams& prm, const SegDesc& sd, uint32_t warp, uint32_t lane);
+
 template <int D, bool G16>
 __global__ void __launch_bounds__(kDecodeWarps * 32)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -605,36 +611,73 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 for (int n = 0; n < NT_O; ++n) wo[n * 32 + lane] = make_float2(o_acc[n][0], o_acc[n][1]);
                 reinterpret_cast<float2*>(prm.work_ml)[unit * 32 + lane] = make_float2(m_run[0], l_run[0]);
             }
+            if (prm.seg_counters) {
+                // Publish: the warp's stores, a warp barrier (orders them before lane 0's next
+                // operation), then a release reduction on the segment's counter for this warp -
+                // fire and forget, nothing waits for a return value.
+                __syncwarp();
+                if (lane == 0) {
+                    uint32_t* c = prm.seg_counters + static_cast<size_t>(d1.y) * kDecodeWarps + warp;
+                    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c) : "memory");
+                }
+            }
             if (pi == 0) stamp(4);
         } else {
             write_rows<D, G16>(prm, req, head, lane, o_acc, m_run, l_run);
         }
         if (pi + 1 == n_pieces) stamp(7);
     }
+
+    // ---- in-kernel merge of the split segments: segment s belongs to CTA s mod gridDim ----
+    // Every CTA of this grid is resident (the grid is at most one CTA per SM and at most two
+    // grids overlap), so the pieces a merger waits for are running or done. The wait is bounded.
+    if (prm.seg_counters && !dead) {
+        for (uint32_t seg = cta; seg < prm.n_segs; seg += gridDim.x) {
+            const uint4 sdw = __ldg(reinterpret_cast<const uint4*>(prm.seg_desc) + seg);
+            SegDesc sd;
+            sd.req = sdw.x; sd.hb = sdw.y; sd.first_slot = sdw.z; sd.n_parts = sdw.w;
+            if (sd.hb * kDecodeWarps + warp >= prm.KVH) continue;
+            uint32_t* c = prm.seg_counters + static_cast<size_t>(seg) * kDecodeWarps + warp;
+            uint32_t seen = 0;
+            if (lane == 0) {
+                for (uint32_t i = 0; i < (1u << 20); ++i) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(c) : "memory");
+                    if (v >= sd.n_parts) {
+                        seen = 1;
+                        break;
+                    }
+                }
+                if (seen) *c = 0;  // ready for the next launch (which starts publishing only after this grid is done)
+                else atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
+            }
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (!seen) continue;
+            merge_segment<D, G16, true>(prm, sd, warp, lane);
+        }
+        stamp(5);
+    }
 }
 
 // ------------------------------------------------------------------------------
-// the merge kernel: one CTA per split (request, head block), one warp per KV head
+// merging the pieces of a split (request, head block): one warp per KV head
 // ------------------------------------------------------------------------------
-template <int D, bool G16>
-__global__ void __launch_bounds__(kDecodeWarps * 32)
-paged_decode_merge_kernel(const DecodeParams prm) {
+// CG: read the partials with L1-bypassing loads. Needed when the merge runs inside the kernel
+// that produced them (this SM's L1 may still hold lines of the same workspace from an earlier
+// launch); a separate merge kernel starts with a clean L1.
+template <typename T, bool CG>
+__device__ __forceinline__ T ld_partial(const T* p) {
+    if constexpr (CG) return __ldcg(p);
+    else return *p;
+}
+
+template <int D, bool G16, bool CG>
+__device__ __forceinline__ void merge_segment(const DecodeParams& prm, const SegDesc& sd, uint32_t warp, uint32_t lane) {
     constexpr int NT_O = D / 8;
     constexpr int ROWSETS = G16 ? 2 : 1;
     constexpr int FR = G16 ? 4 : 2;  // floats per lane per output n-tile
     constexpr int BATCH = (NT_O * FR) <= 16 ? 12 : ((NT_O * FR) <= 32 ? 6 : 3);
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // The segment descriptor is plan data: read it while the attention kernel still runs.
-    // Then let the next kernel in the stream start its own prologue, and wait until the
-    // attention kernel that produced the partials has completed.
-    const uint4 sdw = __ldg(reinterpret_cast<const uint4*>(prm.seg_desc) + blockIdx.x);
-    SegDesc sd;
-    sd.req = sdw.x; sd.hb = sdw.y; sd.first_slot = sdw.z; sd.n_parts = sdw.w;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t head = sd.hb * kDecodeWarps + warp;
-    if (head >= prm.KVH) return;
-
     float o_acc[NT_O][4];
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f;
@@ -649,21 +692,21 @@ paged_decode_merge_kernel(const DecodeParams prm) {
             const uint32_t k = (k0 + bi < sd.n_parts) ? k0 + bi : sd.n_parts - 1;
             const size_t u = static_cast<size_t>(sd.first_slot + k) * kDecodeWarps + warp;
             if (G16) {
-                const float4 ml = reinterpret_cast<const float4*>(prm.work_ml)[u * 32 + lane];
+                const float4 ml = ld_partial<float4, CG>(reinterpret_cast<const float4*>(prm.work_ml) + u * 32 + lane);
                 mlb[bi][0] = ml.x; mlb[bi][1] = ml.y; mlb[bi][FR - 2] = ml.z; mlb[bi][FR - 1] = ml.w;
                 const float4* wo = reinterpret_cast<const float4*>(prm.work_o) + u * NT_O * 32;
 #pragma unroll
                 for (int n = 0; n < NT_O; ++n) {
-                    const float4 v = wo[n * 32 + lane];
+                    const float4 v = ld_partial<float4, CG>(wo + n * 32 + lane);
                     ob[bi][n][0] = v.x; ob[bi][n][1] = v.y; ob[bi][n][FR - 2] = v.z; ob[bi][n][FR - 1] = v.w;
                 }
             } else {
-                const float2 ml = reinterpret_cast<const float2*>(prm.work_ml)[u * 32 + lane];
+                const float2 ml = ld_partial<float2, CG>(reinterpret_cast<const float2*>(prm.work_ml) + u * 32 + lane);
                 mlb[bi][0] = ml.x; mlb[bi][1] = ml.y;
                 const float2* wo = reinterpret_cast<const float2*>(prm.work_o) + u * NT_O * 32;
 #pragma unroll
                 for (int n = 0; n < NT_O; ++n) {
-                    const float2 v = wo[n * 32 + lane];
+                    const float2 v = ld_partial<float2, CG>(wo + n * 32 + lane);
                     ob[bi][n][0] = v.x; ob[bi][n][1] = v.y;
                 }
             }
@@ -687,6 +730,25 @@ paged_decode_merge_kernel(const DecodeParams prm) {
         }
     }
     write_rows<D, G16>(prm, sd.req, head, lane, o_acc, m_run, l_run);
+}
+
+// The merge as a kernel of its own (one CTA per split segment), chained behind the attention
+// kernel by programmatic dependent launch. Used when the launch has no arrival counters
+// (caller-provided scratch).
+template <int D, bool G16>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+paged_decode_merge_kernel(const DecodeParams prm) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // The segment descriptor is plan data: read it while the attention kernel still runs.
+    // Then let the next kernel in the stream start its own prologue, and wait until the
+    // attention kernel that produced the partials has completed.
+    const uint4 sdw = __ldg(reinterpret_cast<const uint4*>(prm.seg_desc) + blockIdx.x);
+    SegDesc sd;
+    sd.req = sdw.x; sd.hb = sdw.y; sd.first_slot = sdw.z; sd.n_parts = sdw.w;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (sd.hb * kDecodeWarps + warp >= prm.KVH) return;
+    merge_segment<D, G16, false>(prm, sd, warp, lane);
 }
 
 // ------------------------------------------------------------------------------
@@ -742,7 +804,7 @@ static int launch_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams
     cfg.numAttrs = prm.pdl ? 1 : 0;
     MLCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<D, G16>, mk, mv, prm));
     ++ctx->launches;
-    if (plan.n_segs) {
+    if (plan.n_segs && !prm.seg_counters) {
         // the merge is always chained programmatically: before its wait it touches nothing
         cudaLaunchConfig_t mc{};
         mc.gridDim = dim3(plan.n_segs);
@@ -772,6 +834,7 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     CUtensorMap mk, mv;
     char* work = nullptr;
     uint32_t parity = 0;
+    bool use_counters = false;
     if (a.ext_work) {
         // Caller-provided workspace: nothing is allocated on this path, neither on the
         // device nor (the tensor maps are encoded on the stack, uncached) on the host.
@@ -785,7 +848,17 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
         parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
         work = static_cast<char*>(a.ext_work) + parity * half;
     } else {
-        st = ensure_workspace(ctx, 2 * (o_bytes + ml_bytes) + 512, 0);
+        // MLC_B200_DECODE_INKERNEL_MERGE=1: merge inside the attention kernel (arrival counters
+        // [n_segs][warps], mergers poll) instead of the chained merge kernel. Measured on cfg2 it is
+        // no faster (17.0 vs 16.8 us per layer on the same GPU): the chained merge kernel is already
+        // resident and waiting when the attention kernel ends. Kept as an option, off by default.
+        static const bool merge_kernel = [] {
+            const char* v = std::getenv("MLC_B200_DECODE_INKERNEL_MERGE");
+            return !(v && *v && std::atoi(v) != 0);
+        }();
+        use_counters = !merge_kernel && plan.n_segs > 0;
+        st = ensure_workspace(ctx, 2 * (o_bytes + ml_bytes) + 512,
+                              use_counters ? static_cast<size_t>(plan.n_segs) * kDecodeWarps : 0);
         if (st != MLC_OK) return st;
         if ((st = get_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
         if ((st = get_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
@@ -825,6 +898,8 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     // plan (and, in a decode step, K/V rows of earlier steps).
     prm.pdl = 1;
     prm.stages = plan.stages;
+    prm.seg_counters = use_counters ? ctx->d_counters : nullptr;
+    prm.n_segs = plan.n_segs;
     // traces of consecutive launches alternate between the two halves of the buffer
     const size_t trace_need = static_cast<size_t>(plan.n_cta) * kDecodeWarps * 8;
     prm.trace = ctx->d_trace && trace_need <= ctx->trace_words / 2 ? ctx->d_trace + parity * (ctx->trace_words / 2) : nullptr;

@@ -114,7 +114,7 @@ int prefill_impl(mlc_ctx* ctx, bool sync, const void* q, const void* k_pages, co
         uint32_t word = 0;
         MLCB_CUDA(ctx, cudaMemcpy(&word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
         if (word) {
-            cudaMemset(ctx->d_err, 0, 4);
+            reset_after_device_error(ctx);
             return ctx->fail(MLC_ERR_DEVICE_FLAG, "prefill attention recorded error word 0x%x", word);
         }
     }

@@ -96,6 +96,11 @@ int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters) {
     return MLC_OK;
 }
 
+void reset_after_device_error(mlc_ctx* ctx) {
+    cudaMemset(ctx->d_err, 0, 4);
+    if (ctx->d_counters && ctx->n_counters) cudaMemset(ctx->d_counters, 0, ctx->n_counters * 4);
+}
+
 size_t resolve_capacity(const mlc_ctx* ctx, const void* pool, size_t claimed, size_t page_bytes) {
     if (claimed) return claimed;
     auto it = ctx->allocs.find(pool);
@@ -200,7 +205,7 @@ int mlc_device_error_word(mlc_ctx* ctx, uint32_t* word) {
     DeviceGuard guard(ctx->device);
     MLCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     MLCB_CUDA(ctx, cudaMemcpy(word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
-    if (*word) MLCB_CUDA(ctx, cudaMemset(ctx->d_err, 0, 4));
+    if (*word) reset_after_device_error(ctx);
     return MLC_OK;
 }
 
@@ -284,7 +289,7 @@ int mlc_pass_flush(mlc_ctx* ctx) {
     uint32_t word = 0;
     MLCB_CUDA(ctx, cudaMemcpy(&word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
     if (word) {
-        cudaMemset(ctx->d_err, 0, 4);
+        reset_after_device_error(ctx);
         return ctx->fail(MLC_ERR_DEVICE_FLAG, "a kernel of this pass recorded error word 0x%x", word);
     }
     return MLC_OK;

@@ -103,6 +103,9 @@ void* stage_to_device(mlc_ctx* ctx, const void* host, size_t bytes);
 bool stage_reserve(mlc_ctx* ctx, size_t bytes, void** host, void** dev);
 bool stage_commit(mlc_ctx* ctx, void* host, void* dev, size_t bytes);
 void stage_reset(mlc_ctx* ctx);
+// After a kernel reported an error word: clears the word and re-zeroes the split-KV arrival
+// counters, which a launch that gave up may have left half counted. The stream is idle here.
+void reset_after_device_error(mlc_ctx* ctx);
 // Grows the split-KV workspace / counters (synchronises when it has to reallocate).
 int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters);
 // Number of pages a pool pointer can hold given the caller's claim (0 = unknown)

@@ -285,3 +285,43 @@ def test_plan_update_follows_growing_requests(executor, oracle_mod):
     # rules: a table that does not fit its pages is rejected and the plan stays usable
     assert not plan.update(flat, off, lens + 10000, q_pos, ids, slots)
     plan.destroy()
+
+
+def test_in_kernel_merge_option_matches_oracle():
+    """MLC_B200_DECODE_INKERNEL_MERGE=1 (arrival counters + polling mergers inside the attention
+    kernel, no merge kernel) in a child process: same results, one launch per layer."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import numpy as np, torch, oracle
+from mlcompiler_b200 import Executor, synth
+from mlcompiler_b200.capi import MLC_F16
+from tests.util import DeviceCase, assert_attention_close
+ex = Executor(0)
+for seed, lens, shape in ((51, [2048, 64, 700, 1500, 33], dict(H=32, KVH=4, D=64)), (52, [3000, 129], dict(H=32, KVH=8, D=128))):
+    case = synth.make_case(seed, lens, **shape)
+    dc = DeviceCase(case)
+    plan = ex.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, case.N, case.H, case.KVH, case.D, case.P,
+                         True, case.capacity, page_ids=case.page_ids, slots_in_page=case.slots)
+    for rep in range(3):
+        o = dc.out()
+        l0 = ex.launchCount()
+        assert ex.beginForwardPassCB()
+        assert ex.encodePagedDecodeStepPlanned(plan, dc.q, dc.k_new, dc.v_new, dc.k_pool, dc.v_pool, o, case.scale, MLC_F16, MLC_F16), ex.last_error()
+        assert ex.flushForwardPassCB(), ex.last_error()
+        assert ex.launchCount() - l0 == 1
+        kp = case.k_pool.view(np.uint16).reshape(-1).copy(); vp = case.v_pool.view(np.uint16).reshape(-1).copy()
+        oracle.scatter_kv_paged_batched_f16(case.k_new, kp, case.page_ids, case.slots, case.P, case.KVH, case.D)
+        oracle.scatter_kv_paged_batched_f16(case.v_new, vp, case.page_ids, case.slots, case.P, case.KVH, case.D)
+        want = oracle.paged_attention(case.q.astype(np.float32), kp.view(np.float16), vp.view(np.float16), case.pt_flat, case.pt_off,
+                                      case.seq_lens, case.q_pos, case.H, case.KVH, case.D, case.P, causal=True, scale=case.scale)
+        assert_attention_close(o.float().cpu().numpy(), want)
+    plan.destroy()
+ex.close()
+print("ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, MLC_B200_DECODE_INKERNEL_MERGE="1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
