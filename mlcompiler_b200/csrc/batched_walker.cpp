@@ -4,6 +4,8 @@
 #include <cmath>
 #include <cstring>
 
+#include <cuda_fp16.h>
+
 #include "ctx.hpp"
 
 namespace mlcb {
@@ -126,6 +128,85 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
         out.per_request.push_back(std::move(p));
     }
     return out;
+}
+
+std::vector<float> BatchedWalker::prefill(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor) {
+    PagedAttentionExecutor& ex = exec_;
+    mlc_ctx* ctx = ex.ctx_;
+    PagedKVStorage* storage = ex.storage_;
+    const size_t n = tokens.size();
+    if (n == 0 || !storage || !ex.pool_) return {};
+    const uint32_t H = ex.H_, KVH = ex.KVH_, D = ex.D_, P = storage->page_size_tokens();
+
+    PagedAttentionExecutor::PerRequest& req = ex.ensure_request(request_id);
+    if (!req.page_state) {
+        req.page_state.reset(new RequestKVState());
+        req.page_state->request_id = request_id;
+        req.page_state->page_size_tokens = ex.page_size_tokens_;
+    }
+    // one (page, slot) per token of the chunk; a pool that runs out fails the prefill and the
+    // pages taken so far stay with the request until it is released, as in the token loop
+    std::vector<uint32_t> page_ids(n), slot_ids(n);
+    std::vector<RequestSlot> slots(n);
+    for (size_t i = 0; i < n; ++i) {
+        auto loc = req.page_state->extend_one_token(*ex.pool_);
+        if (!loc) return {};
+        page_ids[i] = loc->first;
+        slot_ids[i] = loc->second;
+        slots[i] = RequestSlot{request_id, tokens[i], cursor + i};
+    }
+    const std::vector<uint32_t>& table = req.page_state->page_table;
+    const uint32_t pt_off[2] = {0u, static_cast<uint32_t>(table.size())};
+    const uint32_t seq_len = static_cast<uint32_t>(req.page_state->total_tokens());
+    const uint32_t q_start = static_cast<uint32_t>(cursor), q_len = static_cast<uint32_t>(n);
+    if (static_cast<uint64_t>(q_start) + q_len != seq_len) return {};  // the chunk must end the sequence
+
+    const size_t q_elems = n * H * D, kv_elems = n * KVH * D;
+    void* buf_q = mlc_cached_buffer(ctx, "walker_prefill_q_f16", q_elems * 2);
+    void* buf_k = mlc_cached_buffer(ctx, "walker_prefill_k_f16", kv_elems * 2);
+    void* buf_v = mlc_cached_buffer(ctx, "walker_prefill_v_f16", kv_elems * 2);
+    void* buf_o = mlc_cached_buffer(ctx, "walker_prefill_o_f16", q_elems * 2);
+    if (!buf_q || !buf_k || !buf_v || !buf_o) return {};
+    q_host_.resize(q_elems);
+    q16_host_.resize(q_elems);
+    k_host_.resize(kv_elems);
+    v_host_.resize(kv_elems);
+
+    const float scale = 1.0f / std::sqrt(static_cast<float>(D));
+    const size_t cap = storage->capacity_pages();
+    for (uint32_t layer = 0; layer < ex.L_; ++layer) {
+        ex.source_->fill(layer, slots, H, KVH, D, q_host_.data(), k_host_.data(), v_host_.data());
+        for (size_t i = 0; i < q_elems; ++i) {  // the decode kernel makes the same cast when it loads fp32 Q
+            const __half_raw h = __float2half_rn(q_host_[i]);
+            q16_host_[i] = h.x;
+        }
+        if (mlc_upload(ctx, buf_q, q16_host_.data(), q_elems * 2, 0) != MLC_OK ||
+            mlc_upload(ctx, buf_k, k_host_.data(), kv_elems * 2, 0) != MLC_OK ||
+            mlc_upload(ctx, buf_v, v_host_.data(), kv_elems * 2, 0) != MLC_OK)
+            return {};
+        void* kp = storage->k_buffer(layer);
+        void* vp = storage->v_buffer(layer);
+        bool ok = mlc_pass_begin(ctx) == MLC_OK;
+        ok = ok && mlc_encode_scatter_kv_pair_paged_batched_f16(ctx, kp, vp, page_ids.data(), slot_ids.data(), P, KVH,
+                                                                D, n, buf_k, buf_v, cap) == MLC_OK;
+        ok = ok && mlc_encode_paged_prefill_attention(ctx, buf_q, kp, vp, buf_o, table.data(), table.size(), pt_off,
+                                                      &seq_len, &q_start, &q_len, 1, H, KVH, D, P, scale, MLC_F16,
+                                                      MLC_F16, cap) == MLC_OK;
+        ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
+        if (!ok) return {};
+    }
+    // the last token's row of the last layer
+    o16_host_.resize(static_cast<size_t>(H) * D);
+    if (mlc_download(ctx, buf_o, o16_host_.data(), o16_host_.size() * 2, (n - 1) * static_cast<size_t>(H) * D * 2) != MLC_OK)
+        return {};
+    std::vector<float> last(o16_host_.size());
+    for (size_t i = 0; i < last.size(); ++i) {
+        __half_raw h;
+        h.x = o16_host_[i];
+        last[i] = __half2float(__half(h));
+    }
+    req.next_position = cursor + n;
+    return last;
 }
 
 }  // namespace runtime

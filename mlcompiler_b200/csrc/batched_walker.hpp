@@ -14,6 +14,11 @@ class BatchedWalker {
 public:
     explicit BatchedWalker(PagedAttentionExecutor& exec) : exec_(exec) {}
     BatchedDecodeOutput step(const std::vector<RequestSlot>& slots);
+    // All tokens of a prompt chunk in one pass per layer: the chunk's K/V rows are scattered,
+    // then chunked causal attention runs over the request's pages. Returns the last token's
+    // attention output of the last layer, or {} on failure. The reference reaches the same
+    // state with one decode pass per token (batched_executor.cpp:450-467).
+    std::vector<float> prefill(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor);
 
 private:
     PagedAttentionExecutor& exec_;
@@ -21,6 +26,7 @@ private:
     std::vector<float> q_host_;
     std::vector<uint16_t> k_host_, v_host_;
     std::vector<float> o_host_;
+    std::vector<uint16_t> q16_host_, o16_host_;
 };
 
 }  // namespace runtime

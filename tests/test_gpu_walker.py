@@ -20,11 +20,12 @@ H, KVH, D, L, P = 32, 4, 64, 3, 64
 SEED = 0xBEEF
 
 
-def make_stack(executor, capacity=24, layers=L):
+def make_stack(executor, capacity=24, layers=L, shape=None):
+    h, kvh, d = shape or (H, KVH, D)
     pool = PagePool(capacity)
-    storage = PagedKVStorage(executor, capacity, layers, P, KVH, D, 2)
+    storage = PagedKVStorage(executor, capacity, layers, P, kvh, d, 2)
     assert storage.initialize()
-    ex = PagedAttentionExecutor(executor, H, KVH, D, layers, SEED)
+    ex = PagedAttentionExecutor(executor, h, kvh, d, layers, SEED)
     ex.attach_page_pool(pool, P)
     ex.attach_paged_storage(storage)
     return pool, storage, ex
@@ -33,13 +34,15 @@ def make_stack(executor, capacity=24, layers=L):
 class OracleReplay:
     """Host model of what the pools of the LAST layer hold and what attention must return."""
 
-    def __init__(self, oracle_mod, capacity, layer):
+    def __init__(self, oracle_mod, capacity, layer, shape=None):
         self.o, self.layer = oracle_mod, layer
-        self.k = np.zeros((capacity, P, KVH, D), np.float16)
-        self.v = np.zeros((capacity, P, KVH, D), np.float16)
+        self.H, self.KVH, self.D = shape or (H, KVH, D)
+        self.k = np.zeros((capacity, P, self.KVH, self.D), np.float16)
+        self.v = np.zeros((capacity, P, self.KVH, self.D), np.float16)
 
     def step(self, slots, tables):
         """slots: [(rid, token, pos)], tables: {rid: (page_table, total_tokens)} AFTER the extension."""
+        H, KVH, D = self.H, self.KVH, self.D
         qs, flat, off, lens, qpos = [], [], [0], [], []
         for rid, tok, pos in slots:
             table, total = tables[rid]
@@ -100,17 +103,60 @@ def test_pool_exhaustion_fails_the_pass(executor):
     storage.destroy()
 
 
-def test_prefill_is_token_by_token_decode(executor, oracle_mod):
-    """batched_executor.cpp:450-467."""
+@pytest.mark.parametrize("reference_order", [True, False])
+def test_prefill_equals_token_by_token_decode(executor, oracle_mod, reference_order):
+    """batched_executor.cpp:450-467: a prompt is fed as one decode pass per token. The reference call
+    order keeps that loop; the default feeds the chunk at once (scatter of its rows + chunked causal
+    attention) and must land on the same last-token output and the same page state."""
     pool, storage, ex = make_stack(executor)
-    tokens = [11, 22, 33, 44, 55]
+    ex.set_call_order(reference_order)
+    tokens = [11, 22, 33, 44, 55] + list(range(100, 170))      # 75 tokens: crosses a page boundary
     logits = ex.run_prefill(9, tokens)
-    assert logits.size == H * D and ex.known_position(9) == 5
+    assert logits.size == H * D and ex.known_position(9) == len(tokens)
     replay = OracleReplay(oracle_mod, 24, L - 1)
-    table = ex.page_state(9)[0]
+    table, total = ex.page_state(9)
+    assert total == len(tokens) and len(table) == 2
     for pos, tok in enumerate(tokens):
         want = replay.step([(9, tok, pos)], {9: (table, pos + 1)})
     assert_attention_close(logits.reshape(1, H, D), want)
+    # a second chunk on top of the first (cached prefix + new tokens), then a decode step
+    more = [7, 8, 9]
+    logits2 = ex.run_prefill(9, more)
+    table, total = ex.page_state(9)
+    for i, tok in enumerate(more):
+        want2 = replay.step([(9, tok, len(tokens) + i)], {9: (table, len(tokens) + i + 1)})
+    assert_attention_close(logits2.reshape(1, H, D), want2)
+    out = ex.run_decode([(9, 5, len(tokens) + len(more))])
+    table, total = ex.page_state(9)
+    want3 = replay.step([(9, 5, len(tokens) + len(more))], {9: (table, total)})
+    assert out[0][1] and total == len(tokens) + len(more) + 1
+    assert_attention_close(out[0][2].reshape(1, H, D), want3)
+    ex.destroy()
+    storage.destroy()
+
+
+def test_chunked_prefill_runs_on_tcgen05_for_head_dim_128(executor, oracle_mod):
+    shape = (8, 2, 128)
+    pool, storage, ex = make_stack(executor, shape=shape)
+    tokens = list(range(1, 201))                                # 200 tokens: two query tiles, four pages
+    logits = ex.run_prefill(4, tokens)
+    assert executor.lastAttentionKernel() == 3
+    replay = OracleReplay(oracle_mod, 24, L - 1, shape=shape)
+    table, total = ex.page_state(4)
+    assert total == 200 and len(table) == 4
+    for pos, tok in enumerate(tokens):
+        want = replay.step([(4, tok, pos)], {4: (table, pos + 1)})
+    assert_attention_close(logits.reshape(1, shape[0], shape[2]), want)
+    ex.destroy()
+    storage.destroy()
+
+
+def test_chunked_prefill_fails_cleanly_when_the_pool_runs_out(executor):
+    pool, storage, ex = make_stack(executor, capacity=1)
+    assert ex.run_prefill(3, list(range(70))).size == 0       # needs two pages, the pool has one
+    assert ex.known_position(3) == 0
+    ex.release_request(3)
+    assert pool.pages_in_use() == 0
     ex.destroy()
     storage.destroy()
 
