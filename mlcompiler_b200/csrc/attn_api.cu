@@ -109,7 +109,101 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     }
     const bool tma = decode_tma_shape_supported(k.H, k.KVH, k.D, k.P, k.capacity);
     std::vector<SegDesc> segs;
+    bool unit_mode = false;
+    uint32_t n_slices = 0;  // plan slices: one per CTA, or one per warp in unit mode
     if (tma) {
+        // ---- which decomposition? -----------------------------------------------------------
+        // split: requests cut over all CTAs along the sequence, 4 KV heads per CTA, split requests merged
+        //        by a second kernel chained behind (on the critical path, longer with more parts);
+        // unit : a (request, KV head) never leaves its CTA - longest-first packing of whole units onto
+        //        the CTAs, the CTA's warps share a unit and merge in shared memory, no merge kernel; the
+        //        longest unit bounds the launch, so it loses when one request dwarfs the rest.
+        // The estimate below is in microseconds and in "head tiles" (32 tokens of one head, K and V);
+        // its constants come from timing both forms on B200 over a dozen batch shapes (per layer, in a
+        // CUDA graph): ~0.18 us per head tile and SM when the HBM is shared by all SMs, ~0.135 us per
+        // head tile for the CTA that holds the longest unit, fixed costs of ~3 us (unit) and ~9 us plus
+        // ~0.9 us per 12 parts of the most split request (split).
+        const uint32_t TOKu = kTileTokens;
+        std::vector<std::pair<uint32_t, uint32_t>> units;  // (tiles, request * KVH + head)
+        uint64_t head_tiles = 0;
+        for (size_t r = 0; r < N; ++r) {
+            const uint32_t t = (eff[r] + TOKu - 1) / TOKu;
+            if (!t) continue;
+            for (uint32_t h = 0; h < k.KVH; ++h) units.emplace_back(t, static_cast<uint32_t>(r * k.KVH + h));
+            head_tiles += static_cast<uint64_t>(t) * k.KVH;
+        }
+        const int per_sm_u = std::max(env_int("MLC_B200_DECODE_CTAS_PER_SM", 1), 1);
+        const uint32_t cta_cap = static_cast<uint32_t>(ctx->sm_count) * per_sm_u;
+        const uint32_t n_cta_u = static_cast<uint32_t>(std::min<size_t>(cta_cap, units.size()));
+        std::vector<std::vector<uint32_t>> cta_units(n_cta_u);
+        uint64_t critical = 0;
+        if (n_cta_u && k.KVH <= kTileHbMask + 1) {
+            std::sort(units.begin(), units.end(), [](const auto& a, const auto& b) { return a.first != b.first ? a.first > b.first : a.second < b.second; });
+            // longest-first onto the least loaded CTA
+            std::vector<std::pair<uint64_t, uint32_t>> heap;  // (load, cta), min-heap
+            for (uint32_t c = 0; c < n_cta_u; ++c) heap.emplace_back(0, c);
+            auto cmp = [](const auto& a, const auto& b) { return a.first != b.first ? a.first > b.first : a.second > b.second; };
+            std::make_heap(heap.begin(), heap.end(), cmp);
+            for (const auto& u : units) {
+                std::pop_heap(heap.begin(), heap.end(), cmp);
+                auto& slot = heap.back();
+                cta_units[slot.second].push_back(u.second);
+                slot.first += u.first;
+                critical = std::max(critical, slot.first);
+                std::push_heap(heap.begin(), heap.end(), cmp);
+            }
+            const double f = static_cast<double>(k.D) / 64.0;
+            const double per_sm_tiles = static_cast<double>(head_tiles) / ctx->sm_count;
+            const double t_unit = f * std::max(0.135 * static_cast<double>(critical), 0.18 * per_sm_tiles) + 3.0;
+            const uint32_t n_hb_e = static_cast<uint32_t>((k.KVH + kDecodeWarps - 1) / kDecodeWarps);
+            const double hb_tiles = static_cast<double>(head_tiles) / k.KVH * n_hb_e;      // tiles of the split form
+            const double per_cta = std::max(1.0, hb_tiles / cta_cap);
+            const double max_parts = std::min<double>(cta_cap, units.front().first / per_cta + 1.0);
+            const double t_split = f * 0.185 * per_sm_tiles + 9.0 + 0.9 * std::ceil(max_parts / 12.0);
+            const int forced = env_int("MLC_B200_DECODE_MODE", 0);  // 0 auto, 1 split, 2 unit
+            unit_mode = forced == 2 || (forced == 0 && t_unit < t_split);
+        }
+        stages = static_cast<uint32_t>(std::min<int>(decode_tma_max_stages(k.H, k.KVH, k.D),
+                                                     std::max(1, env_int("MLC_B200_DECODE_STAGES", 3))));
+        if (unit_mode) {
+            // the exchange area of the in-CTA merge must fit beside the rings
+            while (stages > 1 && decode_tma_smem_bytes(k.D, k.H / k.KVH > 8, stages, true) > 227 * 1024 - 1024) --stages;  // 1 KiB for the barriers
+            n_cta = n_cta_u;
+            const uint32_t UW = static_cast<uint32_t>(unit_warps(k.D));
+            n_slices = n_cta * UW;
+            cta_pieces.resize(n_slices);
+            cta_tiles.resize(n_slices);
+            for (uint32_t c = 0; c < n_cta; ++c) {
+                for (uint32_t id : cta_units[c]) {
+                    const size_t r = id / k.KVH;
+                    const uint32_t h = static_cast<uint32_t>(id % k.KVH);
+                    const uint32_t T = (eff[r] + TOKu - 1) / TOKu, quarter = (T + UW - 1) / UW;
+                    for (uint32_t w = 0; w < UW; ++w) {
+                        const uint32_t lo = std::min(w * quarter, T), hi = std::min((w + 1) * quarter, T);
+                        PieceDesc d{};
+                        d.req = static_cast<uint32_t>(r);
+                        d.hb = static_cast<uint16_t>(h);   // the KV head itself
+                        d.tile_begin = lo;
+                        d.n_tiles = hi - lo;
+                        d.n_parts = 1;
+                        const bool has_last = hi == T && hi > lo;
+                        d.last_valid = static_cast<uint16_t>(has_last ? eff[r] - (T - 1) * TOKu : TOKu);
+                        d.flags = (fusable && has_last) ? 1u : 0u;
+                        const uint32_t slice = c * UW + w;
+                        cta_pieces[slice].push_back(d);
+                        for (uint32_t t = lo; t < hi; ++t) {
+                            const uint64_t tok0 = static_cast<uint64_t>(t) * TOKu;
+                            const uint32_t page = pt_flat[pt_off[r] + tok0 / k.P];
+                            const uint32_t sub = static_cast<uint32_t>((tok0 % k.P) / TOKu);
+                            const uint32_t fresh = (fusable && t + 1 == T) ? kTileFreshBit : 0u;
+                            cta_tiles[slice].push_back(page | (sub << kTileSubShift) | (h << kTileHbShift) | fresh);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (tma && !unit_mode) {
         const uint32_t TOK = kTileTokens;
         const uint32_t n_hb = static_cast<uint32_t>((k.KVH + kDecodeWarps - 1) / kDecodeWarps);
         uint64_t total = 0;
@@ -117,11 +211,10 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         // One CTA per SM and ~100 KiB of ring per CTA where possible: a decode-step kernel
         // and its programmatic successor can then share an SM.
         int per_sm = env_int("MLC_B200_DECODE_CTAS_PER_SM", 1);
-        stages = static_cast<uint32_t>(std::min<int>(decode_tma_max_stages(k.H, k.KVH, k.D),
-                                                     std::max(1, env_int("MLC_B200_DECODE_STAGES", 3))));
         uint64_t max_cta = static_cast<uint64_t>(ctx->sm_count) * std::max(per_sm, 1);
         int min_tiles = std::max(env_int("MLC_B200_DECODE_MIN_TILES", 1), 1);
         n_cta = static_cast<uint32_t>(std::max<uint64_t>(1, std::min<uint64_t>(max_cta, total / min_tiles)));
+        n_slices = n_cta;
         cta_pieces.resize(n_cta);
         cta_tiles.resize(n_cta);
         uint32_t c = 0;
@@ -172,18 +265,18 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                 }
             }
         }
-        for (uint32_t i = 0; i < n_cta; ++i) {
-            max_pieces = std::max<uint32_t>(max_pieces, static_cast<uint32_t>(cta_pieces[i].size()));
-            max_tiles = std::max<uint32_t>(max_tiles, static_cast<uint32_t>(cta_tiles[i].size()));
-        }
+    }
+    for (uint32_t i = 0; i < n_slices; ++i) {
+        max_pieces = std::max<uint32_t>(max_pieces, static_cast<uint32_t>(cta_pieces[i].size()));
+        max_tiles = std::max<uint32_t>(max_tiles, static_cast<uint32_t>(cta_tiles[i].size()));
     }
 
     // ---- lay the image out
     size_t off = 0;
-    const size_t off_counts = off;   off = align_up(off + size_t(n_cta) * 8, 16);
+    const size_t off_counts = off;   off = align_up(off + size_t(n_slices) * 8, 16);
     // +512 / +128 bytes: the kernel prologue reads 16 descriptors and 32 tile words per CTA unconditionally
-    const size_t off_pieces = off;   off = align_up(off + size_t(n_cta) * max_pieces * sizeof(PieceDesc) + 512, 16);
-    const size_t off_tiles = off;    off = align_up(off + size_t(n_cta) * max_tiles * 4 + 128, 16);
+    const size_t off_pieces = off;   off = align_up(off + size_t(n_slices) * max_pieces * sizeof(PieceDesc) + 512, 16);
+    const size_t off_tiles = off;    off = align_up(off + size_t(n_slices) * max_tiles * 4 + 128, 16);
     const size_t off_flat = off;     off = align_up(off + k.n_flat * 4, 16);
     const size_t off_ptoff = off;    off = align_up(off + (N + 1) * 4, 16);
     const size_t off_eff = off;      off = align_up(off + N * 4, 16);
@@ -212,7 +305,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     auto* counts_h = reinterpret_cast<uint32_t*>(p.host + off_counts);
     auto* pieces_h = reinterpret_cast<PieceDesc*>(p.host + off_pieces);
     auto* tiles_h = reinterpret_cast<uint32_t*>(p.host + off_tiles);
-    for (uint32_t i = 0; i < n_cta; ++i) {
+    for (uint32_t i = 0; i < n_slices; ++i) {
         counts_h[2 * i] = static_cast<uint32_t>(cta_pieces[i].size());
         counts_h[2 * i + 1] = static_cast<uint32_t>(cta_tiles[i].size());
         std::copy(cta_pieces[i].begin(), cta_pieces[i].end(), pieces_h + size_t(i) * max_pieces);
@@ -239,6 +332,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     v.seg_desc = reinterpret_cast<const SegDesc*>(p.dev + off_segs);
     v.has_tma = tma;
     v.step_fusable = tma && fusable;
+    v.unit_mode = unit_mode;
     v.stages = stages;
     v.n_cta = n_cta;
     v.max_pieces = max_pieces;

@@ -266,8 +266,16 @@ __device__ __forceinline__ void write_rows(const DecodeParams& prm, uint32_t req
 template <int D, bool G16, bool CG>
 __device__ __forceinline__ void merge_segment(const DecodeParams& prm, const SegDesc& sd, uint32_t warp, uint32_t lane);
 
-template <int D, bool G16>
-__global__ void __launch_bounds__(kDecodeWarps * 32)
+// UNIT = false: the four warps of a CTA are the four KV heads of a head block over the same tiles
+// (dense 512-byte rows), requests are cut over CTAs and split requests merged afterwards.
+// UNIT = true ("unit mode", the planner's choice unless one request dwarfs the others): no request
+// is split over CTAs. Every warp has its own piece and tile lists; the W warps of a CTA (8 for
+// head_dim 64, 4 for 128) take the W parts of one (request, head) at a time and merge through
+// shared memory, so there are no global partials and no merge kernel. More warps matter: a warp
+// needs ~0.8 us per 32-token tile (dependent mma.sync / ldmatrix / shuffle chains, one warp per
+// scheduler), so the longest unit's time falls with the number of warps that share it.
+template <int D, bool G16, bool UNIT>
+__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const DecodeParams prm) {
     constexpr int TOK = kTileTokens;
@@ -278,9 +286,10 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     constexpr uint32_t kTileBytes = TOK * D * 2;       // one of K or V
     constexpr uint32_t kStageBytes = 2 * kTileBytes;
     constexpr int ROWSETS = G16 ? 2 : 1;
+    constexpr int W = UNIT ? unit_warps(D) : kDecodeWarps;  // warps of this CTA
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[kDecodeWarps][8];
+    __shared__ __align__(8) uint64_t bars[8][8];
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = blockIdx.x;
@@ -292,9 +301,10 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     // cost one memory round trip together: the CTA's counts, its first 32 tile words
     // (one per lane) and its first 16 piece descriptors (half a descriptor per lane).
     // The planner pads both arrays so that these reads stay inside the plan image.
-    const uint32_t* my_tiles = prm.tile_pages + static_cast<size_t>(cta) * prm.max_tiles;
-    const PieceDesc* my_pieces = prm.pieces + static_cast<size_t>(cta) * prm.max_pieces;
-    const uint2 counts = __ldg(reinterpret_cast<const uint2*>(prm.cta_counts) + cta);
+    const uint32_t vcta = UNIT ? cta * W + warp : cta;  // unit mode: one plan slice per warp
+    const uint32_t* my_tiles = prm.tile_pages + static_cast<size_t>(vcta) * prm.max_tiles;
+    const PieceDesc* my_pieces = prm.pieces + static_cast<size_t>(vcta) * prm.max_pieces;
+    const uint2 counts = __ldg(reinterpret_cast<const uint2*>(prm.cta_counts) + vcta);
     uint32_t win_base = 0;
     uint32_t win = __ldg(my_tiles + lane);
     const uint4 desc_half = __ldg(reinterpret_cast<const uint4*>(my_pieces) + lane);
@@ -303,7 +313,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         if (prm.trace && lane == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            prm.trace[(static_cast<size_t>(cta) * kDecodeWarps + warp) * 8 + i] = t;
+            prm.trace[(static_cast<size_t>(cta) * W + warp) * 8 + i] = t;
         }
     };
     stamp(0);
@@ -326,7 +336,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     uint32_t iss = 0, con = 0;
     // Issues the TMA copies of the tile word `e` into the next ring stage.
     auto issue_word = [&](uint32_t e) {
-        const uint32_t head = ((e >> kTileHbShift) & kTileHbMask) * kDecodeWarps + warp;
+        const uint32_t hfield = (e >> kTileHbShift) & kTileHbMask;   // head block, or the head itself in unit mode
+        const uint32_t head = UNIT ? hfield : hfield * kDecodeWarps + warp;
         if (head >= prm.KVH) return;  // this warp has no KV head in that head block
         const uint32_t s = iss % stages;
         ++iss;
@@ -389,7 +400,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     uint32_t j = 0;  // CTA-local tile counter (consume side)
     bool dead = false;
 
-    for (uint32_t pi = 0; pi < n_pieces && !dead; ++pi) {
+    uint32_t pi = 0;
+    for (; pi < n_pieces && !dead; ++pi) {
         uint4 d0, d1;
         if (pi < 16u) {  // prefetched in the prologue: lane 2i holds the first half of piece i
             d0.x = __shfl_sync(0xffffffffu, desc_half.x, 2 * pi);
@@ -408,7 +420,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         const uint32_t n_parts = d1.z & 0xffffu, hb = d1.z >> 16;
         const uint32_t last_valid = d1.w & 0xffffu;
         const bool fresh_piece = prm.step && ((d1.w >> 16) & 1u);  // its last tile holds the new token
-        const uint32_t head = hb * kDecodeWarps + warp;
+        const uint32_t head = UNIT ? hb : hb * kDecodeWarps + warp;
         if (head >= prm.KVH) {  // keep the tile counter and the prefetch stream in step
             for (uint32_t t = 0; t < piece_tiles; ++t, ++j) {
                 if (next_issue < n_tiles) {
@@ -498,19 +510,33 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
 
             // ---- S = Q.K^T (fp32)
+            // The shared-memory loads of a group of score tiles are all issued before the first MMA that
+            // needs one (the asm statements keep their order, so load -> mma -> load -> mma would pay
+            // the ldmatrix latency once per pair: ~1200 clocks per tile, measured), and the MMAs run
+            // over independent accumulators in turn.
             float sc[NT_S][4];
+            constexpr int kScoreGroup = (D == 64) ? NT_S : NT_S / 2;  // 32 fragment registers per group
 #pragma unroll
-            for (int n = 0; n < NT_S; ++n) {
-                sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-                const uint32_t tok = n * 8 + (lane & 7);
+            for (int n0 = 0; n0 < NT_S; n0 += kScoreGroup) {
+                uint32_t kb[kScoreGroup][KSTEPS / 2][4];
+#pragma unroll
+                for (int ni = 0; ni < kScoreGroup; ++ni) {
+                    const uint32_t tok = (n0 + ni) * 8 + (lane & 7);
+#pragma unroll
+                    for (int kp = 0; kp < KSTEPS / 2; ++kp) {
+                        const uint32_t chunk = kp * 4 + (lane >> 3);  // 16-byte chunk of the row
+                        const uint32_t addr = sK + (chunk >> 3) * (TOK * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
+                        ldsm_x4(addr, kb[ni][kp]);
+                    }
+                }
+#pragma unroll
+                for (int ni = 0; ni < kScoreGroup; ++ni) sc[n0 + ni][0] = sc[n0 + ni][1] = sc[n0 + ni][2] = sc[n0 + ni][3] = 0.f;
 #pragma unroll
                 for (int kp = 0; kp < KSTEPS / 2; ++kp) {
-                    const uint32_t chunk = kp * 4 + (lane >> 3);  // 16-byte chunk of the row
-                    const uint32_t addr = sK + (chunk >> 3) * (TOK * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
-                    uint32_t b[4];
-                    ldsm_x4(addr, b);
-                    mma_16816(sc[n], qa[2 * kp], b[0], b[1]);
-                    mma_16816(sc[n], qa[2 * kp + 1], b[2], b[3]);
+#pragma unroll
+                    for (int ni = 0; ni < kScoreGroup; ++ni) mma_16816(sc[n0 + ni], qa[2 * kp], kb[ni][kp][0], kb[ni][kp][1]);
+#pragma unroll
+                    for (int ni = 0; ni < kScoreGroup; ++ni) mma_16816(sc[n0 + ni], qa[2 * kp + 1], kb[ni][kp][2], kb[ni][kp][3]);
                 }
             }
             // V rows past the request's last token may hold anything; make them 0 so
@@ -565,17 +591,25 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
 
             // ---- O += P.V
+            // same batching: the V fragments of 64 output columns first, then their MMAs
+            constexpr int kOutGroup = 4;  // ldmatrix per batch = 16 fragment registers
 #pragma unroll
             for (int kt = 0; kt < TOK / 16; ++kt) {
                 const uint32_t tok = kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
-                for (int np = 0; np < NT_O / 2; ++np) {
-                    const uint32_t chunk = np * 2 + (lane >> 4);
-                    const uint32_t addr = sV + (chunk >> 3) * (TOK * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
-                    uint32_t b[4];
-                    ldsm_x4_trans(addr, b);
-                    mma_16816(o_acc[2 * np], pa[kt], b[0], b[1]);
-                    mma_16816(o_acc[2 * np + 1], pa[kt], b[2], b[3]);
+                for (int np0 = 0; np0 < NT_O / 2; np0 += kOutGroup) {
+                    uint32_t vb[kOutGroup][4];
+#pragma unroll
+                    for (int i = 0; i < kOutGroup; ++i) {
+                        const uint32_t chunk = (np0 + i) * 2 + (lane >> 4);
+                        const uint32_t addr = sV + (chunk >> 3) * (TOK * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
+                        ldsm_x4_trans(addr, vb[i]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < kOutGroup; ++i) {
+                        mma_16816(o_acc[2 * (np0 + i)], pa[kt], vb[i][0], vb[i][1]);
+                        mma_16816(o_acc[2 * (np0 + i) + 1], pa[kt], vb[i][2], vb[i][3]);
+                    }
                 }
             }
             __syncwarp();
@@ -594,7 +628,83 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             l_run[rs] += __shfl_xor_sync(0xffffffffu, l_run[rs], 2);
         }
 
-        if (n_parts > 1) {
+        if (UNIT) {
+            // The W warps hold the W parts of this (request, head): exchange the un-normalised
+            // partials through shared memory, then every warp merges and writes its share of the
+            // output columns.
+            constexpr int FR = G16 ? 4 : 2;
+            constexpr uint32_t kXWarpFloats = (NT_O + 1) * 32 * FR;
+            float* xb = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) +
+                        (static_cast<size_t>(W) * stages * kStageBytes) / 4;
+            float* mine = xb + warp * kXWarpFloats;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+                for (int f = 0; f < FR; ++f) mine[(n * 32 + lane) * FR + f] = o_acc[n][f];
+#pragma unroll
+            for (int rs = 0; rs < ROWSETS; ++rs) {
+                mine[(NT_O * 32 + lane) * FR + 2 * rs] = m_run[rs];
+                mine[(NT_O * 32 + lane) * FR + 2 * rs + 1] = l_run[rs];
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            float wk[W][2], lstar[2], mstar[2];
+#pragma unroll
+            for (int rs = 0; rs < ROWSETS; ++rs) {
+                float mk[W];
+                mstar[rs] = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    mk[k] = xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs];
+                    mstar[rs] = fmaxf(mstar[rs], mk[k]);
+                }
+                lstar[rs] = 0.f;
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    wk[k][rs] = (mk[k] == -INFINITY) ? 0.f : ex2(mk[k] - mstar[rs]);  // an empty quarter weighs nothing
+                    lstar[rs] += xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs + 1] * wk[k][rs];
+                }
+            }
+#pragma unroll
+            for (int nn = 0; nn < NT_O / W; ++nn) {
+                const int n = nn * W + static_cast<int>(warp);  // this warp's output n-tiles
+                float acc[FR];
+#pragma unroll
+                for (int f = 0; f < FR; ++f) acc[f] = 0.f;
+#pragma unroll
+                for (int k = 0; k < W; ++k)
+#pragma unroll
+                    for (int f = 0; f < FR; ++f) acc[f] += xb[k * kXWarpFloats + (n * 32 + lane) * FR + f] * wk[k][f >> 1];
+#pragma unroll
+                for (int rs = 0; rs < ROWSETS; ++rs) {
+                    const uint32_t row = qrow + 8 * rs;
+                    if (row >= prm.G) continue;
+                    const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
+                    if (prm.o_partial) {
+                        *reinterpret_cast<float2*>(prm.o_partial + hrow * D + n * 8 + qcol) = make_float2(acc[2 * rs], acc[2 * rs + 1]);
+                    } else {
+                        const float inv = lstar[rs] > 0.f ? 1.0f / lstar[rs] : 0.f;
+                        if (prm.o_f32)
+                            *reinterpret_cast<float2*>(static_cast<float*>(prm.o) + hrow * D + n * 8 + qcol) =
+                                make_float2(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
+                        else
+                            *reinterpret_cast<__half2*>(static_cast<__half*>(prm.o) + hrow * D + n * 8 + qcol) =
+                                __floats2half2_rn(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
+                    }
+                }
+            }
+            if (prm.o_partial && warp == 0 && (lane & 3) == 0) {
+#pragma unroll
+                for (int rs = 0; rs < ROWSETS; ++rs) {
+                    const uint32_t row = qrow + 8 * rs;
+                    if (row >= prm.G) continue;
+                    const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
+                    prm.ml_partial[hrow * 2] = mstar[rs] * 0.6931471805599453f;   // natural-log units for the caller
+                    prm.ml_partial[hrow * 2 + 1] = lstar[rs];
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");  // the exchange area is free for the next (request, head)
+            if (pi == 0) stamp(4);
+        } else if (n_parts > 1) {
             // un-normalised partial -> workspace, fragment order (coalesced). The merge kernel
             // that follows in the stream reads it; the kernel boundary orders the two.
             const size_t unit = static_cast<size_t>(part_slot) * kDecodeWarps + warp;
@@ -626,6 +736,14 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             write_rows<D, G16>(prm, req, head, lane, o_acc, m_run, l_run);
         }
         if (pi + 1 == n_pieces) stamp(7);
+    }
+
+    if (UNIT && dead) {
+        // this warp gave up on a copy: it still meets its CTA's two barriers per remaining piece
+        for (; pi < n_pieces; ++pi) {
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+        }
     }
 
     // ---- in-kernel merge of the split segments: segment s belongs to CTA s mod gridDim ----
@@ -782,13 +900,22 @@ uint32_t decode_tma_max_stages(size_t H, size_t KVH, size_t D) {
     return static_cast<uint32_t>(std::min<size_t>(8, avail / stage));
 }
 
-template <int D, bool G16>
+// Shared memory of one CTA: the TMA rings, alignment slack and, in unit mode, the exchange
+// area of the in-CTA merge (per warp (D/8 + 1) x 32 lanes x 2 or 4 floats).
+size_t decode_tma_smem_bytes(size_t D, bool g16, uint32_t stages, bool unit) {
+    const size_t warps = unit ? unit_warps(D) : kDecodeWarps;
+    size_t smem = warps * stages * (2 * kTileTokens * D * 2) + 1024;
+    if (unit) smem += warps * (D / 8 + 1) * 32 * (g16 ? 4 : 2) * 4;
+    return smem;
+}
+
+template <int D, bool G16, bool UNIT>
 static int launch_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams& prm, const CUtensorMap& mk,
                     const CUtensorMap& mv) {
-    const size_t smem = static_cast<size_t>(kDecodeWarps) * plan.stages * (2 * kTileTokens * D * 2) + 1024;
-    size_t& configured = ctx->decode_smem_set[(D == 128 ? 2 : 0) + (G16 ? 1 : 0)];
+    const size_t smem = decode_tma_smem_bytes(D, G16, plan.stages, UNIT);
+    size_t& configured = ctx->decode_smem_set[(UNIT ? 4 : 0) + (D == 128 ? 2 : 0) + (G16 ? 1 : 0)];
     if (smem > configured) {
-        MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_decode_tma_kernel<D, G16>,
+        MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_decode_tma_kernel<D, G16, UNIT>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured = smem;
     }
@@ -797,12 +924,12 @@ static int launch_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(plan.n_cta);
-    cfg.blockDim = dim3(kDecodeWarps * 32);
+    cfg.blockDim = dim3((UNIT ? unit_warps(D) : kDecodeWarps) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cfg.attrs = attr;
     cfg.numAttrs = prm.pdl ? 1 : 0;
-    MLCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<D, G16>, mk, mv, prm));
+    MLCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<D, G16, UNIT>, mk, mv, prm));
     ++ctx->launches;
     if (plan.n_segs && !prm.seg_counters) {
         // the merge is always chained programmatically: before its wait it touches nothing
@@ -901,12 +1028,16 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     prm.seg_counters = use_counters ? ctx->d_counters : nullptr;
     prm.n_segs = plan.n_segs;
     // traces of consecutive launches alternate between the two halves of the buffer
-    const size_t trace_need = static_cast<size_t>(plan.n_cta) * kDecodeWarps * 8;
+    const size_t trace_need = static_cast<size_t>(plan.n_cta) * (plan.unit_mode ? unit_warps(a.D) : kDecodeWarps) * 8;
     prm.trace = ctx->d_trace && trace_need <= ctx->trace_words / 2 ? ctx->d_trace + parity * (ctx->trace_words / 2) : nullptr;
     ctx->trace_ctas = prm.trace ? plan.n_cta : 0;
     ctx->trace_parity = parity;
-    if (a.D == 64) return g16 ? launch_t<64, true>(ctx, plan, prm, mk, mv) : launch_t<64, false>(ctx, plan, prm, mk, mv);
-    return g16 ? launch_t<128, true>(ctx, plan, prm, mk, mv) : launch_t<128, false>(ctx, plan, prm, mk, mv);
+    if (plan.unit_mode) {
+        if (a.D == 64) return g16 ? launch_t<64, true, true>(ctx, plan, prm, mk, mv) : launch_t<64, false, true>(ctx, plan, prm, mk, mv);
+        return g16 ? launch_t<128, true, true>(ctx, plan, prm, mk, mv) : launch_t<128, false, true>(ctx, plan, prm, mk, mv);
+    }
+    if (a.D == 64) return g16 ? launch_t<64, true, false>(ctx, plan, prm, mk, mv) : launch_t<64, false, false>(ctx, plan, prm, mk, mv);
+    return g16 ? launch_t<128, true, false>(ctx, plan, prm, mk, mv) : launch_t<128, false, false>(ctx, plan, prm, mk, mv);
 }
 
 }  // namespace mlcb

@@ -39,6 +39,9 @@ struct AttnArgs {
 // merged by a second, tiny kernel.
 static constexpr int kDecodeWarps = 4;   // KV heads per head block = warps per CTA
 static constexpr int kTileTokens = 32;   // tokens per pipeline stage
+// Warps of a CTA in unit mode: with one KV head per CTA a warp's tile costs ~0.8 us of dependent
+// work, so the longest (request, head) is cut into more parts where shared memory allows.
+constexpr int unit_warps(size_t head_dim) { return head_dim == 64 ? 8 : 4; }
 // Tile word: page id | sub-tile within the page | head block | "holds this step's new token".
 static constexpr uint32_t kTilePageMask = (1u << 22) - 1;
 static constexpr uint32_t kTileSubShift = 22;
@@ -75,6 +78,7 @@ struct DecodePlanView {            // device addresses inside one plan blob
     const SegDesc* seg_desc;       // [n_segs] split segments
     bool has_tma = false;          // the per-CTA tile lists above were built
     bool step_fusable = false;     // every request's newest token is the last one it attends to
+    bool unit_mode = false;        // per-warp plan slices, no request split over CTAs (see the kernel)
     uint32_t stages = 3;           // ring depth the plan was cut for
     uint32_t n_cta = 0, max_pieces = 0, max_tiles = 0, n_zero = 0;
     uint32_t n_slots = 0, n_segs = 0;
@@ -88,6 +92,7 @@ bool decode_tma_shape_supported(size_t H, size_t KVH, size_t D, size_t P, size_t
 bool decode_tma_pointers_supported(const AttnArgs& a);
 // Deepest TMA ring that fits in shared memory next to the kernel's merge buffers.
 uint32_t decode_tma_max_stages(size_t H, size_t KVH, size_t D);
+size_t decode_tma_smem_bytes(size_t D, bool g16, uint32_t stages, bool unit);
 // One launch writing this step's K and V rows; page ids and slots already on the device.
 int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, const uint32_t* d_ids,
                                       const uint32_t* d_slots, size_t P, size_t KVH, size_t D,

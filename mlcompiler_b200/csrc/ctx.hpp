@@ -52,7 +52,7 @@ struct mlc_ctx {
     size_t work_bytes = 0;
     uint32_t* d_counters = nullptr;
     size_t n_counters = 0;
-    size_t decode_smem_set[4] = {0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
+    size_t decode_smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
     bool prefill_smem_set = false;             // same, for the chunked-prefill kernel
     // optional per-warp phase stamps of the last decode launch (env MLC_B200_TRACE=1)
     unsigned long long* d_trace = nullptr;

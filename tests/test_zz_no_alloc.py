@@ -59,8 +59,19 @@ def test_static_scratch_rejects_oversized_batches(executor):
     pool = torch.zeros((case.capacity, case.P, case.KVH, case.D), dtype=torch.float16, device=dev)
     q = torch.zeros((case.N, case.H, case.D), dtype=torch.float16, device=dev)
     o = torch.zeros_like(q)
-    plan = executor.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, case.N, case.H, case.KVH,
-                               case.D, case.P, True, case.capacity)
+    # the split decomposition is the one that needs scratch (the planner's other form keeps every
+    # request inside one CTA and needs none): ask for it while this plan is built
+    import os
+    prev = os.environ.get("MLC_B200_DECODE_MODE")
+    os.environ["MLC_B200_DECODE_MODE"] = "1"
+    try:
+        plan = executor.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, case.N, case.H, case.KVH,
+                                   case.D, case.P, True, case.capacity)
+    finally:
+        if prev is None:
+            del os.environ["MLC_B200_DECODE_MODE"]
+        else:
+            os.environ["MLC_B200_DECODE_MODE"] = prev
     assert executor.beginForwardPassCB()
     before = executor.launchCount()
     ok = executor.encodePagedFlashAttentionPlannedStatic(plan, q, pool, pool, o, case.scale, MLC_F16, MLC_F16)
