@@ -46,10 +46,10 @@ UNIT = "GB/s"
 WORKLOAD = ("cfg2: 22-layer continuous-batching decode, 32 requests, H32/KVH4/D64, fp16 KV, 64-token pages, "
             "contexts U[64,2048], random page tables, pool = pages + 10%; per layer: scatter 1 new K/V row "
             "per request, then attention")
-# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch of this workload
-# (37.71 MB read + 3.6 KB written), from the ncu capture summarised in
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel on this workload
+# (37.79 MB read + 1.5 KB written), from the ncu capture summarised in
 # profiles/decode_attention_cfg2.md; the algorithmic KV bytes of that launch are 37.00 MB.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 37_715_712
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 37_794_560
 
 
 def measured_peak_gbs():
@@ -365,7 +365,17 @@ def run_gpu_arm(args):
     sec_per_step = reduce_max(t_step) / args.steps
     value = bytes_step_all / sec_per_step / 1e9
     tokens_per_s = N * world / sec_per_step
-    attn_launch_s = t_attn / (args.steps * LAYERS)
+    # Duration of the dominant kernel. When the timed region is one kernel per layer (the planner kept every
+    # request inside a CTA, so the KV row write, attention and merge are a single launch), the region's
+    # CUDA-event time divided by its launches IS that kernel's average duration. Otherwise (attention + merge
+    # kernel per layer) the attention-only graph, timed the same way right after, gives the pair's duration.
+    kernels_per_step = gpu_launches / max(args.steps, 1)
+    if abs(kernels_per_step - LAYERS) < 0.5:
+        attn_launch_s = t_step / (args.steps * LAYERS)
+        launch_timing = "timed region / launches (one fused kernel per layer)"
+    else:
+        attn_launch_s = t_attn / (args.steps * LAYERS)
+        launch_timing = "attention-only graph (attention + merge kernel per layer)"
     achieved = kv_bytes_layer(lens) / attn_launch_s / 1e9
     peak, peak_kind = measured_peak_gbs()
 
@@ -428,8 +438,10 @@ def run_gpu_arm(args):
             "pct_of_nominal_8TBs": 100.0 * value / world / 8000.0,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_kind,
-                         "kernel": "paged_decode_tma_kernel<64,false>", "bytes_per_launch": kv_bytes_layer(lens),
-                         "us_per_launch": attn_launch_s * 1e6},
+                         "kernel": "paged_decode_tma_kernel<64,false,unit>" if abs(kernels_per_step - LAYERS) < 0.5
+                         else "paged_decode_tma_kernel<64,false,split> + paged_decode_merge_kernel", "bytes_per_launch": kv_bytes_layer(lens),
+                         "us_per_launch": attn_launch_s * 1e6, "launch_timing": launch_timing,
+                         "attention_only_us_per_layer": t_attn / (args.steps * LAYERS) * 1e6},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": t_e2e_max / args.steps * 1e3},
             "gpu_launches": int(gpu_launches),
