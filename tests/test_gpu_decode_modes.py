@@ -1,0 +1,53 @@
+"""The decode kernel has two decompositions (split over CTAs + merge kernel, and whole (request, head)
+units per CTA) and the planner picks one per batch. These tests run the attention and planned-call
+parity suites again with each form forced (MLC_B200_DECODE_MODE=1 / 2), so that neither depends on what
+the planner happens to choose for a test's batch shape."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("mode,name", [("1", "split"), ("2", "unit")])
+def test_parity_suites_with_the_decomposition_forced(mode, name):
+    env = dict(os.environ, MLC_B200_DECODE_MODE=mode)
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+                        "tests/test_gpu_attention.py", "tests/test_gpu_planned.py", "tests/test_gpu_walker.py",
+                        "-k", "not in_kernel_merge"],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, f"{name} mode:\n" + r.stdout[-3000:] + r.stderr[-1000:]
+
+
+def test_planner_choice_follows_the_batch_shape():
+    """Balanced batches run as whole units (one launch per layer); a batch dominated by one long request
+    is split over CTAs (attention + merge kernel)."""
+    import numpy as np
+    import torch
+    from mlcompiler_b200 import Executor, synth
+    from mlcompiler_b200.capi import MLC_F16
+    ex = Executor(0)
+    dev = torch.device("cuda:0")
+
+    def launches(lens):
+        case = synth.make_case(5, lens, fill=False, **synth.SHAPE_A)
+        pool = torch.zeros((case.capacity, case.P, case.KVH, case.D), dtype=torch.float16, device=dev)
+        q = torch.zeros((case.N, case.H, case.D), dtype=torch.float16, device=dev)
+        o = torch.zeros_like(q)
+        plan = ex.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, case.N, case.H, case.KVH, case.D,
+                             case.P, True, case.capacity)
+        assert ex.beginForwardPassCB()
+        before = ex.launchCount()
+        assert ex.encodePagedFlashAttentionPlanned(plan, q, pool, pool, o, case.scale, MLC_F16, MLC_F16), ex.last_error()
+        n = ex.launchCount() - before
+        assert ex.flushForwardPassCB(), ex.last_error()
+        plan.destroy()
+        return n
+
+    assert launches(np.random.default_rng(1).integers(64, 2049, 32)) == 1
+    assert launches(np.array([16384] + [256] * 31)) == 2
+    ex.close()
