@@ -49,11 +49,7 @@ struct Bars {
     uint64_t q, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], p_full[2], pv_done;
     uint32_t tmem_slot;
 };
-#ifdef MLCB_PREFILL_ONE_CTA  // experiment: pad the request so that only one CTA fits an SM
-constexpr uint32_t kSmemBytes = kTileBytes + sizeof(Bars) + 32768;
-#else
 constexpr uint32_t kSmemBytes = kTileBytes + sizeof(Bars);
-#endif
 constexpr uint32_t kTmemCols = 256;              // O: 128 columns, S: 2 x 64 columns
 constexpr uint32_t kTmemO = 0, kTmemS = 128;
 
@@ -192,28 +188,7 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t M, uint32_t N, uint32_
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-#ifdef MLCB_PREFILL_TRACE
-// Build-time profiling aid: SM-clock stamps of one CTA's softmax warp 0 and MMA lane, per tile.
-__device__ unsigned long long g_prefill_trace[64 * 16];
-__device__ unsigned int g_prefill_fail[16];  // [0] = 1 + linear id of the first CTA that timed out, [1 + warp] = where | tile << 8
-#define PF_STAMP(tile, slot)                                                                    \
-    do {                                                                                        \
-        if (trace_cta && (tile) < 64) g_prefill_trace[(tile) * 16 + (slot)] = clock64();        \
-    } while (0)
-#else
-#define PF_STAMP(tile, slot) do { } while (0)
-#endif
-
 }  // namespace
-
-#ifdef MLCB_PREFILL_TRACE
-extern "C" int mlc_debug_read_prefill_trace(unsigned long long* out) {
-    return cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(g_prefill_trace)) == cudaSuccess ? 0 : 1;
-}
-extern "C" int mlc_debug_read_prefill_fail(unsigned int* out) {
-    return cudaMemcpyFromSymbol(out, g_prefill_fail, sizeof(g_prefill_fail)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 __global__ void __launch_bounds__(224, 2)
 paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -278,19 +253,9 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
 
-#ifdef MLCB_PREFILL_TRACE
-    const bool trace_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4);
-#endif
     // A wait that ran out records the timeout bit plus where it gave up: bits 8-15 = which wait
     // (0x1x MMA warp, 0x2x softmax, 0x3x producers), bits 16-31 = the page it was working on.
     auto give_up = [&](uint32_t where, uint32_t tile) {
-#ifdef MLCB_PREFILL_TRACE
-        if (lane == 0) {
-            const unsigned int me = 1u + blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-            const unsigned int prev = atomicCAS(&g_prefill_fail[0], 0u, me);
-            if (prev == 0u || prev == me) g_prefill_fail[1 + warp] = where | (tile << 8) | 0x80000000u;
-        }
-#endif
         // the first failure's detail wins; later ones only (re)set the timeout bit
         if (lane == 0 && atomicCAS(prm.err, 0u, MLC_DEVERR_WAIT_TIMEOUT | (where << 8) | (tile << 16)) != 0u)
             atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
@@ -385,7 +350,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                     }
                     if (!ok) break;
                     tc_fence_after();
-                    PF_STAMP(j, 8);
                     issue_qk(j + 1);
                 }
                 const uint32_t s = j % kStages;
@@ -397,7 +361,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                 }
                 if (!ok) break;
                 tc_fence_after();
-                PF_STAMP(j, 9);
                 const uint32_t sV = sQ_u + kQBytes + s * 2 * kKvBytes + kKvBytes;
                 const uint32_t pj = tmem_u + kTmemS + (j & 1u) * kKvTile;
                 if (elect_one()) {
@@ -411,7 +374,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                     tc_commit(smem_u32(&bar_pv_done));
                 }
                 __syncwarp();
-                PF_STAMP(j, 10);
             }
             if (!ok) give_up(where, at);
         }
@@ -431,7 +393,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             ok = ok && mbar_wait_bounded(smem_u32(&bar_s_full[j & 1u]), (j >> 1) & 1u);
             if (!ok) break;
             tc_fence_after();
-            PF_STAMP(j, 0);
             uint32_t sreg[64];
             {
                 uint32_t lo[32], hi[32];
@@ -441,7 +402,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
 #pragma unroll
                 for (int i = 0; i < 32; ++i) { sreg[i] = lo[i]; sreg[32 + i] = hi[i]; }
             }
-            PF_STAMP(j, 1);
             // mask: causal (kv_pos > q_pos) and past the end of the sequence
             const uint32_t kv0 = j * kKvTile;
             // Scores stay unscaled (scale > 0 keeps their order); the scale is folded into the
@@ -468,7 +428,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             const bool need = (m_new > m_ref + rescale_step) || (m_ref == -INFINITY && m_new > -INFINITY);
             const float alpha = need ? ((m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * prm.scale_log2)) : 1.0f;
             if (need) m_ref = m_new;
-            PF_STAMP(j, 2);
             l_sum *= alpha;
             // P = exp2((s - m_ref) * scale), fp16, computed while the previous P.V may still run, then
             // stored into the swizzled A-operand tile: row `row`, 8 chunks of 16 bytes
@@ -489,8 +448,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                 pk[ch * 4 + 0] = w[0]; pk[ch * 4 + 1] = w[1]; pk[ch * 4 + 2] = w[2]; pk[ch * 4 + 3] = w[3];
             }
             l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-            PF_STAMP(j, 3);
-            PF_STAMP(j, 4);
             if (j > 0 && __any_sync(0xffffffffu, need)) {
                 // O may only be touched once the previous P.V is done (warp-uniform branch)
                 where = 0x21;
@@ -527,7 +484,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             }
             tc_fence_before();
             mbar_arrive(smem_u32(&bar_p_full[j & 1u]));
-            PF_STAMP(j, 5);
         }
         if (ok && n_tiles > 0) {
             where = 0x23;
