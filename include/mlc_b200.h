@@ -289,6 +289,17 @@ int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan
 int mlc_encode_lse_combine(mlc_ctx* ctx, const float* o_parts, const float* ml_parts, size_t parts,
                            size_t rows, size_t head_dim, void* out, int o_dtype);
 
+/* All layers of one decode pass in one call - the layer loop of the reference's walker
+ * (batched_walker.cpp:299-331) on this side of the boundary: for l in [0, n_layers)
+ * mlc_encode_paged_decode_step_planned(plan, q[l], k_new[l], v_new[l], k_pages[l], v_pages[l], o[l]).
+ * The arrays are host arrays of device pointers, read during the call. Stops at the first
+ * layer that fails and returns its status. */
+int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, size_t n_layers,
+                                         const void* const* q, const void* const* k_new,
+                                         const void* const* v_new, void* const* k_pages,
+                                         void* const* v_pages, void* const* o, float scale, int q_dtype,
+                                         int o_dtype);
+
 /* ---- QKV split + rotary embedding + cast, the step that feeds the scatter -------------
  * encodeQkvSplitRopeCast (metal_runtime.hpp:540-547; metal_runtime.mm:7915-8025: 3 x
  * strided_copy_f32 + 2 x batched_rope + 2 x cast_f32_to_f16 in one encoder) as ONE launch.

@@ -87,6 +87,8 @@ _PROTOTYPES = {
     "mlc_static_scratch_bytes": (_sz, []),
     "mlc_encode_paged_flash_attention_planned_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_paged_decode_step_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
+    "mlc_encode_paged_decode_pass_planned": (_i, [_vp, _vp, _sz, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                                  C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _f, _i, _i]),
     "mlc_encode_paged_attention_partial_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i]),
     "mlc_encode_lse_combine": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _i]),
     "mlc_graph_begin_capture": (_i, [_vp]),
@@ -389,6 +391,20 @@ class Executor:
 
     def staticScratchBytes(self) -> int:
         return int(self._lib.mlc_static_scratch_bytes())
+
+    @staticmethod
+    def pointerArray(buffers):
+        """A C array of device pointers (void* const*) for the per-layer entry points; keep it alive
+        as long as it is used and rebuild it only when a buffer moves."""
+        arr = (_vp * len(buffers))(*[_vp(_ptr(b)) for b in buffers])
+        return arr
+
+    def encodePagedDecodePassPlanned(self, plan, q, k_new, v_new, k_pages, v_pages, o, scale=0.0,
+                                     q_dtype=MLC_F32, o_dtype=MLC_F32) -> bool:
+        """All layers of a decode pass in one call: q / k_new / v_new / k_pages / v_pages / o are
+        pointer arrays (pointerArray) with one entry per layer."""
+        return self.status(self._lib.mlc_encode_paged_decode_pass_planned(
+            self._h, plan.handle, len(q), q, k_new, v_new, k_pages, v_pages, o, float(scale), q_dtype, o_dtype))
 
     def encodeQkvSplitRopeCast(self, qkv_buf, q_buf, k_buf, v_buf, k_f16_buf, v_f16_buf, cos_buf, sin_buf, batch,
                                num_heads, kv_heads, head_dim, qkv_rows, q_rows, k_rows, v_rows, rotary_dim) -> bool:

@@ -80,6 +80,37 @@ int env_int(const char* name, int dflt) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Builds the plan image for one set of tables into `p` and uploads it.
+// Lists of varying length for consecutive slices in two flat arrays (a vector per slice costs an
+// allocation or several each, ~100 us for the 1024 slices of a unit-mode plan). Lists are appended
+// to in non-decreasing slice order.
+template <typename T>
+struct FlatLists {
+    std::vector<uint32_t> off;  // off[i] = start of list i; off[n] = total once finished
+    std::vector<T> items;
+    uint32_t cur = 0, n = 0;
+    void reset(uint32_t count, size_t expect) {
+        n = count;
+        off.assign(static_cast<size_t>(count) + 1, 0);
+        items.clear();
+        items.reserve(expect);
+        cur = 0;
+    }
+    void push(uint32_t list, const T& v) {
+        while (cur < list) off[++cur] = static_cast<uint32_t>(items.size());
+        items.push_back(v);
+    }
+    uint32_t size_so_far(uint32_t list) {  // list >= cur
+        while (cur < list) off[++cur] = static_cast<uint32_t>(items.size());
+        return static_cast<uint32_t>(items.size()) - off[list];
+    }
+    void finish() {
+        while (cur < n) off[++cur] = static_cast<uint32_t>(items.size());
+    }
+    uint32_t size(uint32_t list) const { return off[list + 1] - off[list]; }
+    T& at(uint32_t list, uint32_t i) { return items[off[list] + i]; }
+    const T* data(uint32_t list) const { return items.data() + off[list]; }
+};
+
 int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const uint32_t* pt_off,
                const uint32_t* seq_lens, const uint32_t* q_pos, const uint32_t* page_ids,
                const uint32_t* slots) {
@@ -96,8 +127,8 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         if (S == 0) zero_rows.push_back(static_cast<uint32_t>(r));
     }
 
-    std::vector<std::vector<PieceDesc>> cta_pieces;
-    std::vector<std::vector<uint32_t>> cta_tiles;
+    FlatLists<PieceDesc> cta_pieces;   // per plan slice, filled slice after slice
+    FlatLists<uint32_t> cta_tiles;
     uint32_t n_cta = 0, max_pieces = 1, max_tiles = 1, n_slots = 0, n_segs = 0, stages = 3;
     // A decode step can fuse the row write into attention when the newest token of every
     // request (position seq_len - 1, where page_ids / slots must point) is attended to.
@@ -171,14 +202,15 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
             n_cta = n_cta_u;
             const uint32_t UW = static_cast<uint32_t>(unit_warps(k.D));
             n_slices = n_cta * UW;
-            cta_pieces.resize(n_slices);
-            cta_tiles.resize(n_slices);
+            cta_pieces.reset(n_slices, units.size() * UW);
+            cta_tiles.reset(n_slices, static_cast<size_t>(head_tiles) + n_slices);
             for (uint32_t c = 0; c < n_cta; ++c) {
-                for (uint32_t id : cta_units[c]) {
-                    const size_t r = id / k.KVH;
-                    const uint32_t h = static_cast<uint32_t>(id % k.KVH);
-                    const uint32_t T = (eff[r] + TOKu - 1) / TOKu, quarter = (T + UW - 1) / UW;
-                    for (uint32_t w = 0; w < UW; ++w) {
+                for (uint32_t w = 0; w < UW; ++w) {
+                    const uint32_t slice = c * UW + w;
+                    for (uint32_t id : cta_units[c]) {
+                        const size_t r = id / k.KVH;
+                        const uint32_t h = static_cast<uint32_t>(id % k.KVH);
+                        const uint32_t T = (eff[r] + TOKu - 1) / TOKu, quarter = (T + UW - 1) / UW;
                         const uint32_t lo = std::min(w * quarter, T), hi = std::min((w + 1) * quarter, T);
                         PieceDesc d{};
                         d.req = static_cast<uint32_t>(r);
@@ -189,18 +221,19 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                         const bool has_last = hi == T && hi > lo;
                         d.last_valid = static_cast<uint16_t>(has_last ? eff[r] - (T - 1) * TOKu : TOKu);
                         d.flags = (fusable && has_last) ? 1u : 0u;
-                        const uint32_t slice = c * UW + w;
-                        cta_pieces[slice].push_back(d);
+                        cta_pieces.push(slice, d);
                         for (uint32_t t = lo; t < hi; ++t) {
                             const uint64_t tok0 = static_cast<uint64_t>(t) * TOKu;
                             const uint32_t page = pt_flat[pt_off[r] + tok0 / k.P];
                             const uint32_t sub = static_cast<uint32_t>((tok0 % k.P) / TOKu);
                             const uint32_t fresh = (fusable && t + 1 == T) ? kTileFreshBit : 0u;
-                            cta_tiles[slice].push_back(page | (sub << kTileSubShift) | (h << kTileHbShift) | fresh);
+                            cta_tiles.push(slice, page | (sub << kTileSubShift) | (h << kTileHbShift) | fresh);
                         }
                     }
                 }
             }
+            cta_pieces.finish();
+            cta_tiles.finish();
         }
     }
     if (tma && !unit_mode) {
@@ -215,8 +248,8 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         int min_tiles = std::max(env_int("MLC_B200_DECODE_MIN_TILES", 1), 1);
         n_cta = static_cast<uint32_t>(std::max<uint64_t>(1, std::min<uint64_t>(max_cta, total / min_tiles)));
         n_slices = n_cta;
-        cta_pieces.resize(n_cta);
-        cta_tiles.resize(n_cta);
+        cta_pieces.reset(n_cta, N * n_hb + n_cta);
+        cta_tiles.reset(n_cta, total);
         uint32_t c = 0;
         uint64_t g = 0;  // global tile index
         auto cta_end = [&](uint32_t cc) { return (static_cast<uint64_t>(cc) + 1) * total / n_cta; };
@@ -237,14 +270,14 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                     d.last_valid = static_cast<uint16_t>(
                         (t + take == tiles_r) ? eff[r] - (tiles_r - 1) * TOK : TOK);
                     d.flags = (fusable && t + take == tiles_r) ? 1u : 0u;
-                    seg_pieces.emplace_back(c, static_cast<uint32_t>(cta_pieces[c].size()));
-                    cta_pieces[c].push_back(d);
+                    seg_pieces.emplace_back(c, cta_pieces.size_so_far(c));
+                    cta_pieces.push(c, d);
                     for (uint32_t i = 0; i < take; ++i) {
                         uint64_t tok0 = static_cast<uint64_t>(t + i) * TOK;
                         uint32_t page = pt_flat[pt_off[r] + tok0 / k.P];
                         uint32_t sub = static_cast<uint32_t>((tok0 % k.P) / TOK);
                         uint32_t fresh = (fusable && t + i + 1 == tiles_r) ? kTileFreshBit : 0u;
-                        cta_tiles[c].push_back(page | (sub << kTileSubShift) | (hb << kTileHbShift) | fresh);
+                        cta_tiles.push(c, page | (sub << kTileSubShift) | (hb << kTileHbShift) | fresh);
                     }
                     t += take;
                     g += take;
@@ -252,7 +285,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                 uint16_t parts = static_cast<uint16_t>(seg_pieces.size());
                 uint32_t first_slot = n_slots;
                 for (size_t i = 0; i < seg_pieces.size(); ++i) {
-                    PieceDesc& d = cta_pieces[seg_pieces[i].first][seg_pieces[i].second];
+                    PieceDesc& d = cta_pieces.at(seg_pieces[i].first, seg_pieces[i].second);
                     d.n_parts = parts;
                     d.seg = parts > 1 ? n_segs : 0;
                     d.seg_first_slot = first_slot;
@@ -266,9 +299,13 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
             }
         }
     }
+    if (n_slices) {
+        cta_pieces.finish();
+        cta_tiles.finish();
+    }
     for (uint32_t i = 0; i < n_slices; ++i) {
-        max_pieces = std::max<uint32_t>(max_pieces, static_cast<uint32_t>(cta_pieces[i].size()));
-        max_tiles = std::max<uint32_t>(max_tiles, static_cast<uint32_t>(cta_tiles[i].size()));
+        max_pieces = std::max<uint32_t>(max_pieces, cta_pieces.size(i));
+        max_tiles = std::max<uint32_t>(max_tiles, cta_tiles.size(i));
     }
 
     // ---- lay the image out
@@ -306,10 +343,10 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     auto* pieces_h = reinterpret_cast<PieceDesc*>(p.host + off_pieces);
     auto* tiles_h = reinterpret_cast<uint32_t*>(p.host + off_tiles);
     for (uint32_t i = 0; i < n_slices; ++i) {
-        counts_h[2 * i] = static_cast<uint32_t>(cta_pieces[i].size());
-        counts_h[2 * i + 1] = static_cast<uint32_t>(cta_tiles[i].size());
-        std::copy(cta_pieces[i].begin(), cta_pieces[i].end(), pieces_h + size_t(i) * max_pieces);
-        std::copy(cta_tiles[i].begin(), cta_tiles[i].end(), tiles_h + size_t(i) * max_tiles);
+        counts_h[2 * i] = cta_pieces.size(i);
+        counts_h[2 * i + 1] = cta_tiles.size(i);
+        std::copy(cta_pieces.data(i), cta_pieces.data(i) + cta_pieces.size(i), pieces_h + size_t(i) * max_pieces);
+        std::copy(cta_tiles.data(i), cta_tiles.data(i) + cta_tiles.size(i), tiles_h + size_t(i) * max_tiles);
     }
     if (k.n_flat) std::memcpy(p.host + off_flat, pt_flat, k.n_flat * 4);
     std::memcpy(p.host + off_ptoff, pt_off, (N + 1) * 4);
@@ -615,6 +652,20 @@ int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
     if (st != MLC_OK) return st;
     a.k_new = a.v_new = nullptr;
     return launch_with_plan(ctx, a, *plan);
+}
+
+int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, size_t n_layers,
+                                         const void* const* q, const void* const* k_new,
+                                         const void* const* v_new, void* const* k_pages, void* const* v_pages,
+                                         void* const* o, float scale, int q_dtype, int o_dtype) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!q || !k_new || !v_new || !k_pages || !v_pages || !o) return ctx->fail(MLC_ERR_INVALID_ARG, "null pointer array");
+    for (size_t l = 0; l < n_layers; ++l) {
+        const int st = mlc_encode_paged_decode_step_planned(ctx, plan, q[l], k_new[l], v_new[l], k_pages[l], v_pages[l],
+                                                            o[l], scale, q_dtype, o_dtype);
+        if (st != MLC_OK) return st;
+    }
+    return MLC_OK;
 }
 
 int mlc_encode_scatter_kv_pair_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, void* k_page_storage,

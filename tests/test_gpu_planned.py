@@ -325,3 +325,28 @@ print("ok")
     env = dict(os.environ, MLC_B200_DECODE_INKERNEL_MERGE="1", PYTHONPATH=root)
     r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_whole_pass_call_equals_layer_by_layer(executor, oracle_mod):
+    """mlc_encode_paged_decode_pass_planned = the per-layer call in a loop: same pools, same outputs."""
+    import torch
+    case = synth.make_case(61, [100, 257, 33, 2000], 32, 4, 64)
+    layers = 3
+    dcs = [DeviceCase(case) for _ in range(2 * layers)]
+    outs = [dc.out() for dc in dcs]
+    plan = make_plan(executor, case)
+    a, b = dcs[:layers], dcs[layers:]
+    assert executor.beginForwardPassCB()
+    for i, dc in enumerate(a):
+        assert executor.encodePagedDecodeStepPlanned(plan, dc.q, dc.k_new, dc.v_new, dc.k_pool, dc.v_pool, outs[i],
+                                                     case.scale, MLC_F16, MLC_F16), executor.last_error()
+    ptrs = [executor.pointerArray(x) for x in ([dc.q for dc in b], [dc.k_new for dc in b], [dc.v_new for dc in b],
+                                                [dc.k_pool for dc in b], [dc.v_pool for dc in b], outs[layers:])]
+    assert executor.encodePagedDecodePassPlanned(plan, *ptrs, case.scale, MLC_F16, MLC_F16), executor.last_error()
+    assert executor.flushForwardPassCB(), executor.last_error()
+    for i in range(layers):
+        assert torch.equal(outs[i], outs[layers + i])
+        assert torch.equal(a[i].k_pool, b[i].k_pool) and torch.equal(a[i].v_pool, b[i].v_pool)
+    kp, vp, want = oracle_step(oracle_mod, case)
+    assert_attention_close(outs[layers].float().cpu().numpy(), want)
+    plan.destroy()
