@@ -74,11 +74,12 @@ void* mlc_ctx_stream(const mlc_ctx* ctx);
 uint64_t mlc_ctx_launch_count(const mlc_ctx* ctx);
 /* Profiling aid (the reference's are env-gated wall-clock tables,
  * compiler/runtime/batched_walker.cpp:100-125): with MLC_B200_TRACE=1 in the
- * environment when the context is created, every warp of the split-KV attention
+ * environment when the context is created, every warp of the decode attention
  * kernel records 8 %globaltimer stamps (entry, copies issued, first tile landed,
- * first piece computed, partial published, merge done, merge started, exit). Copies
- * the stamps of the most recent launch (previous = 0) or of the one before it
- * (previous = 1) as [ctas][4][8] u64 nanoseconds; returns the number of CTAs. */
+ * first piece computed, partial published / merged, merge done, merge started, exit).
+ * Copies the stamps of the most recent launch (previous = 0) or of the one before it
+ * (previous = 1) as [rows][4][8] u64 nanoseconds, a row being 4 consecutive warps (one
+ * row per CTA, two for the 8-warp CTAs of unit mode); returns the number of rows. */
 uint32_t mlc_ctx_read_trace(mlc_ctx* ctx, unsigned long long* out, size_t max_words, int previous);
 
 /* ---- buffers: allocateScratchBuffer / releaseScratchBuffer / uploadToBuffer /

@@ -1030,7 +1030,8 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     // traces of consecutive launches alternate between the two halves of the buffer
     const size_t trace_need = static_cast<size_t>(plan.n_cta) * (plan.unit_mode ? unit_warps(a.D) : kDecodeWarps) * 8;
     prm.trace = ctx->d_trace && trace_need <= ctx->trace_words / 2 ? ctx->d_trace + parity * (ctx->trace_words / 2) : nullptr;
-    ctx->trace_ctas = prm.trace ? plan.n_cta : 0;
+    // rows of 4 warps: a unit-mode CTA of 8 warps fills two consecutive rows
+    ctx->trace_ctas = prm.trace ? plan.n_cta * (plan.unit_mode ? unit_warps(a.D) : kDecodeWarps) / kDecodeWarps : 0;
     ctx->trace_parity = parity;
     if (plan.unit_mode) {
         if (a.D == 64) return g16 ? launch_t<64, true, true>(ctx, plan, prm, mk, mv) : launch_t<64, false, true>(ctx, plan, prm, mk, mv);
