@@ -197,6 +197,17 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+// Same with a compile-time byte offset folded into the address operand.
+template <int OFF>
+__device__ __forceinline__ void ldsm_x4_off(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ void ldsm_x4_trans_off(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -397,6 +408,26 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     }
 
     const uint32_t qrow = lane >> 2, qcol = (lane & 3) * 2;
+    // Per-lane byte offsets of the ldmatrix rows inside a swizzled tile, computed once: a K fragment of
+    // score tile n, k-pair kp sits at koff[kp] + n * 1024, a V fragment of token block kt, column pair np
+    // at voff[np] + kt * 2048 (the token index only enters through lane & 7 and a multiple of 8 rows).
+    // Kept in registers at head_dim 64 (6 values); at 128 the kernel has none to spare and recomputes them.
+    constexpr bool kKeepOffsets = (D == 64);
+    auto k_offset = [&](int kp) -> uint32_t {
+        const uint32_t chunk = kp * 4 + (lane >> 3);
+        return (chunk >> 3) * (TOK * 128) + (lane & 7) * 128 + (((chunk & 7) ^ (lane & 7)) << 4);
+    };
+    auto v_offset = [&](int np) -> uint32_t {
+        const uint32_t chunk = np * 2 + (lane >> 4);
+        return (chunk >> 3) * (TOK * 128) + ((lane & 7) + ((lane >> 3) & 1) * 8) * 128 + (((chunk & 7) ^ (lane & 7)) << 4);
+    };
+    uint32_t koff[kKeepOffsets ? KSTEPS / 2 : 1], voff[kKeepOffsets ? NT_O / 2 : 1];
+    if constexpr (kKeepOffsets) {
+#pragma unroll
+        for (int kp = 0; kp < KSTEPS / 2; ++kp) koff[kp] = k_offset(kp);
+#pragma unroll
+        for (int np = 0; np < NT_O / 2; ++np) voff[np] = v_offset(np);
+    }
     uint32_t j = 0;  // CTA-local tile counter (consume side)
     bool dead = false;
 
@@ -520,14 +551,13 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             for (int n0 = 0; n0 < NT_S; n0 += kScoreGroup) {
                 uint32_t kb[kScoreGroup][KSTEPS / 2][4];
 #pragma unroll
-                for (int ni = 0; ni < kScoreGroup; ++ni) {
-                    const uint32_t tok = (n0 + ni) * 8 + (lane & 7);
-#pragma unroll
-                    for (int kp = 0; kp < KSTEPS / 2; ++kp) {
-                        const uint32_t chunk = kp * 4 + (lane >> 3);  // 16-byte chunk of the row
-                        const uint32_t addr = sK + (chunk >> 3) * (TOK * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
-                        ldsm_x4(addr, kb[ni][kp]);
-                    }
+                for (int kp = 0; kp < KSTEPS / 2; ++kp) {
+                    const uint32_t addr = sK + (kKeepOffsets ? koff[kKeepOffsets ? kp : 0] : k_offset(kp)) + n0 * 1024;
+                    static_assert(kScoreGroup <= 4, "unrolled by hand below");
+                    ldsm_x4_off<0>(addr, kb[0][kp]);
+                    if constexpr (kScoreGroup > 1) ldsm_x4_off<1024>(addr, kb[1][kp]);
+                    if constexpr (kScoreGroup > 2) ldsm_x4_off<2048>(addr, kb[2][kp]);
+                    if constexpr (kScoreGroup > 3) ldsm_x4_off<3072>(addr, kb[3][kp]);
                 }
 #pragma unroll
                 for (int ni = 0; ni < kScoreGroup; ++ni) sc[n0 + ni][0] = sc[n0 + ni][1] = sc[n0 + ni][2] = sc[n0 + ni][3] = 0.f;
@@ -555,21 +585,31 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
             for (int rs = 0; rs < ROWSETS; ++rs) {
                 float tmax = -INFINITY;
+                if (nv < TOK) {  // only a request's last tile is partly valid (warp-uniform)
 #pragma unroll
-                for (int n = 0; n < NT_S; ++n) {
+                    for (int n = 0; n < NT_S; ++n) {
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const uint32_t tok = n * 8 + qcol + e;
-                        float v = sc[n][2 * rs + e] * prm.scale_log2;
-                        v = tok < nv ? v : -INFINITY;
-                        sc[n][2 * rs + e] = v;
-                        tmax = fmaxf(tmax, v);
+                        for (int e = 0; e < 2; ++e) {
+                            const uint32_t tok = n * 8 + qcol + e;
+                            const float v = tok < nv ? sc[n][2 * rs + e] * prm.scale_log2 : -INFINITY;
+                            sc[n][2 * rs + e] = v;
+                            tmax = fmaxf(tmax, v);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int n = 0; n < NT_S; ++n) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float v = sc[n][2 * rs + e] * prm.scale_log2;
+                            sc[n][2 * rs + e] = v;
+                            tmax = fmaxf(tmax, v);
+                        }
                     }
                 }
                 tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
                 tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
                 const float m_new = fmaxf(m_run[rs], tmax);  // finite: every tile has >= 1 valid token
-                const float alpha = ex2(m_run[rs] - m_new);  // ex2(-inf) = 0 on the first tile
                 float psum = 0.f;
 #pragma unroll
                 for (int n = 0; n < NT_S; ++n) {
@@ -577,13 +617,19 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     psum += p0 + p1;
                     pa[n >> 1][rs + 2 * (n & 1)] = pack_half2(p0, p1);
                 }
-                l_run[rs] = l_run[rs] * alpha + psum;
-                m_run[rs] = m_new;
+                // The accumulators are rescaled only when some row's maximum moved, which after the
+                // first tiles of a request is rare (warp-uniform test).
+                if (__any_sync(0xffffffffu, m_new > m_run[rs])) {
+                    const float alpha = ex2(m_run[rs] - m_new);  // ex2(-inf) = 0 on the first tile
+                    l_run[rs] *= alpha;
+                    m_run[rs] = m_new;
 #pragma unroll
-                for (int n = 0; n < NT_O; ++n) {
-                    o_acc[n][2 * rs] *= alpha;
-                    o_acc[n][2 * rs + 1] *= alpha;
+                    for (int n = 0; n < NT_O; ++n) {
+                        o_acc[n][2 * rs] *= alpha;
+                        o_acc[n][2 * rs + 1] *= alpha;
+                    }
                 }
+                l_run[rs] += psum;
             }
             if (!G16) {
 #pragma unroll
@@ -595,16 +641,12 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             constexpr int kOutGroup = 4;  // ldmatrix per batch = 16 fragment registers
 #pragma unroll
             for (int kt = 0; kt < TOK / 16; ++kt) {
-                const uint32_t tok = kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
                 for (int np0 = 0; np0 < NT_O / 2; np0 += kOutGroup) {
                     uint32_t vb[kOutGroup][4];
 #pragma unroll
-                    for (int i = 0; i < kOutGroup; ++i) {
-                        const uint32_t chunk = (np0 + i) * 2 + (lane >> 4);
-                        const uint32_t addr = sV + (chunk >> 3) * (TOK * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
-                        ldsm_x4_trans(addr, vb[i]);
-                    }
+                    for (int i = 0; i < kOutGroup; ++i)
+                        ldsm_x4_trans(sV + (kKeepOffsets ? voff[kKeepOffsets ? np0 + i : 0] : v_offset(np0 + i)) + kt * 2048, vb[i]);
 #pragma unroll
                     for (int i = 0; i < kOutGroup; ++i) {
                         mma_16816(o_acc[2 * (np0 + i)], pa[kt], vb[i][0], vb[i][1]);
