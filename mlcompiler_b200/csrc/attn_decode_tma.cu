@@ -344,14 +344,16 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     };
     // Ring position counters of this warp. They count only tiles of head blocks in
     // which this warp owns a KV head, in the (identical) order of issue and use.
-    uint32_t iss = 0, con = 0;
+    // (kept as wrapping stage indices and a parity bit: the ring depth is a run-time value, and a
+    // division by it per tile costs tens of instructions)
+    uint32_t iss_stage = 0, con_stage = 0, con_parity = 0;
     // Issues the TMA copies of the tile word `e` into the next ring stage.
     auto issue_word = [&](uint32_t e) {
         const uint32_t hfield = (e >> kTileHbShift) & kTileHbMask;   // head block, or the head itself in unit mode
         const uint32_t head = UNIT ? hfield : hfield * kDecodeWarps + warp;
         if (head >= prm.KVH) return;  // this warp has no KV head in that head block
-        const uint32_t s = iss % stages;
-        ++iss;
+        const uint32_t s = iss_stage;
+        iss_stage = (iss_stage + 1 == stages) ? 0u : iss_stage + 1;
         if (lane == 0) {
             const uint32_t bar = smem_u32(&bars[warp][s]);
             const uint32_t dst = ring + s * kStageBytes;
@@ -507,10 +509,13 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
         for (uint32_t t = 0; t < piece_tiles; ++t, ++j) {
-            const uint32_t s = con % stages;
+            const uint32_t s = con_stage;
             const uint32_t bar = smem_u32(&bars[warp][s]);
-            const uint32_t parity = (con / stages) & 1u;
-            ++con;
+            const uint32_t parity = con_parity;
+            if (++con_stage == stages) {
+                con_stage = 0;
+                con_parity ^= 1u;
+            }
             if (!mbar_wait_bounded(bar, parity)) {
                 if (lane == 0) atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
                 dead = true;
