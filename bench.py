@@ -47,7 +47,7 @@ WORKLOAD = ("cfg2: 22-layer continuous-batching decode, 32 requests, H32/KVH4/D6
             "contexts U[64,2048], random page tables, pool = pages + 10%; per layer: scatter 1 new K/V row "
             "per request, then attention")
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel on this workload
-# (37.79 MB read + 1.5 KB written), from the ncu capture summarised in
+# (37.79 MB read + <= 1.5 KB written), from the ncu captures summarised in
 # profiles/decode_attention_cfg2.md; the algorithmic KV bytes of that launch are 37.00 MB.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 37_794_560
 
