@@ -380,48 +380,51 @@ def run_gpu_arm(args):
     peak, peak_kind = measured_peak_gbs()
 
     # ---- end-to-end arm: host buffers, host tables, reference-shaped calls ---------------
-    q_host = torch.randn((LAYERS, N, H, D), dtype=torch.float16).pin_memory()
-    kn_host = torch.randn((LAYERS, N, KVH, D), dtype=torch.float16).pin_memory()
-    vn_host = torch.randn((LAYERS, N, KVH, D), dtype=torch.float16).pin_memory()
+    # Per layer one packed row [Q | new K | new V] in pinned host memory and on the device, O back to
+    # pinned host memory, all inside the timed region.
+    nq, nkv = N * H * D, N * KVH * D
+    in_host = torch.randn((LAYERS, nq + 2 * nkv), dtype=torch.float16).pin_memory()
+    in_dev = torch.empty((LAYERS, nq + 2 * nkv), device=dev, dtype=torch.float16)
     o_host = torch.zeros((LAYERS, N, H, D), dtype=torch.float16).pin_memory()
-    h2d = q_host.numel() * 2 + kn_host.numel() * 2 + vn_host.numel() * 2
+    h2d = in_host.numel() * 2
     d2h = o_host.numel() * 2
 
-    # The call sequence INTEGRATION.md recommends to a walker: per step one in-place plan update with the
-    # step's host tables, then one fused scatter + attention call per layer; Q / new K / new V rows come
-    # from pinned host memory and O goes back to it inside the timed region.
-    e2e_plan = ex.createPlan(flat, off, lens, q_pos, N, H, KVH, D, P, True, cap, page_ids=ids, slots_in_page=slots)
-
-    e2e_ptrs = [ex.pointerArray(bufs) for bufs in ([q_all[L] for L in range(LAYERS)], [kn_all[L] for L in range(LAYERS)],
-                                                     [vn_all[L] for L in range(LAYERS)], k_pools, v_pools,
-                                                     [o_all[L] for L in range(LAYERS)])]
+    # The call sequence INTEGRATION.md recommends to a walker whose activations are host vectors: per step
+    # one in-place plan update with the step's host tables and one host-buffer pass call. Inside that call
+    # the layers go in a few groups so that the copies overlap the kernels (group g's rows are copied on a
+    # copy stream while group g-1 computes, its O rows go back while group g+1 computes). The tables of
+    # step s+1 do not depend on the results of step s (every request grows by one row), so they are handed
+    # to the library - validated, planned, uploaded, into the other of two plans - while step s still runs.
+    e2e_plans = [ex.createPlan(flat, off, lens, q_pos, N, H, KVH, D, P, True, cap, page_ids=ids, slots_in_page=slots)
+                 for _ in range(2)]
+    pool_ptrs = [ex.pointerArray(k_pools), ex.pointerArray(v_pools)]
 
     # the 16 table sets the growing requests cycle through, built once: what is timed is handing them
     # to the library (validation, planning, upload), not this script's numpy code
     table_sets = [tables(i) for i in range(16)]
 
-    def e2e_step(step):
+    def plan_for(step):
         lens_s, q_pos_s, ids_s, slots_s, flat_s, off_s = table_sets[step % 16]
-        with torch.cuda.stream(stream):
-            q_all.copy_(q_host, non_blocking=True)
-            kn_all.copy_(kn_host, non_blocking=True)
-            vn_all.copy_(vn_host, non_blocking=True)
-        assert ex.beginForwardPassCB()
-        assert e2e_plan.update(flat_s, off_s, lens_s, q_pos_s, ids_s, slots_s), ex.last_error()
-        ok = ex.encodePagedDecodePassPlanned(e2e_plan, *e2e_ptrs, case.scale, MLC_F16, MLC_F16)   # all 22 layers
-        assert ok, ex.last_error()
-        with torch.cuda.stream(stream):
-            o_host.copy_(o_all, non_blocking=True)
-        assert ex.flushForwardPassCB(), ex.last_error()
-        return kv_bytes_layer(lens_s) * LAYERS
+        assert e2e_plans[step % 2].update(flat_s, off_s, lens_s, q_pos_s, ids_s, slots_s), ex.last_error()
 
-    for w in range(max(args.warmup, 3)):
+    def e2e_step(step):
+        assert ex.beginForwardPassCB()
+        ok = ex.encodePagedDecodePassHost(e2e_plans[step % 2], in_host, in_dev, *pool_ptrs, o_all, o_host, case.scale,
+                                          MLC_F16, MLC_F16)                      # all 22 layers, copies included
+        assert ok, ex.last_error()
+        plan_for(step + 1)          # the next step's tables, while this step runs
+        assert ex.flushForwardPassCB(), ex.last_error()      # returns when o_host is complete
+        return kv_bytes_layer(table_sets[step % 16][0]) * LAYERS
+
+    first = max(args.warmup, 3)
+    plan_for(0)
+    for w in range(first):
         e2e_step(w)
     barrier()
     t0 = time.perf_counter()
     e2e_bytes = 0
     for s in range(args.steps):
-        e2e_bytes += e2e_step(max(args.warmup, 3) + s)
+        e2e_bytes += e2e_step(first + s)
     stream.synchronize()
     t_e2e = time.perf_counter() - t0
     barrier()
@@ -459,7 +462,8 @@ def run_gpu_arm(args):
     graph.destroy()
     graph_attn.destroy()
     plan.destroy()
-    e2e_plan.destroy()
+    for pl in e2e_plans:
+        pl.destroy()
     ex.close()
     if world > 1:
         dist.destroy_process_group()

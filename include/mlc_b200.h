@@ -301,6 +301,23 @@ int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
                                          void* const* v_pages, void* const* o, float scale, int q_dtype,
                                          int o_dtype);
 
+/* The same pass for a caller whose activations live in host memory (the reference's walker hands the
+ * runtime host vectors per layer, batched_walker.cpp:299-331, and reads the result back): copies in,
+ * kernels and copies out are pipelined over the layers inside the call.
+ *   host_in  [n_layers] rows of [ Q: batch*H*D of q_dtype | new K: batch*KVH*D fp16 | new V: same ],
+ *            pinned memory if the copies are to overlap the kernels
+ *   dev_in   device staging buffer of the same size, caller-owned
+ *   dev_o / host_o  [n_layers][batch][H][D] of o_dtype on the device and in host memory
+ * The layers go in n_groups groups (0 = 5): group g's rows are copied on a copy stream while group
+ * g-1 computes, its O rows go back on another stream while group g+1 computes. The context's stream
+ * is made to wait for the last copy back, so mlc_pass_flush returns when host_o is complete.
+ * Not capturable (MLC_ERR_UNSUPPORTED between mlc_graph_begin_capture and _end_capture). The streams
+ * and events are created on the first call. */
+int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, size_t n_layers,
+                                      const void* host_in, void* dev_in, void* const* k_pages,
+                                      void* const* v_pages, void* dev_o, void* host_o, float scale,
+                                      int q_dtype, int o_dtype, size_t n_groups);
+
 /* ---- QKV split + rotary embedding + cast, the step that feeds the scatter -------------
  * encodeQkvSplitRopeCast (metal_runtime.hpp:540-547; metal_runtime.mm:7915-8025: 3 x
  * strided_copy_f32 + 2 x batched_rope + 2 x cast_f32_to_f16 in one encoder) as ONE launch.

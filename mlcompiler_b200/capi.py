@@ -89,6 +89,8 @@ _PROTOTYPES = {
     "mlc_encode_paged_decode_step_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i]),
     "mlc_encode_paged_decode_pass_planned": (_i, [_vp, _vp, _sz, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                                   C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _f, _i, _i]),
+    "mlc_encode_paged_decode_pass_host": (_i, [_vp, _vp, _sz, _vp, _vp, C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _f,
+                                               _i, _i, _sz]),
     "mlc_encode_paged_attention_partial_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i]),
     "mlc_encode_lse_combine": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _i]),
     "mlc_graph_begin_capture": (_i, [_vp]),
@@ -405,6 +407,16 @@ class Executor:
         pointer arrays (pointerArray) with one entry per layer."""
         return self.status(self._lib.mlc_encode_paged_decode_pass_planned(
             self._h, plan.handle, len(q), q, k_new, v_new, k_pages, v_pages, o, float(scale), q_dtype, o_dtype))
+
+    def encodePagedDecodePassHost(self, plan, host_in, dev_in, k_pages, v_pages, dev_o, host_o, scale=0.0,
+                                  q_dtype=MLC_F32, o_dtype=MLC_F32, n_groups=0) -> bool:
+        """A decode pass whose activations live in host memory: host_in holds one packed row
+        [Q | new K | new V] per layer (pinned memory lets the copies overlap the kernels), dev_in is a
+        device staging buffer of the same size, k_pages / v_pages are pointer arrays with one pool per
+        layer, O goes to dev_o and from there to host_o. Complete when flushForwardPassCB returns."""
+        return self.status(self._lib.mlc_encode_paged_decode_pass_host(
+            self._h, plan.handle, len(k_pages), _vp(_ptr(host_in)), _vp(_ptr(dev_in)), k_pages, v_pages,
+            _vp(_ptr(dev_o)), _vp(_ptr(host_o)), float(scale), q_dtype, o_dtype, n_groups))
 
     def encodeQkvSplitRopeCast(self, qkv_buf, q_buf, k_buf, v_buf, k_f16_buf, v_f16_buf, cos_buf, sin_buf, batch,
                                num_heads, kv_heads, head_dim, qkv_rows, q_rows, k_rows, v_rows, rotary_dim) -> bool:

@@ -152,7 +152,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         // The estimate below is in microseconds and in "head tiles" (32 tokens of one head, K and V);
         // its constants come from timing both forms on B200 over a dozen batch shapes (per layer, in a
         // CUDA graph): ~0.18 us per head tile and SM when the HBM is shared by all SMs, ~0.135 us per
-        // head tile for the CTA that holds the longest unit, fixed costs of ~3 us (unit) and ~9 us plus
+        // head tile (0.095 with 8 warps at head_dim 64) for the CTA that holds the longest unit, fixed costs of ~3 us (unit) and ~9 us plus
         // ~0.9 us per 12 parts of the most split request (split).
         const uint32_t TOKu = kTileTokens;
         std::vector<std::pair<uint32_t, uint32_t>> units;  // (tiles, request * KVH + head)
@@ -185,7 +185,8 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
             }
             const double f = static_cast<double>(k.D) / 64.0;
             const double per_sm_tiles = static_cast<double>(head_tiles) / ctx->sm_count;
-            const double t_unit = f * std::max(0.135 * static_cast<double>(critical), 0.18 * per_sm_tiles) + 3.0;
+            const double c_lone = k.D == 64 ? 0.095 : 0.135;  // per head tile on the fullest CTA (8 warps at 64, 4 at 128)
+            const double t_unit = f * std::max(c_lone * static_cast<double>(critical), 0.18 * per_sm_tiles) + 3.0;
             const uint32_t n_hb_e = static_cast<uint32_t>((k.KVH + kDecodeWarps - 1) / kDecodeWarps);
             const double hb_tiles = static_cast<double>(head_tiles) / k.KVH * n_hb_e;      // tiles of the split form
             const double per_cta = std::max(1.0, hb_tiles / cta_cap);
@@ -195,7 +196,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
             unit_mode = forced == 2 || (forced == 0 && t_unit < t_split);
         }
         stages = static_cast<uint32_t>(std::min<int>(decode_tma_max_stages(k.H, k.KVH, k.D),
-                                                     std::max(1, env_int("MLC_B200_DECODE_STAGES", 3))));
+                                                     std::max(1, env_int("MLC_B200_DECODE_STAGES", k.D == 128 ? 2 : 3))));
         if (unit_mode) {
             // the exchange area of the in-CTA merge must fit beside the rings
             while (stages > 1 && decode_tma_smem_bytes(k.D, k.H / k.KVH > 8, stages, true) > 227 * 1024 - 1024) --stages;  // 1 KiB for the barriers
@@ -665,6 +666,76 @@ int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
                                                             o[l], scale, q_dtype, o_dtype);
         if (st != MLC_OK) return st;
     }
+    return MLC_OK;
+}
+
+int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, size_t n_layers, const void* host_in,
+                                      void* dev_in, void* const* k_pages, void* const* v_pages, void* dev_o,
+                                      void* host_o, float scale, int q_dtype, int o_dtype, size_t n_groups) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (ctx->capturing) return ctx->fail(MLC_ERR_UNSUPPORTED, "the host-buffer pass uses its own copy streams and cannot be captured");
+    if (!host_in || !dev_in || !k_pages || !v_pages || !dev_o || !host_o || !n_layers) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    if ((q_dtype != MLC_F16 && q_dtype != MLC_F32) || (o_dtype != MLC_F16 && o_dtype != MLC_F32))
+        return ctx->fail(MLC_ERR_INVALID_ARG, "q / o dtype must be MLC_F16 or MLC_F32");
+    const PlanKey& k = plan->key;
+    const size_t q_bytes = k.batch * k.H * k.D * (q_dtype == MLC_F32 ? 4 : 2);
+    const size_t kv_bytes = k.batch * k.KVH * k.D * 2;
+    const size_t in_row = q_bytes + 2 * kv_bytes;
+    const size_t o_row = k.batch * k.H * k.D * (o_dtype == MLC_F32 ? 4 : 2);
+    if (in_row % 16 || q_bytes % 16 || kv_bytes % 16) return ctx->fail(MLC_ERR_UNSUPPORTED, "rows of the packed input must be multiples of 16 bytes");
+    DeviceGuard guard(ctx->device);
+    // group boundaries: two layers first and last (little copy time left uncovered), the rest in equal parts
+    std::vector<size_t> bounds;
+    if (n_groups == 0) n_groups = 5;
+    if (n_groups >= 3 && n_layers >= 2 * n_groups) {
+        bounds.push_back(0);
+        const size_t mid = n_layers - 4, parts = n_groups - 2;
+        for (size_t i = 0; i <= parts; ++i) bounds.push_back(2 + mid * i / parts);
+        bounds.push_back(n_layers);
+    } else {
+        n_groups = std::min(n_groups, n_layers);
+        for (size_t i = 0; i <= n_groups; ++i) bounds.push_back(n_layers * i / n_groups);
+    }
+    const size_t G = bounds.size() - 1;
+    if (!ctx->h2d_stream) {
+        MLCB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+        MLCB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+    }
+    while (ctx->pass_events.size() < 2 * G + 2) {
+        cudaEvent_t e;
+        MLCB_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        ctx->pass_events.push_back(e);
+    }
+    cudaEvent_t ev_start = ctx->pass_events[2 * G], ev_done = ctx->pass_events[2 * G + 1];
+    // the staging buffer may still be read by kernels already in the stream
+    MLCB_CUDA(ctx, cudaEventRecord(ev_start, ctx->stream));
+    MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->h2d_stream, ev_start, 0));
+    const char* hin = static_cast<const char*>(host_in);
+    char* din = static_cast<char*>(dev_in);
+    char* dout = static_cast<char*>(dev_o);
+    char* hout = static_cast<char*>(host_o);
+    for (size_t g = 0; g < G; ++g) {
+        const size_t a = bounds[g], b = bounds[g + 1];
+        MLCB_CUDA(ctx, cudaMemcpyAsync(din + a * in_row, hin + a * in_row, (b - a) * in_row, cudaMemcpyHostToDevice, ctx->h2d_stream));
+        MLCB_CUDA(ctx, cudaEventRecord(ctx->pass_events[g], ctx->h2d_stream));
+    }
+    for (size_t g = 0; g < G; ++g) {
+        const size_t a = bounds[g], b = bounds[g + 1];
+        MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->pass_events[g], 0));
+        for (size_t l = a; l < b; ++l) {
+            const char* row = din + l * in_row;
+            const int st = mlc_encode_paged_decode_step_planned(ctx, plan, row, row + q_bytes, row + q_bytes + kv_bytes, k_pages[l],
+                                                                v_pages[l], dout + l * o_row, scale, q_dtype, o_dtype);
+            if (st != MLC_OK) return st;
+        }
+        MLCB_CUDA(ctx, cudaEventRecord(ctx->pass_events[G + g], ctx->stream));
+        MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ctx->pass_events[G + g], 0));
+        MLCB_CUDA(ctx, cudaMemcpyAsync(hout + a * o_row, dout + a * o_row, (b - a) * o_row, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+    }
+    // the context's stream ends after the last copy back, so a flush covers the whole pass
+    MLCB_CUDA(ctx, cudaEventRecord(ev_done, ctx->d2h_stream));
+    MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ev_done, 0));
     return MLC_OK;
 }
 

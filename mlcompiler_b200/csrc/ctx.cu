@@ -182,6 +182,9 @@ void mlc_ctx_destroy(mlc_ctx* ctx) {
     if (ctx->d_counters) cudaFree(ctx->d_counters);
     if (ctx->d_err) cudaFree(ctx->d_err);
     if (ctx->d_trace) cudaFree(ctx->d_trace);
+    for (cudaEvent_t e : ctx->pass_events) cudaEventDestroy(e);
+    if (ctx->h2d_stream) cudaStreamDestroy(ctx->h2d_stream);
+    if (ctx->d2h_stream) cudaStreamDestroy(ctx->d2h_stream);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }

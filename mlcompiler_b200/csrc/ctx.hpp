@@ -54,6 +54,9 @@ struct mlc_ctx {
     size_t n_counters = 0;
     size_t decode_smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
     bool prefill_smem_set = false;             // same, for the chunked-prefill kernel
+    // copy streams and events of the host-buffer decode pass (created on first use)
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+    std::vector<cudaEvent_t> pass_events;
     // optional per-warp phase stamps of the last decode launch (env MLC_B200_TRACE=1)
     unsigned long long* d_trace = nullptr;
     size_t trace_words = 0;

@@ -350,3 +350,63 @@ def test_whole_pass_call_equals_layer_by_layer(executor, oracle_mod):
     kp, vp, want = oracle_step(oracle_mod, case)
     assert_attention_close(outs[layers].float().cpu().numpy(), want)
     plan.destroy()
+
+
+@pytest.mark.parametrize("layers,groups", [(3, 0), (12, 0), (12, 1), (5, 3)])
+def test_host_buffer_pass_equals_layer_by_layer(executor, layers, groups):
+    """mlc_encode_paged_decode_pass_host = copy in + the per-layer call + copy out, pipelined over groups of
+    layers: same pools and bit-identical outputs, for every way of cutting the layers into groups."""
+    import torch
+    case = synth.make_case(62, [100, 257, 33, 2000], 32, 4, 64)
+    N, H, KVH, D = case.N, case.H, case.KVH, case.D
+    plan = make_plan(executor, case)
+    a = [DeviceCase(case) for _ in range(layers)]
+    b = [DeviceCase(case) for _ in range(layers)]
+    gen = torch.Generator().manual_seed(7)
+    nq, nkv = N * H * D, N * KVH * D
+    host_in = torch.randn((layers, nq + 2 * nkv), generator=gen).to(torch.float16).pin_memory()
+    dev_in = torch.zeros_like(host_in, device="cuda")
+    dev_o = torch.zeros((layers, N, H, D), dtype=torch.float16, device="cuda")
+    host_o = torch.zeros((layers, N, H, D), dtype=torch.float16).pin_memory()
+    want = [dc.out() for dc in a]
+    assert executor.beginForwardPassCB()
+    rows = host_in.cuda()
+    torch.cuda.synchronize()
+    for i, dc in enumerate(a):
+        assert executor.encodePagedDecodeStepPlanned(plan, rows[i, :nq], rows[i, nq:nq + nkv], rows[i, nq + nkv:], dc.k_pool,
+                                                     dc.v_pool, want[i], case.scale, MLC_F16, MLC_F16), executor.last_error()
+    ptrs = [executor.pointerArray(x) for x in ([dc.k_pool for dc in b], [dc.v_pool for dc in b])]
+    assert executor.encodePagedDecodePassHost(plan, host_in, dev_in, *ptrs, dev_o, host_o, case.scale, MLC_F16, MLC_F16,
+                                              groups), executor.last_error()
+    assert executor.flushForwardPassCB(), executor.last_error()      # host_o is complete here, no further sync
+    for i in range(layers):
+        assert torch.equal(host_o[i], want[i].cpu().reshape(N, H, D))
+        assert torch.equal(a[i].k_pool, b[i].k_pool) and torch.equal(a[i].v_pool, b[i].v_pool)
+    assert torch.equal(dev_in.cpu(), host_in)
+    plan.destroy()
+
+
+def test_host_buffer_pass_is_refused_during_capture(executor):
+    import torch
+    case = synth.make_case(63, [70, 130], 8, 2, 64)
+    plan = make_plan(executor, case)
+    dc = DeviceCase(case)
+    row = case.N * (case.H + 2 * case.KVH) * case.D
+    host_in = torch.zeros((1, row), dtype=torch.float16).pin_memory()
+    dev_in = torch.zeros((1, row), dtype=torch.float16, device="cuda")
+    dev_o = torch.zeros((1, case.N, case.H, case.D), dtype=torch.float16, device="cuda")
+    host_o = torch.zeros((1, case.N, case.H, case.D), dtype=torch.float16).pin_memory()
+    ptrs = [executor.pointerArray([dc.k_pool]), executor.pointerArray([dc.v_pool])]
+    torch.cuda.synchronize()
+    assert executor.beginForwardPassCB()
+    assert executor.beginCapture()
+    assert not executor.encodePagedDecodePassHost(plan, host_in, dev_in, *ptrs, dev_o, host_o, case.scale, MLC_F16, MLC_F16)
+    assert "captured" in executor.last_error()
+    out = dc.out()
+    assert executor.encodePagedDecodeStepPlanned(plan, dc.q, dc.k_new, dc.v_new, dc.k_pool, dc.v_pool, out, case.scale,
+                                                 MLC_F16, MLC_F16), executor.last_error()     # the capture itself is intact
+    graph = executor.endCapture()
+    graph.launch()
+    assert executor.flushForwardPassCB(), executor.last_error()
+    graph.destroy()
+    plan.destroy()
