@@ -129,7 +129,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
 
     FlatLists<PieceDesc> cta_pieces;   // per plan slice, filled slice after slice
     FlatLists<uint32_t> cta_tiles;
-    uint32_t n_cta = 0, max_pieces = 1, max_tiles = 1, n_slots = 0, n_segs = 0, stages = 3;
+    uint32_t n_cta = 0, max_pieces = 1, max_tiles = 1, n_slots = 0, n_segs = 0, n_unit_cuts = 0, stages = 3;
     // A decode step can fuse the row write into attention when the newest token of every
     // request (position seq_len - 1, where page_ids / slots must point) is attended to.
     bool fusable = page_ids != nullptr;
@@ -147,8 +147,8 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         // split: requests cut over all CTAs along the sequence, 4 KV heads per CTA, split requests merged
         //        by a second kernel chained behind (on the critical path, longer with more parts);
         // unit : a (request, KV head) never leaves its CTA - longest-first packing of whole units onto
-        //        the CTAs, the CTA's warps share a unit and merge in shared memory, no merge kernel; the
-        //        longest unit bounds the launch, so it loses when one request dwarfs the rest.
+        //        the CTAs, the CTA's warps share a unit and merge in shared memory, no merge kernel; a
+        //        unit that dwarfs a CTA's fair share is cut into runs on different CTAs (see below).
         // The estimate below is in microseconds and in "head tiles" (32 tokens of one head, K and V);
         // its constants come from timing both forms on B200 over a dozen batch shapes (per layer, in a
         // CUDA graph): ~0.18 us per head tile and SM when the HBM is shared by all SMs, ~0.135 us per
@@ -165,28 +165,101 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         }
         const int per_sm_u = std::max(env_int("MLC_B200_DECODE_CTAS_PER_SM", 1), 1);
         const uint32_t cta_cap = static_cast<uint32_t>(ctx->sm_count) * per_sm_u;
-        const uint32_t n_cta_u = static_cast<uint32_t>(std::min<size_t>(cta_cap, units.size()));
-        std::vector<std::vector<uint32_t>> cta_units(n_cta_u);
-        uint64_t critical = 0;
-        if (n_cta_u && k.KVH <= kTileHbMask + 1) {
-            std::sort(units.begin(), units.end(), [](const auto& a, const auto& b) { return a.first != b.first ? a.first > b.first : a.second < b.second; });
-            // longest-first onto the least loaded CTA
-            std::vector<std::pair<uint64_t, uint32_t>> heap;  // (load, cta), min-heap
-            for (uint32_t c = 0; c < n_cta_u; ++c) heap.emplace_back(0, c);
-            auto cmp = [](const auto& a, const auto& b) { return a.first != b.first ? a.first > b.first : a.second > b.second; };
-            std::make_heap(heap.begin(), heap.end(), cmp);
+        const uint32_t UW = static_cast<uint32_t>(unit_warps(k.D));
+        // An item is a unit or, when cutting helps, a run of a unit's tiles: a unit much longer than a
+        // CTA's fair share (all tiles / CTAs) is cut into equal runs that go to different CTAs; each
+        // leaves a partial in the workspace and the CTA that brings a unit's last part combines them
+        // (an arrival counter per cut unit, nobody waits). Items are packed by estimated time, longest
+        // first onto the least loaded CTA: c_lone per tile, ~1 us per item (Q fetch, in-CTA exchange: a
+        // CTA's items do not overlap), and for a run of a cut unit ~0.75 us + 0.135 us per part (store of
+        // the partial, counter round trip, the last arrival's loads). Cutting pays when one unit dwarfs
+        // a CTA's fair share (a lone 16384-token request: 47 -> 10 us per layer; 4 x 32768: 92 -> 27) and
+        // costs when the batch is balanced already (cfg2 forced to cut at the fair share: 8.8 -> 13.6),
+        // so a few run lengths are packed and the whole-unit packing stays unless a cut one is
+        // estimated at least 10 % faster.
+        struct Item { uint32_t tiles, id, lo, hi, part, n_parts, cut, cost_ns; };   // cut: index among the cut units
+        struct Packing {
+            std::vector<Item> items;
+            std::vector<std::vector<uint32_t>> cta_items;   // indices into items
+            uint64_t critical = 0;   // estimated time of the fullest CTA, ns
+            uint32_t n_cta = 0, n_cut = 0, n_parts_total = 0;
+        };
+        const double f_dim = static_cast<double>(k.D) / 64.0;
+        const double c_lone = k.D == 64 ? 0.095 : 0.135;  // us per head tile on the fullest CTA (8 warps at 64, 4 at 128)
+        auto pack = [&](uint32_t cap_tiles, Packing& pk) {
+            pk.items.clear();
+            pk.n_cut = pk.n_parts_total = 0;
             for (const auto& u : units) {
+                uint32_t parts = 1;
+                if (cap_tiles && u.first > cap_tiles + cap_tiles / 4) parts = std::min<uint32_t>((u.first + cap_tiles - 1) / cap_tiles, 64u);
+                for (uint32_t q = 0; q < parts; ++q) {
+                    const uint32_t lo = static_cast<uint32_t>(static_cast<uint64_t>(u.first) * q / parts);
+                    const uint32_t hi = static_cast<uint32_t>(static_cast<uint64_t>(u.first) * (q + 1) / parts);
+                    const double us = f_dim * c_lone * (hi - lo) + 1.0 + (parts > 1 ? 0.75 + 0.135 * parts : 0.0);
+                    pk.items.push_back(Item{hi - lo, u.second, lo, hi, q, parts, parts > 1 ? pk.n_cut : 0u,
+                                            static_cast<uint32_t>(us * 1000.0)});
+                }
+                if (parts > 1) {
+                    ++pk.n_cut;
+                    pk.n_parts_total += parts;
+                }
+            }
+            std::vector<uint32_t> order(pk.items.size());
+            for (uint32_t i = 0; i < order.size(); ++i) order[i] = i;
+            std::sort(order.begin(), order.end(), [&](uint32_t x, uint32_t y) {
+                return pk.items[x].cost_ns != pk.items[y].cost_ns ? pk.items[x].cost_ns > pk.items[y].cost_ns : x < y;
+            });
+            pk.n_cta = static_cast<uint32_t>(std::min<size_t>(cta_cap, pk.items.size()));
+            pk.cta_items.assign(pk.n_cta, {});
+            pk.critical = 0;
+            std::vector<std::pair<uint64_t, uint32_t>> heap;  // (load, cta), min-heap
+            for (uint32_t c = 0; c < pk.n_cta; ++c) heap.emplace_back(0, c);
+            auto cmp = [](const auto& x, const auto& y) { return x.first != y.first ? x.first > y.first : x.second > y.second; };
+            std::make_heap(heap.begin(), heap.end(), cmp);
+            for (uint32_t i : order) {
                 std::pop_heap(heap.begin(), heap.end(), cmp);
                 auto& slot = heap.back();
-                cta_units[slot.second].push_back(u.second);
-                slot.first += u.first;
-                critical = std::max(critical, slot.first);
+                pk.cta_items[slot.second].push_back(i);
+                slot.first += pk.items[i].cost_ns;
+                pk.critical = std::max(pk.critical, slot.first);
                 std::push_heap(heap.begin(), heap.end(), cmp);
             }
-            const double f = static_cast<double>(k.D) / 64.0;
+        };
+        Packing whole, cut, trial;
+        Packing* chosen = nullptr;
+        double t_unit = 0.0;
+        if (!units.empty() && k.KVH <= kTileHbMask + 1) {
+            // (tiles, id) descending so that equal packings come out the same from call to call
+            std::sort(units.begin(), units.end(), [](const auto& x, const auto& y) { return x.first != y.first ? x.first > y.first : x.second < y.second; });
+            const double f = f_dim;
             const double per_sm_tiles = static_cast<double>(head_tiles) / ctx->sm_count;
-            const double c_lone = k.D == 64 ? 0.095 : 0.135;  // per head tile on the fullest CTA (8 warps at 64, 4 at 128)
-            const double t_unit = f * std::max(c_lone * static_cast<double>(critical), 0.18 * per_sm_tiles) + 3.0;
+            const double t_stream = f * 0.18 * per_sm_tiles;   // all SMs sharing the HBM
+            pack(0, whole);
+            chosen = &whole;
+            t_unit = std::max(whole.critical * 1e-3, t_stream) + 2.0;
+            // MLC_B200_DECODE_UNIT_CUT: 0 = never cut, otherwise the run lengths tried are this percentage
+            // of 2.5x, 1.5x and 1x the fair share; MLC_B200_DECODE_UNIT_CUT_FORCE=1 cuts at that percentage.
+            const int cut_pct = env_int("MLC_B200_DECODE_UNIT_CUT", 100);
+            const bool force_cut = env_int("MLC_B200_DECODE_UNIT_CUT_FORCE", 0) != 0;
+            const uint32_t fair = static_cast<uint32_t>((head_tiles + cta_cap - 1) / cta_cap);
+            if (cut_pct > 0 && (force_cut || whole.critical * 1e-3 > 1.3 * t_stream)) {
+                double best = force_cut ? 1e30 : t_unit * 0.9;
+                uint32_t last_cap = 0;
+                for (const int mult : {250, 150, 100}) {   // longest runs first: on a tie the fewer parts win
+                    if (force_cut && mult != 100) continue;
+                    const uint32_t cap_tiles = std::max<uint32_t>(static_cast<uint32_t>(static_cast<uint64_t>(fair) * cut_pct / 100 * mult / 100), 2 * UW);
+                    if (cap_tiles == last_cap || units.front().first <= cap_tiles + cap_tiles / 4) continue;
+                    last_cap = cap_tiles;
+                    pack(cap_tiles, trial);
+                    const double t_cut = std::max(trial.critical * 1e-3, t_stream) + 2.0;
+                    if (trial.n_cut && t_cut < best) {
+                        best = t_cut;
+                        std::swap(cut, trial);
+                        chosen = &cut;
+                        t_unit = t_cut;
+                    }
+                }
+            }
             const uint32_t n_hb_e = static_cast<uint32_t>((k.KVH + kDecodeWarps - 1) / kDecodeWarps);
             const double hb_tiles = static_cast<double>(head_tiles) / k.KVH * n_hb_e;      // tiles of the split form
             const double per_cta = std::max(1.0, hb_tiles / cta_cap);
@@ -200,25 +273,38 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         if (unit_mode) {
             // the exchange area of the in-CTA merge must fit beside the rings
             while (stages > 1 && decode_tma_smem_bytes(k.D, k.H / k.KVH > 8, stages, true) > 227 * 1024 - 1024) --stages;  // 1 KiB for the barriers
-            n_cta = n_cta_u;
-            const uint32_t UW = static_cast<uint32_t>(unit_warps(k.D));
+            const Packing& pk = *chosen;
+            n_cta = pk.n_cta;
             n_slices = n_cta * UW;
-            cta_pieces.reset(n_slices, units.size() * UW);
+            n_unit_cuts = pk.n_cut;
+            n_slots = (pk.n_parts_total + kDecodeWarps - 1) / kDecodeWarps;   // the workspace is sized in groups of kDecodeWarps parts
+            std::vector<uint32_t> cut_first_slot(pk.n_cut + 1, 0);
+            for (const Item& it : pk.items)
+                if (it.n_parts > 1 && it.part == 0) cut_first_slot[it.cut + 1] = it.n_parts;
+            for (uint32_t i = 0; i < pk.n_cut; ++i) cut_first_slot[i + 1] += cut_first_slot[i];
+            cta_pieces.reset(n_slices, pk.items.size() * UW);
             cta_tiles.reset(n_slices, static_cast<size_t>(head_tiles) + n_slices);
             for (uint32_t c = 0; c < n_cta; ++c) {
                 for (uint32_t w = 0; w < UW; ++w) {
                     const uint32_t slice = c * UW + w;
-                    for (uint32_t id : cta_units[c]) {
-                        const size_t r = id / k.KVH;
-                        const uint32_t h = static_cast<uint32_t>(id % k.KVH);
-                        const uint32_t T = (eff[r] + TOKu - 1) / TOKu, quarter = (T + UW - 1) / UW;
-                        const uint32_t lo = std::min(w * quarter, T), hi = std::min((w + 1) * quarter, T);
+                    for (uint32_t ii : pk.cta_items[c]) {
+                        const Item& it = pk.items[ii];
+                        const size_t r = it.id / k.KVH;
+                        const uint32_t h = static_cast<uint32_t>(it.id % k.KVH);
+                        const uint32_t T = (eff[r] + TOKu - 1) / TOKu;       // tiles of the whole unit
+                        const uint32_t run = it.hi - it.lo, share = (run + UW - 1) / UW;
+                        const uint32_t lo = it.lo + std::min(w * share, run), hi = it.lo + std::min((w + 1) * share, run);
                         PieceDesc d{};
                         d.req = static_cast<uint32_t>(r);
                         d.hb = static_cast<uint16_t>(h);   // the KV head itself
                         d.tile_begin = lo;
                         d.n_tiles = hi - lo;
-                        d.n_parts = 1;
+                        d.n_parts = static_cast<uint16_t>(it.n_parts);
+                        if (it.n_parts > 1) {
+                            d.seg = it.cut;
+                            d.seg_first_slot = cut_first_slot[it.cut];
+                            d.part_slot = cut_first_slot[it.cut] + it.part;
+                        }
                         const bool has_last = hi == T && hi > lo;
                         d.last_valid = static_cast<uint16_t>(has_last ? eff[r] - (T - 1) * TOKu : TOKu);
                         d.flags = (fusable && has_last) ? 1u : 0u;
@@ -378,6 +464,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     v.n_zero = static_cast<uint32_t>(zero_rows.size());
     v.n_slots = n_slots;
     v.n_segs = n_segs;
+    v.n_unit_cuts = n_unit_cuts;
     p.d_page_ids = page_ids ? reinterpret_cast<const uint32_t*>(p.dev + off_ids) : nullptr;
     p.d_slots = slots ? reinterpret_cast<const uint32_t*>(p.dev + off_slots) : nullptr;
     return MLC_OK;

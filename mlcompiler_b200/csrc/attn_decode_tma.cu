@@ -58,6 +58,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <vector>
 
 #include "attn_internal.hpp"
@@ -181,6 +182,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: a poll that finds the phase open suspends for a few microseconds (measured ~4 us),
 // so 2^18 polls are about a second before giving up.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    {  // non-blocking test first: a phase that has already completed is the common case (measured ~0.5 % per layer)
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
     for (uint32_t i = 0; i < (1u << 18); ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
@@ -300,7 +310,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     constexpr int W = UNIT ? unit_warps(D) : kDecodeWarps;  // warps of this CTA
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[8][8];
+    __shared__ __align__(8) uint64_t bars[W][8];
+    __shared__ uint32_t last_part_flag;  // unit mode: this CTA brought the last piece of a (request, head) cut over CTAs
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = blockIdx.x;
@@ -711,16 +722,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     lstar[rs] += xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs + 1] * wk[k][rs];
                 }
             }
-#pragma unroll
-            for (int nn = 0; nn < NT_O / W; ++nn) {
-                const int n = nn * W + static_cast<int>(warp);  // this warp's output n-tiles
-                float acc[FR];
-#pragma unroll
-                for (int f = 0; f < FR; ++f) acc[f] = 0.f;
-#pragma unroll
-                for (int k = 0; k < W; ++k)
-#pragma unroll
-                    for (int f = 0; f < FR; ++f) acc[f] += xb[k * kXWarpFloats + (n * 32 + lane) * FR + f] * wk[k][f >> 1];
+            // Writes rows of O (or of the caller's partial output) for output n-tile n.
+            auto emit = [&](int n, const float (&acc)[FR], const float (&ls)[2]) {
 #pragma unroll
                 for (int rs = 0; rs < ROWSETS; ++rs) {
                     const uint32_t row = qrow + 8 * rs;
@@ -729,7 +732,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     if (prm.o_partial) {
                         *reinterpret_cast<float2*>(prm.o_partial + hrow * D + n * 8 + qcol) = make_float2(acc[2 * rs], acc[2 * rs + 1]);
                     } else {
-                        const float inv = lstar[rs] > 0.f ? 1.0f / lstar[rs] : 0.f;
+                        const float inv = ls[rs] > 0.f ? 1.0f / ls[rs] : 0.f;
                         if (prm.o_f32)
                             *reinterpret_cast<float2*>(static_cast<float*>(prm.o) + hrow * D + n * 8 + qcol) =
                                 make_float2(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
@@ -738,16 +741,109 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                                 __floats2half2_rn(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
                     }
                 }
-            }
-            if (prm.o_partial && warp == 0 && (lane & 3) == 0) {
+            };
+            auto emit_ml = [&](const float (&ms)[2], const float (&ls)[2]) {
+                if (prm.o_partial && warp == 0 && (lane & 3) == 0) {
 #pragma unroll
-                for (int rs = 0; rs < ROWSETS; ++rs) {
-                    const uint32_t row = qrow + 8 * rs;
-                    if (row >= prm.G) continue;
-                    const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
-                    prm.ml_partial[hrow * 2] = mstar[rs] * 0.6931471805599453f;   // natural-log units for the caller
-                    prm.ml_partial[hrow * 2 + 1] = lstar[rs];
+                    for (int rs = 0; rs < ROWSETS; ++rs) {
+                        const uint32_t row = qrow + 8 * rs;
+                        if (row >= prm.G) continue;
+                        const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
+                        prm.ml_partial[hrow * 2] = ms[rs] * 0.6931471805599453f;   // natural-log units for the caller
+                        prm.ml_partial[hrow * 2 + 1] = ls[rs];
+                    }
                 }
+            };
+            using FragT = typename std::conditional<G16, float4, float2>::type;
+#pragma unroll
+            for (int nn = 0; nn < (NT_O + W - 1) / W; ++nn) {
+                const int n = nn * W + static_cast<int>(warp);  // this warp's output n-tiles
+                if (NT_O % W != 0 && n >= NT_O) break;
+                float acc[FR];
+#pragma unroll
+                for (int f = 0; f < FR; ++f) acc[f] = 0.f;
+#pragma unroll
+                for (int k = 0; k < W; ++k)
+#pragma unroll
+                    for (int f = 0; f < FR; ++f) acc[f] += xb[k * kXWarpFloats + (n * 32 + lane) * FR + f] * wk[k][f >> 1];
+                if (n_parts > 1) {
+                    // a (request, head) cut over CTAs: this CTA's part goes to the workspace, fragment order
+                    FragT* wo = reinterpret_cast<FragT*>(prm.work_o) + (static_cast<size_t>(part_slot) * NT_O + n) * 32 + lane;
+                    if constexpr (G16) *wo = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    else *wo = make_float2(acc[0], acc[1]);
+                } else {
+                    emit(n, acc, lstar);
+                }
+            }
+            if (n_parts > 1) {
+                if (warp == 0) {
+                    FragT* wm = reinterpret_cast<FragT*>(prm.work_ml) + static_cast<size_t>(part_slot) * 32 + lane;
+                    if constexpr (G16) *wm = make_float4(mstar[0], lstar[0], mstar[1], lstar[1]);
+                    else *wm = make_float2(mstar[0], lstar[0]);
+                }
+                // Publish and count: the CTA meets (its stores then happen before whatever thread 0 does next),
+                // thread 0 adds 1 to the (request, head)'s counter with release + acquire semantics at GPU
+                // scope - cumulative, so the whole CTA's stores are visible to whoever sees the count, and the
+                // other parts' stores to this CTA after the second barrier. Whoever brings the last part
+                // combines all of them; nobody waits for another CTA. The last arrival also puts the counter
+                // back to 0 for the next launch (which cannot touch it before this grid has ended: its
+                // arrivals come after griddepcontrol.wait).
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+                if (threadIdx.x == 0) {
+                    uint32_t* c = prm.seg_counters + d1.y;
+                    uint32_t before;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(c) : "memory");
+                    const bool last = before + 1 == n_parts;
+                    if (last) *c = 0u;
+                    last_part_flag = last ? 1u : 0u;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+                if (last_part_flag) {
+                    const uint32_t first_slot = d1.x;
+                    const FragT* pm = reinterpret_cast<const FragT*>(prm.work_ml) + static_cast<size_t>(first_slot) * 32 + lane;
+                    float ms[2] = {-INFINITY, -INFINITY}, ls[2] = {0.f, 0.f};
+                    for (uint32_t k = 0; k < n_parts; ++k) {
+                        const FragT v = __ldcg(pm + k * 32);
+                        ms[0] = fmaxf(ms[0], v.x);
+                        if constexpr (G16) ms[1] = fmaxf(ms[1], v.z);
+                    }
+#pragma unroll
+                    for (int nn = 0; nn < (NT_O + W - 1) / W; ++nn) {
+                        const int n = nn * W + static_cast<int>(warp);
+                        if (NT_O % W != 0 && n >= NT_O) break;
+                        float acc[FR];
+#pragma unroll
+                        for (int f = 0; f < FR; ++f) acc[f] = 0.f;
+                        ls[0] = ls[1] = 0.f;
+                        const FragT* po = reinterpret_cast<const FragT*>(prm.work_o) + (static_cast<size_t>(first_slot) * NT_O + n) * 32 + lane;
+#pragma unroll 4
+                        for (uint32_t k = 0; k < n_parts; ++k) {
+                            const FragT mv = __ldcg(pm + k * 32);
+                            const FragT ov = __ldcg(po + static_cast<size_t>(k) * NT_O * 32);
+                            const float w0 = (mv.x == -INFINITY) ? 0.f : ex2(mv.x - ms[0]);
+                            ls[0] += mv.y * w0;
+                            acc[0] += ov.x * w0;
+                            acc[1] += ov.y * w0;
+                            if constexpr (G16) {
+                                const float w1 = (mv.z == -INFINITY) ? 0.f : ex2(mv.z - ms[1]);
+                                ls[1] += mv.w * w1;
+                                acc[2] += ov.z * w1;
+                                acc[3] += ov.w * w1;
+                            }
+                        }
+                        emit(n, acc, ls);
+                    }
+                    if (warp >= NT_O) {  // a warp without an output tile still needs the row sums for emit_ml
+                        for (uint32_t k = 0; k < n_parts; ++k) {
+                            const FragT mv = __ldcg(pm + k * 32);
+                            ls[0] += mv.y * ((mv.x == -INFINITY) ? 0.f : ex2(mv.x - ms[0]));
+                            if constexpr (G16) ls[1] += mv.w * ((mv.z == -INFINITY) ? 0.f : ex2(mv.z - ms[1]));
+                        }
+                    }
+                    emit_ml(ms, ls);
+                }
+            } else {
+                emit_ml(mstar, lstar);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");  // the exchange area is free for the next (request, head)
             if (pi == 0) stamp(4);
@@ -788,7 +884,19 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     if (UNIT && dead) {
         // this warp gave up on a copy: it still meets its CTA's two barriers per remaining piece
         for (; pi < n_pieces; ++pi) {
+            const uint4 dd = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi) + 1);
             asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            if ((dd.z & 0xffffu) > 1u) {  // a cut (request, head): the CTA still counts its arrival
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+                if (threadIdx.x == 0) {
+                    uint32_t* c = prm.seg_counters + dd.y;
+                    uint32_t before;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(c) : "memory");
+                    if (before + 1 == (dd.z & 0xffffu)) *c = 0u;
+                    last_part_flag = 0u;  // nothing is combined from a piece that gave up
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            }
             asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
         }
     }
@@ -1009,18 +1117,23 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     char* work = nullptr;
     uint32_t parity = 0;
     bool use_counters = false;
+    uint32_t* ext_counters = nullptr;
     if (a.ext_work) {
         // Caller-provided workspace: nothing is allocated on this path, neither on the
         // device nor (the tensor maps are encoded on the stack, uncached) on the host.
         const size_t half = a.ext_work_bytes / 2 / 256 * 256;
-        if (o_bytes + ml_bytes > half)
+        // arrival counters of cut units live behind the partials; the scratch starts zeroed and every
+        // launch leaves them at zero
+        const size_t cnt_bytes = ((static_cast<size_t>(plan.n_unit_cuts) * 4 + 255) / 256) * 256;
+        if (o_bytes + ml_bytes + cnt_bytes > half)
             return ctx->fail(MLC_ERR_UNSUPPORTED,
                              "this batch needs %zu bytes of split-KV scratch per copy, the fixed scratch holds %zu",
-                             o_bytes + ml_bytes, half);
+                             o_bytes + ml_bytes + cnt_bytes, half);
         if ((st = encode_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
         if ((st = encode_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
         parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
         work = static_cast<char*>(a.ext_work) + parity * half;
+        ext_counters = reinterpret_cast<uint32_t*>(work + o_bytes + ml_bytes);
     } else {
         // MLC_B200_DECODE_INKERNEL_MERGE=1: merge inside the attention kernel (arrival counters
         // [n_segs][warps], mergers poll) instead of the chained merge kernel. Measured on cfg2 it is
@@ -1032,7 +1145,7 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
         }();
         use_counters = !merge_kernel && plan.n_segs > 0;
         st = ensure_workspace(ctx, 2 * (o_bytes + ml_bytes) + 512,
-                              use_counters ? static_cast<size_t>(plan.n_segs) * kDecodeWarps : 0);
+                              use_counters ? static_cast<size_t>(plan.n_segs) * kDecodeWarps : plan.n_unit_cuts);
         if (st != MLC_OK) return st;
         if ((st = get_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
         if ((st = get_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
@@ -1073,6 +1186,7 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     prm.pdl = 1;
     prm.stages = plan.stages;
     prm.seg_counters = use_counters ? ctx->d_counters : nullptr;
+    if (plan.unit_mode && plan.n_unit_cuts) prm.seg_counters = ext_counters ? ext_counters : ctx->d_counters;
     prm.n_segs = plan.n_segs;
     // traces of consecutive launches alternate between the two halves of the buffer
     const size_t trace_need = static_cast<size_t>(plan.n_cta) * (plan.unit_mode ? unit_warps(a.D) : kDecodeWarps) * 8;

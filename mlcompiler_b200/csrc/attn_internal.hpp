@@ -41,7 +41,10 @@ static constexpr int kDecodeWarps = 4;   // KV heads per head block = warps per 
 static constexpr int kTileTokens = 32;   // tokens per pipeline stage
 // Warps of a CTA in unit mode: with one KV head per CTA a warp's tile costs ~0.8 us of dependent
 // work, so the longest (request, head) is cut into more parts where shared memory allows.
-constexpr int unit_warps(size_t head_dim) { return head_dim == 64 ? 8 : 4; }
+#ifndef MLCB_UNIT_WARPS_D64
+#define MLCB_UNIT_WARPS_D64 8
+#endif
+constexpr int unit_warps(size_t head_dim) { return head_dim == 64 ? MLCB_UNIT_WARPS_D64 : 4; }
 // Tile word: page id | sub-tile within the page | head block | "holds this step's new token".
 static constexpr uint32_t kTilePageMask = (1u << 22) - 1;
 static constexpr uint32_t kTileSubShift = 22;
@@ -82,6 +85,7 @@ struct DecodePlanView {            // device addresses inside one plan blob
     uint32_t stages = 3;           // ring depth the plan was cut for
     uint32_t n_cta = 0, max_pieces = 0, max_tiles = 0, n_zero = 0;
     uint32_t n_slots = 0, n_segs = 0;
+    uint32_t n_unit_cuts = 0;      // unit mode: (request, head) units cut over CTAs, one arrival counter each
 };
 
 int launch_attention_general(mlc_ctx* ctx, const AttnArgs& a, const uint32_t* d_pt_flat,

@@ -1,7 +1,8 @@
-"""The decode kernel has two decompositions (split over CTAs + merge kernel, and whole (request, head)
-units per CTA) and the planner picks one per batch. These tests run the attention and planned-call
-parity suites again with each form forced (MLC_B200_DECODE_MODE=1 / 2), so that neither depends on what
-the planner happens to choose for a test's batch shape."""
+"""The decode kernel has two decompositions (split over CTAs + merge kernel, and (request, head) units
+per CTA, whole or - when one dwarfs the rest - cut into runs that are combined by the last CTA to
+arrive) and the planner picks one per batch. These tests run the attention and planned-call parity
+suites again with each form forced (MLC_B200_DECODE_MODE=1 / 2, units never cut / cut at half the fair
+share), so that none depends on what the planner happens to choose for a test's batch shape."""
 import os
 import subprocess
 import sys
@@ -13,9 +14,16 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("mode,name", [("1", "split"), ("2", "unit")])
-def test_parity_suites_with_the_decomposition_forced(mode, name):
-    env = dict(os.environ, MLC_B200_DECODE_MODE=mode)
+FORCED = [
+    ("split", {"MLC_B200_DECODE_MODE": "1"}),
+    ("unit", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "0"}),
+    ("unit_cut", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "50", "MLC_B200_DECODE_UNIT_CUT_FORCE": "1"}),
+]
+
+
+@pytest.mark.parametrize("name,forced", FORCED, ids=[f[0] for f in FORCED])
+def test_parity_suites_with_the_decomposition_forced(name, forced):
+    env = dict(os.environ, **forced)
     r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
                         "tests/test_gpu_attention.py", "tests/test_gpu_planned.py", "tests/test_gpu_walker.py",
                         "-k", "not in_kernel_merge"],
@@ -24,8 +32,9 @@ def test_parity_suites_with_the_decomposition_forced(mode, name):
 
 
 def test_planner_choice_follows_the_batch_shape():
-    """Balanced batches run as whole units (one launch per layer); a batch dominated by one long request
-    is split over CTAs (attention + merge kernel)."""
+    """Balanced batches run as whole units, a batch dominated by one long request has that request's units
+    cut over CTAs - one launch per layer either way; the split form (attention + merge kernel) is what
+    MLC_B200_DECODE_MODE=1 gives."""
     import numpy as np
     import torch
     from mlcompiler_b200 import Executor, synth
@@ -49,5 +58,10 @@ def test_planner_choice_follows_the_batch_shape():
         return n
 
     assert launches(np.random.default_rng(1).integers(64, 2049, 32)) == 1
-    assert launches(np.array([16384] + [256] * 31)) == 2
+    assert launches(np.array([16384] + [256] * 31)) == 1
+    os.environ["MLC_B200_DECODE_MODE"] = "1"
+    try:
+        assert launches(np.array([16384] + [256] * 31)) == 2
+    finally:
+        del os.environ["MLC_B200_DECODE_MODE"]
     ex.close()

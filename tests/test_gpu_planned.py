@@ -61,6 +61,11 @@ STEP_CASES = [
     ("g16_d128", lambda: synth.make_case(34, [100, 257, 33], 32, 2, 128)),
     ("kvh6", lambda: synth.make_case(35, [100, 257, 5], 12, 6, 64)),
     ("page128", lambda: synth.make_case(36, [100, 257, 129, 128], 32, 4, 64, P=128)),
+    # one request dwarfs the others: the planner cuts its (request, head) units over CTAs
+    ("longtail", lambda: synth.make_case(37, [16384, 256, 31, 256], 32, 4, 64)),
+    ("lone_long", lambda: synth.make_case(38, [5000], 32, 4, 64)),
+    ("longtail_d128", lambda: synth.make_case(39, [9000, 100, 70], 32, 8, 128)),
+    ("longtail_g16", lambda: synth.make_case(40, [8001, 64], 32, 2, 64)),
 ]
 
 
