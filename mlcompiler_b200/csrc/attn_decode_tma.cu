@@ -296,7 +296,7 @@ __device__ __forceinline__ void merge_segment(const DecodeParams& prm, const Seg
 // needs ~0.8 us per 32-token tile (dependent mma.sync / ldmatrix / shuffle chains, one warp per
 // scheduler), so the longest unit's time falls with the number of warps that share it.
 template <int D, bool G16, bool UNIT>
-__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32)
+__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32, 1)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const DecodeParams prm) {
     constexpr int TOK = kTileTokens;
@@ -801,44 +801,62 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 if (last_part_flag) {
                     const uint32_t first_slot = d1.x;
                     const FragT* pm = reinterpret_cast<const FragT*>(prm.work_ml) + static_cast<size_t>(first_slot) * 32 + lane;
+                    // One pass over the parts in slot order (the result does not depend on who arrived last),
+                    // running maximum as in the tile loop: the (m, l) and the o fragments of a part are loaded
+                    // together, so the pass costs one trip to L2 per few parts rather than two.
+                    constexpr int NN = (NT_O + W - 1) / W;   // output n-tiles of this warp
                     float ms[2] = {-INFINITY, -INFINITY}, ls[2] = {0.f, 0.f};
-                    for (uint32_t k = 0; k < n_parts; ++k) {
-                        const FragT v = __ldcg(pm + k * 32);
-                        ms[0] = fmaxf(ms[0], v.x);
-                        if constexpr (G16) ms[1] = fmaxf(ms[1], v.z);
-                    }
+                    float cacc[NN][FR];
 #pragma unroll
-                    for (int nn = 0; nn < (NT_O + W - 1) / W; ++nn) {
-                        const int n = nn * W + static_cast<int>(warp);
-                        if (NT_O % W != 0 && n >= NT_O) break;
-                        float acc[FR];
+                    for (int nn = 0; nn < NN; ++nn)
 #pragma unroll
-                        for (int f = 0; f < FR; ++f) acc[f] = 0.f;
-                        ls[0] = ls[1] = 0.f;
-                        const FragT* po = reinterpret_cast<const FragT*>(prm.work_o) + (static_cast<size_t>(first_slot) * NT_O + n) * 32 + lane;
-#pragma unroll 4
-                        for (uint32_t k = 0; k < n_parts; ++k) {
-                            const FragT mv = __ldcg(pm + k * 32);
-                            const FragT ov = __ldcg(po + static_cast<size_t>(k) * NT_O * 32);
-                            const float w0 = (mv.x == -INFINITY) ? 0.f : ex2(mv.x - ms[0]);
-                            ls[0] += mv.y * w0;
-                            acc[0] += ov.x * w0;
-                            acc[1] += ov.y * w0;
-                            if constexpr (G16) {
-                                const float w1 = (mv.z == -INFINITY) ? 0.f : ex2(mv.z - ms[1]);
-                                ls[1] += mv.w * w1;
-                                acc[2] += ov.z * w1;
-                                acc[3] += ov.w * w1;
+                        for (int f = 0; f < FR; ++f) cacc[nn][f] = 0.f;
+                    const FragT* po = reinterpret_cast<const FragT*>(prm.work_o) + (static_cast<size_t>(first_slot) * NT_O + warp) * 32 + lane;
+                    // the loads of CHUNK parts are issued before the first is used (each is a trip to L2)
+                    constexpr int kPartFloats = FR * (1 + NN);
+                    constexpr int CHUNK = 48 / kPartFloats >= 8 ? 8 : (48 / kPartFloats >= 4 ? 4 : 2);
+                    for (uint32_t k0 = 0; k0 < n_parts; k0 += CHUNK) {
+                        FragT mv[CHUNK], ov[CHUNK][NN];
+#pragma unroll
+                        for (int i = 0; i < CHUNK; ++i) {
+                            const uint32_t k = k0 + i;
+                            const bool valid = k < n_parts;
+                            mv[i] = FragT{};
+                            if (valid) mv[i] = __ldcg(pm + k * 32);
+                            else mv[i].x = -INFINITY;   // skipped below
+                            if constexpr (G16) { if (!valid) reinterpret_cast<float*>(&mv[i])[2] = -INFINITY; }
+#pragma unroll
+                            for (int nn = 0; nn < NN; ++nn) {
+                                const int n = nn * W + static_cast<int>(warp);
+                                ov[i][nn] = FragT{};
+                                if (valid && (NT_O % W == 0 || n < NT_O)) ov[i][nn] = __ldcg(po + (static_cast<size_t>(k) * NT_O + nn * W) * 32);
                             }
                         }
-                        emit(n, acc, ls);
-                    }
-                    if (warp >= NT_O) {  // a warp without an output tile still needs the row sums for emit_ml
-                        for (uint32_t k = 0; k < n_parts; ++k) {
-                            const FragT mv = __ldcg(pm + k * 32);
-                            ls[0] += mv.y * ((mv.x == -INFINITY) ? 0.f : ex2(mv.x - ms[0]));
-                            if constexpr (G16) ls[1] += mv.w * ((mv.z == -INFINITY) ? 0.f : ex2(mv.z - ms[1]));
+#pragma unroll
+                        for (int i = 0; i < CHUNK; ++i) {
+#pragma unroll
+                            for (int rs = 0; rs < ROWSETS; ++rs) {
+                                const float mk = reinterpret_cast<const float*>(&mv[i])[2 * rs];
+                                const float lk = reinterpret_cast<const float*>(&mv[i])[2 * rs + 1];
+                                if (mk == -INFINITY) continue;   // a part without a valid token (or past the end) weighs nothing
+                                const float m_new = fmaxf(ms[rs], mk);
+                                const float alpha = ex2(ms[rs] - m_new), w = ex2(mk - m_new);   // ex2(-inf) = 0 for the first part
+                                ms[rs] = m_new;
+                                ls[rs] = ls[rs] * alpha + lk * w;
+#pragma unroll
+                                for (int nn = 0; nn < NN; ++nn) {
+                                    const float* o2 = reinterpret_cast<const float*>(&ov[i][nn]) + 2 * rs;
+                                    cacc[nn][2 * rs] = cacc[nn][2 * rs] * alpha + o2[0] * w;
+                                    cacc[nn][2 * rs + 1] = cacc[nn][2 * rs + 1] * alpha + o2[1] * w;
+                                }
+                            }
                         }
+                    }
+#pragma unroll
+                    for (int nn = 0; nn < NN; ++nn) {
+                        const int n = nn * W + static_cast<int>(warp);
+                        if (NT_O % W != 0 && n >= NT_O) break;
+                        emit(n, cacc[nn], ls);
                     }
                     emit_ml(ms, ls);
                 }
