@@ -71,6 +71,7 @@ namespace mlcb {
 struct TensorMapCache {
     struct Entry {
         const void* pool;
+        const void* pool2;   // second pool of a K/V pair map, else null
         size_t D, KVH, P, capacity;
         CUtensorMap map;
     };
@@ -110,16 +111,45 @@ static int encode_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, 
     return MLC_OK;
 }
 
-static int get_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, CUtensorMap* out) {
+// One map over both pools of a layer: a fifth dimension of extent 2 whose stride is the distance between
+// the pools, so that one TMA instruction fetches the K tile and the V tile of a stage (a TMA instruction
+// costs the issuing lane 75-95 clocks, measured). The lower pool is index 0. Possible when the pools do
+// not coincide and their distance is a multiple of 16 bytes below 2^40 (the tensor-map stride rules).
+static bool pair_map_possible(const void* k_pool, const void* v_pool) {
+    const uintptr_t k = reinterpret_cast<uintptr_t>(k_pool), v = reinterpret_cast<uintptr_t>(v_pool);
+    const uintptr_t dist = k < v ? v - k : k - v;
+    return dist != 0 && dist % 16 == 0 && dist < (uintptr_t(1) << 40);
+}
+static int encode_pair_map(mlc_ctx* ctx, const void* k_pool, const void* v_pool, const AttnArgs& a, CUtensorMap* out) {
+    if (!ctx->tmap_encode_fn) {
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->tmap_encode_fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !ctx->tmap_encode_fn)
+            return ctx->fail(MLC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    }
+    const uintptr_t k = reinterpret_cast<uintptr_t>(k_pool), v = reinterpret_cast<uintptr_t>(v_pool);
+    cuuint64_t dims[5] = {a.D, a.KVH, a.P, a.capacity, 2};
+    cuuint64_t strides[4] = {a.D * 2, a.KVH * a.D * 2, a.P * a.KVH * a.D * 2, k < v ? v - k : k - v};
+    cuuint32_t box[5] = {64, 1, static_cast<cuuint32_t>(kTileTokens), 1, 2};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode_fn)(
+        out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, reinterpret_cast<void*>(k < v ? k : v), dims, strides, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ctx->fail(MLC_ERR_CUDA, "cuTensorMapEncodeTiled (K/V pair) failed (%d)", static_cast<int>(r));
+    return MLC_OK;
+}
+
+static int get_tensor_map(mlc_ctx* ctx, const void* pool, const AttnArgs& a, CUtensorMap* out, const void* pool2 = nullptr) {
     if (!ctx->tmap_cache) ctx->tmap_cache = new TensorMapCache();
     TensorMapCache& tc = *ctx->tmap_cache;
     for (auto& e : tc.entries)
-        if (e.pool == pool && e.D == a.D && e.KVH == a.KVH && e.P == a.P && e.capacity == a.capacity) {
+        if (e.pool == pool && e.pool2 == pool2 && e.D == a.D && e.KVH == a.KVH && e.P == a.P && e.capacity == a.capacity) {
             *out = e.map;
             return MLC_OK;
         }
-    TensorMapCache::Entry e{pool, a.D, a.KVH, a.P, a.capacity, {}};
-    int st = encode_tensor_map(ctx, pool, a, &e.map);
+    TensorMapCache::Entry e{pool, pool2, a.D, a.KVH, a.P, a.capacity, {}};
+    int st = pool2 ? encode_pair_map(ctx, pool, pool2, a, &e.map) : encode_tensor_map(ctx, pool, a, &e.map);
     if (st != MLC_OK) return st;
     if (tc.entries.size() >= 256) tc.entries.erase(tc.entries.begin());
     tc.entries.push_back(e);
@@ -159,6 +189,9 @@ struct DecodeParams {
     // In-kernel merge: one arrival counter per (split segment, warp); null = a merge kernel follows.
     uint32_t* seg_counters;
     uint32_t n_segs;
+    // head_dim 64: the first tensor map covers both pools (one TMA instruction per stage); k_off / v_off are
+    // the tiles' byte offsets inside a stage (the lower pool comes first)
+    uint32_t kv_pair, k_off, v_off;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -201,6 +234,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
@@ -362,7 +403,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     auto issue_word = [&](uint32_t e) {
         const uint32_t hfield = (e >> kTileHbShift) & kTileHbMask;   // head block, or the head itself in unit mode
         const uint32_t head = UNIT ? hfield : hfield * kDecodeWarps + warp;
-        if (head >= prm.KVH) return;  // this warp has no KV head in that head block
+        if (!UNIT && head >= prm.KVH) return;  // this warp has no KV head in that head block
         const uint32_t s = iss_stage;
         iss_stage = (iss_stage + 1 == stages) ? 0u : iss_stage + 1;
         if (lane == 0) {
@@ -372,10 +413,14 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             const int slot0 = static_cast<int>(((e >> kTileSubShift) & 7u) * TOK);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(bar, kStageBytes);
+            if (D == 64 && prm.kv_pair) {
+                tma_load_5d(dst, &tmK, bar, 0, static_cast<int>(head), slot0, page, 0);
+            } else {
 #pragma unroll
-            for (int sub = 0; sub < SUBS; ++sub) {
-                tma_load_4d(dst + sub * (TOK * 128), &tmK, bar, sub * 64, static_cast<int>(head), slot0, page);
-                tma_load_4d(dst + kTileBytes + sub * (TOK * 128), &tmV, bar, sub * 64, static_cast<int>(head), slot0, page);
+                for (int sub = 0; sub < SUBS; ++sub) {
+                    tma_load_4d(dst + sub * (TOK * 128), &tmK, bar, sub * 64, static_cast<int>(head), slot0, page);
+                    tma_load_4d(dst + kTileBytes + sub * (TOK * 128), &tmV, bar, sub * 64, static_cast<int>(head), slot0, page);
+                }
             }
         }
     };
@@ -533,7 +578,10 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 break;
             }
             if (j == 0) stamp(2);
-            const uint32_t sK = ring + s * kStageBytes, sV = sK + kTileBytes;
+            // the next tile word to fetch, taken now so that its shuffle (and every 32nd time the load of
+            // the next window) is long done when lane 0 needs it at the end of the tile
+            const uint32_t e_next = next_issue < n_tiles ? tile_entry(next_issue) : 0u;
+            const uint32_t sK = ring + s * kStageBytes + prm.k_off, sV = ring + s * kStageBytes + prm.v_off;
             const bool last_tile = t + 1 == piece_tiles;
             const uint32_t nv = last_tile ? last_valid : TOK;
 
@@ -672,7 +720,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
             __syncwarp();
             if (next_issue < n_tiles) {
-                issue_word(tile_entry(next_issue));
+                issue_word(e_next);
                 ++next_issue;
             }
         }
@@ -1136,6 +1184,12 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     uint32_t parity = 0;
     bool use_counters = false;
     uint32_t* ext_counters = nullptr;
+    // MLC_B200_DECODE_KV_PAIR=0 keeps one TMA instruction per pool
+    static const bool pair_allowed = [] {
+        const char* v = std::getenv("MLC_B200_DECODE_KV_PAIR");
+        return !(v && *v && std::atoi(v) == 0);
+    }();
+    const bool kv_pair = pair_allowed && a.D == 64 && pair_map_possible(a.k_pages, a.v_pages);
     if (a.ext_work) {
         // Caller-provided workspace: nothing is allocated on this path, neither on the
         // device nor (the tensor maps are encoded on the stack, uncached) on the host.
@@ -1147,8 +1201,13 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
             return ctx->fail(MLC_ERR_UNSUPPORTED,
                              "this batch needs %zu bytes of split-KV scratch per copy, the fixed scratch holds %zu",
                              o_bytes + ml_bytes + cnt_bytes, half);
-        if ((st = encode_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
-        if ((st = encode_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
+        if (kv_pair) {
+            if ((st = encode_pair_map(ctx, a.k_pages, a.v_pages, a, &mk)) != MLC_OK) return st;
+            mv = mk;
+        } else {
+            if ((st = encode_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
+            if ((st = encode_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
+        }
         parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
         work = static_cast<char*>(a.ext_work) + parity * half;
         ext_counters = reinterpret_cast<uint32_t*>(work + o_bytes + ml_bytes);
@@ -1165,8 +1224,13 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
         st = ensure_workspace(ctx, 2 * (o_bytes + ml_bytes) + 512,
                               use_counters ? static_cast<size_t>(plan.n_segs) * kDecodeWarps : plan.n_unit_cuts);
         if (st != MLC_OK) return st;
-        if ((st = get_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
-        if ((st = get_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
+        if (kv_pair) {
+            if ((st = get_tensor_map(ctx, a.k_pages, a, &mk, a.v_pages)) != MLC_OK) return st;
+            mv = mk;
+        } else {
+            if ((st = get_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
+            if ((st = get_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
+        }
         parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
         work = static_cast<char*>(ctx->d_work) + parity * (ctx->work_bytes / 2 / 256 * 256);
     }
@@ -1206,6 +1270,13 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     prm.seg_counters = use_counters ? ctx->d_counters : nullptr;
     if (plan.unit_mode && plan.n_unit_cuts) prm.seg_counters = ext_counters ? ext_counters : ctx->d_counters;
     prm.n_segs = plan.n_segs;
+    {
+        const uint32_t tile_bytes = static_cast<uint32_t>(kTileTokens * a.D * 2);
+        const bool k_first = !kv_pair || reinterpret_cast<uintptr_t>(a.k_pages) < reinterpret_cast<uintptr_t>(a.v_pages);
+        prm.kv_pair = kv_pair ? 1u : 0u;
+        prm.k_off = k_first ? 0u : tile_bytes;
+        prm.v_off = k_first ? tile_bytes : 0u;
+    }
     // traces of consecutive launches alternate between the two halves of the buffer
     const size_t trace_need = static_cast<size_t>(plan.n_cta) * (plan.unit_mode ? unit_warps(a.D) : kDecodeWarps) * 8;
     prm.trace = ctx->d_trace && trace_need <= ctx->trace_words / 2 ? ctx->d_trace + parity * (ctx->trace_words / 2) : nullptr;

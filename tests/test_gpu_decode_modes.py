@@ -15,7 +15,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 FORCED = [
-    ("split", {"MLC_B200_DECODE_MODE": "1"}),
+    # the split form, and one TMA instruction per pool instead of one per K/V pair
+    ("split", {"MLC_B200_DECODE_MODE": "1", "MLC_B200_DECODE_KV_PAIR": "0"}),
     ("unit", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "0"}),
     ("unit_cut", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "50", "MLC_B200_DECODE_UNIT_CUT_FORCE": "1"}),
 ]
