@@ -10,16 +10,19 @@ over per-layer pools sized to the total pages + 10 %. One step = for every layer
 write one new K/V row per request into the pool, then run attention.
 
 `value` is KV GB/s with everything resident in HBM: the step is replayed from a
-CUDA graph (per layer one attention kernel with the KV row write fused in, plus its
-merge kernel for requests split over CTAs; consecutive kernels overlap by programmatic
-dependent launch) and timed with CUDA events on the launching stream. `e2e` is the
-same metric through the C ABI with host buffers, the call sequence a walker makes:
-every step copies Q and the new K/V rows from pinned host memory, hands the step's
-page tables / lengths / positions / (page, slot) pairs over as host arrays (they grow
-by one token per step, as in serving) with one in-place plan update, issues the pass
-(one fused scatter + attention launch per layer) with one call, and copies the attention output back. With N > 1
-(torchrun, one rank per GPU) every rank runs its own
-32-request batch: request sharding, no collective on the data path (weak scaling).
+CUDA graph (per layer one attention kernel with the KV row write and the merge fused
+in; consecutive kernels overlap by programmatic dependent launch) and timed with CUDA
+events on the launching stream. `e2e` is the same metric through the C ABI with host
+buffers, the call sequence a walker with host activations makes: every step one
+host-buffer pass call (Q and the new K/V rows of all layers copied in from pinned host
+memory, one fused launch per layer, the attention output copied back to pinned host
+memory, copies and kernels pipelined over groups of layers inside the call) and one
+in-place plan update that hands over the NEXT step's page tables / lengths / positions
+/ (page, slot) pairs as host arrays (they grow by one token per step, as in serving, and
+do not depend on this step's results) while this step runs; the flush returns when the
+output is complete in host memory. With N > 1 (torchrun, one rank per GPU) every rank
+runs its own 32-request batch: request sharding, no collective on the data path (weak
+scaling).
 
 `--impl reference` times MLcompiler's own executor-CPU attention (compiled from
 its unmodified sources into oracle/_ref, else the C port of it) on the host cores.
@@ -49,7 +52,7 @@ WORKLOAD = ("cfg2: 22-layer continuous-batching decode, 32 requests, H32/KVH4/D6
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel on this workload
 # (37.79 MB read + <= 1.5 KB written), from the ncu captures summarised in
 # profiles/decode_attention_cfg2.md; the algorithmic KV bytes of that launch are 37.00 MB.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 37_794_560
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 37_793_792
 
 
 def measured_peak_gbs():
