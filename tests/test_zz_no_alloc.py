@@ -19,9 +19,19 @@ from tests.util import MAX_ABS, DeviceCase
 pytestmark = pytest.mark.gpu
 
 
-def test_static_scratch_matches_planned_attention_twice(executor):
+CASES = [
+    ("cfg2", lambda: synth.config_case(2)),
+    # one request dwarfs the rest: its (request, head) units are cut over CTAs, so the partials and the
+    # arrival counters in the fixed array are really used (and must be left at zero for the second call)
+    ("longtail", lambda: synth.make_case(11, [12000, 300, 64, 700], 32, 4, 64)),
+    ("longtail_d128", lambda: synth.make_case(12, [7000, 90], 32, 8, 128)),
+]
+
+
+@pytest.mark.parametrize("name,build", CASES, ids=[c[0] for c in CASES])
+def test_static_scratch_matches_planned_attention_twice(executor, name, build):
     import torch
-    case = synth.config_case(2)          # every long request is split, so the scratch is really used
+    case = build()
     dc = DeviceCase(case)
     plan = executor.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, case.N, case.H, case.KVH,
                                case.D, case.P, True, case.capacity)
