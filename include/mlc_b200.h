@@ -309,8 +309,11 @@ int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
  *   dev_in   device staging buffer of the same size, caller-owned
  *   dev_o / host_o  [n_layers][batch][H][D] of o_dtype on the device and in host memory
  * The layers go in n_groups groups (0 = 5): group g's rows are copied on a copy stream while group
- * g-1 computes, its O rows go back on another stream while group g+1 computes. The context's stream
- * is made to wait for the last copy back, so mlc_pass_flush returns when host_o is complete.
+ * g-1 computes, its O rows go back on another stream while group g+1 computes. mlc_pass_flush waits
+ * for the last copy back as well as for the context's stream: host_o is complete when it returns (the
+ * stream itself is not held up by that copy, so an upload queued next - mlc_attn_plan_update for the
+ * following step - runs beside it; a second host-buffer pass without a flush in between is ordered
+ * behind the first one's copies).
  * Not capturable (MLC_ERR_UNSUPPORTED between mlc_graph_begin_capture and _end_capture). The streams
  * and events are created on the first call. */
 int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, size_t n_layers,

@@ -795,6 +795,11 @@ int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, s
         ctx->pass_events.push_back(e);
     }
     cudaEvent_t ev_start = ctx->pass_events[2 * G], ev_done = ctx->pass_events[2 * G + 1];
+    // a previous host-buffer pass that was not flushed: its copies back still read dev_o
+    if (ctx->host_pass_done) {
+        MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->host_pass_done, 0));
+        ctx->host_pass_done = nullptr;
+    }
     // the staging buffer may still be read by kernels already in the stream
     MLCB_CUDA(ctx, cudaEventRecord(ev_start, ctx->stream));
     MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->h2d_stream, ev_start, 0));
@@ -820,9 +825,10 @@ int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, s
         MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ctx->pass_events[G + g], 0));
         MLCB_CUDA(ctx, cudaMemcpyAsync(hout + a * o_row, dout + a * o_row, (b - a) * o_row, cudaMemcpyDeviceToHost, ctx->d2h_stream));
     }
-    // the context's stream ends after the last copy back, so a flush covers the whole pass
+    // mlc_pass_flush waits for this event after the context's stream; the stream itself is not held
+    // up by the last copy back, so what the caller queues next (a plan update's upload) runs beside it
     MLCB_CUDA(ctx, cudaEventRecord(ev_done, ctx->d2h_stream));
-    MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ev_done, 0));
+    ctx->host_pass_done = ev_done;
     return MLC_OK;
 }
 

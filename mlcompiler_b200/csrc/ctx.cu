@@ -181,6 +181,7 @@ void mlc_ctx_destroy(mlc_ctx* ctx) {
     if (ctx->d_work) cudaFree(ctx->d_work);
     if (ctx->d_counters) cudaFree(ctx->d_counters);
     if (ctx->d_err) cudaFree(ctx->d_err);
+    if (ctx->h_err) cudaFreeHost(ctx->h_err);
     if (ctx->d_trace) cudaFree(ctx->d_trace);
     for (cudaEvent_t e : ctx->pass_events) cudaEventDestroy(e);
     if (ctx->h2d_stream) cudaStreamDestroy(ctx->h2d_stream);
@@ -286,11 +287,23 @@ int mlc_pass_flush(mlc_ctx* ctx) {
     if (!ctx->pass_open) return MLC_OK;  // the reference's flush is a no-op without an open CB
     DeviceGuard guard(ctx->device);
     ctx->pass_open = false;
+    // the error word travels behind the pass's kernels, so one synchronisation covers both
+    if (!ctx->h_err && cudaHostAlloc(reinterpret_cast<void**>(&ctx->h_err), 4, cudaHostAllocDefault) != cudaSuccess) ctx->h_err = nullptr;
+    bool word_queued = false;
+    if (ctx->h_err) {
+        *ctx->h_err = 0;
+        word_queued = cudaMemcpyAsync(ctx->h_err, ctx->d_err, 4, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess;
+    }
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess && ctx->host_pass_done) {  // copies back of a host-buffer pass run on their own stream
+        e = cudaEventSynchronize(ctx->host_pass_done);
+        ctx->host_pass_done = nullptr;
+    }
     stage_reset(ctx);
     if (e != cudaSuccess) return ctx->fail(MLC_ERR_CUDA, "pass failed: %s", cudaGetErrorString(e));
     uint32_t word = 0;
-    MLCB_CUDA(ctx, cudaMemcpy(&word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
+    if (word_queued) word = *ctx->h_err;
+    else MLCB_CUDA(ctx, cudaMemcpy(&word, ctx->d_err, 4, cudaMemcpyDeviceToHost));
     if (word) {
         reset_after_device_error(ctx);
         return ctx->fail(MLC_ERR_DEVICE_FLAG, "a kernel of this pass recorded error word 0x%x", word);

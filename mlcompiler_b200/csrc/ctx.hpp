@@ -47,6 +47,7 @@ struct mlc_ctx {
     std::unordered_map<std::string, std::pair<void*, size_t>> cached;
     std::vector<mlcb::StageChunk> stage;
     uint32_t* d_err = nullptr;  // device error word
+    uint32_t* h_err = nullptr;  // pinned copy, filled by an async copy in front of the flush's synchronisation
     // split-KV workspace (partials + arrival counters), grown on demand
     void* d_work = nullptr;
     size_t work_bytes = 0;
@@ -57,6 +58,7 @@ struct mlc_ctx {
     // copy streams and events of the host-buffer decode pass (created on first use)
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
     std::vector<cudaEvent_t> pass_events;
+    cudaEvent_t host_pass_done = nullptr;   // last copy back of the most recent host-buffer pass, while not yet waited for
     // optional per-warp phase stamps of the last decode launch (env MLC_B200_TRACE=1)
     unsigned long long* d_trace = nullptr;
     size_t trace_words = 0;
