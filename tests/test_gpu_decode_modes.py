@@ -66,3 +66,42 @@ def test_planner_choice_follows_the_batch_shape():
     finally:
         del os.environ["MLC_B200_DECODE_MODE"]
     ex.close()
+
+
+LONG_TAIL_SHAPES = [(32, 4, 64), (32, 8, 128), (32, 2, 64), (8, 8, 64), (16, 1, 128)]
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_long_tail_batches_match_the_oracle(executor, oracle_mod, seed):
+    """Batches in which one or two requests dwarf the rest, so that the planner cuts their (request, head)
+    units over CTAs (anything from 2 to dozens of parts, parts shorter than the CTA's warp count included):
+    the fused decode step - row write, attention, in-CTA merge, cross-CTA combine - against the CPU oracle."""
+    import numpy as np
+    import torch
+    from mlcompiler_b200 import synth
+    from mlcompiler_b200.capi import MLC_F16
+    from tests.test_gpu_planned import make_plan, oracle_step
+    from tests.util import DeviceCase, assert_attention_close
+    rng = np.random.default_rng(1000 + seed)
+    H, KVH, D = LONG_TAIL_SHAPES[seed % len(LONG_TAIL_SHAPES)]
+    n_long = int(rng.integers(1, 3))
+    longs = rng.integers(3000, 30000 if D == 64 else 14000, n_long)
+    shorts = rng.integers(1, 700, int(rng.integers(0, 6)))
+    lens = rng.permutation(np.concatenate([longs, shorts])).astype(np.uint32)
+    case = synth.make_case(2000 + seed, lens, H, KVH, D)
+    dc = DeviceCase(case)
+    o = dc.out()
+    plan = make_plan(executor, case)
+    before = executor.launchCount()
+    assert executor.beginForwardPassCB()
+    for _ in range(2):      # twice: the arrival counters must be back at zero after a launch
+        assert executor.encodePagedDecodeStepPlanned(plan, dc.q, dc.k_new, dc.v_new, dc.k_pool, dc.v_pool, o, case.scale,
+                                                     MLC_F16, MLC_F16), executor.last_error()
+    assert executor.flushForwardPassCB(), executor.last_error()
+    assert executor.launchCount() - before in (2, 4)     # one launch per call (two where the planner prefers the split form)
+    torch.cuda.synchronize()
+    kp, vp, want = oracle_step(oracle_mod, case)
+    assert np.array_equal(dc.k_pool.cpu().numpy().view(np.uint16).reshape(-1), kp)
+    assert np.array_equal(dc.v_pool.cpu().numpy().view(np.uint16).reshape(-1), vp)
+    assert_attention_close(o.float().cpu().numpy(), want)
+    plan.destroy()
