@@ -28,7 +28,6 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
-#include <cstdlib>
 #include <cstring>
 
 #include "attn_internal.hpp"
@@ -55,7 +54,6 @@ constexpr uint32_t kTmemCols = 256;              // O: 128 columns, S: 2 x 64 co
 constexpr uint32_t kTmemO = 0, kTmemS = 128;
 
 struct PrefillParams {
-    const void* q;                  // fp16 [sum q_len, H, D] (read directly by the second form)
     void* o;                        // fp16 [sum q_len, H, D]
     const uint32_t* pt_flat;
     const uint32_t* pt_off;
@@ -530,366 +528,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
     if (warp == 4) tmem_dealloc(tmem, kTmemCols);
 }
 
-// ======================================================================================
-// Second form of the kernel: one CTA per SM with all 512 tensor-memory columns.
-//   Q lives in tensor memory (64 columns, two fp16 per column, written once by the softmax threads), so
-//   Q.K^T runs in the TS form: no shared-memory reads for A, 32 instead of 48 clocks per instruction.
-//   Even pages accumulate into O_a, odd pages into O_b, each with its own S / P buffer, running maximum and
-//   softmax warpgroup (warps 0-3 / 4-7; a warp reaches the TMEM lanes 32 * (warp % 4) ...); the two are merged
-//   with the log-sum-exp rule in the epilogue. That is the overlap two CTAs per SM give the first form, with
-//   one copy of Q and a 4-deep K/V ring.
-// Warp 8: MMA issue + TMEM allocation, warps 9 / 10: TMA producers of K / V.
-// ======================================================================================
-namespace {
-constexpr int kStages2 = 4;
-constexpr uint32_t kTileBytes2 = kStages2 * 2 * kKvBytes;   // 128 KiB: also keeps a second CTA off the SM
-struct Bars2 {
-    uint64_t q, k_full[kStages2], k_empty[kStages2], v_full[kStages2], v_empty[kStages2], s_full[2], p_full[2], pv_done[2];
-    uint32_t tmem_slot, group_ok[2];
-    float ml_b[kQTile][2];   // (reference maximum, row sum) of the odd-page group, for the merge
-};
-constexpr uint32_t kSmemBytes2 = kTileBytes2 + sizeof(Bars2);
-constexpr uint32_t kTmemCols2 = 512;
-constexpr uint32_t kTmemO2 = 0, kTmemS2 = 256, kTmemQ2 = 384;   // O: 2 x 128, S / P: 2 x 64, Q: 64
-}  // namespace
-
-__global__ void __launch_bounds__(352, 1)
-paged_prefill_tcgen05_kernel_v2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                                const PrefillParams prm) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    Bars2& bars = *reinterpret_cast<Bars2*>(smem_raw + kTileBytes2);
-    const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
-    const uint32_t req = blockIdx.z, head = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
-    const uint32_t q_len = prm.q_len[req];
-    if (qt * kQTile >= q_len) return;  // uniform over the CTA, before any barrier or TMEM use
-    const uint32_t q_start = prm.q_start[req];
-    const uint32_t seq_len = prm.seq_lens[req];
-    const uint32_t q_row0 = prm.q_row0[req] + qt * kQTile;
-    const uint32_t q_rows = min(static_cast<uint32_t>(kQTile), q_len - qt * kQTile);
-    const uint32_t kv_head = static_cast<uint32_t>((static_cast<uint64_t>(head) * prm.KVH) / prm.H);
-    const uint32_t kv_end = min(seq_len, q_start + qt * kQTile + q_rows);
-    const uint32_t n_tiles = (kv_end + kKvTile - 1) / kKvTile;
-
-    const uint32_t base = smem_u32(smem_raw);
-    if (base & 1023u) {
-        if (threadIdx.x == 0) atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT | (0x40u << 8));
-        return;
-    }
-    const uint32_t sKV = base;   // stage s: K at sKV + s*2*kKvBytes, V right after K
-
-    if (threadIdx.x == 0) {
-        mbar_init(smem_u32(&bars.q), 128);
-        for (int s = 0; s < kStages2; ++s) {
-            mbar_init(smem_u32(&bars.k_full[s]), 1);
-            mbar_init(smem_u32(&bars.k_empty[s]), 1);
-            mbar_init(smem_u32(&bars.v_full[s]), 1);
-            mbar_init(smem_u32(&bars.v_empty[s]), 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&bars.s_full[b]), 1);
-            mbar_init(smem_u32(&bars.p_full[b]), 128);
-            mbar_init(smem_u32(&bars.pv_done[b]), 1);
-            bars.group_ok[b] = 1u;
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 8) tmem_alloc(smem_u32(&bars.tmem_slot), kTmemCols2);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = bars.tmem_slot;
-
-    auto give_up = [&](uint32_t where, uint32_t tile) {
-        if (lane == 0 && atomicCAS(prm.err, 0u, MLC_DEVERR_WAIT_TIMEOUT | (where << 8) | (tile << 16)) != 0u)
-            atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
-    };
-
-    if (warp == 9 || warp == 10) {
-        // ---------------- TMA producers: warp 9 the K tiles, warp 10 the V tiles ----------------
-        if (lane == 0 && n_tiles > 0) {
-            const bool is_k = warp == 9;
-            const CUtensorMap* map = is_k ? &tmK : &tmV;
-            uint64_t* full = is_k ? bars.k_full : bars.v_full;
-            uint64_t* empty = is_k ? bars.k_empty : bars.v_empty;
-            const uint32_t pt_base = prm.pt_off[req];
-            for (uint32_t j = 0; j < n_tiles; ++j) {
-                const uint32_t s = j % kStages2;
-                if (j >= kStages2 && !mbar_wait_bounded(smem_u32(&empty[s]), ((j / kStages2) - 1) & 1u)) {
-                    give_up(is_k ? 0x30 : 0x31, j);
-                    break;
-                }
-                const int page = static_cast<int>(prm.pt_flat[pt_base + j]);
-                const uint32_t bf = smem_u32(&full[s]);
-                const uint32_t dst = sKV + s * 2 * kKvBytes + (is_k ? 0u : kKvBytes);
-                mbar_expect_tx(bf, kKvBytes);
-                tma_load_4d(dst, map, bf, 0, static_cast<int>(kv_head), 0, page);
-                tma_load_4d(dst + kSubBytesKV, map, bf, 64, static_cast<int>(kv_head), 0, page);
-            }
-        }
-    } else if (warp == 8) {
-        // ---------------- MMA issue (whole warp walks the loop, one elected lane issues) ----------------
-        if (n_tiles > 0) {
-            constexpr uint32_t idesc_qk = idesc_f16(kQTile, kKvTile, 0);
-            constexpr uint32_t idesc_pv = idesc_f16(kQTile, kHeadDim, 1);
-            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
-            const uint32_t sKV_u = __shfl_sync(0xffffffffu, sKV, 0);
-            const uint64_t desc_k_major = smem_desc_sw128(0, 16, 1024);
-            const uint64_t desc_v = smem_desc_sw128(0, kSubBytesKV, 1024);
-            auto issue_qk = [&](uint32_t j) {
-                const uint32_t s = j % kStages2;
-                const uint32_t sK = sKV_u + s * 2 * kKvBytes;
-                const uint32_t d = tmem_u + kTmemS2 + (j & 1u) * kKvTile;
-                if (elect_one()) {
-#pragma unroll
-                    for (int k = 0; k < kHeadDim / 16; ++k) {   // Q in TMEM: 16 fp16 = 8 columns per step
-                        const uint32_t b = sK + (k >> 2) * kSubBytesKV + (k & 3) * 32;
-                        tc_mma_f16_ts(d, tmem_u + kTmemQ2 + k * 8, desc_k_major | (b >> 4), idesc_qk, k > 0);
-                    }
-                    tc_commit(smem_u32(&bars.k_empty[s]));
-                    tc_commit(smem_u32(&bars.s_full[j & 1u]));
-                }
-                __syncwarp();
-            };
-            uint32_t where = 0x10, at = 0;
-            bool ok = mbar_wait_bounded(smem_u32(&bars.q), 0) && mbar_wait_bounded(smem_u32(&bars.k_full[0]), 0);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-                if (n_tiles > 1) {
-                    where = 0x15;
-                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars.k_full[1]), 0));
-                    if (ok) {
-                        tc_fence_after();
-                        issue_qk(1);
-                    }
-                }
-            }
-            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
-                at = j;
-                const uint32_t s = j % kStages2, par = j & 1u;
-                where = 0x13;
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars.v_full[s]), (j / kStages2) & 1u));
-                if (ok) {
-                    where = 0x14;
-                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars.p_full[par]), (j >> 1) & 1u));
-                }
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t sV = sKV_u + s * 2 * kKvBytes + kKvBytes;
-                const uint32_t pj = tmem_u + kTmemS2 + par * kKvTile;
-                if (elect_one()) {
-#pragma unroll
-                    for (int k = 0; k < kKvTile / 16; ++k) {
-                        const uint32_t b = sV + k * 16 * 128;
-                        tc_mma_f16_ts(tmem_u + kTmemO2 + par * kHeadDim, pj + k * 8, desc_v | (b >> 4), idesc_pv,
-                                      (j > 1 || k > 0) ? 1u : 0u);
-                    }
-                    tc_commit(smem_u32(&bars.v_empty[s]));
-                    tc_commit(smem_u32(&bars.pv_done[par]));
-                }
-                __syncwarp();
-                if (j + 2 < n_tiles) {   // the scores of this parity's next page: its S buffer holds P of page j until P.V is done
-                    const uint32_t s2 = (j + 2) % kStages2;
-                    where = 0x11;
-                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars.k_full[s2]), ((j + 2) / kStages2) & 1u));
-                    if (ok) {
-                        where = 0x12;
-                        ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars.pv_done[par]), (j >> 1) & 1u));
-                    }
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(j + 2);
-                }
-            }
-            if (!ok) give_up(where, at);
-        }
-    } else {
-        // ---------------- softmax groups: thread = query row; group 0 even pages, group 1 odd pages ----------------
-        const uint32_t grp = warp >> 2;
-        const uint32_t row = threadIdx.x & 127u;               // TMEM lane
-        const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
-        const uint32_t q_pos = q_start + qt * kQTile + row;
-        const uint32_t q_pos_warp = q_start + qt * kQTile + (warp & 3u) * 32u;
-        const float rescale_step = 8.0f / prm.scale_log2;
-        const uint32_t tS = tmem + lane_base + kTmemS2 + grp * kKvTile;
-        const uint32_t tO = tmem + lane_base + kTmemO2 + grp * kHeadDim;
-        float m_ref = -INFINITY, l_sum = 0.f;
-        bool ok = true;
-        uint32_t where = 0x20, at = 0;
-        if (grp == 0 && n_tiles > 0) {
-            // this row of Q into tensor memory: column c = elements 2c, 2c+1 (rows past the chunk: zeros)
-            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __half*>(prm.q) +
-                                                              (static_cast<size_t>(q_row0 + row) * prm.H + head) * kHeadDim);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t qr[32];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint4 v = row < q_rows ? __ldg(src + h * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
-                    qr[4 * i] = v.x; qr[4 * i + 1] = v.y; qr[4 * i + 2] = v.z; qr[4 * i + 3] = v.w;
-                }
-                tmem_st32(tmem + lane_base + kTmemQ2 + h * 32, qr);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(smem_u32(&bars.q));
-        }
-        for (uint32_t j = grp; j < n_tiles; j += 2) {
-            at = j;
-            where = 0x20;
-            const uint32_t ph = (j >> 1) & 1u;
-            ok = ok && mbar_wait_bounded(smem_u32(&bars.s_full[grp]), ph);
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t sreg[64];
-            {
-                uint32_t lo[32], hi[32];
-                tmem_ld32(tS, lo);
-                tmem_ld32(tS + 32, hi);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) { sreg[i] = lo[i]; sreg[32 + i] = hi[i]; }
-            }
-            const uint32_t kv0 = j * kKvTile;
-            if (kv0 + kKvTile - 1 > q_pos_warp || kv0 + kKvTile > seq_len) {
-                const uint32_t lim = min(q_pos + 1, seq_len);  // first masked position
-#pragma unroll
-                for (int c = 0; c < kKvTile; ++c)
-                    if (kv0 + c >= lim) sreg[c] = 0xff800000u;  // -inf
-            }
-            float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < kKvTile; c += 4) {
-                t0 = fmaxf(t0, __uint_as_float(sreg[c]));
-                t1 = fmaxf(t1, __uint_as_float(sreg[c + 1]));
-                t2 = fmaxf(t2, __uint_as_float(sreg[c + 2]));
-                t3 = fmaxf(t3, __uint_as_float(sreg[c + 3]));
-            }
-            const float m_new = fmaxf(m_ref, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
-            const bool need = (m_new > m_ref + rescale_step) || (m_ref == -INFINITY && m_new > -INFINITY);
-            const float alpha = need ? ((m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * prm.scale_log2)) : 1.0f;
-            if (need) m_ref = m_new;
-            l_sum *= alpha;
-            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * prm.scale_log2;
-            float ps[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pk[32];
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i]), prm.scale_log2, neg_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i + 1]), prm.scale_log2, neg_m));
-                    ps[i] += p0 + p1;
-                    __half2 h = __floats2half2_rn(p0, p1);
-                    pk[ch * 4 + i] = *reinterpret_cast<uint32_t*>(&h);
-                }
-            }
-            l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-            if (j > grp && __any_sync(0xffffffffu, need)) {
-                // this group's accumulator may only be touched once its previous P.V (page j-2) is done
-                where = 0x21;
-                ok = mbar_wait_bounded(smem_u32(&bars.pv_done[grp]), ph ^ 1u);
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll 1
-                for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-                    uint32_t oreg[32];
-                    tmem_ld32(tO + c0, oreg);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-                    tmem_st32(tO + c0, oreg);
-                }
-                tmem_wait_st();
-            }
-            tmem_st32(tS, pk);   // P over the first 32 columns of this group's S buffer
-            tmem_wait_st();
-            if (kv0 + kKvTile > seq_len) {   // V rows past the end of the sequence: zero them (last page only)
-                where = 0x22;
-                ok = mbar_wait_bounded(smem_u32(&bars.v_full[j % kStages2]), (j / kStages2) & 1u);
-                if (!ok) break;
-                const uint32_t sV = sKV + (j % kStages2) * 2 * kKvBytes + kKvBytes;
-                const uint32_t first = seq_len - kv0;  // 1..63
-                for (uint32_t i = row; i < (kKvTile - first) * 16; i += 128) {
-                    const uint32_t r = first + (i >> 4), c = i & 15;
-                    const uint32_t addr = sV + (c >> 3) * kSubBytesKV + r * 128 + ((c & 7) << 4);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            tc_fence_before();
-            mbar_arrive(smem_u32(&bars.p_full[grp]));
-        }
-        // the group's last P.V
-        const bool has_pages = n_tiles > grp;
-        if (ok && has_pages) {
-            const uint32_t jl = ((n_tiles - 1 - grp) & ~1u) + grp;   // last page of this parity
-            where = 0x23;
-            ok = mbar_wait_bounded(smem_u32(&bars.pv_done[grp]), (jl >> 1) & 1u);
-        }
-        if (!ok) {
-            give_up(where, at);
-            bars.group_ok[grp] = 0u;
-        }
-        if (grp == 1) {
-            bars.ml_b[row][0] = m_ref;
-            bars.ml_b[row][1] = l_sum;
-        }
-        tc_fence_before();
-        asm volatile("bar.sync 1, 256;" ::: "memory");   // both groups, every warp, whatever happened above
-        tc_fence_after();
-        if (grp == 0 && bars.group_ok[0] && bars.group_ok[1]) {
-            // merge the two accumulators: o = (O_a * w_a + O_b * w_b) / (l_a * w_a + l_b * w_b)
-            const float m_b = bars.ml_b[row][0], l_b = bars.ml_b[row][1];
-            const bool use_b = n_tiles > 1;   // the odd accumulator was written at all
-            const float m_all = fmaxf(m_ref, use_b ? m_b : -INFINITY);
-            const float w_a = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_all) * prm.scale_log2);
-            const float w_b = (!use_b || m_b == -INFINITY) ? 0.f : ex2((m_b - m_all) * prm.scale_log2);
-            const float l_all = l_sum * w_a + (use_b ? l_b * w_b : 0.f);
-            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
-            const float fa = w_a * inv, fb = w_b * inv;
-            __half* dst = static_cast<__half*>(prm.o) + (static_cast<size_t>(q_row0 + row) * prm.H + head) * kHeadDim;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-                uint32_t oa[32], ob[32];
-                if (n_tiles > 0) {
-                    tmem_ld32(tmem + lane_base + kTmemO2 + c0, oa);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) oa[i] = 0u;
-                }
-                if (use_b) {
-                    tmem_ld32(tmem + lane_base + kTmemO2 + kHeadDim + c0, ob);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) ob[i] = 0u;
-                }
-                tmem_wait_ld();
-                if (row < q_rows) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            const float x0 = __uint_as_float(oa[i + 2 * t]) * fa + __uint_as_float(ob[i + 2 * t]) * fb;
-                            const float x1 = __uint_as_float(oa[i + 2 * t + 1]) * fa + __uint_as_float(ob[i + 2 * t + 1]) * fb;
-                            __half2 h = __floats2half2_rn(x0, x1);
-                            w[t] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                        *reinterpret_cast<uint4*>(dst + c0 + i) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                }
-            }
-        }
-    }
-    // ---------------- teardown ----------------
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (warp == 8) tmem_dealloc(tmem, kTmemCols2);
-}
-
 // --------------------------------------------------------------------------------------
 // host side
 // --------------------------------------------------------------------------------------
@@ -942,17 +580,9 @@ int launch_prefill_tcgen05(mlc_ctx* ctx, const void* q, const void* k_pages, con
     if (!ctx->prefill_smem_set) {
         MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(kSmemBytes)));
-        MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_prefill_tcgen05_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(kSmemBytes2)));
         ctx->prefill_smem_set = true;
     }
-    // MLC_B200_PREFILL_FORM: 1 = two CTAs per SM, Q from shared memory; 2 = one CTA per SM, Q in tensor memory
-    static const int form = [] {
-        const char* v = std::getenv("MLC_B200_PREFILL_FORM");
-        return v && *v ? std::atoi(v) : 1;
-    }();
     PrefillParams prm{};
-    prm.q = q;
     prm.o = o;
     prm.pt_flat = d_pt_flat;
     prm.pt_off = d_pt_off;
@@ -966,8 +596,7 @@ int launch_prefill_tcgen05(mlc_ctx* ctx, const void* q, const void* k_pages, con
     prm.G = static_cast<uint32_t>(H / KVH);
     prm.scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(static_cast<unsigned>((max_q_len + kQTile - 1) / kQTile), static_cast<unsigned>(H), static_cast<unsigned>(batch));
-    if (form == 2) paged_prefill_tcgen05_kernel_v2<<<grid, 352, kSmemBytes2, ctx->stream>>>(mk, mv, prm);
-    else paged_prefill_tcgen05_kernel<<<grid, 224, kSmemBytes, ctx->stream>>>(mq, mk, mv, prm);
+    paged_prefill_tcgen05_kernel<<<grid, 224, kSmemBytes, ctx->stream>>>(mq, mk, mv, prm);
     ++ctx->launches;
     MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
