@@ -72,6 +72,16 @@ int mlc_device_error_word(mlc_ctx* ctx, uint32_t* word);
 void* mlc_ctx_stream(const mlc_ctx* ctx);
 /* Number of kernels this context has launched since creation. */
 uint64_t mlc_ctx_launch_count(const mlc_ctx* ctx);
+/* Number of device-memory and pinned-host allocations this context has made since
+ * creation (mlc_alloc, plan buffers, staging chunks, the split-KV workspace, exchange
+ * buffers). A caller that must stay allocation-free in steady state can assert that the
+ * count stops moving. */
+uint64_t mlc_ctx_alloc_count(const mlc_ctx* ctx);
+/* Limit, in polls (about a microsecond each), of the waits on flags that another GPU writes
+ * (the peer exchange kernel). 0 restores the default of about a second. When a wait runs
+ * out, the kernel records MLC_DEVERR_WAIT_TIMEOUT in the device error word, writes no
+ * output and returns; the context stays usable. */
+int mlc_ctx_set_wait_limit(mlc_ctx* ctx, uint32_t polls);
 /* Profiling aid (the reference's are env-gated wall-clock tables,
  * compiler/runtime/batched_walker.cpp:100-125): with MLC_B200_TRACE=1 in the
  * environment when the context is created, every warp of the decode attention
@@ -240,9 +250,12 @@ int mlc_encode_scatter_kv_pair_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, 
  * programmatic stream serialisation and starts fetching K/V pages while earlier work
  * on the stream is still finishing; Q, k_new and v_new are read only after that work
  * has completed. Therefore pool rows OTHER than this step's new rows must not be
- * written by work that is still in flight on the stream when this call is enqueued
- * (they were written by earlier steps; a pass_flush / stream sync between steps, or
- * any non-overlapping kernel in between, satisfies this). */
+ * written by OTHER parties' work that is still in flight on the stream when this call
+ * is enqueued (they were written by earlier steps; a pass_flush / stream sync between
+ * steps, or any ordinary kernel launch in between, satisfies this). The library's own
+ * step launches need no such care: a launch whose pools were written by one of the two
+ * decode launches enqueued just before it on this context (passes of one or two
+ * layers) does not fetch anything before the earlier work has completed. */
 int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
                                          const void* k_new, const void* v_new, void* k_pages,
                                          void* v_pages, void* o, float scale, int q_dtype, int o_dtype);
@@ -256,17 +269,23 @@ int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
  * scratch is a fixed 8 MiB array inside the library (mlc_static_scratch_bytes(); every
  * GPU that loads the library holds it until exit) instead of the context's growing
  * workspace; the call makes no cudaMalloc / cudaFree and no host allocation.
- *   - Limit: a batch whose split requests need more than 4 MiB of partials (about 450
- *     request pieces at head_dim 64) is rejected with MLC_ERR_UNSUPPORTED and a message
+ *   - Limit: the array is used as two halves of 4 MiB, each ending with a 16 KiB block of
+ *     arrival counters. A batch whose split or cut requests need more than 4 MiB - 16 KiB
+ *     of partials (about 450 request pieces at head_dim 64), or that cuts more than 4096
+ *     (request, head) units over CTAs, is rejected with MLC_ERR_UNSUPPORTED and a message
  *     naming the sizes; use the regular entry point for it. The plan itself is created
  *     beforehand with mlc_attn_plan_create, which does allocate.
  *   - The first call on a device resolves the array's device address
  *     (cudaGetSymbolAddress); make that first call before any stream capture.
- *   - All calls on a GPU share the array. Nothing in it has to start at zero (every
- *     partial is fully written before it is read), but two such calls that overlap on
- *     the GPU - different contexts or streams of the same device - race on it.
- *     Consecutive calls on one context are safe: they alternate between its two halves
- *     and are stream-ordered. */
+ *   - All calls on a GPU share the array and it keeps the last call's contents. The
+ *     partials need no initial value (each is fully written before it is read). The
+ *     counter blocks do: they rely on the array's zero initialisation at library load,
+ *     every launch leaves them at zero again, they sit at a fixed place that no plan's
+ *     partials can reach, and the context re-zeroes them after a kernel reported a
+ *     device error. Two such calls that overlap on the GPU - different contexts or
+ *     streams of the same device - race on the array. Consecutive calls on one context
+ *     are safe: they are stream-ordered and alternate between the two halves (counted
+ *     per context over calls of this entry point only). */
 size_t mlc_static_scratch_bytes(void);
 int mlc_encode_paged_flash_attention_planned_static(mlc_ctx* ctx, const mlc_attn_plan* plan,
                                                     const void* q, const void* k_pages,
@@ -399,6 +418,19 @@ typedef struct mlc_exchange mlc_exchange;
 int mlc_exchange_create(mlc_ctx* ctx, int rank, int world, size_t max_rows, size_t head_dim, mlc_exchange** out);
 int mlc_exchange_handle(mlc_ctx* ctx, mlc_exchange* ex, void* handle_out);
 int mlc_exchange_attach(mlc_ctx* ctx, mlc_exchange* ex, const void* handles);
+/* The same for ranks that live in ONE process (one host thread and context per GPU, peer access
+ * enabled by the caller): bases[r] = mlc_exchange_local_buffer of rank r's exchange object, own
+ * entry ignored. Nothing is mapped or closed by the library. */
+int mlc_exchange_attach_pointers(mlc_ctx* ctx, mlc_exchange* ex, void* const* bases);
+void* mlc_exchange_local_buffer(const mlc_exchange* ex);
+/* Floats per (step parity, rank) slot of the gather buffer: max_rows * (head_dim + 2) rounded up
+ * to a multiple of 4, so that every slot starts on a 16-byte boundary. */
+size_t mlc_exchange_slot_floats(const mlc_exchange* ex);
+/* Layout of a rank's gather buffer (pure host arithmetic, no device needed): slots
+ * [2 parities][world] of slot_floats floats each (o rows, then (m, l) pairs), flag words at
+ * flags_offset bytes, total size. Any output pointer may be null. */
+int mlc_exchange_layout(int world, size_t max_rows, size_t head_dim, size_t* slot_floats,
+                        size_t* flags_offset, size_t* total_bytes);
 int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float* o_partial,
                                     const float* ml_partial, size_t rows, void* out, int o_dtype);
 void mlc_exchange_destroy(mlc_ctx* ctx, mlc_exchange* ex);

@@ -44,6 +44,8 @@ _PROTOTYPES = {
     "mlc_device_error_word": (_i, [_vp, _u32p]),
     "mlc_ctx_stream": (_vp, [_vp]),
     "mlc_ctx_launch_count": (C.c_uint64, [_vp]),
+    "mlc_ctx_alloc_count": (C.c_uint64, [_vp]),
+    "mlc_ctx_set_wait_limit": (_i, [_vp, C.c_uint32]),
     "mlc_ctx_set_attention_kernel": (_i, [_vp, _i]),
     "mlc_alloc": (_vp, [_vp, _sz]),
     "mlc_free": (None, [_vp, _vp]),
@@ -74,6 +76,10 @@ _PROTOTYPES = {
     "mlc_exchange_create": (_i, [_vp, _i, _i, _sz, _sz, C.POINTER(_vp)]),
     "mlc_exchange_handle": (_i, [_vp, _vp, _vp]),
     "mlc_exchange_attach": (_i, [_vp, _vp, _vp]),
+    "mlc_exchange_attach_pointers": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "mlc_exchange_local_buffer": (_vp, [_vp]),
+    "mlc_exchange_slot_floats": (_sz, [_vp]),
+    "mlc_exchange_layout": (_i, [_i, _sz, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
     "mlc_encode_exchange_lse_combine": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _i]),
     "mlc_exchange_destroy": (None, [_vp, _vp]),
     "mlc_ctx_last_attention_kernel": (_i, [_vp]),
@@ -187,6 +193,13 @@ class Executor:
 
     def launchCount(self) -> int:
         return int(self._lib.mlc_ctx_launch_count(self._h))
+
+    def allocCount(self) -> int:
+        return int(self._lib.mlc_ctx_alloc_count(self._h))
+
+    def setWaitLimit(self, polls: int) -> bool:
+        """Polls (about a microsecond each) before a wait on another GPU's flag gives up; 0 = default."""
+        return self.status(self._lib.mlc_ctx_set_wait_limit(self._h, int(polls)))
 
     def stream(self) -> int:
         return int(self._lib.mlc_ctx_stream(self._h) or 0)
@@ -518,6 +531,18 @@ class PeerExchange:
         blob = b"".join(handles)
         buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
         self._ex.check(self._ex._lib.mlc_exchange_attach(self._ex._h, self.handle, C.cast(buf, _vp)))
+
+    def local_buffer(self) -> int:
+        return int(self._ex._lib.mlc_exchange_local_buffer(self.handle) or 0)
+
+    def slot_floats(self) -> int:
+        return int(self._ex._lib.mlc_exchange_slot_floats(self.handle))
+
+    def attach_pointers(self, bases: list[int]):
+        """Peers in this process: bases[r] = local_buffer() of rank r's exchange object."""
+        assert len(bases) == self.world
+        arr = (_vp * self.world)(*[_vp(b) for b in bases])
+        self._ex.check(self._ex._lib.mlc_exchange_attach_pointers(self._ex._h, self.handle, arr))
 
     def attach_with_torch_distributed(self, group=None):
         """Exchanges the handles with torch.distributed.all_gather_object and attaches."""

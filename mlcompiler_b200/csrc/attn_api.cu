@@ -422,6 +422,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
             cudaMalloc(reinterpret_cast<void**>(&p.dev), want) != cudaSuccess)
             return ctx->fail(MLC_ERR_OOM, "plan buffer of %zu bytes unavailable", want);
         p.cap = want;
+        ctx->allocations += 2;
     }
     if (!p.uploaded) MLCB_CUDA(ctx, cudaEventCreateWithFlags(&p.uploaded, cudaEventDisableTiming));
 

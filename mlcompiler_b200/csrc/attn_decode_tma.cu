@@ -185,6 +185,7 @@ struct DecodeParams {
     int q_f32, o_f32;
     int step;           // 1: decode-step variant (fused row write, early start)
     int pdl;            // 1: launched with programmatic stream serialisation
+    int early_fetch;    // 1: a decode step may fetch tiles of earlier steps' rows before griddepcontrol.wait
     unsigned long long* trace;  // optional [cta][warp][8] %globaltimer stamps (MLC_B200_TRACE)
     // In-kernel merge: one arrival counter per (split segment, warp); null = a merge kernel follows.
     uint32_t* seg_counters;
@@ -432,7 +433,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     uint32_t next_issue = 0;  // next CTA-local tile to fetch
     const uint32_t window = n_tiles < stages ? n_tiles : stages;
     if (prm.pdl) {
-        if (prm.step) {
+        if (prm.step && prm.early_fetch) {
             while (next_issue < window) {
                 const uint32_t e = tile_entry(next_issue);
                 if (e & kTileFreshBit) break;
@@ -1193,14 +1194,20 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     if (a.ext_work) {
         // Caller-provided workspace: nothing is allocated on this path, neither on the
         // device nor (the tensor maps are encoded on the stack, uncached) on the host.
+        // Each half of the caller's scratch ends with a fixed block of arrival counters for cut units, so
+        // that no plan's partials - whatever its size - can ever be written where another plan's counters
+        // live: the counters rely on the scratch starting zeroed and on every launch leaving them at zero.
         const size_t half = a.ext_work_bytes / 2 / 256 * 256;
-        // arrival counters of cut units live behind the partials; the scratch starts zeroed and every
-        // launch leaves them at zero
-        const size_t cnt_bytes = ((static_cast<size_t>(plan.n_unit_cuts) * 4 + 255) / 256) * 256;
-        if (o_bytes + ml_bytes + cnt_bytes > half)
+        if (half <= kExtCounterBytes) return ctx->fail(MLC_ERR_UNSUPPORTED, "the fixed scratch is too small");
+        const size_t partial_room = half - kExtCounterBytes;
+        if (o_bytes + ml_bytes > partial_room)
             return ctx->fail(MLC_ERR_UNSUPPORTED,
                              "this batch needs %zu bytes of split-KV scratch per copy, the fixed scratch holds %zu",
-                             o_bytes + ml_bytes + cnt_bytes, half);
+                             o_bytes + ml_bytes, partial_room);
+        if (static_cast<size_t>(plan.n_unit_cuts) * 4 > kExtCounterBytes)
+            return ctx->fail(MLC_ERR_UNSUPPORTED,
+                             "this batch cuts %u (request, head) units over CTAs, the fixed scratch has counters for %zu",
+                             plan.n_unit_cuts, kExtCounterBytes / 4);
         if (kv_pair) {
             if ((st = encode_pair_map(ctx, a.k_pages, a.v_pages, a, &mk)) != MLC_OK) return st;
             mv = mk;
@@ -1208,9 +1215,12 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
             if ((st = encode_tensor_map(ctx, a.k_pages, a, &mk)) != MLC_OK) return st;
             if ((st = encode_tensor_map(ctx, a.v_pages, a, &mv)) != MLC_OK) return st;
         }
-        parity = static_cast<uint32_t>(ctx->decode_launches++ & 1u);
+        // consecutive launches on the fixed scratch alternate between its halves, counted apart from the
+        // launches on the context's own workspace
+        parity = static_cast<uint32_t>(ctx->ext_launches++ & 1u);
         work = static_cast<char*>(a.ext_work) + parity * half;
-        ext_counters = reinterpret_cast<uint32_t*>(work + o_bytes + ml_bytes);
+        ext_counters = reinterpret_cast<uint32_t*>(work + partial_room);
+        ctx->ext_counter_block[parity] = ext_counters;   // re-zeroed after a device error
     } else {
         // MLC_B200_DECODE_INKERNEL_MERGE=1: merge inside the attention kernel (arrival counters
         // [n_segs][warps], mergers poll) instead of the chained merge kernel. Measured on cfg2 it is
@@ -1266,6 +1276,18 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     // Every attention launch is allowed to start early: before its wait it reads only the
     // plan (and, in a decode step, K/V rows of earlier steps).
     prm.pdl = 1;
+    // Programmatic launch order is not transitive for what a kernel does before its wait: in
+    // K(step s, pool A) -> K(step s, pool B) -> K(step s + 1, pool A) the third kernel may start once the
+    // second has let its dependents go, while the first is still writing its new rows into pool A. Tiles
+    // fetched before the wait must not come from a pool that one of the two launches before this one
+    // writes, so in that case (passes of one or two layers) the early fetch is left out.
+    prm.early_fetch = 1;
+    for (const void* recent : ctx->recent_step_pools)
+        if (step && recent && (recent == a.k_pages || recent == a.v_pages)) prm.early_fetch = 0;
+    ctx->recent_step_pools[0] = ctx->recent_step_pools[2];
+    ctx->recent_step_pools[1] = ctx->recent_step_pools[3];
+    ctx->recent_step_pools[2] = step ? a.k_pages : nullptr;
+    ctx->recent_step_pools[3] = step ? a.v_pages : nullptr;
     prm.stages = plan.stages;
     prm.seg_counters = use_counters ? ctx->d_counters : nullptr;
     if (plan.unit_mode && plan.n_unit_cuts) prm.seg_counters = ext_counters ? ext_counters : ctx->d_counters;

@@ -37,6 +37,7 @@ bool stage_reserve(mlc_ctx* ctx, size_t bytes, void** host, void** dev) {
         ctx->last_error = "cudaMalloc failed for the staging area";
         return false;
     }
+    ctx->allocations += 2;
     c.used = need;
     *host = c.host;
     *dev = c.dev;
@@ -79,6 +80,7 @@ int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters) {
             return ctx->fail(MLC_ERR_OOM, "split-KV workspace of %zu bytes unavailable", want);
         }
         ctx->work_bytes = want;
+        ++ctx->allocations;
     }
     if (counters > ctx->n_counters) {
         MLCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -92,6 +94,7 @@ int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters) {
         // Counters start at zero and every launch leaves them at zero again.
         MLCB_CUDA(ctx, cudaMemsetAsync(ctx->d_counters, 0, want * 4, ctx->stream));
         ctx->n_counters = want;
+        ++ctx->allocations;
     }
     return MLC_OK;
 }
@@ -99,6 +102,8 @@ int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters) {
 void reset_after_device_error(mlc_ctx* ctx) {
     cudaMemset(ctx->d_err, 0, 4);
     if (ctx->d_counters && ctx->n_counters) cudaMemset(ctx->d_counters, 0, ctx->n_counters * 4);
+    for (uint32_t* block : ctx->ext_counter_block)
+        if (block) cudaMemset(block, 0, kExtCounterBytes);
 }
 
 size_t resolve_capacity(const mlc_ctx* ctx, const void* pool, size_t claimed, size_t page_bytes) {
@@ -198,6 +203,14 @@ void* mlc_ctx_stream(const mlc_ctx* ctx) { return ctx ? ctx->stream : nullptr; }
 
 uint64_t mlc_ctx_launch_count(const mlc_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+uint64_t mlc_ctx_alloc_count(const mlc_ctx* ctx) { return ctx ? ctx->allocations : 0; }
+
+int mlc_ctx_set_wait_limit(mlc_ctx* ctx, uint32_t polls) {
+    if (!ctx) return MLC_ERR_INVALID_ARG;
+    ctx->wait_limit = polls;
+    return MLC_OK;
+}
+
 int mlc_ctx_set_attention_kernel(mlc_ctx* ctx, int which) {
     if (!ctx || which < 0 || which > 1) return MLC_ERR_INVALID_ARG;
     ctx->force_general = which;
@@ -223,6 +236,7 @@ void* mlc_alloc(mlc_ctx* ctx, size_t bytes) {
         return nullptr;
     }
     ctx->allocs[p] = bytes;
+    ++ctx->allocations;
     return p;
 }
 
@@ -288,7 +302,10 @@ int mlc_pass_flush(mlc_ctx* ctx) {
     DeviceGuard guard(ctx->device);
     ctx->pass_open = false;
     // the error word travels behind the pass's kernels, so one synchronisation covers both
-    if (!ctx->h_err && cudaHostAlloc(reinterpret_cast<void**>(&ctx->h_err), 4, cudaHostAllocDefault) != cudaSuccess) ctx->h_err = nullptr;
+    if (!ctx->h_err) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->h_err), 4, cudaHostAllocDefault) != cudaSuccess) ctx->h_err = nullptr;
+        else ++ctx->allocations;
+    }
     bool word_queued = false;
     if (ctx->h_err) {
         *ctx->h_err = 0;

@@ -25,6 +25,11 @@ struct StageChunk {
     size_t used = 0;
 };
 
+// Caller-provided split-KV scratch (the fixed array of the allocation-free entry point): the last
+// kExtCounterBytes of each of its two halves hold the arrival counters of cut units, at an address
+// that does not depend on the plan.
+static constexpr size_t kExtCounterBytes = 16384;
+
 struct AttnPlanCache;  // attn_api.cu
 struct TensorMapCache; // attn_decode_tma.cu
 
@@ -39,9 +44,14 @@ struct mlc_ctx {
     uint64_t launches_at_capture = 0;
     int sm_count = 0;
     int force_general = 0;
+    uint32_t wait_limit = 0;        // polls before a flag wait gives up; 0 = the kernel's default (about a second)
     int last_attention_kernel = 0;  // 0 none yet, 1 general, 2 TMA / tensor-core
     uint64_t launches = 0;
+    uint64_t allocations = 0;       // device and pinned-host allocations made through this context
     uint64_t decode_launches = 0;   // selects the workspace copy of the split-KV kernel
+    const void* recent_step_pools[4] = {nullptr, nullptr, nullptr, nullptr};  // pools written by the last two decode launches
+    uint64_t ext_launches = 0;      // same for launches on caller-provided (fixed) scratch
+    uint32_t* ext_counter_block[2] = {nullptr, nullptr};  // arrival counters inside that scratch, once used
     std::string last_error;
     std::unordered_map<const void*, size_t> allocs;
     std::unordered_map<std::string, std::pair<void*, size_t>> cached;

@@ -36,7 +36,7 @@
 namespace mlcb {
 
 constexpr int kMaxRanks = 16;
-constexpr uint32_t kMaxPolls = 1u << 20;  // ~1 us per system-scope poll: about a second
+constexpr uint32_t kMaxPolls = 1u << 20;  // default limit; ~1 us per system-scope poll: about a second
 
 struct ExchangeParams {
     const float* o_part;    // [rows, D]
@@ -50,6 +50,7 @@ struct ExchangeParams {
     size_t slot_floats;     // floats per (parity, rank) slot = max_rows * (D + 2)
     size_t flags_off;       // byte offset of the flag words [2][world]
     uint32_t rank, world, rows, D;
+    uint32_t max_polls;     // limit of the flag wait (mlc_ctx_set_wait_limit, default kMaxPolls)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256) exchange_lse_combine_kernel(const Exchang
     if (threadIdx.x < p.world) {
         const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.local + p.flags_off) + parity * p.world + threadIdx.x;
         bool seen = false;
-        for (uint32_t i = 0; i < kMaxPolls; ++i) {
+        for (uint32_t i = 0; i < p.max_polls; ++i) {
             if (static_cast<int32_t>(ld_acquire_sys(flag) - stamp) >= 0) {
                 seen = true;
                 break;
@@ -165,9 +166,23 @@ struct mlc_exchange {
     char* local = nullptr;
     char* peer[kMaxRanks] = {};
     bool attached = false;
+    bool by_pointer = false;   // peers given as addresses of this process (nothing to close)
 };
 
 extern "C" {
+
+int mlc_exchange_layout(int world, size_t max_rows, size_t head_dim, size_t* slot_floats, size_t* flags_offset,
+                        size_t* total_bytes) {
+    if (world < 1 || world > kMaxRanks || max_rows == 0 || head_dim == 0 || head_dim % 4) return MLC_ERR_INVALID_ARG;
+    // rounded up to whole 16-byte vectors: every (parity, rank) slot then starts on a 16-byte boundary
+    // whatever the parity of max_rows (the kernel moves the o rows as float4)
+    const size_t slot = (max_rows * (head_dim + 2) + 3) / 4 * 4;
+    const size_t flags = ((2 * static_cast<size_t>(world) * slot * 4 + 255) / 256) * 256;
+    if (slot_floats) *slot_floats = slot;
+    if (flags_offset) *flags_offset = flags;
+    if (total_bytes) *total_bytes = flags + 256 /* flags [2][world] */ + 256 /* seq, done */;
+    return MLC_OK;
+}
 
 int mlc_exchange_create(mlc_ctx* ctx, int rank, int world, size_t max_rows, size_t head_dim, mlc_exchange** out) {
     if (!ctx || !out) return MLC_ERR_INVALID_ARG;
@@ -180,9 +195,7 @@ int mlc_exchange_create(mlc_ctx* ctx, int rank, int world, size_t max_rows, size
     ex->world = world;
     ex->max_rows = max_rows;
     ex->D = head_dim;
-    ex->slot_floats = max_rows * (head_dim + 2);
-    ex->flags_off = ((2 * static_cast<size_t>(world) * ex->slot_floats * 4 + 255) / 256) * 256;
-    ex->bytes = ex->flags_off + 256 /* flags [2][world] */ + 256 /* seq, done */;
+    mlc_exchange_layout(world, max_rows, head_dim, &ex->slot_floats, &ex->flags_off, &ex->bytes);
     // plain cudaMalloc: the block is exported whole through a cudaIpc handle
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ex->local), ex->bytes);
     if (e == cudaSuccess) e = cudaMemset(ex->local, 0, ex->bytes);
@@ -191,6 +204,7 @@ int mlc_exchange_create(mlc_ctx* ctx, int rank, int world, size_t max_rows, size
         delete ex;
         return ctx->fail(MLC_ERR_OOM, "exchange buffer: %s", cudaGetErrorString(e));
     }
+    ++ctx->allocations;
     ex->peer[rank] = ex->local;
     ex->attached = world == 1;
     *out = ex;
@@ -231,6 +245,22 @@ int mlc_exchange_attach(mlc_ctx* ctx, mlc_exchange* ex, const void* handles) {
     return MLC_OK;
 }
 
+int mlc_exchange_attach_pointers(mlc_ctx* ctx, mlc_exchange* ex, void* const* bases) {
+    if (!ctx || !ex || !bases) return MLC_ERR_INVALID_ARG;
+    if (ex->attached) return ctx->fail(MLC_ERR_INVALID_ARG, "exchange already attached");
+    for (int r = 0; r < ex->world; ++r)
+        if (r != ex->rank && !bases[r]) return ctx->fail(MLC_ERR_INVALID_ARG, "null gather buffer for rank %d", r);
+    for (int r = 0; r < ex->world; ++r)
+        if (r != ex->rank) ex->peer[r] = static_cast<char*>(bases[r]);
+    ex->by_pointer = true;
+    ex->attached = true;
+    return MLC_OK;
+}
+
+void* mlc_exchange_local_buffer(const mlc_exchange* ex) { return ex ? ex->local : nullptr; }
+
+size_t mlc_exchange_slot_floats(const mlc_exchange* ex) { return ex ? ex->slot_floats : 0; }
+
 int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float* o_partial, const float* ml_partial,
                                     size_t rows, void* out, int o_dtype) {
     if (!ctx || !ex) return MLC_ERR_INVALID_ARG;
@@ -258,6 +288,7 @@ int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float*
     p.world = static_cast<uint32_t>(ex->world);
     p.rows = static_cast<uint32_t>(rows);
     p.D = static_cast<uint32_t>(ex->D);
+    p.max_polls = ctx->wait_limit ? ctx->wait_limit : kMaxPolls;
     const size_t total = rows * (ex->D / 4);
     size_t blocks = (total + 255) / 256;
     if (blocks < static_cast<size_t>(ex->world)) blocks = ex->world;
@@ -278,7 +309,7 @@ void mlc_exchange_destroy(mlc_ctx* ctx, mlc_exchange* ex) {
         DeviceGuard guard(ctx->device);
         cudaStreamSynchronize(ctx->stream);
         for (int r = 0; r < ex->world; ++r)
-            if (r != ex->rank && ex->peer[r]) cudaIpcCloseMemHandle(ex->peer[r]);
+            if (r != ex->rank && ex->peer[r] && !ex->by_pointer) cudaIpcCloseMemHandle(ex->peer[r]);
         if (ex->local) cudaFree(ex->local);
     }
     delete ex;

@@ -58,3 +58,26 @@ def test_missing_library_is_a_loud_import_error(monkeypatch, tmp_path):
     monkeypatch.setattr(capi, "_PKG", tmp_path)
     with pytest.raises(ImportError):
         capi.load_library()
+
+
+def test_exchange_layout_keeps_every_slot_16_byte_aligned():
+    """Gather-buffer layout of the peer exchange (pure host arithmetic): with head_dim % 4 == 0 a
+    slot of max_rows * (head_dim + 2) floats is only a multiple of 4 floats when max_rows is even;
+    the layout rounds it up, so that the float4 stores and loads of the kernel stay aligned for an
+    odd max_rows, on every (parity, rank) slot, and the flag words follow behind the last slot."""
+    import ctypes as C
+    import mlcompiler_b200
+    lib = mlcompiler_b200.load_library(build_if_missing=True)
+    for world in (1, 2, 3, 8, 16):
+        for max_rows in (1, 3, 127, 128, 129, 4097):
+            for D in (4, 64, 128):
+                slot, flags, total = C.c_size_t(), C.c_size_t(), C.c_size_t()
+                assert lib.mlc_exchange_layout(world, max_rows, D, C.byref(slot), C.byref(flags), C.byref(total)) == 0
+                assert slot.value % 4 == 0 and slot.value >= max_rows * (D + 2)
+                for parity in (0, 1):
+                    for rank in range(world):
+                        assert ((parity * world + rank) * slot.value * 4) % 16 == 0
+                assert flags.value % 256 == 0 and flags.value >= 2 * world * slot.value * 4
+                assert total.value >= flags.value + 2 * world * 4 + 8
+    assert lib.mlc_exchange_layout(0, 8, 64, None, None, None) != 0
+    assert lib.mlc_exchange_layout(2, 8, 66, None, None, None) != 0
