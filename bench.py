@@ -1,28 +1,32 @@
 #!/usr/bin/env python3
 """Benchmark of the paged decode-attention hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-secondary]
 
 Workload (N = 1): continuous-batching decode over 22 layers of the TinyLlama head
 shape (32 q heads / 4 KV heads, d = 64, fp16 KV, 64-token pages), 32 requests with
 context lengths seeded uniform in [64, 2048], non-contiguous random page tables
 over per-layer pools sized to the total pages + 10 %. One step = for every layer:
-write one new K/V row per request into the pool, then run attention.
+write one new K/V row per request into the pool, then run attention. The 22 layers
+are independent layer pools with all inputs resident when the step starts.
 
-`value` is KV GB/s with everything resident in HBM: the step is replayed from a
-CUDA graph (per layer one attention kernel with the KV row write and the merge fused
-in; consecutive kernels overlap by programmatic dependent launch) and timed with CUDA
-events on the launching stream. `e2e` is the same metric through the C ABI with host
-buffers, the call sequence a walker with host activations makes: every step one
-host-buffer pass call (Q and the new K/V rows of all layers copied in from pinned host
-memory, one fused launch per layer, the attention output copied back to pinned host
-memory, copies and kernels pipelined over groups of layers inside the call) and one
-in-place plan update that hands over the NEXT step's page tables / lengths / positions
-/ (page, slot) pairs as host arrays (they grow by one token per step, as in serving, and
-do not depend on this step's results) while this step runs; the flush returns when the
-output is complete in host memory. With N > 1 (torchrun, one rank per GPU) every rank
-runs its own 32-request batch: request sharding, no collective on the data path (weak
-scaling).
+`value` is KV GB/s with everything resident in HBM: one call of the whole-pass entry point
+(mlc_encode_paged_decode_pass_planned: every layer's row write + attention in ONE launch whose
+work items are dealt to the SMs across layers), replayed from a CUDA graph and timed with CUDA
+events on the launching stream. The same step issued layer by layer - one launch per layer, each
+ordered behind the one before, which is what a transformer that feeds layer l into layer l + 1
+must do - and in the reference walker's own call order (scatter K, scatter V, attention with host
+tables per layer) is timed the same way and reported under `call_forms`.
+`e2e` is the same metric through the C ABI with host buffers: every step one host-buffer pass call
+(Q and the new K/V rows of all layers live in pinned host memory, the attention output lands in
+pinned host memory) and one in-place plan update that hands over the NEXT step's page tables /
+lengths / positions / (page, slot) pairs as host arrays (they grow by one token per step, as in
+serving, and do not depend on this step's results) while this step runs; the flush returns when
+the output is complete in host memory. With N > 1 (torchrun, one rank per GPU) every rank runs a
+32-request batch of the same context lengths over its own pools: request sharding, no collective on
+the data path (weak scaling). `secondary` carries the other workloads: cfg3 (long contexts; with
+N > 1 split by KV sequence over the ranks through the peer-memory exchange kernel and checked
+against one GPU), cfg4 (wide GQA) and cfg5 (chunked prefill on tcgen05).
 
 `--impl reference` times MLcompiler's own executor-CPU attention (compiled from
 its unmodified sources into oracle/_ref, else the C port of it) on the host cores.
@@ -49,10 +53,16 @@ UNIT = "GB/s"
 WORKLOAD = ("cfg2: 22-layer continuous-batching decode, 32 requests, H32/KVH4/D64, fp16 KV, 64-token pages, "
             "contexts U[64,2048], random page tables, pool = pages + 10%; per layer: scatter 1 new K/V row "
             "per request, then attention")
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel on this workload
-# (37.79 MB read + <= 1.5 KB written), from the ncu captures summarised in
-# profiles/decode_attention_cfg2.md; the algorithmic KV bytes of that launch are 37.00 MB.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 37_793_792
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel on this workload, from an
+# `ncu --set full` capture (a profiler run, never the source of a timing). `commit` is the revision of the
+# kernel source the capture ran on; `kv_bytes` the algorithmic bytes of the captured launch, so that the
+# figure can be scaled to the launch the bench times (traffic grows in proportion to the KV bytes read).
+NCU_TRAFFIC = {
+    "kernel": "paged_decode_pass_kernel<64,false>",
+    "dram_bytes": 845_519_360,
+    "kv_bytes": 813_170_688,
+    "commit": "b39ff02 + working tree (whole-pass kernel, one head per CTA item)",
+}
 
 
 def measured_peak_gbs():
@@ -76,7 +86,7 @@ class ClockSampler:
     """Polls SM clock and throttle reasons through NVML while the timed region runs."""
 
     def __init__(self, index: int):
-        self.samples, self.reasons, self.stop_flag = [], set(), False
+        self.samples, self.times, self.reasons, self.stop_flag = [], [], set(), False
         self.max_mhz = None
         try:
             import pynvml
@@ -91,6 +101,7 @@ class ClockSampler:
     def _poll_once(self):
         nv = self.nv
         self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+        self.times.append(time.time())
         try:
             r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
         except Exception:
@@ -107,7 +118,13 @@ class ClockSampler:
                 self._poll_once()
             except Exception:
                 break
-            time.sleep(0.02)
+            time.sleep(0.002)
+
+    def median_between(self, t0, t1):
+        """Median SM clock of the samples taken between two host time stamps (None without a sample)."""
+        n = min(len(self.samples), len(self.times))
+        v = [self.samples[i] for i in range(n) if t0 <= self.times[i] <= t1]
+        return float(np.median(v)) if v else None
 
     def start(self):
         if self.nv:
@@ -241,9 +258,27 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------
+def time_blocks(stream, launch, n_blocks, per_block):
+    """CUDA events on the launching stream around each of n_blocks runs of per_block launches;
+    returns the seconds of every block and the host time stamps around it."""
+    import torch
+    out = []
+    for _ in range(n_blocks):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record(stream)
+        for _ in range(per_block):
+            launch()
+        e1.record(stream)
+        stream.synchronize()
+        out.append((e0.elapsed_time(e1) * 1e-3, t0, time.time()))
+    return out
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
+    import bench_more
     from mlcompiler_b200 import Executor, synth
     from mlcompiler_b200.capi import MLC_F16
 
@@ -254,15 +289,18 @@ def run_gpu_arm(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
 
-    # every rank decodes its own 32-request batch (request sharding)
+    # Every rank decodes a 32-request batch of its own (request sharding) with the SAME context lengths and
+    # page tables on every rank, so that the scaling figure measures the machine and not the draw; the pool
+    # contents differ per rank.
     headroom = 17                                      # tokens the end-to-end loop may append
-    lens0 = synth.config_lengths(2, seed=0xBEEF + 2 + 1000 * rank)
-    case = synth.make_case(0xBEEF + 2 + 1000 * rank, lens0 + headroom, P=64, fill=False, **synth.SHAPE_A)
+    lens0 = synth.config_lengths(2)
+    case = synth.make_case(0xBEEF + 2, lens0 + headroom, P=64, fill=False, **synth.SHAPE_A)
     N, H, KVH, D, P = case.N, case.H, case.KVH, case.D, case.P
     cap = case.capacity
 
     stream = torch.cuda.Stream(device=dev)
     ex = Executor(local, stream=stream.cuda_stream)
+    env = bench_more.Env(ex, stream, dev, rank, world)
     g = torch.Generator(device=dev)
     g.manual_seed(1234 + rank)
     with torch.cuda.stream(stream):
@@ -272,6 +310,7 @@ def run_gpu_arm(args):
         kn_all = torch.randn((LAYERS, N, KVH, D), device=dev, dtype=torch.float16, generator=g)
         vn_all = torch.randn((LAYERS, N, KVH, D), device=dev, dtype=torch.float16, generator=g)
         o_all = torch.zeros((LAYERS, N, H, D), device=dev, dtype=torch.float16)
+        o_chk = torch.zeros((LAYERS, N, H, D), device=dev, dtype=torch.float16)
     stream.synchronize()
 
     def tables(step):
@@ -290,118 +329,146 @@ def run_gpu_arm(args):
 
     kv_bytes_layer = lambda lens: int(lens.astype(np.int64).sum()) * 2 * KVH * D * 2
 
-    # ---- device-resident arm: planned calls replayed from a CUDA graph ------------------
+    # ---- device-resident arm: planned calls replayed from CUDA graphs ---------------------
     lens, q_pos, ids, slots, flat, off = tables(0)
     plan = ex.createPlan(flat, off, lens, q_pos, N, H, KVH, D, P, True, cap, page_ids=ids, slots_in_page=slots)
+    ptr = ex.pointerArray
+    pass_ptrs = [ptr(list(q_all)), ptr(list(kn_all)), ptr(list(vn_all)), ptr(k_pools), ptr(v_pools), ptr(list(o_all))]
 
-    def encode_step(fused=True):
+    def encode_pass():          # the whole step in one call: one launch when the plan allows it
+        assert ex.encodePagedDecodePassPlanned(plan, *pass_ptrs, case.scale, MLC_F16, MLC_F16), ex.last_error()
+
+    def encode_layers():        # layer by layer, each launch ordered behind the one before
         for L in range(LAYERS):
-            if fused:   # KV row write + attention of a layer in one launch
-                ok = ex.encodePagedDecodeStepPlanned(plan, q_all[L], kn_all[L], vn_all[L], k_pools[L], v_pools[L],
-                                                     o_all[L], case.scale, MLC_F16, MLC_F16)
-            else:       # attention alone
-                ok = ex.encodePagedFlashAttentionPlanned(plan, q_all[L], k_pools[L], v_pools[L], o_all[L], case.scale,
-                                                         MLC_F16, MLC_F16)
-            assert ok, ex.last_error()
+            assert ex.encodePagedDecodeStepPlanned(plan, q_all[L], kn_all[L], vn_all[L], k_pools[L], v_pools[L],
+                                                   o_chk[L], case.scale, MLC_F16, MLC_F16), ex.last_error()
 
-    assert ex.beginForwardPassCB()
-    encode_step()
-    assert ex.flushForwardPassCB(), ex.last_error()
-    assert ex.lastAttentionKernel() == 2, "the TMA / tensor-core kernel did not run"
-    assert ex.beginForwardPassCB()
-    assert ex.beginCapture(), ex.last_error()
-    encode_step()
-    graph = ex.endCapture()
-    assert ex.beginCapture(), ex.last_error()
-    encode_step(fused=False)
-    graph_attn = ex.endCapture()
+    def encode_reference_order():   # what an unchanged reference walker calls per layer (batched_walker.cpp:299-331)
+        for L in range(LAYERS):
+            assert ex.encodeScatterKVPagedBatched(k_pools[L], ids, slots, P, KVH, D, N, kn_all[L], cap), ex.last_error()
+            assert ex.encodeScatterKVPagedBatched(v_pools[L], ids, slots, P, KVH, D, N, vn_all[L], cap), ex.last_error()
+            assert ex.encodePagedFlashAttention(q_all[L], k_pools[L], v_pools[L], o_chk[L], flat, off, lens, q_pos, N, H,
+                                                KVH, D, P, True, case.scale, MLC_F16, MLC_F16, cap), ex.last_error()
 
-    def barrier():
-        stream.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed_replays(gr, k):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(stream):
-            e0.record(stream)
-            for _ in range(k):
-                gr.launch()
-            e1.record(stream)
-        stream.synchronize()
-        return e0.elapsed_time(e1) * 1e-3
-
-    for _ in range(max(args.warmup, 3)):
-        graph.launch()
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    launches0 = ex.launchCount()
-    t_step = timed_replays(graph, args.steps)
-    gpu_launches = ex.launchCount() - launches0
-    barrier()
-    # the dominant kernel alone, same timed conditions (22 attention launches per replay)
-    for _ in range(3):
-        graph_attn.launch()
-    stream.synchronize()
-    t_attn = timed_replays(graph_attn, args.steps)
-    clocks = sampler.stop()
-    assert ex.flushForwardPassCB(), ex.last_error()
-
-    def reduce_max(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def reduce_sum(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+    graphs, launches_per_step = {}, {}
+    for name, fn in (("whole_pass", encode_pass), ("layer_by_layer", encode_layers)):
+        assert ex.beginForwardPassCB()
+        l0 = ex.launchCount()
+        fn()
+        launches_per_step[name] = ex.launchCount() - l0
+        assert ex.flushForwardPassCB(), ex.last_error()
+        assert ex.lastAttentionKernel() == 2, "the TMA / tensor-core kernel did not run"
+        assert ex.beginForwardPassCB()
+        assert ex.beginCapture(), ex.last_error()
+        fn()
+        graphs[name] = ex.endCapture()
+        assert ex.flushForwardPassCB(), ex.last_error()
+    torch.cuda.synchronize()
+    agree = float((o_all.float() - o_chk.float()).abs().max().item())
+    assert agree <= 2e-3, f"whole-pass and layer-by-layer outputs differ by {agree}"
 
     bytes_step_rank = kv_bytes_layer(lens) * LAYERS
-    bytes_step_all = reduce_sum(float(bytes_step_rank))
-    sec_per_step = reduce_max(t_step) / args.steps
-    value = bytes_step_all / sec_per_step / 1e9
-    tokens_per_s = N * world / sec_per_step
-    # Duration of the dominant kernel. When the timed region is one kernel per layer (the planner kept every
-    # request inside a CTA, so the KV row write, attention and merge are a single launch), the region's
-    # CUDA-event time divided by its launches IS that kernel's average duration. Otherwise (attention + merge
-    # kernel per layer) the attention-only graph, timed the same way right after, gives the pair's duration.
-    kernels_per_step = gpu_launches / max(args.steps, 1)
-    if abs(kernels_per_step - LAYERS) < 0.5:
-        attn_launch_s = t_step / (args.steps * LAYERS)
-        launch_timing = "timed region / launches (one fused kernel per layer)"
-    else:
-        attn_launch_s = t_attn / (args.steps * LAYERS)
-        launch_timing = "attention-only graph (attention + merge kernel per layer)"
-    achieved = kv_bytes_layer(lens) / attn_launch_s / 1e9
+    bytes_step_all = env.reduce(float(bytes_step_rank), "sum")
     peak, peak_kind = measured_peak_gbs()
 
-    # ---- end-to-end arm: host buffers, host tables, reference-shaped calls ---------------
-    # Per layer one packed row [Q | new K | new V] in pinned host memory and on the device, O back to
-    # pinned host memory, all inside the timed region.
+    # ---- the timed region of the contract: W warm-up steps, then exactly K steps between barriers --------
+    warm = max(args.warmup, 3)
+    headline = graphs["whole_pass"]
+    assert ex.beginForwardPassCB()
+    for _ in range(warm):
+        headline.launch()
+    env.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    n_blocks = min(10, args.steps)
+    sizes = [args.steps // n_blocks + (1 if i < args.steps % n_blocks else 0) for i in range(n_blocks)]
+    l0 = ex.launchCount()
+    blocks = []
+    for sz in sizes:
+        blocks += time_blocks(stream, headline.launch, 1, sz)
+    gpu_launches = ex.launchCount() - l0
+    env.barrier()
+    t_step = sum(b[0] for b in blocks)
+    sec_per_step = env.reduce(t_step, "max") / args.steps
+    value = bytes_step_all / sec_per_step / 1e9
+    tokens_per_s = N * world / sec_per_step
+
+    # ---- distribution: >= 200 replays of every call form in blocks, median / min / max, clock per block -----
+    def distribution(launch, per_block, n=10):
+        for _ in range(3):
+            launch()
+        stream.synchronize()
+        bl = time_blocks(stream, launch, n, per_block)
+        us = np.array([b[0] / per_block * 1e6 for b in bl])
+        mhz = [sampler.median_between(b[1], b[2]) for b in bl]
+        return {"replays": n * per_block, "blocks": n, "us_per_step_median": float(np.median(us)),
+                "us_per_step_min": float(us.min()), "us_per_step_max": float(us.max()),
+                "sm_mhz_per_block": mhz}
+
+    def form(name, dist_stats, launches, note):
+        us = dist_stats["us_per_step_median"]
+        gbs = bytes_step_rank / us / 1e3
+        return {"kv_gbps": gbs, "frac_of_peak": gbs / peak, "launches_per_step": launches, **dist_stats, "what": note}
+
+    per_block = max(20, (200 + 9) // 10)
+    forms = {}
+    forms["whole_pass"] = form("whole_pass", distribution(graphs["whole_pass"].launch, per_block), launches_per_step["whole_pass"],
+                               "mlc_encode_paged_decode_pass_planned: all layers in one call (layers independent by contract)")
+    forms["layer_by_layer"] = form("layer_by_layer", distribution(graphs["layer_by_layer"].launch, per_block),
+                                   launches_per_step["layer_by_layer"],
+                                   "mlc_encode_paged_decode_step_planned per layer (row write fused into attention), every "
+                                   "launch ordered behind the previous one; us / launches is a throughput interval under "
+                                   "programmatic dependent launch, not a kernel duration")
+    assert ex.flushForwardPassCB(), ex.last_error()
+
+    def reference_order_step():
+        assert ex.beginForwardPassCB()
+        encode_reference_order()
+    assert ex.beginForwardPassCB()
+    l0 = ex.launchCount()
+    encode_reference_order()
+    ref_launches = ex.launchCount() - l0
+    assert ex.flushForwardPassCB(), ex.last_error()
+    forms["reference_call_order"] = form("reference_call_order", distribution(reference_order_step, per_block), ref_launches,
+                                         "what an unchanged reference walker calls: per layer encodeScatterKVPagedBatched (K), "
+                                         "(V), encodePagedFlashAttention with host tables (batched_walker.cpp:299-331); direct "
+                                         "calls, no CUDA graph, host time of the calls included")
+    assert ex.flushForwardPassCB(), ex.last_error()
+    clocks = sampler.stop()
+
+    # the dominant kernel of the timed region and its duration
+    one_launch = launches_per_step["whole_pass"] == 1
+    if one_launch:
+        kernel = "paged_decode_pass_kernel<64,false>"
+        bytes_per_launch = bytes_step_rank
+        us_per_launch = t_step / args.steps * 1e6
+        launch_timing = ("CUDA events around back-to-back graph replays / replays; one kernel per step, so this is the "
+                         "launch-to-launch interval of that kernel (its duration plus what the next launch cannot overlap)")
+    else:
+        kernel = "paged_decode_tma_kernel<64,false,unit>"
+        bytes_per_launch = kv_bytes_layer(lens)
+        us_per_launch = t_step / args.steps / LAYERS * 1e6
+        launch_timing = "timed region / launches: a throughput interval under programmatic dependent launch, not a kernel duration"
+    achieved = bytes_per_launch / us_per_launch / 1e3
+    traffic = None
+    if NCU_TRAFFIC["kernel"] == kernel:
+        traffic = int(NCU_TRAFFIC["dram_bytes"] * (bytes_per_launch / NCU_TRAFFIC["kv_bytes"]))
+
+    # ---- end-to-end arm: host buffers, host tables -----------------------------------------
+    # Per layer one packed row [Q | new K | new V] in pinned host memory, O in pinned host memory, all inside
+    # the timed region: per step one in-place plan update with the step's host tables and one host-buffer
+    # pass call. The tables of step s+1 do not depend on the results of step s (every request grows by one
+    # row), so they are handed to the library - validated, planned, uploaded, into the other of two plans -
+    # while step s still runs.
     nq, nkv = N * H * D, N * KVH * D
     in_host = torch.randn((LAYERS, nq + 2 * nkv), dtype=torch.float16).pin_memory()
     in_dev = torch.empty((LAYERS, nq + 2 * nkv), device=dev, dtype=torch.float16)
     o_host = torch.zeros((LAYERS, N, H, D), dtype=torch.float16).pin_memory()
     h2d = in_host.numel() * 2
     d2h = o_host.numel() * 2
-
-    # The call sequence INTEGRATION.md recommends to a walker whose activations are host vectors: per step
-    # one in-place plan update with the step's host tables and one host-buffer pass call. Inside that call
-    # the layers go in a few groups so that the copies overlap the kernels (group g's rows are copied on a
-    # copy stream while group g-1 computes, its O rows go back while group g+1 computes). The tables of
-    # step s+1 do not depend on the results of step s (every request grows by one row), so they are handed
-    # to the library - validated, planned, uploaded, into the other of two plans - while step s still runs.
     e2e_plans = [ex.createPlan(flat, off, lens, q_pos, N, H, KVH, D, P, True, cap, page_ids=ids, slots_in_page=slots)
                  for _ in range(2)]
     pool_ptrs = [ex.pointerArray(k_pools), ex.pointerArray(v_pools)]
-
     # the 16 table sets the growing requests cycle through, built once: what is timed is handing them
     # to the library (validation, planning, upload), not this script's numpy code
     table_sets = [tables(i) for i in range(16)]
@@ -413,7 +480,7 @@ def run_gpu_arm(args):
     def e2e_step(step):
         assert ex.beginForwardPassCB()
         ok = ex.encodePagedDecodePassHost(e2e_plans[step % 2], in_host, in_dev, *pool_ptrs, o_all, o_host, case.scale,
-                                          MLC_F16, MLC_F16)                      # all 22 layers, copies included
+                                          MLC_F16, MLC_F16)                      # all 22 layers, transfers included
         assert ok, ex.last_error()
         plan_for(step + 1)          # the next step's tables, while this step runs
         assert ex.flushForwardPassCB(), ex.last_error()      # returns when o_host is complete
@@ -421,18 +488,50 @@ def run_gpu_arm(args):
 
     first = max(args.warmup, 3)
     plan_for(0)
+    l0 = ex.launchCount()
     for w in range(first):
         e2e_step(w)
-    barrier()
+    e2e_launches_per_step = (ex.launchCount() - l0) / first
+    env.barrier()
     t0 = time.perf_counter()
     e2e_bytes = 0
+    e2e_times = []
     for s in range(args.steps):
+        ts = time.perf_counter()
         e2e_bytes += e2e_step(first + s)
+        e2e_times.append(time.perf_counter() - ts)
     stream.synchronize()
     t_e2e = time.perf_counter() - t0
-    barrier()
-    t_e2e_max = reduce_max(t_e2e)
-    e2e_value = reduce_sum(float(e2e_bytes)) / t_e2e_max / 1e9
+    env.barrier()
+    t_e2e_max = env.reduce(t_e2e, "max")
+    e2e_value = env.reduce(float(e2e_bytes), "sum") / t_e2e_max / 1e9
+    # the last end-to-end result checked against the device-resident per-layer path on the same rows
+    last = first + args.steps - 1
+    with torch.cuda.stream(stream):
+        in_dev.copy_(in_host, non_blocking=True)
+    stream.synchronize()
+    chk_plan = ex.createPlan(*[table_sets[last % 16][i] for i in (4, 5, 0, 1)], N, H, KVH, D, P, True, cap,
+                             page_ids=table_sets[last % 16][2], slots_in_page=table_sets[last % 16][3])
+    assert ex.beginForwardPassCB()
+    for L in range(LAYERS):
+        assert ex.encodePagedDecodeStepPlanned(chk_plan, in_dev[L, :nq], in_dev[L, nq:nq + nkv], in_dev[L, nq + nkv:],
+                                               k_pools[L], v_pools[L], o_chk[L], case.scale, MLC_F16, MLC_F16), ex.last_error()
+    assert ex.flushForwardPassCB(), ex.last_error()
+    e2e_err = float((o_chk.cpu().float() - o_host.float()).abs().max().item())
+    chk_plan.destroy()
+
+    secondary = None
+    if not args.no_secondary:
+        secondary = {}
+        for name, fn in (("cfg3", bench_more.run_cfg3), ("cfg4", bench_more.run_cfg4), ("cfg5", bench_more.run_cfg5)):
+            try:
+                r = fn(env, steps=200, warmup=5)
+            except Exception as e:            # a secondary workload must not take the headline line down
+                r = {"error": f"{type(e).__name__}: {e}"}
+            if r is not None:
+                secondary[name] = {k: r[k] for k in r if k in ("metric", "value", "unit", "ms_per_step", "us_per_step", "scaling",
+                                                                "config", "roofline", "gpu_launches", "split_vs_one_gpu",
+                                                                "tokens_per_s", "error")}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -441,29 +540,39 @@ def run_gpu_arm(args):
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
+            "warmup": warm, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "requests_per_gpu": N, "layers": LAYERS, "parallelism": f"request-sharded x{world}",
                        "kv_bytes_per_step": bytes_step_all,
-                       "l2": "the step streams 22 layer pools (~0.8 GB per GPU) > 126 MB L2, so no flush between steps"},
+                       "call": "mlc_encode_paged_decode_pass_planned (whole pass, CUDA-graph replay)",
+                       "l2": "the step streams 22 layer pools (~0.8 GB per GPU) > 126 MB L2, so no flush between steps",
+                       "same_lengths_on_every_rank": True},
             "tokens_per_s": tokens_per_s,
             "pct_of_nominal_8TBs": 100.0 * value / world / 8000.0,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_kind,
-                         "kernel": "paged_decode_tma_kernel<64,false,unit>" if abs(kernels_per_step - LAYERS) < 0.5
-                         else "paged_decode_tma_kernel<64,false,split> + paged_decode_merge_kernel", "bytes_per_launch": kv_bytes_layer(lens),
-                         "us_per_launch": attn_launch_s * 1e6, "launch_timing": launch_timing,
-                         "attention_only_us_per_layer": t_attn / (args.steps * LAYERS) * 1e6},
+                         "traffic": traffic, "traffic_capture": NCU_TRAFFIC, "peak_source": peak_kind,
+                         "kernel": kernel, "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
+                         "launch_timing": launch_timing},
+            "timing": {"timed_region_blocks": [b[0] / sz * 1e6 for b, sz in zip(blocks, sizes)],
+                       "timed_region_block_sizes": sizes, "unit": "us per step"},
+            "call_forms": forms,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": t_e2e_max / args.steps * 1e3},
+                    "ms_per_step": t_e2e_max / args.steps * 1e3,
+                    "ms_per_step_median": float(np.median(e2e_times)) * 1e3,
+                    "launches_per_step": e2e_launches_per_step,
+                    "max_abs_vs_device_path": e2e_err,
+                    "how": ("one launch per step reads the rows from pinned host memory and writes O into it"
+                            if e2e_launches_per_step < 1.5 else "copies in, launches and copies out pipelined over groups of layers")},
             "gpu_launches": int(gpu_launches),
             "clocks": clocks,
         }
+        if secondary is not None:
+            line["secondary"] = secondary
         if cpu_baseline:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line))
-    graph.destroy()
-    graph_attn.destroy()
+    for gph in graphs.values():
+        gph.destroy()
     plan.destroy()
     for pl in e2e_plans:
         pl.destroy()
@@ -481,6 +590,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall-time budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the cfg3 / cfg4 / cfg5 workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

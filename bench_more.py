@@ -1,5 +1,6 @@
 #!/usr/bin/env python3
-"""Secondary workloads of the paged-attention path (bench.py holds the headline one).
+"""Secondary workloads of the paged-attention path (bench.py holds the headline one and runs these
+too, under its `secondary` key).
 
     python bench_more.py --workload cfg3 [--steps K]          # long-context split-KV
     python bench_more.py --workload cfg4 [--steps K]          # wide GQA, requests sharded by KV bytes
@@ -8,8 +9,10 @@
         bench_more.py --workload cfg3|cfg4|cfg5
 
 cfg3: 4 requests of 32768 tokens (512 pages each), H32/KVH4/D64. With N ranks every rank holds
-a contiguous 1/N of every request's pages, computes the un-normalised partial (o, m, l), the
-partials are all-gathered with NCCL and combined by mlc_encode_lse_combine.
+a contiguous 1/N of every request's pages and computes the un-normalised partial (o, m, l); the
+partials are exchanged by this library's peer-memory kernel (or all-gathered with NCCL, --exchange
+nccl) and combined. With N > 1 one step is also checked on rank 0 against attention over the whole
+sequence on that one GPU.
 cfg4: 128 requests, H32/KVH8/D128, contexts U[512, 8192], requests assigned to ranks by greedy
 longest-first packing on KV bytes; no collective.
 cfg5: 8 requests, each a 512-token chunk on top of 1536 cached tokens, H32/KVH8/D128, causal; requests
@@ -31,33 +34,66 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 
-def measured_peak_tflops():
+def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     try:
         d = json.loads(p.read_text())
-        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d["bf16_tflops_sustained"]), "source": "measured"}
     except Exception:
-        return 1590.0, 1400.0, "fallback"
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def run_cfg5(args):
+class Env:
+    """What every workload needs: the rank's device, stream, executor and the reductions over ranks."""
+
+    def __init__(self, ex, stream, dev, rank, world):
+        self.ex, self.stream, self.dev, self.rank, self.world = ex, stream, dev, rank, world
+
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
+        self.stream.synchronize()
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce(self, x, op):
+        import torch
+        import torch.distributed as dist
+        if self.world == 1:
+            return x
+        t = torch.tensor([x], device=self.dev, dtype=torch.float64)
+        dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "sum": dist.ReduceOp.SUM}[op])
+        return float(t.item())
+
+
+def _timed(env, fn, steps):
+    """CUDA events on the launching stream around `steps` calls of fn(i); seconds per step, max over ranks."""
     import torch
-    import torch.distributed as dist
-    from mlcompiler_b200 import Executor, synth
-    from mlcompiler_b200.capi import MLC_F16
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(env.stream)
+    for i in range(steps):
+        fn(i)
+    e1.record(env.stream)
+    env.stream.synchronize()
+    return env.reduce(e0.elapsed_time(e1) * 1e-3, "max") / steps
 
-    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    stream = torch.cuda.Stream(device=dev)
-    ex = Executor(local, stream=stream.cuda_stream)
+
+def run_cfg5(env, steps=200, warmup=10):
+    import torch
+    from mlcompiler_b200 import synth
+    from mlcompiler_b200.capi import MLC_F16
+    ex, stream, dev, rank, world = env.ex, env.stream, env.dev, env.rank, env.world
     P, H, KVH, D = 64, 32, 8, 128
     n_req, new, cached = 8, 512, 1536
     mine = list(range(rank, n_req, world))
     N = len(mine)
+    if N == 0:      # more ranks than requests: this rank only takes part in the reductions
+        env.barrier()
+        env.reduce(0.0, "max")
+        env.reduce(0.0, "sum")
+        return None
     seq = np.full(N, new + cached, np.uint32)
     case = synth.make_case(0xBEEF + 5 + rank, seq, P=P, fill=False, H=H, KVH=KVH, D=D)
     q_start = np.full(N, cached, np.uint32)
@@ -66,8 +102,7 @@ def run_cfg5(args):
     # visible (query, key) pairs per (request, head): sum_i (cached + i + 1)
     pairs = new * cached + new * (new + 1) // 2
     flops_local = 4.0 * D * pairs * H * N
-    kv_bytes = case.kv_bytes
-    copies = max(2, int(np.ceil(300e6 / max(kv_bytes + 2 * N * new * H * D * 2, 1))))
+    copies = max(2, int(np.ceil(300e6 / max(case.kv_bytes + 2 * N * new * H * D * 2, 1))))
     with torch.cuda.stream(stream):
         kp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
         vp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
@@ -80,52 +115,245 @@ def run_cfg5(args):
                                             q_start, q_len, N, H, KVH, D, P, case.scale, MLC_F16, MLC_F16, cap)
         assert ok, ex.last_error()
 
-    def barrier():
-        stream.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     assert ex.beginForwardPassCB()
-    for i in range(max(args.warmup, 3)):
+    for i in range(max(warmup, 3)):
         step(i)
     assert ex.flushForwardPassCB(), ex.last_error()
     assert ex.lastAttentionKernel() == 3, "the tcgen05 kernel did not run"
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    env.barrier()
     l0 = ex.launchCount()
     assert ex.beginForwardPassCB()
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
+    sec = _timed(env, step, steps)
     assert ex.flushForwardPassCB(), ex.last_error()
     launches = ex.launchCount() - l0
-    sec = e0.elapsed_time(e1) * 1e-3 / args.steps
-    flops = flops_local
+    flops = env.reduce(flops_local, "sum")
+    peaks = measured_peaks()
+    value = flops / sec / 1e12
+    per_gpu = value / min(world, n_req)
+    return {
+        "metric": "paged_prefill_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": steps, "warmup": max(warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "dtype": "f16 in, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "cfg5: 8 requests x (512 new + 1536 cached tokens), H32/KVH8/D128, causal chunked prefill",
+                   "parallelism": f"request-sharded x{world}", "pool_copies_rotated": copies},
+        "tokens_per_s": n_req * new / sec,
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": per_gpu / peaks["bf16_tflops"], "peak_source": peaks["source"],
+                     "peak_sustained": peaks["bf16_tflops_sustained"],
+                     "note": "per GPU that holds a request; dense bf16 cuBLAS burst peak"},
+        "gpu_launches": int(launches)}
+
+
+def run_cfg3(env, steps=200, warmup=10, exchange="peer", check=True):
+    import torch
+    from mlcompiler_b200 import sharding, synth
+    from mlcompiler_b200.capi import MLC_F16, PeerExchange
+    ex, stream, dev, rank, world = env.ex, env.stream, env.dev, env.rank, env.world
+    P = 64
+    shape = synth.SHAPE_A
+    H, KVH, D = shape["H"], shape["KVH"], shape["D"]
+    case = synth.make_case(0xBEEF + 3, synth.config_lengths(3), P=P, fill=False, **shape)
+    N = case.N
+    flat, off, lens, _ = sharding.slice_tables_for_rank(case.pt_flat, case.pt_off, case.seq_lens, P, rank, world)
+    # local pool: only this rank's pages, renumbered densely
+    remap = {int(p): i for i, p in enumerate(flat)}
+    flat_local = np.array([remap[int(p)] for p in flat], np.uint32)
+    cap = len(flat_local)
+    local_bytes = int(lens.astype(np.int64).sum()) * 2 * KVH * D * 2
+    copies = max(2, int(np.ceil(300e6 / max(local_bytes, 1))))       # rotate over > 2x L2 worth of pools
+    g = torch.Generator(device=dev)
+    g.manual_seed(3000 + rank)
+    with torch.cuda.stream(stream):
+        kp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16, generator=g) for _ in range(copies)]
+        vp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16, generator=g) for _ in range(copies)]
+        gq = torch.Generator(device=dev)
+        gq.manual_seed(3)      # the same queries on every rank
+        q = torch.randn((N, H, D), device=dev, dtype=torch.float16, generator=gq)
+        o_part = torch.zeros((N, H, D), device=dev, dtype=torch.float32)
+        ml_part = torch.zeros((N, H, 2), device=dev, dtype=torch.float32)
+        out = torch.zeros((N, H, D), device=dev, dtype=torch.float16)
+    plan = ex.createPlan(flat_local, off, lens, np.zeros(N, np.uint32), N, H, KVH, D, P, False, cap)
+    use_peer = world > 1 and exchange == "peer"
+    xc = None
+    if use_peer:
+        xc = PeerExchange(ex, rank, world, N * H, D)
+        xc.attach_with_torch_distributed()
+    graphs = None
+
+    def step(i):
+        if graphs is not None:
+            graphs[i % copies].launch()
+            return
+        assert ex.beginForwardPassCB()
+        c = i % copies
+        if world == 1:
+            ok = ex.encodePagedFlashAttentionPlanned(plan, q, kp[c], vp[c], out, case.scale, MLC_F16, MLC_F16)
+            assert ok, ex.last_error()
+        elif use_peer:
+            ok = ex.encodePagedAttentionPartialPlanned(plan, q, kp[c], vp[c], o_part, ml_part, case.scale, MLC_F16)
+            assert ok, ex.last_error()
+            assert xc.encodeLseCombine(o_part, ml_part, N * H, out, MLC_F16), ex.last_error()
+        else:
+            ok = ex.encodePagedAttentionPartialPlanned(plan, q, kp[c], vp[c], o_part, ml_part, case.scale, MLC_F16)
+            assert ok, ex.last_error()
+            with torch.cuda.stream(stream):
+                o_all, ml_all = sharding.gather_partials(o_part, ml_part)
+            assert ex.encodeLseCombine(o_all, ml_all, world, N * H, D, out, MLC_F16), ex.last_error()
+
+    for i in range(max(warmup, 3)):
+        step(i)
+    assert ex.flushForwardPassCB(), ex.last_error()
+    env.barrier()
+
+    # ---- one step of the split checked against the unsplit attention on one GPU (rank 0) ----
+    checked = None
+    if world > 1 and check:
+        import torch.distributed as dist
+        step(0)
+        assert ex.flushForwardPassCB(), ex.last_error()
+        split_out = out.clone()
+        # rank 0 collects every rank's slice of pool copy 0 and lays the whole sequence out locally
+        sizes = [None] * world
+        dist.all_gather_object(sizes, cap)
+        if rank == 0:
+            full_k = [kp[0]] + [torch.empty((sizes[r], P, KVH, D), device=dev, dtype=torch.float16) for r in range(1, world)]
+            full_v = [vp[0]] + [torch.empty((sizes[r], P, KVH, D), device=dev, dtype=torch.float16) for r in range(1, world)]
+            for r in range(1, world):
+                dist.recv(full_k[r], src=r)
+                dist.recv(full_v[r], src=r)
+            base = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+            all_flat, all_off = [], [0]
+            per_rank = [sharding.slice_tables_for_rank(case.pt_flat, case.pt_off, case.seq_lens, P, r, world) for r in range(world)]
+            for req in range(N):
+                for r in range(world):
+                    f_r, o_r, _, _ = per_rank[r]
+                    # the rank's pages are renumbered densely in the order of its flat table
+                    all_flat.extend(range(int(base[r] + o_r[req]), int(base[r] + o_r[req + 1])))
+                all_off.append(len(all_flat))
+            kw, vw = torch.cat(full_k), torch.cat(full_v)
+            whole = torch.zeros_like(out)
+            ok = ex.runPagedFlashAttention(q, kw, vw, whole, np.array(all_flat, np.uint32), np.array(all_off, np.uint32),
+                                           case.seq_lens, np.zeros(N, np.uint32), N, H, KVH, D, P, False, case.scale,
+                                           MLC_F16, MLC_F16, int(base[-1]))
+            assert ok, ex.last_error()
+            err = float((whole.float() - split_out.float()).abs().max().item())
+            checked = {"max_abs_vs_one_gpu": err, "ok": err <= 2e-3}
+            del kw, vw, full_k, full_v
+        else:
+            dist.send(kp[0], dst=0)
+            dist.send(vp[0], dst=0)
+        env.barrier()
+
+    if world == 1 or use_peer:
+        # only this library's kernels in a step: replay them as CUDA graphs, one per pool copy
+        built = []
+        for c in range(copies):
+            assert ex.beginForwardPassCB()
+            assert ex.beginCapture()
+            step(c)
+            built.append(ex.endCapture())
+        graphs = built
+        for i in range(copies * 2):     # every rank replays the same sequence: the exchange stays in step
+            step(i)
+        assert ex.flushForwardPassCB(), ex.last_error()
+        env.barrier()
+    l0 = ex.launchCount()
+    assert ex.beginForwardPassCB()
+    sec = _timed(env, step, steps)
+    assert ex.flushForwardPassCB(), ex.last_error()
+    launches = ex.launchCount() - l0
+    total_bytes = case.kv_bytes
+    how = ("one GPU" if world == 1 else "partials pushed to the peers' memory, flags, combine - this library's kernels"
+           if use_peer else "NCCL all-gather of (o,m,l), LSE combine")
+    peaks = measured_peaks()
+    value = total_bytes / sec / 1e9
+    res = {
+        "metric": "paged_decode_attn_kv_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
+        "warmup": max(warmup, 3), "ms_per_step": sec * 1e3, "us_per_step": sec * 1e6, "higher_is_better": True,
+        "scaling": "strong", "dtype": "f16 in, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "cfg3: 4 requests x 32768 tokens, H32/KVH4/D64, KV sequence split over ranks, " + how,
+                   "parallelism": f"sequence-sharded x{world}", "pool_copies_rotated": copies,
+                   "cuda_graph": graphs is not None,
+                   "gather_bytes_per_rank": int((o_part.numel() + ml_part.numel()) * 4) if world > 1 else 0},
+        "tokens_per_s": N / sec,
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": value / world / peaks["hbm_gbs"], "peak_source": peaks["source"], "note": "per GPU"},
+        "gpu_launches": int(launches)}
+    if checked is not None:
+        res["split_vs_one_gpu"] = checked
+    if graphs:
+        for gph in graphs:
+            gph.destroy()
     if world > 1:
-        t = torch.tensor([sec, flops_local], device=dev, dtype=torch.float64)
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        sec, flops = float(tmax[0].item()), float(t[1].item())
-    burst, sustained, kind = measured_peak_tflops()
-    if rank == 0:
-        value = flops / sec / 1e12
-        print(json.dumps({
-            "metric": "paged_prefill_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "strong", "dtype": "f16 in, f32 accumulate", "data": "synthetic",
-            "config": {"workload": "cfg5: 8 requests x (512 new + 1536 cached tokens), H32/KVH8/D128, causal chunked prefill",
-                       "parallelism": f"request-sharded x{world}", "pool_copies_rotated": copies},
-            "tokens_per_s": n_req * new / sec,
-            "roofline": {"bound": "tensor", "achieved": value / world, "peak": burst, "unit": "TFLOP/s",
-                         "frac": value / world / burst, "peak_source": kind, "peak_sustained": sustained,
-                         "note": "per GPU; dense bf16 cuBLAS burst peak"},
-            "gpu_launches": int(launches)}))
-    ex.close()
-    if world > 1:
-        dist.destroy_process_group()
+        env.barrier()
+    if xc is not None:
+        xc.destroy()
+    plan.destroy()
+    return res
+
+
+def run_cfg4(env, steps=200, warmup=10):
+    import torch
+    from mlcompiler_b200 import synth
+    from mlcompiler_b200.capi import MLC_F16
+    ex, stream, dev, rank, world = env.ex, env.stream, env.dev, env.rank, env.world
+    P = 64
+    shape = synth.SHAPE_B
+    H, KVH, D = shape["H"], shape["KVH"], shape["D"]
+    all_lens = synth.config_lengths(4)
+    shards = synth.shard_requests_by_kv_bytes(all_lens, world)
+    mine = all_lens[shards[rank]]
+    case = synth.make_case(0xBEEF + 4 + rank, mine, P=P, fill=False, **shape)
+    N, cap = case.N, case.capacity
+    local_bytes = case.kv_bytes
+    copies = max(2, int(np.ceil(300e6 / max(local_bytes, 1))))
+    with torch.cuda.stream(stream):
+        kp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
+        vp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
+        q = torch.randn((N, H, D), device=dev, dtype=torch.float16)
+        kn = torch.randn((N, KVH, D), device=dev, dtype=torch.float16)
+        vn = torch.randn((N, KVH, D), device=dev, dtype=torch.float16)
+        out = torch.zeros((N, H, D), device=dev, dtype=torch.float16)
+    plan = ex.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, N, H, KVH, D, P, True, cap,
+                         page_ids=case.page_ids, slots_in_page=case.slots)
+
+    def enc():
+        for c in range(copies):
+            assert ex.encodePagedDecodeStepPlanned(plan, q, kn, vn, kp[c], vp[c], out, case.scale, MLC_F16, MLC_F16), ex.last_error()
+
+    assert ex.beginForwardPassCB()
+    enc()
+    assert ex.flushForwardPassCB(), ex.last_error()
+    assert ex.beginForwardPassCB()
+    assert ex.beginCapture()
+    enc()
+    graph = ex.endCapture()
+    for _ in range(max(warmup, 3)):
+        graph.launch()
+    env.barrier()
+    l0 = ex.launchCount()
+    reps = max(steps // copies, 1)
+    sec = _timed(env, lambda i: graph.launch(), reps) / copies
+    launches = ex.launchCount() - l0
+    assert ex.flushForwardPassCB(), ex.last_error()
+    total_bytes = env.reduce(float(local_bytes), "sum")
+    loads = np.array([all_lens[s].sum() for s in shards], np.float64)
+    peaks = measured_peaks()
+    value = total_bytes / sec / 1e9
+    graph.destroy()
+    plan.destroy()
+    return {
+        "metric": "paged_decode_attn_kv_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": reps * copies,
+        "warmup": max(warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "dtype": "f16 in, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "cfg4: 128 requests, H32/KVH8/D128, contexts U[512,8192], requests sharded by KV bytes; "
+                               "scatter + attention fused, one launch per layer",
+                   "parallelism": f"request-sharded x{world}", "pool_copies_rotated": copies,
+                   "kv_byte_imbalance_max_over_mean": float(loads.max() / loads.mean())},
+        "tokens_per_s": len(all_lens) / sec,
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": value / world / peaks["hbm_gbs"], "peak_source": peaks["source"], "note": "per GPU"},
+        "gpu_launches": int(launches)}
 
 
 def main():
@@ -136,14 +364,10 @@ def main():
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="cfg3 on several GPUs: peer-memory exchange kernel (default) or NCCL all-gather + combine")
     args = ap.parse_args()
-    if args.workload == "cfg5":
-        return run_cfg5(args)
 
     import torch
     import torch.distributed as dist
-    from bench import measured_peak_gbs
-    from mlcompiler_b200 import Executor, sharding, synth
-    from mlcompiler_b200.capi import MLC_F16, MLC_F32, PeerExchange
+    from mlcompiler_b200 import Executor
 
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     if world > 1:
@@ -153,170 +377,15 @@ def main():
     dev = torch.device("cuda", local)
     stream = torch.cuda.Stream(device=dev)
     ex = Executor(local, stream=stream.cuda_stream)
-    P = 64
-
-    def barrier():
-        stream.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def reduce(x, op):
-        if world == 1:
-            return x
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=op)
-        return float(t.item())
-
-    if args.workload == "cfg3":
-        shape = synth.SHAPE_A
-        H, KVH, D = shape["H"], shape["KVH"], shape["D"]
-        case = synth.make_case(0xBEEF + 3, synth.config_lengths(3), P=P, fill=False, **shape)
-        N = case.N
-        flat, off, lens, _ = sharding.slice_tables_for_rank(case.pt_flat, case.pt_off, case.seq_lens, P, rank, world)
-        # local pool: only this rank's pages, renumbered densely
-        remap = {int(p): i for i, p in enumerate(flat)}
-        flat_local = np.array([remap[int(p)] for p in flat], np.uint32)
-        cap = len(flat_local)
-        local_bytes = int(lens.astype(np.int64).sum()) * 2 * KVH * D * 2
-        copies = max(2, int(np.ceil(300e6 / max(local_bytes, 1))))       # rotate over > 2x L2 worth of pools
-        with torch.cuda.stream(stream):
-            kp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
-            vp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
-            q = torch.randn((N, H, D), device=dev, dtype=torch.float16)
-            o_part = torch.zeros((N, H, D), device=dev, dtype=torch.float32)
-            ml_part = torch.zeros((N, H, 2), device=dev, dtype=torch.float32)
-            out = torch.zeros((N, H, D), device=dev, dtype=torch.float16)
-        plan = ex.createPlan(flat_local, off, lens, np.zeros(N, np.uint32), N, H, KVH, D, P, False, cap)
-        use_peer = world > 1 and args.exchange == "peer"
-        xc = None
-        if use_peer:
-            xc = PeerExchange(ex, rank, world, N * H, D)
-            xc.attach_with_torch_distributed()
-        graphs = None
-
-        def step(i):
-            if graphs is not None:
-                graphs[i % copies].launch()
-                return
-            assert ex.beginForwardPassCB()
-            if world == 1:
-                ok = ex.encodePagedFlashAttentionPlanned(plan, q, kp[i % copies], vp[i % copies], out, case.scale, MLC_F16, MLC_F16)
-                assert ok, ex.last_error()
-            elif use_peer:
-                ok = ex.encodePagedAttentionPartialPlanned(plan, q, kp[i % copies], vp[i % copies], o_part, ml_part, case.scale, MLC_F16)
-                assert ok, ex.last_error()
-                assert xc.encodeLseCombine(o_part, ml_part, N * H, out, MLC_F16), ex.last_error()
-            else:
-                ok = ex.encodePagedAttentionPartialPlanned(plan, q, kp[i % copies], vp[i % copies], o_part, ml_part, case.scale, MLC_F16)
-                assert ok, ex.last_error()
-                with torch.cuda.stream(stream):
-                    o_all, ml_all = sharding.gather_partials(o_part, ml_part)
-                assert ex.encodeLseCombine(o_all, ml_all, world, N * H, D, out, MLC_F16), ex.last_error()
-            ex._lib.mlc_pass_is_open(ex.handle)  # keep the pass open across steps: one flush at the end
-
-        for i in range(max(args.warmup, 3)):
-            step(i)
-        assert ex.flushForwardPassCB(), ex.last_error()
-        barrier()
-        if world == 1 or use_peer:
-            # only this library's kernels in a step: replay them as CUDA graphs, one per pool copy
-            built = []
-            for c in range(copies):
-                assert ex.beginForwardPassCB()
-                assert ex.beginCapture()
-                step(c)
-                built.append(ex.endCapture())
-            graphs = built
-            for i in range(copies * 2):     # every rank replays the same sequence: the exchange stays in step
-                step(i)
-            assert ex.flushForwardPassCB(), ex.last_error()
-            barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = ex.launchCount()
-        assert ex.beginForwardPassCB()
-        e0.record(stream)
-        for i in range(args.steps):
-            step(i)
-        e1.record(stream)
-        assert ex.flushForwardPassCB(), ex.last_error()
-        launches = ex.launchCount() - l0
-        sec = reduce(e0.elapsed_time(e1) * 1e-3, dist.ReduceOp.MAX if world > 1 else None) / args.steps
-        total_bytes = case.kv_bytes
-        how = ("one GPU" if world == 1 else "partials pushed to the peers' memory, flags, combine - one kernel" if use_peer
-               else "NCCL all-gather of (o,m,l), LSE combine")
-        workload = "cfg3: 4 requests x 32768 tokens, H32/KVH4/D64, KV sequence split over ranks, " + how
-        extra = {"parallelism": f"sequence-sharded x{world}", "pool_copies_rotated": copies, "cuda_graph": graphs is not None,
-                 "gather_bytes_per_rank": int((o_part.numel() + ml_part.numel()) * 4) if world > 1 else 0}
-        n_req = N
+    env = Env(ex, stream, dev, rank, world)
+    if args.workload == "cfg5":
+        res = run_cfg5(env, args.steps, args.warmup)
+    elif args.workload == "cfg3":
+        res = run_cfg3(env, args.steps, args.warmup, args.exchange)
     else:
-        shape = synth.SHAPE_B
-        H, KVH, D = shape["H"], shape["KVH"], shape["D"]
-        all_lens = synth.config_lengths(4)
-        shards = synth.shard_requests_by_kv_bytes(all_lens, world)
-        mine = all_lens[shards[rank]]
-        case = synth.make_case(0xBEEF + 4 + rank, mine, P=P, fill=False, **shape)
-        N, cap = case.N, case.capacity
-        local_bytes = case.kv_bytes
-        copies = max(2, int(np.ceil(300e6 / max(local_bytes, 1))))
-        with torch.cuda.stream(stream):
-            kp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
-            vp = [torch.randn((cap, P, KVH, D), device=dev, dtype=torch.float16) for _ in range(copies)]
-            q = torch.randn((N, H, D), device=dev, dtype=torch.float16)
-            kn = torch.randn((N, KVH, D), device=dev, dtype=torch.float16)
-            vn = torch.randn((N, KVH, D), device=dev, dtype=torch.float16)
-            out = torch.zeros((N, H, D), device=dev, dtype=torch.float16)
-        plan = ex.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, N, H, KVH, D, P, True, cap,
-                             page_ids=case.page_ids, slots_in_page=case.slots)
-
-        def enc():
-            for c in range(copies):
-                assert ex.encodePagedDecodeStepPlanned(plan, q, kn, vn, kp[c], vp[c], out, case.scale, MLC_F16, MLC_F16), ex.last_error()
-
-        assert ex.beginForwardPassCB()
-        enc()
-        assert ex.flushForwardPassCB(), ex.last_error()
-        assert ex.beginForwardPassCB()
-        assert ex.beginCapture()
-        enc()
-        graph = ex.endCapture()
-        for _ in range(max(args.warmup, 3)):
-            graph.launch()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = ex.launchCount()
-        reps = max(args.steps // copies, 1)
-        e0.record(stream)
-        for _ in range(reps):
-            graph.launch()
-        e1.record(stream)
-        stream.synchronize()
-        launches = ex.launchCount() - l0
-        assert ex.flushForwardPassCB(), ex.last_error()
-        sec = reduce(e0.elapsed_time(e1) * 1e-3, dist.ReduceOp.MAX if world > 1 else None) / (reps * copies)
-        total_bytes = reduce(float(local_bytes), dist.ReduceOp.SUM if world > 1 else None)
-        loads = np.array([all_lens[s].sum() for s in shards], np.float64)
-        workload = "cfg4: 128 requests, H32/KVH8/D128, contexts U[512,8192], requests sharded by KV bytes; scatter + attention fused"
-        extra = {"parallelism": f"request-sharded x{world}", "pool_copies_rotated": copies,
-                 "kv_byte_imbalance_max_over_mean": float(loads.max() / loads.mean())}
-        n_req = len(all_lens)
-
-    peak, kind = measured_peak_gbs()
+        res = run_cfg4(env, args.steps, args.warmup)
     if rank == 0:
-        value = total_bytes / sec / 1e9
-        print(json.dumps({
-            "metric": "paged_decode_attn_kv_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "strong", "dtype": "f16 in, f32 accumulate", "data": "synthetic",
-            "config": {"workload": workload, **extra}, "tokens_per_s": n_req / sec,
-            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
-                         "frac": value / world / peak, "peak_source": kind, "note": "per GPU"},
-            "gpu_launches": int(launches)}))
-    if world > 1:
-        dist.barrier()
-    if args.workload == "cfg3" and xc is not None:
-        xc.destroy()
-    plan.destroy()
+        print(json.dumps(res))
     ex.close()
     if world > 1:
         dist.destroy_process_group()

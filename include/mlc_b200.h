@@ -310,10 +310,21 @@ int mlc_encode_lse_combine(mlc_ctx* ctx, const float* o_parts, const float* ml_p
                            size_t rows, size_t head_dim, void* out, int o_dtype);
 
 /* All layers of one decode pass in one call - the layer loop of the reference's walker
- * (batched_walker.cpp:299-331) on this side of the boundary: for l in [0, n_layers)
- * mlc_encode_paged_decode_step_planned(plan, q[l], k_new[l], v_new[l], k_pages[l], v_pages[l], o[l]).
- * The arrays are host arrays of device pointers, read during the call. Stops at the first
- * layer that fails and returns its status. */
+ * (batched_walker.cpp:299-331) on this side of the boundary: the result is that of, for l in
+ * [0, n_layers), mlc_encode_paged_decode_step_planned(plan, q[l], k_new[l], v_new[l], k_pages[l],
+ * v_pages[l], o[l]). The arrays are host arrays of device pointers, read during the call.
+ * CONTRACT: every layer's q / k_new / v_new must be complete when the work enqueued before this
+ * call on the stream has finished - no layer's input may depend on another layer's output of the
+ * same call (layers of a model whose attention inputs are produced ahead of time, or independent
+ * layer pools as in a bandwidth benchmark; a transformer that feeds layer l's output into layer
+ * l + 1 calls the per-layer entry point instead). Under that contract the library is free to
+ * interleave the layers: when the plan keeps every (request, head) inside one CTA and was
+ * created with page_ids / slots_in_page, the whole pass is ONE launch of at most 64 layers whose
+ * (layer, request, head) work items are dealt to the SMs across layers, so that every SM gets
+ * the same number of KV bytes whatever the spread of context lengths inside a layer and there
+ * is no per-layer tail or launch hand-over; otherwise (or with MLC_B200_DECODE_PASS=0 in the
+ * environment) it is one launch per layer. The pools of different layers must not overlap.
+ * Stops at the first layer that fails and returns its status. */
 int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, size_t n_layers,
                                          const void* const* q, const void* const* k_new,
                                          const void* const* v_new, void* const* k_pages,
@@ -334,7 +345,15 @@ int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
  * following step - runs beside it; a second host-buffer pass without a flush in between is ordered
  * behind the first one's copies).
  * Not capturable (MLC_ERR_UNSUPPORTED between mlc_graph_begin_capture and _end_capture). The streams
- * and events are created on the first call. */
+ * and events are created on the first call.
+ * Zero-copy form: when the pass can run as one launch (see mlc_encode_paged_decode_pass_planned; the
+ * same contract on the layers' independence holds) and host_in / host_o are pinned host memory that
+ * the GPU can address (cudaHostAlloc, cudaHostRegister, torch pin_memory), there are no copies at
+ * all: the kernel reads every Q / new K / new V row from host memory itself - once, one work item
+ * ahead of its use - and stores O straight into host_o, so the transfers run beside the KV stream.
+ * dev_in and dev_o are then left untouched (their contents after the call are unspecified either
+ * way). host_o is complete when mlc_pass_flush returns. MLC_B200_DECODE_ZERO_COPY=0 in the
+ * environment keeps the copy pipeline. */
 int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, size_t n_layers,
                                       const void* host_in, void* dev_in, void* const* k_pages,
                                       void* const* v_pages, void* dev_o, void* host_o, float scale,

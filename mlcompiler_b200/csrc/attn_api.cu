@@ -19,6 +19,8 @@
 
 namespace mlcb {
 
+static constexpr size_t kMaxPassLayersApi = 64;   // layers of one whole-pass launch (decode_pass_supported checks it)
+
 struct PlanKey {
     size_t batch = 0, H = 0, KVH = 0, D = 0, P = 0, capacity = 0, n_flat = 0;
     int causal = 0;
@@ -41,6 +43,7 @@ struct mlc_attn_plan {
     size_t cap = 0;
     cudaEvent_t uploaded = nullptr;
     mlcb::DecodePlanView view;
+    mlcb::DecodePlanView view_pass;   // work lists of the whole-pass launch (pass_ready says whether they exist)
     const uint32_t* d_page_ids = nullptr;  // this step's (page, slot) per request, when given
     const uint32_t* d_slots = nullptr;
     uint64_t stamp = 0;
@@ -141,6 +144,12 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     const bool tma = decode_tma_shape_supported(k.H, k.KVH, k.D, k.P, k.capacity);
     std::vector<SegDesc> segs;
     bool unit_mode = false;
+    uint32_t unit_mode_hpc = 1;
+    // second work list for whole-pass launches (see below); absent when the TMA kernel or the fused row write do not apply
+    FlatLists<PieceDesc> pass_pieces;
+    FlatLists<uint32_t> pass_tiles;
+    bool pass_built = false, pass_same_as_primary = false;
+    uint32_t pass_hpc = 1, pass_n_cta = 0, pass_max_pieces = 1, pass_max_tiles = 1, pass_stages = 1;
     uint32_t n_slices = 0;  // plan slices: one per CTA, or one per warp in unit mode
     if (tma) {
         // ---- which decomposition? -----------------------------------------------------------
@@ -155,17 +164,34 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         // head tile (0.095 with 8 warps at head_dim 64) for the CTA that holds the longest unit, fixed costs of ~3 us (unit) and ~9 us plus
         // ~0.9 us per 12 parts of the most split request (split).
         const uint32_t TOKu = kTileTokens;
-        std::vector<std::pair<uint32_t, uint32_t>> units;  // (tiles, request * KVH + head)
+        const uint32_t UW = static_cast<uint32_t>(unit_warps(k.D));
+        // Heads per CTA item (hpc): 1 = a unit is a (request, KV head) shared by all warps of a CTA; h > 1 = a
+        // unit is a (request, group of h adjacent KV heads), warp w taking head w % h and part w / h of the
+        // tiles, so that the CTA reads h adjacent 128-byte (256-byte at head_dim 128) chunks of every token
+        // row together. Needs h | KVH and h | warps.
+        // A launch per layer uses hpc = 1 (many small units balance a single layer best; MLC_B200_DECODE_HPC
+        // overrides); the whole-pass launch, which balances across layers, uses the largest h (measured on
+        // B200, 22 layers of 32 requests: 0.78 of the copy bandwidth with h = 1, 0.86 with 2, 0.88 with 4).
+        uint32_t hpc = static_cast<uint32_t>(std::max(env_int("MLC_B200_DECODE_HPC", 1), 1));
+        if (hpc > 1 && (k.KVH % hpc != 0 || UW % hpc != 0)) hpc = 1;
+        using UnitList = std::vector<std::pair<uint32_t, uint32_t>>;  // (tiles of a head x h, request * (KVH / h) + head group)
         uint64_t head_tiles = 0;
-        for (size_t r = 0; r < N; ++r) {
-            const uint32_t t = (eff[r] + TOKu - 1) / TOKu;
-            if (!t) continue;
-            for (uint32_t h = 0; h < k.KVH; ++h) units.emplace_back(t, static_cast<uint32_t>(r * k.KVH + h));
-            head_tiles += static_cast<uint64_t>(t) * k.KVH;
-        }
+        for (size_t r = 0; r < N; ++r) head_tiles += static_cast<uint64_t>((eff[r] + TOKu - 1) / TOKu) * k.KVH;
+        auto make_units = [&](uint32_t h) {
+            UnitList u;
+            const uint32_t groups = static_cast<uint32_t>(k.KVH) / h;
+            for (size_t r = 0; r < N; ++r) {
+                const uint32_t t = (eff[r] + TOKu - 1) / TOKu;
+                if (!t) continue;
+                for (uint32_t hg = 0; hg < groups; ++hg) u.emplace_back(t * h, static_cast<uint32_t>(r * groups + hg));
+            }
+            // (tiles, id) descending so that equal packings come out the same from call to call
+            std::sort(u.begin(), u.end(), [](const auto& x, const auto& y) { return x.first != y.first ? x.first > y.first : x.second < y.second; });
+            return u;
+        };
+        UnitList units = make_units(hpc);
         const int per_sm_u = std::max(env_int("MLC_B200_DECODE_CTAS_PER_SM", 1), 1);
         const uint32_t cta_cap = static_cast<uint32_t>(ctx->sm_count) * per_sm_u;
-        const uint32_t UW = static_cast<uint32_t>(unit_warps(k.D));
         // An item is a unit or, when cutting helps, a run of a unit's tiles: a unit much longer than a
         // CTA's fair share (all tiles / CTAs) is cut into equal runs that go to different CTAs; each
         // leaves a partial in the workspace and the CTA that brings a unit's last part combines them
@@ -186,10 +212,10 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         };
         const double f_dim = static_cast<double>(k.D) / 64.0;
         const double c_lone = k.D == 64 ? 0.095 : 0.135;  // us per head tile on the fullest CTA (8 warps at 64, 4 at 128)
-        auto pack = [&](uint32_t cap_tiles, Packing& pk) {
+        auto pack = [&](const UnitList& ulist, uint32_t cap_tiles, Packing& pk) {
             pk.items.clear();
             pk.n_cut = pk.n_parts_total = 0;
-            for (const auto& u : units) {
+            for (const auto& u : ulist) {
                 uint32_t parts = 1;
                 if (cap_tiles && u.first > cap_tiles + cap_tiles / 4) parts = std::min<uint32_t>((u.first + cap_tiles - 1) / cap_tiles, 64u);
                 for (uint32_t q = 0; q < parts; ++q) {
@@ -229,17 +255,15 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         Packing* chosen = nullptr;
         double t_unit = 0.0;
         if (!units.empty() && k.KVH <= kTileHbMask + 1) {
-            // (tiles, id) descending so that equal packings come out the same from call to call
-            std::sort(units.begin(), units.end(), [](const auto& x, const auto& y) { return x.first != y.first ? x.first > y.first : x.second < y.second; });
             const double f = f_dim;
             const double per_sm_tiles = static_cast<double>(head_tiles) / ctx->sm_count;
             const double t_stream = f * 0.18 * per_sm_tiles;   // all SMs sharing the HBM
-            pack(0, whole);
+            pack(units, 0, whole);
             chosen = &whole;
             t_unit = std::max(whole.critical * 1e-3, t_stream) + 2.0;
             // MLC_B200_DECODE_UNIT_CUT: 0 = never cut, otherwise the run lengths tried are this percentage
             // of 2.5x, 1.5x and 1x the fair share; MLC_B200_DECODE_UNIT_CUT_FORCE=1 cuts at that percentage.
-            const int cut_pct = env_int("MLC_B200_DECODE_UNIT_CUT", 100);
+            const int cut_pct = hpc > 1 ? 0 : env_int("MLC_B200_DECODE_UNIT_CUT", 100);   // head groups are never cut
             const bool force_cut = env_int("MLC_B200_DECODE_UNIT_CUT_FORCE", 0) != 0;
             const uint32_t fair = static_cast<uint32_t>((head_tiles + cta_cap - 1) / cta_cap);
             if (cut_pct > 0 && (force_cut || whole.critical * 1e-3 > 1.3 * t_stream)) {
@@ -250,7 +274,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                     const uint32_t cap_tiles = std::max<uint32_t>(static_cast<uint32_t>(static_cast<uint64_t>(fair) * cut_pct / 100 * mult / 100), 2 * UW);
                     if (cap_tiles == last_cap || units.front().first <= cap_tiles + cap_tiles / 4) continue;
                     last_cap = cap_tiles;
-                    pack(cap_tiles, trial);
+                    pack(units, cap_tiles, trial);
                     const double t_cut = std::max(trial.critical * 1e-3, t_stream) + 2.0;
                     if (trial.n_cut && t_cut < best) {
                         best = t_cut;
@@ -270,33 +294,41 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         }
         stages = static_cast<uint32_t>(std::min<int>(decode_tma_max_stages(k.H, k.KVH, k.D),
                                                      std::max(1, env_int("MLC_B200_DECODE_STAGES", k.D == 128 ? 2 : 3))));
-        if (unit_mode) {
-            // the exchange area of the in-CTA merge must fit beside the rings
-            while (stages > 1 && decode_tma_smem_bytes(k.D, k.H / k.KVH > 8, stages, true) > 227 * 1024 - 1024) --stages;  // 1 KiB for the barriers
-            const Packing& pk = *chosen;
-            n_cta = pk.n_cta;
-            n_slices = n_cta * UW;
-            n_unit_cuts = pk.n_cut;
-            n_slots = (pk.n_parts_total + kDecodeWarps - 1) / kDecodeWarps;   // the workspace is sized in groups of kDecodeWarps parts
+        // Lays a packing out as per-warp piece and tile lists: slice rank * UW + w belongs to warp w of the CTA
+        // with the rank-th largest load (the heaviest start first, and a whole-pass launch deals (layer,
+        // rank) items to the SMs by this rank, see decode_body).
+        auto emit_units = [&](const Packing& pk, uint32_t h, FlatLists<PieceDesc>& pieces, FlatLists<uint32_t>& tiles) {
+            const uint32_t groups = static_cast<uint32_t>(k.KVH) / h;
+            const uint32_t slices = pk.n_cta * UW;
             std::vector<uint32_t> cut_first_slot(pk.n_cut + 1, 0);
             for (const Item& it : pk.items)
                 if (it.n_parts > 1 && it.part == 0) cut_first_slot[it.cut + 1] = it.n_parts;
             for (uint32_t i = 0; i < pk.n_cut; ++i) cut_first_slot[i + 1] += cut_first_slot[i];
-            cta_pieces.reset(n_slices, pk.items.size() * UW);
-            cta_tiles.reset(n_slices, static_cast<size_t>(head_tiles) + n_slices);
-            for (uint32_t c = 0; c < n_cta; ++c) {
+            pieces.reset(slices, pk.items.size() * UW);
+            tiles.reset(slices, static_cast<size_t>(head_tiles) + slices);
+            std::vector<uint32_t> cta_rank(pk.n_cta);
+            std::vector<uint64_t> cta_load(pk.n_cta, 0);
+            for (uint32_t c = 0; c < pk.n_cta; ++c) {
+                cta_rank[c] = c;
+                for (uint32_t ii : pk.cta_items[c]) cta_load[c] += pk.items[ii].cost_ns;
+            }
+            std::stable_sort(cta_rank.begin(), cta_rank.end(), [&](uint32_t x, uint32_t y) { return cta_load[x] > cta_load[y]; });
+            for (uint32_t rank = 0; rank < pk.n_cta; ++rank) {
+                const uint32_t c = cta_rank[rank];
                 for (uint32_t w = 0; w < UW; ++w) {
-                    const uint32_t slice = c * UW + w;
+                    const uint32_t slice = rank * UW + w;
                     for (uint32_t ii : pk.cta_items[c]) {
                         const Item& it = pk.items[ii];
-                        const size_t r = it.id / k.KVH;
-                        const uint32_t h = static_cast<uint32_t>(it.id % k.KVH);
-                        const uint32_t T = (eff[r] + TOKu - 1) / TOKu;       // tiles of the whole unit
-                        const uint32_t run = it.hi - it.lo, share = (run + UW - 1) / UW;
-                        const uint32_t lo = it.lo + std::min(w * share, run), hi = it.lo + std::min((w + 1) * share, run);
+                        const size_t r = it.id / groups;
+                        const uint32_t hd = static_cast<uint32_t>(it.id % groups) * h + w % h;   // this warp's KV head
+                        const uint32_t T = (eff[r] + TOKu - 1) / TOKu;       // tiles of one head of the unit
+                        // the warps of a head (all, or every h-th) share its run of tiles in equal parts
+                        const uint32_t run = (it.hi - it.lo) / h, run_lo = it.lo / h, wparts = UW / h, wp = w / h;
+                        const uint32_t share = (run + wparts - 1) / wparts;
+                        const uint32_t lo = run_lo + std::min(wp * share, run), hi = run_lo + std::min((wp + 1) * share, run);
                         PieceDesc d{};
                         d.req = static_cast<uint32_t>(r);
-                        d.hb = static_cast<uint16_t>(h);   // the KV head itself
+                        d.hb = static_cast<uint16_t>(hd);   // the KV head itself
                         d.tile_begin = lo;
                         d.n_tiles = hi - lo;
                         d.n_parts = static_cast<uint16_t>(it.n_parts);
@@ -308,19 +340,52 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
                         const bool has_last = hi == T && hi > lo;
                         d.last_valid = static_cast<uint16_t>(has_last ? eff[r] - (T - 1) * TOKu : TOKu);
                         d.flags = (fusable && has_last) ? 1u : 0u;
-                        cta_pieces.push(slice, d);
+                        pieces.push(slice, d);
                         for (uint32_t t = lo; t < hi; ++t) {
                             const uint64_t tok0 = static_cast<uint64_t>(t) * TOKu;
                             const uint32_t page = pt_flat[pt_off[r] + tok0 / k.P];
                             const uint32_t sub = static_cast<uint32_t>((tok0 % k.P) / TOKu);
                             const uint32_t fresh = (fusable && t + 1 == T) ? kTileFreshBit : 0u;
-                            cta_tiles.push(slice, page | (sub << kTileSubShift) | (h << kTileHbShift) | fresh);
+                            tiles.push(slice, page | (sub << kTileSubShift) | (hd << kTileHbShift) | fresh);
                         }
                     }
                 }
             }
-            cta_pieces.finish();
-            cta_tiles.finish();
+            pieces.finish();
+            tiles.finish();
+        };
+        // the exchange area of the in-CTA merge must fit beside the rings
+        uint32_t unit_stages = stages;
+        while (unit_stages > 1 && decode_tma_smem_bytes(k.D, k.H / k.KVH > 8, unit_stages, true) > 227 * 1024 - 1024) --unit_stages;  // 1 KiB for the barriers
+        pass_stages = unit_stages;
+        if (unit_mode) {
+            stages = unit_stages;
+            unit_mode_hpc = hpc;
+            const Packing& pk = *chosen;
+            n_cta = pk.n_cta;
+            n_slices = n_cta * UW;
+            n_unit_cuts = pk.n_cut;
+            n_slots = (pk.n_parts_total + kDecodeWarps - 1) / kDecodeWarps;   // the workspace is sized in groups of kDecodeWarps parts
+            emit_units(pk, hpc, cta_pieces, cta_tiles);
+        }
+        // ---- the view a whole-pass launch uses: whole units of as many adjacent heads as the warps allow
+        if (fusable && chosen && k.KVH <= kTileHbMask + 1 && env_int("MLC_B200_DECODE_PASS", 1) != 0) {
+            uint32_t h = 1;
+            for (uint32_t c = static_cast<uint32_t>(std::min<size_t>(k.KVH, UW)); c > 1; --c)
+                if (k.KVH % c == 0 && UW % c == 0) { h = c; break; }
+            if (const int forced_h = env_int("MLC_B200_DECODE_PASS_HPC", 0); forced_h > 0 && k.KVH % forced_h == 0 && UW % forced_h == 0)
+                h = static_cast<uint32_t>(forced_h);
+            pass_hpc = h;
+            if (unit_mode && n_unit_cuts == 0 && h == hpc) {
+                pass_same_as_primary = true;
+            } else {
+                const UnitList pass_units = make_units(h);
+                Packing pass_pk;
+                pack(pass_units, 0, pass_pk);
+                pass_n_cta = pass_pk.n_cta;
+                emit_units(pass_pk, h, pass_pieces, pass_tiles);
+            }
+            pass_built = true;
         }
     }
     if (tma && !unit_mode) {
@@ -394,6 +459,12 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         max_pieces = std::max<uint32_t>(max_pieces, cta_pieces.size(i));
         max_tiles = std::max<uint32_t>(max_tiles, cta_tiles.size(i));
     }
+    const bool pass_own = pass_built && !pass_same_as_primary;   // the pass view has lists of its own
+    const uint32_t pass_slices = pass_own ? pass_n_cta * static_cast<uint32_t>(unit_warps(k.D)) : 0;
+    for (uint32_t i = 0; i < pass_slices; ++i) {
+        pass_max_pieces = std::max<uint32_t>(pass_max_pieces, pass_pieces.size(i));
+        pass_max_tiles = std::max<uint32_t>(pass_max_tiles, pass_tiles.size(i));
+    }
 
     // ---- lay the image out
     size_t off = 0;
@@ -408,6 +479,9 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     const size_t off_segs = off;     off = align_up(off + segs.size() * sizeof(SegDesc), 16);
     const size_t off_ids = off;      off = align_up(off + (page_ids ? N * 4 : 0), 16);
     const size_t off_slots = off;    off = align_up(off + (slots ? N * 4 : 0), 16);
+    const size_t off_pcounts = off;  off = align_up(off + size_t(pass_slices) * 8, 16);
+    const size_t off_ppieces = off;  off = align_up(off + (pass_own ? size_t(pass_slices) * pass_max_pieces * sizeof(PieceDesc) + 512 : 0), 16);
+    const size_t off_ptiles = off;   off = align_up(off + (pass_own ? size_t(pass_slices) * pass_max_tiles * 4 + 128 : 0), 16);
     const size_t bytes = std::max<size_t>(off, 16);
 
     if (p.uploaded) MLCB_CUDA(ctx, cudaEventSynchronize(p.uploaded));
@@ -435,6 +509,17 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         counts_h[2 * i + 1] = cta_tiles.size(i);
         std::copy(cta_pieces.data(i), cta_pieces.data(i) + cta_pieces.size(i), pieces_h + size_t(i) * max_pieces);
         std::copy(cta_tiles.data(i), cta_tiles.data(i) + cta_tiles.size(i), tiles_h + size_t(i) * max_tiles);
+    }
+    if (pass_own) {
+        auto* pc = reinterpret_cast<uint32_t*>(p.host + off_pcounts);
+        auto* pp = reinterpret_cast<PieceDesc*>(p.host + off_ppieces);
+        auto* pt = reinterpret_cast<uint32_t*>(p.host + off_ptiles);
+        for (uint32_t i = 0; i < pass_slices; ++i) {
+            pc[2 * i] = pass_pieces.size(i);
+            pc[2 * i + 1] = pass_tiles.size(i);
+            std::copy(pass_pieces.data(i), pass_pieces.data(i) + pass_pieces.size(i), pp + size_t(i) * pass_max_pieces);
+            std::copy(pass_tiles.data(i), pass_tiles.data(i) + pass_tiles.size(i), pt + size_t(i) * pass_max_tiles);
+        }
     }
     if (k.n_flat) std::memcpy(p.host + off_flat, pt_flat, k.n_flat * 4);
     std::memcpy(p.host + off_ptoff, pt_off, (N + 1) * 4);
@@ -466,6 +551,24 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     v.n_slots = n_slots;
     v.n_segs = n_segs;
     v.n_unit_cuts = n_unit_cuts;
+    v.hpc = unit_mode_hpc;
+    // the view of whole-pass launches: the same lists when they already are whole units of the widest head
+    // group, else the second set
+    DecodePlanView& pv = p.view_pass;
+    pv = v;
+    pv.pass_ready = pass_built;
+    if (pass_own) {
+        pv.cta_counts = reinterpret_cast<const uint32_t*>(p.dev + off_pcounts);
+        pv.pieces = reinterpret_cast<const PieceDesc*>(p.dev + off_ppieces);
+        pv.tile_pages = reinterpret_cast<const uint32_t*>(p.dev + off_ptiles);
+        pv.unit_mode = true;
+        pv.stages = pass_stages;
+        pv.n_cta = pass_n_cta;
+        pv.max_pieces = pass_max_pieces;
+        pv.max_tiles = pass_max_tiles;
+        pv.n_slots = pv.n_segs = pv.n_unit_cuts = 0;
+        pv.hpc = pass_hpc;
+    }
     p.d_page_ids = page_ids ? reinterpret_cast<const uint32_t*>(p.dev + off_ids) : nullptr;
     p.d_slots = slots ? reinterpret_cast<const uint32_t*>(p.dev + off_slots) : nullptr;
     return MLC_OK;
@@ -749,6 +852,23 @@ int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
                                          void* const* o, float scale, int q_dtype, int o_dtype) {
     if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
     if (!q || !k_new || !v_new || !k_pages || !v_pages || !o) return ctx->fail(MLC_ERR_INVALID_ARG, "null pointer array");
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    // One launch for the whole pass when the plan keeps every (request, head) inside a CTA: the layers of
+    // this call are independent of one another by contract (all their inputs are given up front), so their
+    // work items can be dealt to the CTAs across layers. MLC_B200_DECODE_PASS=0 keeps one launch per layer.
+    static const bool pass_allowed = env_int("MLC_B200_DECODE_PASS", 1) != 0;
+    if (pass_allowed && !ctx->force_general && decode_pass_supported(plan->view_pass, n_layers) &&
+        (q_dtype == MLC_F32 || q_dtype == MLC_F16) && (o_dtype == MLC_F32 || o_dtype == MLC_F16)) {
+        DeviceGuard guard(ctx->device);
+        const PlanKey& k = plan->key;
+        AttnArgs shape;
+        shape.batch = k.batch; shape.H = k.H; shape.KVH = k.KVH; shape.D = k.D; shape.P = k.P; shape.capacity = k.capacity;
+        shape.scale = scale > 0.f ? scale : 1.0f / std::sqrt(static_cast<float>(k.D));  // mm:7133
+        shape.q_dtype = q_dtype; shape.o_dtype = o_dtype;
+        const int st = launch_decode_pass_tma(ctx, shape, plan->view_pass, n_layers, q, k_new, v_new, k_pages, v_pages, o);
+        if (st == MLC_OK) ctx->last_attention_kernel = 2;
+        if (st != MLC_ERR_UNSUPPORTED) return st;
+    }
     for (size_t l = 0; l < n_layers; ++l) {
         const int st = mlc_encode_paged_decode_step_planned(ctx, plan, q[l], k_new[l], v_new[l], k_pages[l], v_pages[l],
                                                             o[l], scale, q_dtype, o_dtype);
@@ -773,6 +893,42 @@ int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, s
     const size_t o_row = k.batch * k.H * k.D * (o_dtype == MLC_F32 ? 4 : 2);
     if (in_row % 16 || q_bytes % 16 || kv_bytes % 16) return ctx->fail(MLC_ERR_UNSUPPORTED, "rows of the packed input must be multiples of 16 bytes");
     DeviceGuard guard(ctx->device);
+    // Zero-copy form: when the whole pass can be one launch and both host buffers are pinned memory the GPU can
+    // address, the kernel reads Q and the new rows straight from host memory (each row once, a work item
+    // ahead of its use) and writes O straight into it, so the transfers run inside the kernel, beside the KV
+    // stream, instead of in front of and behind it. MLC_B200_DECODE_ZERO_COPY=0 keeps the copy pipeline below.
+    static const bool zero_copy_allowed = env_int("MLC_B200_DECODE_ZERO_COPY", 1) != 0 && env_int("MLC_B200_DECODE_PASS", 1) != 0;
+    if (zero_copy_allowed && !ctx->force_general && decode_pass_supported(plan->view_pass, n_layers)) {
+        cudaPointerAttributes ai{}, ao{};
+        const bool mapped = cudaPointerGetAttributes(&ai, host_in) == cudaSuccess && ai.type == cudaMemoryTypeHost && ai.devicePointer &&
+                            cudaPointerGetAttributes(&ao, host_o) == cudaSuccess && ao.type == cudaMemoryTypeHost && ao.devicePointer;
+        cudaGetLastError();   // a pointer the runtime does not know is not an error here
+        if (mapped) {
+            if (ctx->host_pass_done) {   // an earlier host-buffer pass of the copying form may still read dev_o
+                MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->host_pass_done, 0));
+                ctx->host_pass_done = nullptr;
+            }
+            const char* gin = static_cast<const char*>(ai.devicePointer);
+            char* gout = static_cast<char*>(ao.devicePointer);
+            const void* qv[kMaxPassLayersApi];
+            const void* knv[kMaxPassLayersApi];
+            const void* vnv[kMaxPassLayersApi];
+            void* ov[kMaxPassLayersApi];
+            for (size_t l = 0; l < n_layers; ++l) {
+                qv[l] = gin + l * in_row;
+                knv[l] = gin + l * in_row + q_bytes;
+                vnv[l] = gin + l * in_row + q_bytes + kv_bytes;
+                ov[l] = gout + l * o_row;
+            }
+            AttnArgs shape;
+            shape.batch = k.batch; shape.H = k.H; shape.KVH = k.KVH; shape.D = k.D; shape.P = k.P; shape.capacity = k.capacity;
+            shape.scale = scale > 0.f ? scale : 1.0f / std::sqrt(static_cast<float>(k.D));  // mm:7133
+            shape.q_dtype = q_dtype; shape.o_dtype = o_dtype;
+            const int st = launch_decode_pass_tma(ctx, shape, plan->view_pass, n_layers, qv, knv, vnv, k_pages, v_pages, ov);
+            if (st == MLC_OK) ctx->last_attention_kernel = 2;
+            if (st != MLC_ERR_UNSUPPORTED) return st;
+        }
+    }
     // group boundaries: two layers first and last (little copy time left uncovered), the rest in equal parts
     std::vector<size_t> bounds;
     if (n_groups == 0) n_groups = 5;

@@ -193,6 +193,31 @@ struct DecodeParams {
     // head_dim 64: the first tensor map covers both pools (one TMA instruction per stage); k_off / v_off are
     // the tiles' byte offsets inside a stage (the lower pool comes first)
     uint32_t kv_pair, k_off, v_off;
+    // whole-pass launch: layers of the pass, and the CTAs the (single-layer) plan was made for
+    uint32_t n_layers, plan_ctas;
+    // unit mode: KV heads a CTA works on at a time (1: the W warps share one (request, head); h > 1: warp w
+    // holds head w % h of the item's head group and part w / h of that head's tiles, so that the CTA's
+    // warps fetch h adjacent 128-byte chunks of every token row at about the same time)
+    uint32_t hpc;
+};
+
+// One layer of a whole-pass launch: what differs between the layers of a decode pass.
+struct alignas(64) LayerArgs {
+    CUtensorMap map_k;   // the K/V pair map at head_dim 64 when the pools allow it, else the K pool's
+    CUtensorMap map_v;
+    const void* q;
+    void* o;
+    const __half* k_new;
+    const __half* v_new;
+    __half* k_pool;
+    __half* v_pool;
+    uint32_t kv_pair, k_off, v_off, pad;
+};
+static constexpr int kMaxPassLayers = 64;
+// All layers of a pass as ONE kernel parameter (20 KiB; kernel parameters may be up to 32764 bytes), so that
+// the launch needs no staging copy and is captured whole by a CUDA graph.
+struct PassArgs {
+    LayerArgs layer[kMaxPassLayers];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -337,10 +362,17 @@ __device__ __forceinline__ void merge_segment(const DecodeParams& prm, const Seg
 // shared memory, so there are no global partials and no merge kernel. More warps matter: a warp
 // needs ~0.8 us per 32-token tile (dependent mma.sync / ldmatrix / shuffle chains, one warp per
 // scheduler), so the longest unit's time falls with the number of warps that share it.
-template <int D, bool G16, bool UNIT>
-__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32, 1)
-paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                        const DecodeParams prm) {
+// PASS = true (unit mode only): ONE launch runs every layer of a decode pass. The plan is the one of a
+// single layer (the layers share their page tables), with its CTAs in descending order of load ("ranks").
+// The n_layers x gridDim (layer, rank) items, listed rank-major - i.e. heaviest first - are dealt to the
+// CTAs in serpentine order, one per CTA and round: in round j CTA c takes item j * gridDim + c (even j) or
+// j * gridDim + gridDim - 1 - c (odd j), item k being (rank k / n_layers, layer k % n_layers). Every CTA thus
+// gets n_layers items whose loads add up to nearly the same, whatever the spread inside a layer, and the
+// grid has no tail per layer. Nothing is exchanged between CTAs; a warp's TMA ring runs on across the item
+// boundaries. The layers must be independent of one another (all inputs ready when the launch starts).
+template <int D, bool G16, bool UNIT, bool PASS>
+__device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtensorMap* tmV, const LayerArgs* layers,
+                                            const DecodeParams& prm) {
     constexpr int TOK = kTileTokens;
     constexpr int NT_S = TOK / 8;          // score n-tiles per tile
     constexpr int KSTEPS = D / 16;         // k-steps of Q.K^T
@@ -350,6 +382,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     constexpr uint32_t kStageBytes = 2 * kTileBytes;
     constexpr int ROWSETS = G16 ? 2 : 1;
     constexpr int W = UNIT ? unit_warps(D) : kDecodeWarps;  // warps of this CTA
+    static_assert(!PASS || UNIT, "a whole-pass launch runs unit-mode plans");
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[W][8];
@@ -361,18 +394,86 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t ring = smem_base + warp * stages * kStageBytes;
 
-    // The three plan reads of the prologue are independent of one another, so they
-    // cost one memory round trip together: the CTA's counts, its first 32 tile words
-    // (one per lane) and its first 16 piece descriptors (half a descriptor per lane).
-    // The planner pads both arrays so that these reads stay inside the plan image.
-    const uint32_t vcta = UNIT ? cta * W + warp : cta;  // unit mode: one plan slice per warp
-    const uint32_t* my_tiles = prm.tile_pages + static_cast<size_t>(vcta) * prm.max_tiles;
-    const PieceDesc* my_pieces = prm.pieces + static_cast<size_t>(vcta) * prm.max_pieces;
-    const uint2 counts = __ldg(reinterpret_cast<const uint2*>(prm.cta_counts) + vcta);
-    uint32_t win_base = 0;
-    uint32_t win = __ldg(my_tiles + lane);
-    const uint4 desc_half = __ldg(reinterpret_cast<const uint4*>(my_pieces) + lane);
-    const uint32_t n_pieces = counts.x, n_tiles = counts.y;
+    // ---- the items of this CTA: one per round. Without PASS there is one round: the CTA's own plan slice.
+    const uint32_t n_rounds = PASS ? prm.n_layers : 1u;
+    auto round_item = [&](uint32_t j, uint32_t& rank, uint32_t& layer) {
+        if constexpr (PASS) {
+            const uint32_t V = gridDim.x;
+            const uint32_t k = j * V + ((j & 1u) ? V - 1u - cta : cta);
+            rank = k / prm.n_layers;
+            layer = k - rank * prm.n_layers;
+        } else {
+            rank = cta;
+            layer = 0;
+        }
+    };
+    auto slice_of = [&](uint32_t rank) -> uint32_t { return UNIT ? rank * W + warp : rank; };  // unit mode: one plan slice per warp
+
+    // ---- issue side: walks this warp's tile lists, item after item, ahead of the consume side ----
+    // Every read of the plan it needs is taken one step ahead of its use - the next item's tile count and
+    // first 32 tile words (one per lane) while the current item is being fetched, the next 32 words of a long
+    // list while the current 32 are in use - so that no tile waits on a trip to global memory for its word.
+    uint32_t iss_round = 0, iss_pos = 0, iss_n = 0, iss_layer = 0;
+    const uint32_t* iss_tiles = prm.tile_pages;
+    uint32_t win_base = 0, win = 0, win_nx = 0;
+    uint32_t pf_n = 0, pf_win = 0, pf_layer = 0;      // the following item, prefetched
+    const uint32_t* pf_tiles = prm.tile_pages;
+    auto iss_prefetch = [&](uint32_t j) {
+        uint32_t rank;
+        round_item(j, rank, pf_layer);
+        pf_n = 0;
+        if (PASS && rank >= prm.plan_ctas) return;   // a rank without work in this plan
+        const uint32_t slice = slice_of(rank);
+        pf_tiles = prm.tile_pages + static_cast<size_t>(slice) * prm.max_tiles;
+        // independent loads (one memory round trip). The planner pads the arrays so that the 32-word read
+        // stays inside the plan image.
+        pf_n = __ldg(prm.cta_counts + 2 * slice + 1);
+        pf_win = __ldg(pf_tiles + lane);
+    };
+    auto iss_open = [&](uint32_t j) {   // item j was prefetched
+        iss_round = j;
+        iss_pos = 0;
+        win_base = 0;
+        iss_layer = pf_layer;
+        iss_tiles = pf_tiles;
+        iss_n = pf_n;
+        win = pf_win;
+        if (iss_n > 32u) win_nx = (32u + lane < iss_n) ? __ldg(iss_tiles + 32u + lane) : 0u;
+        if (j + 1u < n_rounds) iss_prefetch(j + 1u);
+    };
+    // the next tile word to fetch, if any is left (moves on to the next item's list when one is used up)
+    auto iss_peek = [&](uint32_t& e) -> bool {
+        while (iss_pos >= iss_n) {
+            if (iss_round + 1u >= n_rounds) return false;
+            iss_open(iss_round + 1u);
+        }
+        if (iss_pos - win_base >= 32u) {  // uniform across the warp; positions advance by one
+            win_base += 32u;
+            win = win_nx;
+            if (win_base + 32u < iss_n) win_nx = (win_base + 32u + lane < iss_n) ? __ldg(iss_tiles + win_base + 32u + lane) : 0u;
+        }
+        e = __shfl_sync(0xffffffffu, win, iss_pos - win_base);
+        return true;
+    };
+
+    // Consume side of round 0: counts and the first 16 piece descriptors (half a descriptor per lane),
+    // read together with the issue side's loads.
+    uint32_t c_rank, c_layer;
+    round_item(0, c_rank, c_layer);
+    iss_prefetch(0);
+    iss_open(0);
+    const bool first_has_work = !(PASS && c_rank >= prm.plan_ctas);
+    uint32_t n_pieces = 0;
+    uint4 desc_half = make_uint4(0u, 0u, 0u, 0u);
+    const PieceDesc* my_pieces = prm.pieces;
+    const uint32_t* my_tiles = prm.tile_pages;
+    if (first_has_work) {
+        const uint32_t slice = slice_of(c_rank);
+        my_pieces = prm.pieces + static_cast<size_t>(slice) * prm.max_pieces;
+        my_tiles = prm.tile_pages + static_cast<size_t>(slice) * prm.max_tiles;
+        n_pieces = __ldg(prm.cta_counts + 2 * slice);
+        desc_half = __ldg(reinterpret_cast<const uint4*>(my_pieces) + lane);
+    }
     auto stamp = [&](int i) {
         if (prm.trace && lane == 0) {
             unsigned long long t;
@@ -388,20 +489,13 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     }
     __syncwarp();
 
-    auto tile_entry = [&](uint32_t j) -> uint32_t {
-        if (j - win_base >= 32u) {  // uniform across the warp
-            win_base = j & ~31u;
-            win = (win_base + lane < n_tiles) ? __ldg(my_tiles + win_base + lane) : 0u;
-        }
-        return __shfl_sync(0xffffffffu, win, j - win_base);
-    };
     // Ring position counters of this warp. They count only tiles of head blocks in
     // which this warp owns a KV head, in the (identical) order of issue and use.
     // (kept as wrapping stage indices and a parity bit: the ring depth is a run-time value, and a
     // division by it per tile costs tens of instructions)
     uint32_t iss_stage = 0, con_stage = 0, con_parity = 0;
-    // Issues the TMA copies of the tile word `e` into the next ring stage.
-    auto issue_word = [&](uint32_t e) {
+    // Issues the TMA copies of the tile word `e` (of layer `layer` in a whole-pass launch) into the next ring stage.
+    auto issue_word = [&](uint32_t e, uint32_t layer) {
         const uint32_t hfield = (e >> kTileHbShift) & kTileHbMask;   // head block, or the head itself in unit mode
         const uint32_t head = UNIT ? hfield : hfield * kDecodeWarps + warp;
         if (!UNIT && head >= prm.KVH) return;  // this warp has no KV head in that head block
@@ -412,57 +506,65 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             const uint32_t dst = ring + s * kStageBytes;
             const int page = static_cast<int>(e & kTilePageMask);
             const int slot0 = static_cast<int>(((e >> kTileSubShift) & 7u) * TOK);
+            const CUtensorMap* mk = PASS ? &layers[layer].map_k : tmK;
+            const CUtensorMap* mv = PASS ? &layers[layer].map_v : tmV;
+            const bool pair = PASS ? layers[layer].kv_pair != 0u : prm.kv_pair != 0u;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(bar, kStageBytes);
-            if (D == 64 && prm.kv_pair) {
-                tma_load_5d(dst, &tmK, bar, 0, static_cast<int>(head), slot0, page, 0);
+            if (D == 64 && pair) {
+                tma_load_5d(dst, mk, bar, 0, static_cast<int>(head), slot0, page, 0);
             } else {
 #pragma unroll
                 for (int sub = 0; sub < SUBS; ++sub) {
-                    tma_load_4d(dst + sub * (TOK * 128), &tmK, bar, sub * 64, static_cast<int>(head), slot0, page);
-                    tma_load_4d(dst + kTileBytes + sub * (TOK * 128), &tmV, bar, sub * 64, static_cast<int>(head), slot0, page);
+                    tma_load_4d(dst + sub * (TOK * 128), mk, bar, sub * 64, static_cast<int>(head), slot0, page);
+                    tma_load_4d(dst + kTileBytes + sub * (TOK * 128), mv, bar, sub * 64, static_cast<int>(head), slot0, page);
                 }
             }
         }
     };
 
-    // Prefetches run ahead over piece boundaries; they need nothing but the tile list.
+    // Prefetches run ahead over piece (and item) boundaries; they need nothing but the tile lists.
     // In a decode step, tiles that hold a row written in this step ("fresh" tiles: the
     // ones containing the new token) are not fetched before griddepcontrol.wait;
     // everything older may be.
-    uint32_t next_issue = 0;  // next CTA-local tile to fetch
-    const uint32_t window = n_tiles < stages ? n_tiles : stages;
+    uint32_t in_flight = 0;   // tiles issued into the ring at start-up (at most the ring depth)
     if (prm.pdl) {
         if (prm.step && prm.early_fetch) {
-            while (next_issue < window) {
-                const uint32_t e = tile_entry(next_issue);
+            uint32_t e;
+            while (in_flight < stages && iss_peek(e)) {
                 if (e & kTileFreshBit) break;
-                issue_word(e);
-                ++next_issue;
+                issue_word(e, iss_layer);
+                ++iss_pos;
+                ++in_flight;
             }
         }
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
-    while (next_issue < window) {
-        issue_word(tile_entry(next_issue));
-        ++next_issue;
+    {
+        uint32_t e;
+        while (in_flight < stages && iss_peek(e)) {
+            issue_word(e, iss_layer);
+            ++iss_pos;
+            ++in_flight;
+        }
     }
     stamp(1);
 
     // Requests that attend to nothing: their O rows are zeros (mm:2254-2257).
-    for (uint32_t i = cta; i < prm.n_zero; i += gridDim.x) {
-        const uint32_t r = prm.zero_rows[i];
+    for (uint32_t i = cta; i < prm.n_zero * n_rounds; i += gridDim.x) {
+        const uint32_t r = prm.zero_rows[i % prm.n_zero];
+        void* o_ptr = PASS ? layers[i / prm.n_zero].o : prm.o;
         for (uint32_t e = threadIdx.x; e < prm.H * D; e += blockDim.x) {
             const size_t idx = static_cast<size_t>(r) * prm.H * D + e;
-            if (prm.o_partial) {
+            if (!PASS && prm.o_partial) {
                 prm.o_partial[idx] = 0.f;
                 if (e % D == 0) {
                     prm.ml_partial[(idx / D) * 2] = -INFINITY;
                     prm.ml_partial[(idx / D) * 2 + 1] = 0.f;
                 }
-            } else if (prm.o_f32) static_cast<float*>(prm.o)[idx] = 0.f;
-            else static_cast<__half*>(prm.o)[idx] = __float2half_rn(0.f);
+            } else if (prm.o_f32) static_cast<float*>(o_ptr)[idx] = 0.f;
+            else static_cast<__half*>(o_ptr)[idx] = __float2half_rn(0.f);
         }
     }
 
@@ -487,66 +589,155 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
         for (int np = 0; np < NT_O / 2; ++np) voff[np] = v_offset(np);
     }
-    uint32_t j = 0;  // CTA-local tile counter (consume side)
+    // A warp whose bounded wait ran out is `dead`: it records the error, fetches and computes nothing more, but
+    // keeps walking its pieces so that it still meets its CTA's barriers (its parts weigh nothing).
     bool dead = false;
+    // Look-ahead of the consume side. A piece starts with two dependent trips to memory (its descriptor, then
+    // the Q rows the descriptor names) before its first MMA; both are taken one piece ahead - across item
+    // boundaries too - wherever registers allow (head_dim 64).
+    constexpr bool kLookAhead = UNIT && D == 64;
+    uint32_t nx_rank = 0, nx_layer = 0, nx_pieces = 0;
+    uint4 nx_desc_half = make_uint4(0u, 0u, 0u, 0u);
+    bool pre_valid = false;          // pre_d0 / pre_d1 / pre_qa hold the piece about to start
+    uint4 pre_d0 = make_uint4(0u, 0u, 0u, 0u), pre_d1 = pre_d0;
+    uint32_t pre_qa[kLookAhead ? KSTEPS : 1][4];
+    auto desc_from = [&](const uint4& halves, uint32_t i, uint4& a, uint4& b) {   // piece i < 16 of a prefetched list
+        a.x = __shfl_sync(0xffffffffu, halves.x, 2 * i);
+        a.y = __shfl_sync(0xffffffffu, halves.y, 2 * i);
+        a.z = __shfl_sync(0xffffffffu, halves.z, 2 * i);
+        a.w = __shfl_sync(0xffffffffu, halves.w, 2 * i);
+        b.x = __shfl_sync(0xffffffffu, halves.x, 2 * i + 1);
+        b.y = __shfl_sync(0xffffffffu, halves.y, 2 * i + 1);
+        b.z = __shfl_sync(0xffffffffu, halves.z, 2 * i + 1);
+        b.w = __shfl_sync(0xffffffffu, halves.w, 2 * i + 1);
+    };
+    // Q fragments (A operand) of one (request, KV head): rows = the query heads of the head's group
+    auto load_q = [&](const void* q_base, uint32_t req, uint32_t head, uint32_t (&qa)[KSTEPS][4]) {
+        const size_t q_row0 = (static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G) * D;
+        const uint32_t qrow_ = lane >> 2, qcol_ = (lane & 3) * 2;
+#pragma unroll
+        for (int rs = 0; rs < 2; ++rs) {
+            const uint32_t row = qrow_ + 8 * rs;
+            const bool live = (rs < ROWSETS) && row < prm.G;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t v = 0;
+                    if (live) {
+                        const size_t idx = q_row0 + static_cast<size_t>(row) * D + kk * 16 + hh * 8 + qcol_;
+                        if (prm.q_f32) {
+                            const float2 f = *reinterpret_cast<const float2*>(static_cast<const float*>(q_base) + idx);
+                            v = pack_half2(f.x, f.y);
+                        } else {
+                            v = *reinterpret_cast<const uint32_t*>(static_cast<const __half*>(q_base) + idx);
+                        }
+                    }
+                    qa[kk][rs + 2 * hh] = v;
+                }
+            }
+        }
+    };
+
+  for (uint32_t round = 0; round < n_rounds; ++round) {
+    // ---- per item: the slice's piece list and, in a whole-pass launch, the layer's buffers
+    const void* q_ptr = prm.q;
+    void* o_ptr = prm.o;
+    const __half *k_new_ptr = prm.k_new, *v_new_ptr = prm.v_new;
+    __half *k_pool_ptr = prm.k_pool, *v_pool_ptr = prm.v_pool;
+    uint32_t k_off = prm.k_off, v_off = prm.v_off;
+    if constexpr (PASS) {
+        if (round > 0) {   // read while the round before was running
+            c_rank = nx_rank;
+            c_layer = nx_layer;
+            n_pieces = nx_pieces;
+            desc_half = nx_desc_half;
+            if (c_rank < prm.plan_ctas) {
+                const uint32_t slice = slice_of(c_rank);
+                my_pieces = prm.pieces + static_cast<size_t>(slice) * prm.max_pieces;
+                my_tiles = prm.tile_pages + static_cast<size_t>(slice) * prm.max_tiles;
+            }
+        }
+        // the next round's piece count and first 16 descriptors: issued now, used a whole item later
+        nx_pieces = 0;
+        if (round + 1 < n_rounds) {
+            round_item(round + 1, nx_rank, nx_layer);
+            if (nx_rank < prm.plan_ctas) {
+                const uint32_t slice = slice_of(nx_rank);
+                nx_pieces = __ldg(prm.cta_counts + 2 * slice);
+                nx_desc_half = __ldg(reinterpret_cast<const uint4*>(prm.pieces + static_cast<size_t>(slice) * prm.max_pieces) + lane);
+            }
+        }
+        if (c_rank >= prm.plan_ctas) {   // the same for every warp of the CTA
+            pre_valid = false;
+            continue;
+        }
+        const LayerArgs& la = layers[c_layer];
+        q_ptr = la.q; o_ptr = la.o;
+        k_new_ptr = la.k_new; v_new_ptr = la.v_new;
+        k_pool_ptr = la.k_pool; v_pool_ptr = la.v_pool;
+        k_off = la.k_off; v_off = la.v_off;
+    }
+    uint32_t j = 0;  // tile counter within the slice (consume side)
 
     uint32_t pi = 0;
-    for (; pi < n_pieces && !dead; ++pi) {
+    for (; pi < n_pieces; ++pi) {
         uint4 d0, d1;
-        if (pi < 16u) {  // prefetched in the prologue: lane 2i holds the first half of piece i
-            d0.x = __shfl_sync(0xffffffffu, desc_half.x, 2 * pi);
-            d0.y = __shfl_sync(0xffffffffu, desc_half.y, 2 * pi);
-            d0.z = __shfl_sync(0xffffffffu, desc_half.z, 2 * pi);
-            d0.w = __shfl_sync(0xffffffffu, desc_half.w, 2 * pi);
-            d1.x = __shfl_sync(0xffffffffu, desc_half.x, 2 * pi + 1);
-            d1.y = __shfl_sync(0xffffffffu, desc_half.y, 2 * pi + 1);
-            d1.z = __shfl_sync(0xffffffffu, desc_half.z, 2 * pi + 1);
-            d1.w = __shfl_sync(0xffffffffu, desc_half.w, 2 * pi + 1);
+        const bool was_pre = kLookAhead && pre_valid;
+        if (was_pre) {
+            d0 = pre_d0;
+            d1 = pre_d1;
+        } else if (pi < 16u) {  // prefetched with the counts: lane 2i holds the first half of piece i
+            desc_from(desc_half, pi, d0, d1);
         } else {
             d0 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi));
             d1 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi) + 1);
         }
-        const uint32_t req = d0.x, piece_tiles = d0.z, part_slot = d0.w;
+        const uint32_t req = d0.x, piece_tiles = dead ? 0u : d0.z, part_slot = d0.w;
         const uint32_t n_parts = d1.z & 0xffffu, hb = d1.z >> 16;
         const uint32_t last_valid = d1.w & 0xffffu;
         const bool fresh_piece = prm.step && ((d1.w >> 16) & 1u);  // its last tile holds the new token
         const uint32_t head = UNIT ? hb : hb * kDecodeWarps + warp;
         if (head >= prm.KVH) {  // keep the tile counter and the prefetch stream in step
             for (uint32_t t = 0; t < piece_tiles; ++t, ++j) {
-                if (next_issue < n_tiles) {
-                    issue_word(tile_entry(next_issue));
-                    ++next_issue;
+                uint32_t e;
+                if (iss_peek(e)) {
+                    issue_word(e, iss_layer);
+                    ++iss_pos;
                 }
             }
             continue;
         }
 
-        // ---- Q fragments (A operand), rows = query heads of this KV head's group
+        // ---- Q fragments of this piece, and the look-ahead for the next one
         uint32_t qa[KSTEPS][4];
-        {
-            const size_t q_row0 = (static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G) * D;
+        if constexpr (kLookAhead) {
+            if (was_pre) {
 #pragma unroll
-            for (int rs = 0; rs < 2; ++rs) {
-                const uint32_t row = qrow + 8 * rs;
-                const bool live = (rs < ROWSETS) && row < prm.G;
+                for (int kk = 0; kk < KSTEPS; ++kk)
 #pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        uint32_t v = 0;
-                        if (live) {
-                            const size_t idx = q_row0 + static_cast<size_t>(row) * D + kk * 16 + hh * 8 + qcol;
-                            if (prm.q_f32) {
-                                const float2 f = *reinterpret_cast<const float2*>(static_cast<const float*>(prm.q) + idx);
-                                v = pack_half2(f.x, f.y);
-                            } else {
-                                v = *reinterpret_cast<const uint32_t*>(static_cast<const __half*>(prm.q) + idx);
-                            }
-                        }
-                        qa[kk][rs + 2 * hh] = v;
-                    }
-                }
+                    for (int i = 0; i < 4; ++i) qa[kk][i] = pre_qa[kk][i];
+            } else {
+                load_q(q_ptr, req, head, qa);
             }
+            pre_valid = false;
+            const void* nq_ptr = q_ptr;
+            if (pi + 1 < n_pieces) {
+                if (pi + 1 < 16u) {
+                    desc_from(desc_half, pi + 1, pre_d0, pre_d1);
+                } else {
+                    pre_d0 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi + 1));
+                    pre_d1 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi + 1) + 1);
+                }
+                pre_valid = true;
+            } else if (PASS && nx_pieces > 0) {   // the first piece of the next item
+                desc_from(nx_desc_half, 0, pre_d0, pre_d1);
+                nq_ptr = layers[nx_layer].q;
+                pre_valid = true;
+            }
+            if (pre_valid) load_q(nq_ptr, pre_d0.x, pre_d1.z >> 16, pre_qa);
+        } else {
+            load_q(q_ptr, req, head, qa);
         }
         // ---- decode step: this step's new K/V row of (request, head), one 16-byte chunk per
         // lane (lanes [0, D/8) hold K, lanes [16, 16 + D/8) hold V). It is written to the pool
@@ -555,7 +746,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         constexpr uint32_t kRowChunks = D / 8;
         const bool row_lane = (lane & 15u) < kRowChunks;
         if (fresh_piece && row_lane) {
-            const __half* src = (lane < 16u ? prm.k_new : prm.v_new) +
+            const __half* src = (lane < 16u ? k_new_ptr : v_new_ptr) +
                                 (static_cast<size_t>(req) * prm.KVH + head) * D + (lane & 15u) * 8;
             new_row = *reinterpret_cast<const uint4*>(src);
         }
@@ -578,11 +769,14 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 dead = true;
                 break;
             }
-            if (j == 0) stamp(2);
+            if (!PASS && j == 0) stamp(2);
             // the next tile word to fetch, taken now so that its shuffle (and every 32nd time the load of
-            // the next window) is long done when lane 0 needs it at the end of the tile
-            const uint32_t e_next = next_issue < n_tiles ? tile_entry(next_issue) : 0u;
-            const uint32_t sK = ring + s * kStageBytes + prm.k_off, sV = ring + s * kStageBytes + prm.v_off;
+            // the next window, or the opening of the next item's list) is long done when lane 0 needs it at
+            // the end of the tile
+            uint32_t e_next = 0u;
+            const bool have_next = iss_peek(e_next);
+            const uint32_t next_layer = iss_layer;
+            const uint32_t sK = ring + s * kStageBytes + k_off, sV = ring + s * kStageBytes + v_off;
             const bool last_tile = t + 1 == piece_tiles;
             const uint32_t nv = last_tile ? last_valid : TOK;
 
@@ -599,7 +793,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                                  "r"(new_row.z), "r"(new_row.w) : "memory");
                     const size_t prow = (static_cast<size_t>(e & kTilePageMask) * prm.P +
                                          ((e >> kTileSubShift) & 7u) * TOK + rowi) * prm.KVH + head;
-                    __half* dstp = (lane < 16u ? prm.k_pool : prm.v_pool) + prow * D + chunk * 8;
+                    __half* dstp = (lane < 16u ? k_pool_ptr : v_pool_ptr) + prow * D + chunk * 8;
                     *reinterpret_cast<uint4*>(dstp) = new_row;
                 }
                 __syncwarp();
@@ -720,13 +914,18 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
             }
             __syncwarp();
-            if (next_issue < n_tiles) {
-                issue_word(e_next);
-                ++next_issue;
+            if (have_next) {
+                issue_word(e_next, next_layer);
+                ++iss_pos;
             }
         }
-        if (dead) break;
-        if (pi == 0) stamp(3);
+        if (dead) {   // this piece's part (and every later one of this warp) weighs nothing
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n) o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f;
+            m_run[0] = m_run[1] = -INFINITY;
+            l_run[0] = l_run[1] = 0.f;
+        }
+        if (!PASS && pi == 0) stamp(3);
 
         // ---- end of piece: row sums over the quad
 #pragma unroll
@@ -754,6 +953,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 mine[(NT_O * 32 + lane) * FR + 2 * rs + 1] = l_run[rs];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            // the warps that hold parts of this warp's head: all of them, or every hpc-th
+            const uint32_t hpc = prm.hpc, wpart = warp / hpc, wgroup = W / hpc;
             float wk[W][2], lstar[2], mstar[2];
 #pragma unroll
             for (int rs = 0; rs < ROWSETS; ++rs) {
@@ -761,7 +962,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 mstar[rs] = -INFINITY;
 #pragma unroll
                 for (int k = 0; k < W; ++k) {
-                    mk[k] = xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs];
+                    const bool same_head = hpc == 1u || (static_cast<uint32_t>(k) % hpc) == (warp % hpc);
+                    mk[k] = same_head ? xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs] : -INFINITY;
                     mstar[rs] = fmaxf(mstar[rs], mk[k]);
                 }
                 lstar[rs] = 0.f;
@@ -783,16 +985,16 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     } else {
                         const float inv = ls[rs] > 0.f ? 1.0f / ls[rs] : 0.f;
                         if (prm.o_f32)
-                            *reinterpret_cast<float2*>(static_cast<float*>(prm.o) + hrow * D + n * 8 + qcol) =
+                            *reinterpret_cast<float2*>(static_cast<float*>(o_ptr) + hrow * D + n * 8 + qcol) =
                                 make_float2(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
                         else
-                            *reinterpret_cast<__half2*>(static_cast<__half*>(prm.o) + hrow * D + n * 8 + qcol) =
+                            *reinterpret_cast<__half2*>(static_cast<__half*>(o_ptr) + hrow * D + n * 8 + qcol) =
                                 __floats2half2_rn(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
                     }
                 }
             };
             auto emit_ml = [&](const float (&ms)[2], const float (&ls)[2]) {
-                if (prm.o_partial && warp == 0 && (lane & 3) == 0) {
+                if (prm.o_partial && wpart == 0 && (lane & 3) == 0) {
 #pragma unroll
                     for (int rs = 0; rs < ROWSETS; ++rs) {
                         const uint32_t row = qrow + 8 * rs;
@@ -804,10 +1006,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
             };
             using FragT = typename std::conditional<G16, float4, float2>::type;
-#pragma unroll
-            for (int nn = 0; nn < (NT_O + W - 1) / W; ++nn) {
-                const int n = nn * W + static_cast<int>(warp);  // this warp's output n-tiles
-                if (NT_O % W != 0 && n >= NT_O) break;
+#pragma unroll 1
+            for (int n = static_cast<int>(wpart); n < NT_O; n += static_cast<int>(wgroup)) {   // this warp's output n-tiles
                 float acc[FR];
 #pragma unroll
                 for (int f = 0; f < FR; ++f) acc[f] = 0.f;
@@ -948,25 +1148,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         if (pi + 1 == n_pieces) stamp(7);
     }
 
-    if (UNIT && dead) {
-        // this warp gave up on a copy: it still meets its CTA's two barriers per remaining piece
-        for (; pi < n_pieces; ++pi) {
-            const uint4 dd = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi) + 1);
-            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
-            if ((dd.z & 0xffffu) > 1u) {  // a cut (request, head): the CTA still counts its arrival
-                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
-                if (threadIdx.x == 0) {
-                    uint32_t* c = prm.seg_counters + dd.y;
-                    uint32_t before;
-                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(c) : "memory");
-                    if (before + 1 == (dd.z & 0xffffu)) *c = 0u;
-                    last_part_flag = 0u;  // nothing is combined from a piece that gave up
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
-        }
-    }
+  }  // rounds
 
     // ---- in-kernel merge of the split segments: segment s belongs to CTA s mod gridDim ----
     // Every CTA of this grid is resident (the grid is at most one CTA per SM and at most two
@@ -997,6 +1179,20 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
         stamp(5);
     }
+}
+
+template <int D, bool G16, bool UNIT>
+__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32, 1)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const DecodeParams prm) {
+    decode_body<D, G16, UNIT, false>(&tmK, &tmV, nullptr, prm);
+}
+
+// Every layer of a decode pass in one launch (see decode_body, PASS).
+template <int D, bool G16>
+__global__ void __launch_bounds__(unit_warps(D) * 32, 1)
+paged_decode_pass_kernel(const __grid_constant__ PassArgs pass, const DecodeParams prm) {
+    decode_body<D, G16, true, true>(nullptr, nullptr, pass.layer, prm);
 }
 
 // ------------------------------------------------------------------------------
@@ -1168,6 +1364,128 @@ static int launch_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams
     return MLC_OK;
 }
 
+// True when one of the two decode launches enqueued before this one on the context writes into either pool.
+static bool recently_written(const mlc_ctx* ctx, const void* k_pool, const void* v_pool) {
+    for (const PoolWrites& w : ctx->recent_writes) {
+        for (const void* p : w.few)
+            if (p && (p == k_pool || p == v_pool)) return true;
+        for (const void* p : w.many)
+            if (p == k_pool || p == v_pool) return true;
+    }
+    return false;
+}
+
+void destroy_pass_args(mlc_ctx* ctx) {
+    delete static_cast<PassArgs*>(ctx->pass_args);
+    ctx->pass_args = nullptr;
+}
+
+template <int D, bool G16>
+static int launch_pass_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams& prm, const PassArgs& pass) {
+    const size_t smem = decode_tma_smem_bytes(D, G16, plan.stages, true);
+    size_t& configured = ctx->decode_smem_set[8 + (D == 128 ? 2 : 0) + (G16 ? 1 : 0)];
+    if (smem > configured) {
+        MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_decode_pass_kernel<D, G16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(smem)));
+        configured = smem;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctx->sm_count));   // one CTA per SM, whatever the plan's CTA count
+    cfg.blockDim = dim3(unit_warps(D) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MLCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, paged_decode_pass_kernel<D, G16>, pass, prm));
+    ++ctx->launches;
+    return MLC_OK;
+}
+
+bool decode_pass_supported(const DecodePlanView& plan, size_t n_layers) {
+    return plan.pass_ready && plan.has_tma && plan.unit_mode && plan.n_unit_cuts == 0 && plan.step_fusable && n_layers >= 2 &&
+           n_layers <= static_cast<size_t>(kMaxPassLayers);
+}
+
+int launch_decode_pass_tma(mlc_ctx* ctx, const AttnArgs& shape, const DecodePlanView& plan, size_t n_layers,
+                           const void* const* q, const void* const* k_new, const void* const* v_new,
+                           void* const* k_pages, void* const* v_pages, void* const* o) {
+    const uint32_t G = static_cast<uint32_t>(shape.H / shape.KVH);
+    const bool g16 = G > 8;
+    static const bool pair_allowed = [] {
+        const char* v = std::getenv("MLC_B200_DECODE_KV_PAIR");
+        return !(v && *v && std::atoi(v) == 0);
+    }();
+    // 20 KiB of kernel parameters, assembled in a buffer the context keeps (no allocation per call)
+    if (!ctx->pass_args) ctx->pass_args = new PassArgs();
+    PassArgs& pass = *static_cast<PassArgs*>(ctx->pass_args);
+    const uint32_t tile_bytes = static_cast<uint32_t>(kTileTokens * shape.D * 2);
+    for (size_t l = 0; l < n_layers; ++l) {
+        AttnArgs a = shape;
+        a.q = q[l]; a.o = o[l]; a.k_new = k_new[l]; a.v_new = v_new[l]; a.k_pages = k_pages[l]; a.v_pages = v_pages[l];
+        if (!a.q || !a.o || !a.k_new || !a.v_new || !a.k_pages || !a.v_pages) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer in layer %zu", l);
+        if (!decode_tma_pointers_supported(a)) return MLC_ERR_UNSUPPORTED;   // the caller falls back to per-layer launches
+        LayerArgs& la = pass.layer[l];
+        const bool kv_pair = pair_allowed && shape.D == 64 && pair_map_possible(a.k_pages, a.v_pages);
+        int st;
+        if (kv_pair) {
+            if ((st = get_tensor_map(ctx, a.k_pages, a, &la.map_k, a.v_pages)) != MLC_OK) return st;
+            la.map_v = la.map_k;
+        } else {
+            if ((st = get_tensor_map(ctx, a.k_pages, a, &la.map_k)) != MLC_OK) return st;
+            if ((st = get_tensor_map(ctx, a.v_pages, a, &la.map_v)) != MLC_OK) return st;
+        }
+        const bool k_first = !kv_pair || reinterpret_cast<uintptr_t>(a.k_pages) < reinterpret_cast<uintptr_t>(a.v_pages);
+        la.q = a.q; la.o = a.o;
+        la.k_new = static_cast<const __half*>(a.k_new);
+        la.v_new = static_cast<const __half*>(a.v_new);
+        la.k_pool = static_cast<__half*>(const_cast<void*>(a.k_pages));
+        la.v_pool = static_cast<__half*>(const_cast<void*>(a.v_pages));
+        la.kv_pair = kv_pair ? 1u : 0u;
+        la.k_off = k_first ? 0u : tile_bytes;
+        la.v_off = k_first ? tile_bytes : 0u;
+        la.pad = 0;
+    }
+    DecodeParams prm{};
+    prm.cta_counts = plan.cta_counts;
+    prm.pieces = plan.pieces;
+    prm.tile_pages = plan.tile_pages;
+    prm.zero_rows = plan.zero_rows;
+    prm.seg_desc = plan.seg_desc;
+    prm.err = ctx->d_err;
+    prm.max_pieces = plan.max_pieces;
+    prm.max_tiles = plan.max_tiles;
+    prm.n_zero = plan.n_zero;
+    prm.H = static_cast<uint32_t>(shape.H);
+    prm.KVH = static_cast<uint32_t>(shape.KVH);
+    prm.G = G;
+    prm.P = static_cast<uint32_t>(shape.P);
+    prm.scale_log2 = shape.scale * 1.4426950408889634f;
+    prm.q_f32 = shape.q_dtype == MLC_F32;
+    prm.o_f32 = shape.o_dtype == MLC_F32;
+    prm.step = 1;
+    prm.pdl = 1;
+    // as in launch_attention_decode_tma: no fetch before the wait from a pool that one of the two decode
+    // launches enqueued just before this one writes (here: any layer's pool)
+    prm.early_fetch = 1;
+    for (size_t l = 0; l < n_layers; ++l)
+        if (recently_written(ctx, k_pages[l], v_pages[l])) prm.early_fetch = 0;
+    ctx->recent_writes[0] = std::move(ctx->recent_writes[1]);
+    ctx->recent_writes[1].few[0] = ctx->recent_writes[1].few[1] = nullptr;
+    ctx->recent_writes[1].many.assign(k_pages, k_pages + n_layers);
+    ctx->recent_writes[1].many.insert(ctx->recent_writes[1].many.end(), v_pages, v_pages + n_layers);
+    prm.stages = plan.stages;
+    prm.n_layers = static_cast<uint32_t>(n_layers);
+    prm.plan_ctas = plan.n_cta;
+    prm.hpc = plan.hpc ? plan.hpc : 1u;
+    prm.trace = nullptr;
+    ctx->trace_ctas = 0;
+    if (shape.D == 64) return g16 ? launch_pass_t<64, true>(ctx, plan, prm, pass) : launch_pass_t<64, false>(ctx, plan, prm, pass);
+    return g16 ? launch_pass_t<128, true>(ctx, plan, prm, pass) : launch_pass_t<128, false>(ctx, plan, prm, pass);
+}
+
 int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan) {
     const uint32_t G = static_cast<uint32_t>(a.H / a.KVH);
     const bool g16 = G > 8;
@@ -1281,14 +1599,13 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     // second has let its dependents go, while the first is still writing its new rows into pool A. Tiles
     // fetched before the wait must not come from a pool that one of the two launches before this one
     // writes, so in that case (passes of one or two layers) the early fetch is left out.
-    prm.early_fetch = 1;
-    for (const void* recent : ctx->recent_step_pools)
-        if (step && recent && (recent == a.k_pages || recent == a.v_pages)) prm.early_fetch = 0;
-    ctx->recent_step_pools[0] = ctx->recent_step_pools[2];
-    ctx->recent_step_pools[1] = ctx->recent_step_pools[3];
-    ctx->recent_step_pools[2] = step ? a.k_pages : nullptr;
-    ctx->recent_step_pools[3] = step ? a.v_pages : nullptr;
+    prm.early_fetch = (step && recently_written(ctx, a.k_pages, a.v_pages)) ? 0 : 1;
+    std::swap(ctx->recent_writes[0], ctx->recent_writes[1]);   // no allocation: the lists keep their storage
+    ctx->recent_writes[1].few[0] = step ? a.k_pages : nullptr;
+    ctx->recent_writes[1].few[1] = step ? a.v_pages : nullptr;
+    ctx->recent_writes[1].many.clear();
     prm.stages = plan.stages;
+    prm.hpc = plan.hpc ? plan.hpc : 1u;
     prm.seg_counters = use_counters ? ctx->d_counters : nullptr;
     if (plan.unit_mode && plan.n_unit_cuts) prm.seg_counters = ext_counters ? ext_counters : ctx->d_counters;
     prm.n_segs = plan.n_segs;

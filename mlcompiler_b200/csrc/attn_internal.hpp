@@ -86,6 +86,8 @@ struct DecodePlanView {            // device addresses inside one plan blob
     uint32_t n_cta = 0, max_pieces = 0, max_tiles = 0, n_zero = 0;
     uint32_t n_slots = 0, n_segs = 0;
     uint32_t n_unit_cuts = 0;      // unit mode: (request, head) units cut over CTAs, one arrival counter each
+    uint32_t hpc = 1;              // unit mode: KV heads a CTA works on at a time (see DecodeParams::hpc)
+    bool pass_ready = false;       // this view was laid out for whole-pass launches
 };
 
 int launch_attention_general(mlc_ctx* ctx, const AttnArgs& a, const uint32_t* d_pt_flat,
@@ -102,6 +104,13 @@ int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, 
                                       const uint32_t* d_slots, size_t P, size_t KVH, size_t D,
                                       size_t batch, const void* k_src, const void* v_src, size_t capacity);
 int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan);
+// Whole-pass launch: every layer's decode step (row write + attention) in one kernel. `shape` carries the
+// plan's shape, scale and dtypes. MLC_ERR_UNSUPPORTED (without an error text) when a layer's pointers do not
+// meet the TMA kernel's alignment rules: the caller then launches layer by layer.
+bool decode_pass_supported(const DecodePlanView& plan, size_t n_layers);
+int launch_decode_pass_tma(mlc_ctx* ctx, const AttnArgs& shape, const DecodePlanView& plan, size_t n_layers,
+                           const void* const* q, const void* const* k_new, const void* const* v_new,
+                           void* const* k_pages, void* const* v_pages, void* const* o);
 
 // Chunked causal prefill on tcgen05 (attn_prefill_tcgen05.cu): D = 128, 64-token pages, fp16 q / o.
 bool prefill_tcgen05_supported(size_t H, size_t KVH, size_t D, size_t P, size_t capacity);

@@ -178,6 +178,7 @@ void mlc_ctx_destroy(mlc_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     destroy_plan_cache(ctx);
     destroy_tmap_cache(ctx);
+    destroy_pass_args(ctx);
     for (auto& kv : ctx->allocs) cudaFree(const_cast<void*>(kv.first));
     for (auto& c : ctx->stage) {
         cudaFreeHost(c.host);

@@ -30,6 +30,12 @@ struct StageChunk {
 // that does not depend on the plan.
 static constexpr size_t kExtCounterBytes = 16384;
 
+// Pools a decode launch writes its step's rows into: two for a layer's launch, all layers' for a whole pass.
+struct PoolWrites {
+    const void* few[2] = {nullptr, nullptr};
+    std::vector<const void*> many;
+};
+
 struct AttnPlanCache;  // attn_api.cu
 struct TensorMapCache; // attn_decode_tma.cu
 
@@ -49,7 +55,8 @@ struct mlc_ctx {
     uint64_t launches = 0;
     uint64_t allocations = 0;       // device and pinned-host allocations made through this context
     uint64_t decode_launches = 0;   // selects the workspace copy of the split-KV kernel
-    const void* recent_step_pools[4] = {nullptr, nullptr, nullptr, nullptr};  // pools written by the last two decode launches
+    mlcb::PoolWrites recent_writes[2];   // pools written by the last two decode launches on this context
+    void* pass_args = nullptr;           // parameter block of the whole-pass decode launch (attn_decode_tma.cu)
     uint64_t ext_launches = 0;      // same for launches on caller-provided (fixed) scratch
     uint32_t* ext_counter_block[2] = {nullptr, nullptr};  // arrival counters inside that scratch, once used
     std::string last_error;
@@ -63,7 +70,7 @@ struct mlc_ctx {
     size_t work_bytes = 0;
     uint32_t* d_counters = nullptr;
     size_t n_counters = 0;
-    size_t decode_smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
+    size_t decode_smem_set[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
     bool prefill_smem_set = false;             // same, for the chunked-prefill kernel
     // copy streams and events of the host-buffer decode pass (created on first use)
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
@@ -128,5 +135,6 @@ int ensure_workspace(mlc_ctx* ctx, size_t bytes, size_t counters);
 size_t resolve_capacity(const mlc_ctx* ctx, const void* pool, size_t claimed, size_t page_bytes);
 void destroy_plan_cache(mlc_ctx* ctx);
 void destroy_tmap_cache(mlc_ctx* ctx);
+void destroy_pass_args(mlc_ctx* ctx);
 
 }  // namespace mlcb

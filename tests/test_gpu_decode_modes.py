@@ -19,6 +19,11 @@ FORCED = [
     ("split", {"MLC_B200_DECODE_MODE": "1", "MLC_B200_DECODE_KV_PAIR": "0"}),
     ("unit", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "0"}),
     ("unit_cut", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "50", "MLC_B200_DECODE_UNIT_CUT_FORCE": "1"}),
+    # several KV heads per CTA item in the per-layer launches too (the whole-pass launch always works that way)
+    ("head_groups", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_HPC": "4"}),
+    # the pass entry points as one launch per layer, and the host-buffer pass through its copy pipeline
+    ("layer_launches", {"MLC_B200_DECODE_PASS": "0"}),
+    ("copy_pipeline", {"MLC_B200_DECODE_ZERO_COPY": "0"}),
 ]
 
 

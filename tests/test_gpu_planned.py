@@ -333,7 +333,8 @@ print("ok")
 
 
 def test_whole_pass_call_equals_layer_by_layer(executor, oracle_mod):
-    """mlc_encode_paged_decode_pass_planned = the per-layer call in a loop: same pools, same outputs."""
+    """mlc_encode_paged_decode_pass_planned = the per-layer call in a loop: same pools, same outputs
+    (within the parity tolerance: the single launch of the pass call groups the work differently)."""
     import torch
     case = synth.make_case(61, [100, 257, 33, 2000], 32, 4, 64)
     layers = 3
@@ -349,18 +350,20 @@ def test_whole_pass_call_equals_layer_by_layer(executor, oracle_mod):
                                                 [dc.k_pool for dc in b], [dc.v_pool for dc in b], outs[layers:])]
     assert executor.encodePagedDecodePassPlanned(plan, *ptrs, case.scale, MLC_F16, MLC_F16), executor.last_error()
     assert executor.flushForwardPassCB(), executor.last_error()
-    for i in range(layers):
-        assert torch.equal(outs[i], outs[layers + i])
-        assert torch.equal(a[i].k_pool, b[i].k_pool) and torch.equal(a[i].v_pool, b[i].v_pool)
     kp, vp, want = oracle_step(oracle_mod, case)
-    assert_attention_close(outs[layers].float().cpu().numpy(), want)
+    for i in range(layers):
+        # the pass call may sum a head's tokens in other parts than the per-layer launch: same result within
+        # the parity tolerance, pools bit for bit
+        assert_attention_close(outs[layers + i].float().cpu().numpy(), outs[i].float().cpu().numpy())
+        assert_attention_close(outs[layers + i].float().cpu().numpy(), want)
+        assert torch.equal(a[i].k_pool, b[i].k_pool) and torch.equal(a[i].v_pool, b[i].v_pool)
     plan.destroy()
 
 
 @pytest.mark.parametrize("layers,groups", [(3, 0), (12, 0), (12, 1), (5, 3)])
 def test_host_buffer_pass_equals_layer_by_layer(executor, layers, groups):
-    """mlc_encode_paged_decode_pass_host = copy in + the per-layer call + copy out, pipelined over groups of
-    layers: same pools and bit-identical outputs, for every way of cutting the layers into groups."""
+    """mlc_encode_paged_decode_pass_host = copy in + the per-layer call + copy out: same pools and the same
+    outputs (within the parity tolerance), for every way of cutting the layers into groups."""
     import torch
     case = synth.make_case(62, [100, 257, 33, 2000], 32, 4, 64)
     N, H, KVH, D = case.N, case.H, case.KVH, case.D
@@ -385,9 +388,10 @@ def test_host_buffer_pass_equals_layer_by_layer(executor, layers, groups):
                                               groups), executor.last_error()
     assert executor.flushForwardPassCB(), executor.last_error()      # host_o is complete here, no further sync
     for i in range(layers):
-        assert torch.equal(host_o[i], want[i].cpu().reshape(N, H, D))
+        # one launch for the pass (rows read from and written to host memory by the kernel) or copies +
+        # a launch per layer: the same result within the parity tolerance, the same pools bit for bit
+        assert_attention_close(host_o[i].float().numpy(), want[i].float().cpu().reshape(N, H, D).numpy())
         assert torch.equal(a[i].k_pool, b[i].k_pool) and torch.equal(a[i].v_pool, b[i].v_pool)
-    assert torch.equal(dev_in.cpu(), host_in)
     plan.destroy()
 
 
