@@ -405,34 +405,39 @@ def run_gpu_arm(args):
                 "us_per_step_min": float(us.min()), "us_per_step_max": float(us.max()),
                 "sm_mhz_per_block": mhz}
 
-    def form(name, dist_stats, launches, note):
+    def form(dist_stats, launches, note):
         us = dist_stats["us_per_step_median"]
         gbs = bytes_step_rank / us / 1e3
         return {"kv_gbps": gbs, "frac_of_peak": gbs / peak, "launches_per_step": launches, **dist_stats, "what": note}
 
     per_block = max(20, (200 + 9) // 10)
-    forms = {}
-    forms["whole_pass"] = form("whole_pass", distribution(graphs["whole_pass"].launch, per_block), launches_per_step["whole_pass"],
-                               "mlc_encode_paged_decode_pass_planned: all layers in one call (layers independent by contract)")
-    forms["layer_by_layer"] = form("layer_by_layer", distribution(graphs["layer_by_layer"].launch, per_block),
-                                   launches_per_step["layer_by_layer"],
-                                   "mlc_encode_paged_decode_step_planned per layer (row write fused into attention), every "
-                                   "launch ordered behind the previous one; us / launches is a throughput interval under "
-                                   "programmatic dependent launch, not a kernel duration")
-    assert ex.flushForwardPassCB(), ex.last_error()
 
     def reference_order_step():
         assert ex.beginForwardPassCB()
         encode_reference_order()
-    assert ex.beginForwardPassCB()
-    l0 = ex.launchCount()
-    encode_reference_order()
-    ref_launches = ex.launchCount() - l0
-    assert ex.flushForwardPassCB(), ex.last_error()
-    forms["reference_call_order"] = form("reference_call_order", distribution(reference_order_step, per_block), ref_launches,
-                                         "what an unchanged reference walker calls: per layer encodeScatterKVPagedBatched (K), "
-                                         "(V), encodePagedFlashAttention with host tables (batched_walker.cpp:299-331); direct "
-                                         "calls, no CUDA graph, host time of the calls included")
+
+    def measure_forms():
+        out = {}
+        out["whole_pass"] = form(distribution(graphs["whole_pass"].launch, per_block), launches_per_step["whole_pass"],
+                                 "mlc_encode_paged_decode_pass_planned: all layers in one call (layers independent by contract)")
+        out["layer_by_layer"] = form(distribution(graphs["layer_by_layer"].launch, per_block), launches_per_step["layer_by_layer"],
+                                     "mlc_encode_paged_decode_step_planned per layer (row write fused into attention), every "
+                                     "launch ordered behind the previous one; us / launches is a throughput interval under "
+                                     "programmatic dependent launch, not a kernel duration")
+        assert ex.flushForwardPassCB(), ex.last_error()
+        assert ex.beginForwardPassCB()
+        l0 = ex.launchCount()
+        encode_reference_order()
+        ref_launches = ex.launchCount() - l0
+        assert ex.flushForwardPassCB(), ex.last_error()
+        out["reference_call_order"] = form(distribution(reference_order_step, per_block), ref_launches,
+                                           "what an unchanged reference walker calls: per layer encodeScatterKVPagedBatched (K), "
+                                           "(V), encodePagedFlashAttention with host tables (batched_walker.cpp:299-331); direct "
+                                           "calls, no CUDA graph, host time of the calls included")
+        return out
+
+    # (--no-forms: a short run for a profiler's launch list - the timed region and the e2e leg only)
+    forms = None if args.no_forms else measure_forms()
     assert ex.flushForwardPassCB(), ex.last_error()
     clocks = sampler.stop()
 
@@ -555,7 +560,6 @@ def run_gpu_arm(args):
                          "launch_timing": launch_timing},
             "timing": {"timed_region_blocks": [b[0] / sz * 1e6 for b, sz in zip(blocks, sizes)],
                        "timed_region_block_sizes": sizes, "unit": "us per step"},
-            "call_forms": forms,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": t_e2e_max / args.steps * 1e3,
                     "ms_per_step_median": float(np.median(e2e_times)) * 1e3,
@@ -566,6 +570,8 @@ def run_gpu_arm(args):
             "gpu_launches": int(gpu_launches),
             "clocks": clocks,
         }
+        if forms is not None:
+            line["call_forms"] = forms
         if secondary is not None:
             line["secondary"] = secondary
         if cpu_baseline:
@@ -591,6 +597,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall-time budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the cfg3 / cfg4 / cfg5 workloads")
+    ap.add_argument("--no-forms", action="store_true", help="skip the per-call-form distributions (short run for a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -169,11 +169,10 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
         // unit is a (request, group of h adjacent KV heads), warp w taking head w % h and part w / h of the
         // tiles, so that the CTA reads h adjacent 128-byte (256-byte at head_dim 128) chunks of every token
         // row together. Needs h | KVH and h | warps.
-        // A launch per layer uses hpc = 1 (many small units balance a single layer best; MLC_B200_DECODE_HPC
-        // overrides); the whole-pass launch, which balances across layers, uses the largest h (measured on
-        // B200, 22 layers of 32 requests: 0.78 of the copy bandwidth with h = 1, 0.86 with 2, 0.88 with 4).
-        uint32_t hpc = static_cast<uint32_t>(std::max(env_int("MLC_B200_DECODE_HPC", 1), 1));
-        if (hpc > 1 && (k.KVH % hpc != 0 || UW % hpc != 0)) hpc = 1;
+        // A launch per layer uses hpc = 1 (many small units balance a single layer best); the whole-pass
+        // launch, which balances across layers, uses the largest h (measured on B200, 22 layers of 32
+        // requests: 0.78 of the copy bandwidth with h = 1, 0.86 with 2, 0.88 with 4).
+        const uint32_t hpc = 1;   // the per-layer kernel
         using UnitList = std::vector<std::pair<uint32_t, uint32_t>>;  // (tiles of a head x h, request * (KVH / h) + head group)
         uint64_t head_tiles = 0;
         for (size_t r = 0; r < N; ++r) head_tiles += static_cast<uint64_t>((eff[r] + TOKu - 1) / TOKu) * k.KVH;
@@ -469,9 +468,9 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     // ---- lay the image out
     size_t off = 0;
     const size_t off_counts = off;   off = align_up(off + size_t(n_slices) * 8, 16);
-    // +512 / +128 bytes: the kernel prologue reads 16 descriptors and 32 tile words per CTA unconditionally
+    // +512 / +256 bytes: the kernel reads 16 descriptors and 64 tile words per plan slice unconditionally
     const size_t off_pieces = off;   off = align_up(off + size_t(n_slices) * max_pieces * sizeof(PieceDesc) + 512, 16);
-    const size_t off_tiles = off;    off = align_up(off + size_t(n_slices) * max_tiles * 4 + 128, 16);
+    const size_t off_tiles = off;    off = align_up(off + size_t(n_slices) * max_tiles * 4 + 256, 16);
     const size_t off_flat = off;     off = align_up(off + k.n_flat * 4, 16);
     const size_t off_ptoff = off;    off = align_up(off + (N + 1) * 4, 16);
     const size_t off_eff = off;      off = align_up(off + N * 4, 16);
@@ -481,7 +480,7 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     const size_t off_slots = off;    off = align_up(off + (slots ? N * 4 : 0), 16);
     const size_t off_pcounts = off;  off = align_up(off + size_t(pass_slices) * 8, 16);
     const size_t off_ppieces = off;  off = align_up(off + (pass_own ? size_t(pass_slices) * pass_max_pieces * sizeof(PieceDesc) + 512 : 0), 16);
-    const size_t off_ptiles = off;   off = align_up(off + (pass_own ? size_t(pass_slices) * pass_max_tiles * 4 + 128 : 0), 16);
+    const size_t off_ptiles = off;   off = align_up(off + (pass_own ? size_t(pass_slices) * pass_max_tiles * 4 + 256 : 0), 16);
     const size_t bytes = std::max<size_t>(off, 16);
 
     if (p.uploaded) MLCB_CUDA(ctx, cudaEventSynchronize(p.uploaded));
@@ -897,8 +896,8 @@ int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, s
     // address, the kernel reads Q and the new rows straight from host memory (each row once, a work item
     // ahead of its use) and writes O straight into it, so the transfers run inside the kernel, beside the KV
     // stream, instead of in front of and behind it. MLC_B200_DECODE_ZERO_COPY=0 keeps the copy pipeline below.
-    static const bool zero_copy_allowed = env_int("MLC_B200_DECODE_ZERO_COPY", 1) != 0 && env_int("MLC_B200_DECODE_PASS", 1) != 0;
-    if (zero_copy_allowed && !ctx->force_general && decode_pass_supported(plan->view_pass, n_layers)) {
+    static const int zero_copy_mode = env_int("MLC_B200_DECODE_PASS", 1) != 0 ? env_int("MLC_B200_DECODE_ZERO_COPY", 1) : 0;
+    if (zero_copy_mode != 0 && !ctx->force_general && decode_pass_supported(plan->view_pass, n_layers)) {
         cudaPointerAttributes ai{}, ao{};
         const bool mapped = cudaPointerGetAttributes(&ai, host_in) == cudaSuccess && ai.type == cudaMemoryTypeHost && ai.devicePointer &&
                             cudaPointerGetAttributes(&ao, host_o) == cudaSuccess && ao.type == cudaMemoryTypeHost && ao.devicePointer;
@@ -910,6 +909,12 @@ int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, s
             }
             const char* gin = static_cast<const char*>(ai.devicePointer);
             char* gout = static_cast<char*>(ao.devicePointer);
+            if (zero_copy_mode == 2) {   // experiment: inputs by one bulk copy, outputs written by the kernel
+                MLCB_CUDA(ctx, cudaMemcpyAsync(dev_in, host_in, n_layers * in_row, cudaMemcpyHostToDevice, ctx->stream));
+                gin = static_cast<const char*>(dev_in);
+            } else if (zero_copy_mode == 3) {   // experiment: inputs read by the kernel, outputs by one bulk copy
+                gout = static_cast<char*>(dev_o);
+            }
             const void* qv[kMaxPassLayersApi];
             const void* knv[kMaxPassLayersApi];
             const void* vnv[kMaxPassLayersApi];
@@ -926,6 +931,8 @@ int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, s
             shape.q_dtype = q_dtype; shape.o_dtype = o_dtype;
             const int st = launch_decode_pass_tma(ctx, shape, plan->view_pass, n_layers, qv, knv, vnv, k_pages, v_pages, ov);
             if (st == MLC_OK) ctx->last_attention_kernel = 2;
+            if (st == MLC_OK && zero_copy_mode == 3)
+                MLCB_CUDA(ctx, cudaMemcpyAsync(host_o, dev_o, n_layers * o_row, cudaMemcpyDeviceToHost, ctx->stream));
             if (st != MLC_ERR_UNSUPPORTED) return st;
         }
     }

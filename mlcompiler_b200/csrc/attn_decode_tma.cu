@@ -199,6 +199,10 @@ struct DecodeParams {
     // holds head w % h of the item's head group and part w / h of that head's tiles, so that the CTA's
     // warps fetch h adjacent 128-byte chunks of every token row at about the same time)
     uint32_t hpc;
+    // whole-pass launch: bytes of the Q block and of the O block of one work item (the hpc * G query heads of a
+    // request's head group are adjacent rows), staged through shared memory so that both cross the memory
+    // system - or the PCIe link, when the caller's buffers are host memory - in whole 16-byte-per-thread rows
+    uint32_t q_block_bytes, o_block_bytes;
 };
 
 // One layer of a whole-pass launch: what differs between the layers of a decode pass.
@@ -354,6 +358,12 @@ __device__ __forceinline__ void write_rows(const DecodeParams& prm, uint32_t req
 template <int D, bool G16, bool CG>
 __device__ __forceinline__ void merge_segment(const DecodeParams& prm, const SegDesc& sd, uint32_t warp, uint32_t lane);
 
+// The kernel of the per-layer entry points. It is the same algorithm as decode_body below with a single item
+// per CTA (no layers to walk, one KV head per CTA item) and is kept as a body of its own on purpose: the tile
+// loop of this kernel runs at about a quarter of an instruction per clock on one warp per scheduler, and the
+// register allocation the compiler finds for it moves its time per layer by several per cent when code is
+// added around the loop (measured: 8.37 us per layer for this body, 8.6 - 8.9 us for the generalised one at
+// the same work), so the generalised body is used where it is needed - the whole-pass launch - only.
 // UNIT = false: the four warps of a CTA are the four KV heads of a head block over the same tiles
 // (dense 512-byte rows), requests are cut over CTAs and split requests merged afterwards.
 // UNIT = true ("unit mode", the planner's choice unless one request dwarfs the others): no request
@@ -362,8 +372,678 @@ __device__ __forceinline__ void merge_segment(const DecodeParams& prm, const Seg
 // shared memory, so there are no global partials and no merge kernel. More warps matter: a warp
 // needs ~0.8 us per 32-token tile (dependent mma.sync / ldmatrix / shuffle chains, one warp per
 // scheduler), so the longest unit's time falls with the number of warps that share it.
-// PASS = true (unit mode only): ONE launch runs every layer of a decode pass. The plan is the one of a
-// single layer (the layers share their page tables), with its CTAs in descending order of load ("ranks").
+template <int D, bool G16, bool UNIT>
+__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32, 1)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const DecodeParams prm) {
+    constexpr int TOK = kTileTokens;
+    constexpr int NT_S = TOK / 8;          // score n-tiles per tile
+    constexpr int KSTEPS = D / 16;         // k-steps of Q.K^T
+    constexpr int NT_O = D / 8;            // output n-tiles
+    constexpr int SUBS = D / 64;           // 64-half boxes per row
+    constexpr uint32_t kTileBytes = TOK * D * 2;       // one of K or V
+    constexpr uint32_t kStageBytes = 2 * kTileBytes;
+    constexpr int ROWSETS = G16 ? 2 : 1;
+    constexpr int W = UNIT ? unit_warps(D) : kDecodeWarps;  // warps of this CTA
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[W][8];
+    __shared__ uint32_t last_part_flag;  // unit mode: this CTA brought the last piece of a (request, head) cut over CTAs
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = blockIdx.x;
+    const uint32_t stages = prm.stages;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t ring = smem_base + warp * stages * kStageBytes;
+
+    // The three plan reads of the prologue are independent of one another, so they
+    // cost one memory round trip together: the CTA's counts, its first 32 tile words
+    // (one per lane) and its first 16 piece descriptors (half a descriptor per lane).
+    // The planner pads both arrays so that these reads stay inside the plan image.
+    const uint32_t vcta = UNIT ? cta * W + warp : cta;  // unit mode: one plan slice per warp
+    const uint32_t* my_tiles = prm.tile_pages + static_cast<size_t>(vcta) * prm.max_tiles;
+    const PieceDesc* my_pieces = prm.pieces + static_cast<size_t>(vcta) * prm.max_pieces;
+    const uint2 counts = __ldg(reinterpret_cast<const uint2*>(prm.cta_counts) + vcta);
+    uint32_t win_base = 0;
+    uint32_t win = __ldg(my_tiles + lane);
+    const uint4 desc_half = __ldg(reinterpret_cast<const uint4*>(my_pieces) + lane);
+    const uint32_t n_pieces = counts.x, n_tiles = counts.y;
+    auto stamp = [&](int i) {
+        if (prm.trace && lane == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            prm.trace[(static_cast<size_t>(cta) * W + warp) * 8 + i] = t;
+        }
+    };
+    stamp(0);
+
+    if (lane == 0) {
+        for (uint32_t s = 0; s < stages; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    auto tile_entry = [&](uint32_t j) -> uint32_t {
+        if (j - win_base >= 32u) {  // uniform across the warp
+            win_base = j & ~31u;
+            win = (win_base + lane < n_tiles) ? __ldg(my_tiles + win_base + lane) : 0u;
+        }
+        return __shfl_sync(0xffffffffu, win, j - win_base);
+    };
+    // Ring position counters of this warp. They count only tiles of head blocks in
+    // which this warp owns a KV head, in the (identical) order of issue and use.
+    // (kept as wrapping stage indices and a parity bit: the ring depth is a run-time value, and a
+    // division by it per tile costs tens of instructions)
+    uint32_t iss_stage = 0, con_stage = 0, con_parity = 0;
+    // Issues the TMA copies of the tile word `e` into the next ring stage.
+    auto issue_word = [&](uint32_t e) {
+        const uint32_t hfield = (e >> kTileHbShift) & kTileHbMask;   // head block, or the head itself in unit mode
+        const uint32_t head = UNIT ? hfield : hfield * kDecodeWarps + warp;
+        if (!UNIT && head >= prm.KVH) return;  // this warp has no KV head in that head block
+        const uint32_t s = iss_stage;
+        iss_stage = (iss_stage + 1 == stages) ? 0u : iss_stage + 1;
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&bars[warp][s]);
+            const uint32_t dst = ring + s * kStageBytes;
+            const int page = static_cast<int>(e & kTilePageMask);
+            const int slot0 = static_cast<int>(((e >> kTileSubShift) & 7u) * TOK);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(bar, kStageBytes);
+            if (D == 64 && prm.kv_pair) {
+                tma_load_5d(dst, &tmK, bar, 0, static_cast<int>(head), slot0, page, 0);
+            } else {
+#pragma unroll
+                for (int sub = 0; sub < SUBS; ++sub) {
+                    tma_load_4d(dst + sub * (TOK * 128), &tmK, bar, sub * 64, static_cast<int>(head), slot0, page);
+                    tma_load_4d(dst + kTileBytes + sub * (TOK * 128), &tmV, bar, sub * 64, static_cast<int>(head), slot0, page);
+                }
+            }
+        }
+    };
+
+    // Prefetches run ahead over piece boundaries; they need nothing but the tile list.
+    // In a decode step, tiles that hold a row written in this step ("fresh" tiles: the
+    // ones containing the new token) are not fetched before griddepcontrol.wait;
+    // everything older may be.
+    uint32_t next_issue = 0;  // next CTA-local tile to fetch
+    const uint32_t window = n_tiles < stages ? n_tiles : stages;
+    if (prm.pdl) {
+        if (prm.step && prm.early_fetch) {
+            while (next_issue < window) {
+                const uint32_t e = tile_entry(next_issue);
+                if (e & kTileFreshBit) break;
+                issue_word(e);
+                ++next_issue;
+            }
+        }
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    while (next_issue < window) {
+        issue_word(tile_entry(next_issue));
+        ++next_issue;
+    }
+    stamp(1);
+
+    // Requests that attend to nothing: their O rows are zeros (mm:2254-2257).
+    for (uint32_t i = cta; i < prm.n_zero; i += gridDim.x) {
+        const uint32_t r = prm.zero_rows[i];
+        for (uint32_t e = threadIdx.x; e < prm.H * D; e += blockDim.x) {
+            const size_t idx = static_cast<size_t>(r) * prm.H * D + e;
+            if (prm.o_partial) {
+                prm.o_partial[idx] = 0.f;
+                if (e % D == 0) {
+                    prm.ml_partial[(idx / D) * 2] = -INFINITY;
+                    prm.ml_partial[(idx / D) * 2 + 1] = 0.f;
+                }
+            } else if (prm.o_f32) static_cast<float*>(prm.o)[idx] = 0.f;
+            else static_cast<__half*>(prm.o)[idx] = __float2half_rn(0.f);
+        }
+    }
+
+    const uint32_t qrow = lane >> 2, qcol = (lane & 3) * 2;
+    // Per-lane byte offsets of the ldmatrix rows inside a swizzled tile, computed once: a K fragment of
+    // score tile n, k-pair kp sits at koff[kp] + n * 1024, a V fragment of token block kt, column pair np
+    // at voff[np] + kt * 2048 (the token index only enters through lane & 7 and a multiple of 8 rows).
+    // Kept in registers at head_dim 64 (6 values); at 128 the kernel has none to spare and recomputes them.
+    constexpr bool kKeepOffsets = (D == 64);
+    auto k_offset = [&](int kp) -> uint32_t {
+        const uint32_t chunk = kp * 4 + (lane >> 3);
+        return (chunk >> 3) * (TOK * 128) + (lane & 7) * 128 + (((chunk & 7) ^ (lane & 7)) << 4);
+    };
+    auto v_offset = [&](int np) -> uint32_t {
+        const uint32_t chunk = np * 2 + (lane >> 4);
+        return (chunk >> 3) * (TOK * 128) + ((lane & 7) + ((lane >> 3) & 1) * 8) * 128 + (((chunk & 7) ^ (lane & 7)) << 4);
+    };
+    uint32_t koff[kKeepOffsets ? KSTEPS / 2 : 1], voff[kKeepOffsets ? NT_O / 2 : 1];
+    if constexpr (kKeepOffsets) {
+#pragma unroll
+        for (int kp = 0; kp < KSTEPS / 2; ++kp) koff[kp] = k_offset(kp);
+#pragma unroll
+        for (int np = 0; np < NT_O / 2; ++np) voff[np] = v_offset(np);
+    }
+    uint32_t j = 0;  // CTA-local tile counter (consume side)
+    bool dead = false;
+
+    uint32_t pi = 0;
+    for (; pi < n_pieces && !dead; ++pi) {
+        uint4 d0, d1;
+        if (pi < 16u) {  // prefetched in the prologue: lane 2i holds the first half of piece i
+            d0.x = __shfl_sync(0xffffffffu, desc_half.x, 2 * pi);
+            d0.y = __shfl_sync(0xffffffffu, desc_half.y, 2 * pi);
+            d0.z = __shfl_sync(0xffffffffu, desc_half.z, 2 * pi);
+            d0.w = __shfl_sync(0xffffffffu, desc_half.w, 2 * pi);
+            d1.x = __shfl_sync(0xffffffffu, desc_half.x, 2 * pi + 1);
+            d1.y = __shfl_sync(0xffffffffu, desc_half.y, 2 * pi + 1);
+            d1.z = __shfl_sync(0xffffffffu, desc_half.z, 2 * pi + 1);
+            d1.w = __shfl_sync(0xffffffffu, desc_half.w, 2 * pi + 1);
+        } else {
+            d0 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi));
+            d1 = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi) + 1);
+        }
+        const uint32_t req = d0.x, piece_tiles = d0.z, part_slot = d0.w;
+        const uint32_t n_parts = d1.z & 0xffffu, hb = d1.z >> 16;
+        const uint32_t last_valid = d1.w & 0xffffu;
+        const bool fresh_piece = prm.step && ((d1.w >> 16) & 1u);  // its last tile holds the new token
+        const uint32_t head = UNIT ? hb : hb * kDecodeWarps + warp;
+        if (head >= prm.KVH) {  // keep the tile counter and the prefetch stream in step
+            for (uint32_t t = 0; t < piece_tiles; ++t, ++j) {
+                if (next_issue < n_tiles) {
+                    issue_word(tile_entry(next_issue));
+                    ++next_issue;
+                }
+            }
+            continue;
+        }
+
+        // ---- Q fragments (A operand), rows = query heads of this KV head's group
+        uint32_t qa[KSTEPS][4];
+        {
+            const size_t q_row0 = (static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G) * D;
+#pragma unroll
+            for (int rs = 0; rs < 2; ++rs) {
+                const uint32_t row = qrow + 8 * rs;
+                const bool live = (rs < ROWSETS) && row < prm.G;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        uint32_t v = 0;
+                        if (live) {
+                            const size_t idx = q_row0 + static_cast<size_t>(row) * D + kk * 16 + hh * 8 + qcol;
+                            if (prm.q_f32) {
+                                const float2 f = *reinterpret_cast<const float2*>(static_cast<const float*>(prm.q) + idx);
+                                v = pack_half2(f.x, f.y);
+                            } else {
+                                v = *reinterpret_cast<const uint32_t*>(static_cast<const __half*>(prm.q) + idx);
+                            }
+                        }
+                        qa[kk][rs + 2 * hh] = v;
+                    }
+                }
+            }
+        }
+        // ---- decode step: this step's new K/V row of (request, head), one 16-byte chunk per
+        // lane (lanes [0, D/8) hold K, lanes [16, 16 + D/8) hold V). It is written to the pool
+        // here and patched over the fresh tile's copy in shared memory below.
+        uint4 new_row = make_uint4(0u, 0u, 0u, 0u);
+        constexpr uint32_t kRowChunks = D / 8;
+        const bool row_lane = (lane & 15u) < kRowChunks;
+        if (fresh_piece && row_lane) {
+            const __half* src = (lane < 16u ? prm.k_new : prm.v_new) +
+                                (static_cast<size_t>(req) * prm.KVH + head) * D + (lane & 15u) * 8;
+            new_row = *reinterpret_cast<const uint4*>(src);
+        }
+
+        float o_acc[NT_O][4];
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f;
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+        for (uint32_t t = 0; t < piece_tiles; ++t, ++j) {
+            const uint32_t s = con_stage;
+            const uint32_t bar = smem_u32(&bars[warp][s]);
+            const uint32_t parity = con_parity;
+            if (++con_stage == stages) {
+                con_stage = 0;
+                con_parity ^= 1u;
+            }
+            if (!mbar_wait_bounded(bar, parity)) {
+                if (lane == 0) atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
+                dead = true;
+                break;
+            }
+            if (j == 0) stamp(2);
+            // the next tile word to fetch, taken now so that its shuffle (and every 32nd time the load of
+            // the next window) is long done when lane 0 needs it at the end of the tile
+            const uint32_t e_next = next_issue < n_tiles ? tile_entry(next_issue) : 0u;
+            const uint32_t sK = ring + s * kStageBytes + prm.k_off, sV = ring + s * kStageBytes + prm.v_off;
+            const bool last_tile = t + 1 == piece_tiles;
+            const uint32_t nv = last_tile ? last_valid : TOK;
+
+            if (fresh_piece && last_tile) {
+                // The new token is the last valid row of this tile; its pool address follows
+                // from the tile word (page, sub-tile).
+                const uint32_t rowi = nv - 1;
+                const uint32_t e = __ldg(my_tiles + j);
+                if (row_lane) {
+                    const uint32_t chunk = lane & 15u;
+                    const uint32_t addr = (lane < 16u ? sK : sV) + (chunk >> 3) * (TOK * 128) + rowi * 128 +
+                                          (((chunk & 7) ^ (rowi & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(new_row.x), "r"(new_row.y),
+                                 "r"(new_row.z), "r"(new_row.w) : "memory");
+                    const size_t prow = (static_cast<size_t>(e & kTilePageMask) * prm.P +
+                                         ((e >> kTileSubShift) & 7u) * TOK + rowi) * prm.KVH + head;
+                    __half* dstp = (lane < 16u ? prm.k_pool : prm.v_pool) + prow * D + chunk * 8;
+                    *reinterpret_cast<uint4*>(dstp) = new_row;
+                }
+                __syncwarp();
+            }
+
+            // ---- S = Q.K^T (fp32)
+            // The shared-memory loads of a group of score tiles are all issued before the first MMA that
+            // needs one (the asm statements keep their order, so load -> mma -> load -> mma would pay
+            // the ldmatrix latency once per pair: ~1200 clocks per tile, measured), and the MMAs run
+            // over independent accumulators in turn.
+            float sc[NT_S][4];
+            constexpr int kScoreGroup = (D == 64) ? NT_S : NT_S / 2;  // 32 fragment registers per group
+#pragma unroll
+            for (int n0 = 0; n0 < NT_S; n0 += kScoreGroup) {
+                uint32_t kb[kScoreGroup][KSTEPS / 2][4];
+#pragma unroll
+                for (int kp = 0; kp < KSTEPS / 2; ++kp) {
+                    const uint32_t addr = sK + (kKeepOffsets ? koff[kKeepOffsets ? kp : 0] : k_offset(kp)) + n0 * 1024;
+                    static_assert(kScoreGroup <= 4, "unrolled by hand below");
+                    ldsm_x4_off<0>(addr, kb[0][kp]);
+                    if constexpr (kScoreGroup > 1) ldsm_x4_off<1024>(addr, kb[1][kp]);
+                    if constexpr (kScoreGroup > 2) ldsm_x4_off<2048>(addr, kb[2][kp]);
+                    if constexpr (kScoreGroup > 3) ldsm_x4_off<3072>(addr, kb[3][kp]);
+                }
+#pragma unroll
+                for (int ni = 0; ni < kScoreGroup; ++ni) sc[n0 + ni][0] = sc[n0 + ni][1] = sc[n0 + ni][2] = sc[n0 + ni][3] = 0.f;
+#pragma unroll
+                for (int kp = 0; kp < KSTEPS / 2; ++kp) {
+#pragma unroll
+                    for (int ni = 0; ni < kScoreGroup; ++ni) mma_16816(sc[n0 + ni], qa[2 * kp], kb[ni][kp][0], kb[ni][kp][1]);
+#pragma unroll
+                    for (int ni = 0; ni < kScoreGroup; ++ni) mma_16816(sc[n0 + ni], qa[2 * kp + 1], kb[ni][kp][2], kb[ni][kp][3]);
+                }
+            }
+            // V rows past the request's last token may hold anything; make them 0 so
+            // that 0-weight times garbage cannot produce NaN.
+            if (nv < TOK) {
+                for (uint32_t i = lane; i < (TOK - nv) * 8 * SUBS; i += 32) {
+                    const uint32_t rowi = nv + (i >> 3) % (TOK - nv), sub = (i >> 3) / (TOK - nv);
+                    const uint32_t addr = sV + sub * (TOK * 128) + rowi * 128 + ((i & 7) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
+
+            // ---- online softmax on this tile (base-2 domain)
+            uint32_t pa[TOK / 16][4];
+#pragma unroll
+            for (int rs = 0; rs < ROWSETS; ++rs) {
+                float tmax = -INFINITY;
+                if (nv < TOK) {  // only a request's last tile is partly valid (warp-uniform)
+#pragma unroll
+                    for (int n = 0; n < NT_S; ++n) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const uint32_t tok = n * 8 + qcol + e;
+                            const float v = tok < nv ? sc[n][2 * rs + e] * prm.scale_log2 : -INFINITY;
+                            sc[n][2 * rs + e] = v;
+                            tmax = fmaxf(tmax, v);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int n = 0; n < NT_S; ++n) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float v = sc[n][2 * rs + e] * prm.scale_log2;
+                            sc[n][2 * rs + e] = v;
+                            tmax = fmaxf(tmax, v);
+                        }
+                    }
+                }
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+                const float m_new = fmaxf(m_run[rs], tmax);  // finite: every tile has >= 1 valid token
+                float psum = 0.f;
+#pragma unroll
+                for (int n = 0; n < NT_S; ++n) {
+                    const float p0 = ex2(sc[n][2 * rs] - m_new), p1 = ex2(sc[n][2 * rs + 1] - m_new);
+                    psum += p0 + p1;
+                    pa[n >> 1][rs + 2 * (n & 1)] = pack_half2(p0, p1);
+                }
+                // The accumulators are rescaled only when some row's maximum moved, which after the
+                // first tiles of a request is rare (warp-uniform test).
+                if (__any_sync(0xffffffffu, m_new > m_run[rs])) {
+                    const float alpha = ex2(m_run[rs] - m_new);  // ex2(-inf) = 0 on the first tile
+                    l_run[rs] *= alpha;
+                    m_run[rs] = m_new;
+#pragma unroll
+                    for (int n = 0; n < NT_O; ++n) {
+                        o_acc[n][2 * rs] *= alpha;
+                        o_acc[n][2 * rs + 1] *= alpha;
+                    }
+                }
+                l_run[rs] += psum;
+            }
+            if (!G16) {
+#pragma unroll
+                for (int kt = 0; kt < TOK / 16; ++kt) pa[kt][1] = pa[kt][3] = 0u;
+            }
+
+            // ---- O += P.V
+            // same batching: the V fragments of 64 output columns first, then their MMAs
+            constexpr int kOutGroup = 4;  // ldmatrix per batch = 16 fragment registers
+#pragma unroll
+            for (int kt = 0; kt < TOK / 16; ++kt) {
+#pragma unroll
+                for (int np0 = 0; np0 < NT_O / 2; np0 += kOutGroup) {
+                    uint32_t vb[kOutGroup][4];
+#pragma unroll
+                    for (int i = 0; i < kOutGroup; ++i)
+                        ldsm_x4_trans(sV + (kKeepOffsets ? voff[kKeepOffsets ? np0 + i : 0] : v_offset(np0 + i)) + kt * 2048, vb[i]);
+#pragma unroll
+                    for (int i = 0; i < kOutGroup; ++i) {
+                        mma_16816(o_acc[2 * (np0 + i)], pa[kt], vb[i][0], vb[i][1]);
+                        mma_16816(o_acc[2 * (np0 + i) + 1], pa[kt], vb[i][2], vb[i][3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (next_issue < n_tiles) {
+                issue_word(e_next);
+                ++next_issue;
+            }
+        }
+        if (dead) break;
+        if (pi == 0) stamp(3);
+
+        // ---- end of piece: row sums over the quad
+#pragma unroll
+        for (int rs = 0; rs < ROWSETS; ++rs) {
+            l_run[rs] += __shfl_xor_sync(0xffffffffu, l_run[rs], 1);
+            l_run[rs] += __shfl_xor_sync(0xffffffffu, l_run[rs], 2);
+        }
+
+        if (UNIT) {
+            // The W warps hold the W parts of this (request, head): exchange the un-normalised
+            // partials through shared memory, then every warp merges and writes its share of the
+            // output columns.
+            constexpr int FR = G16 ? 4 : 2;
+            constexpr uint32_t kXWarpFloats = (NT_O + 1) * 32 * FR;
+            float* xb = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) +
+                        (static_cast<size_t>(W) * stages * kStageBytes) / 4;
+            float* mine = xb + warp * kXWarpFloats;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+                for (int f = 0; f < FR; ++f) mine[(n * 32 + lane) * FR + f] = o_acc[n][f];
+#pragma unroll
+            for (int rs = 0; rs < ROWSETS; ++rs) {
+                mine[(NT_O * 32 + lane) * FR + 2 * rs] = m_run[rs];
+                mine[(NT_O * 32 + lane) * FR + 2 * rs + 1] = l_run[rs];
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            float wk[W][2], lstar[2], mstar[2];
+#pragma unroll
+            for (int rs = 0; rs < ROWSETS; ++rs) {
+                float mk[W];
+                mstar[rs] = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    mk[k] = xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs];
+                    mstar[rs] = fmaxf(mstar[rs], mk[k]);
+                }
+                lstar[rs] = 0.f;
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    wk[k][rs] = (mk[k] == -INFINITY) ? 0.f : ex2(mk[k] - mstar[rs]);  // an empty quarter weighs nothing
+                    lstar[rs] += xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs + 1] * wk[k][rs];
+                }
+            }
+            // Writes rows of O (or of the caller's partial output) for output n-tile n.
+            auto emit = [&](int n, const float (&acc)[FR], const float (&ls)[2]) {
+#pragma unroll
+                for (int rs = 0; rs < ROWSETS; ++rs) {
+                    const uint32_t row = qrow + 8 * rs;
+                    if (row >= prm.G) continue;
+                    const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
+                    if (prm.o_partial) {
+                        *reinterpret_cast<float2*>(prm.o_partial + hrow * D + n * 8 + qcol) = make_float2(acc[2 * rs], acc[2 * rs + 1]);
+                    } else {
+                        const float inv = ls[rs] > 0.f ? 1.0f / ls[rs] : 0.f;
+                        if (prm.o_f32)
+                            *reinterpret_cast<float2*>(static_cast<float*>(prm.o) + hrow * D + n * 8 + qcol) =
+                                make_float2(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
+                        else
+                            *reinterpret_cast<__half2*>(static_cast<__half*>(prm.o) + hrow * D + n * 8 + qcol) =
+                                __floats2half2_rn(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
+                    }
+                }
+            };
+            auto emit_ml = [&](const float (&ms)[2], const float (&ls)[2]) {
+                if (prm.o_partial && warp == 0 && (lane & 3) == 0) {
+#pragma unroll
+                    for (int rs = 0; rs < ROWSETS; ++rs) {
+                        const uint32_t row = qrow + 8 * rs;
+                        if (row >= prm.G) continue;
+                        const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
+                        prm.ml_partial[hrow * 2] = ms[rs] * 0.6931471805599453f;   // natural-log units for the caller
+                        prm.ml_partial[hrow * 2 + 1] = ls[rs];
+                    }
+                }
+            };
+            using FragT = typename std::conditional<G16, float4, float2>::type;
+#pragma unroll
+            for (int nn = 0; nn < (NT_O + W - 1) / W; ++nn) {
+                const int n = nn * W + static_cast<int>(warp);  // this warp's output n-tiles
+                if (NT_O % W != 0 && n >= NT_O) break;
+                float acc[FR];
+#pragma unroll
+                for (int f = 0; f < FR; ++f) acc[f] = 0.f;
+#pragma unroll
+                for (int k = 0; k < W; ++k)
+#pragma unroll
+                    for (int f = 0; f < FR; ++f) acc[f] += xb[k * kXWarpFloats + (n * 32 + lane) * FR + f] * wk[k][f >> 1];
+                if (n_parts > 1) {
+                    // a (request, head) cut over CTAs: this CTA's part goes to the workspace, fragment order
+                    FragT* wo = reinterpret_cast<FragT*>(prm.work_o) + (static_cast<size_t>(part_slot) * NT_O + n) * 32 + lane;
+                    if constexpr (G16) *wo = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    else *wo = make_float2(acc[0], acc[1]);
+                } else {
+                    emit(n, acc, lstar);
+                }
+            }
+            if (n_parts > 1) {
+                if (warp == 0) {
+                    FragT* wm = reinterpret_cast<FragT*>(prm.work_ml) + static_cast<size_t>(part_slot) * 32 + lane;
+                    if constexpr (G16) *wm = make_float4(mstar[0], lstar[0], mstar[1], lstar[1]);
+                    else *wm = make_float2(mstar[0], lstar[0]);
+                }
+                // Publish and count: the CTA meets (its stores then happen before whatever thread 0 does next),
+                // thread 0 adds 1 to the (request, head)'s counter with release + acquire semantics at GPU
+                // scope - cumulative, so the whole CTA's stores are visible to whoever sees the count, and the
+                // other parts' stores to this CTA after the second barrier. Whoever brings the last part
+                // combines all of them; nobody waits for another CTA. The last arrival also puts the counter
+                // back to 0 for the next launch (which cannot touch it before this grid has ended: its
+                // arrivals come after griddepcontrol.wait).
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+                if (threadIdx.x == 0) {
+                    uint32_t* c = prm.seg_counters + d1.y;
+                    uint32_t before;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(c) : "memory");
+                    const bool last = before + 1 == n_parts;
+                    if (last) *c = 0u;
+                    last_part_flag = last ? 1u : 0u;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+                if (last_part_flag) {
+                    const uint32_t first_slot = d1.x;
+                    const FragT* pm = reinterpret_cast<const FragT*>(prm.work_ml) + static_cast<size_t>(first_slot) * 32 + lane;
+                    // One pass over the parts in slot order (the result does not depend on who arrived last),
+                    // running maximum as in the tile loop: the (m, l) and the o fragments of a part are loaded
+                    // together, so the pass costs one trip to L2 per few parts rather than two.
+                    constexpr int NN = (NT_O + W - 1) / W;   // output n-tiles of this warp
+                    float ms[2] = {-INFINITY, -INFINITY}, ls[2] = {0.f, 0.f};
+                    float cacc[NN][FR];
+#pragma unroll
+                    for (int nn = 0; nn < NN; ++nn)
+#pragma unroll
+                        for (int f = 0; f < FR; ++f) cacc[nn][f] = 0.f;
+                    const FragT* po = reinterpret_cast<const FragT*>(prm.work_o) + (static_cast<size_t>(first_slot) * NT_O + warp) * 32 + lane;
+                    // the loads of CHUNK parts are issued before the first is used (each is a trip to L2)
+                    constexpr int kPartFloats = FR * (1 + NN);
+                    constexpr int CHUNK = 48 / kPartFloats >= 8 ? 8 : (48 / kPartFloats >= 4 ? 4 : 2);
+                    for (uint32_t k0 = 0; k0 < n_parts; k0 += CHUNK) {
+                        FragT mv[CHUNK], ov[CHUNK][NN];
+#pragma unroll
+                        for (int i = 0; i < CHUNK; ++i) {
+                            const uint32_t k = k0 + i;
+                            const bool valid = k < n_parts;
+                            mv[i] = FragT{};
+                            if (valid) mv[i] = __ldcg(pm + k * 32);
+                            else mv[i].x = -INFINITY;   // skipped below
+                            if constexpr (G16) { if (!valid) reinterpret_cast<float*>(&mv[i])[2] = -INFINITY; }
+#pragma unroll
+                            for (int nn = 0; nn < NN; ++nn) {
+                                const int n = nn * W + static_cast<int>(warp);
+                                ov[i][nn] = FragT{};
+                                if (valid && (NT_O % W == 0 || n < NT_O)) ov[i][nn] = __ldcg(po + (static_cast<size_t>(k) * NT_O + nn * W) * 32);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < CHUNK; ++i) {
+#pragma unroll
+                            for (int rs = 0; rs < ROWSETS; ++rs) {
+                                const float mk = reinterpret_cast<const float*>(&mv[i])[2 * rs];
+                                const float lk = reinterpret_cast<const float*>(&mv[i])[2 * rs + 1];
+                                if (mk == -INFINITY) continue;   // a part without a valid token (or past the end) weighs nothing
+                                const float m_new = fmaxf(ms[rs], mk);
+                                const float alpha = ex2(ms[rs] - m_new), w = ex2(mk - m_new);   // ex2(-inf) = 0 for the first part
+                                ms[rs] = m_new;
+                                ls[rs] = ls[rs] * alpha + lk * w;
+#pragma unroll
+                                for (int nn = 0; nn < NN; ++nn) {
+                                    const float* o2 = reinterpret_cast<const float*>(&ov[i][nn]) + 2 * rs;
+                                    cacc[nn][2 * rs] = cacc[nn][2 * rs] * alpha + o2[0] * w;
+                                    cacc[nn][2 * rs + 1] = cacc[nn][2 * rs + 1] * alpha + o2[1] * w;
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int nn = 0; nn < NN; ++nn) {
+                        const int n = nn * W + static_cast<int>(warp);
+                        if (NT_O % W != 0 && n >= NT_O) break;
+                        emit(n, cacc[nn], ls);
+                    }
+                    emit_ml(ms, ls);
+                }
+            } else {
+                emit_ml(mstar, lstar);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");  // the exchange area is free for the next (request, head)
+            if (pi == 0) stamp(4);
+        } else if (n_parts > 1) {
+            // un-normalised partial -> workspace, fragment order (coalesced). The merge kernel
+            // that follows in the stream reads it; the kernel boundary orders the two.
+            const size_t unit = static_cast<size_t>(part_slot) * kDecodeWarps + warp;
+            if (G16) {
+                float4* wo = reinterpret_cast<float4*>(prm.work_o) + unit * NT_O * 32;
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n)
+                    wo[n * 32 + lane] = make_float4(o_acc[n][0], o_acc[n][1], o_acc[n][2], o_acc[n][3]);
+                reinterpret_cast<float4*>(prm.work_ml)[unit * 32 + lane] =
+                    make_float4(m_run[0], l_run[0], m_run[1], l_run[1]);
+            } else {
+                float2* wo = reinterpret_cast<float2*>(prm.work_o) + unit * NT_O * 32;
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n) wo[n * 32 + lane] = make_float2(o_acc[n][0], o_acc[n][1]);
+                reinterpret_cast<float2*>(prm.work_ml)[unit * 32 + lane] = make_float2(m_run[0], l_run[0]);
+            }
+            if (prm.seg_counters) {
+                // Publish: the warp's stores, a warp barrier (orders them before lane 0's next
+                // operation), then a release reduction on the segment's counter for this warp -
+                // fire and forget, nothing waits for a return value.
+                __syncwarp();
+                if (lane == 0) {
+                    uint32_t* c = prm.seg_counters + static_cast<size_t>(d1.y) * kDecodeWarps + warp;
+                    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c) : "memory");
+                }
+            }
+            if (pi == 0) stamp(4);
+        } else {
+            write_rows<D, G16>(prm, req, head, lane, o_acc, m_run, l_run);
+        }
+        if (pi + 1 == n_pieces) stamp(7);
+    }
+
+    if (UNIT && dead) {
+        // this warp gave up on a copy: it still meets its CTA's two barriers per remaining piece
+        for (; pi < n_pieces; ++pi) {
+            const uint4 dd = __ldg(reinterpret_cast<const uint4*>(my_pieces + pi) + 1);
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            if ((dd.z & 0xffffu) > 1u) {  // a cut (request, head): the CTA still counts its arrival
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+                if (threadIdx.x == 0) {
+                    uint32_t* c = prm.seg_counters + dd.y;
+                    uint32_t before;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(c) : "memory");
+                    if (before + 1 == (dd.z & 0xffffu)) *c = 0u;
+                    last_part_flag = 0u;  // nothing is combined from a piece that gave up
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+        }
+    }
+
+    // ---- in-kernel merge of the split segments: segment s belongs to CTA s mod gridDim ----
+    // Every CTA of this grid is resident (the grid is at most one CTA per SM and at most two
+    // grids overlap), so the pieces a merger waits for are running or done. The wait is bounded.
+    if (prm.seg_counters && !dead) {
+        for (uint32_t seg = cta; seg < prm.n_segs; seg += gridDim.x) {
+            const uint4 sdw = __ldg(reinterpret_cast<const uint4*>(prm.seg_desc) + seg);
+            SegDesc sd;
+            sd.req = sdw.x; sd.hb = sdw.y; sd.first_slot = sdw.z; sd.n_parts = sdw.w;
+            if (sd.hb * kDecodeWarps + warp >= prm.KVH) continue;
+            uint32_t* c = prm.seg_counters + static_cast<size_t>(seg) * kDecodeWarps + warp;
+            uint32_t seen = 0;
+            if (lane == 0) {
+                for (uint32_t i = 0; i < (1u << 20); ++i) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(c) : "memory");
+                    if (v >= sd.n_parts) {
+                        seen = 1;
+                        break;
+                    }
+                }
+                if (seen) *c = 0;  // ready for the next launch (which starts publishing only after this grid is done)
+                else atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT);
+            }
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (!seen) continue;
+            merge_segment<D, G16, true>(prm, sd, warp, lane);
+        }
+        stamp(5);
+    }
+}
+
+// ------------------------------------------------------------------------------
+// every layer of a pass in one launch
+// ------------------------------------------------------------------------------
+// The body of the whole-pass launch (instantiated with UNIT = PASS = true; the flags keep the places visible
+// where it differs from the per-layer kernel above).
+// ONE launch runs every layer of a decode pass. The plan is the one of a single layer (the layers share their
+// page tables), with its CTAs in descending order of load ("ranks"). A CTA item is a (request, group of hpc
+// adjacent KV heads): warp w holds head w % hpc of the group and part w / hpc of that head's tiles, so that the
+// warps of a CTA fetch hpc adjacent 128-byte chunks of every token row at about the same time - whole rows
+// when hpc = KVH - which the memory system serves ~13 % faster than one head's chunks alone (measured).
 // The n_layers x gridDim (layer, rank) items, listed rank-major - i.e. heaviest first - are dealt to the
 // CTAs in serpentine order, one per CTA and round: in round j CTA c takes item j * gridDim + c (even j) or
 // j * gridDim + gridDim - 1 - c (odd j), item k being (rank k / n_layers, layer k % n_layers). Every CTA thus
@@ -438,7 +1118,9 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
         iss_tiles = pf_tiles;
         iss_n = pf_n;
         win = pf_win;
-        if (iss_n > 32u) win_nx = (32u + lane < iss_n) ? __ldg(iss_tiles + 32u + lane) : 0u;
+        // unconditional (the plan image is padded for it): a test on the count would make this load wait for
+        // the count's own trip to memory in the prologue
+        win_nx = __ldg(iss_tiles + 32u + lane);
         if (j + 1u < n_rounds) iss_prefetch(j + 1u);
     };
     // the next tile word to fetch, if any is left (moves on to the next item's list when one is used up)
@@ -461,7 +1143,6 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
     uint32_t c_rank, c_layer;
     round_item(0, c_rank, c_layer);
     iss_prefetch(0);
-    iss_open(0);
     const bool first_has_work = !(PASS && c_rank >= prm.plan_ctas);
     uint32_t n_pieces = 0;
     uint4 desc_half = make_uint4(0u, 0u, 0u, 0u);
@@ -474,6 +1155,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
         n_pieces = __ldg(prm.cta_counts + 2 * slice);
         desc_half = __ldg(reinterpret_cast<const uint4*>(my_pieces) + lane);
     }
+    iss_open(0);   // after the loads above have been issued: all of the prologue's plan reads share one trip to memory
     auto stamp = [&](int i) {
         if (prm.trace && lane == 0) {
             unsigned long long t;
@@ -589,13 +1271,30 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
 #pragma unroll
         for (int np = 0; np < NT_O / 2; ++np) voff[np] = v_offset(np);
     }
+    // Unit mode: the warps that hold parts of this warp's head - all of them, or every hpc-th (a bit per warp) -
+    // this warp's place among them and their number
+    const uint32_t wgroup = UNIT ? W / prm.hpc : 1u, wpart = UNIT ? warp / prm.hpc : 0u;
+    uint32_t same_head_mask = 0;
+#pragma unroll
+    for (int k = 0; k < W; ++k)
+        if (prm.hpc == 1u || static_cast<uint32_t>(k) % prm.hpc == warp % prm.hpc) same_head_mask |= 1u << k;
     // A warp whose bounded wait ran out is `dead`: it records the error, fetches and computes nothing more, but
     // keeps walking its pieces so that it still meets its CTA's barriers (its parts weigh nothing).
     bool dead = false;
     // Look-ahead of the consume side. A piece starts with two dependent trips to memory (its descriptor, then
     // the Q rows the descriptor names) before its first MMA; both are taken one piece ahead - across item
     // boundaries too - wherever registers allow (head_dim 64).
-    constexpr bool kLookAhead = UNIT && D == 64;
+    constexpr bool kLookAhead = PASS && D == 64;   // (in a launch per layer a CTA mostly has one piece: nothing to look ahead to)
+    // Whole-pass launch: the next piece's Q block is copied into shared memory (cp.async, 16 bytes per thread,
+    // the CTA's threads together) while the current piece runs, and a piece's O block is put together in shared
+    // memory and written out by all threads in 16-byte pieces. Two Q buffers (current / next), one O buffer,
+    // behind the exchange area of the in-CTA merge.
+    constexpr bool kStageQ = kLookAhead;
+    constexpr bool kStageO = PASS;
+    constexpr uint32_t kXchgBytes = UNIT ? static_cast<uint32_t>(W) * (NT_O + 1) * 32 * (G16 ? 4 : 2) * 4 : 0;
+    uint8_t* const io_base = smem_raw + (smem_base - smem_u32(smem_raw)) + static_cast<size_t>(W) * stages * kStageBytes + kXchgBytes;
+    uint8_t* const o_stage = io_base + 2u * prm.q_block_bytes;
+    uint32_t q_sel = 0;            // the Q buffer the next prefetch goes to
     uint32_t nx_rank = 0, nx_layer = 0, nx_pieces = 0;
     uint4 nx_desc_half = make_uint4(0u, 0u, 0u, 0u);
     bool pre_valid = false;          // pre_d0 / pre_d1 / pre_qa hold the piece about to start
@@ -712,7 +1411,34 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
         // ---- Q fragments of this piece, and the look-ahead for the next one
         uint32_t qa[KSTEPS][4];
         if constexpr (kLookAhead) {
-            if (was_pre) {
+            if (was_pre && kStageQ) {
+                // staged by the whole CTA during the piece before (complete and visible since that piece's
+                // merge barrier): this warp's head is G rows inside the block
+                const uint8_t* blk = io_base + (q_sel ^ 1u) * prm.q_block_bytes;
+                const size_t esz = prm.q_f32 ? 4 : 2;
+#pragma unroll
+                for (int rs = 0; rs < 2; ++rs) {
+                    const uint32_t row = qrow + 8 * rs;
+                    const bool live = (rs < ROWSETS) && row < prm.G;
+#pragma unroll
+                    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            uint32_t v = 0;
+                            if (live) {
+                                const size_t idx = (static_cast<size_t>(warp % prm.hpc) * prm.G + row) * D + kk * 16 + hh * 8 + qcol;
+                                if (prm.q_f32) {
+                                    const float2 f = *reinterpret_cast<const float2*>(blk + idx * esz);
+                                    v = pack_half2(f.x, f.y);
+                                } else {
+                                    v = *reinterpret_cast<const uint32_t*>(blk + idx * esz);
+                                }
+                            }
+                            qa[kk][rs + 2 * hh] = v;
+                        }
+                    }
+                }
+            } else if (was_pre) {
 #pragma unroll
                 for (int kk = 0; kk < KSTEPS; ++kk)
 #pragma unroll
@@ -735,7 +1461,21 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
                 nq_ptr = layers[nx_layer].q;
                 pre_valid = true;
             }
-            if (pre_valid) load_q(nq_ptr, pre_d0.x, pre_d1.z >> 16, pre_qa);
+            if (pre_valid) {
+                if constexpr (kStageQ) {
+                    // the block of the next piece's head group: its hpc * G query heads are adjacent rows
+                    const uint32_t nhead = pre_d1.z >> 16;
+                    const size_t first_row = static_cast<size_t>(pre_d0.x) * prm.H + static_cast<size_t>(nhead - warp % prm.hpc) * prm.G;
+                    const char* src = static_cast<const char*>(nq_ptr) + first_row * D * (prm.q_f32 ? 4 : 2);
+                    const uint32_t dst = smem_u32(io_base + q_sel * prm.q_block_bytes);
+                    for (uint32_t off = threadIdx.x * 16u; off < prm.q_block_bytes; off += blockDim.x * 16u)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + off), "l"(src + off) : "memory");
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    q_sel ^= 1u;
+                } else {
+                    load_q(nq_ptr, pre_d0.x, pre_d1.z >> 16, pre_qa);
+                }
+            }
         } else {
             load_q(q_ptr, req, head, qa);
         }
@@ -934,6 +1674,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
             l_run[rs] += __shfl_xor_sync(0xffffffffu, l_run[rs], 2);
         }
 
+        if constexpr (kStageQ) asm volatile("cp.async.wait_group 0;" ::: "memory");   // the next piece's Q block (made visible by the barrier below)
         if (UNIT) {
             // The W warps hold the W parts of this (request, head): exchange the un-normalised
             // partials through shared memory, then every warp merges and writes its share of the
@@ -953,8 +1694,6 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
                 mine[(NT_O * 32 + lane) * FR + 2 * rs + 1] = l_run[rs];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
-            // the warps that hold parts of this warp's head: all of them, or every hpc-th
-            const uint32_t hpc = prm.hpc, wpart = warp / hpc, wgroup = W / hpc;
             float wk[W][2], lstar[2], mstar[2];
 #pragma unroll
             for (int rs = 0; rs < ROWSETS; ++rs) {
@@ -962,7 +1701,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
                 mstar[rs] = -INFINITY;
 #pragma unroll
                 for (int k = 0; k < W; ++k) {
-                    const bool same_head = hpc == 1u || (static_cast<uint32_t>(k) % hpc) == (warp % hpc);
+                    const bool same_head = (same_head_mask >> k) & 1u;
                     mk[k] = same_head ? xb[k * kXWarpFloats + (NT_O * 32 + lane) * FR + 2 * rs] : -INFINITY;
                     mstar[rs] = fmaxf(mstar[rs], mk[k]);
                 }
@@ -982,6 +1721,14 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
                     const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
                     if (prm.o_partial) {
                         *reinterpret_cast<float2*>(prm.o_partial + hrow * D + n * 8 + qcol) = make_float2(acc[2 * rs], acc[2 * rs + 1]);
+                    } else if (kStageO) {
+                        // into the O block in shared memory: row (head inside the group) * G + row
+                        const float inv = ls[rs] > 0.f ? 1.0f / ls[rs] : 0.f;
+                        const size_t idx = (static_cast<size_t>(warp % prm.hpc) * prm.G + row) * D + n * 8 + qcol;
+                        if (prm.o_f32)
+                            *reinterpret_cast<float2*>(o_stage + idx * 4) = make_float2(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
+                        else
+                            *reinterpret_cast<__half2*>(o_stage + idx * 2) = __floats2half2_rn(acc[2 * rs] * inv, acc[2 * rs + 1] * inv);
                     } else {
                         const float inv = ls[rs] > 0.f ? 1.0f / ls[rs] : 0.f;
                         if (prm.o_f32)
@@ -1113,6 +1860,13 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
                 emit_ml(mstar, lstar);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");  // the exchange area is free for the next (request, head)
+            if constexpr (kStageO) {
+                // the O block is complete: all threads write it out, 16 bytes each, rows of the head group adjacent
+                const size_t first_row = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head - warp % prm.hpc) * prm.G;
+                char* dst = static_cast<char*>(o_ptr) + first_row * D * (prm.o_f32 ? 4 : 2);
+                for (uint32_t off = threadIdx.x * 16u; off < prm.o_block_bytes; off += blockDim.x * 16u)
+                    *reinterpret_cast<uint4*>(dst + off) = *reinterpret_cast<const uint4*>(o_stage + off);
+            }
             if (pi == 0) stamp(4);
         } else if (n_parts > 1) {
             // un-normalised partial -> workspace, fragment order (coalesced). The merge kernel
@@ -1181,12 +1935,6 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
     }
 }
 
-template <int D, bool G16, bool UNIT>
-__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32, 1)
-paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                        const DecodeParams prm) {
-    decode_body<D, G16, UNIT, false>(&tmK, &tmV, nullptr, prm);
-}
 
 // Every layer of a decode pass in one launch (see decode_body, PASS).
 template <int D, bool G16>
@@ -1382,7 +2130,8 @@ void destroy_pass_args(mlc_ctx* ctx) {
 
 template <int D, bool G16>
 static int launch_pass_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams& prm, const PassArgs& pass) {
-    const size_t smem = decode_tma_smem_bytes(D, G16, plan.stages, true);
+    (void)plan;
+    const size_t smem = decode_tma_smem_bytes(D, G16, prm.stages, true) + 2 * prm.q_block_bytes + prm.o_block_bytes;
     size_t& configured = ctx->decode_smem_set[8 + (D == 128 ? 2 : 0) + (G16 ? 1 : 0)];
     if (smem > configured) {
         MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_decode_pass_kernel<D, G16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1476,10 +2225,23 @@ int launch_decode_pass_tma(mlc_ctx* ctx, const AttnArgs& shape, const DecodePlan
     ctx->recent_writes[1].few[0] = ctx->recent_writes[1].few[1] = nullptr;
     ctx->recent_writes[1].many.assign(k_pages, k_pages + n_layers);
     ctx->recent_writes[1].many.insert(ctx->recent_writes[1].many.end(), v_pages, v_pages + n_layers);
-    prm.stages = plan.stages;
     prm.n_layers = static_cast<uint32_t>(n_layers);
     prm.plan_ctas = plan.n_cta;
     prm.hpc = plan.hpc ? plan.hpc : 1u;
+    // Q / O blocks of a work item, staged through shared memory (Q only where the kernel looks a piece ahead)
+    prm.q_block_bytes = shape.D == 64 ? static_cast<uint32_t>(prm.hpc * G * shape.D * (prm.q_f32 ? 4 : 2)) : 0u;
+    prm.o_block_bytes = static_cast<uint32_t>(prm.hpc * G * shape.D * (prm.o_f32 ? 4 : 2));
+    // Ring depth: what fits beside the staging buffers, at most MLC_B200_DECODE_PASS_STAGES (default 2 at
+    // head_dim 64: with every SM streaming all the time a third stage measured 2 % slower, 22 layers x 32
+    // requests; the plan's depth at 128)
+    static const int pass_stages_env = [] {
+        const char* v = std::getenv("MLC_B200_DECODE_PASS_STAGES");
+        return v && *v ? std::atoi(v) : 0;
+    }();
+    prm.stages = pass_stages_env > 0 ? static_cast<uint32_t>(pass_stages_env) : (shape.D == 64 ? 2u : plan.stages);
+    if (prm.stages > 8u) prm.stages = 8u;
+    while (prm.stages > 1 && decode_tma_smem_bytes(shape.D, g16, prm.stages, true) + 2 * prm.q_block_bytes + prm.o_block_bytes > 227 * 1024 - 1024) --prm.stages;
+    if (decode_tma_smem_bytes(shape.D, g16, prm.stages, true) + 2 * prm.q_block_bytes + prm.o_block_bytes > 227 * 1024 - 1024) return MLC_ERR_UNSUPPORTED;
     prm.trace = nullptr;
     ctx->trace_ctas = 0;
     if (shape.D == 64) return g16 ? launch_pass_t<64, true>(ctx, plan, prm, pass) : launch_pass_t<64, false>(ctx, plan, prm, pass);

@@ -19,8 +19,9 @@ FORCED = [
     ("split", {"MLC_B200_DECODE_MODE": "1", "MLC_B200_DECODE_KV_PAIR": "0"}),
     ("unit", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "0"}),
     ("unit_cut", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_UNIT_CUT": "50", "MLC_B200_DECODE_UNIT_CUT_FORCE": "1"}),
-    # several KV heads per CTA item in the per-layer launches too (the whole-pass launch always works that way)
-    ("head_groups", {"MLC_B200_DECODE_MODE": "2", "MLC_B200_DECODE_HPC": "4"}),
+    # the whole-pass launch with one, and with two, KV heads per CTA item instead of as many as fit
+    ("pass_single_heads", {"MLC_B200_DECODE_PASS_HPC": "1"}),
+    ("pass_head_pairs", {"MLC_B200_DECODE_PASS_HPC": "2"}),
     # the pass entry points as one launch per layer, and the host-buffer pass through its copy pipeline
     ("layer_launches", {"MLC_B200_DECODE_PASS": "0"}),
     ("copy_pipeline", {"MLC_B200_DECODE_ZERO_COPY": "0"}),
@@ -30,8 +31,10 @@ FORCED = [
 @pytest.mark.parametrize("name,forced", FORCED, ids=[f[0] for f in FORCED])
 def test_parity_suites_with_the_decomposition_forced(name, forced):
     env = dict(os.environ, **forced)
-    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
-                        "tests/test_gpu_attention.py", "tests/test_gpu_planned.py", "tests/test_gpu_walker.py",
+    files = ["tests/test_gpu_attention.py", "tests/test_gpu_planned.py", "tests/test_gpu_walker.py"]
+    if forced.get("MLC_B200_DECODE_PASS") != "0":      # that file asserts that a pass is ONE launch
+        files.append("tests/test_gpu_pass_launch.py")
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider", *files,
                         "-k", "not in_kernel_merge"],
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, f"{name} mode:\n" + r.stdout[-3000:] + r.stderr[-1000:]
