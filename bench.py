@@ -59,9 +59,9 @@ WORKLOAD = ("cfg2: 22-layer continuous-batching decode, 32 requests, H32/KVH4/D6
 # figure can be scaled to the launch the bench times (traffic grows in proportion to the KV bytes read).
 NCU_TRAFFIC = {
     "kernel": "paged_decode_pass_kernel<64,false>",
-    "dram_bytes": 845_519_360,
-    "kv_bytes": 813_170_688,
-    "commit": "b39ff02 + working tree (whole-pass kernel, one head per CTA item)",
+    "dram_bytes": 834_393_088,        # 828,432,384 read + 5,960,704 written
+    "kv_bytes": 813_959_168,
+    "commit": "0e86983",
 }
 
 
