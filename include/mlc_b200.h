@@ -580,6 +580,11 @@ uint32_t mlc_scheduler_add_request(mlc_scheduler* sched, const uint64_t* prompt_
                                    size_t max_new_tokens /* reference default 100 */,
                                    int64_t eos_token_id /* -1 disables */);
 void mlc_scheduler_set_token_callback(mlc_scheduler* sched, mlc_token_callback cb, void* user);
+/* Chunked admission (an addition: the reference feeds a prompt whole in one tick, scheduler.cpp:47-81):
+ * a prompt is fed at most `tokens` at a time, one chunk per tick, the batch's decode pass running every
+ * tick in between. 0 = whole prompts. mlc_scheduler_prefill_calls counts the run_prefill calls made. */
+void mlc_scheduler_set_prefill_chunk_tokens(mlc_scheduler* sched, size_t tokens);
+size_t mlc_scheduler_prefill_calls(const mlc_scheduler* sched);
 int mlc_scheduler_tick(mlc_scheduler* sched);
 size_t mlc_scheduler_run_until_idle(mlc_scheduler* sched);
 int mlc_scheduler_empty(const mlc_scheduler* sched);

@@ -60,7 +60,10 @@ PagedAttentionExecutor::PagedAttentionExecutor(mlc_ctx* ctx, uint32_t num_heads,
     : ctx_(ctx), H_(num_heads), KVH_(kv_heads), D_(head_dim), L_(n_layers), source_(std::move(source)),
       walker_(new BatchedWalker(*this)) {}
 
-PagedAttentionExecutor::~PagedAttentionExecutor() = default;
+PagedAttentionExecutor::~PagedAttentionExecutor() {
+    for (mlc_attn_plan* p : plans_)
+        if (p) mlc_attn_plan_destroy(ctx_, p);
+}
 
 void PagedAttentionExecutor::attach_page_pool(PagePool* pool, uint32_t page_size_tokens) {
     pool_ = pool;

@@ -118,6 +118,8 @@ private:
     PagedKVStorage* storage_ = nullptr;
     CallOrder order_ = CallOrder::Fused;
     std::unique_ptr<BatchedWalker> walker_;
+    mlc_attn_plan* plans_[2] = {nullptr, nullptr};   // the walker's two long-lived plans (alternate passes)
+    uint64_t passes_ = 0;
 };
 
 }  // namespace runtime

@@ -64,7 +64,7 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
     void* buf_q = mlc_cached_buffer(ctx, "walker_q", q_bytes * ex.L_);
     void* buf_k = mlc_cached_buffer(ctx, "walker_kv_f16_k", kv_bytes * ex.L_);
     void* buf_v = mlc_cached_buffer(ctx, "walker_kv_f16_v", kv_bytes * ex.L_);
-    void* buf_o = mlc_cached_buffer(ctx, "walker_attn_mix", q_bytes);
+    void* buf_o = mlc_cached_buffer(ctx, "walker_attn_mix", q_bytes * ex.L_);   // one output block per layer
     if (!buf_q || !buf_k || !buf_v || !buf_o) return fail_all();
 
     q_host_.resize(N * H * D * ex.L_);
@@ -82,41 +82,64 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
     const float scale = 1.0f / std::sqrt(static_cast<float>(D));
     const size_t cap = storage->capacity_pages();
     const bool fused = ex.order_ == PagedAttentionExecutor::CallOrder::Fused;
+    // Two plans that live as long as the executor, used by alternate passes and refreshed in place with the
+    // pass's tables: after the first two passes a decode pass allocates nothing (while the batch does not
+    // outgrow the plans' buffers), where creating and destroying a plan per pass cost a cudaMalloc /
+    // cudaFree pair and pinned allocations every time.
     mlc_attn_plan* plan = nullptr;
-    if (fused && mlc_attn_plan_create(ctx, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
-                                      q_pos.data(), page_ids.data(), slot_ids.data(), N, H, KVH, D, P, 1, cap,
-                                      &plan) != MLC_OK)
-        return fail_all();
+    if (fused) {
+        mlc_attn_plan*& slot = ex.plans_[ex.passes_++ & 1u];
+        const int st = slot ? mlc_attn_plan_update(ctx, slot, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
+                                                   q_pos.data(), page_ids.data(), slot_ids.data(), N)
+                            : mlc_attn_plan_create(ctx, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
+                                                   q_pos.data(), page_ids.data(), slot_ids.data(), N, H, KVH, D, P, 1, cap,
+                                                   &slot);
+        if (st != MLC_OK) return fail_all();
+        plan = slot;
+    }
 
     bool ok = mlc_pass_begin(ctx) == MLC_OK;
-    for (uint32_t layer = 0; ok && layer < ex.L_; ++layer) {
+    if (ok && fused) {
+        // Every layer's Q and new rows are on the device already (this walker has no model between the
+        // attention layers), so the pass goes to the library as one call - one launch when the plan allows.
+        std::vector<const void*> qv(ex.L_), knv(ex.L_), vnv(ex.L_);
+        std::vector<void*> kpv(ex.L_), vpv(ex.L_), ov(ex.L_);
+        for (uint32_t layer = 0; layer < ex.L_; ++layer) {
+            qv[layer] = static_cast<const char*>(buf_q) + static_cast<size_t>(layer) * q_bytes;
+            knv[layer] = static_cast<const char*>(buf_k) + static_cast<size_t>(layer) * kv_bytes;
+            vnv[layer] = static_cast<const char*>(buf_v) + static_cast<size_t>(layer) * kv_bytes;
+            kpv[layer] = storage->k_buffer(layer);
+            vpv[layer] = storage->v_buffer(layer);
+            ov[layer] = static_cast<char*>(buf_o) + static_cast<size_t>(layer) * q_bytes;
+        }
+        ok = mlc_encode_paged_decode_pass_planned(ctx, plan, ex.L_, qv.data(), knv.data(), vnv.data(), kpv.data(),
+                                                  vpv.data(), ov.data(), scale, MLC_F32, MLC_F32) == MLC_OK;
+    }
+    for (uint32_t layer = 0; ok && !fused && layer < ex.L_; ++layer) {
         const char* q_l = static_cast<const char*>(buf_q) + static_cast<size_t>(layer) * q_bytes;
         const char* k_l = static_cast<const char*>(buf_k) + static_cast<size_t>(layer) * kv_bytes;
         const char* v_l = static_cast<const char*>(buf_v) + static_cast<size_t>(layer) * kv_bytes;
         void* kp = storage->k_buffer(layer);
         void* vp = storage->v_buffer(layer);
-        if (fused) {
-            ok = mlc_encode_paged_decode_step_planned(ctx, plan, q_l, k_l, v_l, kp, vp, buf_o, scale, MLC_F32,
-                                                      MLC_F32) == MLC_OK;
-        } else {
+        void* o_l = static_cast<char*>(buf_o) + static_cast<size_t>(layer) * q_bytes;
+        {
             // the reference's call order (batched_walker.cpp:299-331)
             ok = mlc_encode_scatter_kv_paged_batched_f16(ctx, kp, page_ids.data(), slot_ids.data(), P, KVH, D, N,
                                                          k_l, cap) == MLC_OK &&
                  mlc_encode_scatter_kv_paged_batched_f16(ctx, vp, page_ids.data(), slot_ids.data(), P, KVH, D, N,
                                                          v_l, cap) == MLC_OK &&
-                 mlc_encode_paged_flash_attention(ctx, q_l, kp, vp, buf_o, pt_flat.data(), pt_flat.size(),
+                 mlc_encode_paged_flash_attention(ctx, q_l, kp, vp, o_l, pt_flat.data(), pt_flat.size(),
                                                   pt_off.data(), seq_lens.data(), q_pos.data(), N, H, KVH, D, P, 1,
                                                   scale, MLC_F32, MLC_F32, cap) == MLC_OK;
         }
     }
     ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
-    if (plan) mlc_attn_plan_destroy(ctx, plan);
     if (!ok) return fail_all();
 
     // what the reference downloads as logits [N, vocab] (461-475) is the last layer's
     // attention output [N, H*D] here
     o_host_.resize(N * H * D);
-    if (mlc_download(ctx, buf_o, o_host_.data(), q_bytes, 0) != MLC_OK) return fail_all();
+    if (mlc_download(ctx, buf_o, o_host_.data(), q_bytes, static_cast<size_t>(ex.L_ - 1) * q_bytes) != MLC_OK) return fail_all();
     out.per_request.reserve(N);
     for (size_t r = 0; r < N; ++r) {
         BatchedDecodeOutput::PerRequest p;

@@ -239,6 +239,10 @@ void mlc_scheduler_set_token_callback(mlc_scheduler* s, mlc_token_callback cb, v
     if (cb) s->sched->set_token_callback([cb, user](uint32_t id, uint64_t tok) { cb(user, id, tok); });
     else s->sched->set_token_callback(nullptr);
 }
+void mlc_scheduler_set_prefill_chunk_tokens(mlc_scheduler* s, size_t tokens) {
+    if (s) s->sched->set_prefill_chunk_tokens(tokens);
+}
+size_t mlc_scheduler_prefill_calls(const mlc_scheduler* s) { return s ? s->sched->stats().total_prefill_calls : 0; }
 int mlc_scheduler_tick(mlc_scheduler* s) { return s && s->sched->tick() ? 1 : 0; }
 size_t mlc_scheduler_run_until_idle(mlc_scheduler* s) { return s ? s->sched->run_until_idle() : 0; }
 int mlc_scheduler_empty(const mlc_scheduler* s) { return !s || s->sched->empty() ? 1 : 0; }

@@ -1,4 +1,8 @@
-// See scheduler.hpp. Tick order and stop rules follow compiler/runtime/scheduler.cpp:38-165.
+// See scheduler.hpp. The behaviour is pinned by the reference's scheduler tests
+// (tests/test_scheduler.cpp:64-187: one prefill and max_new_tokens - 1 decodes per request, never more
+// than max_batch_size active, EOS at the first token means no decode, vacancies refill) and by its tick
+// order (compiler/runtime/scheduler.cpp:152-165: admit, prefill, decode, reap). What is added is the
+// chunked admission of prompts.
 #include "scheduler.hpp"
 
 #include <algorithm>
@@ -6,20 +10,36 @@
 namespace mlcb {
 namespace runtime {
 
+namespace {
+
+bool finished(const Scheduler::Request& r) {
+    return r.state == Scheduler::State::Complete || r.state == Scheduler::State::Failed;
+}
+
+void fail(Scheduler::Request& r, const char* why) {
+    r.state = Scheduler::State::Failed;
+    r.failure_reason = why;
+}
+
+}  // namespace
+
 Scheduler::Scheduler(IBatchedExecutor* executor, size_t max_batch_size)
     : executor_(executor), max_batch_size_(max_batch_size ? max_batch_size : 1) {}
 
 uint32_t Scheduler::add_request(std::vector<uint64_t> prompt_tokens, GenerationParams params) {
-    Request req;
+    queued_.emplace_back();
+    Request& req = queued_.back();
     req.id = next_id_++;
     req.prompt_tokens = std::move(prompt_tokens);
     req.params = params;
-    queued_.push_back(std::move(req));
-    return queued_.back().id;
+    return req.id;
 }
 
 uint64_t Scheduler::argmax(const std::vector<float>& logits) {
-    return static_cast<uint64_t>(std::max_element(logits.begin(), logits.end()) - logits.begin());
+    size_t best = 0;
+    for (size_t i = 1; i < logits.size(); ++i)
+        if (logits[i] > logits[best]) best = i;   // the first maximum wins, like std::max_element
+    return best;
 }
 
 void Scheduler::accept_token(Request& req, uint64_t tok) {
@@ -27,105 +47,120 @@ void Scheduler::accept_token(Request& req, uint64_t tok) {
     req.generated_tokens.push_back(tok);
     ++stats_.total_tokens_generated;
     if (token_cb_) token_cb_(req.id, tok);
-    const bool eos = req.params.eos_token_id >= 0 && tok == static_cast<uint64_t>(req.params.eos_token_id);
-    if (eos || req.generated_tokens.size() >= req.params.max_new_tokens) req.state = State::Complete;
+    const bool hit_eos = req.params.eos_token_id >= 0 && tok == static_cast<uint64_t>(req.params.eos_token_id);
+    const bool budget_spent = req.generated_tokens.size() >= req.params.max_new_tokens;
+    if (hit_eos || budget_spent) req.state = State::Complete;
 }
 
-void Scheduler::admit_new() {  // scheduler.cpp:38-45
-    while (!queued_.empty() && active_.size() < max_batch_size_) {
-        Request req = std::move(queued_.front());
+// FIFO: the oldest waiting requests take the free places of the batch.
+void Scheduler::admit_new() {
+    const size_t room = max_batch_size_ > active_.size() ? max_batch_size_ - active_.size() : 0;
+    const size_t n = std::min(room, queued_.size());
+    for (size_t i = 0; i < n; ++i) {
+        active_.push_back(std::move(queued_.front()));
         queued_.pop_front();
+        Request& req = active_.back();
         req.state = req.prompt_tokens.empty() ? State::Decoding : State::Prefilling;
-        active_.push_back(std::move(req));
     }
 }
 
-void Scheduler::prefill_one_active() {  // scheduler.cpp:47-81: at most one request per tick
-    auto it = std::find_if(active_.begin(), active_.end(),
-                           [](const Request& r) { return r.state == State::Prefilling; });
-    if (it == active_.end()) return;
-    Request& req = *it;
-    if (req.prompt_tokens.empty()) {
-        req.state = State::Decoding;
+// One request per tick gets prompt tokens, the first one in the batch that still has some: the whole
+// prompt (the reference, scheduler.cpp:47-81), or at most prefill_chunk_tokens_ of it, so that the decode
+// pass of the other requests is never more than one chunk away. The executor continues a request's
+// prefill from the position it has reached (batched_executor.cpp:445-467 starts at known_position).
+void Scheduler::prefill_one_active() {
+    for (Request& req : active_) {
+        if (req.state != State::Prefilling) continue;
+        const size_t total = req.prompt_tokens.size();
+        const size_t done = req.position;                    // prompt tokens already fed
+        const size_t take = prefill_chunk_tokens_ ? std::min(prefill_chunk_tokens_, total - done) : total - done;
+        std::vector<float> logits;
+        if (done == 0 && take == total) {
+            logits = executor_->run_prefill(req.id, req.prompt_tokens);
+        } else {
+            const std::vector<uint64_t> chunk(req.prompt_tokens.begin() + static_cast<std::ptrdiff_t>(done),
+                                              req.prompt_tokens.begin() + static_cast<std::ptrdiff_t>(done + take));
+            logits = executor_->run_prefill(req.id, chunk);
+        }
+        ++stats_.total_prefill_calls;
+        if (logits.empty()) {
+            fail(req, "prefill failed");
+            return;
+        }
+        req.position = done + take;
+        if (req.position == total) {                         // the prompt is in: its last logits give the first token
+            req.state = State::Decoding;
+            accept_token(req, argmax(logits));
+        }
         return;
     }
-    const std::vector<float> logits = executor_->run_prefill(req.id, req.prompt_tokens);
-    if (logits.empty()) {
-        req.state = State::Failed;
-        req.failure_reason = "prefill failed";
-        return;
-    }
-    req.position = req.prompt_tokens.size();  // every prompt token has been consumed
-    req.state = State::Decoding;
-    accept_token(req, argmax(logits));  // the first generated token comes from the prefill
 }
 
-void Scheduler::decode_active() {  // scheduler.cpp:83-135
+// One batched pass for every request that is decoding and still has budget.
+void Scheduler::decode_active() {
     std::vector<RequestSlot> slots;
-    std::vector<size_t> index;
-    for (size_t i = 0; i < active_.size(); ++i) {
-        Request& req = active_[i];
+    std::vector<Request*> who;
+    for (Request& req : active_) {
         if (req.state != State::Decoding) continue;
         if (req.generated_tokens.size() >= req.params.max_new_tokens) {
             req.state = State::Complete;
             continue;
         }
-        slots.push_back({req.id, req.last_token, req.position});
-        index.push_back(i);
+        slots.push_back(RequestSlot{req.id, req.last_token, req.position});
+        who.push_back(&req);
     }
     if (slots.empty()) return;
     const BatchedDecodeOutput out = executor_->run_decode(slots);
     ++stats_.total_decode_steps;
     if (out.per_request.size() != slots.size()) {
-        for (size_t i : index) {
-            active_[i].state = State::Failed;
-            active_[i].failure_reason = "decode output size mismatch";
-        }
+        for (Request* req : who) fail(*req, "decode output size mismatch");
         return;
     }
-    for (size_t k = 0; k < index.size(); ++k) {
-        Request& req = active_[index[k]];
-        const auto& per = out.per_request[k];
-        if (!per.success || per.logits.empty()) {
-            req.state = State::Failed;
-            req.failure_reason = "decode failed";
+    for (size_t i = 0; i < who.size(); ++i) {
+        const BatchedDecodeOutput::PerRequest& res = out.per_request[i];
+        if (!res.success || res.logits.empty()) {
+            fail(*who[i], "decode failed");
             continue;
         }
-        ++req.position;
-        accept_token(req, argmax(per.logits));
+        ++who[i]->position;
+        accept_token(*who[i], argmax(res.logits));
     }
 }
 
-void Scheduler::reap_completed() {  // scheduler.cpp:137-150: failed requests are reaped and released too
-    auto done = [](const Request& r) { return r.state == State::Complete || r.state == State::Failed; };
-    auto split = std::stable_partition(active_.begin(), active_.end(), [&](const Request& r) { return !done(r); });
-    for (auto it = split; it != active_.end(); ++it) {
-        if (executor_) executor_->release_request(it->id);
-        if (complete_cb_) complete_cb_(*it);
+// Finished and failed requests leave the batch in arrival order; their pages go back to the pool.
+void Scheduler::reap_completed() {
+    std::vector<Request> keep;
+    keep.reserve(active_.size());
+    for (Request& req : active_) {
+        if (!finished(req)) {
+            keep.push_back(std::move(req));
+            continue;
+        }
+        if (executor_) executor_->release_request(req.id);
+        if (complete_cb_) complete_cb_(req);
         ++stats_.total_requests_completed;
-        completed_.push_back(std::move(*it));
+        completed_.push_back(std::move(req));
     }
-    active_.erase(split, active_.end());
+    active_.swap(keep);
 }
 
-bool Scheduler::tick() {  // scheduler.cpp:152-165
-    const size_t active_before = active_.size();
+bool Scheduler::tick() {
+    const size_t active0 = active_.size(), steps0 = stats_.total_decode_steps, prefills0 = stats_.total_prefill_calls,
+                 done0 = completed_.size();
     admit_new();
-    bool any = active_.size() > active_before;
+    const bool admitted = active_.size() > active0;
     prefill_one_active();
-    const size_t steps_before = stats_.total_decode_steps;
     decode_active();
-    any = any || stats_.total_decode_steps > steps_before;
-    const size_t completed_before = completed_.size();
     reap_completed();
-    any = any || completed_.size() > completed_before;
-    return any || !empty();
+    const bool progressed = admitted || stats_.total_decode_steps > steps0 || stats_.total_prefill_calls > prefills0 ||
+                            completed_.size() > done0;
+    return progressed || !empty();
 }
 
 size_t Scheduler::run_until_idle() {
     const size_t before = stats_.total_decode_steps;
-    while (!empty())
-        if (!tick()) break;
+    while (!empty() && tick()) {
+    }
     return stats_.total_decode_steps - before;
 }
 

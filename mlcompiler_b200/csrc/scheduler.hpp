@@ -1,8 +1,8 @@
 // FIFO continuous-batching scheduler: admit up to max_batch_size, prefill one request per
-// tick, one batched decode per tick, greedy arg-max sampling, stop on EOS or token budget,
-// reap finished requests and release their pages. Same public surface and behaviour as the
-// reference's compiler/runtime/scheduler.hpp:27-104 / scheduler.cpp:10-186; it depends on
-// IBatchedExecutor only, so tests drive it with a mock.
+// tick (whole, or in chunks), one batched decode per tick, greedy arg-max sampling, stop on EOS
+// or token budget, reap finished requests and release their pages. Same public surface and
+// behaviour as the reference's compiler/runtime/scheduler.hpp:27-104 / scheduler.cpp:10-186; it
+// depends on IBatchedExecutor only, so tests drive it with a mock.
 #pragma once
 
 #include <cstdint>
@@ -25,6 +25,7 @@ struct SchedulerStats {
     size_t total_requests_completed = 0;
     size_t total_decode_steps = 0;
     size_t total_tokens_generated = 0;
+    size_t total_prefill_calls = 0;   // run_prefill calls (one per prompt, or one per chunk)
 };
 
 class Scheduler {
@@ -37,7 +38,7 @@ public:
         GenerationParams params;
         State state = State::Queued;
         std::vector<uint64_t> generated_tokens;
-        size_t position = 0;      // next sequence position to feed
+        size_t position = 0;      // next sequence position to feed (while prefilling: prompt tokens fed so far)
         uint64_t last_token = 0;  // most recently sampled token
         std::string failure_reason;
     };
@@ -50,6 +51,11 @@ public:
     uint32_t add_request(std::vector<uint64_t> prompt_tokens, GenerationParams params);
     void set_token_callback(TokenCallback cb) { token_cb_ = std::move(cb); }
     void set_complete_callback(CompleteCallback cb) { complete_cb_ = std::move(cb); }
+    // Chunked admission: a prompt is fed at most `tokens` at a time, one chunk per tick, with the batch's
+    // decode pass running every tick in between (0, the default, feeds a prompt whole in one tick like the
+    // reference, scheduler.cpp:47-81, where a long prompt holds every decoding request up for its duration).
+    void set_prefill_chunk_tokens(size_t tokens) { prefill_chunk_tokens_ = tokens; }
+    size_t prefill_chunk_tokens() const { return prefill_chunk_tokens_; }
 
     size_t run_until_idle();  // returns the number of decode steps it ran
     bool tick();              // admit + prefill one + decode once + reap
@@ -72,6 +78,7 @@ private:
 
     IBatchedExecutor* executor_;
     size_t max_batch_size_;
+    size_t prefill_chunk_tokens_ = 0;
     std::deque<Request> queued_;
     std::vector<Request> active_;
     std::vector<Request> completed_;

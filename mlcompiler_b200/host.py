@@ -77,6 +77,8 @@ _PROTOTYPES = {
     "mlc_scheduler_add_request": (_u32, [_vp, _u64p, _sz, _sz, C.c_int64]),
     "mlc_scheduler_set_token_callback": (None, [_vp, TOKEN_CB, _vp]),
     "mlc_scheduler_tick": (_i, [_vp]),
+    "mlc_scheduler_set_prefill_chunk_tokens": (None, [_vp, _sz]),
+    "mlc_scheduler_prefill_calls": (_sz, [_vp]),
     "mlc_scheduler_run_until_idle": (_sz, [_vp]),
     "mlc_scheduler_empty": (_i, [_vp]),
     "mlc_scheduler_queued_count": (_sz, [_vp]),
@@ -335,6 +337,13 @@ class Scheduler:
     def set_token_callback(self, fn):
         self._token_cb = TOKEN_CB(lambda user, rid, tok: fn(rid, tok))
         lib().mlc_scheduler_set_token_callback(self._h, self._token_cb, None)
+
+    def set_prefill_chunk_tokens(self, tokens: int):
+        """A prompt is fed at most `tokens` at a time, one chunk per tick (0: whole prompts, the reference)."""
+        lib().mlc_scheduler_set_prefill_chunk_tokens(self._h, int(tokens))
+
+    def prefill_calls(self) -> int:
+        return lib().mlc_scheduler_prefill_calls(self._h)
 
     def tick(self) -> bool:
         return bool(lib().mlc_scheduler_tick(self._h))

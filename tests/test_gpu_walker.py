@@ -181,3 +181,52 @@ def test_scheduler_over_the_real_executor(executor):
     assert all(0 <= t < H * D for d in done.values() for t in d["generated_tokens"])
     steps2, done2, _ = run()
     assert steps2 == steps and all(done2[i]["generated_tokens"] == done[i]["generated_tokens"] for i in done)
+
+
+def test_decode_passes_allocate_nothing_in_steady_state(executor):
+    """The walker keeps two plans for the executor's lifetime and refreshes them in place: after the first
+    passes a decode pass makes no device or pinned allocation and, in the fused order, a single launch."""
+    pool, storage, ex = make_stack(executor)
+    positions = {1: 0, 2: 0, 3: 0, 4: 0}
+    def one_pass():
+        slots = [(rid, 7 + rid, positions[rid]) for rid in positions]
+        out = ex.run_decode(slots)
+        assert all(o[1] for o in out)
+        for rid in positions:
+            positions[rid] += 1
+    for _ in range(4):          # both plans created, cached buffers and staging sized
+        one_pass()
+    allocs, launches = executor.allocCount(), executor.launchCount()
+    for _ in range(30):
+        one_pass()
+    assert executor.allocCount() == allocs, "a decode pass allocated"
+    assert executor.launchCount() - launches == 30, "a fused decode pass is one launch"
+    ex.destroy()
+    storage.destroy()
+
+
+def test_chunked_admission_over_the_real_executor(executor):
+    """A long prompt admitted in chunks of 16 tokens generates exactly what it generates when it is fed
+    whole, next to a request that keeps decoding meanwhile; the prompt took several prefill calls."""
+    def run(chunk):
+        pool, storage, ex = make_stack(executor, capacity=40)
+        sched = Scheduler(ex, 4)
+        sched.set_prefill_chunk_tokens(chunk)
+        sched.add_request([3, 1, 4], max_new_tokens=12)
+        sched.tick()
+        sched.add_request(list(range(200, 270)), max_new_tokens=5)      # 70 tokens: two pages
+        sched.run_until_idle()
+        done = {d["id"]: d["generated_tokens"] for d in sched.drain_completed()}
+        calls, used = sched.prefill_calls(), pool.pages_in_use()
+        ex.destroy()
+        storage.destroy()
+        return done, calls, used
+    whole, calls_whole, used_whole = run(0)
+    chunked, calls_chunked, used_chunked = run(16)
+    assert calls_whole == 2 and calls_chunked == 1 + 5 and used_whole == 0 and used_chunked == 0
+    assert len(whole[2]) == 5 and len(whole[1]) == 12
+    # Request 2's tokens do not depend on how its prompt was cut (chunked causal attention over the pages
+    # written so far gives the same last-token output within rounding; greedy arg-max of these outputs is
+    # stable for this seed). Request 1 decodes alone either way.
+    assert chunked[1] == whole[1]
+    assert chunked[2] == whole[2]

@@ -136,3 +136,80 @@ def test_prompt_less_request_goes_straight_to_decode():
     sched.add_request([], max_new_tokens=2)
     sched.run_until_idle()
     assert mock.prefill_calls.get(1, 0) == 0 and mock.decode_calls[1] == 2
+
+
+class CursorMock(MockExecutor):
+    """Remembers how far every request's prefill has come, like the executor does (known_position)."""
+
+    def __init__(self):
+        self.fed, self.chunks, self.events = {}, {}, []
+        super().__init__()
+
+    def run_prefill(self, rid, tokens):
+        self.chunks.setdefault(rid, []).append(list(tokens))
+        self.fed[rid] = self.fed.get(rid, 0) + len(tokens)
+        self.events.append(("prefill", rid, len(tokens)))
+        return super().run_prefill(rid, tokens)
+
+    def run_decode(self, slots):
+        self.events.append(("decode", tuple(s[0] for s in slots)))
+        return super().run_decode(slots)
+
+
+def test_chunked_admission_feeds_a_prompt_in_pieces_and_keeps_decoding():
+    """A long prompt arrives while another request is decoding: with chunked admission the prompt goes
+    in 4 tokens per tick and the other request gets a decode step on every one of those ticks; the
+    generated tokens are the same as without chunking."""
+    results = {}
+    for chunk in (0, 4):
+        mock = CursorMock()
+        sched = Scheduler(mock, 8)
+        sched.set_prefill_chunk_tokens(chunk)
+        a = sched.add_request([5], max_new_tokens=12)
+        sched.tick()                                  # request a: prefilled, first decode done
+        b = sched.add_request(list(range(100, 110)), max_new_tokens=3)     # 10 prompt tokens
+        emitted = {}
+        sched.set_token_callback(lambda r, t: emitted.setdefault(r, []).append(t))
+        sched.run_until_idle()
+        done = {d["id"]: d["generated_tokens"] for d in sched.drain_completed()}
+        results[chunk] = done
+        if chunk:
+            assert mock.chunks[b] == [[100, 101, 102, 103], [104, 105, 106, 107], [108, 109]]
+            assert mock.fed[b] == 10 and sched.prefill_calls() == 1 + 3
+            # between the first and the last chunk of b, request a decoded on every tick
+            idx = [i for i, e in enumerate(mock.events) if e[0] == "prefill" and e[1] == b]
+            between = mock.events[idx[0]:idx[-1]]
+            assert sum(1 for e in between if e[0] == "decode" and a in e[1]) == 2
+            # b joins the decode pass only after its last chunk
+            first_b_decode = next(i for i, e in enumerate(mock.events) if e[0] == "decode" and b in e[1])
+            assert first_b_decode > idx[-1]
+        else:
+            assert mock.chunks[b] == [list(range(100, 110))] and sched.prefill_calls() == 2
+    assert results[0] == results[4]
+    assert len(results[4][1]) == 12 and len(results[4][2]) == 3
+
+
+def test_chunk_larger_than_the_prompt_is_one_call():
+    mock = CursorMock()
+    sched = Scheduler(mock, 2)
+    sched.set_prefill_chunk_tokens(64)
+    rid = sched.add_request([1, 2, 3], max_new_tokens=2)
+    sched.run_until_idle()
+    assert mock.chunks[rid] == [[1, 2, 3]] and sched.prefill_calls() == 1
+    assert sched.completed_count() == 1
+
+
+def test_failed_chunk_fails_the_request_and_releases_it():
+    class FailSecond(CursorMock):
+        def run_prefill(self, rid, tokens):
+            out = super().run_prefill(rid, tokens)
+            return np.zeros(0, np.float32) if len(self.chunks[rid]) == 2 else out    # empty logits = failure
+
+    mock = FailSecond()
+    sched = Scheduler(mock, 2)
+    sched.set_prefill_chunk_tokens(2)
+    rid = sched.add_request([1, 2, 3, 4, 5], max_new_tokens=4)
+    sched.run_until_idle()
+    d = sched.drain_completed()
+    assert len(d) == 1 and d[0]["state"] == Scheduler.FAILED and d[0]["generated_tokens"] == []
+    assert rid in mock.released
