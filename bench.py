@@ -528,7 +528,9 @@ def run_gpu_arm(args):
     secondary = None
     if not args.no_secondary:
         secondary = {}
-        for name, fn in (("cfg3", bench_more.run_cfg3), ("cfg4", bench_more.run_cfg4), ("cfg5", bench_more.run_cfg5)):
+        long_cfg3 = lambda e, steps, warmup: bench_more.run_cfg3(e, steps=steps, warmup=warmup, check=False, seq_len=262144)
+        for name, fn in (("cfg3", bench_more.run_cfg3), ("cfg3_262144_tokens", long_cfg3), ("cfg4", bench_more.run_cfg4),
+                         ("cfg5", bench_more.run_cfg5)):
             try:
                 r = fn(env, steps=200, warmup=5)
             except Exception as e:            # a secondary workload must not take the headline line down

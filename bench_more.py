@@ -144,7 +144,7 @@ def run_cfg5(env, steps=200, warmup=10):
         "gpu_launches": int(launches)}
 
 
-def run_cfg3(env, steps=200, warmup=10, exchange="peer", check=True):
+def run_cfg3(env, steps=200, warmup=10, exchange="fused", check=True, seq_len=None):
     import torch
     from mlcompiler_b200 import sharding, synth
     from mlcompiler_b200.capi import MLC_F16, PeerExchange
@@ -152,7 +152,8 @@ def run_cfg3(env, steps=200, warmup=10, exchange="peer", check=True):
     P = 64
     shape = synth.SHAPE_A
     H, KVH, D = shape["H"], shape["KVH"], shape["D"]
-    case = synth.make_case(0xBEEF + 3, synth.config_lengths(3), P=P, fill=False, **shape)
+    seq = synth.config_lengths(3) if seq_len is None else np.full(4, seq_len, np.uint32)
+    case = synth.make_case(0xBEEF + 3, seq, P=P, fill=False, **shape)
     N = case.N
     flat, off, lens, _ = sharding.slice_tables_for_rank(case.pt_flat, case.pt_off, case.seq_lens, P, rank, world)
     # local pool: only this rank's pages, renumbered densely
@@ -173,7 +174,8 @@ def run_cfg3(env, steps=200, warmup=10, exchange="peer", check=True):
         ml_part = torch.zeros((N, H, 2), device=dev, dtype=torch.float32)
         out = torch.zeros((N, H, D), device=dev, dtype=torch.float16)
     plan = ex.createPlan(flat_local, off, lens, np.zeros(N, np.uint32), N, H, KVH, D, P, False, cap)
-    use_peer = world > 1 and exchange == "peer"
+    use_peer = world > 1 and exchange in ("peer", "fused")
+    fused = use_peer and exchange == "fused"
     xc = None
     if use_peer:
         xc = PeerExchange(ex, rank, world, N * H, D)
@@ -189,6 +191,8 @@ def run_cfg3(env, steps=200, warmup=10, exchange="peer", check=True):
         if world == 1:
             ok = ex.encodePagedFlashAttentionPlanned(plan, q, kp[c], vp[c], out, case.scale, MLC_F16, MLC_F16)
             assert ok, ex.last_error()
+        elif fused:     # partial attention + exchange + combine: one launch
+            assert xc.encodeAttentionExchange(plan, q, kp[c], vp[c], out, case.scale, MLC_F16, MLC_F16), ex.last_error()
         elif use_peer:
             ok = ex.encodePagedAttentionPartialPlanned(plan, q, kp[c], vp[c], o_part, ml_part, case.scale, MLC_F16)
             assert ok, ex.last_error()
@@ -263,15 +267,17 @@ def run_cfg3(env, steps=200, warmup=10, exchange="peer", check=True):
     assert ex.flushForwardPassCB(), ex.last_error()
     launches = ex.launchCount() - l0
     total_bytes = case.kv_bytes
-    how = ("one GPU" if world == 1 else "partials pushed to the peers' memory, flags, combine - this library's kernels"
-           if use_peer else "NCCL all-gather of (o,m,l), LSE combine")
+    how = ("one GPU" if world == 1 else
+           "one launch per rank: rows pushed to the peers' memory as each (request, head) finishes, flags, combine" if fused else
+           "partial attention, then this library's exchange + combine kernel over peer memory" if use_peer else
+           "NCCL all-gather of (o,m,l), LSE combine")
     peaks = measured_peaks()
     value = total_bytes / sec / 1e9
     res = {
         "metric": "paged_decode_attn_kv_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
         "warmup": max(warmup, 3), "ms_per_step": sec * 1e3, "us_per_step": sec * 1e6, "higher_is_better": True,
         "scaling": "strong", "dtype": "f16 in, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "cfg3: 4 requests x 32768 tokens, H32/KVH4/D64, KV sequence split over ranks, " + how,
+        "config": {"workload": f"cfg3: 4 requests x {int(seq[0])} tokens, H32/KVH4/D64, KV sequence split over ranks, " + how,
                    "parallelism": f"sequence-sharded x{world}", "pool_copies_rotated": copies,
                    "cuda_graph": graphs is not None,
                    "gather_bytes_per_rank": int((o_part.numel() + ml_part.numel()) * 4) if world > 1 else 0},
@@ -361,8 +367,10 @@ def main():
     ap.add_argument("--workload", choices=["cfg3", "cfg4", "cfg5"], required=True)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
-                    help="cfg3 on several GPUs: peer-memory exchange kernel (default) or NCCL all-gather + combine")
+    ap.add_argument("--exchange", choices=["fused", "peer", "nccl"], default="fused",
+                    help="cfg3 on several GPUs: exchange fused into the attention kernel (default), the separate "
+                         "peer-memory exchange kernel, or NCCL all-gather + combine")
+    ap.add_argument("--seq-len", type=int, default=None, help="cfg3: tokens per request instead of 32768")
     args = ap.parse_args()
 
     import torch
@@ -381,7 +389,7 @@ def main():
     if args.workload == "cfg5":
         res = run_cfg5(env, args.steps, args.warmup)
     elif args.workload == "cfg3":
-        res = run_cfg3(env, args.steps, args.warmup, args.exchange)
+        res = run_cfg3(env, args.steps, args.warmup, args.exchange, seq_len=args.seq_len)
     else:
         res = run_cfg4(env, args.steps, args.warmup)
     if rank == 0:

@@ -442,14 +442,32 @@ int mlc_exchange_attach(mlc_ctx* ctx, mlc_exchange* ex, const void* handles);
  * entry ignored. Nothing is mapped or closed by the library. */
 int mlc_exchange_attach_pointers(mlc_ctx* ctx, mlc_exchange* ex, void* const* bases);
 void* mlc_exchange_local_buffer(const mlc_exchange* ex);
+/* Profiling aid (context created with MLC_B200_TRACE=1): %globaltimer stamps, in ns, of CTA 0 of the
+ * most recent exchange kernel: [0] start, [1] this rank's rows stored to a peer, [2] that peer's flag
+ * stored, [3] every rank's flag seen, [4] combine done. */
+int mlc_exchange_read_trace(mlc_ctx* ctx, unsigned long long* out8);
 /* Floats per (step parity, rank) slot of the gather buffer: max_rows * (head_dim + 2) rounded up
  * to a multiple of 4, so that every slot starts on a 16-byte boundary. */
 size_t mlc_exchange_slot_floats(const mlc_exchange* ex);
 /* Layout of a rank's gather buffer (pure host arithmetic, no device needed): slots
  * [2 parities][world] of slot_floats floats each (o rows, then (m, l) pairs), flag words at
- * flags_offset bytes, total size. Any output pointer may be null. */
+ * flags_offset bytes, behind them the stamped slots of the fused attention + exchange kernel
+ * (every float beside a 4-byte step stamp), total size. Any output pointer may be null. */
 int mlc_exchange_layout(int world, size_t max_rows, size_t head_dim, size_t* slot_floats,
                         size_t* flags_offset, size_t* total_bytes);
+/* Partial attention over this rank's slice of the pages, the exchange and the combine as ONE launch:
+ * the CTA that finishes a (request, head) stores its un-normalised rows straight into every rank's
+ * gather buffer - every float beside the step's stamp in one 8-byte unit, so a row is complete when
+ * its own bytes say so: no flag, no fence - then reads every rank's rows of that (request, head) from
+ * its own memory, waiting - bounded, as above - for stamps that are not there yet, combines them and
+ * writes `out` ([batch, num_heads, head_dim] of o_dtype, the full attention output, on every rank). `plan` covers this rank's slice (tables of its pages, the
+ * tokens that fall into them, apply_causal 0 on all but the rank with the last tokens - as for
+ * mlc_encode_paged_attention_partial_planned); every rank makes the same sequence of calls on an
+ * exchange created for >= batch * num_heads rows. Plans the unit-mode kernel does not take fall back
+ * to the partial + mlc_encode_exchange_lse_combine pair inside the call. Capturable. */
+int mlc_encode_paged_attention_exchange_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, mlc_exchange* ex,
+                                                const void* q, const void* k_pages, const void* v_pages,
+                                                void* out, float scale, int q_dtype, int o_dtype);
 int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float* o_partial,
                                     const float* ml_partial, size_t rows, void* out, int o_dtype);
 void mlc_exchange_destroy(mlc_ctx* ctx, mlc_exchange* ex);

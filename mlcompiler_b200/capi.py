@@ -78,9 +78,11 @@ _PROTOTYPES = {
     "mlc_exchange_attach": (_i, [_vp, _vp, _vp]),
     "mlc_exchange_attach_pointers": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "mlc_exchange_local_buffer": (_vp, [_vp]),
+    "mlc_exchange_read_trace": (_i, [_vp, C.POINTER(C.c_uint64)]),
     "mlc_exchange_slot_floats": (_sz, [_vp]),
     "mlc_exchange_layout": (_i, [_i, _sz, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
     "mlc_encode_exchange_lse_combine": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _i]),
+    "mlc_encode_paged_attention_exchange_planned": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_float, _i, _i]),
     "mlc_exchange_destroy": (None, [_vp, _vp]),
     "mlc_ctx_last_attention_kernel": (_i, [_vp]),
     "mlc_ctx_read_trace": (C.c_uint32, [_vp, C.POINTER(C.c_uint64), _sz, _i]),
@@ -532,6 +534,12 @@ class PeerExchange:
         buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
         self._ex.check(self._ex._lib.mlc_exchange_attach(self._ex._h, self.handle, C.cast(buf, _vp)))
 
+    def read_trace(self) -> np.ndarray:
+        """ns stamps of CTA 0 of the last exchange kernel (context created with MLC_B200_TRACE=1)."""
+        buf = np.zeros(8, np.uint64)
+        self._ex.check(self._ex._lib.mlc_exchange_read_trace(self._ex._h, buf.ctypes.data_as(C.POINTER(C.c_uint64))))
+        return buf
+
     def local_buffer(self) -> int:
         return int(self._ex._lib.mlc_exchange_local_buffer(self.handle) or 0)
 
@@ -552,6 +560,13 @@ class PeerExchange:
         handles = [None] * self.world
         dist.all_gather_object(handles, self.ipc_handle(), group=group)
         self.attach(handles)
+
+    def encodeAttentionExchange(self, plan, q, k_pages, v_pages, out, scale=0.0, q_dtype=MLC_F32, o_dtype=MLC_F32) -> bool:
+        """Partial attention over this rank's slice + exchange + combine in one launch; `out` is the full
+        attention output on every rank."""
+        return self._ex.status(self._ex._lib.mlc_encode_paged_attention_exchange_planned(
+            self._ex._h, plan.handle, self.handle, _vp(_ptr(q)), _vp(_ptr(k_pages)), _vp(_ptr(v_pages)), _vp(_ptr(out)),
+            float(scale), q_dtype, o_dtype))
 
     def encodeLseCombine(self, o_partial, ml_partial, rows, out, o_dtype=MLC_F32) -> bool:
         return self._ex.status(self._ex._lib.mlc_encode_exchange_lse_combine(

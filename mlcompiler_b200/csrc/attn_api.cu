@@ -822,6 +822,49 @@ int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan
     return launch_with_plan(ctx, a, *plan);
 }
 
+int mlc_encode_paged_attention_exchange_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, mlc_exchange* ex, const void* q,
+                                                const void* k_pages, const void* v_pages, void* out, float scale,
+                                                int q_dtype, int o_dtype) {
+    if (!ctx || !plan || !ex) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (!q || !k_pages || !v_pages || !out) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    if ((q_dtype != MLC_F32 && q_dtype != MLC_F16) || (o_dtype != MLC_F32 && o_dtype != MLC_F16))
+        return ctx->fail(MLC_ERR_INVALID_ARG, "dtype must be MLC_F32 or MLC_F16");
+    ExchangeView xv;
+    if (!exchange_describe(ex, &xv)) return ctx->fail(MLC_ERR_INVALID_ARG, "exchange not attached to its peers");
+    const PlanKey& k = plan->key;
+    const size_t rows = k.batch * k.H;
+    if (rows == 0 || rows > xv.max_rows || xv.D != k.D)
+        return ctx->fail(MLC_ERR_INVALID_ARG, "the exchange was created for %zu rows of head_dim %zu, the plan has %zu of %zu",
+                         xv.max_rows, xv.D, rows, k.D);
+    if (reinterpret_cast<uintptr_t>(out) % 16) return ctx->fail(MLC_ERR_INVALID_ARG, "out must be 16-byte aligned");
+    DeviceGuard guard(ctx->device);
+    AttnArgs a;
+    a.q = q; a.k_pages = k_pages; a.v_pages = v_pages;
+    a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
+    a.batch = k.batch; a.H = k.H; a.KVH = k.KVH; a.D = k.D; a.P = k.P; a.capacity = k.capacity;
+    if (a.scale <= 0.f) a.scale = 1.0f / std::sqrt(static_cast<float>(a.D));  // mm:7133
+    AttnArgs probe = a;
+    probe.o = out;
+    if (plan->view.has_tma && plan->view.unit_mode && plan->view.hpc <= 1 && !ctx->force_general && k.D % 4 == 0 &&
+        decode_tma_pointers_supported(probe)) {
+        a.exchange = &xv;
+        a.exchange_out = out;
+        ctx->last_attention_kernel = 2;
+        return launch_attention_decode_tma(ctx, a, plan->view);
+    }
+    // Any other plan (split form, odd shapes): the partial into scratch kept by the context, then the
+    // separate exchange + combine kernel.
+    const size_t o_bytes = rows * k.D * 4, ml_bytes = rows * 2 * 4;
+    char* scratch = static_cast<char*>(mlc_cached_buffer(ctx, "mlc_exchange_partials", ((o_bytes + 255) / 256) * 256 + ml_bytes));
+    if (!scratch) return ctx->fail(MLC_ERR_OOM, "scratch for the partials unavailable");
+    float* o_partial = reinterpret_cast<float*>(scratch);
+    float* ml_partial = reinterpret_cast<float*>(scratch + ((o_bytes + 255) / 256) * 256);
+    int st = mlc_encode_paged_attention_partial_planned(ctx, plan, q, k_pages, v_pages, o_partial, ml_partial, scale, q_dtype);
+    if (st != MLC_OK) return st;
+    return mlc_encode_exchange_lse_combine(ctx, ex, o_partial, ml_partial, rows, out, o_dtype);
+}
+
 int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
                                          const void* k_new, const void* v_new, void* k_pages,
                                          void* v_pages, void* o, float scale, int q_dtype, int o_dtype) {

@@ -358,6 +358,19 @@ __device__ __forceinline__ void write_rows(const DecodeParams& prm, uint32_t req
 template <int D, bool G16, bool CG>
 __device__ __forceinline__ void merge_segment(const DecodeParams& prm, const SegDesc& sd, uint32_t warp, uint32_t lane);
 
+// Split-KV across GPUs, fused into the attention kernel (PEER instantiation of the body below): what a
+// rank needs to hand the finished rows of a (request, head) to every rank and to combine all ranks' rows.
+struct PeerParams {
+    char* peer[16];          // gather buffers of all ranks as mapped into this process (own one included)
+    char* local;             // this rank's own gather buffer
+    void* out;               // final O [rows, D] on this rank
+    uint32_t* seq;           // step counter (local; advanced by the last CTA of a launch to finish)
+    uint32_t* done;          // CTAs of this launch that have finished
+    size_t ll_off;           // byte offset of the stamped slots [2 parities][world]
+    size_t ll_slot_bytes;    // bytes of one slot: max_rows * (D * 8 + 16)
+    uint32_t rank, world, max_rows, max_polls, out_f32;
+};
+
 // The kernel of the per-layer entry points. It is the same algorithm as decode_body below with a single item
 // per CTA (no layers to walk, one KV head per CTA item) and is kept as a body of its own on purpose: the tile
 // loop of this kernel runs at about a quarter of an instruction per clock on one warp per scheduler, and the
@@ -372,10 +385,17 @@ __device__ __forceinline__ void merge_segment(const DecodeParams& prm, const Seg
 // shared memory, so there are no global partials and no merge kernel. More warps matter: a warp
 // needs ~0.8 us per 32-token tile (dependent mma.sync / ldmatrix / shuffle chains, one warp per
 // scheduler), so the longest unit's time falls with the number of warps that share it.
-template <int D, bool G16, bool UNIT>
-__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32, 1)
-paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                        const DecodeParams prm) {
+// PEER (unit mode): the rank holds a slice of every request's pages. The CTA that finishes a (request, head)
+// - the only one that worked on it, or the last of the CTAs it was cut over - stores the un-normalised rows
+// (o, m, l) straight into every rank's gather buffer over NVLink peer memory (plain 16-byte stores, no loads
+// from a peer, no TMA, no multicast). Every float travels beside the step's stamp in one 8-byte unit
+// {value, stamp} (two per store), so a reader knows from the bytes themselves that a value is this step's:
+// no flag behind a system-scope fence, whose round trips cost more than the 33 KiB of rows do. The same CTA
+// then reads every rank's rows of that (request, head) from its OWN memory, polling - bounded - the units
+// whose stamp is not there yet, combines them with the log-sum-exp rule and writes O. One launch per step.
+template <int D, bool G16, bool UNIT, bool PEER>
+__device__ __forceinline__ void decode_layer_body(const CUtensorMap& tmK, const CUtensorMap& tmV, const DecodeParams& prm,
+                                                  const PeerParams* pp) {
     constexpr int TOK = kTileTokens;
     constexpr int NT_S = TOK / 8;          // score n-tiles per tile
     constexpr int KSTEPS = D / 16;         // k-steps of Q.K^T
@@ -484,10 +504,84 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         ++next_issue;
     }
     stamp(1);
+    // PEER: the step number (read after the launch before this one has completed: its last CTA advances it),
+    // the slots this rank writes in every rank's buffer and the flags it sets and waits for
+    uint32_t peer_step = 0;
+    if constexpr (PEER) peer_step = *reinterpret_cast<volatile uint32_t*>(pp->seq);
+    const uint32_t peer_parity = peer_step & 1u, peer_stamp = peer_step + 1u;   // never 0: zeroed flags match nothing
+    auto peer_slot = [&](uint32_t r) -> char* {    // this rank's stamped slot in rank r's buffer
+        return pp->peer[r] + pp->ll_off + (static_cast<size_t>(peer_parity) * pp->world + pp->rank) * pp->ll_slot_bytes;
+    };
+    // two values of row `hrow`, columns col / col + 1 (col even), to every rank
+    auto peer_store_o = [&](size_t hrow, uint32_t col, float a, float b) {
+        const uint4 v = make_uint4(__float_as_uint(a), peer_stamp, __float_as_uint(b), peer_stamp);
+        for (uint32_t k = 0; k < pp->world; ++k)
+            *reinterpret_cast<uint4*>(peer_slot(k) + (hrow * D + col) * 8) = v;
+    };
+    auto peer_store_ml = [&](size_t hrow, float m_nat, float l) {
+        const uint4 v = make_uint4(__float_as_uint(m_nat), peer_stamp, __float_as_uint(l), peer_stamp);
+        for (uint32_t k = 0; k < pp->world; ++k)
+            *reinterpret_cast<uint4*>(peer_slot(k) + static_cast<size_t>(pp->max_rows) * D * 8 + hrow * 16) = v;
+    };
+    // Reads a stamped 16-byte unit of this rank's own memory, again and again until both halves carry this
+    // step's stamp; false when the limit runs out.
+    auto peer_wait = [&](const char* addr, float& a, float& b) -> bool {
+        for (uint32_t i = 0; i < pp->max_polls; ++i) {
+            uint4 v;
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(addr) : "memory");
+            if (v.y == peer_stamp && v.w == peer_stamp) {
+                a = __uint_as_float(v.x);
+                b = __uint_as_float(v.z);
+                return true;
+            }
+        }
+        return false;
+    };
+    // Rows [row0, row0 + G) of a (request, head) this CTA has just stored to every rank: combine what every
+    // rank stored here. m* = max_k m_k, w_k = exp(m_k - m*), O = sum_k o_k w_k / sum_k l_k w_k.
+    auto peer_finish = [&](size_t row0) {
+        if constexpr (PEER) {
+            const char* base = pp->local + pp->ll_off + static_cast<size_t>(peer_parity) * pp->world * pp->ll_slot_bytes;
+            for (uint32_t t = threadIdx.x; t < prm.G * (D / 2); t += blockDim.x) {
+                const size_t row = row0 + t / (D / 2);
+                const uint32_t col = (t % (D / 2)) * 2;
+                float m[16], l[16], mstar = -INFINITY;
+                bool ok = true;
+                for (uint32_t k = 0; k < pp->world && ok; ++k) {
+                    ok = peer_wait(base + k * pp->ll_slot_bytes + static_cast<size_t>(pp->max_rows) * D * 8 + row * 16, m[k], l[k]);
+                    mstar = fmaxf(mstar, m[k]);
+                }
+                float lsum = 0.f, a0 = 0.f, a1 = 0.f;
+                for (uint32_t k = 0; k < pp->world && ok; ++k) {
+                    float x, y;
+                    ok = peer_wait(base + k * pp->ll_slot_bytes + (row * D + col) * 8, x, y);
+                    const float w = (m[k] == -INFINITY) ? 0.f : expf(m[k] - mstar);
+                    lsum += l[k] * w;
+                    a0 += x * w;
+                    a1 += y * w;
+                }
+                if (!ok) {    // a rank's rows did not arrive in time: no output for this row, the context stays usable
+                    atomicOr(prm.err, MLC_DEVERR_WAIT_TIMEOUT | (0x51u << 8));
+                    continue;
+                }
+                const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+                if (pp->out_f32) *reinterpret_cast<float2*>(static_cast<float*>(pp->out) + row * D + col) = make_float2(a0 * inv, a1 * inv);
+                else *reinterpret_cast<__half2*>(static_cast<__half*>(pp->out) + row * D + col) = __floats2half2_rn(a0 * inv, a1 * inv);
+            }
+        }
+    };
 
     // Requests that attend to nothing: their O rows are zeros (mm:2254-2257).
     for (uint32_t i = cta; i < prm.n_zero; i += gridDim.x) {
         const uint32_t r = prm.zero_rows[i];
+        if constexpr (PEER) {
+            // this rank holds no token of the request: its rows weigh nothing, but the other ranks wait for them
+            for (uint32_t e = threadIdx.x; e < prm.H * (D / 2); e += blockDim.x)
+                peer_store_o(static_cast<size_t>(r) * prm.H + e / (D / 2), (e % (D / 2)) * 2, 0.f, 0.f);
+            for (uint32_t e = threadIdx.x; e < prm.H; e += blockDim.x) peer_store_ml(static_cast<size_t>(r) * prm.H + e, -INFINITY, 0.f);
+            for (uint32_t h = 0; h < prm.KVH; ++h) peer_finish(static_cast<size_t>(r) * prm.H + static_cast<size_t>(h) * prm.G);
+            continue;
+        }
         for (uint32_t e = threadIdx.x; e < prm.H * D; e += blockDim.x) {
             const size_t idx = static_cast<size_t>(r) * prm.H * D + e;
             if (prm.o_partial) {
@@ -813,7 +907,9 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     const uint32_t row = qrow + 8 * rs;
                     if (row >= prm.G) continue;
                     const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
-                    if (prm.o_partial) {
+                    if constexpr (PEER) {
+                        peer_store_o(hrow, n * 8 + qcol, acc[2 * rs], acc[2 * rs + 1]);
+                    } else if (prm.o_partial) {
                         *reinterpret_cast<float2*>(prm.o_partial + hrow * D + n * 8 + qcol) = make_float2(acc[2 * rs], acc[2 * rs + 1]);
                     } else {
                         const float inv = ls[rs] > 0.f ? 1.0f / ls[rs] : 0.f;
@@ -827,14 +923,18 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
             };
             auto emit_ml = [&](const float (&ms)[2], const float (&ls)[2]) {
-                if (prm.o_partial && warp == 0 && (lane & 3) == 0) {
+                if ((PEER || prm.o_partial) && warp == 0 && (lane & 3) == 0) {
 #pragma unroll
                     for (int rs = 0; rs < ROWSETS; ++rs) {
                         const uint32_t row = qrow + 8 * rs;
                         if (row >= prm.G) continue;
                         const size_t hrow = static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G + row;
-                        prm.ml_partial[hrow * 2] = ms[rs] * 0.6931471805599453f;   // natural-log units for the caller
-                        prm.ml_partial[hrow * 2 + 1] = ls[rs];
+                        if constexpr (PEER) {
+                            peer_store_ml(hrow, ms[rs] * 0.6931471805599453f, ls[rs]);   // natural-log units, as in the caller-visible partial
+                        } else {
+                            prm.ml_partial[hrow * 2] = ms[rs] * 0.6931471805599453f;   // natural-log units for the caller
+                            prm.ml_partial[hrow * 2 + 1] = ls[rs];
+                        }
                     }
                 }
             };
@@ -948,6 +1048,11 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 emit_ml(mstar, lstar);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");  // the exchange area is free for the next (request, head)
+            if constexpr (PEER) {
+                // this CTA wrote the (request, head)'s final rows: alone, or as the last of the CTAs it was cut over
+                if (n_parts == 1 || last_part_flag)
+                    peer_finish(static_cast<size_t>(req) * prm.H + static_cast<size_t>(head) * prm.G);
+            }
             if (pi == 0) stamp(4);
         } else if (n_parts > 1) {
             // un-normalised partial -> workspace, fragment order (coalesced). The merge kernel
@@ -1032,6 +1137,33 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
         stamp(5);
     }
+    if constexpr (PEER) {
+        // the last CTA to finish advances the step counter (graph replays need no host argument)
+        asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(pp->done, 1u) == gridDim.x - 1) {
+                *pp->done = 0;
+                __threadfence();
+                *reinterpret_cast<volatile uint32_t*>(pp->seq) = peer_step + 1u;
+            }
+        }
+    }
+}
+
+template <int D, bool G16, bool UNIT>
+__global__ void __launch_bounds__((UNIT ? unit_warps(D) : kDecodeWarps) * 32, 1)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const DecodeParams prm) {
+    decode_layer_body<D, G16, UNIT, false>(tmK, tmV, prm, nullptr);
+}
+
+// Partial attention over this rank's slice of the pages + exchange + combine, one launch (unit-mode plans).
+template <int D, bool G16>
+__global__ void __launch_bounds__(unit_warps(D) * 32, 1)
+paged_decode_exchange_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                             const DecodeParams prm, const PeerParams pp) {
+    decode_layer_body<D, G16, true, true>(tmK, tmV, prm, &pp);
 }
 
 // ------------------------------------------------------------------------------
@@ -2112,6 +2244,31 @@ static int launch_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams
     return MLC_OK;
 }
 
+template <int D, bool G16>
+static int launch_exchange_t(mlc_ctx* ctx, const DecodePlanView& plan, const DecodeParams& prm, const CUtensorMap& mk,
+                             const CUtensorMap& mv, const PeerParams& pp) {
+    const size_t smem = decode_tma_smem_bytes(D, G16, plan.stages, true);
+    size_t& configured = ctx->decode_smem_set[12 + (D == 128 ? 2 : 0) + (G16 ? 1 : 0)];
+    if (smem > configured) {
+        MLCB_CUDA(ctx, cudaFuncSetAttribute(paged_decode_exchange_kernel<D, G16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(smem)));
+        configured = smem;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(plan.n_cta);      // at most one CTA per SM: every CTA of the launch is resident while it waits
+    cfg.blockDim = dim3(unit_warps(D) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MLCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, paged_decode_exchange_kernel<D, G16>, mk, mv, prm, pp));
+    ++ctx->launches;
+    return MLC_OK;
+}
+
 // True when one of the two decode launches enqueued before this one on the context writes into either pool.
 static bool recently_written(const mlc_ctx* ctx, const void* k_pool, const void* v_pool) {
     for (const PoolWrites& w : ctx->recent_writes) {
@@ -2384,6 +2541,27 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     // rows of 4 warps: a unit-mode CTA of 8 warps fills two consecutive rows
     ctx->trace_ctas = prm.trace ? plan.n_cta * (plan.unit_mode ? unit_warps(a.D) : kDecodeWarps) / kDecodeWarps : 0;
     ctx->trace_parity = parity;
+    if (a.exchange) {
+        // fused with the exchange across GPUs: the finished rows go to every rank, each rank combines
+        const ExchangeView& xv = *a.exchange;
+        PeerParams pp{};
+        for (uint32_t r = 0; r < xv.world; ++r) pp.peer[r] = xv.peer[r];
+        pp.local = xv.local;
+        pp.out = a.exchange_out;
+        pp.seq = xv.seq;
+        pp.done = xv.done;
+        pp.ll_off = xv.ll_off;
+        pp.ll_slot_bytes = xv.ll_slot_bytes;
+        pp.rank = xv.rank;
+        pp.world = xv.world;
+        pp.max_rows = static_cast<uint32_t>(xv.max_rows);
+        pp.max_polls = ctx->wait_limit ? ctx->wait_limit : (1u << 20);
+        pp.out_f32 = a.o_dtype == MLC_F32;
+        prm.trace = nullptr;
+        ctx->trace_ctas = 0;
+        if (a.D == 64) return g16 ? launch_exchange_t<64, true>(ctx, plan, prm, mk, mv, pp) : launch_exchange_t<64, false>(ctx, plan, prm, mk, mv, pp);
+        return g16 ? launch_exchange_t<128, true>(ctx, plan, prm, mk, mv, pp) : launch_exchange_t<128, false>(ctx, plan, prm, mk, mv, pp);
+    }
     if (plan.unit_mode) {
         if (a.D == 64) return g16 ? launch_t<64, true, true>(ctx, plan, prm, mk, mv) : launch_t<64, false, true>(ctx, plan, prm, mk, mv);
         return g16 ? launch_t<128, true, true>(ctx, plan, prm, mk, mv) : launch_t<128, false, true>(ctx, plan, prm, mk, mv);

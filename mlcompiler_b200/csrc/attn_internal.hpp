@@ -28,6 +28,10 @@ struct AttnArgs {
     // when set, the launch makes no device or host allocation at all.
     void* ext_work = nullptr;
     size_t ext_work_bytes = 0;
+    // Fused exchange across GPUs (unit-mode plans): finished rows go to every rank's gather buffer, this rank
+    // combines all ranks' rows into exchange_out (of o_dtype). q / o above are not used for output then.
+    const ExchangeView* exchange = nullptr;
+    void* exchange_out = nullptr;
 };
 
 // ---- work plan of the TMA / tensor-core kernel ----------------------------------

@@ -36,6 +36,17 @@ struct PoolWrites {
     std::vector<const void*> many;
 };
 
+// An exchange object (peer_exchange.cu) as the fused attention + exchange kernel sees it.
+struct ExchangeView {
+    char* peer[16] = {};
+    char* local = nullptr;
+    uint32_t* seq = nullptr;
+    uint32_t* done = nullptr;
+    size_t slot_floats = 0, flags_off = 0, max_rows = 0, D = 0;
+    size_t ll_off = 0, ll_slot_bytes = 0;   // the stamped slots of the fused attention + exchange kernel
+    uint32_t rank = 0, world = 1;
+};
+
 struct AttnPlanCache;  // attn_api.cu
 struct TensorMapCache; // attn_decode_tma.cu
 
@@ -70,7 +81,7 @@ struct mlc_ctx {
     size_t work_bytes = 0;
     uint32_t* d_counters = nullptr;
     size_t n_counters = 0;
-    size_t decode_smem_set[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
+    size_t decode_smem_set[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // dynamic-smem opt-in already applied, per kernel variant
     bool prefill_smem_set = false;             // same, for the chunked-prefill kernel
     // copy streams and events of the host-buffer decode pass (created on first use)
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
@@ -136,5 +147,9 @@ size_t resolve_capacity(const mlc_ctx* ctx, const void* pool, size_t claimed, si
 void destroy_plan_cache(mlc_ctx* ctx);
 void destroy_tmap_cache(mlc_ctx* ctx);
 void destroy_pass_args(mlc_ctx* ctx);
+}  // namespace mlcb
+struct mlc_exchange;
+namespace mlcb {
+bool exchange_describe(const mlc_exchange* ex, ExchangeView* v);
 
 }  // namespace mlcb

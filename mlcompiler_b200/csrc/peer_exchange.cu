@@ -48,9 +48,11 @@ struct ExchangeParams {
     uint32_t* seq;          // step counter (local)
     uint32_t* done;         // CTAs finished in this launch (local)
     size_t slot_floats;     // floats per (parity, rank) slot = max_rows * (D + 2)
-    size_t flags_off;       // byte offset of the flag words [2][world]
+    size_t flags_off;       // byte offset of the flag words [2][world] (max_units = 1)
+    uint32_t max_units;
     uint32_t rank, world, rows, D;
     uint32_t max_polls;     // limit of the flag wait (mlc_ctx_set_wait_limit, default kMaxPolls)
+    unsigned long long* trace;   // optional: 8 %globaltimer stamps of CTA 0 (MLC_B200_TRACE=1), else null
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -66,12 +68,20 @@ template <typename OT>
 __global__ void __launch_bounds__(256) exchange_lse_combine_kernel(const ExchangeParams p) {
     __shared__ uint32_t s_step;
     __shared__ int s_ok;
+    auto stamp = [&](int i) {
+        if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[i] = t;
+        }
+    };
+    stamp(0);
     if (threadIdx.x == 0) {
         s_step = *reinterpret_cast<volatile uint32_t*>(p.seq);
         s_ok = 1;
     }
     __syncthreads();
-    const uint32_t step = s_step, parity = step & 1u, stamp = step + 1u;  // stamp is never 0: zeroed flags match nothing
+    const uint32_t step = s_step, parity = step & 1u, stamp_value = step + 1u;  // never 0: zeroed flags match nothing
     const size_t o_floats = static_cast<size_t>(p.rows) * p.D, ml_floats = static_cast<size_t>(p.rows) * 2;
 
     // ---- 1. push this rank's partial into one peer's buffer ----
@@ -86,18 +96,22 @@ __global__ void __launch_bounds__(256) exchange_lse_combine_kernel(const Exchang
         for (size_t i = threadIdx.x; i < ml_floats / 2; i += blockDim.x) d2[i] = sm[i];
         __threadfence_system();
         __syncthreads();
+        stamp(1);
         if (threadIdx.x == 0) {
-            uint32_t* flag = reinterpret_cast<uint32_t*>(p.peer[dst_rank] + p.flags_off) + parity * p.world + p.rank;
-            st_release_sys(flag, stamp);
+            uint32_t* flag = reinterpret_cast<uint32_t*>(p.peer[dst_rank] + p.flags_off) +
+                             (static_cast<size_t>(parity) * p.world + p.rank) * p.max_units;
+            st_release_sys(flag, stamp_value);
         }
+        stamp(2);
     }
 
     // ---- 2. wait (bounded) until every rank's partial of this step is in local memory ----
     if (threadIdx.x < p.world) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.local + p.flags_off) + parity * p.world + threadIdx.x;
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.local + p.flags_off) +
+                               (static_cast<size_t>(parity) * p.world + threadIdx.x) * p.max_units;
         bool seen = false;
         for (uint32_t i = 0; i < p.max_polls; ++i) {
-            if (static_cast<int32_t>(ld_acquire_sys(flag) - stamp) >= 0) {
+            if (static_cast<int32_t>(ld_acquire_sys(flag) - stamp_value) >= 0) {
                 seen = true;
                 break;
             }
@@ -109,6 +123,7 @@ __global__ void __launch_bounds__(256) exchange_lse_combine_kernel(const Exchang
         }
     }
     __syncthreads();
+    stamp(3);
 
     // ---- 3. combine: m* = max_k m_k, w_k = exp(m_k - m*), O = sum_k o_k w_k / sum_k l_k w_k ----
     if (s_ok) {
@@ -146,6 +161,7 @@ __global__ void __launch_bounds__(256) exchange_lse_combine_kernel(const Exchang
 
     // ---- the last CTA to finish advances the step counter (graph replays need no host argument) ----
     __syncthreads();
+    stamp(4);
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(p.done, 1u) == gridDim.x - 1) {
@@ -180,7 +196,13 @@ int mlc_exchange_layout(int world, size_t max_rows, size_t head_dim, size_t* slo
     const size_t flags = ((2 * static_cast<size_t>(world) * slot * 4 + 255) / 256) * 256;
     if (slot_floats) *slot_floats = slot;
     if (flags_offset) *flags_offset = flags;
-    if (total_bytes) *total_bytes = flags + 256 /* flags [2][world] */ + 256 /* seq, done */;
+    // behind the flag words [2 parities][world] (256 bytes): the slots of the fused attention + exchange
+    // kernel, [2 parities][world] of max_rows * (head_dim * 8 + 16) bytes - every float travels beside a
+    // 4-byte step stamp, so that a row is known to be complete from its own bytes, without a flag behind a
+    // fence - then the step counter and the CTA count (256 bytes)
+    const size_t ll_slot = max_rows * (head_dim * 8 + 16);
+    const size_t ll_bytes = ((2 * static_cast<size_t>(world) * ll_slot + 255) / 256) * 256;
+    if (total_bytes) *total_bytes = flags + 256 + ll_bytes + 256;
     return MLC_OK;
 }
 
@@ -259,6 +281,38 @@ int mlc_exchange_attach_pointers(mlc_ctx* ctx, mlc_exchange* ex, void* const* ba
 
 void* mlc_exchange_local_buffer(const mlc_exchange* ex) { return ex ? ex->local : nullptr; }
 
+}  // extern "C"
+
+namespace mlcb {
+// What the fused attention + exchange kernel needs to know about an exchange object (attn_decode_tma.cu).
+bool exchange_describe(const mlc_exchange* ex, ExchangeView* v) {
+    if (!ex || !ex->attached) return false;
+    for (int r = 0; r < ex->world; ++r) v->peer[r] = ex->peer[r];
+    v->local = ex->local;
+    v->seq = reinterpret_cast<uint32_t*>(ex->local + ex->bytes - 256);
+    v->done = v->seq + 1;
+    v->slot_floats = ex->slot_floats;
+    v->flags_off = ex->flags_off;
+    v->ll_off = ex->flags_off + 256;
+    v->ll_slot_bytes = ex->max_rows * (ex->D * 8 + 16);
+    v->rank = static_cast<uint32_t>(ex->rank);
+    v->world = static_cast<uint32_t>(ex->world);
+    v->max_rows = ex->max_rows;
+    v->D = ex->D;
+    return true;
+}
+}  // namespace mlcb
+
+extern "C" {
+
+int mlc_exchange_read_trace(mlc_ctx* ctx, unsigned long long* out8) {
+    if (!ctx || !out8 || !ctx->d_trace) return MLC_ERR_INVALID_ARG;
+    DeviceGuard guard(ctx->device);
+    MLCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    MLCB_CUDA(ctx, cudaMemcpy(out8, ctx->d_trace + ctx->trace_words - 8, 64, cudaMemcpyDeviceToHost));
+    return MLC_OK;
+}
+
 size_t mlc_exchange_slot_floats(const mlc_exchange* ex) { return ex ? ex->slot_floats : 0; }
 
 int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float* o_partial, const float* ml_partial,
@@ -280,7 +334,8 @@ int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float*
     p.local = ex->local;
     p.out = out;
     p.err = ctx->d_err;
-    p.seq = reinterpret_cast<uint32_t*>(ex->local + ex->flags_off + 256);
+    p.seq = reinterpret_cast<uint32_t*>(ex->local + ex->bytes - 256);
+    p.max_units = 1;
     p.done = p.seq + 1;
     p.slot_floats = ex->slot_floats;
     p.flags_off = ex->flags_off;
@@ -289,6 +344,8 @@ int mlc_encode_exchange_lse_combine(mlc_ctx* ctx, mlc_exchange* ex, const float*
     p.rows = static_cast<uint32_t>(rows);
     p.D = static_cast<uint32_t>(ex->D);
     p.max_polls = ctx->wait_limit ? ctx->wait_limit : kMaxPolls;
+    // stamps of the exchange go behind the decode kernel's in the trace buffer (its last 8 words)
+    p.trace = ctx->d_trace ? ctx->d_trace + ctx->trace_words - 8 : nullptr;
     const size_t total = rows * (ex->D / 4);
     size_t blocks = (total + 255) / 256;
     if (blocks < static_cast<size_t>(ex->world)) blocks = ex->world;

@@ -66,3 +66,41 @@ def test_exchange_wait_runs_out_and_context_stays_usable(executor, oracle_mod):
     want = oracle_mod.paged_attention(case.q.astype(np.float32), case.k_pool, case.v_pool, case.pt_flat, case.pt_off,
                                       case.seq_lens, case.q_pos, case.H, case.KVH, case.D, case.P, scale=case.scale)
     assert_attention_close(o.float().cpu().numpy(), want)
+
+
+def test_fused_exchange_wait_runs_out_and_context_stays_usable(executor, oracle_mod):
+    """The same with the fused attention + exchange kernel: rank 1 never runs, so the CTAs that finish a
+    (request, head) wait for its flag in vain, record the timeout and skip their combine."""
+    import torch
+    case = synth.make_case(6, [300, 64, 1000], **synth.SHAPE_A)
+    dc = DeviceCase(case)
+    rows = case.N * case.H
+    ex0 = PeerExchange(executor, 0, 2, rows, case.D)
+    ex1 = PeerExchange(executor, 1, 2, rows, case.D)    # the absent rank
+    ex0.attach_pointers([0, ex1.local_buffer()])
+    plan = executor.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, case.N, case.H, case.KVH, case.D,
+                               case.P, True, case.capacity)
+    out = dc.out()
+    assert executor.setWaitLimit(1000)
+    try:
+        assert executor.beginForwardPassCB()
+        assert ex0.encodeAttentionExchange(plan, dc.q, dc.k_pool, dc.v_pool, out, case.scale, MLC_F16, MLC_F16), \
+            executor.last_error()
+        assert not executor.flushForwardPassCB()
+        assert executor.last_status == MLC_ERR_DEVICE_FLAG, executor.last_error()
+        word = int(executor.last_error().split("0x")[1].split()[0], 16)
+        assert word & MLC_DEVERR_WAIT_TIMEOUT and (word >> 8) & 0xFF == 0x51
+        torch.cuda.synchronize()
+        assert torch.isnan(out.float()).all(), "no combine may have written output"
+    finally:
+        assert executor.setWaitLimit(0)
+        ex0.destroy()
+        ex1.destroy()
+        plan.destroy()
+    o = dc.out()
+    assert executor.runPagedFlashAttention(dc.q, dc.k_pool, dc.v_pool, o, case.pt_flat, case.pt_off, case.seq_lens,
+                                           case.q_pos, case.N, case.H, case.KVH, case.D, case.P, True,
+                                           scale=case.scale, q_dtype=MLC_F16, o_dtype=MLC_F16), executor.last_error()
+    want = oracle_mod.paged_attention(case.q.astype(np.float32), case.k_pool, case.v_pool, case.pt_flat, case.pt_off,
+                                      case.seq_lens, case.q_pos, case.H, case.KVH, case.D, case.P, scale=case.scale)
+    assert_attention_close(o.float().cpu().numpy(), want)
