@@ -125,3 +125,33 @@ def shard_requests_by_kv_bytes(seq_lens, n_shards: int) -> list[list[int]]:
     for lst in out:
         lst.sort()
     return out
+
+
+# ---- synthetic quantised weights for the ops around attention -------------------------------------------
+# The reference's walker multiplies activations with GGUF tensors in Q4_0 (projections) and Q6_K (lm_head)
+# format. No model file exists here, so weight matrices are drawn directly in the quantised formats: any
+# byte pattern with a finite scale is a valid matrix, and scales are chosen so that the de-quantised weights
+# have about the spread of a trained projection (standard deviation ~ 1 / sqrt(cols)).
+def random_q4_0(rng: np.random.Generator, rows: int, cols: int) -> np.ndarray:
+    """uint8 [rows, cols / 32 * 18]: per block an fp16 scale and 16 bytes of nibbles (quantization.cpp:71-74)."""
+    assert cols % 32 == 0
+    nb = cols // 32
+    out = np.zeros((rows, nb, 18), np.uint8)
+    # nibbles uniform in 0..15 -> (q - 8) has standard deviation ~4.6; d sets the weight spread
+    d = (np.abs(rng.standard_normal((rows, nb))) * 0.3 + 0.7) / (4.6 * np.sqrt(cols))
+    out[:, :, 0:2] = d.astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    out[:, :, 2:] = rng.integers(0, 256, size=(rows, nb, 16), dtype=np.uint8)
+    return out.reshape(rows, nb * 18)
+
+
+def random_q6_k(rng: np.random.Generator, rows: int, cols: int) -> np.ndarray:
+    """uint8 [rows, cols / 256 * 210]: ql[128] | qh[64] | int8 scales[16] | fp16 d (quantization.cpp:142-147)."""
+    assert cols % 256 == 0
+    nb = cols // 256
+    out = np.zeros((rows, nb, 210), np.uint8)
+    out[:, :, 0:192] = rng.integers(0, 256, size=(rows, nb, 192), dtype=np.uint8)
+    out[:, :, 192:208] = rng.integers(-96, 97, size=(rows, nb, 16)).astype(np.int8).view(np.uint8)
+    # 6-bit values (q - 32) have standard deviation ~18.5, scales ~55
+    d = (np.abs(rng.standard_normal((rows, nb))) * 0.3 + 0.7) / (18.5 * 55.0 * np.sqrt(cols))
+    out[:, :, 208:210] = d.astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    return out.reshape(rows, nb * 210)

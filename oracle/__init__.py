@@ -29,11 +29,15 @@ _fp = C.POINTER(C.c_float)
 _vp, _sz, _u32, _i, _f = C.c_void_p, C.c_size_t, C.c_uint32, C.c_int, C.c_float
 
 
+PORT_SOURCES = ["paged_oracle.c", "layer_oracle.c"]
+
+
 def build_port(force: bool = False) -> Path:
-    src = HERE / "paged_oracle.c"
-    if force or not PORT_LIB.exists() or PORT_LIB.stat().st_mtime < src.stat().st_mtime:
-        subprocess.run(["gcc", "-O2", "-fPIC", "-shared", "-std=c11", "-o", str(PORT_LIB), str(src), "-lm"],
-                       check=True)
+    srcs = [HERE / n for n in PORT_SOURCES]
+    # -ffp-contract=off: the restatements must round like the reference's scalar C++ (no fused multiply-add)
+    if force or not PORT_LIB.exists() or PORT_LIB.stat().st_mtime < max(s.stat().st_mtime for s in srcs):
+        subprocess.run(["gcc", "-O2", "-fPIC", "-shared", "-std=c11", "-ffp-contract=off", "-o", str(PORT_LIB),
+                        *map(str, srcs), "-lm"], check=True)
     return PORT_LIB
 
 
@@ -82,6 +86,25 @@ def port():
         lib.orc_pool_free.restype = _sz
         lib.orc_pool_free.argtypes = [_vp]
         lib.orc_kvstate_extend.argtypes = [_vp, _u32, _u32p, C.POINTER(_sz), _u32p, _u32p, _u32p]
+        # layer_oracle.c
+        _u8p = C.POINTER(C.c_uint8)
+        lib.orc_rms_norm_batched.restype = None
+        lib.orc_rms_norm_batched.argtypes = [_fp, _fp, _f, _u32, _u32, _fp]
+        lib.orc_add.restype = None
+        lib.orc_add.argtypes = [_fp, _fp, _fp, _sz]
+        lib.orc_silu_mul.restype = None
+        lib.orc_silu_mul.argtypes = [_fp, _fp, _fp, _sz]
+        lib.orc_gate_up_split_silu_mul.restype = None
+        lib.orc_gate_up_split_silu_mul.argtypes = [_fp, _u32, _u32, _u32, _fp, _fp, _fp]
+        for q in ("q4_0", "q6_k"):
+            getattr(lib, f"orc_row_size_{q}").restype = _sz
+            getattr(lib, f"orc_row_size_{q}").argtypes = [_sz]
+            getattr(lib, f"orc_dequant_row_{q}").restype = None
+            getattr(lib, f"orc_dequant_row_{q}").argtypes = [_u8p, _sz, _fp]
+            getattr(lib, f"orc_dot_row_{q}").restype = _f
+            getattr(lib, f"orc_dot_row_{q}").argtypes = [_u8p, _sz, _fp]
+            getattr(lib, f"orc_matmul_{q}_batched").restype = None
+            getattr(lib, f"orc_matmul_{q}_batched").argtypes = [_u8p, _fp, _u32, _u32, _u32, _sz, _fp]
         _port = lib
     return _port
 
@@ -130,6 +153,15 @@ def ref():
         lib.ref_kvstate_total.restype = _sz
         lib.ref_kvstate_total.argtypes = [_vp]
         lib.ref_kvstate_release.argtypes = [_vp, _vp]
+        _u8p = C.POINTER(C.c_uint8)
+        lib.ref_elementwise_node.argtypes = [_i, _fp, _fp, _sz, _fp]
+        for q in ("q4_0", "q6_k"):
+            getattr(lib, f"ref_dequant_{q}").restype = None
+            getattr(lib, f"ref_dequant_{q}").argtypes = [_u8p, _sz, _fp]
+            getattr(lib, f"ref_dot_{q}").restype = _f
+            getattr(lib, f"ref_dot_{q}").argtypes = [_u8p, _sz, _fp]
+            getattr(lib, f"ref_row_size_{q}").restype = _sz
+            getattr(lib, f"ref_row_size_{q}").argtypes = [_sz]
         _ref = lib
     return _ref
 
@@ -285,3 +317,57 @@ def qkv_split_rope_cast(qkv, cos_t, sin_t, H, KVH, D, rotary_dim):
                                    _p(v16, _u16p), _p(cos_t, _fp), _p(sin_t, _fp), batch, H, KVH, D,
                                    qkv_rows, q_rows, k_rows, k_rows, rotary_dim)
     return q, k, v, k16, v16
+
+
+# ---- the walker step's other ops (layer_oracle.c) ---------------------------------------
+_u8p = C.POINTER(C.c_uint8)
+
+
+def rms_norm_batched(x, weight, eps=1e-5):
+    """x [batch, length] fp32, weight [length] -> [batch, length] (orc_rms_norm_batched)."""
+    x = _c(x, np.float32)
+    w = _c(weight, np.float32)
+    out = np.zeros_like(x)
+    port().orc_rms_norm_batched(_p(x, _fp), _p(w, _fp), float(eps), x.shape[0], x.shape[1], _p(out, _fp))
+    return out
+
+
+def add(a, b):
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    out = np.zeros_like(a)
+    port().orc_add(_p(a, _fp), _p(b, _fp), _p(out, _fp), a.size)
+    return out
+
+
+def gate_up_split_silu_mul(gate_up, ffn_inner):
+    """gate_up [batch, rows >= 2 * ffn_inner] -> (gate, up, SiLU(gate) * up), each [batch, ffn_inner]."""
+    gu = _c(gate_up, np.float32)
+    batch, rows = gu.shape
+    gate, up, out = (np.zeros((batch, ffn_inner), np.float32) for _ in range(3))
+    port().orc_gate_up_split_silu_mul(_p(gu, _fp), batch, ffn_inner, rows, _p(gate, _fp), _p(up, _fp), _p(out, _fp))
+    return gate, up, out
+
+
+def row_size(kind: str, cols: int) -> int:
+    return int(getattr(port(), f"orc_row_size_{kind}")(cols))
+
+
+def dequant_rows(kind: str, weights, rows: int, cols: int):
+    """Quantised rows (uint8 [rows, row_stride]) -> fp32 [rows, cols]."""
+    w = _c(weights, np.uint8).reshape(rows, -1)
+    out = np.zeros((rows, cols), np.float32)
+    fn = getattr(port(), f"orc_dequant_row_{kind}")
+    for r in range(rows):
+        fn(w[r].ctypes.data_as(_u8p), cols, out[r].ctypes.data_as(_fp))
+    return out
+
+
+def matmul_quant_batched(kind: str, weights, x, rows: int, cols: int):
+    """out[n, r] = sum_c W[r, c] * x[n, c] with W quantised as `kind` ("q4_0" / "q6_k"), fp32 sums in the
+    order of the reference's CPU row functions."""
+    w = _c(weights, np.uint8).reshape(rows, -1)
+    x = _c(x, np.float32)
+    out = np.zeros((x.shape[0], rows), np.float32)
+    getattr(port(), f"orc_matmul_{kind}_batched")(w.ctypes.data_as(_u8p), _p(x, _fp), x.shape[0], rows, cols,
+                                                  w.shape[1], _p(out, _fp))
+    return out

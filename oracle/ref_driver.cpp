@@ -243,4 +243,67 @@ void ref_apply_rotary(float* data, const float* cos_in, const float* sin_in, siz
     applyRotaryEmbedding(data, c, s, head_dim, rotary_dim);
 }
 
+
+// ---- the other ops of the batched walker's step (compiler/runtime/batched_walker.cpp:248-297, 333-458),
+// through the reference's own CPU code: quantised rows through quantization.cpp's row functions, RMSNorm /
+// SiLU-mul / Add through CpuExecutionBackend nodes of a one-node graph (operator_backend.cpp:574-643, 645-886,
+// 1144-1200).
+void ref_dequant_q4_0(const uint8_t* src, size_t cols, float* dst) { dequantizeRowQ4_0(src, cols, 2, dst); }
+float ref_dot_q4_0(const uint8_t* src, size_t cols, const float* vec) { return dotProductRowQ4_0(src, cols, 2, vec); }
+size_t ref_row_size_q4_0(size_t cols) { return q4_0RowSize(cols, 2); }
+void ref_dequant_q6_k(const uint8_t* src, size_t cols, float* dst) { dequantizeRowQ6_K(src, cols, dst); }
+float ref_dot_q6_k(const uint8_t* src, size_t cols, const float* vec) { return dotProductRowQ6_K(src, cols, vec); }
+size_t ref_row_size_q6_k(size_t cols) { return q6_kRowSize(cols); }
+
+// One CPU node over fp32 vectors. kind 0: Norm (RMS) with `weight` (n floats, served from a one-tensor GGUF as
+// the model parameter "norm.weight"); kind 1: FeedForward in its gate / up input form (SiLU(a) * b);
+// kind 2: Add (a + b). Returns 0 on success.
+int ref_elementwise_node(int kind, const float* a, const float* b_or_weight, size_t n, float* out) {
+    static std::atomic<int> counter{0};
+    std::string path = "/tmp/mlc_b200_oracle_ops_" + std::to_string(getpid()) + "_" + std::to_string(counter++) + ".gguf";
+    try {
+        {
+            std::ofstream f(path, std::ios::binary);
+            auto u32 = [&](uint32_t v) { f.write(reinterpret_cast<const char*>(&v), 4); };
+            auto u64 = [&](uint64_t v) { f.write(reinterpret_cast<const char*>(&v), 8); };
+            auto str = [&](const std::string& s) { u64(s.size()); f.write(s.data(), s.size()); };
+            u32(0x46554747); u32(1); u64(1); u64(0);
+            str("norm.weight"); u32(2); u64(2); u32(static_cast<uint32_t>(n)); u32(1); u32(0); u64(256);
+            f.seekp(256, std::ios::beg);
+            std::vector<float> w(n, 1.0f);
+            if (kind == 0) w.assign(b_or_weight, b_or_weight + n);
+            f.write(reinterpret_cast<const char*>(w.data()), static_cast<std::streamsize>(n * sizeof(float)));
+        }
+        Session session(path);
+        ExecutionGraph graph;
+        const std::vector<int64_t> shape{static_cast<int64_t>(n)};
+        graph.addTensor("a", shape, mlc::ir::DataType::F32);
+        graph.addTensor("b", shape, mlc::ir::DataType::F32);
+        graph.addTensor("y", shape, mlc::ir::DataType::F32);
+        if (kind == 0) {
+            auto& node = graph.addNode("norm", ExecOpType::Norm, {"a"}, {"y"}, BackendKind::CPU);
+            node.annotations["weight"] = "norm.weight";
+        } else if (kind == 1) {
+            graph.addNode("ffn", ExecOpType::FeedForward, {"a", "b"}, {"y"}, BackendKind::CPU);
+        } else {
+            graph.addNode("add", ExecOpType::Add, {"a", "b"}, {"y"}, BackendKind::CPU);
+        }
+        ExecutionContext context(session, &graph);
+        context.setTensor("a", std::vector<float>(a, a + n));
+        if (kind != 0) context.setTensor("b", std::vector<float>(b_or_weight, b_or_weight + n));
+        ExecutionExecutor executor(graph, nullptr, &context);
+        auto res = executor.run();
+        ::unlink(path.c_str());
+        if (!res.success) return -1;
+        const auto* y = context.getTensor("y");
+        if (!y || y->size() != n) return -2;
+        std::memcpy(out, y->data(), n * sizeof(float));
+        return 0;
+    } catch (const std::exception& e) {
+        ::unlink(path.c_str());
+        std::fprintf(stderr, "ref_elementwise_node: %s\n", e.what());
+        return -3;
+    }
+}
+
 }  // extern "C"
