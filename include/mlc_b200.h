@@ -54,6 +54,7 @@ typedef enum mlc_dtype { MLC_F32 = 0, MLC_F16 = 1 } mlc_dtype;
 #define MLC_DEVERR_WAIT_TIMEOUT 0x1u  /* a bounded mbarrier wait ran out */
 #define MLC_DEVERR_BAD_PAGE 0x2u      /* page id >= capacity seen by a checking kernel */
 #define MLC_DEVERR_BAD_SLOT 0x4u      /* slot >= page_size seen by a checking kernel */
+#define MLC_DEVERR_BAD_TOKEN 0x8u     /* token id >= vocabulary size seen by the embedding kernel */
 
 typedef struct mlc_ctx mlc_ctx;
 
@@ -389,6 +390,58 @@ int mlc_encode_qkv_split_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan*
 int mlc_compute_rotary_coefficients(size_t position, size_t rotary_dim, float freq_base, float freq_scale,
                                     float* cos_out, float* sin_out);
 
+/* ---- the other ops of the walker's decode step ------------------------------------------
+ * What compiler/runtime/batched_walker.cpp:248-297 and :333-458 encode around attention, on
+ * device buffers, onto the open pass (MLC_ERR_NO_OPEN_PASS otherwise, as every encode* of the
+ * reference returns false without an open command buffer). Weights are device pointers: the
+ * reference keeps them in a name-keyed buffer cache filled on first use, which a caller gets
+ * from mlc_cached_buffer + mlc_upload. Activations are fp32 like the reference's. */
+
+/* encodeRmsNormBatched (metal_runtime.hpp:474-479; kernel rms_norm_batched, metal_runtime.mm:166-209):
+ * out[r, i] = in[r, i] * (1 / sqrt(mean(in[r, :]^2) + epsilon)) * weight[i], fp32, factors in the
+ * order of operator_backend.cpp:186-204. weight: device fp32 [length]. out_f16 (may be NULL; no
+ * counterpart in the reference) receives the same rows rounded to fp16. */
+int mlc_encode_rms_norm_batched(mlc_ctx* ctx, const void* in, const void* weight, float epsilon, size_t batch,
+                                size_t length, void* out, void* out_f16);
+/* encodeAddBatched (metal_runtime.hpp:501-502; add_vectors, metal_runtime.mm:44-52): out = a + b. */
+int mlc_encode_add_batched(mlc_ctx* ctx, const void* a, const void* b, void* out, size_t total_elements);
+/* encodeSiluMulBatched (metal_runtime.hpp:505-506; feedforward_silu_mul, metal_runtime.mm:32-42):
+ * out = gate / (1 + exp(-gate)) * up. */
+int mlc_encode_silu_mul_batched(mlc_ctx* ctx, const void* gate, const void* up, void* out, size_t total_elements);
+/* encodeGateUpSplitSiluMul (metal_runtime.hpp:549-552; metal_runtime.mm:8030-8088: two strided
+ * copies + SiLU * mul in one encoder) as one launch. gate_up [batch, ffn_gate_up_rows] holds gate in
+ * columns [0, ffn_inner) and up in [ffn_inner, 2 * ffn_inner); gate / up ([batch, ffn_inner]) receive
+ * the copies and may be NULL; out [batch, ffn_inner]. */
+int mlc_encode_gate_up_split_silu_mul(mlc_ctx* ctx, const void* gate_up, void* gate, void* up, void* out, size_t batch,
+                                      size_t ffn_inner, size_t ffn_gate_up_rows);
+/* encodeMatMulQ4_0Batched / encodeMatMulQ6KBatched (metal_runtime.hpp:481-498; kernels
+ * q4_0_matmul_v3_batched, metal_runtime.mm:710-785, and q6_k_matmul_v3_batched, mm:1581-1655):
+ * out[n, r] = sum_c W[r, c] * in[n, c]. weights: device bytes, `rows` rows of `row_stride` bytes in
+ * the block format of quantization.cpp:71-74 (Q4_0: fp16 scale + 16 bytes per 32 weights) or
+ * :142-147 (Q6_K: 210 bytes per 256 weights); in [batch, cols], out [batch, rows] fp32.
+ * Tensor-core kernel: block integers exact, activations rounded to fp16, fp32 sums and scales.
+ * Limits (MLC_ERR_UNSUPPORTED): batch <= 64, cols a whole number of blocks, weights and
+ * row_stride 16-byte aligned. */
+int mlc_encode_matmul_q4_0_batched(mlc_ctx* ctx, const void* weights, const void* in, size_t batch, size_t rows,
+                                   size_t cols, size_t row_stride, void* out);
+int mlc_encode_matmul_q6k_batched(mlc_ctx* ctx, const void* weights, const void* in, size_t batch, size_t rows,
+                                  size_t cols, size_t row_stride, void* out);
+/* Embedding rows of a Q4_0 token table, dequantised on the device: the host loop of
+ * batched_walker.cpp:183-208 (dequantizeRowTo per request, then one upload) as one launch, bit for
+ * bit the CPU's rows. table: device bytes, `vocab` rows of row_stride bytes; token_ids: device
+ * uint32 [batch]; out fp32 [batch, cols]. A token id >= vocab yields a zero row and
+ * MLC_DEVERR_BAD_TOKEN in the device error word. */
+int mlc_encode_embedding_q4_0(mlc_ctx* ctx, const void* table, size_t row_stride, const void* token_ids, size_t batch,
+                              size_t cols, size_t vocab, void* out);
+/* The same mat-vec with its neighbours in the walker fused in (no counterpart in the reference):
+ * with silu_mul_input != 0 the input row n is SiLU(in[n, c]) * in[n, cols + c] computed on load
+ * (in = the gate | up buffer, in_stride >= 2 * cols: the step of batched_walker.cpp:379-394 without
+ * the intermediate buffers); with residual != NULL, out = residual + W in (the add of :349 / :403).
+ * quant: 0 = Q4_0, 1 = Q6_K. in_stride = floats between input rows. */
+int mlc_encode_matmul_quant_fused(mlc_ctx* ctx, int quant, const void* weights, const void* in, size_t in_stride,
+                                  int silu_mul_input, const void* residual, size_t batch, size_t rows, size_t cols,
+                                  size_t row_stride, void* out);
+
 /* ---- chunked (multi-token) causal paged attention ------------------------------------
  * The reference runs a paged prefill as q_len single-token decode passes
  * (compiler/runtime/batched_executor.cpp:450-467); these entry points compute the same
@@ -565,6 +618,37 @@ typedef struct mlc_executor mlc_executor;
 mlc_executor* mlc_paged_executor_create(mlc_ctx* ctx, uint32_t num_heads, uint32_t kv_heads, uint32_t head_dim,
                                         uint32_t n_layers, uint64_t qkv_seed);
 mlc_executor* mlc_callback_executor_create(const mlc_executor_callbacks* callbacks);
+/* A model for the paged executor: device-resident weights in the tensor roles the reference's
+ * walker reads from the GGUF file (batched_walker.cpp:183-208 token_embd, :248-405 per layer
+ * attn_norm / attn_qkv / attn_output / ffn_norm / ffn gate | up / ffn_down, :407-435 output_norm
+ * and the lm_head). Norm weights are fp32 [hidden_size]; mat-vec weights and the token table are
+ * Q4_0 rows, tightly packed; the lm_head is Q6_K (lm_head_quant = 1) or Q4_0 (0). hidden_size
+ * must equal num_heads * head_dim and, like ffn_inner, be a multiple of 256.
+ * With a model attached, mlc_executor_run_decode runs the whole walker step on the GPU and returns
+ * vocab_size logits per request; in the fused call order (the default) a layer is 8 launches, in
+ * the reference's call order (mlc_executor_set_call_order) the reference's 13, op for op. A prompt
+ * is fed token by token through the decode path, as batched_executor.cpp:450-467 does. The
+ * pointers must stay valid while the executor lives. */
+typedef struct mlc_layer_weights {
+    const void* attn_norm;
+    const void* attn_qkv;      /* [(num_heads + 2 kv_heads) * head_dim] rows of hidden_size */
+    const void* attn_output;   /* [hidden_size] rows of hidden_size */
+    const void* ffn_norm;
+    const void* ffn_gate_up;   /* [2 * ffn_inner] rows of hidden_size: gate rows, then up rows */
+    const void* ffn_down;      /* [hidden_size] rows of ffn_inner */
+} mlc_layer_weights;
+typedef struct mlc_model_desc {
+    uint32_t hidden_size, ffn_inner, vocab_size, rotary_dim;
+    float rope_base, rope_scale, rms_epsilon;
+    int32_t lm_head_quant;
+    const void* token_embd;    /* [vocab_size] Q4_0 rows of hidden_size */
+    const void* output_norm;
+    const void* lm_head;       /* [vocab_size] rows of hidden_size */
+    const mlc_layer_weights* layers;
+    uint32_t n_layers;
+} mlc_model_desc;
+int mlc_executor_attach_model(mlc_executor* exec, const mlc_model_desc* model);
+
 void mlc_executor_destroy(mlc_executor* exec);
 /* attach_page_pool / attach_paged_storage (batched_executor.hpp:73, 90); mlc_status. */
 int mlc_executor_attach_page_pool(mlc_executor* exec, mlc_page_pool* pool, uint32_t page_size_tokens);

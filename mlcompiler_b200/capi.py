@@ -72,6 +72,13 @@ _PROTOTYPES = {
     "mlc_encode_qkv_split_rope_cast": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz,
                                             _sz, _sz, _sz, _sz]),
     "mlc_encode_qkv_split_rope_scatter_planned": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _sz, _sz]),
+    "mlc_encode_rms_norm_batched": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
+    "mlc_encode_add_batched": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "mlc_encode_silu_mul_batched": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "mlc_encode_gate_up_split_silu_mul": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "mlc_encode_matmul_q4_0_batched": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp]),
+    "mlc_encode_matmul_q6k_batched": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp]),
+    "mlc_encode_matmul_quant_fused": (_i, [_vp, _i, _vp, _vp, _sz, _i, _vp, _sz, _sz, _sz, _sz, _vp]),
     "mlc_compute_rotary_coefficients": (_i, [_sz, _sz, _f, _f, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mlc_exchange_create": (_i, [_vp, _i, _i, _sz, _sz, C.POINTER(_vp)]),
     "mlc_exchange_handle": (_i, [_vp, _vp, _vp]),
@@ -432,6 +439,50 @@ class Executor:
         return self.status(self._lib.mlc_encode_paged_decode_pass_host(
             self._h, plan.handle, len(k_pages), _vp(_ptr(host_in)), _vp(_ptr(dev_in)), k_pages, v_pages,
             _vp(_ptr(dev_o)), _vp(_ptr(host_o)), float(scale), q_dtype, o_dtype, n_groups))
+
+    # -- the ops of the walker step around attention (metal_runtime.hpp:474-506, 549-552) --------
+    # Weights are device buffers here (the reference takes host vectors and caches them on the
+    # device by name: getOrAllocCachedBuffer + uploadToBuffer do the same).
+    def encodeRmsNormBatched(self, in_buf, weight_buf, epsilon, batch, length, out_buf, out_f16_buf=None) -> bool:
+        """metal_runtime.hpp:474-479. weight_buf: device fp32 [length]."""
+        return self.status(self._lib.mlc_encode_rms_norm_batched(
+            self._h, _vp(_ptr(in_buf)), _vp(_ptr(weight_buf)), epsilon, batch, length, _vp(_ptr(out_buf)),
+            _vp(_ptr(out_f16_buf)) if out_f16_buf is not None else None))
+
+    def encodeMatMulQ4_0Batched(self, weights_buf, in_buf, batch, rows, cols, row_stride, out_buf) -> bool:
+        """metal_runtime.hpp:481-489 (without weight_name / quant_version: the weights are already a device buffer)."""
+        return self.status(self._lib.mlc_encode_matmul_q4_0_batched(
+            self._h, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), batch, rows, cols, row_stride, _vp(_ptr(out_buf))))
+
+    def encodeMatMulQ6KBatched(self, weights_buf, in_buf, batch, rows, cols, row_stride, out_buf) -> bool:
+        """metal_runtime.hpp:491-498."""
+        return self.status(self._lib.mlc_encode_matmul_q6k_batched(
+            self._h, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), batch, rows, cols, row_stride, _vp(_ptr(out_buf))))
+
+    def encodeMatMulQuantFused(self, quant, weights_buf, in_buf, in_stride, silu_mul_input, residual_buf, batch, rows,
+                               cols, row_stride, out_buf) -> bool:
+        """The mat-vec with SiLU(gate) * up computed on load and / or the residual add in its epilogue."""
+        return self.status(self._lib.mlc_encode_matmul_quant_fused(
+            self._h, quant, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), in_stride, int(bool(silu_mul_input)),
+            _vp(_ptr(residual_buf)) if residual_buf is not None else None, batch, rows, cols, row_stride,
+            _vp(_ptr(out_buf))))
+
+    def encodeAddBatched(self, a_buf, b_buf, out_buf, total_elements) -> bool:
+        """metal_runtime.hpp:501-502."""
+        return self.status(self._lib.mlc_encode_add_batched(self._h, _vp(_ptr(a_buf)), _vp(_ptr(b_buf)),
+                                                            _vp(_ptr(out_buf)), total_elements))
+
+    def encodeSiluMulBatched(self, gate_buf, up_buf, out_buf, total_elements) -> bool:
+        """metal_runtime.hpp:505-506."""
+        return self.status(self._lib.mlc_encode_silu_mul_batched(self._h, _vp(_ptr(gate_buf)), _vp(_ptr(up_buf)),
+                                                                 _vp(_ptr(out_buf)), total_elements))
+
+    def encodeGateUpSplitSiluMul(self, gate_up_buf, gate_buf, up_buf, out_buf, batch, ffn_inner, ffn_gate_up_rows) -> bool:
+        """metal_runtime.hpp:549-552; gate_buf / up_buf may be None."""
+        opt = lambda b: _vp(_ptr(b)) if b is not None else None
+        return self.status(self._lib.mlc_encode_gate_up_split_silu_mul(
+            self._h, _vp(_ptr(gate_up_buf)), opt(gate_buf), opt(up_buf), _vp(_ptr(out_buf)), batch, ffn_inner,
+            ffn_gate_up_rows))
 
     def encodeQkvSplitRopeCast(self, qkv_buf, q_buf, k_buf, v_buf, k_f16_buf, v_f16_buf, cos_buf, sin_buf, batch,
                                num_heads, kv_heads, head_dim, qkv_rows, q_rows, k_rows, v_rows, rotary_dim) -> bool:

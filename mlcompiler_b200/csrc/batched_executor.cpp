@@ -112,6 +112,17 @@ BatchedDecodeOutput PagedAttentionExecutor::run_decode(const std::vector<Request
     return walker_->step(slots);
 }
 
+bool PagedAttentionExecutor::attach_model(const ModelWeights& m) {
+    if (m.layers.size() != L_ || !m.hidden_size || !m.ffn_inner || !m.vocab_size) return false;
+    if (m.hidden_size != H_ * D_ || m.hidden_size % 256 || m.ffn_inner % 256) return false;
+    if (m.rotary_dim > D_ || m.rotary_dim % 2) return false;
+    if (!m.token_embd || !m.output_norm || !m.lm_head) return false;
+    for (const auto& l : m.layers)
+        if (!l.attn_norm || !l.attn_qkv || !l.attn_output || !l.ffn_norm || !l.ffn_gate_up || !l.ffn_down) return false;
+    model_.reset(new ModelWeights(m));
+    return true;
+}
+
 std::vector<float> PagedAttentionExecutor::run_prefill(uint32_t request_id, const std::vector<uint64_t>& tokens) {
     // With paged storage the reference fills the pages token by token through the decode
     // path (batched_executor.cpp:450-467); that loop is kept for the reference call order.
@@ -120,7 +131,7 @@ std::vector<float> PagedAttentionExecutor::run_prefill(uint32_t request_id, cons
     std::vector<float> last;
     if (tokens.empty()) return last;
     size_t cursor = known_position(request_id);
-    if (order_ == CallOrder::Fused && storage_ && pool_) return walker_->prefill(request_id, tokens, cursor);
+    if (order_ == CallOrder::Fused && storage_ && pool_ && !model_) return walker_->prefill(request_id, tokens, cursor);
     for (uint64_t tok : tokens) {
         std::vector<RequestSlot> slot{{request_id, tok, cursor}};
         BatchedDecodeOutput out = run_decode(slot);

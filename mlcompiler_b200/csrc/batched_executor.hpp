@@ -70,6 +70,29 @@ private:
     uint64_t seed_;
 };
 
+// Device-resident weights of a Llama-style decoder in the reference's GGUF tensor roles
+// (batched_walker.cpp:248-458): per layer attn_norm, fused attn_qkv, attn_output, ffn_norm, fused
+// ffn gate | up, ffn_down (mat-vec weights Q4_0), then output_norm and the lm_head (Q6_K or Q4_0);
+// token_embd is a Q4_0 table. Rows are tightly packed (row stride = the format's row size).
+struct LayerWeights {
+    const float* attn_norm = nullptr;
+    const uint8_t* attn_qkv = nullptr;
+    const uint8_t* attn_output = nullptr;
+    const float* ffn_norm = nullptr;
+    const uint8_t* ffn_gate_up = nullptr;
+    const uint8_t* ffn_down = nullptr;
+};
+
+struct ModelWeights {
+    uint32_t hidden_size = 0, ffn_inner = 0, vocab_size = 0, rotary_dim = 0;
+    float rope_base = 10000.0f, rope_scale = 1.0f, rms_epsilon = 1e-5f;
+    int lm_head_quant = 1;   // 0 = Q4_0, 1 = Q6_K
+    const uint8_t* token_embd = nullptr;
+    const float* output_norm = nullptr;
+    const uint8_t* lm_head = nullptr;
+    std::vector<LayerWeights> layers;
+};
+
 class BatchedWalker;
 
 class PagedAttentionExecutor : public IBatchedExecutor {
@@ -88,6 +111,12 @@ public:
     void attach_page_pool(PagePool* pool, uint32_t page_size_tokens = 64);
     void attach_paged_storage(PagedKVStorage* storage) { storage_ = storage; }
     void set_call_order(CallOrder o) { order_ = o; }
+    // With a model attached a decode pass is the whole walker step - embedding, every layer's norms,
+    // mat-vecs, rotary, attention and residual adds, final norm and lm_head - and the logits are the model's
+    // [vocab_size] per request; a prompt is fed token by token through the decode path
+    // (batched_executor.cpp:450-467). Returns false if the description does not fit the executor.
+    bool attach_model(const ModelWeights& model);
+    bool has_model() const { return model_ != nullptr; }
     const RequestKVState* page_state(uint32_t request_id) const;
 
     BatchedDecodeOutput run_decode(const std::vector<RequestSlot>& slots) override;
@@ -112,6 +141,7 @@ private:
     mlc_ctx* ctx_;
     uint32_t H_, KVH_, D_, L_;
     std::unique_ptr<IQkvSource> source_;
+    std::unique_ptr<ModelWeights> model_;
     std::unordered_map<uint32_t, PerRequest> requests_;
     PagePool* pool_ = nullptr;
     uint32_t page_size_tokens_ = 64;

@@ -1,6 +1,7 @@
 // See batched_walker.hpp.
 #include "batched_walker.hpp"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 
@@ -59,6 +60,48 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
     }
     pt_off[N] = static_cast<uint32_t>(pt_flat.size());
 
+    const float scale = 1.0f / std::sqrt(static_cast<float>(D));
+    const size_t cap = storage->capacity_pages();
+    const bool fused = ex.order_ == PagedAttentionExecutor::CallOrder::Fused;
+    // Two plans that live as long as the executor, used by alternate passes and refreshed in place with the
+    // pass's tables: after the first two passes a decode pass allocates nothing (while the batch does not
+    // outgrow the plans' buffers), where creating and destroying a plan per pass cost a cudaMalloc /
+    // cudaFree pair and pinned allocations every time.
+    mlc_attn_plan* plan = nullptr;
+    if (fused) {
+        mlc_attn_plan*& slot = ex.plans_[ex.passes_++ & 1u];
+        const int st = slot ? mlc_attn_plan_update(ctx, slot, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
+                                                   q_pos.data(), page_ids.data(), slot_ids.data(), N)
+                            : mlc_attn_plan_create(ctx, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
+                                                   q_pos.data(), page_ids.data(), slot_ids.data(), N, H, KVH, D, P, 1, cap,
+                                                   &slot);
+        if (st != MLC_OK) return fail_all();
+        plan = slot;
+    }
+
+    if (ex.model_) {
+        // The whole walker step on the device; logits [N, vocab] come back (batched_walker.cpp:461-475).
+        void* logits_dev = nullptr;
+        bool ok = mlc_pass_begin(ctx) == MLC_OK;
+        ok = ok && encode_model_pass(slots, plan, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos, &logits_dev);
+        ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
+        if (!ok || !logits_dev) return fail_all();
+        const size_t vocab = ex.model_->vocab_size;
+        o_host_.resize(N * vocab);
+        if (mlc_download(ctx, logits_dev, o_host_.data(), o_host_.size() * sizeof(float), 0) != MLC_OK) return fail_all();
+        out.per_request.reserve(N);
+        for (size_t r = 0; r < N; ++r) {
+            BatchedDecodeOutput::PerRequest p;
+            p.request_id = slots[r].request_id;
+            p.success = true;
+            p.logits.assign(o_host_.begin() + static_cast<std::ptrdiff_t>(r * vocab),
+                            o_host_.begin() + static_cast<std::ptrdiff_t>((r + 1) * vocab));
+            reqs[r]->next_position = slots[r].sequence_position + 1;
+            out.per_request.push_back(std::move(p));
+        }
+        return out;
+    }
+
     // Name-keyed persistent device buffers, as the reference's walker keeps (163-180).
     const size_t q_bytes = N * H * D * sizeof(float), kv_bytes = N * KVH * D * sizeof(uint16_t);
     void* buf_q = mlc_cached_buffer(ctx, "walker_q", q_bytes * ex.L_);
@@ -79,24 +122,6 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
         mlc_upload(ctx, buf_v, v_host_.data(), kv_bytes * ex.L_, 0) != MLC_OK)
         return fail_all();
 
-    const float scale = 1.0f / std::sqrt(static_cast<float>(D));
-    const size_t cap = storage->capacity_pages();
-    const bool fused = ex.order_ == PagedAttentionExecutor::CallOrder::Fused;
-    // Two plans that live as long as the executor, used by alternate passes and refreshed in place with the
-    // pass's tables: after the first two passes a decode pass allocates nothing (while the batch does not
-    // outgrow the plans' buffers), where creating and destroying a plan per pass cost a cudaMalloc /
-    // cudaFree pair and pinned allocations every time.
-    mlc_attn_plan* plan = nullptr;
-    if (fused) {
-        mlc_attn_plan*& slot = ex.plans_[ex.passes_++ & 1u];
-        const int st = slot ? mlc_attn_plan_update(ctx, slot, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
-                                                   q_pos.data(), page_ids.data(), slot_ids.data(), N)
-                            : mlc_attn_plan_create(ctx, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
-                                                   q_pos.data(), page_ids.data(), slot_ids.data(), N, H, KVH, D, P, 1, cap,
-                                                   &slot);
-        if (st != MLC_OK) return fail_all();
-        plan = slot;
-    }
 
     bool ok = mlc_pass_begin(ctx) == MLC_OK;
     if (ok && fused) {
@@ -152,6 +177,129 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
     }
     return out;
 }
+
+// One decode pass of the model, layer by layer as the reference's walker encodes it
+// (batched_walker.cpp:183-458). In the reference's call order every op is its own launch, 13 per layer:
+// RMSNorm, QKV mat-vec, split + rotary + cast, scatter K, scatter V, attention, output mat-vec, add, RMSNorm,
+// gate | up mat-vec, split + SiLU * up, down mat-vec, add. The fused order makes the same step with 8:
+// the rotary kernel writes the K / V rows into the pools itself, the output and down projections add the
+// residual in their epilogue, and the down projection computes SiLU(gate) * up as it loads its input.
+bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc_attn_plan* plan,
+                                      const std::vector<uint32_t>& page_ids, const std::vector<uint32_t>& slot_ids,
+                                      const std::vector<uint32_t>& pt_flat, const std::vector<uint32_t>& pt_off,
+                                      const std::vector<uint32_t>& seq_lens, const std::vector<uint32_t>& q_pos,
+                                      void** logits_dev) {
+    PagedAttentionExecutor& ex = exec_;
+    mlc_ctx* ctx = ex.ctx_;
+    PagedKVStorage* storage = ex.storage_;
+    const ModelWeights& m = *ex.model_;
+    const size_t N = slots.size();
+    const uint32_t H = ex.H_, KVH = ex.KVH_, D = ex.D_, P = storage->page_size_tokens();
+    const size_t hidden = m.hidden_size, inner = m.ffn_inner, vocab = m.vocab_size;
+    const size_t q_rows = static_cast<size_t>(H) * D, k_rows = static_cast<size_t>(KVH) * D, qkv_rows = q_rows + 2 * k_rows;
+    const size_t row_h = hidden / 32 * 18, row_i = inner / 32 * 18;   // Q4_0 row sizes
+    const size_t cap = storage->capacity_pages();
+    const bool fused = ex.order_ == PagedAttentionExecutor::CallOrder::Fused && plan;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(D));
+    const float eps = m.rms_epsilon;
+
+    auto scratch = [&](const char* name, size_t bytes) { return mlc_cached_buffer(ctx, name, bytes); };
+    const size_t fb = sizeof(float);
+    void* residual = scratch("w_residual", N * hidden * fb);
+    void* norm_o = scratch("w_norm_out", N * hidden * fb);
+    void* qkv = scratch("w_qkv", N * qkv_rows * fb);
+    void* q = scratch("w_q", N * q_rows * fb);
+    void* attn_mix = scratch("w_attn_mix", N * hidden * fb);
+    void* resid1 = scratch("w_resid1", N * hidden * fb);
+    void* gate_up = scratch("w_gate_up", N * 2 * inner * fb);
+    void* final_n = scratch("w_final_norm", N * hidden * fb);
+    void* logits = scratch("w_logits", N * vocab * fb);
+    void* tokens = scratch("w_tokens", N * sizeof(uint32_t));
+    const size_t pairs = m.rotary_dim / 2;
+    void* cos_t = scratch("w_rope_cos", std::max<size_t>(1, N * pairs) * fb);
+    void* sin_t = scratch("w_rope_sin", std::max<size_t>(1, N * pairs) * fb);
+    if (!residual || !norm_o || !qkv || !q || !attn_mix || !resid1 || !gate_up || !final_n || !logits || !tokens ||
+        !cos_t || !sin_t)
+        return false;
+    // buffers only the reference's call order needs
+    void *k32 = nullptr, *v32 = nullptr, *k16 = nullptr, *v16 = nullptr, *attn_out = nullptr, *ffn_mix = nullptr,
+         *ffn_down = nullptr;
+    if (!fused) {
+        k32 = scratch("w_k", N * k_rows * fb);
+        v32 = scratch("w_v", N * k_rows * fb);
+        k16 = scratch("w_kv_f16_k", N * k_rows * 2);
+        v16 = scratch("w_kv_f16_v", N * k_rows * 2);
+        attn_out = scratch("w_attn_out", N * hidden * fb);
+        ffn_mix = scratch("w_ffn_mix", N * inner * fb);
+        ffn_down = scratch("w_ffn_down", N * hidden * fb);
+        if (!k32 || !v32 || !k16 || !v16 || !attn_out || !ffn_mix || !ffn_down) return false;
+    }
+
+    // token ids and the pass's rotary tables (position-only: one upload serves every layer, 215-236)
+    tok_host_.resize(N);
+    for (size_t r = 0; r < N; ++r) {
+        if (slots[r].input_token >= vocab) return false;
+        tok_host_[r] = static_cast<uint32_t>(slots[r].input_token);
+    }
+    if (mlc_upload(ctx, tokens, tok_host_.data(), N * sizeof(uint32_t), 0) != MLC_OK) return false;
+    if (pairs) {
+        cos_host_.resize(N * pairs);
+        sin_host_.resize(N * pairs);
+        for (size_t r = 0; r < N; ++r)
+            mlc_compute_rotary_coefficients(slots[r].sequence_position, m.rotary_dim, m.rope_base, m.rope_scale,
+                                            cos_host_.data() + r * pairs, sin_host_.data() + r * pairs);
+        if (mlc_upload(ctx, cos_t, cos_host_.data(), N * pairs * fb, 0) != MLC_OK ||
+            mlc_upload(ctx, sin_t, sin_host_.data(), N * pairs * fb, 0) != MLC_OK)
+            return false;
+    }
+
+    bool ok = mlc_encode_embedding_q4_0(ctx, m.token_embd, row_h, tokens, N, hidden, vocab, residual) == MLC_OK;
+    for (uint32_t L = 0; ok && L < ex.L_; ++L) {
+        const LayerWeights& w = m.layers[L];
+        void* kp = storage->k_buffer(L);
+        void* vp = storage->v_buffer(L);
+        ok = mlc_encode_rms_norm_batched(ctx, residual, w.attn_norm, eps, N, hidden, norm_o, nullptr) == MLC_OK &&
+             mlc_encode_matmul_q4_0_batched(ctx, w.attn_qkv, norm_o, N, qkv_rows, hidden, row_h, qkv) == MLC_OK;
+        if (!ok) break;
+        if (fused) {
+            ok = mlc_encode_qkv_split_rope_scatter_planned(ctx, plan, qkv, q, MLC_F16, kp, vp, cos_t, sin_t, qkv_rows,
+                                                           m.rotary_dim) == MLC_OK &&
+                 mlc_encode_paged_flash_attention_planned(ctx, plan, q, kp, vp, attn_mix, scale, MLC_F16, MLC_F32) == MLC_OK &&
+                 mlc_encode_matmul_quant_fused(ctx, 0, w.attn_output, attn_mix, hidden, 0, residual, N, hidden, hidden,
+                                               row_h, resid1) == MLC_OK &&
+                 mlc_encode_rms_norm_batched(ctx, resid1, w.ffn_norm, eps, N, hidden, norm_o, nullptr) == MLC_OK &&
+                 mlc_encode_matmul_q4_0_batched(ctx, w.ffn_gate_up, norm_o, N, 2 * inner, hidden, row_h, gate_up) == MLC_OK &&
+                 mlc_encode_matmul_quant_fused(ctx, 0, w.ffn_down, gate_up, 2 * inner, 1, resid1, N, hidden, inner, row_i,
+                                               residual) == MLC_OK;
+        } else {
+            ok = mlc_encode_qkv_split_rope_cast(ctx, qkv, q, k32, v32, k16, v16, cos_t, sin_t, N, H, KVH, D, qkv_rows,
+                                                q_rows, k_rows, k_rows, m.rotary_dim) == MLC_OK &&
+                 mlc_encode_scatter_kv_paged_batched_f16(ctx, kp, page_ids.data(), slot_ids.data(), P, KVH, D, N, k16,
+                                                         cap) == MLC_OK &&
+                 mlc_encode_scatter_kv_paged_batched_f16(ctx, vp, page_ids.data(), slot_ids.data(), P, KVH, D, N, v16,
+                                                         cap) == MLC_OK &&
+                 mlc_encode_paged_flash_attention(ctx, q, kp, vp, attn_mix, pt_flat.data(), pt_flat.size(), pt_off.data(),
+                                                  seq_lens.data(), q_pos.data(), N, H, KVH, D, P, 1, scale, MLC_F32,
+                                                  MLC_F32, cap) == MLC_OK &&
+                 mlc_encode_matmul_q4_0_batched(ctx, w.attn_output, attn_mix, N, hidden, hidden, row_h, attn_out) == MLC_OK &&
+                 mlc_encode_add_batched(ctx, residual, attn_out, resid1, N * hidden) == MLC_OK &&
+                 mlc_encode_rms_norm_batched(ctx, resid1, w.ffn_norm, eps, N, hidden, norm_o, nullptr) == MLC_OK &&
+                 mlc_encode_matmul_q4_0_batched(ctx, w.ffn_gate_up, norm_o, N, 2 * inner, hidden, row_h, gate_up) == MLC_OK &&
+                 mlc_encode_gate_up_split_silu_mul(ctx, gate_up, nullptr, nullptr, ffn_mix, N, inner, 2 * inner) == MLC_OK &&
+                 mlc_encode_matmul_q4_0_batched(ctx, w.ffn_down, ffn_mix, N, hidden, inner, row_i, ffn_down) == MLC_OK &&
+                 mlc_encode_add_batched(ctx, resid1, ffn_down, residual, N * hidden) == MLC_OK;
+        }
+    }
+    ok = ok && mlc_encode_rms_norm_batched(ctx, residual, m.output_norm, eps, N, hidden, final_n, nullptr) == MLC_OK;
+    if (ok) {
+        ok = m.lm_head_quant == 1
+                 ? mlc_encode_matmul_q6k_batched(ctx, m.lm_head, final_n, N, vocab, hidden, hidden / 256 * 210, logits) == MLC_OK
+                 : mlc_encode_matmul_q4_0_batched(ctx, m.lm_head, final_n, N, vocab, hidden, row_h, logits) == MLC_OK;
+    }
+    *logits_dev = logits;
+    return ok;
+}
+
 
 std::vector<float> BatchedWalker::prefill(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor) {
     PagedAttentionExecutor& ex = exec_;

@@ -21,7 +21,15 @@ public:
     std::vector<float> prefill(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor);
 
 private:
+    // The layers of a pass with a model attached: encodes embedding .. lm_head onto the open pass.
+    bool encode_model_pass(const std::vector<RequestSlot>& slots, mlc_attn_plan* plan, const std::vector<uint32_t>& page_ids,
+                           const std::vector<uint32_t>& slot_ids, const std::vector<uint32_t>& pt_flat,
+                           const std::vector<uint32_t>& pt_off, const std::vector<uint32_t>& seq_lens,
+                           const std::vector<uint32_t>& q_pos, void** logits_dev);
+
     PagedAttentionExecutor& exec_;
+    std::vector<float> cos_host_, sin_host_;
+    std::vector<uint32_t> tok_host_;
     // host staging, reused across passes
     std::vector<float> q_host_;
     std::vector<uint16_t> k_host_, v_host_;

@@ -169,6 +169,29 @@ int mlc_executor_attach_paged_storage(mlc_executor* e, mlc_kv_storage* storage) 
     e->paged->attach_paged_storage(storage ? storage->s.get() : nullptr);
     return MLC_OK;
 }
+int mlc_executor_attach_model(mlc_executor* e, const mlc_model_desc* d) {
+    if (!e || !e->paged || !d || !d->layers) return MLC_ERR_INVALID_ARG;
+    ModelWeights m;
+    m.hidden_size = d->hidden_size;
+    m.ffn_inner = d->ffn_inner;
+    m.vocab_size = d->vocab_size;
+    m.rotary_dim = d->rotary_dim;
+    m.rope_base = d->rope_base;
+    m.rope_scale = d->rope_scale;
+    m.rms_epsilon = d->rms_epsilon > 0.0f ? d->rms_epsilon : 1e-5f;
+    m.lm_head_quant = d->lm_head_quant;
+    m.token_embd = static_cast<const uint8_t*>(d->token_embd);
+    m.output_norm = static_cast<const float*>(d->output_norm);
+    m.lm_head = static_cast<const uint8_t*>(d->lm_head);
+    m.layers.resize(d->n_layers);
+    for (uint32_t i = 0; i < d->n_layers; ++i) {
+        const mlc_layer_weights& w = d->layers[i];
+        m.layers[i] = {static_cast<const float*>(w.attn_norm), static_cast<const uint8_t*>(w.attn_qkv),
+                       static_cast<const uint8_t*>(w.attn_output), static_cast<const float*>(w.ffn_norm),
+                       static_cast<const uint8_t*>(w.ffn_gate_up), static_cast<const uint8_t*>(w.ffn_down)};
+    }
+    return e->paged->attach_model(m) ? MLC_OK : MLC_ERR_INVALID_ARG;
+}
 int mlc_executor_set_call_order(mlc_executor* e, int reference_order) {
     if (!e || !e->paged) return MLC_ERR_INVALID_ARG;
     e->paged->set_call_order(reference_order ? PagedAttentionExecutor::CallOrder::Reference

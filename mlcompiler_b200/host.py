@@ -30,6 +30,17 @@ RELEASE_CB = C.CFUNCTYPE(None, _vp, _u32)
 TOKEN_CB = C.CFUNCTYPE(None, _vp, _u32, _u64)
 
 
+class LayerWeightsC(C.Structure):
+    _fields_ = [(n, _vp) for n in ("attn_norm", "attn_qkv", "attn_output", "ffn_norm", "ffn_gate_up", "ffn_down")]
+
+
+class ModelDescC(C.Structure):
+    _fields_ = [("hidden_size", _u32), ("ffn_inner", _u32), ("vocab_size", _u32), ("rotary_dim", _u32),
+                ("rope_base", C.c_float), ("rope_scale", C.c_float), ("rms_epsilon", C.c_float),
+                ("lm_head_quant", C.c_int32), ("token_embd", _vp), ("output_norm", _vp), ("lm_head", _vp),
+                ("layers", C.POINTER(LayerWeightsC)), ("n_layers", _u32)]
+
+
 class ExecutorCallbacksC(C.Structure):
     _fields_ = [("user", _vp), ("run_decode", RUN_DECODE_CB), ("run_prefill", RUN_PREFILL_CB),
                 ("release_request", RELEASE_CB)]
@@ -65,6 +76,7 @@ _PROTOTYPES = {
     "mlc_executor_attach_page_pool": (_i, [_vp, _vp, _u32]),
     "mlc_executor_attach_paged_storage": (_i, [_vp, _vp]),
     "mlc_executor_set_call_order": (_i, [_vp, _i]),
+    "mlc_executor_attach_model": (_i, [_vp, C.POINTER(ModelDescC)]),
     "mlc_executor_run_decode": (_sz, [_vp, C.POINTER(RequestSlotC), _sz, C.POINTER(C.c_uint8), _fp, _sz]),
     "mlc_executor_run_prefill": (_sz, [_vp, _u32, _u64p, _sz, _fp, _sz]),
     "mlc_executor_release_request": (None, [_vp, _u32]),
@@ -244,19 +256,39 @@ class PagedAttentionExecutor(_ExecutorBase):
     def set_call_order(self, reference_order: bool):
         assert lib().mlc_executor_set_call_order(self._h, 1 if reference_order else 0) == 0
 
+    def attach_model(self, model) -> bool:
+        """model: a synth.SyntheticModel (or anything with its fields) whose `device` dict maps tensor names to
+        device buffers. Afterwards run_decode returns vocab_size logits per request."""
+        dev = model.device
+        ptr = lambda name: _vp(int(dev[name].data_ptr()))
+        layers = (LayerWeightsC * self.L)()
+        for l in range(self.L):
+            pre = f"blk.{l}."
+            layers[l] = LayerWeightsC(ptr(pre + "attn_norm.weight"), ptr(pre + "attn_qkv.weight"),
+                                      ptr(pre + "attn_output.weight"), ptr(pre + "ffn_norm.weight"),
+                                      ptr(pre + "ffn_gate_up.weight"), ptr(pre + "ffn_down.weight"))
+        desc = ModelDescC(model.hidden_size, model.ffn_inner, model.vocab_size, model.rotary_dim, model.rope_base,
+                          model.rope_scale, model.rms_epsilon, 1 if model.lm_head_quant == "q6_k" else 0,
+                          ptr("token_embd.weight"), ptr("output_norm.weight"), ptr("output.weight"), layers, self.L)
+        self._model = (model, layers)          # the executor keeps the pointers: keep the buffers alive
+        ok = lib().mlc_executor_attach_model(self._h, C.byref(desc)) == 0
+        if ok:
+            self._logit_count = model.vocab_size
+        return ok
+
     def run_decode(self, slots):
         """slots: [(request_id, input_token, sequence_position)] -> [(request_id, success, logits or None)]"""
         n = len(slots)
         arr = (RequestSlotC * max(n, 1))(*[RequestSlotC(*s) for s in slots])
         success = (C.c_uint8 * max(n, 1))()
-        stride = self.H * self.D
+        stride = getattr(self, "_logit_count", self.H * self.D)
         logits = np.zeros((max(n, 1), stride), np.float32)
         got = lib().mlc_executor_run_decode(self._h, arr, n, success, logits.ctypes.data_as(_fp), stride)
         return [(slots[i][0], bool(success[i]), logits[i].copy() if success[i] else None) for i in range(got)]
 
     def run_prefill(self, request_id, tokens):
         toks = (C.c_uint64 * max(len(tokens), 1))(*tokens)
-        out = np.zeros(self.H * self.D, np.float32)
+        out = np.zeros(getattr(self, "_logit_count", self.H * self.D), np.float32)
         n = lib().mlc_executor_run_prefill(self._h, request_id, toks, len(tokens), out.ctypes.data_as(_fp), out.size)
         return out[:n].copy()
 

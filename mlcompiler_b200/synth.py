@@ -155,3 +155,48 @@ def random_q6_k(rng: np.random.Generator, rows: int, cols: int) -> np.ndarray:
     d = (np.abs(rng.standard_normal((rows, nb))) * 0.3 + 0.7) / (18.5 * 55.0 * np.sqrt(cols))
     out[:, :, 208:210] = d.astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
     return out.reshape(rows, nb * 210)
+
+
+class SyntheticModel:
+    """Seeded random weights of a Llama-style decoder in the tensor names and formats the reference's walker
+    reads (compiler/runtime/batched_walker.cpp:183-458): Q4_0 token table and mat-vec weights, fp32 norm
+    weights, Q6_K (or Q4_0) lm_head. `host` maps tensor name -> numpy array; to_device() fills `device`
+    with torch tensors of the same bytes. There is no checkpoint to load in this repository's tests and
+    benchmarks, so the values are synthetic; shapes and formats are the model's."""
+
+    def __init__(self, seed, n_layers, num_heads, kv_heads, head_dim, ffn_inner, vocab_size, rotary_dim=None,
+                 lm_head_quant="q6_k", rope_base=10000.0, rope_scale=1.0, rms_epsilon=1e-5):
+        rng = np.random.default_rng(seed)
+        self.n_layers, self.num_heads, self.kv_heads, self.head_dim = n_layers, num_heads, kv_heads, head_dim
+        self.hidden_size = num_heads * head_dim
+        self.ffn_inner, self.vocab_size = ffn_inner, vocab_size
+        self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
+        self.lm_head_quant, self.rope_base, self.rope_scale, self.rms_epsilon = lm_head_quant, rope_base, rope_scale, rms_epsilon
+        self.qkv_rows = (num_heads + 2 * kv_heads) * head_dim
+        h = self.hidden_size
+        t = {}
+        # embedding rows of unit scale: the generic generator normalises by sqrt(cols), undo that
+        emb = random_q4_0(rng, vocab_size, h).reshape(vocab_size, h // 32, 18)
+        d = emb[:, :, 0:2].copy().view(np.float16).astype(np.float32) * np.sqrt(h)
+        emb[:, :, 0:2] = d.astype(np.float16).view(np.uint8).reshape(vocab_size, h // 32, 2)
+        t["token_embd.weight"] = emb.reshape(vocab_size, -1)
+        for l in range(n_layers):
+            pre = f"blk.{l}."
+            t[pre + "attn_norm.weight"] = rng.uniform(0.8, 1.2, h).astype(np.float32)
+            t[pre + "attn_qkv.weight"] = random_q4_0(rng, self.qkv_rows, h)
+            t[pre + "attn_output.weight"] = random_q4_0(rng, h, h)
+            t[pre + "ffn_norm.weight"] = rng.uniform(0.8, 1.2, h).astype(np.float32)
+            t[pre + "ffn_gate_up.weight"] = random_q4_0(rng, 2 * ffn_inner, h)
+            t[pre + "ffn_down.weight"] = random_q4_0(rng, h, ffn_inner)
+        t["output_norm.weight"] = rng.uniform(0.8, 1.2, h).astype(np.float32)
+        t["output.weight"] = random_q6_k(rng, vocab_size, h) if lm_head_quant == "q6_k" else random_q4_0(rng, vocab_size, h)
+        self.host = t
+        self.device = {}
+
+    def weight_bytes(self) -> int:
+        return int(sum(a.nbytes for a in self.host.values()))
+
+    def to_device(self, device="cuda"):
+        import torch
+        self.device = {k: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k, v in self.host.items()}
+        return self

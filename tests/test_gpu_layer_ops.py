@@ -1,0 +1,208 @@
+"""The walker step's ops around attention on the GPU against the CPU oracle (oracle/layer_oracle.c, itself
+pinned bit for bit on the reference's CPU code by tests/test_layer_oracle.py).
+
+What is compared, and how closely:
+  add                       bit for bit.
+  gate / up copies          bit for bit.
+  RMSNorm                   the GPU sums the squares in another order: rtol 1e-5, atol 1e-6 (fp32).
+  SiLU(gate) * up           CUDA's expf against libm's (both within 2 ulp): rtol 1e-5, atol 1e-6.
+  Q4_0 / Q6_K mat-vec       the kernel keeps the block integers exact and sums in fp32, and rounds the
+                            activations to fp16. With activations that are fp16 numbers already only the
+                            order of the fp32 sum differs:   |err| <= 2e-5 * sum_c |W[r,c] x[n,c]|.
+                            With general fp32 activations each term is off by at most 2^-11 relative:
+                            |err| <= (2^-11 + 2e-5) * sum_c |W[r,c] x[n,c]|,
+                            and the error is unbiased: its rms stays below 2.5e-4 of the output's rms.
+"""
+import zlib
+
+import numpy as np
+import pytest
+
+from mlcompiler_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return t.cuda()
+
+
+def _run(executor, fn):
+    import torch
+    assert executor.beginForwardPassCB()
+    ok = fn()
+    assert ok, executor.last_error()
+    assert executor.flushForwardPassCB(), executor.last_error()
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("batch,length", [(32, 2048), (1, 2050), (5, 64), (3, 4099), (64, 5632)])
+def test_rms_norm_batched(executor, oracle_mod, batch, length):
+    import torch
+    rng = np.random.default_rng(batch * 7919 + length)
+    x = (rng.standard_normal((batch, length)) * rng.uniform(0.1, 8.0, (batch, 1))).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, length).astype(np.float32)
+    want = oracle_mod.rms_norm_batched(x, w, 1e-5)
+    dx, dw = _dev(x), _dev(w)
+    out = torch.full((batch, length), float("nan"), device="cuda")
+    out16 = torch.full((batch, length), float("nan"), device="cuda", dtype=torch.float16)
+    _run(executor, lambda: executor.encodeRmsNormBatched(dx, dw, 1e-5, batch, length, out, out16))
+    got = out.cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+    assert torch.equal(out16, out.half()), "the fp16 copy is not the rounded fp32 row"
+    out2 = torch.full((batch, length), float("nan"), device="cuda")
+    _run(executor, lambda: executor.encodeRmsNormBatched(dx, dw, 1e-5, batch, length, out2))
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("n", [32 * 2048, 1027, 3, 4])
+def test_add_batched_bit_exact(executor, oracle_mod, n):
+    import torch
+    rng = np.random.default_rng(n)
+    a = rng.standard_normal(n).astype(np.float32)
+    b = (rng.standard_normal(n) * 100).astype(np.float32)
+    out = torch.full((n,), float("nan"), device="cuda")
+    da, db = _dev(a), _dev(b)
+    _run(executor, lambda: executor.encodeAddBatched(da, db, out, n))
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), oracle_mod.add(a, b).view(np.uint32))
+
+
+@pytest.mark.parametrize("batch,inner,rows", [(32, 5632, 11264), (3, 100, 260), (1, 7, 14)])
+def test_gate_up_split_silu_mul(executor, oracle_mod, batch, inner, rows):
+    import torch
+    rng = np.random.default_rng(batch + inner)
+    gu = (rng.standard_normal((batch, rows)) * 3).astype(np.float32)
+    gu[0, :4] = [0.0, -0.0, 60.0, -60.0][:min(4, rows)]
+    g_want, u_want, want = oracle_mod.gate_up_split_silu_mul(gu, inner)
+    dgu = _dev(gu)
+    gate, up, out = (torch.full((batch, inner), float("nan"), device="cuda") for _ in range(3))
+    _run(executor, lambda: executor.encodeGateUpSplitSiluMul(dgu, gate, up, out, batch, inner, rows))
+    assert np.array_equal(gate.cpu().numpy().view(np.uint32), g_want.view(np.uint32))
+    assert np.array_equal(up.cpu().numpy().view(np.uint32), u_want.view(np.uint32))
+    np.testing.assert_allclose(out.cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+    # without the copies, and as the two-buffer op
+    out2 = torch.full((batch, inner), float("nan"), device="cuda")
+    _run(executor, lambda: executor.encodeGateUpSplitSiluMul(dgu, None, None, out2, batch, inner, rows))
+    assert torch.equal(out, out2)
+    out3 = torch.full((batch, inner), float("nan"), device="cuda")
+    _run(executor, lambda: executor.encodeSiluMulBatched(gate, up, out3, batch * inner))
+    assert torch.equal(out, out3)
+
+
+def _weights(kind, rng, rows, cols, pad_to=16):
+    raw = synth.random_q4_0(rng, rows, cols) if kind == "q4_0" else synth.random_q6_k(rng, rows, cols)
+    row_bytes = raw.shape[1]
+    stride = (row_bytes + pad_to - 1) // pad_to * pad_to
+    w = np.zeros((rows, stride), np.uint8)
+    w[:, :row_bytes] = raw
+    if stride > row_bytes:
+        w[:, row_bytes:] = 0xA5          # bytes between rows must not matter
+    return w, stride
+
+
+def _oracle_matvec(oracle_mod, kind, w, x, rows, cols):
+    want = oracle_mod.matmul_quant_batched(kind, w, x, rows, cols)
+    dense = oracle_mod.dequant_rows(kind, w, rows, cols)
+    absdot = np.abs(x).astype(np.float64) @ np.abs(dense).astype(np.float64).T
+    return want, absdot
+
+
+def _encode(executor, kind, dw, dx, batch, rows, cols, stride, out):
+    if kind == "q4_0":
+        return executor.encodeMatMulQ4_0Batched(dw, dx, batch, rows, cols, stride, out)
+    return executor.encodeMatMulQ6KBatched(dw, dx, batch, rows, cols, stride, out)
+
+
+MATVEC = [
+    # kind, batch, rows, cols
+    ("q4_0", 32, 2560, 2048),       # fused QKV of the 1.1B model
+    ("q4_0", 32, 2048, 5632),       # ffn_down: 11 column slices
+    ("q4_0", 1, 256, 2048),
+    ("q4_0", 7, 100, 64),           # rows short of a tile, 36-byte rows padded to 48
+    ("q4_0", 64, 300, 1024),
+    ("q4_0", 33, 129, 416),         # ragged everywhere: 13 blocks, one row into a second tile
+    ("q4_0", 16, 11264, 2048),      # gate | up
+    ("q6_k", 32, 4000, 2048),       # a slice of the lm_head
+    ("q6_k", 3, 130, 256),
+    ("q6_k", 64, 512, 512),
+    ("q6_k", 9, 200, 1280),         # 5 super-blocks: slices of 2 + 2 + 1
+]
+
+
+@pytest.mark.parametrize("kind,batch,rows,cols", MATVEC, ids=[f"{c[0]}-{c[1]}x{c[2]}x{c[3]}" for c in MATVEC])
+def test_quant_matvec(executor, oracle_mod, kind, batch, rows, cols):
+    import torch
+    rng = np.random.default_rng(zlib.crc32(f"{kind}-{batch}-{rows}-{cols}".encode()))
+    w, stride = _weights(kind, rng, rows, cols)
+    dw = _dev(w)
+    for form in ("fp16_numbers", "fp32"):
+        x = rng.standard_normal((batch, cols)).astype(np.float32) * 2.0
+        if form == "fp16_numbers":
+            x = x.astype(np.float16).astype(np.float32)
+        want, absdot = _oracle_matvec(oracle_mod, kind, w, x, rows, cols)
+        dx = _dev(x)
+        out = torch.full((batch, rows), float("nan"), device="cuda")
+        _run(executor, lambda: _encode(executor, kind, dw, dx, batch, rows, cols, stride, out))
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        err = np.abs(got.astype(np.float64) - want)
+        rel = 2e-5 if form == "fp16_numbers" else 2.0 ** -11 + 2e-5
+        worst = (err - rel * absdot).max()
+        assert worst <= 1e-7, f"{form}: error {err.max():.3e} exceeds {rel:.1e} * sum |w x| by {worst:.3e}"
+        if form == "fp32":
+            assert np.sqrt((err ** 2).mean()) <= 2.5e-4 * np.sqrt((want.astype(np.float64) ** 2).mean())
+        out2 = torch.full((batch, rows), float("nan"), device="cuda")
+        _run(executor, lambda: _encode(executor, kind, dw, dx, batch, rows, cols, stride, out2))
+        assert torch.equal(out, out2), "two runs of the mat-vec differ"
+
+
+@pytest.mark.parametrize("batch,inner,hidden", [(32, 5632, 2048), (5, 256, 200)])
+def test_matvec_with_silu_mul_input_and_residual(executor, oracle_mod, batch, inner, hidden):
+    """ffn_down fused with its neighbours: input = SiLU(gate) * up from the gate | up rows, output = residual +
+    W input - against the oracle's three separate ops."""
+    import torch
+    rng = np.random.default_rng(inner)
+    w, stride = _weights("q4_0", rng, hidden, inner)
+    gu = (rng.standard_normal((batch, 2 * inner + 8)) * 2).astype(np.float32)
+    resid = rng.standard_normal((batch, hidden)).astype(np.float32)
+    _, _, mix = oracle_mod.gate_up_split_silu_mul(gu, inner)
+    down, absdot = _oracle_matvec(oracle_mod, "q4_0", w, mix, hidden, inner)
+    want = oracle_mod.add(resid, down)
+    dw, dgu, dres = _dev(w), _dev(gu), _dev(resid)
+    out = torch.full((batch, hidden), float("nan"), device="cuda")
+    _run(executor, lambda: executor.encodeMatMulQuantFused(0, dw, dgu, gu.shape[1], True, dres, batch, hidden, inner,
+                                                           stride, out))
+    err = np.abs(out.cpu().numpy().astype(np.float64) - want)
+    bound = (2.0 ** -11 + 4e-5) * absdot + 1e-6 * (1 + np.abs(want))
+    assert (err <= bound).all(), f"max error {err.max():.3e}"
+    # the residual alone (the output projection's form), plain input
+    x = rng.standard_normal((batch, inner)).astype(np.float32)
+    down, absdot = _oracle_matvec(oracle_mod, "q4_0", w, x, hidden, inner)
+    want = oracle_mod.add(resid, down)
+    dx = _dev(x)
+    _run(executor, lambda: executor.encodeMatMulQuantFused(0, dw, dx, inner, False, dres, batch, hidden, inner, stride, out))
+    err = np.abs(out.cpu().numpy().astype(np.float64) - want)
+    assert (err <= (2.0 ** -11 + 2e-5) * absdot + 1e-6 * (1 + np.abs(want))).all()
+
+
+def test_layer_ops_argument_rules(executor):
+    import torch
+    x = torch.zeros((2, 64), device="cuda")
+    w = torch.zeros((64,), device="cuda")
+    out = torch.zeros((2, 64), device="cuda")
+    wq = torch.zeros((128, 48), device="cuda", dtype=torch.uint8)
+    # no open pass: every encode* refuses, like the reference's (metal_runtime.mm:7935)
+    assert not executor.encodeRmsNormBatched(x, w, 1e-5, 2, 64, out)
+    assert "open pass" in executor.last_error()
+    assert not executor.encodeAddBatched(x, x, out, 128)
+    assert not executor.encodeMatMulQ4_0Batched(wq, x, 2, 128, 64, 48, out)
+    assert executor.beginForwardPassCB()
+    assert not executor.encodeMatMulQ4_0Batched(wq, x, 2, 128, 48, 48, out)       # 1.5 blocks per row
+    assert not executor.encodeMatMulQ4_0Batched(wq, x, 2, 128, 64, 32, out)       # stride shorter than a row
+    assert not executor.encodeMatMulQ4_0Batched(wq, x, 65, 128, 64, 48, out)      # batch above the limit
+    assert not executor.encodeMatMulQ6KBatched(wq, x, 2, 128, 64, 48, out)        # not a whole super-block
+    assert not executor.encodeGateUpSplitSiluMul(x, None, None, out, 2, 40, 64)   # row shorter than gate + up
+    assert executor.encodeAddBatched(x, x, out, 0)                                # nothing to do is not an error
+    assert executor.flushForwardPassCB(), executor.last_error()
