@@ -5,6 +5,7 @@ too, under its `secondary` key).
     python bench_more.py --workload cfg3 [--steps K]          # long-context split-KV
     python bench_more.py --workload cfg4 [--steps K]          # wide GQA, requests sharded by KV bytes
     python bench_more.py --workload cfg5 [--steps K]          # chunked prefill on tcgen05
+    python bench_more.py --workload model [--steps K]         # whole decode step of a 1.1B-shaped model
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         bench_more.py --workload cfg3|cfg4|cfg5
 
@@ -18,6 +19,13 @@ longest-first packing on KV bytes; no collective.
 cfg5: 8 requests, each a 512-token chunk on top of 1536 cached tokens, H32/KVH8/D128, causal; requests
 are dealt round-robin to ranks, no collective. Metric: attention TFLOP/s (4*D flops per visible
 (query, key) pair), against the measured dense bf16 tensor peak.
+model: the whole walker step (compiler/runtime/batched_walker.cpp:183-458) of a model with TinyLlama-1.1B's
+shape - 22 layers, hidden 2048, H32/KVH4/D64, FFN 5632, vocabulary 32000, Q4_0 weights, Q6_K lm_head - for
+32 requests with contexts U[512, 2048], through the paged executor's run_decode: page extension, plan update,
+token upload, every launch of the pass, logits [32, 32000] back on the host. Weights are seeded synthetic
+bytes in the real formats (there is no checkpoint to load here), the contexts' K/V rows random. Metric:
+generated tokens per second, wall clock around run_decode (the call returns when the logits are on the
+host). With N ranks every rank serves its own 32 requests on its own copy of the weights.
 Prints one JSON line (rank 0). Pools rotate so that consecutive steps never re-read L2-resident data.
 """
 from __future__ import annotations
@@ -362,14 +370,91 @@ def run_cfg4(env, steps=200, warmup=10):
         "gpu_launches": int(launches)}
 
 
+class _RawHalf:
+    """A device buffer of this library as something torch.as_tensor can wrap."""
+
+    def __init__(self, ptr, n_halves):
+        self.__cuda_array_interface__ = {"shape": (n_halves,), "typestr": "<f2", "data": (int(ptr), False), "version": 3}
+
+
+def run_model(env, steps=40, warmup=5, batch=32, reference_order=False):
+    import time
+    import torch
+    from mlcompiler_b200 import synth
+    from mlcompiler_b200.host import PagePool, PagedAttentionExecutor, PagedKVStorage
+    ex, stream, dev, rank, world = env.ex, env.stream, env.dev, env.rank, env.world
+    P, L, H, KVH, D, inner, vocab = 64, 22, 32, 4, 64, 5632, 32000
+    model = synth.SyntheticModel(0x11B, L, H, KVH, D, inner, vocab, lm_head_quant="q6_k")
+    lens = synth.config_lengths(2)[:batch].astype(np.int64)
+    total_steps = steps + max(warmup, 3)
+    capacity = int(sum((int(l) + total_steps + P - 1) // P for l in lens)) + 4
+    pool = PagePool(capacity)
+    storage = PagedKVStorage(ex, capacity, L, P, KVH, D, 2)
+    assert storage.initialize()
+    pex = PagedAttentionExecutor(ex, H, KVH, D, L, 0)
+    pex.attach_page_pool(pool, P)
+    pex.attach_paged_storage(storage)
+    pex.set_call_order(reference_order)
+    with torch.cuda.stream(stream):
+        model.to_device(dev)
+        n_halves = capacity * P * KVH * D
+        for l in range(L):
+            for ptr in (storage.k_buffer(l), storage.v_buffer(l)):
+                torch.as_tensor(_RawHalf(ptr, n_halves), device=dev).normal_()
+    stream.synchronize()
+    assert pex.attach_model(model)
+    for r in range(batch):
+        assert pex.assume_context(r, int(lens[r]) - 1)
+    pos = [int(l) - 1 for l in lens]
+    rng = np.random.default_rng(rank)
+
+    def step():
+        slots = [(r, int(rng.integers(0, vocab)), pos[r]) for r in range(batch)]
+        out = pex.run_decode(slots)
+        assert len(out) == batch and all(o[1] for o in out), ex.last_error()
+        for r in range(batch):
+            pos[r] += 1
+        return out
+
+    for _ in range(max(warmup, 3)):
+        out = step()
+    assert all(np.isfinite(o[2]).all() for o in out)
+    env.barrier()
+    l0 = ex.launchCount()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    launches = ex.launchCount() - l0
+    sec = env.reduce(float(np.mean(times)), "max")
+    kv_bytes = float(sum(pos)) * 2 * KVH * D * 2 * L
+    pex.destroy()
+    storage.destroy()
+    return {
+        "metric": "decode_tokens_per_s", "value": world * batch / sec, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": max(warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "dtype": "Q4_0 / Q6_K weights, f16 KV, f32 activations", "data": "synthetic",
+        "config": {"workload": "model: 1.1B-shaped decoder (22 layers, hidden 2048, H32/KVH4/D64, FFN 5632, vocabulary "
+                               "32000), 32 requests, contexts U[512,2048], whole walker step through run_decode",
+                   "call_order": "reference" if reference_order else "fused",
+                   "parallelism": f"replicas x{world}, {batch} requests each", "timed": "wall clock around run_decode, "
+                   "logits on the host when it returns"},
+        "ms_per_step_median_min_max": [float(np.median(times)) * 1e3, float(np.min(times)) * 1e3, float(np.max(times)) * 1e3],
+        "bytes_per_step": {"weights": model.weight_bytes() - model.host["token_embd.weight"].nbytes, "kv": kv_bytes},
+        "gpu_launches": int(launches), "launches_per_step": launches / steps}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=["cfg3", "cfg4", "cfg5"], required=True)
+    ap.add_argument("--workload", choices=["cfg3", "cfg4", "cfg5", "model"], required=True)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--exchange", choices=["fused", "peer", "nccl"], default="fused",
                     help="cfg3 on several GPUs: exchange fused into the attention kernel (default), the separate "
                          "peer-memory exchange kernel, or NCCL all-gather + combine")
+    ap.add_argument("--reference-order", action="store_true",
+                    help="model: the reference walker's 13 launches per layer instead of the fused 8")
     ap.add_argument("--seq-len", type=int, default=None, help="cfg3: tokens per request instead of 32768")
     args = ap.parse_args()
 
@@ -390,6 +475,8 @@ def main():
         res = run_cfg5(env, args.steps, args.warmup)
     elif args.workload == "cfg3":
         res = run_cfg3(env, args.steps, args.warmup, args.exchange, seq_len=args.seq_len)
+    elif args.workload == "model":
+        res = run_model(env, min(args.steps, 100), args.warmup, reference_order=args.reference_order)
     else:
         res = run_cfg4(env, args.steps, args.warmup)
     if rank == 0:

@@ -420,8 +420,10 @@ int mlc_encode_gate_up_split_silu_mul(mlc_ctx* ctx, const void* gate_up, void* g
  * the block format of quantization.cpp:71-74 (Q4_0: fp16 scale + 16 bytes per 32 weights) or
  * :142-147 (Q6_K: 210 bytes per 256 weights); in [batch, cols], out [batch, rows] fp32.
  * Tensor-core kernel: block integers exact, activations rounded to fp16, fp32 sums and scales.
- * Limits (MLC_ERR_UNSUPPORTED): batch <= 64, cols a whole number of blocks, weights and
- * row_stride 16-byte aligned. */
+ * Limits (MLC_ERR_UNSUPPORTED): batch <= 64, cols a whole number of blocks. Rows are copied
+ * with 16-byte loads when weights and row_stride are 16-byte aligned (every real model's are:
+ * cols a multiple of 256), with 2-byte loads otherwise. out and residual must be 16-byte aligned
+ * when rows is a multiple of 4. */
 int mlc_encode_matmul_q4_0_batched(mlc_ctx* ctx, const void* weights, const void* in, size_t batch, size_t rows,
                                    size_t cols, size_t row_stride, void* out);
 int mlc_encode_matmul_q6k_batched(mlc_ctx* ctx, const void* weights, const void* in, size_t batch, size_t rows,
@@ -648,6 +650,12 @@ typedef struct mlc_model_desc {
     uint32_t n_layers;
 } mlc_model_desc;
 int mlc_executor_attach_model(mlc_executor* exec, const mlc_model_desc* model);
+/* No counterpart in the reference. Gives a request without pages a context of `tokens` tokens whose
+ * K/V rows the caller has put (or will put) into the storage itself: reserves its pages
+ * (RequestKVState::reserve) and sets its next position to `tokens`. For restoring a saved context and
+ * for benchmarks that start from long contexts. MLC_ERR_INVALID_ARG if the request already has pages
+ * or the pool cannot supply them. */
+int mlc_executor_assume_context(mlc_executor* exec, uint32_t request_id, size_t tokens);
 
 void mlc_executor_destroy(mlc_executor* exec);
 /* attach_page_pool / attach_paged_storage (batched_executor.hpp:73, 90); mlc_status. */

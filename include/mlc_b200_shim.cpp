@@ -10,11 +10,15 @@
 //   g++ -std=c++17 -I<MLcompiler> -I<MLcompiler>/compiler -I<this repo>/include -c mlc_b200_shim.cpp
 //   and link with mlcompiler_b200/libmlc_b200.so
 //
-// Members of MetalExecutor outside the paged-attention path (mat-vecs, norms, MPS attention ...)
+// Also defined: the other encode* ops of the walker's decode step (batched RMSNorm, Q4_0 / Q6_K batched
+// mat-vec, add, SiLU * up). Members outside that step (single-vector mat-vecs, MPS attention, layer norm ...)
 // are not defined here; a build that keeps using them links its own definitions of those.
 //
 // MLC_B200_SHIM_DEVICE (environment, default 0) selects the CUDA device of the singleton.
+#include <cstdint>
 #include <cstdlib>
+#include <string>
+#include <unordered_set>
 
 #include "runtime/metal_runtime.hpp"
 
@@ -155,6 +159,57 @@ bool MetalExecutor::encodeQkvSplitRopeCast(void* qkv_buf, void* q_buf, void* k_b
     return mlc_encode_qkv_split_rope_cast(impl_->ctx, qkv_buf, q_buf, k_buf, v_buf, k_f16_buf, v_f16_buf, cos_buf, sin_buf,
                                           batch, num_heads, kv_heads, head_dim, qkv_rows, q_rows, k_rows, v_rows,
                                           rotary_dim) == MLC_OK;
+}
+
+// ---- the walker step's other ops (metal_runtime.hpp:474-506, 549-552)
+// The reference keeps every weight it has seen in a device buffer keyed by the tensor's name and fills it
+// on first use; the same here, on the library's name-keyed buffer cache.
+static const void* cached_weight(mlc_ctx* ctx, const std::string& name, const void* host, size_t bytes) {
+    static std::unordered_set<std::string> uploaded;
+    void* dev = mlc_cached_buffer(ctx, name.c_str(), (bytes + 15) / 16 * 16);
+    if (dev && uploaded.insert(name).second && mlc_upload(ctx, dev, host, bytes, 0) != MLC_OK) {
+        uploaded.erase(name);
+        return nullptr;
+    }
+    return dev;
+}
+
+bool MetalExecutor::encodeRmsNormBatched(void* in_buf, const std::vector<float>& weight, float epsilon, size_t batch,
+                                         size_t length, void* out_buf) const {
+    if (!impl_->ctx || weight.size() < length) return false;
+    // norm weights carry no name in this call: key the cache on the host vector's address and length
+    const std::string key = "rms_w@" + std::to_string(reinterpret_cast<uintptr_t>(weight.data())) + ":" + std::to_string(length);
+    const void* w = cached_weight(impl_->ctx, key, weight.data(), length * sizeof(float));
+    return w && mlc_encode_rms_norm_batched(impl_->ctx, in_buf, w, epsilon, batch, length, out_buf, nullptr) == MLC_OK;
+}
+
+bool MetalExecutor::encodeMatMulQ4_0Batched(const std::string& weight_name, const std::vector<uint8_t>& weights, void* in_buf,
+                                            size_t batch, size_t rows, size_t cols, size_t row_stride,
+                                            uint32_t /*quant_version*/, void* out_buf) const {
+    if (!impl_->ctx || weights.size() < rows * row_stride) return false;
+    const void* w = cached_weight(impl_->ctx, weight_name, weights.data(), rows * row_stride);
+    return w && mlc_encode_matmul_q4_0_batched(impl_->ctx, w, in_buf, batch, rows, cols, row_stride, out_buf) == MLC_OK;
+}
+
+bool MetalExecutor::encodeMatMulQ6KBatched(const std::string& weight_name, const std::vector<uint8_t>& weights, void* in_buf,
+                                           size_t batch, size_t rows, size_t cols, size_t row_stride, void* out_buf) const {
+    if (!impl_->ctx || weights.size() < rows * row_stride) return false;
+    const void* w = cached_weight(impl_->ctx, weight_name, weights.data(), rows * row_stride);
+    return w && mlc_encode_matmul_q6k_batched(impl_->ctx, w, in_buf, batch, rows, cols, row_stride, out_buf) == MLC_OK;
+}
+
+bool MetalExecutor::encodeAddBatched(void* a_buf, void* b_buf, void* out_buf, size_t total_elements) const {
+    return impl_->ctx && mlc_encode_add_batched(impl_->ctx, a_buf, b_buf, out_buf, total_elements) == MLC_OK;
+}
+
+bool MetalExecutor::encodeSiluMulBatched(void* gate_buf, void* up_buf, void* out_buf, size_t total_elements) const {
+    return impl_->ctx && mlc_encode_silu_mul_batched(impl_->ctx, gate_buf, up_buf, out_buf, total_elements) == MLC_OK;
+}
+
+bool MetalExecutor::encodeGateUpSplitSiluMul(void* gate_up_buf, void* gate_buf, void* up_buf, void* out_buf, size_t batch,
+                                             size_t ffn_inner, size_t ffn_gate_up_rows) const {
+    return impl_->ctx && mlc_encode_gate_up_split_silu_mul(impl_->ctx, gate_up_buf, gate_buf, up_buf, out_buf, batch,
+                                                           ffn_inner, ffn_gate_up_rows) == MLC_OK;
 }
 
 }  // namespace runtime

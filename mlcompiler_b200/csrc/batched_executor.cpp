@@ -84,6 +84,20 @@ PagedAttentionExecutor::PerRequest& PagedAttentionExecutor::ensure_request(uint3
     return requests_[request_id];
 }
 
+bool PagedAttentionExecutor::assume_context(uint32_t request_id, size_t tokens) {
+    if (!pool_ || tokens == 0) return false;
+    PerRequest& req = ensure_request(request_id);
+    if (req.page_state && req.page_state->total_tokens() > 0) return false;
+    if (!req.page_state) {
+        req.page_state.reset(new RequestKVState());
+        req.page_state->request_id = request_id;
+        req.page_state->page_size_tokens = page_size_tokens_;
+    }
+    if (!req.page_state->reserve(*pool_, tokens)) return false;
+    req.next_position = tokens;
+    return true;
+}
+
 void PagedAttentionExecutor::release_request(uint32_t request_id) {
     auto it = requests_.find(request_id);
     if (it == requests_.end()) return;

@@ -117,6 +117,11 @@ public:
     // (batched_executor.cpp:450-467). Returns false if the description does not fit the executor.
     bool attach_model(const ModelWeights& model);
     bool has_model() const { return model_ != nullptr; }
+    // Gives a request that has no pages yet a context of `tokens` tokens whose K/V rows the caller has put
+    // (or will put) into the pools itself: pages are reserved and the next position is `tokens`. For
+    // restoring a saved context and for benchmarks that start from long contexts. False if the request
+    // already has pages or the pool cannot supply them.
+    bool assume_context(uint32_t request_id, size_t tokens);
     const RequestKVState* page_state(uint32_t request_id) const;
 
     BatchedDecodeOutput run_decode(const std::vector<RequestSlot>& slots) override;

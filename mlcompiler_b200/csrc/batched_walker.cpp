@@ -6,11 +6,16 @@
 #include <cstring>
 
 #include <cuda_fp16.h>
+#include <cuda_runtime.h>
 
 #include "ctx.hpp"
 
 namespace mlcb {
 namespace runtime {
+
+BatchedWalker::~BatchedWalker() {
+    if (logits_pinned_) cudaFreeHost(logits_pinned_);
+}
 
 BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
     BatchedDecodeOutput out;
@@ -87,15 +92,24 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
         ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
         if (!ok || !logits_dev) return fail_all();
         const size_t vocab = ex.model_->vocab_size;
-        o_host_.resize(N * vocab);
-        if (mlc_download(ctx, logits_dev, o_host_.data(), o_host_.size() * sizeof(float), 0) != MLC_OK) return fail_all();
+        if (logits_pinned_floats_ < N * vocab) {   // pageable memory would make this copy several times slower
+            if (logits_pinned_) cudaFreeHost(logits_pinned_);
+            logits_pinned_ = nullptr;
+            logits_pinned_floats_ = 0;
+            DeviceGuard guard(ctx->device);
+            if (cudaHostAlloc(reinterpret_cast<void**>(&logits_pinned_), N * vocab * sizeof(float), cudaHostAllocDefault) !=
+                cudaSuccess)
+                return fail_all();
+            logits_pinned_floats_ = N * vocab;
+            ++ctx->allocations;
+        }
+        if (mlc_download(ctx, logits_dev, logits_pinned_, N * vocab * sizeof(float), 0) != MLC_OK) return fail_all();
         out.per_request.reserve(N);
         for (size_t r = 0; r < N; ++r) {
             BatchedDecodeOutput::PerRequest p;
             p.request_id = slots[r].request_id;
             p.success = true;
-            p.logits.assign(o_host_.begin() + static_cast<std::ptrdiff_t>(r * vocab),
-                            o_host_.begin() + static_cast<std::ptrdiff_t>((r + 1) * vocab));
+            p.logits.assign(logits_pinned_ + r * vocab, logits_pinned_ + (r + 1) * vocab);
             reqs[r]->next_position = slots[r].sequence_position + 1;
             out.per_request.push_back(std::move(p));
         }

@@ -13,6 +13,7 @@ namespace runtime {
 class BatchedWalker {
 public:
     explicit BatchedWalker(PagedAttentionExecutor& exec) : exec_(exec) {}
+    ~BatchedWalker();
     BatchedDecodeOutput step(const std::vector<RequestSlot>& slots);
     // All tokens of a prompt chunk in one pass per layer: the chunk's K/V rows are scattered,
     // then chunked causal attention runs over the request's pages. Returns the last token's
@@ -30,6 +31,8 @@ private:
     PagedAttentionExecutor& exec_;
     std::vector<float> cos_host_, sin_host_;
     std::vector<uint32_t> tok_host_;
+    float* logits_pinned_ = nullptr;   // page-locked landing area of the logits download, grown on demand
+    size_t logits_pinned_floats_ = 0;
     // host staging, reused across passes
     std::vector<float> q_host_;
     std::vector<uint16_t> k_host_, v_host_;

@@ -192,6 +192,10 @@ int mlc_executor_attach_model(mlc_executor* e, const mlc_model_desc* d) {
     }
     return e->paged->attach_model(m) ? MLC_OK : MLC_ERR_INVALID_ARG;
 }
+int mlc_executor_assume_context(mlc_executor* e, uint32_t request_id, size_t tokens) {
+    if (!e || !e->paged) return MLC_ERR_INVALID_ARG;
+    return e->paged->assume_context(request_id, tokens) ? MLC_OK : MLC_ERR_INVALID_ARG;
+}
 int mlc_executor_set_call_order(mlc_executor* e, int reference_order) {
     if (!e || !e->paged) return MLC_ERR_INVALID_ARG;
     e->paged->set_call_order(reference_order ? PagedAttentionExecutor::CallOrder::Reference

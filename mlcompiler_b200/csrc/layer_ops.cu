@@ -8,22 +8,68 @@
 //
 // The mat-vec is a [rows x cols] x [cols x batch] product with batch <= 64: weight rows are the M side of
 // mma.sync.m16n8k16, the batch the N side. A block's integers go into the A fragment as exact fp16
-// values (nibble - 8, or 6-bit value - 32), the activations into B rounded to fp16, products accumulate
-// in fp32 inside the MMA and each 16- or 32-weight group's sum is multiplied by its fp32 scale
-// afterwards - so the only rounding beyond the CPU's is that of the activations to fp16.
-// A CTA owns 128 weight rows and one slice of the columns; slices of a row tile leave their partial
-// sums in a scratch buffer and the last CTA to finish a row tile adds them in slice order (a counter per
-// row tile; the order is fixed, so results repeat bit for bit), with the residual add fused there when
-// the caller asks for it. Weight bytes are read once from HBM; the activations (L2-resident) are read
-// once per row tile.
+// values (nibble - 8, or 6-bit value - 32), each activation into B as two fp16 numbers (hi = fp16(x),
+// lo = fp16(x - hi): 22 bits of x) against the same weight in two MMAs, products accumulate in fp32 inside
+// the MMA and each 16- or 32-weight
+// group's sum is multiplied by its fp32 scale afterwards - so results differ from the CPU's fp32 loop by
+// the order of the sums, not by the precision of the operands.
+// A CTA owns 64 weight rows and one slice of the columns (8 warps: 4 m-tiles x 2 halves of every chunk); the slices of a row tile are the CTAs of one
+// thread-block cluster, which add their partial tiles through distributed shared memory in slice order
+// (fixed, so results repeat bit for bit), with the residual add fused there when the caller asks for it.
+// Weight bytes are read once from HBM; the activations (L2-resident) are read once per row tile.
 #include <cuda_fp16.h>
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 
 #include "ctx.hpp"
 
 namespace mlcb {
+
+// Every kernel of this file is launched as a programmatic dependent of the kernel before it on the stream
+// (MLC_B200_LAYER_PDL=0 in the environment turns that off): its CTAs may start while that kernel drains, and
+// wait (griddepcontrol.wait) before they touch anything a kernel writes. What runs before the wait reads only
+// weights, which no kernel writes.
+static bool layer_pdl() {
+    static const bool on = [] {
+        const char* e = std::getenv("MLC_B200_LAYER_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_layer_kernel(mlc_ctx* ctx, void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                                       unsigned cluster, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (layer_pdl()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+__device__ __forceinline__ void dependent_launch_gate() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 // ---------------------------------------------------------------------------------------------------
 // RMSNorm, add, SiLU * up
@@ -36,6 +82,7 @@ __global__ void __launch_bounds__(256) rms_norm_batched_kernel(const float* __re
                                                                float eps, uint32_t length, float* __restrict__ out,
                                                                __half* __restrict__ out16) {
     __shared__ float part[8];
+    dependent_launch_gate();
     const float* x = in + static_cast<size_t>(blockIdx.x) * length;
     float* y = out + static_cast<size_t>(blockIdx.x) * length;
     float s = 0.0f;
@@ -83,6 +130,7 @@ __global__ void __launch_bounds__(256) rms_norm_batched_kernel(const float* __re
 
 __global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                   float* __restrict__ out, size_t n4, size_t n) {
+    dependent_launch_gate();
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n4) {
         const float4 x = reinterpret_cast<const float4*>(a)[i], y = reinterpret_cast<const float4*>(b)[i];
@@ -101,6 +149,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 __global__ void __launch_bounds__(256) gate_up_silu_mul_kernel(const float* __restrict__ gate_up, float* __restrict__ gate,
                                                                float* __restrict__ up, float* __restrict__ out,
                                                                uint32_t batch, uint32_t inner, uint32_t rows) {
+    dependent_launch_gate();
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= static_cast<size_t>(batch) * inner) return;
     const uint32_t r = static_cast<uint32_t>(i / inner), c = static_cast<uint32_t>(i - static_cast<size_t>(r) * inner);
@@ -113,6 +162,7 @@ __global__ void __launch_bounds__(256) gate_up_silu_mul_kernel(const float* __re
 
 __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                                        float* __restrict__ out, size_t n) {
+    dependent_launch_gate();
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) out[i] = silu_mul(gate[i], up[i]);
 }
@@ -128,6 +178,7 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t bits) {
 __global__ void __launch_bounds__(256) embedding_q4_0_kernel(const uint8_t* __restrict__ table, size_t row_stride,
                                                              const uint32_t* __restrict__ tokens, uint32_t vocab,
                                                              uint32_t cols, float* __restrict__ out, uint32_t* err) {
+    dependent_launch_gate();
     const uint32_t tok = tokens[blockIdx.x];
     float* y = out + static_cast<size_t>(blockIdx.x) * cols;
     if (tok >= vocab) {
@@ -150,10 +201,11 @@ __global__ void __launch_bounds__(256) embedding_q4_0_kernel(const uint8_t* __re
 // Quantised batched mat-vec
 // ---------------------------------------------------------------------------------------------------
 
-constexpr int kMvRows = 128;        // weight rows per CTA (4 warps x 2 m-tiles of 16)
-constexpr int kMvThreads = 128;
-constexpr int kMvSliceMax = 512;    // columns per CTA slice at most (a multiple of both block sizes)
-constexpr int kXPad = 8;            // halves of padding per activation row in shared memory
+constexpr int kMvRows = 64;         // weight rows per CTA: 4 m-tiles of 16, each worked on by two warps (half the columns each)
+constexpr int kMvThreads = 256;
+constexpr int kMvChunk = 256;       // columns staged in shared memory at a time (a multiple of both block sizes)
+constexpr int kXPadWords = 4;       // words of padding per activation row in shared memory: rows land 4 banks apart
+constexpr int kMvStages = 2;        // chunks in flight per CTA
 
 enum : int { kQ4_0 = 0, kQ6_K = 1 };
 enum : int { kInPlain = 0, kInSiluMul = 1 };
@@ -161,13 +213,9 @@ enum : int { kInPlain = 0, kInSiluMul = 1 };
 template <int QT> struct QuantFormat;
 template <> struct QuantFormat<kQ4_0> {
     static constexpr int kBlockBytes = 18, kBlockWeights = 32;
-    static constexpr int kSliceBytesMax = kMvSliceMax / 32 * 18;          // 288
-    static constexpr int kPitch = 304;                                     // 76 words: rows g land 12 banks apart
 };
 template <> struct QuantFormat<kQ6_K> {
     static constexpr int kBlockBytes = 210, kBlockWeights = 256;
-    static constexpr int kSliceBytesMax = kMvSliceMax / 256 * 210;        // 420
-    static constexpr int kPitch = 464;                                     // 116 words: rows g land 20 banks apart
 };
 
 struct MatVecParams {
@@ -175,12 +223,13 @@ struct MatVecParams {
     const float* x;          // [batch, x_stride] fp32; with kInSiluMul gate at column c, up at column c + cols
     const float* residual;   // [batch, rows] added in the epilogue, or null
     float* out;              // [batch, rows]
-    float* partial;          // [slices, batch, rows] when slices > 1
-    uint32_t* counters;      // [row tiles], zero between launches
     size_t row_stride;
     uint32_t batch, rows, cols, x_stride;
     uint32_t slice_cols;     // columns per slice (a multiple of the block size)
-    uint32_t slices;
+    uint32_t chunk_cols;     // columns staged in shared memory at a time
+    uint32_t w_pitch;        // bytes between weight rows in shared memory
+    uint32_t slices;         // CTAs per cluster
+    uint32_t aligned16;      // weights and row_stride on 16-byte boundaries: vector copies
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -189,234 +238,331 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Two integers 0..63 in the low bytes of the two halves of `v` -> half2 of (value - bias), exact:
-// 0x6400 | n is the fp16 number 1024 + n.
-__device__ __forceinline__ uint32_t ints_to_half2(uint32_t v, uint32_t bias_bits) {
-    const uint32_t h = v | 0x64006400u;
-    __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), *reinterpret_cast<const __half2*>(&bias_bits));
-    return *reinterpret_cast<uint32_t*>(&r);
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// A fragments of one Q4_0 block (two 16-weight groups: low nibbles, high nibbles) for rows g and g + 8 of
-// an m-tile. `row` points at the block in shared memory (2-byte aligned), t = lane & 3.
-__device__ __forceinline__ void q4_0_fragments(const uint8_t* blk_g, const uint8_t* blk_g8, int t, uint32_t (&lo)[4],
-                                               uint32_t (&hi)[4], float& d_g, float& d_g8) {
-    const uint16_t* pg = reinterpret_cast<const uint16_t*>(blk_g);
-    const uint16_t* p8 = reinterpret_cast<const uint16_t*>(blk_g8);
-    d_g = half_bits_to_float(pg[0]);
-    d_g8 = half_bits_to_float(p8[0]);
-    // weights 2t, 2t+1 are bytes 2t, 2t+1 of the 16 (u16 index 1 + t); weights 2t+8, 2t+9 are u16 index 5 + t
-    const uint32_t v[4] = {pg[1 + t], p8[1 + t], pg[5 + t], p8[5 + t]};
-    constexpr uint32_t kBias = 0x64086408u;   // 1032 = 1024 + 8
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t l = (v[i] & 0x000Fu) | ((v[i] & 0x0F00u) << 8);
-        const uint32_t h = ((v[i] >> 4) & 0x000Fu) | ((v[i] & 0xF000u) << 4);
-        lo[i] = ints_to_half2(l, kBias);
-        hi[i] = ints_to_half2(h, kBias);
-    }
+// 16 bytes at `local_smem_addr` of CTA `rank` of this cluster.
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_smem_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
 }
 
-// A fragment of 16-weight group j (0..15) of a Q6_K super-block for rows g and g + 8, and the groups' scales
-// d * sc[j]. Weight l of a 128-weight half lives in ql / qh as quantization.cpp:1469-1499 lays out.
-__device__ __forceinline__ void q6_k_fragment(const uint8_t* blk_g, const uint8_t* blk_g8, int j, int t, uint32_t (&a)[4],
-                                              float& s_g, float& s_g8) {
-    const int h = j >> 3, quarter = (j & 7) >> 1, sub = j & 1;
-    const int ql_off = 64 * h + ((quarter & 1) ? 32 : 0) + 16 * sub;   // q2 / q4 read ql[l + 32]
-    const int qh_off = 128 + 32 * h + 16 * sub;
-    const int nib_shift = (quarter >> 1) * 4;                           // q3 / q4 take the high nibble
-    const int hi_shift = quarter * 2;
-    constexpr uint32_t kBias = 0x64206420u;   // 1056 = 1024 + 32
-    const uint8_t* rowp[2] = {blk_g, blk_g8};
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int l = 2 * t + 8 * k;
-            const uint32_t ql = *reinterpret_cast<const uint16_t*>(rowp[r] + ql_off + l);
-            const uint32_t qh = *reinterpret_cast<const uint16_t*>(rowp[r] + qh_off + l);
-            const uint32_t n0 = ((ql >> nib_shift) & 0xFu) | ((((qh) >> hi_shift) & 3u) << 4);
-            const uint32_t n1 = ((ql >> (8 + nib_shift)) & 0xFu) | ((((qh >> 8) >> hi_shift) & 3u) << 4);
-            a[r + 2 * k] = ints_to_half2(n0 | (n1 << 16), kBias);
-        }
-    }
-    const float dg = half_bits_to_float(*reinterpret_cast<const uint16_t*>(blk_g + 208));
-    const float d8 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(blk_g8 + 208));
-    s_g = __fmul_rn(dg, static_cast<float>(static_cast<int8_t>(blk_g[192 + j])));
-    s_g8 = __fmul_rn(d8, static_cast<float>(static_cast<int8_t>(blk_g8[192 + j])));
-}
+constexpr int kRedPitch = 68;    // floats per batch row of a partial tile (64 rows + 4): lanes t land 8 banks apart
 
+// Shared memory of one pipeline stage: the chunk's activations as fp32 words [kXRows][chunk + 4] (turned in
+// place into {hi, lo} fp16 pairs), with SiLU input a second such array for the `up` half, then the chunk's
+// weight bytes [128][w_pitch].
 template <int QT, int NT, int IN>
 __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecParams p) {
     using F = QuantFormat<QT>;
     constexpr int kXRows = NT * 8;
+    constexpr int kXArrays = IN == kInSiluMul ? 2 : 1;
     extern __shared__ __align__(16) uint8_t smem[];
-    __half* xs = reinterpret_cast<__half*>(smem);                                    // [kXRows][slice + pad]
-    const uint32_t x_pitch = p.slice_cols + kXPad;
-    uint8_t* ws = smem + static_cast<size_t>(kXRows) * x_pitch * sizeof(__half);     // [kMvRows][F::kPitch]
-    __shared__ uint32_t ticket;
+    const uint32_t x_pitch = p.chunk_cols + kXPadWords;                  // words
+    const uint32_t x_bytes = kXRows * x_pitch * 4;
+    const uint32_t stage_bytes = kXArrays * x_bytes + kMvRows * p.w_pitch;
 
-    const uint32_t tile = blockIdx.x, slice = blockIdx.y;
+    // The CTAs of a cluster share a row tile and split its columns: blockIdx.x = tile * slices + slice, and the
+    // slice is the CTA's rank in the cluster.
+    const uint32_t S = p.slices;
+    const uint32_t tile = blockIdx.x / S, slice = blockIdx.x - tile * S;
     const uint32_t row0 = tile * kMvRows;
-    const uint32_t c0 = slice * p.slice_cols;
-    const uint32_t ncols = min(p.slice_cols, p.cols - c0);
+    const uint32_t c_begin = min(slice * p.slice_cols, p.cols), c_end = min(c_begin + p.slice_cols, p.cols);
+    const uint32_t n_chunks = (c_end - c_begin + p.chunk_cols - 1) / p.chunk_cols;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int mt = warp & 3, kh = warp >> 2;   // the warp's m-tile and its half of every chunk's columns
 
-    // weight bytes of this slice: [b0, b1) of every row; copied as the enclosing 16-byte range
-    const uint32_t b0 = c0 / F::kBlockWeights * F::kBlockBytes;
-    const uint32_t b1 = b0 + ncols / F::kBlockWeights * F::kBlockBytes;
-    const uint32_t a0 = b0 & ~15u;
-    const uint32_t nvec = (b1 - a0 + 15) >> 4;
-    const uint32_t w_shift = b0 - a0;
-    for (uint32_t i = tid; i < kMvRows * nvec; i += kMvThreads) {
-        const uint32_t r = i / nvec, v = i - r * nvec;
-        const uint32_t row = min(row0 + r, p.rows - 1);
-        const uint4 d = __ldg(reinterpret_cast<const uint4*>(p.w + static_cast<size_t>(row) * p.row_stride + a0) + v);
-        *reinterpret_cast<uint4*>(ws + static_cast<size_t>(r) * F::kPitch + v * 16) = d;
-    }
-    // activations of this slice, rounded to fp16; rows past the batch are zero
-    const uint32_t q4 = ncols >> 2;
-    for (uint32_t i = tid; i < kXRows * q4; i += kMvThreads) {
-        const uint32_t n = i / q4, c = (i - n * q4) << 2;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (n < p.batch) {
-            const float* src = p.x + static_cast<size_t>(n) * p.x_stride + c0 + c;
-            v = *reinterpret_cast<const float4*>(src);
-            if (IN == kInSiluMul) {
-                const float4 u = *reinterpret_cast<const float4*>(src + p.cols);
-                v = make_float4(silu_mul(v.x, u.x), silu_mul(v.y, u.y), silu_mul(v.z, u.z), silu_mul(v.w, u.w));
+    // Every byte of a chunk arrives by cp.async, issued at once: one round trip to L2 / HBM per chunk, and the
+    // next chunk's is under way while this one is computed.
+    auto issue_weights = [&](uint32_t chunk) {
+        if (chunk < n_chunks) {
+            uint8_t* st = smem + (chunk % kMvStages) * stage_bytes;
+            const uint32_t c0 = c_begin + chunk * p.chunk_cols;
+            const uint32_t ncols = min(p.chunk_cols, c_end - c0);
+            const uint32_t b0 = c0 / F::kBlockWeights * F::kBlockBytes;
+            const uint32_t b1 = b0 + ncols / F::kBlockWeights * F::kBlockBytes;
+            uint8_t* ws = st + kXArrays * x_bytes;
+            if (p.aligned16) {
+                // 16 lanes across a row's 16-byte vectors (a chunk's row is at most 15 of them), 16 rows per pass
+                const uint32_t a0 = b0 & ~15u, nvec = (b1 - a0 + 15) >> 4;
+                const uint32_t v = tid & 15;
+                if (v < nvec) {
+#pragma unroll
+                    for (uint32_t r = tid >> 4; r < kMvRows; r += kMvThreads / 16) {
+                        const uint32_t row = min(row0 + r, p.rows - 1);
+                        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(ws + r * p.w_pitch + v * 16));
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                                     "l"(p.w + static_cast<size_t>(row) * p.row_stride + a0 + v * 16) : "memory");
+                    }
+                }
+            } else {
+                // rows that do not start on 16-byte boundaries (a Q6_K row of 256 columns is 210 bytes): 2-byte copies
+                const uint32_t n16 = (b1 - b0) >> 1, w_shift = b0 & 15u;
+                for (uint32_t i = tid; i < kMvRows * n16; i += kMvThreads) {
+                    const uint32_t r = i / n16, v = i - r * n16;
+                    const uint32_t row = min(row0 + r, p.rows - 1);
+                    const uint16_t d = __ldg(reinterpret_cast<const uint16_t*>(p.w + static_cast<size_t>(row) * p.row_stride + b0) + v);
+                    *reinterpret_cast<uint16_t*>(ws + static_cast<size_t>(r) * p.w_pitch + w_shift + v * 2) = d;
+                }
             }
         }
-        __half2* dst = reinterpret_cast<__half2*>(xs + static_cast<size_t>(n) * x_pitch + c);
-        dst[0] = __floats2half2_rn(v.x, v.y);
-        dst[1] = __floats2half2_rn(v.z, v.w);
-    }
-    __syncthreads();
-
-    float acc[2][NT][4];
-#pragma unroll
-    for (int m = 0; m < 2; ++m)
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[m][n][e] = 0.0f;
-
-    const uint8_t* wrow[2][2];
-#pragma unroll
-    for (int m = 0; m < 2; ++m) {
-        wrow[m][0] = ws + static_cast<size_t>(warp * 32 + m * 16 + g) * F::kPitch + w_shift;
-        wrow[m][1] = wrow[m][0] + 8 * F::kPitch;
-    }
-    const __half* xrow = xs + static_cast<size_t>(g) * x_pitch + 2 * t;
-
-    if (QT == kQ4_0) {
-        const uint32_t nblk = ncols >> 5;
-        for (uint32_t b = 0; b < nblk; ++b) {
-            uint32_t bl[NT][2], bh[NT][2];
-#pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                const __half* xp = xrow + static_cast<size_t>(n) * 8 * x_pitch + b * 32;
-                bl[n][0] = *reinterpret_cast<const uint32_t*>(xp);
-                bl[n][1] = *reinterpret_cast<const uint32_t*>(xp + 8);
-                bh[n][0] = *reinterpret_cast<const uint32_t*>(xp + 16);
-                bh[n][1] = *reinterpret_cast<const uint32_t*>(xp + 24);
+    };
+    auto issue_activations = [&](uint32_t chunk) {
+        if (chunk < n_chunks) {
+            uint8_t* st = smem + (chunk % kMvStages) * stage_bytes;
+            const uint32_t c0 = c_begin + chunk * p.chunk_cols;
+            const uint32_t ncols = min(p.chunk_cols, c_end - c0);
+            // 64 lanes across a row's float4 (a chunk is at most 256 columns), 4 batch rows per pass
+            const uint32_t cq = tid & 63;
+            if (cq < (ncols >> 2)) {
+                const float* src = p.x + static_cast<size_t>(tid >> 6) * p.x_stride + c0 + cq * 4;
+                uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(st + ((tid >> 6) * x_pitch + cq * 4) * 4));
+                for (uint32_t n = tid >> 6; n < p.batch; n += kMvThreads / 64) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                    if (IN == kInSiluMul)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + x_bytes), "l"(src + p.cols) : "memory");
+                    src += static_cast<size_t>(kMvThreads / 64) * p.x_stride;
+                    dst += (kMvThreads / 64) * x_pitch * 4;
+                }
             }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per chunk index, empty or not
+    };
+
+    float acc[NT][4];
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                uint32_t lo[4], hi[4];
-                float dg, d8;
-                q4_0_fragments(wrow[m][0] + b * 18, wrow[m][1] + b * 18, t, lo, hi, dg, d8);
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.0f;
+
+    // Launched as a programmatic dependent of the kernel before it: the first chunk's weights (never written by
+    // any kernel) are on their way while that kernel finishes; its output - this kernel's activations - is
+    // touched only after the wait. Without the launch attribute both instructions do nothing.
+    static_assert(kMvStages == 2, "the prologue below issues exactly one chunk");
+    issue_weights(0);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    issue_activations(0);
+
+    for (uint32_t chunk = 0; chunk < n_chunks; ++chunk) {
+        issue_weights(chunk + 1);            // into the stage the previous iteration finished with
+        issue_activations(chunk + 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(kMvStages - 1) : "memory");
+        __syncthreads();
+        uint8_t* st = smem + (chunk % kMvStages) * stage_bytes;
+        uint32_t* xw = reinterpret_cast<uint32_t*>(st);
+        const uint8_t* ws = st + kXArrays * x_bytes;
+        const uint32_t c0 = c_begin + chunk * p.chunk_cols;
+        const uint32_t ncols = min(p.chunk_cols, c_end - c0);
+        const uint32_t w_shift = (c0 / F::kBlockWeights * F::kBlockBytes) & 15u;
+
+        // Activations in place, two columns at a time: fp32 (x0, x1) -> the words {hi0, hi1} and {lo0, lo1} with
+        // hi = fp16(x), lo = fp16(x - hi): 22 bits of x, so the products lose nothing that fp32 keeps. Rows past
+        // the batch become zero.
+        {
+            const uint32_t cq = tid & 63;
+            if (cq < (ncols >> 2)) {
+#pragma unroll 2
+                for (uint32_t n = tid >> 6; n < kXRows; n += kMvThreads / 64) {
+                    uint4* wp = reinterpret_cast<uint4*>(xw + n * x_pitch + cq * 4);
+                    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                    if (n < p.batch) {
+                        float4 w = *reinterpret_cast<const float4*>(wp);
+                        if (IN == kInSiluMul) {
+                            const float4 u = *reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(wp) + x_bytes);
+                            w = make_float4(silu_mul(w.x, u.x), silu_mul(w.y, u.y), silu_mul(w.z, u.z), silu_mul(w.w, u.w));
+                        }
+                        const __half2 h01 = __floats2half2_rn(w.x, w.y), h23 = __floats2half2_rn(w.z, w.w);
+                        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                        const __half2 l01 = __floats2half2_rn(w.x - f01.x, w.y - f01.y);
+                        const __half2 l23 = __floats2half2_rn(w.z - f23.x, w.w - f23.y);
+                        o = make_uint4(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&l01),
+                                       *reinterpret_cast<const uint32_t*>(&h23), *reinterpret_cast<const uint32_t*>(&l23));
+                    }
+                    *wp = o;
+                }
+            }
+        }
+        __syncthreads();
+
+        // Lane t of a quad owns a contiguous run of columns, so its B words are one or two 16-byte loads and its
+        // weights a few adjacent bytes: k slots (2t, 2t + 1) and (2t + 8, 2t + 9) of an MMA are two column pairs of
+        // that run, once against the {hi, hi} words and once against the {lo, lo} words, with the same A registers.
+        const uint8_t* wg = ws + (mt * 16 + g) * p.w_pitch + w_shift;
+        const uint8_t* w8 = wg + 8 * p.w_pitch;
+        const uint32_t* xrow = xw + g * x_pitch;
+
+        if (QT == kQ4_0) {
+            // columns [8t, 8t + 8) of a block: low (t < 2) or high nibbles of bytes [8 (t & 1), 8 (t & 1) + 8).
+            // 0x6400 | n is the fp16 number 1024 + n, 0x6400 | (n << 4) is 1024 + 16 n: one fused multiply-add
+            // takes either to n - 8 exactly.
+            const bool high = t >= 2;
+            const uint32_t nib_mask = high ? 0x00F000F0u : 0x000F000Fu;
+            const __half2 mul = high ? __floats2half2_rn(0.0625f, 0.0625f) : __floats2half2_rn(1.0f, 1.0f);
+            const __half2 add = high ? __floats2half2_rn(-72.0f, -72.0f) : __floats2half2_rn(-1032.0f, -1032.0f);
+            const uint32_t byte_off = 2 + 8 * (t & 1);
+            const uint32_t nblk = ncols >> 5, half0 = (nblk + 1) >> 1;
+            const uint32_t b_lo = kh ? half0 : 0u, b_hi = kh ? nblk : half0;
+            for (uint32_t b = b_lo; b < b_hi; ++b) {
+                uint4 bx[NT][2];   // words of columns 8t .. 8t + 7: {hi, lo} x 4 pairs
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(xrow + n * 8 * x_pitch + b * 32 + 8 * t);
+                    bx[n][0] = xp[0];
+                    bx[n][1] = xp[1];
+                }
+                const uint8_t* bg = wg + b * 18;
+                const uint8_t* b8 = w8 + b * 18;
+                const float dg = half_bits_to_float(*reinterpret_cast<const uint16_t*>(bg));
+                const float d8 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(b8));
+                uint32_t ag[4], a8[4];   // pair p = columns 8t + 2p, 8t + 2p + 1
+#pragma unroll
+                for (int pr = 0; pr < 4; ++pr) {
+                    const uint32_t vg = *reinterpret_cast<const uint16_t*>(bg + byte_off + 2 * pr);
+                    const uint32_t v8 = *reinterpret_cast<const uint16_t*>(b8 + byte_off + 2 * pr);
+                    const uint32_t hg = (__byte_perm(vg, 0u, 0x4140) & nib_mask) | 0x64006400u;
+                    const uint32_t h8 = (__byte_perm(v8, 0u, 0x4140) & nib_mask) | 0x64006400u;
+                    const __half2 rg = __hfma2(*reinterpret_cast<const __half2*>(&hg), mul, add);
+                    const __half2 r8 = __hfma2(*reinterpret_cast<const __half2*>(&h8), mul, add);
+                    ag[pr] = *reinterpret_cast<const uint32_t*>(&rg);
+                    a8[pr] = *reinterpret_cast<const uint32_t*>(&r8);
+                }
+                const uint32_t a01[4] = {ag[0], a8[0], ag[1], a8[1]}, a23[4] = {ag[2], a8[2], ag[3], a8[3]};
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma16816(c, lo, bl[n][0], bl[n][1]);
-                    mma16816(c, hi, bh[n][0], bh[n][1]);
-                    acc[m][n][0] = fmaf(dg, c[0], acc[m][n][0]);
-                    acc[m][n][1] = fmaf(dg, c[1], acc[m][n][1]);
-                    acc[m][n][2] = fmaf(d8, c[2], acc[m][n][2]);
-                    acc[m][n][3] = fmaf(d8, c[3], acc[m][n][3]);
+                    mma16816(c, a01, bx[n][0].y, bx[n][0].w);   // the small terms first: lo words
+                    mma16816(c, a23, bx[n][1].y, bx[n][1].w);
+                    mma16816(c, a01, bx[n][0].x, bx[n][0].z);
+                    mma16816(c, a23, bx[n][1].x, bx[n][1].z);
+                    acc[n][0] = fmaf(dg, c[0], acc[n][0]);
+                    acc[n][1] = fmaf(dg, c[1], acc[n][1]);
+                    acc[n][2] = fmaf(d8, c[2], acc[n][2]);
+                    acc[n][3] = fmaf(d8, c[3], acc[n][3]);
                 }
             }
-        }
-    } else {
-        const uint32_t ngroups = ncols >> 4;
-        for (uint32_t j = 0; j < ngroups; ++j) {
-            uint32_t bx[NT][2];
+        } else {
+            // columns [4t, 4t + 4) of a 16-weight group; weight l of a 128-weight half sits in ql / qh as
+            // quantization.cpp:1469-1499 lays out
+            const uint32_t ngroups = ncols >> 4, half0 = (ngroups + 1) >> 1;
+            const uint32_t j_lo = kh ? half0 : 0u, j_hi = kh ? ngroups : half0;
+            const __half2 bias = __floats2half2_rn(1056.0f, 1056.0f);   // 1024 + 32
+            for (uint32_t j = j_lo; j < j_hi; ++j) {
+                uint4 bx[NT];
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                const __half* xp = xrow + static_cast<size_t>(n) * 8 * x_pitch + j * 16;
-                bx[n][0] = *reinterpret_cast<const uint32_t*>(xp);
-                bx[n][1] = *reinterpret_cast<const uint32_t*>(xp + 8);
-            }
-            const uint32_t blk = (j >> 4) * 210;
+                for (int n = 0; n < NT; ++n) bx[n] = *reinterpret_cast<const uint4*>(xrow + n * 8 * x_pitch + j * 16 + 4 * t);
+                const uint32_t blk = (j >> 4) * 210, jj = j & 15;
+                const uint32_t h = jj >> 3, quarter = (jj & 7) >> 1, sub = jj & 1;
+                const uint32_t ql_off = 64 * h + ((quarter & 1) ? 32 : 0) + 16 * sub + 4 * t;   // q2 / q4 read ql[l + 32]
+                const uint32_t qh_off = 128 + 32 * h + 16 * sub + 4 * t;
+                const uint32_t nib_shift = (quarter >> 1) * 4, hi_shift = quarter * 2;          // q3 / q4: high nibble
+                const uint8_t* bg = wg + blk;
+                const uint8_t* b8 = w8 + blk;
+                const float sg = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t*>(bg + 208)),
+                                           static_cast<float>(static_cast<int8_t>(bg[192 + jj])));
+                const float s8 = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t*>(b8 + 208)),
+                                           static_cast<float>(static_cast<int8_t>(b8[192 + jj])));
+                uint32_t a[4];   // {row g pair 0, row g + 8 pair 0, row g pair 1, row g + 8 pair 1}
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                uint32_t a[4];
-                float sg, s8;
-                q6_k_fragment(wrow[m][0] + blk, wrow[m][1] + blk, static_cast<int>(j & 15), t, a, sg, s8);
+                for (int pr = 0; pr < 2; ++pr) {
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const uint8_t* bp = r ? b8 : bg;
+                        const uint32_t lo2 = *reinterpret_cast<const uint16_t*>(bp + ql_off + 2 * pr);
+                        const uint32_t hi2 = *reinterpret_cast<const uint16_t*>(bp + qh_off + 2 * pr);
+                        const uint32_t q2 = ((lo2 >> nib_shift) & 0x0F0Fu) | (((hi2 >> hi_shift) & 0x0303u) << 4);
+                        const uint32_t hw = __byte_perm(q2, 0u, 0x4140) | 0x64006400u;
+                        const __half2 rr = __hsub2(*reinterpret_cast<const __half2*>(&hw), bias);
+                        a[2 * pr + r] = *reinterpret_cast<const uint32_t*>(&rr);
+                    }
+                }
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma16816(c, a, bx[n][0], bx[n][1]);
-                    acc[m][n][0] = fmaf(sg, c[0], acc[m][n][0]);
-                    acc[m][n][1] = fmaf(sg, c[1], acc[m][n][1]);
-                    acc[m][n][2] = fmaf(s8, c[2], acc[m][n][2]);
-                    acc[m][n][3] = fmaf(s8, c[3], acc[m][n][3]);
+                    mma16816(c, a, bx[n].y, bx[n].w);
+                    mma16816(c, a, bx[n].x, bx[n].z);
+                    acc[n][0] = fmaf(sg, c[0], acc[n][0]);
+                    acc[n][1] = fmaf(sg, c[1], acc[n][1]);
+                    acc[n][2] = fmaf(s8, c[2], acc[n][2]);
+                    acc[n][3] = fmaf(s8, c[3], acc[n][3]);
                 }
             }
         }
+        __syncthreads();   // this stage may be refilled by the next iteration's issue
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
 
-    // C fragment: c0, c1 = (row g, batch 2t, 2t + 1); c2, c3 = (row g + 8, same)
-    const bool direct = p.slices == 1;
-    float* dst = direct ? p.out : p.partial + static_cast<size_t>(slice) * p.batch * p.rows;
+    // Every warp leaves its partial tile (its m-tile, its half of the columns) in shared memory:
+    // red[kh][batch][row], C fragment c0, c1 = (row g, batch 2t, 2t + 1), c2, c3 = (row g + 8, same).
+    // The column slices of a row tile are the CTAs of one cluster: after the cluster barrier CTA s adds rows
+    // [s * 64 / S, (s + 1) * 64 / S) of all 2 S partial tiles, slice by slice and half by half, through
+    // distributed shared memory - no round trip through L2, and the order is fixed, so results repeat bit for
+    // bit. The second barrier keeps every CTA's tiles alive until their readers are done.
+    float* red = reinterpret_cast<float*>(smem);   // [2][kXRows][kRedPitch], over the first stage
 #pragma unroll
-    for (int m = 0; m < 2; ++m)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t row = row0 + warp * 32 + m * 16 + g + ((e & 2) ? 8 : 0);
-                const uint32_t bn = n * 8 + 2 * t + (e & 1);
-                if (row < p.rows && bn < p.batch) {
-                    const size_t o = static_cast<size_t>(bn) * p.rows + row;
-                    float v = acc[m][n][e];
-                    if (direct && p.residual) v = __fadd_rn(p.residual[o], v);
-                    dst[o] = v;
-                }
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t lrow = mt * 16 + g + ((e & 2) ? 8 : 0);
+            const uint32_t bn = n * 8 + 2 * t + (e & 1);
+            red[(kh * kXRows + bn) * kRedPitch + lrow] = acc[n][e];
+        }
+    if (S > 1) cluster_sync_all(); else __syncthreads();
+    const uint32_t rs4 = (kMvRows / S) >> 2;                 // float4 per batch row in this CTA's share
+    const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
+    const bool vec_out = (p.rows & 3u) == 0;
+    for (uint32_t i = tid; i < kXRows * rs4; i += kMvThreads) {
+        const uint32_t bn = i / rs4, lrow = slice * (kMvRows / S) + ((i - bn * rs4) << 2);
+        if (bn >= p.batch || row0 + lrow >= p.rows) continue;
+        const uint32_t addr0 = red_base + (bn * kRedPitch + lrow) * 4;
+        const uint32_t addr1 = addr0 + kXRows * kRedPitch * 4;
+        float4 sum = ld_cluster_f4(addr0, 0);
+        for (uint32_t k = 0; k < S; ++k) {
+            if (k) {
+                const float4 v = ld_cluster_f4(addr0, k);
+                sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
             }
-    if (direct) return;
-
-    // the last slice of this row tile to arrive adds the partial sums in slice order
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) ticket = atomicAdd(p.counters + tile, 1u);
-    __syncthreads();
-    if (ticket != p.slices - 1) return;
-    __threadfence();
-    const uint32_t tile_rows = min(static_cast<uint32_t>(kMvRows), p.rows - row0);
-    for (uint32_t i = tid; i < p.batch * tile_rows; i += kMvThreads) {
-        const uint32_t bn = i / tile_rows, r = i - bn * tile_rows;
-        const size_t o = static_cast<size_t>(bn) * p.rows + row0 + r;
-        float s = __ldcg(p.partial + o);
-        for (uint32_t k = 1; k < p.slices; ++k) s = __fadd_rn(s, __ldcg(p.partial + static_cast<size_t>(k) * p.batch * p.rows + o));
-        if (p.residual) s = __fadd_rn(p.residual[o], s);
-        p.out[o] = s;
+            const float4 v = ld_cluster_f4(addr1, k);
+            sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
+        }
+        const size_t o = static_cast<size_t>(bn) * p.rows + row0 + lrow;
+        if (vec_out) {
+            if (p.residual) {
+                const float4 r = *reinterpret_cast<const float4*>(p.residual + o);
+                sum = make_float4(__fadd_rn(r.x, sum.x), __fadd_rn(r.y, sum.y), __fadd_rn(r.z, sum.z), __fadd_rn(r.w, sum.w));
+            }
+            *reinterpret_cast<float4*>(p.out + o) = sum;
+        } else {
+            const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (row0 + lrow + e < p.rows) p.out[o + e] = p.residual ? __fadd_rn(p.residual[o + e], vals[e]) : vals[e];
+        }
     }
-    if (tid == 0) p.counters[tile] = 0;   // ready for the next launch on this stream
+    if (S > 1) cluster_sync_all();
+}
+
+static uint32_t weight_pitch(uint32_t chunk_bytes) {
+    // room for the enclosing 16-byte range of a chunk, and rows 4 banks apart (pitch / 4 = 4 mod 8)
+    uint32_t p = (chunk_bytes + 16 + 15) / 16 * 16;
+    while ((p / 4) % 8 != 4) p += 16;
+    return p;
 }
 
 template <int QT, int NT, int IN>
-static int launch_matvec_nt(mlc_ctx* ctx, const MatVecParams& p, dim3 grid, size_t smem) {
+static int launch_matvec_nt(mlc_ctx* ctx, const MatVecParams& p, unsigned ctas, size_t smem) {
     auto kernel = quant_matvec_kernel<QT, NT, IN>;
     static bool attr_set[16] = {};
     if (ctx->device >= 0 && ctx->device < 16 && !attr_set[ctx->device]) {
-        MLCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+        MLCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set[ctx->device] = true;
     }
-    kernel<<<grid, kMvThreads, smem, ctx->stream>>>(p);
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, kernel, ctas, kMvThreads, smem, p.slices, p));
     ++ctx->launches;
-    MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
 }
 
@@ -424,36 +570,26 @@ template <int QT, int IN>
 static int launch_matvec(mlc_ctx* ctx, MatVecParams p) {
     using F = QuantFormat<QT>;
     const uint32_t tiles = (p.rows + kMvRows - 1) / kMvRows;
-    // enough CTAs for two per SM where the columns allow it; a slice is a whole number of blocks
-    const uint32_t unit = QT == kQ6_K ? 256u : 128u;
-    const uint32_t max_slices = (p.cols + unit - 1) / unit;
-    uint32_t want = std::max(1u, (2u * static_cast<uint32_t>(ctx->sm_count) + tiles - 1) / tiles);
-    want = std::min(want, max_slices);
-    uint32_t slice_cols = ((p.cols + want - 1) / want + unit - 1) / unit * unit;
-    slice_cols = std::min<uint32_t>(slice_cols, kMvSliceMax);
-    p.slice_cols = slice_cols;
-    p.slices = (p.cols + slice_cols - 1) / slice_cols;
+    // Column slices (= CTAs per cluster): as many as it takes to put two CTAs on every SM, 8 at most, and never
+    // slices of less than one block. A slice is worked through in chunks of kMvChunk columns.
+    uint32_t S = 1;
+    while (S < 8 && tiles * S < 2u * static_cast<uint32_t>(ctx->sm_count) && p.cols / (2 * S) >= F::kBlockWeights) S *= 2;
+    const uint32_t unit = F::kBlockWeights;
+    p.slices = S;
+    p.slice_cols = ((p.cols + S - 1) / S + unit - 1) / unit * unit;
+    p.chunk_cols = std::min<uint32_t>(p.slice_cols, kMvChunk);
+    p.w_pitch = weight_pitch(p.chunk_cols / F::kBlockWeights * F::kBlockBytes);
     const uint32_t nt = (p.batch + 7) / 8;
     const int NT = nt <= 1 ? 1 : (nt <= 2 ? 2 : (nt <= 4 ? 4 : 8));
-    if (p.slices > 1) {
-        const size_t part_bytes = static_cast<size_t>(p.slices) * p.batch * p.rows * sizeof(float);
-        p.partial = static_cast<float*>(mlc_cached_buffer(ctx, "mlc_matvec_partials", part_bytes));
-        // counters: one block for any row-tile count this context sees; zeroed when (re)allocated
-        const size_t cnt_bytes = std::max<size_t>(4096, static_cast<size_t>(tiles) * 4);
-        auto it = ctx->cached.find("mlc_matvec_counters");
-        const bool fresh = it == ctx->cached.end() || it->second.second < cnt_bytes;
-        p.counters = static_cast<uint32_t*>(mlc_cached_buffer(ctx, "mlc_matvec_counters", cnt_bytes));
-        if (!p.partial || !p.counters) return ctx->fail(MLC_ERR_CUDA, "scratch allocation for the mat-vec failed");
-        if (fresh) MLCB_CUDA(ctx, cudaMemsetAsync(p.counters, 0, cnt_bytes, ctx->stream));
-    }
-    const size_t smem = static_cast<size_t>(NT) * 8 * (slice_cols + kXPad) * sizeof(__half) +
-                        static_cast<size_t>(kMvRows) * F::kPitch;
-    const dim3 grid(tiles, p.slices);
+    const size_t stage = static_cast<size_t>(IN == kInSiluMul ? 2 : 1) * NT * 8 * (p.chunk_cols + kXPadWords) * 4 +
+                         static_cast<size_t>(kMvRows) * p.w_pitch;
+    const size_t smem = std::max(stage * kMvStages, static_cast<size_t>(2) * NT * 8 * kRedPitch * sizeof(float));
+    const unsigned ctas = tiles * S;
     switch (NT) {
-        case 1: return launch_matvec_nt<QT, 1, IN>(ctx, p, grid, smem);
-        case 2: return launch_matvec_nt<QT, 2, IN>(ctx, p, grid, smem);
-        case 4: return launch_matvec_nt<QT, 4, IN>(ctx, p, grid, smem);
-        default: return launch_matvec_nt<QT, 8, IN>(ctx, p, grid, smem);
+        case 1: return launch_matvec_nt<QT, 1, IN>(ctx, p, ctas, smem);
+        case 2: return launch_matvec_nt<QT, 2, IN>(ctx, p, ctas, smem);
+        case 4: return launch_matvec_nt<QT, 4, IN>(ctx, p, ctas, smem);
+        default: return launch_matvec_nt<QT, 8, IN>(ctx, p, ctas, smem);
     }
 }
 
@@ -464,9 +600,9 @@ static int check_matvec(mlc_ctx* ctx, int qt, const void* w, const void* in, con
     const size_t bw = qt == kQ6_K ? 256 : 32, bb = qt == kQ6_K ? 210 : 18;
     if (cols % bw) return ctx->fail(MLC_ERR_UNSUPPORTED, "cols must be a whole number of quantisation blocks");
     if (row_stride < cols / bw * bb) return ctx->fail(MLC_ERR_INVALID_ARG, "row_stride shorter than a row");
-    if (row_stride % 16 || reinterpret_cast<uintptr_t>(w) % 16)
-        return ctx->fail(MLC_ERR_UNSUPPORTED, "weights and row_stride must be 16-byte aligned");
+    if (row_stride % 2 || reinterpret_cast<uintptr_t>(w) % 2) return ctx->fail(MLC_ERR_INVALID_ARG, "weights and row_stride must be even");
     if (reinterpret_cast<uintptr_t>(in) % 16 || x_stride % 4) return ctx->fail(MLC_ERR_INVALID_ARG, "input must be 16-byte aligned");
+    if (rows % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 16) return ctx->fail(MLC_ERR_INVALID_ARG, "output must be 16-byte aligned");
     if (batch > 64) return ctx->fail(MLC_ERR_UNSUPPORTED, "batch above 64");
     if (rows >= (1u << 31) || cols >= (1u << 31)) return ctx->fail(MLC_ERR_UNSUPPORTED, "dimension too large");
     return MLC_OK;
@@ -489,11 +625,10 @@ int mlc_encode_rms_norm_batched(mlc_ctx* ctx, const void* in, const void* weight
                                reinterpret_cast<uintptr_t>(weight)) % 16))
         return ctx->fail(MLC_ERR_INVALID_ARG, "buffers must be 16-byte aligned");
     DeviceGuard guard(ctx->device);
-    rms_norm_batched_kernel<<<static_cast<unsigned>(batch), 256, 0, ctx->stream>>>(
-        static_cast<const float*>(in), static_cast<const float*>(weight), epsilon, static_cast<uint32_t>(length),
-        static_cast<float*>(out), static_cast<__half*>(out_f16));
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, rms_norm_batched_kernel, static_cast<unsigned>(batch), 256, 0, 1,
+                                       static_cast<const float*>(in), static_cast<const float*>(weight), epsilon,
+                                       static_cast<uint32_t>(length), static_cast<float*>(out), static_cast<__half*>(out_f16)));
     ++ctx->launches;
-    MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
 }
 
@@ -507,10 +642,10 @@ int mlc_encode_add_batched(mlc_ctx* ctx, const void* a, const void* b, void* out
     DeviceGuard guard(ctx->device);
     const size_t n4 = total_elements / 4;
     const size_t threads = std::max<size_t>(n4, total_elements - n4 * 4);
-    add_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, ctx->stream>>>(
-        static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(out), n4, total_elements);
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, add_kernel, static_cast<unsigned>((threads + 255) / 256), 256, 0, 1,
+                                       static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(out), n4,
+                                       total_elements));
     ++ctx->launches;
-    MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
 }
 
@@ -520,10 +655,10 @@ int mlc_encode_silu_mul_batched(mlc_ctx* ctx, const void* gate, const void* up, 
     if (!gate || !up || !out) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
     if (total_elements == 0) return MLC_OK;
     DeviceGuard guard(ctx->device);
-    silu_mul_kernel<<<static_cast<unsigned>((total_elements + 255) / 256), 256, 0, ctx->stream>>>(
-        static_cast<const float*>(gate), static_cast<const float*>(up), static_cast<float*>(out), total_elements);
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, silu_mul_kernel, static_cast<unsigned>((total_elements + 255) / 256), 256, 0, 1,
+                                       static_cast<const float*>(gate), static_cast<const float*>(up), static_cast<float*>(out),
+                                       total_elements));
     ++ctx->launches;
-    MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
 }
 
@@ -537,11 +672,11 @@ int mlc_encode_gate_up_split_silu_mul(mlc_ctx* ctx, const void* gate_up, void* g
     if (batch * ffn_gate_up_rows >= (size_t(1) << 32)) return ctx->fail(MLC_ERR_UNSUPPORTED, "batch too large");
     DeviceGuard guard(ctx->device);
     const size_t n = batch * ffn_inner;
-    gate_up_silu_mul_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
-        static_cast<const float*>(gate_up), static_cast<float*>(gate), static_cast<float*>(up), static_cast<float*>(out),
-        static_cast<uint32_t>(batch), static_cast<uint32_t>(ffn_inner), static_cast<uint32_t>(ffn_gate_up_rows));
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, gate_up_silu_mul_kernel, static_cast<unsigned>((n + 255) / 256), 256, 0, 1,
+                                       static_cast<const float*>(gate_up), static_cast<float*>(gate), static_cast<float*>(up),
+                                       static_cast<float*>(out), static_cast<uint32_t>(batch), static_cast<uint32_t>(ffn_inner),
+                                       static_cast<uint32_t>(ffn_gate_up_rows)));
     ++ctx->launches;
-    MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
 }
 
@@ -556,11 +691,10 @@ int mlc_encode_embedding_q4_0(mlc_ctx* ctx, const void* table, size_t row_stride
         return ctx->fail(MLC_ERR_INVALID_ARG, "row_stride shorter than a row, or odd");
     if (batch >= (1u << 31) || cols >= (1u << 31) || vocab >= (size_t(1) << 32)) return ctx->fail(MLC_ERR_UNSUPPORTED, "dimension too large");
     DeviceGuard guard(ctx->device);
-    embedding_q4_0_kernel<<<static_cast<unsigned>(batch), 256, 0, ctx->stream>>>(
-        static_cast<const uint8_t*>(table), row_stride, static_cast<const uint32_t*>(token_ids), static_cast<uint32_t>(vocab),
-        static_cast<uint32_t>(cols), static_cast<float*>(out), ctx->d_err);
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, embedding_q4_0_kernel, static_cast<unsigned>(batch), 256, 0, 1,
+                                       static_cast<const uint8_t*>(table), row_stride, static_cast<const uint32_t*>(token_ids),
+                                       static_cast<uint32_t>(vocab), static_cast<uint32_t>(cols), static_cast<float*>(out), ctx->d_err));
     ++ctx->launches;
-    MLCB_CUDA(ctx, cudaGetLastError());
     return MLC_OK;
 }
 
@@ -571,6 +705,8 @@ static int encode_matvec(mlc_ctx* ctx, int qt, int in_mode, const void* weights,
     int st = check_matvec(ctx, qt, weights, in, out, batch, rows, cols, row_stride, x_stride);
     if (st != MLC_OK) return st;
     if (in_mode == kInSiluMul && x_stride < 2 * cols) return ctx->fail(MLC_ERR_INVALID_ARG, "row shorter than gate + up");
+    if (residual && rows % 4 == 0 && reinterpret_cast<uintptr_t>(residual) % 16)
+        return ctx->fail(MLC_ERR_INVALID_ARG, "residual must be 16-byte aligned");
     DeviceGuard guard(ctx->device);
     MatVecParams p{};
     p.w = static_cast<const uint8_t*>(weights);
@@ -582,6 +718,7 @@ static int encode_matvec(mlc_ctx* ctx, int qt, int in_mode, const void* weights,
     p.rows = static_cast<uint32_t>(rows);
     p.cols = static_cast<uint32_t>(cols);
     p.x_stride = static_cast<uint32_t>(x_stride);
+    p.aligned16 = (row_stride % 16 == 0 && reinterpret_cast<uintptr_t>(weights) % 16 == 0) ? 1u : 0u;
     if (qt == kQ6_K) return in_mode == kInSiluMul ? launch_matvec<kQ6_K, kInSiluMul>(ctx, p) : launch_matvec<kQ6_K, kInPlain>(ctx, p);
     return in_mode == kInSiluMul ? launch_matvec<kQ4_0, kInSiluMul>(ctx, p) : launch_matvec<kQ4_0, kInPlain>(ctx, p);
 }

@@ -77,6 +77,7 @@ _PROTOTYPES = {
     "mlc_executor_attach_paged_storage": (_i, [_vp, _vp]),
     "mlc_executor_set_call_order": (_i, [_vp, _i]),
     "mlc_executor_attach_model": (_i, [_vp, C.POINTER(ModelDescC)]),
+    "mlc_executor_assume_context": (_i, [_vp, _u32, _sz]),
     "mlc_executor_run_decode": (_sz, [_vp, C.POINTER(RequestSlotC), _sz, C.POINTER(C.c_uint8), _fp, _sz]),
     "mlc_executor_run_prefill": (_sz, [_vp, _u32, _u64p, _sz, _fp, _sz]),
     "mlc_executor_release_request": (None, [_vp, _u32]),
@@ -255,6 +256,10 @@ class PagedAttentionExecutor(_ExecutorBase):
 
     def set_call_order(self, reference_order: bool):
         assert lib().mlc_executor_set_call_order(self._h, 1 if reference_order else 0) == 0
+
+    def assume_context(self, request_id: int, tokens: int) -> bool:
+        """Reserve pages for a context whose K/V rows the caller fills in itself; next position = tokens."""
+        return lib().mlc_executor_assume_context(self._h, request_id, tokens) == 0
 
     def attach_model(self, model) -> bool:
         """model: a synth.SyntheticModel (or anything with its fields) whose `device` dict maps tensor names to

@@ -11,9 +11,18 @@
 // out.bin: o (encode path) f32 [N,H,D] | o (run path) f32 [N,H,D] | k_pool f16 | v_pool f16 | gathered K of request 0
 //          f16 [KVH, seq_lens[0], D]
 // Exit code 0 when every call behaved as the reference's contract says; the numbers are checked by the test.
+//
+//   shim_driver ops <in.bin> <out.bin> batch rows cols
+//
+// The walker's other encode* ops through the same class, weights as host vectors like the walker passes them
+// (compiler/runtime/batched_walker.cpp:248-270, 340-350, 379-383):
+// in.bin : x f32 [batch, cols] | norm weight f32 [cols] | W Q4_0 [rows, cols / 32 * 18] | resid f32 [batch, rows] |
+//          gate_up f32 [batch, rows]   (gate = first half of a row, up = second half)
+// out.bin: RMSNorm(x) f32 [batch, cols] | W * that f32 [batch, rows] | that + resid | SiLU(gate) * up f32 [batch, rows / 2]
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <string>
 #include <vector>
 
 #include "runtime/metal_runtime.hpp"
@@ -30,7 +39,60 @@ static bool read_exact(FILE* f, void* dst, size_t bytes) { return bytes == 0 || 
         }                                                                    \
     } while (0)
 
+static int run_ops(int argc, char** argv) {
+    if (argc != 7) return 2;
+    const size_t batch = std::strtoull(argv[4], nullptr, 10), rows = std::strtoull(argv[5], nullptr, 10);
+    const size_t cols = std::strtoull(argv[6], nullptr, 10), stride = cols / 32 * 18, inner = rows / 2;
+    std::vector<float> x(batch * cols), nw(cols), resid(batch * rows), gate_up(batch * rows);
+    std::vector<uint8_t> w(rows * stride);
+    FILE* in = std::fopen(argv[2], "rb");
+    REQUIRE(in != nullptr);
+    REQUIRE(read_exact(in, x.data(), x.size() * 4) && read_exact(in, nw.data(), nw.size() * 4) &&
+            read_exact(in, w.data(), w.size()) && read_exact(in, resid.data(), resid.size() * 4) &&
+            read_exact(in, gate_up.data(), gate_up.size() * 4));
+    std::fclose(in);
+    MetalExecutor& ex = MetalExecutor::Instance();
+    REQUIRE(ex.isAvailable());
+    void* d_x = ex.getOrAllocCachedBuffer("w_residual", x.size() * 4);
+    void* d_n = ex.getOrAllocCachedBuffer("w_norm_out", x.size() * 4);
+    void* d_z = ex.getOrAllocCachedBuffer("w_attn_out", resid.size() * 4);
+    void* d_r = ex.getOrAllocCachedBuffer("w_resid_in", resid.size() * 4);
+    void* d_a = ex.getOrAllocCachedBuffer("w_resid1", resid.size() * 4);
+    void* d_gu = ex.getOrAllocCachedBuffer("w_gate_up", gate_up.size() * 4);
+    void* d_g = ex.getOrAllocCachedBuffer("w_gate", batch * inner * 4);
+    void* d_u = ex.getOrAllocCachedBuffer("w_up", batch * inner * 4);
+    void* d_s = ex.getOrAllocCachedBuffer("w_ffn_mix", batch * inner * 4);
+    REQUIRE(d_x && d_n && d_z && d_r && d_a && d_gu && d_g && d_u && d_s);
+    ex.uploadToBuffer(d_x, x.data(), x.size() * 4);
+    ex.uploadToBuffer(d_r, resid.data(), resid.size() * 4);
+    ex.uploadToBuffer(d_gu, gate_up.data(), gate_up.size() * 4);
+    REQUIRE(!ex.encodeRmsNormBatched(d_x, nw, 1e-5f, batch, cols, d_n));   // no open pass
+    REQUIRE(ex.beginForwardPassCB());
+    REQUIRE(ex.encodeRmsNormBatched(d_x, nw, 1e-5f, batch, cols, d_n));
+    REQUIRE(ex.encodeMatMulQ4_0Batched("blk.0.attn_output.weight", w, d_n, batch, rows, cols, stride, 2, d_z));
+    REQUIRE(ex.encodeAddBatched(d_z, d_r, d_a, batch * rows));
+    REQUIRE(ex.encodeGateUpSplitSiluMul(d_gu, d_g, d_u, d_s, batch, inner, rows));
+    // a second call with the same weight name reuses the device copy (getOrCacheWeight, metal_runtime.mm:3715)
+    REQUIRE(ex.encodeMatMulQ4_0Batched("blk.0.attn_output.weight", w, d_n, batch, rows, cols, stride, 2, d_z));
+    REQUIRE(ex.flushForwardPassCB());
+    std::vector<float> n(x.size()), z(resid.size()), a(resid.size()), sm(batch * inner);
+    ex.downloadFromBuffer(d_n, n.data(), n.size() * 4);
+    ex.downloadFromBuffer(d_z, z.data(), z.size() * 4);
+    ex.downloadFromBuffer(d_a, a.data(), a.size() * 4);
+    ex.downloadFromBuffer(d_s, sm.data(), sm.size() * 4);
+    FILE* out = std::fopen(argv[3], "wb");
+    REQUIRE(out != nullptr);
+    std::fwrite(n.data(), 4, n.size(), out);
+    std::fwrite(z.data(), 4, z.size(), out);
+    std::fwrite(a.data(), 4, a.size(), out);
+    std::fwrite(sm.data(), 4, sm.size(), out);
+    std::fclose(out);
+    std::puts("shim_driver: ok");
+    return 0;
+}
+
 int main(int argc, char** argv) {
+    if (argc >= 2 && std::string(argv[1]) == "ops") return run_ops(argc, argv);
     if (argc != 10) {
         std::fprintf(stderr, "usage: shim_driver in out N H KVH D P capacity n_flat\n");
         return 2;

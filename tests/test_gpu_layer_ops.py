@@ -6,12 +6,11 @@ What is compared, and how closely:
   gate / up copies          bit for bit.
   RMSNorm                   the GPU sums the squares in another order: rtol 1e-5, atol 1e-6 (fp32).
   SiLU(gate) * up           CUDA's expf against libm's (both within 2 ulp): rtol 1e-5, atol 1e-6.
-  Q4_0 / Q6_K mat-vec       the kernel keeps the block integers exact and sums in fp32, and rounds the
-                            activations to fp16. With activations that are fp16 numbers already only the
-                            order of the fp32 sum differs:   |err| <= 2e-5 * sum_c |W[r,c] x[n,c]|.
-                            With general fp32 activations each term is off by at most 2^-11 relative:
-                            |err| <= (2^-11 + 2e-5) * sum_c |W[r,c] x[n,c]|,
-                            and the error is unbiased: its rms stays below 2.5e-4 of the output's rms.
+  Q4_0 / Q6_K mat-vec       the kernel keeps the block integers exact, carries every activation as two fp16
+                            numbers (22 bits) and sums in fp32, so only the order of the fp32 sum differs
+                            from the CPU loop:   |err| <= 2e-5 * sum_c |W[r,c] x[n,c]|
+                            (the CPU's own chain of up to 5632 fp32 additions is the larger part of that),
+                            for activations that are fp16 numbers and for general fp32 ones alike.
 """
 import zlib
 
@@ -148,11 +147,10 @@ def test_quant_matvec(executor, oracle_mod, kind, batch, rows, cols):
         got = out.cpu().numpy()
         assert np.isfinite(got).all()
         err = np.abs(got.astype(np.float64) - want)
-        rel = 2e-5 if form == "fp16_numbers" else 2.0 ** -11 + 2e-5
+        rel = 2e-5
         worst = (err - rel * absdot).max()
         assert worst <= 1e-7, f"{form}: error {err.max():.3e} exceeds {rel:.1e} * sum |w x| by {worst:.3e}"
-        if form == "fp32":
-            assert np.sqrt((err ** 2).mean()) <= 2.5e-4 * np.sqrt((want.astype(np.float64) ** 2).mean())
+        assert np.sqrt((err ** 2).mean()) <= 2e-6 * np.sqrt((absdot ** 2).mean())
         out2 = torch.full((batch, rows), float("nan"), device="cuda")
         _run(executor, lambda: _encode(executor, kind, dw, dx, batch, rows, cols, stride, out2))
         assert torch.equal(out, out2), "two runs of the mat-vec differ"
@@ -175,7 +173,7 @@ def test_matvec_with_silu_mul_input_and_residual(executor, oracle_mod, batch, in
     _run(executor, lambda: executor.encodeMatMulQuantFused(0, dw, dgu, gu.shape[1], True, dres, batch, hidden, inner,
                                                            stride, out))
     err = np.abs(out.cpu().numpy().astype(np.float64) - want)
-    bound = (2.0 ** -11 + 4e-5) * absdot + 1e-6 * (1 + np.abs(want))
+    bound = 4e-5 * absdot + 1e-6 * (1 + np.abs(want))
     assert (err <= bound).all(), f"max error {err.max():.3e}"
     # the residual alone (the output projection's form), plain input
     x = rng.standard_normal((batch, inner)).astype(np.float32)
@@ -184,7 +182,7 @@ def test_matvec_with_silu_mul_input_and_residual(executor, oracle_mod, batch, in
     dx = _dev(x)
     _run(executor, lambda: executor.encodeMatMulQuantFused(0, dw, dx, inner, False, dres, batch, hidden, inner, stride, out))
     err = np.abs(out.cpu().numpy().astype(np.float64) - want)
-    assert (err <= (2.0 ** -11 + 2e-5) * absdot + 1e-6 * (1 + np.abs(want))).all()
+    assert (err <= 2e-5 * absdot + 1e-6 * (1 + np.abs(want))).all()
 
 
 def test_layer_ops_argument_rules(executor):

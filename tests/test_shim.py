@@ -98,3 +98,34 @@ def test_walker_call_order_through_the_cpp_class(oracle_mod, tmp_path, name, bui
     rows = want_k.reshape(case.capacity, case.P, case.KVH, case.D)[case.pt_flat[case.pt_off[0]:case.pt_off[1]]]
     rows = rows.reshape(-1, case.KVH, case.D)[:S0].transpose(1, 0, 2)
     assert np.array_equal(gathered.reshape(case.KVH, S0, case.D), rows)
+
+
+@pytest.mark.gpu
+def test_layer_ops_through_the_cpp_class(oracle_mod, tmp_path):
+    """RMSNorm -> Q4_0 mat-vec -> add, and the gate | up split with SiLU * up, called as the walker calls them:
+    weights as host vectors, cached on the device under the tensor's name."""
+    binary = _binary()
+    batch, rows, cols = 5, 384, 512
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((batch, cols)).astype(np.float32)
+    nw = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    w = synth.random_q4_0(rng, rows, cols)
+    resid = rng.standard_normal((batch, rows)).astype(np.float32)
+    gate_up = (rng.standard_normal((batch, rows)) * 2).astype(np.float32)
+    inp, out = tmp_path / "ops_in.bin", tmp_path / "ops_out.bin"
+    with open(inp, "wb") as f:
+        for a in (x, nw, w, resid, gate_up):
+            f.write(np.ascontiguousarray(a).tobytes())
+    res = subprocess.run([str(binary), "ops", str(inp), str(out), str(batch), str(rows), str(cols)],
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr + res.stdout
+    raw = np.fromfile(out, dtype=np.float32)
+    n, z, a, sm = np.split(raw, np.cumsum([batch * cols, batch * rows, batch * rows]))
+    n_want = oracle_mod.rms_norm_batched(x, nw, 1e-5)
+    np.testing.assert_allclose(n.reshape(batch, cols), n_want, rtol=1e-5, atol=1e-6)
+    z_want = oracle_mod.matmul_quant_batched("q4_0", w, n_want, rows, cols)
+    absdot = np.abs(n_want).astype(np.float64) @ np.abs(oracle_mod.dequant_rows("q4_0", w, rows, cols)).astype(np.float64).T
+    assert (np.abs(z.reshape(batch, rows) - z_want) <= 4e-5 * absdot + 1e-6).all()
+    assert np.array_equal(a.view(np.uint32), oracle_mod.add(z.reshape(batch, rows), resid).reshape(-1).view(np.uint32))
+    _, _, sm_want = oracle_mod.gate_up_split_silu_mul(gate_up, rows // 2)
+    np.testing.assert_allclose(sm.reshape(batch, rows // 2), sm_want, rtol=1e-5, atol=1e-6)
