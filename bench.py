@@ -26,7 +26,8 @@ the output is complete in host memory. With N > 1 (torchrun, one rank per GPU) e
 32-request batch of the same context lengths over its own pools: request sharding, no collective on
 the data path (weak scaling). `secondary` carries the other workloads: cfg3 (long contexts; with
 N > 1 split by KV sequence over the ranks through the peer-memory exchange kernel and checked
-against one GPU), cfg4 (wide GQA) and cfg5 (chunked prefill on tcgen05).
+against one GPU), cfg4 (wide GQA), cfg5 (chunked prefill on tcgen05) and model_step (the whole walker step
+of a 1.1B-shaped decoder with synthetic Q4_0 / Q6_K weights through the paged executor: tokens per second).
 
 `--impl reference` times MLcompiler's own executor-CPU attention (compiled from
 its unmodified sources into oracle/_ref, else the C port of it) on the host cores.
@@ -529,8 +530,9 @@ def run_gpu_arm(args):
     if not args.no_secondary:
         secondary = {}
         long_cfg3 = lambda e, steps, warmup: bench_more.run_cfg3(e, steps=steps, warmup=warmup, check=False, seq_len=262144)
+        model_step = lambda e, steps, warmup: bench_more.run_model(e, steps=30, warmup=warmup)
         for name, fn in (("cfg3", bench_more.run_cfg3), ("cfg3_262144_tokens", long_cfg3), ("cfg4", bench_more.run_cfg4),
-                         ("cfg5", bench_more.run_cfg5)):
+                         ("cfg5", bench_more.run_cfg5), ("model_step", model_step)):
             try:
                 r = fn(env, steps=200, warmup=5)
             except Exception as e:            # a secondary workload must not take the headline line down
@@ -538,7 +540,8 @@ def run_gpu_arm(args):
             if r is not None:
                 secondary[name] = {k: r[k] for k in r if k in ("metric", "value", "unit", "ms_per_step", "us_per_step", "scaling",
                                                                 "config", "roofline", "gpu_launches", "split_vs_one_gpu",
-                                                                "tokens_per_s", "error")}
+                                                                "tokens_per_s", "error", "ms_per_step_median_min_max",
+                                                                "bytes_per_step", "launches_per_step")}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

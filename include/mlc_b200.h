@@ -435,14 +435,24 @@ int mlc_encode_matmul_q6k_batched(mlc_ctx* ctx, const void* weights, const void*
  * MLC_DEVERR_BAD_TOKEN in the device error word. */
 int mlc_encode_embedding_q4_0(mlc_ctx* ctx, const void* table, size_t row_stride, const void* token_ids, size_t batch,
                               size_t cols, size_t vocab, void* out);
-/* The same mat-vec with its neighbours in the walker fused in (no counterpart in the reference):
- * with silu_mul_input != 0 the input row n is SiLU(in[n, c]) * in[n, cols + c] computed on load
- * (in = the gate | up buffer, in_stride >= 2 * cols: the step of batched_walker.cpp:379-394 without
- * the intermediate buffers); with residual != NULL, out = residual + W in (the add of :349 / :403).
- * quant: 0 = Q4_0, 1 = Q6_K. in_stride = floats between input rows. */
+/* The same mat-vec with its neighbours in the walker fused in (no counterpart in the reference).
+ * input_kind 0: in = fp32 [batch, in_stride], as above.
+ * input_kind 1: the input row n is SiLU(in[n, c]) * in[n, cols + c], computed on load (in = the
+ *   gate | up buffer, in_stride >= 2 * cols: the step of batched_walker.cpp:379-394 without the
+ *   intermediate buffers).
+ * input_kind 2: in holds the activations in the kernel's operand format, written by
+ *   mlc_encode_rms_norm_batched_packed (same size and shape as the fp32 buffer) - the kernel then
+ *   skips its own conversion.
+ * residual != NULL: out = residual + W in (the add of batched_walker.cpp:349 / :403).
+ * quant: 0 = Q4_0, 1 = Q6_K. in_stride = 4-byte words between input rows. */
 int mlc_encode_matmul_quant_fused(mlc_ctx* ctx, int quant, const void* weights, const void* in, size_t in_stride,
-                                  int silu_mul_input, const void* residual, size_t batch, size_t rows, size_t cols,
+                                  int input_kind, const void* residual, size_t batch, size_t rows, size_t cols,
                                   size_t row_stride, void* out);
+/* RMSNorm whose output goes to `packed` in the mat-vec kernel's operand format: per pair of columns
+ * the 32-bit words {fp16(y0), fp16(y1)} and {fp16(y0 - hi0), fp16(y1 - hi1)} - 22 bits of every value,
+ * in a buffer of the fp32 output's size. out (fp32) may be NULL. length must be divisible by 4. */
+int mlc_encode_rms_norm_batched_packed(mlc_ctx* ctx, const void* in, const void* weight, float epsilon, size_t batch,
+                                       size_t length, void* out, void* packed);
 
 /* ---- chunked (multi-token) causal paged attention ------------------------------------
  * The reference runs a paged prefill as q_len single-token decode passes

@@ -73,6 +73,7 @@ _PROTOTYPES = {
                                             _sz, _sz, _sz, _sz]),
     "mlc_encode_qkv_split_rope_scatter_planned": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _sz, _sz]),
     "mlc_encode_rms_norm_batched": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
+    "mlc_encode_rms_norm_batched_packed": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
     "mlc_encode_add_batched": (_i, [_vp, _vp, _vp, _vp, _sz]),
     "mlc_encode_silu_mul_batched": (_i, [_vp, _vp, _vp, _vp, _sz]),
     "mlc_encode_gate_up_split_silu_mul": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
@@ -459,11 +460,18 @@ class Executor:
         return self.status(self._lib.mlc_encode_matmul_q6k_batched(
             self._h, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), batch, rows, cols, row_stride, _vp(_ptr(out_buf))))
 
-    def encodeMatMulQuantFused(self, quant, weights_buf, in_buf, in_stride, silu_mul_input, residual_buf, batch, rows,
+    def encodeRmsNormBatchedPacked(self, in_buf, weight_buf, epsilon, batch, length, out_buf, packed_buf) -> bool:
+        """RMSNorm into the mat-vec kernel's operand format (input_kind 2 of encodeMatMulQuantFused); out_buf may be None."""
+        return self.status(self._lib.mlc_encode_rms_norm_batched_packed(
+            self._h, _vp(_ptr(in_buf)), _vp(_ptr(weight_buf)), epsilon, batch, length,
+            _vp(_ptr(out_buf)) if out_buf is not None else None, _vp(_ptr(packed_buf))))
+
+    def encodeMatMulQuantFused(self, quant, weights_buf, in_buf, in_stride, input_kind, residual_buf, batch, rows,
                                cols, row_stride, out_buf) -> bool:
-        """The mat-vec with SiLU(gate) * up computed on load and / or the residual add in its epilogue."""
+        """The mat-vec with its input computed on load (input_kind 1: SiLU(gate) * up; True counts as 1) or already in
+        operand format (2), and / or the residual add in its epilogue."""
         return self.status(self._lib.mlc_encode_matmul_quant_fused(
-            self._h, quant, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), in_stride, int(bool(silu_mul_input)),
+            self._h, quant, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), in_stride, int(input_kind),
             _vp(_ptr(residual_buf)) if residual_buf is not None else None, batch, rows, cols, row_stride,
             _vp(_ptr(out_buf))))
 

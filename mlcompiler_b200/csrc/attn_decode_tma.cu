@@ -1270,7 +1270,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap* tmK, const CUtens
         return true;
     };
 
-    // Consume side of round 0: counts and the first 16 piece descriptors (half a descriptor per lane),
+    // Consume side of the first deal: counts and the first 16 piece descriptors (half a descriptor per lane),
     // read together with the issue side's loads.
     uint32_t c_rank, c_layer;
     round_item(0, c_rank, c_layer);

@@ -272,8 +272,12 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
         const LayerWeights& w = m.layers[L];
         void* kp = storage->k_buffer(L);
         void* vp = storage->v_buffer(L);
-        ok = mlc_encode_rms_norm_batched(ctx, residual, w.attn_norm, eps, N, hidden, norm_o, nullptr) == MLC_OK &&
-             mlc_encode_matmul_q4_0_batched(ctx, w.attn_qkv, norm_o, N, qkv_rows, hidden, row_h, qkv) == MLC_OK;
+        // fused order: the norms write the mat-vec's operand format directly (the mat-vec then converts nothing)
+        ok = fused ? mlc_encode_rms_norm_batched_packed(ctx, residual, w.attn_norm, eps, N, hidden, nullptr, norm_o) == MLC_OK &&
+                         mlc_encode_matmul_quant_fused(ctx, 0, w.attn_qkv, norm_o, hidden, 2, nullptr, N, qkv_rows, hidden, row_h,
+                                                       qkv) == MLC_OK
+                   : mlc_encode_rms_norm_batched(ctx, residual, w.attn_norm, eps, N, hidden, norm_o, nullptr) == MLC_OK &&
+                         mlc_encode_matmul_q4_0_batched(ctx, w.attn_qkv, norm_o, N, qkv_rows, hidden, row_h, qkv) == MLC_OK;
         if (!ok) break;
         if (fused) {
             ok = mlc_encode_qkv_split_rope_scatter_planned(ctx, plan, qkv, q, MLC_F16, kp, vp, cos_t, sin_t, qkv_rows,
@@ -281,8 +285,9 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                  mlc_encode_paged_flash_attention_planned(ctx, plan, q, kp, vp, attn_mix, scale, MLC_F16, MLC_F32) == MLC_OK &&
                  mlc_encode_matmul_quant_fused(ctx, 0, w.attn_output, attn_mix, hidden, 0, residual, N, hidden, hidden,
                                                row_h, resid1) == MLC_OK &&
-                 mlc_encode_rms_norm_batched(ctx, resid1, w.ffn_norm, eps, N, hidden, norm_o, nullptr) == MLC_OK &&
-                 mlc_encode_matmul_q4_0_batched(ctx, w.ffn_gate_up, norm_o, N, 2 * inner, hidden, row_h, gate_up) == MLC_OK &&
+                 mlc_encode_rms_norm_batched_packed(ctx, resid1, w.ffn_norm, eps, N, hidden, nullptr, norm_o) == MLC_OK &&
+                 mlc_encode_matmul_quant_fused(ctx, 0, w.ffn_gate_up, norm_o, hidden, 2, nullptr, N, 2 * inner, hidden, row_h,
+                                               gate_up) == MLC_OK &&
                  mlc_encode_matmul_quant_fused(ctx, 0, w.ffn_down, gate_up, 2 * inner, 1, resid1, N, hidden, inner, row_i,
                                                residual) == MLC_OK;
         } else {
@@ -304,11 +309,18 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                  mlc_encode_add_batched(ctx, resid1, ffn_down, residual, N * hidden) == MLC_OK;
         }
     }
-    ok = ok && mlc_encode_rms_norm_batched(ctx, residual, m.output_norm, eps, N, hidden, final_n, nullptr) == MLC_OK;
-    if (ok) {
-        ok = m.lm_head_quant == 1
-                 ? mlc_encode_matmul_q6k_batched(ctx, m.lm_head, final_n, N, vocab, hidden, hidden / 256 * 210, logits) == MLC_OK
-                 : mlc_encode_matmul_q4_0_batched(ctx, m.lm_head, final_n, N, vocab, hidden, row_h, logits) == MLC_OK;
+    const size_t head_stride = m.lm_head_quant == 1 ? hidden / 256 * 210 : row_h;
+    if (fused) {
+        ok = ok && mlc_encode_rms_norm_batched_packed(ctx, residual, m.output_norm, eps, N, hidden, nullptr, final_n) == MLC_OK &&
+             mlc_encode_matmul_quant_fused(ctx, m.lm_head_quant == 1 ? 1 : 0, m.lm_head, final_n, hidden, 2, nullptr, N, vocab,
+                                           hidden, head_stride, logits) == MLC_OK;
+    } else {
+        ok = ok && mlc_encode_rms_norm_batched(ctx, residual, m.output_norm, eps, N, hidden, final_n, nullptr) == MLC_OK;
+        if (ok) {
+            ok = m.lm_head_quant == 1
+                     ? mlc_encode_matmul_q6k_batched(ctx, m.lm_head, final_n, N, vocab, hidden, head_stride, logits) == MLC_OK
+                     : mlc_encode_matmul_q4_0_batched(ctx, m.lm_head, final_n, N, vocab, hidden, row_h, logits) == MLC_OK;
+        }
     }
     *logits_dev = logits;
     return ok;

@@ -24,6 +24,7 @@
 #include <cstdlib>
 
 #include "ctx.hpp"
+#include "tcgen05_util.hpp"
 
 namespace mlcb {
 
@@ -80,11 +81,11 @@ __device__ __forceinline__ void dependent_launch_gate() {
 // operator_backend.cpp:186-204, so that only the order of the sum differs from the CPU code.
 __global__ void __launch_bounds__(256) rms_norm_batched_kernel(const float* __restrict__ in, const float* __restrict__ w,
                                                                float eps, uint32_t length, float* __restrict__ out,
-                                                               __half* __restrict__ out16) {
+                                                               __half* __restrict__ out16, uint32_t* __restrict__ packed) {
     __shared__ float part[8];
     dependent_launch_gate();
     const float* x = in + static_cast<size_t>(blockIdx.x) * length;
-    float* y = out + static_cast<size_t>(blockIdx.x) * length;
+    float* y = out ? out + static_cast<size_t>(blockIdx.x) * length : nullptr;
     float s = 0.0f;
     const bool vec = (length & 3) == 0;
     if (vec) {
@@ -113,7 +114,15 @@ __global__ void __launch_bounds__(256) rms_norm_batched_kernel(const float* __re
             r.y = __fmul_rn(__fmul_rn(v.y, inv), g.y);
             r.z = __fmul_rn(__fmul_rn(v.z, inv), g.z);
             r.w = __fmul_rn(__fmul_rn(v.w, inv), g.w);
-            *reinterpret_cast<float4*>(y + i) = r;
+            if (y) *reinterpret_cast<float4*>(y + i) = r;
+            if (packed) {   // the mat-vec kernel's operand format: {hi0, hi1}, {lo0, lo1} per pair of columns
+                const __half2 h01 = __floats2half2_rn(r.x, r.y), h23 = __floats2half2_rn(r.z, r.w);
+                const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                const __half2 l01 = __floats2half2_rn(r.x - f01.x, r.y - f01.y), l23 = __floats2half2_rn(r.z - f23.x, r.w - f23.y);
+                *reinterpret_cast<uint4*>(packed + static_cast<size_t>(blockIdx.x) * length + i) =
+                    make_uint4(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&l01),
+                               *reinterpret_cast<const uint32_t*>(&h23), *reinterpret_cast<const uint32_t*>(&l23));
+            }
             if (y16) {
                 *reinterpret_cast<__half2*>(y16 + i) = __floats2half2_rn(r.x, r.y);
                 *reinterpret_cast<__half2*>(y16 + i + 2) = __floats2half2_rn(r.z, r.w);
@@ -122,7 +131,7 @@ __global__ void __launch_bounds__(256) rms_norm_batched_kernel(const float* __re
     } else {
         for (uint32_t i = threadIdx.x; i < length; i += blockDim.x) {
             const float r = __fmul_rn(__fmul_rn(x[i], inv), w[i]);
-            y[i] = r;
+            if (y) y[i] = r;
             if (y16) y16[i] = __float2half_rn(r);
         }
     }
@@ -208,7 +217,7 @@ constexpr int kXPadWords = 4;       // words of padding per activation row in sh
 constexpr int kMvStages = 2;        // chunks in flight per CTA
 
 enum : int { kQ4_0 = 0, kQ6_K = 1 };
-enum : int { kInPlain = 0, kInSiluMul = 1 };
+enum : int { kInPlain = 0, kInSiluMul = 1, kInPacked = 2 };   // kInPacked: the input already holds {hi, lo} words
 
 template <int QT> struct QuantFormat;
 template <> struct QuantFormat<kQ4_0> {
@@ -238,8 +247,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void cluster_sync_all() {
+// The first cluster barrier publishes every CTA's partial sums (release / acquire); the second only keeps a
+// CTA's shared memory alive until its readers are done and orders nothing.
+__device__ __forceinline__ void cluster_sync_publish() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_sync_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
 }
 
 // 16 bytes at `local_smem_addr` of CTA `rank` of this cluster.
@@ -363,7 +377,13 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
         // Activations in place, two columns at a time: fp32 (x0, x1) -> the words {hi0, hi1} and {lo0, lo1} with
         // hi = fp16(x), lo = fp16(x - hi): 22 bits of x, so the products lose nothing that fp32 keeps. Rows past
         // the batch become zero.
-        {
+        if (IN == kInPacked) {
+            // the words came in ready; only the rows past the batch need their zeros
+            const uint32_t cq = tid & 63;
+            if (cq < (ncols >> 2))
+                for (uint32_t n = p.batch + (tid >> 6); n < kXRows; n += kMvThreads / 64)
+                    *reinterpret_cast<uint4*>(xw + n * x_pitch + cq * 4) = make_uint4(0u, 0u, 0u, 0u);
+        } else {
             const uint32_t cq = tid & 63;
             if (cq < (ncols >> 2)) {
 #pragma unroll 2
@@ -511,7 +531,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
             const uint32_t bn = n * 8 + 2 * t + (e & 1);
             red[(kh * kXRows + bn) * kRedPitch + lrow] = acc[n][e];
         }
-    if (S > 1) cluster_sync_all(); else __syncthreads();
+    if (S > 1) cluster_sync_publish(); else __syncthreads();
     const uint32_t rs4 = (kMvRows / S) >> 2;                 // float4 per batch row in this CTA's share
     const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
     const bool vec_out = (p.rows & 3u) == 0;
@@ -543,7 +563,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 if (row0 + lrow + e < p.rows) p.out[o + e] = p.residual ? __fadd_rn(p.residual[o + e], vals[e]) : vals[e];
         }
     }
-    if (S > 1) cluster_sync_all();
+    if (S > 1) cluster_sync_relaxed();
 }
 
 static uint32_t weight_pitch(uint32_t chunk_bytes) {
@@ -593,6 +613,484 @@ static int launch_matvec(mlc_ctx* ctx, MatVecParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The same mat-vec on the fifth-generation tensor cores (batch <= 32, 16-byte aligned rows)
+// ---------------------------------------------------------------------------------------------------
+// mma.sync runs at a fraction of the tensor cores' rate on this GPU (one m16n8k16 per 8 cycles and SM, about
+// 144 TFLOP/s in all), and with 2 x 32 multiply-adds per weight (hi and lo activations, 32 requests) the kernel
+// above is bound by it. Here the products run as tcgen05.mma with the accumulator in tensor memory:
+//   A = 128 weight rows x 64 columns, the block integers as exact fp16 values, written by 8 dequantising warps
+//       into shared memory in the K-major 128-byte-swizzle layout (4 slots in flight);
+//   B = the chunk's activations, hi and lo fp16 planes [32 requests x 256 columns] in the same layout;
+//   D = one 128 x 32 fp32 tile of tensor memory per scale group (a Q4_0 block of 32 columns: 2 k-steps x
+//       {hi, lo} = 4 MMAs; a Q6_K group of 16 columns: 2 MMAs), 8 tiles in flight;
+//   4 epilogue warps (thread = weight row) read each finished tile (tcgen05.ld) and add it, times the row's
+//   fp32 scale of that group, to 32 accumulators in registers - the same arithmetic as above, group by group.
+// One warp issues the MMAs. Rings are handed over with mbarriers (every wait bounded: a wait that runs out
+// sets the device error word and the roles wind down). Column slices are CTAs of a cluster and add up through
+// distributed shared memory as above. A CTA owns one 128-row tile.
+constexpr int kTcRows = 128;
+constexpr int kTcN = 32;            // requests per MMA (the batch, padded)
+constexpr int kTcChunk = 256;       // columns per chunk: 4 atoms of 64
+constexpr int kTcRawStages = 3;
+constexpr int kTcSlots = 4;         // A atoms in flight
+constexpr int kTcBufs = 8;          // D tiles in flight (32 columns of tensor memory each)
+constexpr int kTcDequantThreads = 256;
+constexpr int kTcThreads = 128 + kTcDequantThreads + 32;   // epilogue | dequantise + load | MMA issue
+constexpr uint32_t kTcAtomABytes = kTcRows * 128;          // 16 KiB
+constexpr uint32_t kTcAtomBBytes = kTcN * 128;             // 4 KiB
+constexpr uint32_t kTcBPlaneBytes = 4 * kTcAtomBBytes;     // one plane (hi or lo) of a chunk
+
+struct TcBars {
+    uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages], raw_done[kTcRawStages];
+    uint64_t a_full[kTcSlots], a_empty[kTcSlots];
+    uint64_t d_full[kTcBufs], d_empty[kTcBufs];
+    uint64_t b_full[2], b_empty[2];
+    uint32_t tmem_slot, abort;
+};
+
+struct TcParams {
+    const uint8_t* w;
+    const float* x;          // fp32 [batch, x_stride] (kInPlain / kInSiluMul) or the packed words (kInPacked)
+    const float* residual;
+    float* out;
+    uint32_t* err;
+    size_t row_stride;
+    uint32_t batch, rows, cols, x_stride;
+    uint32_t slice_cols, slices, w_pitch;
+};
+
+template <int QT, int IN>
+__global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcParams p) {
+    using F = QuantFormat<QT>;
+    constexpr int kGroupCols = QT == kQ4_0 ? 32 : 16;            // columns that share one fp32 scale
+    constexpr int kGroupsPerAtom = 64 / kGroupCols;
+    constexpr int kStepsPerGroup = kGroupCols / 16;
+    extern __shared__ __align__(1024) uint8_t smem_unaligned[];
+    // the swizzled tiles need 1024-byte alignment: the launch asks for 1 KiB more than the layout takes
+    uint8_t* smem = smem_unaligned + ((1024u - (tc::smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    const uint32_t base = tc::smem_u32(smem);
+    const uint32_t sB = base;                                    // two buffers of {hi plane, lo plane}
+    const uint32_t sA = sB + 4 * kTcBPlaneBytes;                 // kTcSlots atoms
+    uint8_t* raw = smem + 4 * kTcBPlaneBytes + kTcSlots * kTcAtomABytes;
+    const uint32_t raw_bytes = kTcRows * p.w_pitch;
+    TcBars& bars = *reinterpret_cast<TcBars*>(raw + kTcRawStages * raw_bytes);
+    float* red = reinterpret_cast<float*>(raw);                  // [32][128 + 4], over the raw ring once it is done
+
+    const uint32_t S = p.slices;
+    const uint32_t tile = blockIdx.x / S, slice = blockIdx.x - tile * S;
+    const uint32_t row0 = tile * kTcRows;
+    const uint32_t c_begin = min(slice * p.slice_cols, p.cols), c_end = min(c_begin + p.slice_cols, p.cols);
+    const uint32_t n_chunks = (c_end - c_begin + kTcChunk - 1) / kTcChunk;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int i = 0; i < kTcRawStages; ++i) {
+            tc::mbar_init(tc::smem_u32(&bars.raw_full[i]), kTcDequantThreads);
+            tc::mbar_init(tc::smem_u32(&bars.raw_empty[i]), 128);
+            tc::mbar_init(tc::smem_u32(&bars.raw_done[i]), kTcDequantThreads);
+        }
+        for (int i = 0; i < kTcSlots; ++i) {
+            tc::mbar_init(tc::smem_u32(&bars.a_full[i]), kTcDequantThreads);
+            tc::mbar_init(tc::smem_u32(&bars.a_empty[i]), 1);
+        }
+        for (int i = 0; i < kTcBufs; ++i) {
+            tc::mbar_init(tc::smem_u32(&bars.d_full[i]), 1);
+            tc::mbar_init(tc::smem_u32(&bars.d_empty[i]), 128);
+        }
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(tc::smem_u32(&bars.b_full[i]), kTcDequantThreads);
+            tc::mbar_init(tc::smem_u32(&bars.b_empty[i]), 1);
+        }
+        bars.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // rows of B past the batch stay zero for the whole kernel
+    for (uint32_t i = tid; i < 4 * kTcBPlaneBytes / 16; i += kTcThreads) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (warp == 12) tc::tmem_alloc(tc::smem_u32(&bars.tmem_slot), kTcBufs * kTcN);
+    tc::fence_proxy_async_smem();
+    tc::fence_before();
+    __syncthreads();
+    tc::fence_after();
+    const uint32_t tmem = bars.tmem_slot;
+
+    // A wait that ran out: timeout bit plus where (0x6x = this kernel: 0 dequantise, 1 MMA, 2 epilogue) and the chunk.
+    auto give_up = [&](uint32_t where, uint32_t chunk) {
+        bars.abort = 1;
+        if (atomicCAS(p.err, 0u, MLC_DEVERR_WAIT_TIMEOUT | ((0x60u + where) << 8) | (chunk << 16)) != 0u)
+            atomicOr(p.err, MLC_DEVERR_WAIT_TIMEOUT);
+    };
+
+    float acc[kTcN];
+#pragma unroll
+    for (int n = 0; n < kTcN; ++n) acc[n] = 0.0f;
+
+    if (warp >= 4 && warp < 12) {
+        // ---------------- weight loads, activation conversion, dequantisation ----------------
+        const uint32_t dt = tid - 128;                     // 0..255
+        const uint32_t drow = dt & 127, dhalf = dt >> 7;   // this thread's weight row, and which 32 columns of an atom
+        uint32_t a_off[4];                                 // its four 16-byte chunks inside an A atom
+#pragma unroll
+        for (int c = 0; c < 4; ++c) a_off[c] = tc::sw128_offset(drow, dhalf * 32 + c * 8);
+        auto issue_raw = [&](uint32_t chunk) {
+            if (chunk < n_chunks) {
+                uint8_t* ws = raw + (chunk % kTcRawStages) * raw_bytes;
+                const uint32_t c0 = c_begin + chunk * kTcChunk;
+                const uint32_t ncols = min(static_cast<uint32_t>(kTcChunk), c_end - c0);
+                const uint32_t b0 = c0 / F::kBlockWeights * F::kBlockBytes;
+                const uint32_t b1 = b0 + ncols / F::kBlockWeights * F::kBlockBytes;
+                const uint32_t a0 = b0 & ~15u, nvec = (b1 - a0 + 15) >> 4;
+                const uint32_t v = dt & 15;
+                if (v < nvec) {
+#pragma unroll
+                    for (uint32_t r = dt >> 4; r < kTcRows; r += kTcDequantThreads / 16) {
+                        const uint32_t row = min(row0 + r, p.rows - 1);
+                        const uint32_t dst = tc::smem_u32(ws + r * p.w_pitch + v * 16);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                                     "l"(p.w + static_cast<size_t>(row) * p.row_stride + a0 + v * 16) : "memory");
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // this thread's share of a chunk's activations: 8 x 4 columns (request n = e * 4 + dt / 64, columns 4 (dt % 64) ..)
+        constexpr int kXU = IN == kInSiluMul ? 8 : 1;
+        float4 xv[8], xu[kXU];
+        auto load_x = [&](uint32_t chunk) {
+            const uint32_t c0 = c_begin + chunk * kTcChunk;
+            const uint32_t ncols = chunk < n_chunks ? min(static_cast<uint32_t>(kTcChunk), c_end - c0) : 0u;
+            const uint32_t cq = dt & 63;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t n = e * 4 + (dt >> 6);
+                xv[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (IN == kInSiluMul) xu[e % kXU] = xv[e];
+                if (n < p.batch && cq * 4 < ncols) {
+                    const float* src = p.x + static_cast<size_t>(n) * p.x_stride + c0 + cq * 4;
+                    xv[e] = __ldcg(reinterpret_cast<const float4*>(src));
+                    if (IN == kInSiluMul) xu[e % kXU] = __ldcg(reinterpret_cast<const float4*>(src + p.cols));
+                }
+            }
+        };
+        uint32_t x_off[8];                                 // where its 8 float4 of a chunk go in a B plane
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            x_off[e] = ((dt & 63) >> 4) * kTcAtomBBytes + tc::sw128_offset(e * 4 + (dt >> 6), ((dt & 63) & 15) * 4);
+        auto store_x = [&](uint32_t bb) {
+            uint8_t* bdst = smem + bb * 2 * kTcBPlaneBytes;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t n = e * 4 + (dt >> 6);
+                uint32_t h01, h23, l01, l23;
+                if (IN == kInPacked) {   // {hi0, hi1}, {lo0, lo1}, {hi2, hi3}, {lo2, lo3}
+                    h01 = __float_as_uint(xv[e].x); l01 = __float_as_uint(xv[e].y);
+                    h23 = __float_as_uint(xv[e].z); l23 = __float_as_uint(xv[e].w);
+                } else {
+                    float4 w = xv[e];
+                    if (IN == kInSiluMul) {
+                        const float4 u = xu[e % kXU];
+                        w = make_float4(silu_mul(w.x, u.x), silu_mul(w.y, u.y), silu_mul(w.z, u.z), silu_mul(w.w, u.w));
+                    }
+                    const __half2 a = __floats2half2_rn(w.x, w.y), b = __floats2half2_rn(w.z, w.w);
+                    const float2 fa = __half22float2(a), fb = __half22float2(b);
+                    const __half2 la = __floats2half2_rn(w.x - fa.x, w.y - fa.y), lb = __floats2half2_rn(w.z - fb.x, w.w - fb.y);
+                    h01 = *reinterpret_cast<const uint32_t*>(&a); h23 = *reinterpret_cast<const uint32_t*>(&b);
+                    l01 = *reinterpret_cast<const uint32_t*>(&la); l23 = *reinterpret_cast<const uint32_t*>(&lb);
+                }
+                const uint32_t off = x_off[e];
+                if (n < p.batch) {
+                    *reinterpret_cast<uint2*>(bdst + off) = make_uint2(h01, h23);
+                    *reinterpret_cast<uint2*>(bdst + kTcBPlaneBytes + off) = make_uint2(l01, l23);
+                }
+            }
+        };
+
+        // Weights never change: their first chunks are on their way before the kernel in front of this one has
+        // finished; its output - the activations - is touched only after the wait.
+        for (uint32_t c = 0; c < kTcRawStages; ++c) issue_raw(c);
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        load_x(0);
+        if (n_chunks > 0) {
+            store_x(0);
+            tc::fence_proxy_async_smem();
+            tc::mbar_arrive(tc::smem_u32(&bars.b_full[0]));
+        }
+        load_x(1);
+
+        uint32_t atom_count = 0;
+        bool ok = true;
+        for (uint32_t chunk = 0; chunk < n_chunks && ok; ++chunk) {
+            const uint32_t stage = chunk % kTcRawStages;
+            const uint32_t c0 = c_begin + chunk * kTcChunk;
+            const uint32_t ncols = min(static_cast<uint32_t>(kTcChunk), c_end - c0);
+            asm volatile("cp.async.wait_group %0;" ::"n"(kTcRawStages - 1) : "memory");
+            tc::mbar_arrive(tc::smem_u32(&bars.raw_full[stage]));
+            if (!tc::mbar_wait_bounded(tc::smem_u32(&bars.raw_full[stage]), (chunk / kTcRawStages) & 1u)) { give_up(0, chunk); ok = false; break; }
+            const uint8_t* wrow = raw + stage * raw_bytes + drow * p.w_pitch + ((c0 / F::kBlockWeights * F::kBlockBytes) & 15u);
+            const uint32_t n_atoms = (ncols + 63) >> 6;
+            for (uint32_t a = 0; a < n_atoms; ++a, ++atom_count) {
+                const uint32_t slot = atom_count % kTcSlots;
+                if (atom_count >= kTcSlots &&
+                    !tc::mbar_wait_bounded(tc::smem_u32(&bars.a_empty[slot]), ((atom_count / kTcSlots) - 1) & 1u)) { give_up(0, chunk); ok = false; break; }
+                uint8_t* dstA = smem + 4 * kTcBPlaneBytes + slot * kTcAtomABytes;
+                const uint32_t col = a * 64 + dhalf * 32;          // this thread's 32 columns inside the chunk
+                uint4 out4[4];
+                if (col < ncols) {
+                    if (QT == kQ4_0) {
+                        // 0x6400 | n is the fp16 number 1024 + n, 0x6400 | (n << 4) is 1024 + 16 n: one fused
+                        // multiply-add takes either to n - 8 exactly
+                        const uint8_t* blk = wrow + (col >> 5) * 18 + 2;
+                        const __half2 m1 = __floats2half2_rn(1.0f, 1.0f), a1 = __floats2half2_rn(-1032.0f, -1032.0f);
+                        const __half2 m2 = __floats2half2_rn(0.0625f, 0.0625f), a2 = __floats2half2_rn(-72.0f, -72.0f);
+                        uint32_t lo[8], hi[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const uint32_t v = __byte_perm(*reinterpret_cast<const uint16_t*>(blk + 2 * i), 0u, 0x4140);
+                            const uint32_t l = (v & 0x000F000Fu) | 0x64006400u, h = (v & 0x00F000F0u) | 0x64006400u;
+                            const __half2 rl = __hfma2(*reinterpret_cast<const __half2*>(&l), m1, a1);
+                            const __half2 rh = __hfma2(*reinterpret_cast<const __half2*>(&h), m2, a2);
+                            lo[i] = *reinterpret_cast<const uint32_t*>(&rl);
+                            hi[i] = *reinterpret_cast<const uint32_t*>(&rh);
+                        }
+                        out4[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);   // columns 0..7: low nibbles of bytes 0..7
+                        out4[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                        out4[2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);   // columns 16..23: their high nibbles
+                        out4[3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                    } else {
+                        // 32 columns = two 16-weight groups jj, jj + 1 of the super-block (quantization.cpp:1469-1499)
+                        const uint8_t* sb = wrow + (col >> 8) * 210;
+                        const uint32_t jj = (col & 255) >> 4;
+                        const __half2 bias = __floats2half2_rn(1056.0f, 1056.0f);
+#pragma unroll
+                        for (int gq = 0; gq < 2; ++gq) {
+                            const uint32_t j = jj + gq, h = j >> 3, quarter = (j & 7) >> 1, sub = j & 1;
+                            const uint32_t ql_off = 64 * h + ((quarter & 1) ? 32 : 0) + 16 * sub, qh_off = 128 + 32 * h + 16 * sub;
+                            const uint32_t nib_shift = (quarter >> 1) * 4, hi_shift = quarter * 2;
+                            uint32_t wv[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const uint32_t l2 = *reinterpret_cast<const uint16_t*>(sb + ql_off + 2 * i);
+                                const uint32_t h2 = *reinterpret_cast<const uint16_t*>(sb + qh_off + 2 * i);
+                                const uint32_t q2 = ((l2 >> nib_shift) & 0x0F0Fu) | (((h2 >> hi_shift) & 0x0303u) << 4);
+                                const uint32_t hw = __byte_perm(q2, 0u, 0x4140) | 0x64006400u;
+                                const __half2 rr = __hsub2(*reinterpret_cast<const __half2*>(&hw), bias);
+                                wv[i] = *reinterpret_cast<const uint32_t*>(&rr);
+                            }
+                            out4[2 * gq] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                            out4[2 * gq + 1] = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dstA + a_off[c]) = out4[c];
+                }
+                tc::fence_proxy_async_smem();
+                tc::mbar_arrive(tc::smem_u32(&bars.a_full[slot]));
+            }
+            if (!ok) break;
+            // the next chunk's activations into the other B buffer, free once the MMAs of the chunk before this one have run
+            if (chunk + 1 < n_chunks) {
+                const uint32_t nb = (chunk + 1) & 1u;
+                if (chunk >= 1 && !tc::mbar_wait_bounded(tc::smem_u32(&bars.b_empty[nb]), (((chunk + 1) >> 1) - 1) & 1u)) { give_up(0, chunk); ok = false; break; }
+                store_x(nb);
+                tc::fence_proxy_async_smem();
+                tc::mbar_arrive(tc::smem_u32(&bars.b_full[nb]));
+                load_x(chunk + 2);
+            }
+            // refill this raw stage once every dequantising thread is done with it and the epilogue has its scales
+            tc::mbar_arrive(tc::smem_u32(&bars.raw_done[stage]));
+            if (chunk + kTcRawStages < n_chunks &&
+                !(tc::mbar_wait_bounded(tc::smem_u32(&bars.raw_done[stage]), (chunk / kTcRawStages) & 1u) &&
+                  tc::mbar_wait_bounded(tc::smem_u32(&bars.raw_empty[stage]), (chunk / kTcRawStages) & 1u))) { give_up(0, chunk); ok = false; break; }
+            issue_raw(chunk + kTcRawStages);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (warp == 12) {
+        // ---------------- MMA issue: the whole warp walks the loop, one elected lane issues ----------------
+        constexpr uint32_t idesc = tc::idesc_f16_kmajor(kTcRows, kTcN);
+        const uint64_t desc = tc::smem_desc_sw128(0, 16, 1024);
+        uint32_t atom_count = 0, group_count = 0;
+        bool ok = true;
+        for (uint32_t chunk = 0; chunk < n_chunks && ok; ++chunk) {
+            const uint32_t c0 = c_begin + chunk * kTcChunk;
+            const uint32_t ncols = min(static_cast<uint32_t>(kTcChunk), c_end - c0);
+            ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.b_full[chunk & 1u]), (chunk >> 1) & 1u);
+            if (!ok) { give_up(1, chunk); break; }
+            const uint32_t n_atoms = (ncols + 63) >> 6;
+            for (uint32_t a = 0; a < n_atoms && ok; ++a, ++atom_count) {
+                const uint32_t slot = atom_count % kTcSlots;
+                ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.a_full[slot]), (atom_count / kTcSlots) & 1u);
+                if (!ok) { give_up(1, chunk); break; }
+                tc::fence_after();
+                const uint32_t groups = min(static_cast<uint32_t>(kGroupsPerAtom), (ncols - a * 64 + kGroupCols - 1) / kGroupCols);
+                for (uint32_t gi = 0; gi < groups; ++gi, ++group_count) {
+                    const uint32_t buf = group_count % kTcBufs;
+                    if (group_count >= kTcBufs) {
+                        ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.d_empty[buf]), ((group_count / kTcBufs) - 1) & 1u);
+                        if (!ok) { give_up(1, chunk); break; }
+                        tc::fence_after();
+                    }
+                    if (tc::elect_one()) {
+                        const uint32_t d = tmem + buf * kTcN;
+#pragma unroll
+                        for (int plane = 1; plane >= 0; --plane) {   // the small terms first: lo plane, then hi
+#pragma unroll
+                            for (int ks = 0; ks < kStepsPerGroup; ++ks) {
+                                const uint32_t kstep = gi * kStepsPerGroup + ks;   // 16-column step inside the atom
+                                const uint32_t a_addr = sA + slot * kTcAtomABytes + kstep * 32;
+                                const uint32_t b_addr = sB + ((chunk & 1u) * 2 + plane) * kTcBPlaneBytes + a * kTcAtomBBytes + kstep * 32;
+                                tc::mma_f16(d, desc | (a_addr >> 4), desc | (b_addr >> 4), idesc, (plane == 1 && ks == 0) ? 0u : 1u);
+                            }
+                        }
+                        tc::commit(tc::smem_u32(&bars.d_full[buf]));
+                    }
+                    __syncwarp();
+                }
+                if (ok && tc::elect_one()) tc::commit(tc::smem_u32(&bars.a_empty[slot]));
+                __syncwarp();
+            }
+            if (ok && tc::elect_one()) tc::commit(tc::smem_u32(&bars.b_empty[chunk & 1u]));
+            __syncwarp();
+        }
+        // the last commits' arrivals land in this CTA's shared memory: see them before it is given up
+        if (ok && n_chunks > 0) {
+            const uint32_t last = n_chunks - 1;
+            if (!tc::mbar_wait_bounded(tc::smem_u32(&bars.b_empty[last & 1u]), (last >> 1) & 1u)) give_up(1, last);
+        }
+    } else if (warp < 4) {
+        // ---------------- epilogue: thread = weight row, TMEM lane = tid ----------------
+        const uint32_t lane_base = (warp * 32u) << 16;
+        uint32_t group_count = 0;
+        bool ok = true;
+        for (uint32_t chunk = 0; chunk < n_chunks && ok; ++chunk) {
+            const uint32_t stage = chunk % kTcRawStages;
+            const uint32_t c0 = c_begin + chunk * kTcChunk;
+            const uint32_t ncols = min(static_cast<uint32_t>(kTcChunk), c_end - c0);
+            ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.raw_full[stage]), (chunk / kTcRawStages) & 1u);
+            if (!__all_sync(0xffffffffu, ok)) { ok = false; give_up(2, chunk); break; }
+            // this row's scales of the chunk
+            const uint8_t* wrow = raw + stage * raw_bytes + tid * p.w_pitch + ((c0 / F::kBlockWeights * F::kBlockBytes) & 15u);
+            constexpr int kGroupsPerChunk = kTcChunk / kGroupCols;
+            float scale[kGroupsPerChunk];
+            const uint32_t n_groups = ncols / kGroupCols;
+            if (QT == kQ4_0) {
+#pragma unroll
+                for (int i = 0; i < kGroupsPerChunk; ++i)
+                    scale[i] = static_cast<uint32_t>(i) < n_groups ? half_bits_to_float(*reinterpret_cast<const uint16_t*>(wrow + i * 18)) : 0.0f;
+            } else {
+                const float d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(wrow + 208));
+#pragma unroll
+                for (int i = 0; i < kGroupsPerChunk; ++i)
+                    scale[i] = static_cast<uint32_t>(i) < n_groups ? __fmul_rn(d, static_cast<float>(static_cast<int8_t>(wrow[192 + i]))) : 0.0f;
+            }
+            tc::mbar_arrive(tc::smem_u32(&bars.raw_empty[stage]));
+#pragma unroll
+            for (int gi = 0; gi < kGroupsPerChunk; ++gi) {
+                if (static_cast<uint32_t>(gi) >= n_groups || !ok) break;
+                const uint32_t buf = group_count % kTcBufs;
+                ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.d_full[buf]), (group_count / kTcBufs) & 1u);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; give_up(2, chunk); break; }
+                tc::fence_after();
+                uint32_t v[32];
+                tc::tmem_ld32(tmem + lane_base + buf * kTcN, v);
+                tc::tmem_wait_ld();
+                tc::fence_before();
+                tc::mbar_arrive(tc::smem_u32(&bars.d_empty[buf]));
+                const float sc = scale[gi];
+#pragma unroll
+                for (int n = 0; n < kTcN; ++n) acc[n] = fmaf(sc, __uint_as_float(v[n]), acc[n]);
+                ++group_count;
+            }
+        }
+    }
+
+    // ---------------- every role is done: partial tile to shared memory, tensor memory back ----------------
+    tc::fence_before();
+    __syncthreads();
+    tc::fence_after();
+    if (warp == 12) tc::tmem_dealloc(tmem, kTcBufs * kTcN);
+    constexpr uint32_t kPitch = kTcRows + 4;
+    if (warp < 4) {
+#pragma unroll
+        for (int n = 0; n < kTcN; ++n) red[n * kPitch + tid] = bars.abort ? 0.0f : acc[n];
+    }
+    if (S > 1) cluster_sync_publish(); else __syncthreads();
+    const uint32_t r4n = kTcRows >> 2, items = p.batch * r4n;
+    const uint32_t red_base = tc::smem_u32(red);
+    const bool vec_out = (p.rows & 3u) == 0;
+    for (uint32_t i = slice + S * tid; i < items; i += S * kTcThreads) {
+        const uint32_t bn = i / r4n, lrow = (i - bn * r4n) << 2;
+        if (row0 + lrow >= p.rows) continue;
+        const uint32_t addr = red_base + (bn * kPitch + lrow) * 4;
+        float4 sum = ld_cluster_f4(addr, 0);
+        for (uint32_t k = 1; k < S; ++k) {
+            const float4 v = ld_cluster_f4(addr, k);
+            sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
+        }
+        const size_t o = static_cast<size_t>(bn) * p.rows + row0 + lrow;
+        if (vec_out) {
+            if (p.residual) {
+                const float4 r = *reinterpret_cast<const float4*>(p.residual + o);
+                sum = make_float4(__fadd_rn(r.x, sum.x), __fadd_rn(r.y, sum.y), __fadd_rn(r.z, sum.z), __fadd_rn(r.w, sum.w));
+            }
+            *reinterpret_cast<float4*>(p.out + o) = sum;
+        } else {
+            const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (row0 + lrow + e < p.rows) p.out[o + e] = p.residual ? __fadd_rn(p.residual[o + e], vals[e]) : vals[e];
+        }
+    }
+    if (S > 1) cluster_sync_relaxed();
+}
+
+// Which kernel: MLC_B200_MATVEC=tcgen05 in the environment selects the tensor-memory kernel for batches of up to
+// 32 requests; the default is the mma.sync kernel, which is the faster of the two as they stand (both are
+// bound by instruction issue in their dequantising, converting and scaling code, not by the tensor cores or HBM).
+static bool matvec_tc_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("MLC_B200_MATVEC");
+        return e && e[0] == 't';
+    }();
+    return on;
+}
+
+template <int QT, int IN>
+static int launch_matvec_tc(mlc_ctx* ctx, const MatVecParams& mp) {
+    using F = QuantFormat<QT>;
+    TcParams p{};
+    p.w = mp.w;
+    p.x = mp.x;
+    p.residual = mp.residual;
+    p.out = mp.out;
+    p.err = ctx->d_err;
+    p.row_stride = mp.row_stride;
+    p.batch = mp.batch;
+    p.rows = mp.rows;
+    p.cols = mp.cols;
+    p.x_stride = mp.x_stride;
+    // column slices: as many CTAs as fit one wave, 8 per cluster at most, a slice a whole number of atoms
+    const uint32_t sms = static_cast<uint32_t>(std::max(ctx->sm_count, 1));
+    const uint32_t tiles = (mp.rows + kTcRows - 1) / kTcRows;
+    const uint32_t unit = std::max<uint32_t>(F::kBlockWeights, 64);
+    uint32_t S = std::max(1u, std::min(8u, sms / std::max(tiles, 1u)));
+    while (S > 1 && mp.cols / S < unit) --S;
+    p.slices = S;
+    p.slice_cols = ((mp.cols + S - 1) / S + unit - 1) / unit * unit;
+    p.w_pitch = weight_pitch(kTcChunk / F::kBlockWeights * F::kBlockBytes);
+    const size_t smem = 4 * kTcBPlaneBytes + kTcSlots * kTcAtomABytes + static_cast<size_t>(kTcRawStages) * kTcRows * p.w_pitch +
+                        sizeof(TcBars) + 1024;   // slack for the 1024-byte alignment of the tiles
+    auto kernel = quant_matvec_tc_kernel<QT, IN>;
+    static bool attr_set[16] = {};
+    if (ctx->device >= 0 && ctx->device < 16 && !attr_set[ctx->device]) {
+        MLCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[ctx->device] = true;
+    }
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, kernel, tiles * S, kTcThreads, smem, S, p));
+    ++ctx->launches;
+    return MLC_OK;
+}
+
 static int check_matvec(mlc_ctx* ctx, int qt, const void* w, const void* in, const void* out, size_t batch, size_t rows,
                         size_t cols, size_t row_stride, size_t x_stride) {
     if (!w || !in || !out) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
@@ -614,22 +1112,36 @@ using namespace mlcb;
 
 extern "C" {
 
-int mlc_encode_rms_norm_batched(mlc_ctx* ctx, const void* in, const void* weight, float epsilon, size_t batch,
-                                size_t length, void* out, void* out_f16) {
+static int encode_rms_norm(mlc_ctx* ctx, const void* in, const void* weight, float epsilon, size_t batch, size_t length,
+                           void* out, void* out_f16, void* packed) {
     if (!ctx) return MLC_ERR_INVALID_ARG;
     if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
-    if (!in || !weight || !out) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    if (!in || !weight || (!out && !packed)) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
     if (batch == 0 || length == 0) return ctx->fail(MLC_ERR_INVALID_ARG, "zero dimension");
     if (batch >= (1u << 31) || length >= (1u << 31)) return ctx->fail(MLC_ERR_UNSUPPORTED, "dimension too large");
+    if (packed && length % 4) return ctx->fail(MLC_ERR_UNSUPPORTED, "packed output needs a length divisible by 4");
     if ((length % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
-                               reinterpret_cast<uintptr_t>(weight)) % 16))
+                               reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(packed)) % 16))
         return ctx->fail(MLC_ERR_INVALID_ARG, "buffers must be 16-byte aligned");
     DeviceGuard guard(ctx->device);
     MLCB_CUDA(ctx, launch_layer_kernel(ctx, rms_norm_batched_kernel, static_cast<unsigned>(batch), 256, 0, 1,
                                        static_cast<const float*>(in), static_cast<const float*>(weight), epsilon,
-                                       static_cast<uint32_t>(length), static_cast<float*>(out), static_cast<__half*>(out_f16)));
+                                       static_cast<uint32_t>(length), static_cast<float*>(out), static_cast<__half*>(out_f16),
+                                       static_cast<uint32_t*>(packed)));
     ++ctx->launches;
     return MLC_OK;
+}
+
+int mlc_encode_rms_norm_batched(mlc_ctx* ctx, const void* in, const void* weight, float epsilon, size_t batch,
+                                size_t length, void* out, void* out_f16) {
+    if (ctx && !out) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    return encode_rms_norm(ctx, in, weight, epsilon, batch, length, out, out_f16, nullptr);
+}
+
+int mlc_encode_rms_norm_batched_packed(mlc_ctx* ctx, const void* in, const void* weight, float epsilon, size_t batch,
+                                       size_t length, void* out, void* packed) {
+    if (ctx && !packed) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    return encode_rms_norm(ctx, in, weight, epsilon, batch, length, out, nullptr, packed);
 }
 
 int mlc_encode_add_batched(mlc_ctx* ctx, const void* a, const void* b, void* out, size_t total_elements) {
@@ -719,8 +1231,15 @@ static int encode_matvec(mlc_ctx* ctx, int qt, int in_mode, const void* weights,
     p.cols = static_cast<uint32_t>(cols);
     p.x_stride = static_cast<uint32_t>(x_stride);
     p.aligned16 = (row_stride % 16 == 0 && reinterpret_cast<uintptr_t>(weights) % 16 == 0) ? 1u : 0u;
-    if (qt == kQ6_K) return in_mode == kInSiluMul ? launch_matvec<kQ6_K, kInSiluMul>(ctx, p) : launch_matvec<kQ6_K, kInPlain>(ctx, p);
-    return in_mode == kInSiluMul ? launch_matvec<kQ4_0, kInSiluMul>(ctx, p) : launch_matvec<kQ4_0, kInPlain>(ctx, p);
+    const bool tcore = matvec_tc_enabled() && p.aligned16 && batch <= static_cast<size_t>(kTcN);
+#define MLCB_MATVEC_DISPATCH(QT, IN) (tcore ? launch_matvec_tc<QT, IN>(ctx, p) : launch_matvec<QT, IN>(ctx, p))
+    if (qt == kQ6_K) {
+        if (in_mode == kInSiluMul) return MLCB_MATVEC_DISPATCH(kQ6_K, kInSiluMul);
+        return in_mode == kInPacked ? MLCB_MATVEC_DISPATCH(kQ6_K, kInPacked) : MLCB_MATVEC_DISPATCH(kQ6_K, kInPlain);
+    }
+    if (in_mode == kInSiluMul) return MLCB_MATVEC_DISPATCH(kQ4_0, kInSiluMul);
+    return in_mode == kInPacked ? MLCB_MATVEC_DISPATCH(kQ4_0, kInPacked) : MLCB_MATVEC_DISPATCH(kQ4_0, kInPlain);
+#undef MLCB_MATVEC_DISPATCH
 }
 
 int mlc_encode_matmul_q4_0_batched(mlc_ctx* ctx, const void* weights, const void* in, size_t batch, size_t rows,
@@ -734,11 +1253,12 @@ int mlc_encode_matmul_q6k_batched(mlc_ctx* ctx, const void* weights, const void*
 }
 
 int mlc_encode_matmul_quant_fused(mlc_ctx* ctx, int quant, const void* weights, const void* in, size_t in_stride,
-                                  int silu_mul_input, const void* residual, size_t batch, size_t rows, size_t cols,
+                                  int input_kind, const void* residual, size_t batch, size_t rows, size_t cols,
                                   size_t row_stride, void* out) {
     if (quant != kQ4_0 && quant != kQ6_K) return ctx ? ctx->fail(MLC_ERR_INVALID_ARG, "unknown quantisation") : MLC_ERR_INVALID_ARG;
-    return encode_matvec(ctx, quant, silu_mul_input ? kInSiluMul : kInPlain, weights, in, residual, batch, rows, cols,
-                         row_stride, in_stride, out);
+    if (input_kind < kInPlain || input_kind > kInPacked)
+        return ctx ? ctx->fail(MLC_ERR_INVALID_ARG, "unknown input kind") : MLC_ERR_INVALID_ARG;
+    return encode_matvec(ctx, quant, input_kind, weights, in, residual, batch, rows, cols, row_stride, in_stride, out);
 }
 
 }  // extern "C"

@@ -3,7 +3,7 @@
  * TEST INFRASTRUCTURE ONLY. Compiled into oracle/libpaged_oracle.so beside paged_oracle.c; only tests/,
  * __graft_entry__.smoke() and the CPU-baseline leg of bench.py may load it. Every function cites the lines
  * of MLcompiler it follows, and is pinned bit for bit (tests/test_layer_oracle.py) on golden vectors made
- * by running the reference's own CPU code for the same op (tests/golden/make_golden.py).
+ * by running the reference's own CPU code for the same op (tests/golden/make_layer_golden.py).
  *
  * One decode pass of the reference's walker (compiler/runtime/batched_walker.cpp:248-297, 333-458) is, per
  * layer: RMSNorm -> Q4_0 mat-vec (fused QKV) -> split / RoPE / cast -> KV scatter -> paged attention ->

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generates tests/golden/reference_attention.npz from MLcompiler's own CPU attention.
 
-Run in the container that has the reference checkout (/root/reference): it builds
+Run where the MLcompiler checkout is present (MLC_REFERENCE_ROOT, default: a directory `reference` beside this repository): it builds
 oracle/_ref/libref_attention.so from the reference's unmodified sources
 (oracle/build_ref.py) and records, for a set of seeded cases, the inputs and the
 output of the reference's executor-CPU attention path

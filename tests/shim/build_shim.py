@@ -23,7 +23,7 @@ CXX = os.environ.get("CXX", "g++")
 
 
 def reference_root() -> Path | None:
-    root = Path(os.environ.get("MLC_REFERENCE_ROOT", "/root/reference"))
+    root = Path(os.environ.get("MLC_REFERENCE_ROOT", str(REPO.parent / "reference")))
     return root if (root / "compiler" / "runtime" / "metal_runtime.hpp").exists() else None
 
 

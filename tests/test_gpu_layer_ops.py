@@ -185,6 +185,39 @@ def test_matvec_with_silu_mul_input_and_residual(executor, oracle_mod, batch, in
     assert (err <= 2e-5 * absdot + 1e-6 * (1 + np.abs(want))).all()
 
 
+@pytest.mark.parametrize("kind,batch,rows,cols", [("q4_0", 32, 2560, 2048), ("q6_k", 5, 300, 512), ("q4_0", 9, 70, 416)])
+def test_packed_activations_give_the_same_bits(executor, kind, batch, rows, cols):
+    """RMSNorm writing the mat-vec's operand format + a mat-vec that takes it (input_kind 2) must equal, bit for
+    bit, RMSNorm to fp32 + the plain mat-vec: the packed words are what the plain kernel makes of the fp32 values."""
+    import torch
+    rng = np.random.default_rng(cols + rows)
+    w, stride = _weights(kind, rng, rows, cols)
+    x = (rng.standard_normal((batch, cols)) * 3).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    dw, dx, dg = _dev(w), _dev(x), _dev(g)
+    norm = torch.full((batch, cols), float("nan"), device="cuda")
+    norm2 = torch.full((batch, cols), float("nan"), device="cuda")
+    packed = torch.zeros((batch, cols), device="cuda", dtype=torch.int32)
+    want = torch.full((batch, rows), float("nan"), device="cuda")
+    got = torch.full((batch, rows), float("nan"), device="cuda")
+    quant = 0 if kind == "q4_0" else 1
+
+    def both():
+        return (executor.encodeRmsNormBatched(dx, dg, 1e-5, batch, cols, norm) and
+                _encode(executor, kind, dw, norm, batch, rows, cols, stride, want) and
+                executor.encodeRmsNormBatchedPacked(dx, dg, 1e-5, batch, cols, norm2, packed) and
+                executor.encodeMatMulQuantFused(quant, dw, packed, cols, 2, None, batch, rows, cols, stride, got))
+    _run(executor, both)
+    assert torch.equal(norm, norm2)
+    assert torch.equal(want, got)
+    # without the fp32 copy
+    got2 = torch.full((batch, rows), float("nan"), device="cuda")
+    packed.zero_()
+    _run(executor, lambda: executor.encodeRmsNormBatchedPacked(dx, dg, 1e-5, batch, cols, None, packed) and
+         executor.encodeMatMulQuantFused(quant, dw, packed, cols, 2, None, batch, rows, cols, stride, got2))
+    assert torch.equal(want, got2)
+
+
 def test_layer_ops_argument_rules(executor):
     import torch
     x = torch.zeros((2, 64), device="cuda")
@@ -204,3 +237,18 @@ def test_layer_ops_argument_rules(executor):
     assert not executor.encodeGateUpSplitSiluMul(x, None, None, out, 2, 40, 64)   # row shorter than gate + up
     assert executor.encodeAddBatched(x, x, out, 0)                                # nothing to do is not an error
     assert executor.flushForwardPassCB(), executor.last_error()
+
+
+def test_layer_op_suites_on_the_tensor_memory_kernel():
+    """The mat-vec has two kernels: mma.sync (the default) and tcgen05 with the accumulator in tensor memory
+    (MLC_B200_MATVEC=tcgen05, batches of up to 32). The op tests above and the whole-model replay run again with
+    the second one selected."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, MLC_B200_MATVEC="tcgen05")
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+                        "tests/test_gpu_layer_ops.py", "tests/test_gpu_model_walker.py", "-k", "not tensor_memory_kernel"],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-1000:]

@@ -152,7 +152,7 @@ def test_scatter_gather_patterns(oracle_mod):
 
 
 def test_live_differential_against_reference(oracle_mod):
-    """With the reference library present (built from /root/reference, or prebuilt and shipped):
+    """With the reference library present (built from the MLcompiler checkout, or prebuilt and shipped):
     random cases through ExecutionExecutor::run (and RunAttentionCPU called directly) vs the oracle."""
     lib = oracle_mod.ref()
     if lib is None:
