@@ -42,6 +42,11 @@ struct mlc_attn_plan {
     uint8_t* dev = nullptr;
     size_t cap = 0;
     cudaEvent_t uploaded = nullptr;
+    // Bookkeeping of the launches that read the device copy (mutable: a plan is const to the entry points that
+    // use it): the stream epoch of the last such launch, and whether the last upload went to the copy stream
+    // and the next launch therefore has to wait for it.
+    mutable uint64_t use_epoch = 0;
+    mutable bool upload_on_copy_stream = false;
     mlcb::DecodePlanView view;
     mlcb::DecodePlanView view_pass;   // work lists of the whole-pass launch (pass_ready says whether they exist)
     const uint32_t* d_page_ids = nullptr;  // this step's (page, slot) per request, when given
@@ -58,12 +63,26 @@ struct AttnPlanCache {
 };
 
 static void release_plan_buffers(mlc_attn_plan& p) {
+    if (p.uploaded) cudaEventSynchronize(p.uploaded);   // an upload may still be under way on the copy stream
     if (p.host) cudaFreeHost(p.host);
     if (p.dev) cudaFree(p.dev);
     if (p.uploaded) cudaEventDestroy(p.uploaded);
     p.host = p.dev = nullptr;
     p.uploaded = nullptr;
     p.cap = 0;
+}
+
+// Called by every entry point that launches with a plan: the launch must see the plan's latest upload (which
+// may have gone to the copy stream), and the plan remembers in which stream epoch it was last used.
+int use_plan(mlc_ctx* ctx, const mlc_attn_plan* plan) {
+    if (plan->upload_on_copy_stream) {
+        // inside a capture the event counts as an external one (a wait node that is long satisfied at replay)
+        MLCB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, plan->uploaded, ctx->capturing ? cudaEventWaitExternal : 0));
+        plan->upload_on_copy_stream = false;
+    }
+    // a launch captured into a graph can be replayed at any time: such a plan is only ever updated in stream order
+    plan->use_epoch = ctx->capturing ? UINT64_MAX : std::max(plan->use_epoch, ctx->sync_epoch);
+    return MLC_OK;
 }
 
 void destroy_plan_cache(mlc_ctx* ctx) {
@@ -527,8 +546,20 @@ int build_plan(mlc_ctx* ctx, mlc_attn_plan& p, const uint32_t* pt_flat, const ui
     if (!segs.empty()) std::memcpy(p.host + off_segs, segs.data(), segs.size() * sizeof(SegDesc));
     if (page_ids) std::memcpy(p.host + off_ids, page_ids, N * 4);
     if (slots) std::memcpy(p.host + off_slots, slots, N * 4);
-    MLCB_CUDA(ctx, cudaMemcpyAsync(p.dev, p.host, bytes, cudaMemcpyHostToDevice, ctx->stream));
-    MLCB_CUDA(ctx, cudaEventRecord(p.uploaded, ctx->stream));
+    // Where the upload goes: if the stream has been synchronised since the plan's last launch, nothing in flight
+    // reads its device copy, and the upload runs on the copy stream beside whatever the main stream is doing
+    // (the kernels of the pass that uses the OTHER plan, in a walker that alternates two). Otherwise in stream
+    // order, behind the kernels already enqueued with the old tables.
+    if (p.use_epoch < ctx->sync_epoch && !ctx->capturing) {
+        if (!ctx->h2d_stream) MLCB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+        MLCB_CUDA(ctx, cudaMemcpyAsync(p.dev, p.host, bytes, cudaMemcpyHostToDevice, ctx->h2d_stream));
+        MLCB_CUDA(ctx, cudaEventRecord(p.uploaded, ctx->h2d_stream));
+        p.upload_on_copy_stream = true;
+    } else {
+        MLCB_CUDA(ctx, cudaMemcpyAsync(p.dev, p.host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        MLCB_CUDA(ctx, cudaEventRecord(p.uploaded, ctx->stream));
+        p.upload_on_copy_stream = false;
+    }
 
     DecodePlanView& v = p.view;
     v.cta_counts = reinterpret_cast<const uint32_t*>(p.dev + off_counts);
@@ -678,6 +709,7 @@ int attention_impl(mlc_ctx* ctx, bool sync, AttnArgs a, const uint32_t* pt_flat,
     DeviceGuard guard(ctx->device);
     mlc_attn_plan* plan = nullptr;
     if ((st = get_cached_plan(ctx, key, pt_flat, pt_off, seq_lens, q_pos, &plan)) != MLC_OK) return st;
+    if ((st = use_plan(ctx, plan)) != MLC_OK) return st;
     if ((st = launch_with_plan(ctx, a, *plan)) != MLC_OK) return st;
     return sync ? finish_sync(ctx, "attention") : MLC_OK;
 }
@@ -801,6 +833,7 @@ int mlc_encode_paged_flash_attention_planned(mlc_ctx* ctx, const mlc_attn_plan* 
     if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
     if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
     DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
     AttnArgs a;
     a.q = q; a.k_pages = k_pages; a.v_pages = v_pages; a.o = o;
     a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
@@ -815,6 +848,7 @@ int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan
     if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
     if (!o_partial || !ml_partial) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
     DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
     AttnArgs a;
     a.q = q; a.k_pages = k_pages; a.v_pages = v_pages;
     a.o_partial = o_partial; a.ml_partial = ml_partial;
@@ -839,6 +873,7 @@ int mlc_encode_paged_attention_exchange_planned(mlc_ctx* ctx, const mlc_attn_pla
                          xv.max_rows, xv.D, rows, k.D);
     if (reinterpret_cast<uintptr_t>(out) % 16) return ctx->fail(MLC_ERR_INVALID_ARG, "out must be 16-byte aligned");
     DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
     AttnArgs a;
     a.q = q; a.k_pages = k_pages; a.v_pages = v_pages;
     a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
@@ -873,6 +908,7 @@ int mlc_encode_paged_decode_step_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
     if (!plan->d_page_ids) return ctx->fail(MLC_ERR_INVALID_ARG, "the plan was created without page_ids / slots_in_page");
     if (!k_new || !v_new || !k_pages || !v_pages) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
     DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
     AttnArgs a;
     a.q = q; a.k_pages = k_pages; a.v_pages = v_pages; a.o = o;
     a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
@@ -902,6 +938,7 @@ int mlc_encode_paged_decode_pass_planned(mlc_ctx* ctx, const mlc_attn_plan* plan
     if (pass_allowed && !ctx->force_general && decode_pass_supported(plan->view_pass, n_layers) &&
         (q_dtype == MLC_F32 || q_dtype == MLC_F16) && (o_dtype == MLC_F32 || o_dtype == MLC_F16)) {
         DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
         const PlanKey& k = plan->key;
         AttnArgs shape;
         shape.batch = k.batch; shape.H = k.H; shape.KVH = k.KVH; shape.D = k.D; shape.P = k.P; shape.capacity = k.capacity;
@@ -935,6 +972,7 @@ int mlc_encode_paged_decode_pass_host(mlc_ctx* ctx, const mlc_attn_plan* plan, s
     const size_t o_row = k.batch * k.H * k.D * (o_dtype == MLC_F32 ? 4 : 2);
     if (in_row % 16 || q_bytes % 16 || kv_bytes % 16) return ctx->fail(MLC_ERR_UNSUPPORTED, "rows of the packed input must be multiples of 16 bytes");
     DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
     // Zero-copy form: when the whole pass can be one launch and both host buffers are pinned memory the GPU can
     // address, the kernel reads Q and the new rows straight from host memory (each row once, a work item
     // ahead of its use) and writes O straight into it, so the transfers run inside the kernel, beside the KV
@@ -1046,6 +1084,7 @@ int mlc_encode_scatter_kv_pair_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, 
     if (!plan->d_page_ids) return ctx->fail(MLC_ERR_INVALID_ARG, "the plan was created without page_ids / slots_in_page");
     if (!k_page_storage || !v_page_storage || !k_src || !v_src) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
     DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
     const PlanKey& k = plan->key;
     return launch_scatter_rows_device_tables(ctx, k_page_storage, v_page_storage, plan->d_page_ids,
                                              plan->d_slots, k.P, k.KVH, k.D, k.batch, k_src, v_src, k.capacity);
@@ -1065,6 +1104,7 @@ int mlc_encode_qkv_split_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan*
                                  k.KVH * k.D, k.KVH * k.D, rotary_dim);
     if (st != MLC_OK) return st;
     DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
     QkvRopeParams p{};
     p.qkv = static_cast<const float*>(qkv);
     if (q_dtype == MLC_F32) p.q = static_cast<float*>(q_out);

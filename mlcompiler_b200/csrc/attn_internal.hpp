@@ -4,6 +4,7 @@
 #include "ctx.hpp"
 
 struct mlc_attn_plan;
+struct mlc_ctx;
 
 namespace mlcb {
 
@@ -125,5 +126,9 @@ int launch_prefill_tcgen05(mlc_ctx* ctx, const void* q, const void* k_pages, con
                            float scale);
 // Launches attention for an already created plan (the plan's shape fields fill `a`).
 int launch_attention_with_plan(mlc_ctx* ctx, AttnArgs a, const mlc_attn_plan* plan);
+
+// Before a launch that reads a plan's device copy: waits for an upload that went to the copy stream and notes
+// the use (attn_api.cu).
+int use_plan(mlc_ctx* ctx, const mlc_attn_plan* plan);
 
 }  // namespace mlcb

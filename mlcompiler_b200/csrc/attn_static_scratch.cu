@@ -51,6 +51,7 @@ int mlc_encode_paged_flash_attention_planned_static(mlc_ctx* ctx, const mlc_attn
     if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
     if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
     DeviceGuard guard(ctx->device);
+    if (int ust = mlcb::use_plan(ctx, plan); ust != MLC_OK) return ust;
     void* scratch = nullptr;
     int st = static_scratch_address(ctx, &scratch);
     if (st != MLC_OK) return st;

@@ -313,6 +313,7 @@ int mlc_pass_flush(mlc_ctx* ctx) {
         word_queued = cudaMemcpyAsync(ctx->h_err, ctx->d_err, 4, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess;
     }
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) ++ctx->sync_epoch;
     if (e == cudaSuccess && ctx->host_pass_done) {  // copies back of a host-buffer pass run on their own stream
         e = cudaEventSynchronize(ctx->host_pass_done);
         ctx->host_pass_done = nullptr;

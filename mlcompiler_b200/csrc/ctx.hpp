@@ -64,6 +64,7 @@ struct mlc_ctx {
     uint32_t wait_limit = 0;        // polls before a flag wait gives up; 0 = the kernel's default (about a second)
     int last_attention_kernel = 0;  // 0 none yet, 1 general, 2 TMA / tensor-core
     uint64_t launches = 0;
+    uint64_t sync_epoch = 1;        // counts full synchronisations of the stream (mlc_pass_flush): work enqueued in an earlier epoch is done
     uint64_t allocations = 0;       // device and pinned-host allocations made through this context
     uint64_t decode_launches = 0;   // selects the workspace copy of the split-KV kernel
     mlcb::PoolWrites recent_writes[2];   // pools written by the last two decode launches on this context
