@@ -6,6 +6,7 @@ too, under its `secondary` key).
     python bench_more.py --workload cfg4 [--steps K]          # wide GQA, requests sharded by KV bytes
     python bench_more.py --workload cfg5 [--steps K]          # chunked prefill on tcgen05
     python bench_more.py --workload model [--steps K]         # whole decode step of a 1.1B-shaped model
+    python bench_more.py --workload matvec --rows R --cols C [--quant q4_0|q6_k] [--batch B]   # one quantised mat-vec
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         bench_more.py --workload cfg3|cfg4|cfg5
 
@@ -26,6 +27,10 @@ token upload, every launch of the pass, logits [32, 32000] back on the host. Wei
 bytes in the real formats (there is no checkpoint to load here), the contexts' K/V rows random. Metric:
 generated tokens per second, wall clock around run_decode (the call returns when the logits are on the
 host). With N ranks every rank serves its own 32 requests on its own copy of the weights.
+matvec: one quantised batched mat-vec (mlc_encode_matmul_q4_0_batched / _q6k_batched) at a given shape, default
+the 1.1B model's gate | up projection (11264 x 2048, Q4_0, 32 requests); the weights rotate over enough copies
+to exceed L2, so every launch streams them from HBM. MLC_B200_MATVEC=tcgen05 selects the tensor-memory kernel.
+Metric: GB/s of weight bytes against the measured copy bandwidth.
 Prints one JSON line (rank 0). Pools rotate so that consecutive steps never re-read L2-resident data.
 """
 from __future__ import annotations
@@ -445,9 +450,54 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False):
         "gpu_launches": int(launches), "launches_per_step": launches / steps}
 
 
+def run_matvec(env, steps=200, warmup=10, rows=11264, cols=2048, quant="q4_0", batch=32):
+    import torch
+    from mlcompiler_b200 import synth
+    ex, stream, dev = env.ex, env.stream, env.dev
+    rng = np.random.default_rng(7)
+    raw = synth.random_q4_0(rng, rows, cols) if quant == "q4_0" else synth.random_q6_k(rng, rows, cols)
+    copies = max(2, int(np.ceil(300e6 / raw.nbytes)))
+    with torch.cuda.stream(stream):
+        ws = [torch.from_numpy(raw).to(dev) for _ in range(copies)]
+        x = torch.randn((batch, cols), device=dev)
+        out = torch.zeros((batch, rows), device=dev)
+    stream.synchronize()
+
+    def enc():
+        for w in ws:
+            ok = (ex.encodeMatMulQ4_0Batched(w, x, batch, rows, cols, raw.shape[1], out) if quant == "q4_0" else
+                  ex.encodeMatMulQ6KBatched(w, x, batch, rows, cols, raw.shape[1], out))
+            assert ok, ex.last_error()
+
+    assert ex.beginForwardPassCB()
+    enc()
+    assert ex.flushForwardPassCB(), ex.last_error()
+    assert ex.beginForwardPassCB()
+    assert ex.beginCapture()
+    enc()
+    graph = ex.endCapture()
+    for _ in range(max(warmup, 3)):
+        graph.launch()
+    env.barrier()
+    reps = max(steps // copies, 1)
+    sec = _timed(env, lambda i: graph.launch(), reps) / copies
+    assert ex.flushForwardPassCB(), ex.last_error()
+    graph.destroy()
+    peaks = measured_peaks()
+    value = raw.nbytes / sec / 1e9
+    flop = 2.0 * rows * cols * batch * 2          # hi and lo activation planes
+    return {"metric": "quant_matvec_weight_gbps", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": reps * copies,
+            "warmup": max(warmup, 3), "us_per_launch": sec * 1e6, "higher_is_better": True, "dtype": f"{quant} weights, f32 activations",
+            "data": "synthetic", "config": {"workload": f"matvec {rows} x {cols} {quant}, batch {batch}", "weight_copies_rotated": copies,
+                                            "kernel": os.environ.get("MLC_B200_MATVEC", "mma.sync (default)")},
+            "tensor_tflops": flop / sec / 1e12,
+            "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": value / peaks["hbm_gbs"],
+                         "peak_source": peaks["source"], "bytes_per_launch": int(raw.nbytes)}}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=["cfg3", "cfg4", "cfg5", "model"], required=True)
+    ap.add_argument("--workload", choices=["cfg3", "cfg4", "cfg5", "model", "matvec"], required=True)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--exchange", choices=["fused", "peer", "nccl"], default="fused",
@@ -455,6 +505,10 @@ def main():
                          "peer-memory exchange kernel, or NCCL all-gather + combine")
     ap.add_argument("--reference-order", action="store_true",
                     help="model: the reference walker's 13 launches per layer instead of the fused 8")
+    ap.add_argument("--rows", type=int, default=11264, help="matvec: weight rows")
+    ap.add_argument("--cols", type=int, default=2048, help="matvec: weight columns")
+    ap.add_argument("--quant", choices=["q4_0", "q6_k"], default="q4_0", help="matvec: weight format")
+    ap.add_argument("--batch", type=int, default=32, help="matvec: requests")
     ap.add_argument("--seq-len", type=int, default=None, help="cfg3: tokens per request instead of 32768")
     args = ap.parse_args()
 
@@ -475,6 +529,8 @@ def main():
         res = run_cfg5(env, args.steps, args.warmup)
     elif args.workload == "cfg3":
         res = run_cfg3(env, args.steps, args.warmup, args.exchange, seq_len=args.seq_len)
+    elif args.workload == "matvec":
+        res = run_matvec(env, args.steps, args.warmup, args.rows, args.cols, args.quant, args.batch)
     elif args.workload == "model":
         res = run_model(env, min(args.steps, 100), args.warmup, reference_order=args.reference_order)
     else:

@@ -22,6 +22,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstdlib>
+#include <vector>
 
 #include "ctx.hpp"
 #include "tcgen05_util.hpp"
@@ -566,6 +567,34 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     if (S > 1) cluster_sync_relaxed();
 }
 
+// How many clusters of S CTAs of `kernel` (threads, dynamic shared memory) the device holds at once; cached.
+// Clusters are placed inside one GPC each, so this is often less than (CTAs that fit) / S - and a launch that
+// needs one cluster more than fit runs as two waves.
+static uint32_t max_active_clusters(mlc_ctx* ctx, const void* kernel, unsigned threads, size_t smem, unsigned S) {
+    struct Entry { const void* f; size_t smem; unsigned S; int dev; uint32_t n; };
+    static std::vector<Entry> cache;
+    for (const Entry& e : cache)
+        if (e.f == kernel && e.smem == smem && e.S == S && e.dev == ctx->device) return e.n;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(S * 64);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = std::max(1, ctx->sm_count / static_cast<int>(S));   // a guess; only the choice of S depends on it
+    }
+    cache.push_back({kernel, smem, S, ctx->device, static_cast<uint32_t>(n)});
+    return static_cast<uint32_t>(n);
+}
+
 static uint32_t weight_pitch(uint32_t chunk_bytes) {
     // room for the enclosing 16-byte range of a chunk, and rows 4 banks apart (pitch / 4 = 4 mod 8)
     uint32_t p = (chunk_bytes + 16 + 15) / 16 * 16;
@@ -573,44 +602,54 @@ static uint32_t weight_pitch(uint32_t chunk_bytes) {
     return p;
 }
 
+// Column slices (= CTAs per cluster, 8 at most, never less than one block per slice): the most slices whose
+// clusters - one per 64-row tile - are all resident at once; if even unsliced tiles do not fit one wave, the
+// slicing that leaves the fewest chunks per CTA per wave. A slice is worked through in chunks of kMvChunk columns.
 template <int QT, int NT, int IN>
-static int launch_matvec_nt(mlc_ctx* ctx, const MatVecParams& p, unsigned ctas, size_t smem) {
+static int launch_matvec_nt(mlc_ctx* ctx, MatVecParams p) {
+    using F = QuantFormat<QT>;
     auto kernel = quant_matvec_kernel<QT, NT, IN>;
     static bool attr_set[16] = {};
     if (ctx->device >= 0 && ctx->device < 16 && !attr_set[ctx->device]) {
         MLCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set[ctx->device] = true;
     }
-    MLCB_CUDA(ctx, launch_layer_kernel(ctx, kernel, ctas, kMvThreads, smem, p.slices, p));
+    const uint32_t tiles = (p.rows + kMvRows - 1) / kMvRows;
+    const uint32_t unit = F::kBlockWeights;
+    size_t smem = 0;
+    auto shape = [&](uint32_t S) {
+        p.slices = S;
+        p.slice_cols = ((p.cols + S - 1) / S + unit - 1) / unit * unit;
+        p.chunk_cols = std::min<uint32_t>(p.slice_cols, kMvChunk);
+        p.w_pitch = weight_pitch(p.chunk_cols / F::kBlockWeights * F::kBlockBytes);
+        const size_t stage = static_cast<size_t>(IN == kInSiluMul ? 2 : 1) * NT * 8 * (p.chunk_cols + kXPadWords) * 4 +
+                             static_cast<size_t>(kMvRows) * p.w_pitch;
+        smem = std::max(stage * kMvStages, static_cast<size_t>(2) * NT * 8 * kRedPitch * sizeof(float));
+    };
+    uint32_t best_S = 1;
+    uint64_t best_cost = ~0ull;
+    for (uint32_t S = 8; S >= 1; S >>= 1) {
+        if (S > 1 && p.cols / S < unit) continue;
+        shape(S);
+        const uint32_t fit = max_active_clusters(ctx, reinterpret_cast<const void*>(kernel), kMvThreads, smem, S);
+        const uint64_t waves = (tiles + fit - 1) / fit;
+        const uint64_t chunks = (p.slice_cols + p.chunk_cols - 1) / p.chunk_cols;
+        const uint64_t cost = waves * (chunks + 1);   // + 1: what a wave costs beside its chunks
+        if (cost < best_cost) best_cost = cost, best_S = S;
+    }
+    shape(best_S);
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, kernel, tiles * best_S, kMvThreads, smem, best_S, p));
     ++ctx->launches;
     return MLC_OK;
 }
 
 template <int QT, int IN>
 static int launch_matvec(mlc_ctx* ctx, MatVecParams p) {
-    using F = QuantFormat<QT>;
-    const uint32_t tiles = (p.rows + kMvRows - 1) / kMvRows;
-    // Column slices (= CTAs per cluster): as many as it takes to put two CTAs on every SM, 8 at most, and never
-    // slices of less than one block. A slice is worked through in chunks of kMvChunk columns.
-    uint32_t S = 1;
-    while (S < 8 && tiles * S < 2u * static_cast<uint32_t>(ctx->sm_count) && p.cols / (2 * S) >= F::kBlockWeights) S *= 2;
-    const uint32_t unit = F::kBlockWeights;
-    p.slices = S;
-    p.slice_cols = ((p.cols + S - 1) / S + unit - 1) / unit * unit;
-    p.chunk_cols = std::min<uint32_t>(p.slice_cols, kMvChunk);
-    p.w_pitch = weight_pitch(p.chunk_cols / F::kBlockWeights * F::kBlockBytes);
     const uint32_t nt = (p.batch + 7) / 8;
-    const int NT = nt <= 1 ? 1 : (nt <= 2 ? 2 : (nt <= 4 ? 4 : 8));
-    const size_t stage = static_cast<size_t>(IN == kInSiluMul ? 2 : 1) * NT * 8 * (p.chunk_cols + kXPadWords) * 4 +
-                         static_cast<size_t>(kMvRows) * p.w_pitch;
-    const size_t smem = std::max(stage * kMvStages, static_cast<size_t>(2) * NT * 8 * kRedPitch * sizeof(float));
-    const unsigned ctas = tiles * S;
-    switch (NT) {
-        case 1: return launch_matvec_nt<QT, 1, IN>(ctx, p, ctas, smem);
-        case 2: return launch_matvec_nt<QT, 2, IN>(ctx, p, ctas, smem);
-        case 4: return launch_matvec_nt<QT, 4, IN>(ctx, p, ctas, smem);
-        default: return launch_matvec_nt<QT, 8, IN>(ctx, p, ctas, smem);
-    }
+    if (nt <= 1) return launch_matvec_nt<QT, 1, IN>(ctx, p);
+    if (nt <= 2) return launch_matvec_nt<QT, 2, IN>(ctx, p);
+    if (nt <= 4) return launch_matvec_nt<QT, 4, IN>(ctx, p);
+    return launch_matvec_nt<QT, 8, IN>(ctx, p);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -984,22 +1023,29 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
                     scale[i] = static_cast<uint32_t>(i) < n_groups ? __fmul_rn(d, static_cast<float>(static_cast<int8_t>(wrow[192 + i]))) : 0.0f;
             }
             tc::mbar_arrive(tc::smem_u32(&bars.raw_empty[stage]));
+            // Two register tiles: the load of group g + 1 is in flight while group g is multiplied and added.
+            uint32_t v[2][32];
+            auto fetch = [&](uint32_t (&dst)[32]) -> bool {   // waits for the next finished tile and starts its load
+                const uint32_t buf = group_count % kTcBufs;
+                bool got = tc::mbar_wait_bounded(tc::smem_u32(&bars.d_full[buf]), (group_count / kTcBufs) & 1u);
+                got = __all_sync(0xffffffffu, got);
+                if (!got) return false;
+                tc::fence_after();
+                tc::tmem_ld32(tmem + lane_base + buf * kTcN, dst);
+                return true;
+            };
+            if (n_groups > 0 && !fetch(v[0])) { ok = false; give_up(2, chunk); break; }
 #pragma unroll
             for (int gi = 0; gi < kGroupsPerChunk; ++gi) {
-                if (static_cast<uint32_t>(gi) >= n_groups || !ok) break;
-                const uint32_t buf = group_count % kTcBufs;
-                ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.d_full[buf]), (group_count / kTcBufs) & 1u);
-                if (!__all_sync(0xffffffffu, ok)) { ok = false; give_up(2, chunk); break; }
-                tc::fence_after();
-                uint32_t v[32];
-                tc::tmem_ld32(tmem + lane_base + buf * kTcN, v);
-                tc::tmem_wait_ld();
+                if (static_cast<uint32_t>(gi) >= n_groups) break;
+                tc::tmem_wait_ld();                       // v[gi & 1] is in registers
                 tc::fence_before();
-                tc::mbar_arrive(tc::smem_u32(&bars.d_empty[buf]));
+                tc::mbar_arrive(tc::smem_u32(&bars.d_empty[group_count % kTcBufs]));
+                ++group_count;
+                if (static_cast<uint32_t>(gi + 1) < n_groups && !fetch(v[(gi + 1) & 1])) { ok = false; give_up(2, chunk); break; }
                 const float sc = scale[gi];
 #pragma unroll
-                for (int n = 0; n < kTcN; ++n) acc[n] = fmaf(sc, __uint_as_float(v[n]), acc[n]);
-                ++group_count;
+                for (int n = 0; n < kTcN; ++n) acc[n] = fmaf(sc, __uint_as_float(v[gi & 1][n]), acc[n]);
             }
         }
     }
@@ -1069,14 +1115,10 @@ static int launch_matvec_tc(mlc_ctx* ctx, const MatVecParams& mp) {
     p.rows = mp.rows;
     p.cols = mp.cols;
     p.x_stride = mp.x_stride;
-    // column slices: as many CTAs as fit one wave, 8 per cluster at most, a slice a whole number of atoms
-    const uint32_t sms = static_cast<uint32_t>(std::max(ctx->sm_count, 1));
+    // column slices (CTAs per cluster, a slice a whole number of atoms): the most whose clusters - one per 128-row
+    // tile - are all resident at once, else none
     const uint32_t tiles = (mp.rows + kTcRows - 1) / kTcRows;
     const uint32_t unit = std::max<uint32_t>(F::kBlockWeights, 64);
-    uint32_t S = std::max(1u, std::min(8u, sms / std::max(tiles, 1u)));
-    while (S > 1 && mp.cols / S < unit) --S;
-    p.slices = S;
-    p.slice_cols = ((mp.cols + S - 1) / S + unit - 1) / unit * unit;
     p.w_pitch = weight_pitch(kTcChunk / F::kBlockWeights * F::kBlockBytes);
     const size_t smem = 4 * kTcBPlaneBytes + kTcSlots * kTcAtomABytes + static_cast<size_t>(kTcRawStages) * kTcRows * p.w_pitch +
                         sizeof(TcBars) + 1024;   // slack for the 1024-byte alignment of the tiles
@@ -1086,6 +1128,13 @@ static int launch_matvec_tc(mlc_ctx* ctx, const MatVecParams& mp) {
         MLCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_set[ctx->device] = true;
     }
+    uint32_t S = 1;
+    for (uint32_t c = 8; c > 1; c >>= 1) {
+        if (mp.cols / c < unit) continue;
+        if (tiles <= max_active_clusters(ctx, reinterpret_cast<const void*>(kernel), kTcThreads, smem, c)) { S = c; break; }
+    }
+    p.slices = S;
+    p.slice_cols = ((mp.cols + S - 1) / S + unit - 1) / unit * unit;
     MLCB_CUDA(ctx, launch_layer_kernel(ctx, kernel, tiles * S, kTcThreads, smem, S, p));
     ++ctx->launches;
     return MLC_OK;

@@ -24,10 +24,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// A poll that finds the phase open suspends for a few microseconds: 2^18 polls are about a second.
+// Bounded wait. A poll that finds the phase still open comes back at once on this GPU, and a dozen warps
+// spinning on barriers take issue slots from the warps that work; so after the first few polls a waiting warp
+// sleeps between them. 2^22 polls of >= 64 ns are at least a quarter of a second.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 18); ++i)
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (i >= 4) __nanosleep(64);
+    }
     return false;
 }
 __device__ __forceinline__ bool elect_one() {

@@ -287,9 +287,9 @@ class PagedAttentionExecutor(_ExecutorBase):
         arr = (RequestSlotC * max(n, 1))(*[RequestSlotC(*s) for s in slots])
         success = (C.c_uint8 * max(n, 1))()
         stride = getattr(self, "_logit_count", self.H * self.D)
-        logits = np.zeros((max(n, 1), stride), np.float32)
+        logits = np.empty((max(n, 1), stride), np.float32)    # rows are returned as views of this one array
         got = lib().mlc_executor_run_decode(self._h, arr, n, success, logits.ctypes.data_as(_fp), stride)
-        return [(slots[i][0], bool(success[i]), logits[i].copy() if success[i] else None) for i in range(got)]
+        return [(slots[i][0], bool(success[i]), logits[i] if success[i] else None) for i in range(got)]
 
     def run_prefill(self, request_id, tokens):
         toks = (C.c_uint64 * max(len(tokens), 1))(*tokens)
