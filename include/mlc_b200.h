@@ -675,7 +675,9 @@ int mlc_executor_attach_paged_storage(mlc_executor* exec, mlc_kv_storage* storag
  * attention with host tables per layer (batched_walker.cpp:299-331). mlc_status. */
 int mlc_executor_set_call_order(mlc_executor* exec, int reference_order);
 /* run_decode: returns the number of per-request results; success[i] and, for successful
- * requests, logits[i * logits_stride ...] are filled. */
+ * requests, logits[i * logits_stride ...] are filled. With a model attached and logits_stride >=
+ * vocab_size the rows are written without intermediate per-request vectors - straight from the
+ * device when `logits` is page-locked host memory (cudaHostAlloc / cudaHostRegister / pin_memory). */
 size_t mlc_executor_run_decode(mlc_executor* exec, const mlc_request_slot* slots, size_t n, uint8_t* success,
                                float* logits, size_t logits_stride);
 /* run_prefill: returns the number of logits (0 = failed). */

@@ -126,6 +126,18 @@ BatchedDecodeOutput PagedAttentionExecutor::run_decode(const std::vector<Request
     return walker_->step(slots);
 }
 
+BatchedDecodeOutput PagedAttentionExecutor::run_decode_into(const std::vector<RequestSlot>& slots, float* logits, size_t stride) {
+    if (slots.empty() || !storage_ || !pool_ || !model_) return run_decode(slots);
+    BatchedWalker::LogitsSink sink;
+    sink.dst = logits;
+    sink.stride = stride;
+    return walker_->step(slots, &sink);
+}
+
+size_t PagedAttentionExecutor::logits_per_request() const {
+    return model_ ? model_->vocab_size : static_cast<size_t>(H_) * D_;
+}
+
 bool PagedAttentionExecutor::attach_model(const ModelWeights& m) {
     if (m.layers.size() != L_ || !m.hidden_size || !m.ffn_inner || !m.vocab_size) return false;
     if (m.hidden_size != H_ * D_ || m.hidden_size % 256 || m.ffn_inner % 256) return false;

@@ -125,6 +125,11 @@ public:
     const RequestKVState* page_state(uint32_t request_id) const;
 
     BatchedDecodeOutput run_decode(const std::vector<RequestSlot>& slots) override;
+    // The same pass with a model attached, the logits written to the caller's rows (row r at logits + r * stride
+    // floats, stride >= vocabulary size) instead of into per-request vectors; straight from the device when the
+    // buffer is page-locked memory. The returned entries carry request ids and success flags only.
+    BatchedDecodeOutput run_decode_into(const std::vector<RequestSlot>& slots, float* logits, size_t stride);
+    size_t logits_per_request() const;
     std::vector<float> run_prefill(uint32_t request_id, const std::vector<uint64_t>& tokens) override;
     void release_request(uint32_t request_id) override;
     void reset();

@@ -2,7 +2,10 @@
 #include "batched_walker.hpp"
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include <cuda_fp16.h>
@@ -17,9 +20,22 @@ BatchedWalker::~BatchedWalker() {
     if (logits_pinned_) cudaFreeHost(logits_pinned_);
 }
 
-BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
+// MLC_B200_WALKER_TRACE=1 in the environment: one line per model pass on stderr with the host time of its phases.
+static bool walker_trace() {
+    static const bool on = [] {
+        const char* e = std::getenv("MLC_B200_WALKER_TRACE");
+        return e && e[0] == '1';
+    }();
+    return on;
+}
+static double now_us() {
+    return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, const LogitsSink* sink) {
     BatchedDecodeOutput out;
     if (slots.empty()) return out;
+    const double t_start = walker_trace() ? now_us() : 0.0;
     PagedAttentionExecutor& ex = exec_;
     mlc_ctx* ctx = ex.ctx_;
     PagedKVStorage* storage = ex.storage_;
@@ -87,32 +103,58 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots) {
     if (ex.model_) {
         // The whole walker step on the device; logits [N, vocab] come back (batched_walker.cpp:461-475).
         void* logits_dev = nullptr;
+        const double t_plan = walker_trace() ? now_us() : 0.0;
         bool ok = mlc_pass_begin(ctx) == MLC_OK;
         ok = ok && encode_model_pass(slots, plan, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos, &logits_dev);
+        const double t_enc = walker_trace() ? now_us() : 0.0;
         ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
+        const double t_flush = walker_trace() ? now_us() : 0.0;
         if (!ok || !logits_dev) return fail_all();
         const size_t vocab = ex.model_->vocab_size;
-        if (logits_pinned_floats_ < N * vocab) {   // pageable memory would make this copy several times slower
-            if (logits_pinned_) cudaFreeHost(logits_pinned_);
-            logits_pinned_ = nullptr;
-            logits_pinned_floats_ = 0;
-            DeviceGuard guard(ctx->device);
-            if (cudaHostAlloc(reinterpret_cast<void**>(&logits_pinned_), N * vocab * sizeof(float), cudaHostAllocDefault) !=
-                cudaSuccess)
-                return fail_all();
-            logits_pinned_floats_ = N * vocab;
-            ++ctx->allocations;
+        // A caller's buffer in page-locked memory takes the rows straight from the device; anything else goes
+        // through this walker's page-locked landing area (a copy into pageable memory is several times slower).
+        bool direct = false;
+        if (sink && sink->dst && sink->stride >= vocab) {
+            cudaPointerAttributes attr{};
+            direct = cudaPointerGetAttributes(&attr, sink->dst) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+            cudaGetLastError();   // a pointer the runtime does not know is not an error here
         }
-        if (mlc_download(ctx, logits_dev, logits_pinned_, N * vocab * sizeof(float), 0) != MLC_OK) return fail_all();
+        if (direct) {
+            DeviceGuard guard(ctx->device);
+            if (cudaMemcpy2DAsync(sink->dst, sink->stride * sizeof(float), logits_dev, vocab * sizeof(float), vocab * sizeof(float), N,
+                                  cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+                cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+                return fail_all();
+        } else {
+            if (logits_pinned_floats_ < N * vocab) {
+                if (logits_pinned_) cudaFreeHost(logits_pinned_);
+                logits_pinned_ = nullptr;
+                logits_pinned_floats_ = 0;
+                DeviceGuard guard(ctx->device);
+                if (cudaHostAlloc(reinterpret_cast<void**>(&logits_pinned_), N * vocab * sizeof(float), cudaHostAllocDefault) !=
+                    cudaSuccess)
+                    return fail_all();
+                logits_pinned_floats_ = N * vocab;
+                ++ctx->allocations;
+            }
+            if (mlc_download(ctx, logits_dev, logits_pinned_, N * vocab * sizeof(float), 0) != MLC_OK) return fail_all();
+            if (sink && sink->dst && sink->stride >= vocab)
+                for (size_t r = 0; r < N; ++r)
+                    std::memcpy(sink->dst + r * sink->stride, logits_pinned_ + r * vocab, vocab * sizeof(float));
+        }
+        const bool to_sink = sink && sink->dst && sink->stride >= vocab;
         out.per_request.reserve(N);
         for (size_t r = 0; r < N; ++r) {
             BatchedDecodeOutput::PerRequest p;
             p.request_id = slots[r].request_id;
             p.success = true;
-            p.logits.assign(logits_pinned_ + r * vocab, logits_pinned_ + (r + 1) * vocab);
+            if (!to_sink) p.logits.assign(logits_pinned_ + r * vocab, logits_pinned_ + (r + 1) * vocab);
             reqs[r]->next_position = slots[r].sequence_position + 1;
             out.per_request.push_back(std::move(p));
         }
+        if (walker_trace())
+            std::fprintf(stderr, "[walker] tables+plan %.0f us | encode %.0f | flush %.0f | logits %.0f | total %.0f\n",
+                         t_plan - t_start, t_enc - t_plan, t_flush - t_enc, now_us() - t_flush, now_us() - t_start);
         return out;
     }
 

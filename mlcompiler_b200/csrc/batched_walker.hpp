@@ -14,7 +14,12 @@ class BatchedWalker {
 public:
     explicit BatchedWalker(PagedAttentionExecutor& exec) : exec_(exec) {}
     ~BatchedWalker();
-    BatchedDecodeOutput step(const std::vector<RequestSlot>& slots);
+    // Where a model pass may put its logits instead of into per-request vectors: row r at dst + r * stride floats.
+    struct LogitsSink {
+        float* dst = nullptr;
+        size_t stride = 0;
+    };
+    BatchedDecodeOutput step(const std::vector<RequestSlot>& slots, const LogitsSink* sink = nullptr);
     // All tokens of a prompt chunk in one pass per layer: the chunk's K/V rows are scattered,
     // then chunked causal attention runs over the request's pages. Returns the last token's
     // attention output of the last layer, or {} on failure. The reference reaches the same

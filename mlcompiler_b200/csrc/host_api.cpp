@@ -208,10 +208,12 @@ size_t mlc_executor_run_decode(mlc_executor* e, const mlc_request_slot* slots, s
     std::vector<RequestSlot> in(n);
     for (size_t i = 0; i < n; ++i)
         in[i] = {slots[i].request_id, slots[i].input_token, static_cast<size_t>(slots[i].sequence_position)};
-    const BatchedDecodeOutput out = e->exec->run_decode(in);
+    // with a model attached the logits go straight into the caller's rows (no per-request vectors in between)
+    const bool into = e->paged && e->paged->has_model() && logits && logits_stride >= e->paged->logits_per_request();
+    const BatchedDecodeOutput out = into ? e->paged->run_decode_into(in, logits, logits_stride) : e->exec->run_decode(in);
     for (size_t i = 0; i < out.per_request.size() && i < n; ++i) {
         if (success) success[i] = out.per_request[i].success ? 1 : 0;
-        if (logits && out.per_request[i].success)
+        if (logits && out.per_request[i].success && !into)
             std::memcpy(logits + i * logits_stride, out.per_request[i].logits.data(),
                         std::min(logits_stride, out.per_request[i].logits.size()) * sizeof(float));
     }

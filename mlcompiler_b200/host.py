@@ -281,13 +281,29 @@ class PagedAttentionExecutor(_ExecutorBase):
             self._logit_count = model.vocab_size
         return ok
 
+    def _logits_rows(self, n, stride):
+        """The array the library writes a pass's logits into. With a model attached it is page-locked (the rows then
+        come straight from the device) and REUSED by the next call: copy what has to outlive it."""
+        if not hasattr(self, "_logit_count"):
+            return np.empty((n, stride), np.float32)
+        buf = getattr(self, "_logits_buf", None)
+        if buf is None or buf.shape[0] < n or buf.shape[1] != stride:
+            try:
+                import torch
+                self._logits_pin = torch.empty((n, stride), dtype=torch.float32).pin_memory()
+                buf = self._logits_pin.numpy()
+            except Exception:
+                buf = np.empty((n, stride), np.float32)
+            self._logits_buf = buf
+        return buf[:n]
+
     def run_decode(self, slots):
         """slots: [(request_id, input_token, sequence_position)] -> [(request_id, success, logits or None)]"""
         n = len(slots)
         arr = (RequestSlotC * max(n, 1))(*[RequestSlotC(*s) for s in slots])
         success = (C.c_uint8 * max(n, 1))()
         stride = getattr(self, "_logit_count", self.H * self.D)
-        logits = np.empty((max(n, 1), stride), np.float32)    # rows are returned as views of this one array
+        logits = self._logits_rows(max(n, 1), stride)          # rows are returned as views of this one array
         got = lib().mlc_executor_run_decode(self._h, arr, n, success, logits.ctypes.data_as(_fp), stride)
         return [(slots[i][0], bool(success[i]), logits[i] if success[i] else None) for i in range(got)]
 
