@@ -655,9 +655,8 @@ static int launch_matvec(mlc_ctx* ctx, MatVecParams p) {
 // ---------------------------------------------------------------------------------------------------
 // The same mat-vec on the fifth-generation tensor cores (batch <= 32, 16-byte aligned rows)
 // ---------------------------------------------------------------------------------------------------
-// mma.sync runs at a fraction of the tensor cores' rate on this GPU (one m16n8k16 per 8 cycles and SM, about
-// 144 TFLOP/s in all), and with 2 x 32 multiply-adds per weight (hi and lo activations, 32 requests) the kernel
-// above is bound by it. Here the products run as tcgen05.mma with the accumulator in tensor memory:
+// mma.sync reaches a fraction of the tensor cores' rate on this GPU, and the kernel above keeps that pipe
+// occupied most of the time. Here the products run as tcgen05.mma with the accumulator in tensor memory:
 //   A = 128 weight rows x 64 columns, the block integers as exact fp16 values, written by 8 dequantising warps
 //       into shared memory in the K-major 128-byte-swizzle layout (4 slots in flight);
 //   B = the chunk's activations, hi and lo fp16 planes [32 requests x 256 columns] in the same layout;
@@ -1092,7 +1091,8 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
 
 // Which kernel: MLC_B200_MATVEC=tcgen05 in the environment selects the tensor-memory kernel for batches of up to
 // 32 requests; the default is the mma.sync kernel, which is the faster of the two as they stand (both are
-// bound by instruction issue in their dequantising, converting and scaling code, not by the tensor cores or HBM).
+// bound by the instructions around the tensor-core work - dequantising, converting, scaling - and by
+// per-launch latency, not by the tensor cores or HBM).
 static bool matvec_tc_enabled() {
     static const bool on = [] {
         const char* e = std::getenv("MLC_B200_MATVEC");
