@@ -486,8 +486,13 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
             mbar_arrive(smem_u32(&bar_p_full[j & 1u]));
         }
         if (ok && n_tiles > 0) {
+            // The last P.V must be complete before O is read. A parity wait tells "phase k done" from "phase
+            // k - 2 done" only if the barrier cannot be two phases behind - and here it can: this warp may have
+            // finished the last page's softmax (its scores were issued early) while P.V of the page before is
+            // still running. So the wait is taken in two steps, each at most one phase ahead of the barrier.
             where = 0x23;
-            ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 1) & 1u);
+            if (n_tiles >= 2) ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 2) & 1u);
+            ok = ok && mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 1) & 1u);
         }
         if (!ok) {
             give_up(where, at);
