@@ -482,17 +482,24 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ, const __gr
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
+            // Every warp follows bar_pv_done phase by phase: a parity wait tells "phase k done" from "phase k - 2
+            // done" only for a waiter that is at most one phase behind, and a warp that only waited when it had to
+            // rescale O could reach the epilogue's wait two phases behind (the last page's scores are issued
+            // early, so its softmax can finish while P.V of the page before still runs) and read O too soon.
+            // Waiting here costs nothing: P.V of this page cannot start before the one before it has finished,
+            // and it cannot have been issued yet (this warp has not arrived), so the barrier is 0 or 1 phases on.
+            if (j > 0) {
+                where = 0x24;
+                ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (j - 1) & 1u);
+                if (!ok) break;
+            }
             tc_fence_before();
             mbar_arrive(smem_u32(&bar_p_full[j & 1u]));
         }
         if (ok && n_tiles > 0) {
-            // The last P.V must be complete before O is read. A parity wait tells "phase k done" from "phase
-            // k - 2 done" only if the barrier cannot be two phases behind - and here it can: this warp may have
-            // finished the last page's softmax (its scores were issued early) while P.V of the page before is
-            // still running. So the wait is taken in two steps, each at most one phase ahead of the barrier.
+            // the last P.V must be complete before O is read (this warp has seen every earlier phase, see above)
             where = 0x23;
-            if (n_tiles >= 2) ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 2) & 1u);
-            ok = ok && mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 1) & 1u);
+            ok = mbar_wait_bounded(smem_u32(&bar_pv_done), (n_tiles - 1) & 1u);
         }
         if (!ok) {
             give_up(where, at);

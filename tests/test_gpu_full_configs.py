@@ -197,9 +197,9 @@ def test_config5_full_size(executor, oracle_mod):
 
 def test_config5_launches_repeat_bit_for_bit(executor):
     """The prefill kernel's result must not depend on timing: the same launch repeated gives the same bits.
-    (A parity wait in its epilogue could pass two barrier phases early - when a warp finished the last page's
-    softmax while P.V of the page before was still running - and O was then read without the last two pages;
-    rare, and visible only as run-to-run differences in one warp's rows.)"""
+    (A parity wait in its epilogue could pass two barrier phases early - when a warp that had not followed the
+    barrier phase by phase finished the last page's softmax while P.V of the page before was still running - and
+    O was then read without the last two pages; rare, and visible only as run-to-run differences in one warp's rows.)"""
     import torch
     N, cached, new = 8, 1536, 512
     case = synth.make_case(0xBEEF + 5, np.full(N, cached + new, np.uint32), P=64, fill=False, **synth.SHAPE_B)
