@@ -10,6 +10,7 @@
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include "ctx.hpp"
 
@@ -19,6 +20,16 @@ namespace runtime {
 BatchedWalker::~BatchedWalker() {
     if (logits_pinned_) cudaFreeHost(logits_pinned_);
 }
+
+// NVTX range for the lifetime of the object: a pass, and inside a model pass every layer, show up by name in a
+// timeline tool (where the reference prints its MLC_BATCHED_PROFILE table, batched_walker.cpp:100-125). Without a
+// tool attached the calls do nothing.
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 // MLC_B200_WALKER_TRACE=1 in the environment: one line per model pass on stderr with the host time of its phases.
 static bool walker_trace() {
@@ -35,6 +46,7 @@ static double now_us() {
 BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, const LogitsSink* sink) {
     BatchedDecodeOutput out;
     if (slots.empty()) return out;
+    NvtxRange pass_range("mlc decode pass");
     const double t_start = walker_trace() ? now_us() : 0.0;
     PagedAttentionExecutor& ex = exec_;
     mlc_ctx* ctx = ex.ctx_;
@@ -310,7 +322,10 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
     }
 
     bool ok = mlc_encode_embedding_q4_0(ctx, m.token_embd, row_h, tokens, N, hidden, vocab, residual) == MLC_OK;
+    char range_name[32];
     for (uint32_t L = 0; ok && L < ex.L_; ++L) {
+        std::snprintf(range_name, sizeof(range_name), "mlc layer %u", L);
+        NvtxRange layer_range(range_name);
         const LayerWeights& w = m.layers[L];
         void* kp = storage->k_buffer(L);
         void* vp = storage->v_buffer(L);
@@ -351,6 +366,7 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                  mlc_encode_add_batched(ctx, resid1, ffn_down, residual, N * hidden) == MLC_OK;
         }
     }
+    NvtxRange head_range("mlc final norm + lm_head");
     const size_t head_stride = m.lm_head_quant == 1 ? hidden / 256 * 210 : row_h;
     if (fused) {
         ok = ok && mlc_encode_rms_norm_batched_packed(ctx, residual, m.output_norm, eps, N, hidden, nullptr, final_n) == MLC_OK &&
