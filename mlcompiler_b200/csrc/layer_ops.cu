@@ -659,25 +659,29 @@ static int launch_matvec(mlc_ctx* ctx, MatVecParams p) {
 // occupied most of the time. Here the products run as tcgen05.mma with the accumulator in tensor memory:
 //   A = 128 weight rows x 64 columns, the block integers as exact fp16 values, written by 8 dequantising warps
 //       into shared memory in the K-major 128-byte-swizzle layout (4 slots in flight);
-//   B = the chunk's activations, hi and lo fp16 planes [32 requests x 256 columns] in the same layout;
-//   D = one 128 x 32 fp32 tile of tensor memory per scale group (a Q4_0 block of 32 columns: 2 k-steps x
-//       {hi, lo} = 4 MMAs; a Q6_K group of 16 columns: 2 MMAs), 8 tiles in flight;
-//   4 epilogue warps (thread = weight row) read each finished tile (tcgen05.ld) and add it, times the row's
-//   fp32 scale of that group, to 32 accumulators in registers - the same arithmetic as above, group by group.
+//   B = the chunk's activations [64 x 256 columns] in the same layout: rows 0..31 the requests' hi parts,
+//       rows 32..63 their lo parts - one MMA of N = 64 instead of two of N = 32 (an MMA of this size costs
+//       about the same to issue whatever its N);
+//   D = one 128 x 64 fp32 tile of tensor memory per scale group (a Q4_0 block of 32 columns: 2 MMAs; a Q6_K
+//       group of 16 columns: 1), 8 tiles in flight;
+//   4 epilogue warps (thread = weight row) read each finished tile (tcgen05.ld), add its hi and lo halves and
+//   add that, times the row's fp32 scale of the group, to 32 accumulators in registers - the same arithmetic
+//   as above, group by group.
 // One warp issues the MMAs. Rings are handed over with mbarriers (every wait bounded: a wait that runs out
 // sets the device error word and the roles wind down). Column slices are CTAs of a cluster and add up through
 // distributed shared memory as above. A CTA owns one 128-row tile.
 constexpr int kTcRows = 128;
-constexpr int kTcN = 32;            // requests per MMA (the batch, padded)
+constexpr int kTcN = 32;            // requests (the batch, padded)
+constexpr int kTcND = 2 * kTcN;     // MMA N: the hi activations of the 32 requests, then their lo parts
 constexpr int kTcChunk = 256;       // columns per chunk: 4 atoms of 64
 constexpr int kTcRawStages = 3;
 constexpr int kTcSlots = 4;         // A atoms in flight
-constexpr int kTcBufs = 8;          // D tiles in flight (32 columns of tensor memory each)
+constexpr int kTcBufs = 8;          // D tiles in flight (64 columns of tensor memory each: all 512)
 constexpr int kTcDequantThreads = 256;
 constexpr int kTcThreads = 128 + kTcDequantThreads + 32;   // epilogue | dequantise + load | MMA issue
 constexpr uint32_t kTcAtomABytes = kTcRows * 128;          // 16 KiB
-constexpr uint32_t kTcAtomBBytes = kTcN * 128;             // 4 KiB
-constexpr uint32_t kTcBPlaneBytes = 4 * kTcAtomBBytes;     // one plane (hi or lo) of a chunk
+constexpr uint32_t kTcAtomBBytes = kTcND * 128;            // 8 KiB: rows 0..31 hi, rows 32..63 lo
+constexpr uint32_t kTcBBytes = 4 * kTcAtomBBytes;          // a chunk's activations
 
 struct TcBars {
     uint64_t raw_full[kTcRawStages], raw_empty[kTcRawStages], raw_done[kTcRawStages];
@@ -708,9 +712,9 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
     // the swizzled tiles need 1024-byte alignment: the launch asks for 1 KiB more than the layout takes
     uint8_t* smem = smem_unaligned + ((1024u - (tc::smem_u32(smem_unaligned) & 1023u)) & 1023u);
     const uint32_t base = tc::smem_u32(smem);
-    const uint32_t sB = base;                                    // two buffers of {hi plane, lo plane}
-    const uint32_t sA = sB + 4 * kTcBPlaneBytes;                 // kTcSlots atoms
-    uint8_t* raw = smem + 4 * kTcBPlaneBytes + kTcSlots * kTcAtomABytes;
+    const uint32_t sB = base;                                    // two buffers of a chunk's activations
+    const uint32_t sA = sB + 2 * kTcBBytes;                      // kTcSlots atoms
+    uint8_t* raw = smem + 2 * kTcBBytes + kTcSlots * kTcAtomABytes;
     const uint32_t raw_bytes = kTcRows * p.w_pitch;
     TcBars& bars = *reinterpret_cast<TcBars*>(raw + kTcRawStages * raw_bytes);
     float* red = reinterpret_cast<float*>(raw);                  // [32][128 + 4], over the raw ring once it is done
@@ -744,8 +748,8 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // rows of B past the batch stay zero for the whole kernel
-    for (uint32_t i = tid; i < 4 * kTcBPlaneBytes / 16; i += kTcThreads) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (warp == 12) tc::tmem_alloc(tc::smem_u32(&bars.tmem_slot), kTcBufs * kTcN);
+    for (uint32_t i = tid; i < 2 * kTcBBytes / 16; i += kTcThreads) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (warp == 12) tc::tmem_alloc(tc::smem_u32(&bars.tmem_slot), kTcBufs * kTcND);
     tc::fence_proxy_async_smem();
     tc::fence_before();
     __syncthreads();
@@ -814,8 +818,9 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
 #pragma unroll
         for (int e = 0; e < 8; ++e)
             x_off[e] = ((dt & 63) >> 4) * kTcAtomBBytes + tc::sw128_offset(e * 4 + (dt >> 6), ((dt & 63) & 15) * 4);
+        // the lo row of request n is row 32 + n of the tile: 4 groups of 8 rows = 4096 bytes further, same swizzle
         auto store_x = [&](uint32_t bb) {
-            uint8_t* bdst = smem + bb * 2 * kTcBPlaneBytes;
+            uint8_t* bdst = smem + bb * kTcBBytes;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const uint32_t n = e * 4 + (dt >> 6);
@@ -838,7 +843,7 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
                 const uint32_t off = x_off[e];
                 if (n < p.batch) {
                     *reinterpret_cast<uint2*>(bdst + off) = make_uint2(h01, h23);
-                    *reinterpret_cast<uint2*>(bdst + kTcBPlaneBytes + off) = make_uint2(l01, l23);
+                    *reinterpret_cast<uint2*>(bdst + 4096 + off) = make_uint2(l01, l23);
                 }
             }
         };
@@ -871,7 +876,7 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
                 const uint32_t slot = atom_count % kTcSlots;
                 if (atom_count >= kTcSlots &&
                     !tc::mbar_wait_bounded(tc::smem_u32(&bars.a_empty[slot]), ((atom_count / kTcSlots) - 1) & 1u)) { give_up(0, chunk); ok = false; break; }
-                uint8_t* dstA = smem + 4 * kTcBPlaneBytes + slot * kTcAtomABytes;
+                uint8_t* dstA = smem + 2 * kTcBBytes + slot * kTcAtomABytes;
                 const uint32_t col = a * 64 + dhalf * 32;          // this thread's 32 columns inside the chunk
                 uint4 out4[4];
                 if (col < ncols) {
@@ -945,7 +950,7 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (warp == 12) {
         // ---------------- MMA issue: the whole warp walks the loop, one elected lane issues ----------------
-        constexpr uint32_t idesc = tc::idesc_f16_kmajor(kTcRows, kTcN);
+        constexpr uint32_t idesc = tc::idesc_f16_kmajor(kTcRows, kTcND);
         const uint64_t desc = tc::smem_desc_sw128(0, 16, 1024);
         uint32_t atom_count = 0, group_count = 0;
         bool ok = true;
@@ -960,6 +965,9 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
                 ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.a_full[slot]), (atom_count / kTcSlots) & 1u);
                 if (!ok) { give_up(1, chunk); break; }
                 tc::fence_after();
+                // descriptors of this atom's first 16-column step; the start address field counts 16-byte units
+                const uint64_t a_desc = desc | ((sA + slot * kTcAtomABytes) >> 4);
+                const uint64_t b_desc = desc | ((sB + (chunk & 1u) * kTcBBytes + a * kTcAtomBBytes) >> 4);
                 const uint32_t groups = min(static_cast<uint32_t>(kGroupsPerAtom), (ncols - a * 64 + kGroupCols - 1) / kGroupCols);
                 for (uint32_t gi = 0; gi < groups; ++gi, ++group_count) {
                     const uint32_t buf = group_count % kTcBufs;
@@ -969,16 +977,11 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
                         tc::fence_after();
                     }
                     if (tc::elect_one()) {
-                        const uint32_t d = tmem + buf * kTcN;
+                        const uint32_t d = tmem + buf * kTcND;
 #pragma unroll
-                        for (int plane = 1; plane >= 0; --plane) {   // the small terms first: lo plane, then hi
-#pragma unroll
-                            for (int ks = 0; ks < kStepsPerGroup; ++ks) {
-                                const uint32_t kstep = gi * kStepsPerGroup + ks;   // 16-column step inside the atom
-                                const uint32_t a_addr = sA + slot * kTcAtomABytes + kstep * 32;
-                                const uint32_t b_addr = sB + ((chunk & 1u) * 2 + plane) * kTcBPlaneBytes + a * kTcAtomBBytes + kstep * 32;
-                                tc::mma_f16(d, desc | (a_addr >> 4), desc | (b_addr >> 4), idesc, (plane == 1 && ks == 0) ? 0u : 1u);
-                            }
+                        for (int ks = 0; ks < kStepsPerGroup; ++ks) {
+                            const uint32_t kstep = gi * kStepsPerGroup + ks;   // 16-column step inside the atom
+                            tc::mma_f16(d, a_desc + 2 * kstep, b_desc + 2 * kstep, idesc, ks == 0 ? 0u : 1u);   // 32 bytes = 2 units
                         }
                         tc::commit(tc::smem_u32(&bars.d_full[buf]));
                     }
@@ -1022,30 +1025,25 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
                     scale[i] = static_cast<uint32_t>(i) < n_groups ? __fmul_rn(d, static_cast<float>(static_cast<int8_t>(wrow[192 + i]))) : 0.0f;
             }
             tc::mbar_arrive(tc::smem_u32(&bars.raw_empty[stage]));
-            // Two register tiles: the load of group g + 1 is in flight while group g is multiplied and added.
-            uint32_t v[2][32];
-            auto fetch = [&](uint32_t (&dst)[32]) -> bool {   // waits for the next finished tile and starts its load
-                const uint32_t buf = group_count % kTcBufs;
-                bool got = tc::mbar_wait_bounded(tc::smem_u32(&bars.d_full[buf]), (group_count / kTcBufs) & 1u);
-                got = __all_sync(0xffffffffu, got);
-                if (!got) return false;
-                tc::fence_after();
-                tc::tmem_ld32(tmem + lane_base + buf * kTcN, dst);
-                return true;
-            };
-            if (n_groups > 0 && !fetch(v[0])) { ok = false; give_up(2, chunk); break; }
 #pragma unroll
             for (int gi = 0; gi < kGroupsPerChunk; ++gi) {
                 if (static_cast<uint32_t>(gi) >= n_groups) break;
-                tc::tmem_wait_ld();                       // v[gi & 1] is in registers
+                const uint32_t buf = group_count % kTcBufs;
+                ok = tc::mbar_wait_bounded(tc::smem_u32(&bars.d_full[buf]), (group_count / kTcBufs) & 1u);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; give_up(2, chunk); break; }
+                tc::fence_after();
+                uint32_t vh[32], vl[32];
+                tc::tmem_ld32(tmem + lane_base + buf * kTcND, vh);
+                tc::tmem_ld32(tmem + lane_base + buf * kTcND + kTcN, vl);
+                tc::tmem_wait_ld();
                 tc::fence_before();
-                tc::mbar_arrive(tc::smem_u32(&bars.d_empty[group_count % kTcBufs]));
+                tc::mbar_arrive(tc::smem_u32(&bars.d_empty[buf]));
                 ++group_count;
-                if (static_cast<uint32_t>(gi + 1) < n_groups && !fetch(v[(gi + 1) & 1])) { ok = false; give_up(2, chunk); break; }
                 const float sc = scale[gi];
 #pragma unroll
-                for (int n = 0; n < kTcN; ++n) acc[n] = fmaf(sc, __uint_as_float(v[gi & 1][n]), acc[n]);
+                for (int n = 0; n < kTcN; ++n) acc[n] = fmaf(sc, __fadd_rn(__uint_as_float(vl[n]), __uint_as_float(vh[n])), acc[n]);
             }
+            if (!ok) break;
         }
     }
 
@@ -1053,7 +1051,7 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
     tc::fence_before();
     __syncthreads();
     tc::fence_after();
-    if (warp == 12) tc::tmem_dealloc(tmem, kTcBufs * kTcN);
+    if (warp == 12) tc::tmem_dealloc(tmem, kTcBufs * kTcND);
     constexpr uint32_t kPitch = kTcRows + 4;
     if (warp < 4) {
 #pragma unroll
@@ -1120,7 +1118,7 @@ static int launch_matvec_tc(mlc_ctx* ctx, const MatVecParams& mp) {
     const uint32_t tiles = (mp.rows + kTcRows - 1) / kTcRows;
     const uint32_t unit = std::max<uint32_t>(F::kBlockWeights, 64);
     p.w_pitch = weight_pitch(kTcChunk / F::kBlockWeights * F::kBlockBytes);
-    const size_t smem = 4 * kTcBPlaneBytes + kTcSlots * kTcAtomABytes + static_cast<size_t>(kTcRawStages) * kTcRows * p.w_pitch +
+    const size_t smem = 2 * kTcBBytes + kTcSlots * kTcAtomABytes + static_cast<size_t>(kTcRawStages) * kTcRows * p.w_pitch +
                         sizeof(TcBars) + 1024;   // slack for the 1024-byte alignment of the tiles
     auto kernel = quant_matvec_tc_kernel<QT, IN>;
     static bool attr_set[16] = {};
