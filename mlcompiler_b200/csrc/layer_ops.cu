@@ -211,7 +211,9 @@ __global__ void __launch_bounds__(256) embedding_q4_0_kernel(const uint8_t* __re
 // Quantised batched mat-vec
 // ---------------------------------------------------------------------------------------------------
 
-constexpr int kMvRows = 64;         // weight rows per CTA: 4 m-tiles of 16, each worked on by two warps (half the columns each)
+// Weight rows per CTA (the kernel's ROWS): 64 - 4 m-tiles of 16, each worked on by two warps (half the columns
+// each) - or 128 - one m-tile per warp. Every row tile reads the activations again (through L2), so the tall
+// tile pays where a matrix has more row tiles than the GPU holds at once, and costs CTAs where it has few.
 constexpr int kMvThreads = 256;
 constexpr int kMvChunk = 256;       // columns staged in shared memory at a time (a multiple of both block sizes)
 constexpr int kXPadWords = 4;       // words of padding per activation row in shared memory: rows land 4 banks apart
@@ -250,6 +252,14 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 
 // The first cluster barrier publishes every CTA's partial sums (release / acquire); the second only keeps a
 // CTA's shared memory alive until its readers are done and orders nothing.
+// The same with a zero accumulator coming in: d = a . b (no registers to clear beforehand).
+__device__ __forceinline__ void mma16816_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    const float z = 0.0f;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(z));
+}
+
 __device__ __forceinline__ void cluster_sync_publish() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -266,14 +276,16 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_smem_addr, uint32
     return v;
 }
 
-constexpr int kRedPitch = 68;    // floats per batch row of a partial tile (64 rows + 4): lanes t land 8 banks apart
 
 // Shared memory of one pipeline stage: the chunk's activations as fp32 words [kXRows][chunk + 4] (turned in
 // place into {hi, lo} fp16 pairs), with SiLU input a second such array for the `up` half, then the chunk's
-// weight bytes [128][w_pitch].
-template <int QT, int NT, int IN>
+// weight bytes [ROWS][w_pitch].
+template <int QT, int NT, int IN, int ROWS>
 __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecParams p) {
     using F = QuantFormat<QT>;
+    constexpr int kMvRows = ROWS;
+    constexpr int kHalves = 128 / ROWS;     // warps per m-tile, each with its share of every chunk's columns
+    constexpr int kRedPitch = ROWS + 4;     // floats per batch row of a partial tile: lanes t land 8 banks apart
     constexpr int kXRows = NT * 8;
     constexpr int kXArrays = IN == kInSiluMul ? 2 : 1;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -289,7 +301,8 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     const uint32_t c_begin = min(slice * p.slice_cols, p.cols), c_end = min(c_begin + p.slice_cols, p.cols);
     const uint32_t n_chunks = (c_end - c_begin + p.chunk_cols - 1) / p.chunk_cols;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int mt = warp & 3, kh = warp >> 2;   // the warp's m-tile and its half of every chunk's columns
+    const int mt = kHalves == 2 ? (warp & 3) : warp;   // the warp's m-tile
+    const int kh = kHalves == 2 ? (warp >> 2) : 0;     // and its half of every chunk's columns
 
     // Every byte of a chunk arrives by cp.async, issued at once: one round trip to L2 / HBM per chunk, and the
     // next chunk's is under way while this one is computed.
@@ -426,7 +439,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
             const __half2 mul = high ? __floats2half2_rn(0.0625f, 0.0625f) : __floats2half2_rn(1.0f, 1.0f);
             const __half2 add = high ? __floats2half2_rn(-72.0f, -72.0f) : __floats2half2_rn(-1032.0f, -1032.0f);
             const uint32_t byte_off = 2 + 8 * (t & 1);
-            const uint32_t nblk = ncols >> 5, half0 = (nblk + 1) >> 1;
+            const uint32_t nblk = ncols >> 5, half0 = kHalves == 2 ? (nblk + 1) >> 1 : nblk;
             const uint32_t b_lo = kh ? half0 : 0u, b_hi = kh ? nblk : half0;
             for (uint32_t b = b_lo; b < b_hi; ++b) {
                 uint4 bx[NT][2];   // words of columns 8t .. 8t + 7: {hi, lo} x 4 pairs
@@ -455,8 +468,8 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 const uint32_t a01[4] = {ag[0], a8[0], ag[1], a8[1]}, a23[4] = {ag[2], a8[2], ag[3], a8[3]};
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma16816(c, a01, bx[n][0].y, bx[n][0].w);   // the small terms first: lo words
+                    float c[4];
+                    mma16816_zero(c, a01, bx[n][0].y, bx[n][0].w);   // the small terms first: lo words
                     mma16816(c, a23, bx[n][1].y, bx[n][1].w);
                     mma16816(c, a01, bx[n][0].x, bx[n][0].z);
                     mma16816(c, a23, bx[n][1].x, bx[n][1].z);
@@ -469,7 +482,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
         } else {
             // columns [4t, 4t + 4) of a 16-weight group; weight l of a 128-weight half sits in ql / qh as
             // quantization.cpp:1469-1499 lays out
-            const uint32_t ngroups = ncols >> 4, half0 = (ngroups + 1) >> 1;
+            const uint32_t ngroups = ncols >> 4, half0 = kHalves == 2 ? (ngroups + 1) >> 1 : ngroups;
             const uint32_t j_lo = kh ? half0 : 0u, j_hi = kh ? ngroups : half0;
             const __half2 bias = __floats2half2_rn(1056.0f, 1056.0f);   // 1024 + 32
             for (uint32_t j = j_lo; j < j_hi; ++j) {
@@ -503,8 +516,8 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 }
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma16816(c, a, bx[n].y, bx[n].w);
+                    float c[4];
+                    mma16816_zero(c, a, bx[n].y, bx[n].w);
                     mma16816(c, a, bx[n].x, bx[n].z);
                     acc[n][0] = fmaf(sg, c[0], acc[n][0]);
                     acc[n][1] = fmaf(sg, c[1], acc[n][1]);
@@ -520,10 +533,10 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     // Every warp leaves its partial tile (its m-tile, its half of the columns) in shared memory:
     // red[kh][batch][row], C fragment c0, c1 = (row g, batch 2t, 2t + 1), c2, c3 = (row g + 8, same).
     // The column slices of a row tile are the CTAs of one cluster: after the cluster barrier CTA s adds rows
-    // [s * 64 / S, (s + 1) * 64 / S) of all 2 S partial tiles, slice by slice and half by half, through
+    // [s * ROWS / S, (s + 1) * ROWS / S) of all partial tiles, slice by slice and half by half, through
     // distributed shared memory - no round trip through L2, and the order is fixed, so results repeat bit for
     // bit. The second barrier keeps every CTA's tiles alive until their readers are done.
-    float* red = reinterpret_cast<float*>(smem);   // [2][kXRows][kRedPitch], over the first stage
+    float* red = reinterpret_cast<float*>(smem);   // [kHalves][kXRows][kRedPitch], over the first stage
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -547,8 +560,10 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 const float4 v = ld_cluster_f4(addr0, k);
                 sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
             }
-            const float4 v = ld_cluster_f4(addr1, k);
-            sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
+            if (kHalves == 2) {
+                const float4 v = ld_cluster_f4(addr1, k);
+                sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
+            }
         }
         const size_t o = static_cast<size_t>(bn) * p.rows + row0 + lrow;
         if (vec_out) {
@@ -603,12 +618,13 @@ static uint32_t weight_pitch(uint32_t chunk_bytes) {
 }
 
 // Column slices (= CTAs per cluster, 8 at most, never less than one block per slice): the most slices whose
-// clusters - one per 64-row tile - are all resident at once; if even unsliced tiles do not fit one wave, the
+// clusters - one per row tile - are all resident at once; if even unsliced tiles do not fit one wave, the
 // slicing that leaves the fewest chunks per CTA per wave. A slice is worked through in chunks of kMvChunk columns.
-template <int QT, int NT, int IN>
+template <int QT, int NT, int IN, int ROWS = 64>
 static int launch_matvec_nt(mlc_ctx* ctx, MatVecParams p) {
     using F = QuantFormat<QT>;
-    auto kernel = quant_matvec_kernel<QT, NT, IN>;
+    constexpr int kMvRows = ROWS;
+    auto kernel = quant_matvec_kernel<QT, NT, IN, ROWS>;
     static bool attr_set[16] = {};
     if (ctx->device >= 0 && ctx->device < 16 && !attr_set[ctx->device]) {
         MLCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -624,7 +640,7 @@ static int launch_matvec_nt(mlc_ctx* ctx, MatVecParams p) {
         p.w_pitch = weight_pitch(p.chunk_cols / F::kBlockWeights * F::kBlockBytes);
         const size_t stage = static_cast<size_t>(IN == kInSiluMul ? 2 : 1) * NT * 8 * (p.chunk_cols + kXPadWords) * 4 +
                              static_cast<size_t>(kMvRows) * p.w_pitch;
-        smem = std::max(stage * kMvStages, static_cast<size_t>(2) * NT * 8 * kRedPitch * sizeof(float));
+        smem = std::max(stage * kMvStages, static_cast<size_t>(128 / ROWS) * NT * 8 * (ROWS + 4) * sizeof(float));
     };
     uint32_t best_S = 1;
     uint64_t best_cost = ~0ull;
@@ -648,7 +664,12 @@ static int launch_matvec(mlc_ctx* ctx, MatVecParams p) {
     const uint32_t nt = (p.batch + 7) / 8;
     if (nt <= 1) return launch_matvec_nt<QT, 1, IN>(ctx, p);
     if (nt <= 2) return launch_matvec_nt<QT, 2, IN>(ctx, p);
-    if (nt <= 4) return launch_matvec_nt<QT, 4, IN>(ctx, p);
+    if (nt <= 4) {
+        // measured at 32 requests: 11264 x 2048 30 -> 27 us and 32000 x 2048 65 -> 51 us with the tall tile,
+        // 2048 x 5632 16 -> 20 us; Q6_K's rows are too wide for two tall CTAs per SM
+        if (QT == kQ4_0 && p.rows >= 8192) return launch_matvec_nt<QT, 4, IN, 128>(ctx, p);
+        return launch_matvec_nt<QT, 4, IN>(ctx, p);
+    }
     return launch_matvec_nt<QT, 8, IN>(ctx, p);
 }
 
