@@ -284,7 +284,8 @@ template <int QT, int NT, int IN, int ROWS>
 __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecParams p) {
     using F = QuantFormat<QT>;
     constexpr int kMvRows = ROWS;
-    constexpr int kHalves = 128 / ROWS;     // warps per m-tile, each with its share of every chunk's columns
+    constexpr int MT = ROWS / 64;           // m-tiles per warp: they share the warp's activation fragments
+    constexpr int kHalves = 2;              // warps per m-tile group, each with its half of every chunk's columns
     constexpr int kRedPitch = ROWS + 4;     // floats per batch row of a partial tile: lanes t land 8 banks apart
     constexpr int kXRows = NT * 8;
     constexpr int kXArrays = IN == kInSiluMul ? 2 : 1;
@@ -301,8 +302,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     const uint32_t c_begin = min(slice * p.slice_cols, p.cols), c_end = min(c_begin + p.slice_cols, p.cols);
     const uint32_t n_chunks = (c_end - c_begin + p.chunk_cols - 1) / p.chunk_cols;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int mt = kHalves == 2 ? (warp & 3) : warp;   // the warp's m-tile
-    const int kh = kHalves == 2 ? (warp >> 2) : 0;     // and its half of every chunk's columns
+    const int mt = warp & 3, kh = warp >> 2;   // the warp's group of MT m-tiles and its half of every chunk's columns
 
     // Every byte of a chunk arrives by cp.async, issued at once: one round trip to L2 / HBM per chunk, and the
     // next chunk's is under way while this one is computed.
@@ -361,11 +361,13 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
         asm volatile("cp.async.commit_group;" ::: "memory");   // one group per chunk index, empty or not
     };
 
-    float acc[NT][4];
+    float acc[MT][NT][4];
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[n][e] = 0.0f;
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[m][n][e] = 0.0f;
 
     // Launched as a programmatic dependent of the kernel before it: the first chunk's weights (never written by
     // any kernel) are on their way while that kernel finishes; its output - this kernel's activations - is
@@ -426,8 +428,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
         // Lane t of a quad owns a contiguous run of columns, so its B words are one or two 16-byte loads and its
         // weights a few adjacent bytes: k slots (2t, 2t + 1) and (2t + 8, 2t + 9) of an MMA are two column pairs of
         // that run, once against the {hi, hi} words and once against the {lo, lo} words, with the same A registers.
-        const uint8_t* wg = ws + (mt * 16 + g) * p.w_pitch + w_shift;
-        const uint8_t* w8 = wg + 8 * p.w_pitch;
+        const uint8_t* wg = ws + (mt * MT * 16 + g) * p.w_pitch + w_shift;
         const uint32_t* xrow = xw + g * x_pitch;
 
         if (QT == kQ4_0) {
@@ -439,7 +440,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
             const __half2 mul = high ? __floats2half2_rn(0.0625f, 0.0625f) : __floats2half2_rn(1.0f, 1.0f);
             const __half2 add = high ? __floats2half2_rn(-72.0f, -72.0f) : __floats2half2_rn(-1032.0f, -1032.0f);
             const uint32_t byte_off = 2 + 8 * (t & 1);
-            const uint32_t nblk = ncols >> 5, half0 = kHalves == 2 ? (nblk + 1) >> 1 : nblk;
+            const uint32_t nblk = ncols >> 5, half0 = (nblk + 1) >> 1;
             const uint32_t b_lo = kh ? half0 : 0u, b_hi = kh ? nblk : half0;
             for (uint32_t b = b_lo; b < b_hi; ++b) {
                 uint4 bx[NT][2];   // words of columns 8t .. 8t + 7: {hi, lo} x 4 pairs
@@ -449,40 +450,43 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                     bx[n][0] = xp[0];
                     bx[n][1] = xp[1];
                 }
-                const uint8_t* bg = wg + b * 18;
-                const uint8_t* b8 = w8 + b * 18;
-                const float dg = half_bits_to_float(*reinterpret_cast<const uint16_t*>(bg));
-                const float d8 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(b8));
-                uint32_t ag[4], a8[4];   // pair p = columns 8t + 2p, 8t + 2p + 1
 #pragma unroll
-                for (int pr = 0; pr < 4; ++pr) {
-                    const uint32_t vg = *reinterpret_cast<const uint16_t*>(bg + byte_off + 2 * pr);
-                    const uint32_t v8 = *reinterpret_cast<const uint16_t*>(b8 + byte_off + 2 * pr);
-                    const uint32_t hg = (__byte_perm(vg, 0u, 0x4140) & nib_mask) | 0x64006400u;
-                    const uint32_t h8 = (__byte_perm(v8, 0u, 0x4140) & nib_mask) | 0x64006400u;
-                    const __half2 rg = __hfma2(*reinterpret_cast<const __half2*>(&hg), mul, add);
-                    const __half2 r8 = __hfma2(*reinterpret_cast<const __half2*>(&h8), mul, add);
-                    ag[pr] = *reinterpret_cast<const uint32_t*>(&rg);
-                    a8[pr] = *reinterpret_cast<const uint32_t*>(&r8);
-                }
-                const uint32_t a01[4] = {ag[0], a8[0], ag[1], a8[1]}, a23[4] = {ag[2], a8[2], ag[3], a8[3]};
+                for (int m = 0; m < MT; ++m) {
+                    const uint8_t* bg = wg + m * 16 * p.w_pitch + b * 18;
+                    const uint8_t* b8 = bg + 8 * p.w_pitch;
+                    const float dg = half_bits_to_float(*reinterpret_cast<const uint16_t*>(bg));
+                    const float d8 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(b8));
+                    uint32_t ag[4], a8[4];   // pair p = columns 8t + 2p, 8t + 2p + 1
 #pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                    float c[4];
-                    mma16816_zero(c, a01, bx[n][0].y, bx[n][0].w);   // the small terms first: lo words
-                    mma16816(c, a23, bx[n][1].y, bx[n][1].w);
-                    mma16816(c, a01, bx[n][0].x, bx[n][0].z);
-                    mma16816(c, a23, bx[n][1].x, bx[n][1].z);
-                    acc[n][0] = fmaf(dg, c[0], acc[n][0]);
-                    acc[n][1] = fmaf(dg, c[1], acc[n][1]);
-                    acc[n][2] = fmaf(d8, c[2], acc[n][2]);
-                    acc[n][3] = fmaf(d8, c[3], acc[n][3]);
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const uint32_t vg = *reinterpret_cast<const uint16_t*>(bg + byte_off + 2 * pr);
+                        const uint32_t v8 = *reinterpret_cast<const uint16_t*>(b8 + byte_off + 2 * pr);
+                        const uint32_t hg = (__byte_perm(vg, 0u, 0x4140) & nib_mask) | 0x64006400u;
+                        const uint32_t h8 = (__byte_perm(v8, 0u, 0x4140) & nib_mask) | 0x64006400u;
+                        const __half2 rg = __hfma2(*reinterpret_cast<const __half2*>(&hg), mul, add);
+                        const __half2 r8 = __hfma2(*reinterpret_cast<const __half2*>(&h8), mul, add);
+                        ag[pr] = *reinterpret_cast<const uint32_t*>(&rg);
+                        a8[pr] = *reinterpret_cast<const uint32_t*>(&r8);
+                    }
+                    const uint32_t a01[4] = {ag[0], a8[0], ag[1], a8[1]}, a23[4] = {ag[2], a8[2], ag[3], a8[3]};
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) {
+                        float c[4];
+                        mma16816_zero(c, a01, bx[n][0].y, bx[n][0].w);   // the small terms first: lo words
+                        mma16816(c, a23, bx[n][1].y, bx[n][1].w);
+                        mma16816(c, a01, bx[n][0].x, bx[n][0].z);
+                        mma16816(c, a23, bx[n][1].x, bx[n][1].z);
+                        acc[m][n][0] = fmaf(dg, c[0], acc[m][n][0]);
+                        acc[m][n][1] = fmaf(dg, c[1], acc[m][n][1]);
+                        acc[m][n][2] = fmaf(d8, c[2], acc[m][n][2]);
+                        acc[m][n][3] = fmaf(d8, c[3], acc[m][n][3]);
+                    }
                 }
             }
         } else {
             // columns [4t, 4t + 4) of a 16-weight group; weight l of a 128-weight half sits in ql / qh as
             // quantization.cpp:1469-1499 lays out
-            const uint32_t ngroups = ncols >> 4, half0 = kHalves == 2 ? (ngroups + 1) >> 1 : ngroups;
+            const uint32_t ngroups = ncols >> 4, half0 = (ngroups + 1) >> 1;
             const uint32_t j_lo = kh ? half0 : 0u, j_hi = kh ? ngroups : half0;
             const __half2 bias = __floats2half2_rn(1056.0f, 1056.0f);   // 1024 + 32
             for (uint32_t j = j_lo; j < j_hi; ++j) {
@@ -494,35 +498,38 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 const uint32_t ql_off = 64 * h + ((quarter & 1) ? 32 : 0) + 16 * sub + 4 * t;   // q2 / q4 read ql[l + 32]
                 const uint32_t qh_off = 128 + 32 * h + 16 * sub + 4 * t;
                 const uint32_t nib_shift = (quarter >> 1) * 4, hi_shift = quarter * 2;          // q3 / q4: high nibble
-                const uint8_t* bg = wg + blk;
-                const uint8_t* b8 = w8 + blk;
-                const float sg = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t*>(bg + 208)),
-                                           static_cast<float>(static_cast<int8_t>(bg[192 + jj])));
-                const float s8 = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t*>(b8 + 208)),
-                                           static_cast<float>(static_cast<int8_t>(b8[192 + jj])));
-                uint32_t a[4];   // {row g pair 0, row g + 8 pair 0, row g pair 1, row g + 8 pair 1}
 #pragma unroll
-                for (int pr = 0; pr < 2; ++pr) {
+                for (int m = 0; m < MT; ++m) {
+                    const uint8_t* bg = wg + m * 16 * p.w_pitch + blk;
+                    const uint8_t* b8 = bg + 8 * p.w_pitch;
+                    const float sg = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t*>(bg + 208)),
+                                               static_cast<float>(static_cast<int8_t>(bg[192 + jj])));
+                    const float s8 = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t*>(b8 + 208)),
+                                               static_cast<float>(static_cast<int8_t>(b8[192 + jj])));
+                    uint32_t a[4];   // {row g pair 0, row g + 8 pair 0, row g pair 1, row g + 8 pair 1}
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        const uint8_t* bp = r ? b8 : bg;
-                        const uint32_t lo2 = *reinterpret_cast<const uint16_t*>(bp + ql_off + 2 * pr);
-                        const uint32_t hi2 = *reinterpret_cast<const uint16_t*>(bp + qh_off + 2 * pr);
-                        const uint32_t q2 = ((lo2 >> nib_shift) & 0x0F0Fu) | (((hi2 >> hi_shift) & 0x0303u) << 4);
-                        const uint32_t hw = __byte_perm(q2, 0u, 0x4140) | 0x64006400u;
-                        const __half2 rr = __hsub2(*reinterpret_cast<const __half2*>(&hw), bias);
-                        a[2 * pr + r] = *reinterpret_cast<const uint32_t*>(&rr);
+                    for (int pr = 0; pr < 2; ++pr) {
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const uint8_t* bp = r ? b8 : bg;
+                            const uint32_t lo2 = *reinterpret_cast<const uint16_t*>(bp + ql_off + 2 * pr);
+                            const uint32_t hi2 = *reinterpret_cast<const uint16_t*>(bp + qh_off + 2 * pr);
+                            const uint32_t q2 = ((lo2 >> nib_shift) & 0x0F0Fu) | (((hi2 >> hi_shift) & 0x0303u) << 4);
+                            const uint32_t hw = __byte_perm(q2, 0u, 0x4140) | 0x64006400u;
+                            const __half2 rr = __hsub2(*reinterpret_cast<const __half2*>(&hw), bias);
+                            a[2 * pr + r] = *reinterpret_cast<const uint32_t*>(&rr);
+                        }
                     }
-                }
 #pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                    float c[4];
-                    mma16816_zero(c, a, bx[n].y, bx[n].w);
-                    mma16816(c, a, bx[n].x, bx[n].z);
-                    acc[n][0] = fmaf(sg, c[0], acc[n][0]);
-                    acc[n][1] = fmaf(sg, c[1], acc[n][1]);
-                    acc[n][2] = fmaf(s8, c[2], acc[n][2]);
-                    acc[n][3] = fmaf(s8, c[3], acc[n][3]);
+                    for (int n = 0; n < NT; ++n) {
+                        float c[4];
+                        mma16816_zero(c, a, bx[n].y, bx[n].w);
+                        mma16816(c, a, bx[n].x, bx[n].z);
+                        acc[m][n][0] = fmaf(sg, c[0], acc[m][n][0]);
+                        acc[m][n][1] = fmaf(sg, c[1], acc[m][n][1]);
+                        acc[m][n][2] = fmaf(s8, c[2], acc[m][n][2]);
+                        acc[m][n][3] = fmaf(s8, c[3], acc[m][n][3]);
+                    }
                 }
             }
         }
@@ -538,20 +545,23 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     // bit. The second barrier keeps every CTA's tiles alive until their readers are done.
     float* red = reinterpret_cast<float*>(smem);   // [kHalves][kXRows][kRedPitch], over the first stage
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const uint32_t lrow = mt * 16 + g + ((e & 2) ? 8 : 0);
-            const uint32_t bn = n * 8 + 2 * t + (e & 1);
-            red[(kh * kXRows + bn) * kRedPitch + lrow] = acc[n][e];
-        }
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t lrow = (mt * MT + m) * 16 + g + ((e & 2) ? 8 : 0);
+                const uint32_t bn = n * 8 + 2 * t + (e & 1);
+                red[(kh * kXRows + bn) * kRedPitch + lrow] = acc[m][n][e];
+            }
     if (S > 1) cluster_sync_publish(); else __syncthreads();
-    const uint32_t rs4 = (kMvRows / S) >> 2;                 // float4 per batch row in this CTA's share
+    const uint32_t share = ((kMvRows + S - 1) / S + 3u) & ~3u;   // rows this CTA adds up: a multiple of 4, the last CTA's may be short
+    const uint32_t rs4 = share >> 2;                         // float4 per batch row in this CTA's share
     const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
     const bool vec_out = (p.rows & 3u) == 0;
     for (uint32_t i = tid; i < kXRows * rs4; i += kMvThreads) {
-        const uint32_t bn = i / rs4, lrow = slice * (kMvRows / S) + ((i - bn * rs4) << 2);
-        if (bn >= p.batch || row0 + lrow >= p.rows) continue;
+        const uint32_t bn = i / rs4, lrow = slice * share + ((i - bn * rs4) << 2);
+        if (bn >= p.batch || lrow >= kMvRows || row0 + lrow >= p.rows) continue;
         const uint32_t addr0 = red_base + (bn * kRedPitch + lrow) * 4;
         const uint32_t addr1 = addr0 + kXRows * kRedPitch * 4;
         float4 sum = ld_cluster_f4(addr0, 0);
@@ -640,11 +650,11 @@ static int launch_matvec_nt(mlc_ctx* ctx, MatVecParams p) {
         p.w_pitch = weight_pitch(p.chunk_cols / F::kBlockWeights * F::kBlockBytes);
         const size_t stage = static_cast<size_t>(IN == kInSiluMul ? 2 : 1) * NT * 8 * (p.chunk_cols + kXPadWords) * 4 +
                              static_cast<size_t>(kMvRows) * p.w_pitch;
-        smem = std::max(stage * kMvStages, static_cast<size_t>(128 / ROWS) * NT * 8 * (ROWS + 4) * sizeof(float));
+        smem = std::max(stage * kMvStages, static_cast<size_t>(2) * NT * 8 * (ROWS + 4) * sizeof(float));
     };
     uint32_t best_S = 1;
     uint64_t best_cost = ~0ull;
-    for (uint32_t S = 8; S >= 1; S >>= 1) {
+    for (uint32_t S = 8; S >= 1; --S) {
         if (S > 1 && p.cols / S < unit) continue;
         shape(S);
         const uint32_t fit = max_active_clusters(ctx, reinterpret_cast<const void*>(kernel), kMvThreads, smem, S);
