@@ -448,6 +448,15 @@ int mlc_encode_embedding_q4_0(mlc_ctx* ctx, const void* table, size_t row_stride
 int mlc_encode_matmul_quant_fused(mlc_ctx* ctx, int quant, const void* weights, const void* in, size_t in_stride,
                                   int input_kind, const void* residual, size_t batch, size_t rows, size_t cols,
                                   size_t row_stride, void* out);
+/* The gate | up projection with SiLU(gate) * up in its epilogue (batched_walker.cpp:364-394 in one launch):
+ * weights = 2 * ffn_inner rows, the gate rows first, then the up rows (the layout of the walker's fused
+ * ffn_gate_up tensor). Every row tile holds gate rows and the up rows that go with them, so the kernel that
+ * has added up a gate sum also holds its up sum; packed [batch, ffn_inner] receives SiLU(gate) * up in the
+ * operand format (input_kind 2 of the next mat-vec, the down projection). input_kind 0 or 2 as above.
+ * ffn_inner must be divisible by 4. */
+int mlc_encode_matmul_gate_up_silu_packed(mlc_ctx* ctx, int quant, const void* weights, const void* in, size_t in_stride,
+                                          int input_kind, size_t batch, size_t ffn_inner, size_t cols, size_t row_stride,
+                                          void* packed);
 /* RMSNorm whose output goes to `packed` in the mat-vec kernel's operand format: per pair of columns
  * the 32-bit words {fp16(y0), fp16(y1)} and {fp16(y0 - hi0), fp16(y1 - hi1)} - 22 bits of every value,
  * in a buffer of the fp32 output's size. out (fp32) may be NULL. length must be divisible by 4. */

@@ -80,6 +80,7 @@ _PROTOTYPES = {
     "mlc_encode_matmul_q4_0_batched": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp]),
     "mlc_encode_matmul_q6k_batched": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp]),
     "mlc_encode_matmul_quant_fused": (_i, [_vp, _i, _vp, _vp, _sz, _i, _vp, _sz, _sz, _sz, _sz, _vp]),
+    "mlc_encode_matmul_gate_up_silu_packed": (_i, [_vp, _i, _vp, _vp, _sz, _i, _sz, _sz, _sz, _sz, _vp]),
     "mlc_compute_rotary_coefficients": (_i, [_sz, _sz, _f, _f, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mlc_exchange_create": (_i, [_vp, _i, _i, _sz, _sz, C.POINTER(_vp)]),
     "mlc_exchange_handle": (_i, [_vp, _vp, _vp]),
@@ -474,6 +475,13 @@ class Executor:
             self._h, quant, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), in_stride, int(input_kind),
             _vp(_ptr(residual_buf)) if residual_buf is not None else None, batch, rows, cols, row_stride,
             _vp(_ptr(out_buf))))
+
+    def encodeMatMulGateUpSiluPacked(self, quant, weights_buf, in_buf, in_stride, input_kind, batch, ffn_inner, cols,
+                                     row_stride, packed_buf) -> bool:
+        """gate | up projection with SiLU(gate) * up in its epilogue, written in operand format [batch, ffn_inner]."""
+        return self.status(self._lib.mlc_encode_matmul_gate_up_silu_packed(
+            self._h, quant, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), in_stride, int(input_kind), batch, ffn_inner, cols,
+            row_stride, _vp(_ptr(packed_buf))))
 
     def encodeAddBatched(self, a_buf, b_buf, out_buf, total_elements) -> bool:
         """metal_runtime.hpp:501-502."""

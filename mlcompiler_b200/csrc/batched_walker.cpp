@@ -343,9 +343,10 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                  mlc_encode_matmul_quant_fused(ctx, 0, w.attn_output, attn_mix, hidden, 0, residual, N, hidden, hidden,
                                                row_h, resid1) == MLC_OK &&
                  mlc_encode_rms_norm_batched_packed(ctx, resid1, w.ffn_norm, eps, N, hidden, nullptr, norm_o) == MLC_OK &&
-                 mlc_encode_matmul_quant_fused(ctx, 0, w.ffn_gate_up, norm_o, hidden, 2, nullptr, N, 2 * inner, hidden, row_h,
-                                               gate_up) == MLC_OK &&
-                 mlc_encode_matmul_quant_fused(ctx, 0, w.ffn_down, gate_up, 2 * inner, 1, resid1, N, hidden, inner, row_i,
+                 // SiLU(gate) * up leaves the gate | up kernel as operand words [N, inner] (in the gate_up scratch)
+                 mlc_encode_matmul_gate_up_silu_packed(ctx, 0, w.ffn_gate_up, norm_o, hidden, 2, N, inner, hidden, row_h,
+                                                       gate_up) == MLC_OK &&
+                 mlc_encode_matmul_quant_fused(ctx, 0, w.ffn_down, gate_up, inner, 2, resid1, N, hidden, inner, row_i,
                                                residual) == MLC_OK;
         } else {
             ok = mlc_encode_qkv_split_rope_cast(ctx, qkv, q, k32, v32, k16, v16, cos_t, sin_t, N, H, KVH, D, qkv_rows,

@@ -240,6 +240,8 @@ struct MatVecParams {
     uint32_t slice_cols;     // columns per slice (a multiple of the block size)
     uint32_t chunk_cols;     // columns staged in shared memory at a time
     uint32_t w_pitch;        // bytes between weight rows in shared memory
+    uint32_t pair_inner;     // 0, or: rows = gate rows [0, pair_inner) then up rows [pair_inner, 2 pair_inner); a row tile is
+                             // half gate rows, half the up rows that go with them, and out gets SiLU(gate) * up as operand words
     uint32_t slices;         // CTAs per cluster
     uint32_t aligned16;      // weights and row_stride on 16-byte boundaries: vector copies
 };
@@ -299,6 +301,13 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     const uint32_t S = p.slices;
     const uint32_t tile = blockIdx.x / S, slice = blockIdx.x - tile * S;
     const uint32_t row0 = tile * kMvRows;
+    constexpr uint32_t kPairHalf = kMvRows / 2;
+    // weight row behind row r of the tile (rows past the matrix repeat its last row; their sums are never stored)
+    auto weight_row = [&](uint32_t r) -> uint32_t {
+        if (!p.pair_inner) return min(row0 + r, p.rows - 1);
+        const uint32_t up = r >= kPairHalf ? 1u : 0u;
+        return up * p.pair_inner + min(tile * kPairHalf + r - up * kPairHalf, p.pair_inner - 1);
+    };
     const uint32_t c_begin = min(slice * p.slice_cols, p.cols), c_end = min(c_begin + p.slice_cols, p.cols);
     const uint32_t n_chunks = (c_end - c_begin + p.chunk_cols - 1) / p.chunk_cols;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -321,7 +330,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 if (v < nvec) {
 #pragma unroll
                     for (uint32_t r = tid >> 4; r < kMvRows; r += kMvThreads / 16) {
-                        const uint32_t row = min(row0 + r, p.rows - 1);
+                        const uint32_t row = weight_row(r);
                         const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(ws + r * p.w_pitch + v * 16));
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
                                      "l"(p.w + static_cast<size_t>(row) * p.row_stride + a0 + v * 16) : "memory");
@@ -332,7 +341,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 const uint32_t n16 = (b1 - b0) >> 1, w_shift = b0 & 15u;
                 for (uint32_t i = tid; i < kMvRows * n16; i += kMvThreads) {
                     const uint32_t r = i / n16, v = i - r * n16;
-                    const uint32_t row = min(row0 + r, p.rows - 1);
+                    const uint32_t row = weight_row(r);
                     const uint16_t d = __ldg(reinterpret_cast<const uint16_t*>(p.w + static_cast<size_t>(row) * p.row_stride + b0) + v);
                     *reinterpret_cast<uint16_t*>(ws + static_cast<size_t>(r) * p.w_pitch + w_shift + v * 2) = d;
                 }
@@ -555,13 +564,9 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 red[(kh * kXRows + bn) * kRedPitch + lrow] = acc[m][n][e];
             }
     if (S > 1) cluster_sync_publish(); else __syncthreads();
-    const uint32_t share = ((kMvRows + S - 1) / S + 3u) & ~3u;   // rows this CTA adds up: a multiple of 4, the last CTA's may be short
-    const uint32_t rs4 = share >> 2;                         // float4 per batch row in this CTA's share
     const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
-    const bool vec_out = (p.rows & 3u) == 0;
-    for (uint32_t i = tid; i < kXRows * rs4; i += kMvThreads) {
-        const uint32_t bn = i / rs4, lrow = slice * share + ((i - bn * rs4) << 2);
-        if (bn >= p.batch || lrow >= kMvRows || row0 + lrow >= p.rows) continue;
+    // rows [lrow, lrow + 4) of batch row bn, added up over the cluster's partial tiles in slice order
+    auto sum_tiles = [&](uint32_t bn, uint32_t lrow) -> float4 {
         const uint32_t addr0 = red_base + (bn * kRedPitch + lrow) * 4;
         const uint32_t addr1 = addr0 + kXRows * kRedPitch * 4;
         float4 sum = ld_cluster_f4(addr0, 0);
@@ -570,23 +575,48 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
                 const float4 v = ld_cluster_f4(addr0, k);
                 sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
             }
-            if (kHalves == 2) {
-                const float4 v = ld_cluster_f4(addr1, k);
-                sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
-            }
+            const float4 v = ld_cluster_f4(addr1, k);
+            sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
         }
-        const size_t o = static_cast<size_t>(bn) * p.rows + row0 + lrow;
-        if (vec_out) {
-            if (p.residual) {
-                const float4 r = *reinterpret_cast<const float4*>(p.residual + o);
-                sum = make_float4(__fadd_rn(r.x, sum.x), __fadd_rn(r.y, sum.y), __fadd_rn(r.z, sum.z), __fadd_rn(r.w, sum.w));
-            }
-            *reinterpret_cast<float4*>(p.out + o) = sum;
-        } else {
-            const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+        return sum;
+    };
+    if (p.pair_inner) {
+        // CTA s finishes gate rows [s * share, (s + 1) * share) of the tile and the up rows that go with them
+        const uint32_t share = ((kPairHalf + S - 1) / S + 3u) & ~3u, rs4 = share >> 2;
+        for (uint32_t i = tid; i < kXRows * rs4; i += kMvThreads) {
+            const uint32_t bn = i / rs4, lrow = slice * share + ((i - bn * rs4) << 2);
+            const uint32_t col = tile * kPairHalf + lrow;   // column of the [batch, pair_inner] output
+            if (bn >= p.batch || lrow >= kPairHalf || col >= p.pair_inner) continue;
+            const float4 gt = sum_tiles(bn, lrow), up = sum_tiles(bn, lrow + kPairHalf);
+            const float4 r = make_float4(silu_mul(gt.x, up.x), silu_mul(gt.y, up.y), silu_mul(gt.z, up.z), silu_mul(gt.w, up.w));
+            const __half2 h01 = __floats2half2_rn(r.x, r.y), h23 = __floats2half2_rn(r.z, r.w);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const __half2 l01 = __floats2half2_rn(r.x - f01.x, r.y - f01.y), l23 = __floats2half2_rn(r.z - f23.x, r.w - f23.y);
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p.out) + static_cast<size_t>(bn) * p.pair_inner + col) =
+                make_uint4(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&l01),
+                           *reinterpret_cast<const uint32_t*>(&h23), *reinterpret_cast<const uint32_t*>(&l23));
+        }
+    } else {
+        const uint32_t share = ((kMvRows + S - 1) / S + 3u) & ~3u;   // rows this CTA adds up: a multiple of 4, the last CTA's may be short
+        const uint32_t rs4 = share >> 2;                             // float4 per batch row in this CTA's share
+        const bool vec_out = (p.rows & 3u) == 0;
+        for (uint32_t i = tid; i < kXRows * rs4; i += kMvThreads) {
+            const uint32_t bn = i / rs4, lrow = slice * share + ((i - bn * rs4) << 2);
+            if (bn >= p.batch || lrow >= kMvRows || row0 + lrow >= p.rows) continue;
+            float4 sum = sum_tiles(bn, lrow);
+            const size_t o = static_cast<size_t>(bn) * p.rows + row0 + lrow;
+            if (vec_out) {
+                if (p.residual) {
+                    const float4 r = *reinterpret_cast<const float4*>(p.residual + o);
+                    sum = make_float4(__fadd_rn(r.x, sum.x), __fadd_rn(r.y, sum.y), __fadd_rn(r.z, sum.z), __fadd_rn(r.w, sum.w));
+                }
+                *reinterpret_cast<float4*>(p.out + o) = sum;
+            } else {
+                const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (row0 + lrow + e < p.rows) p.out[o + e] = p.residual ? __fadd_rn(p.residual[o + e], vals[e]) : vals[e];
+                for (int e = 0; e < 4; ++e)
+                    if (row0 + lrow + e < p.rows) p.out[o + e] = p.residual ? __fadd_rn(p.residual[o + e], vals[e]) : vals[e];
+            }
         }
     }
     if (S > 1) cluster_sync_relaxed();
@@ -640,7 +670,7 @@ static int launch_matvec_nt(mlc_ctx* ctx, MatVecParams p) {
         MLCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set[ctx->device] = true;
     }
-    const uint32_t tiles = (p.rows + kMvRows - 1) / kMvRows;
+    const uint32_t tiles = p.pair_inner ? (p.pair_inner + kMvRows / 2 - 1) / (kMvRows / 2) : (p.rows + kMvRows - 1) / kMvRows;
     const uint32_t unit = F::kBlockWeights;
     size_t smem = 0;
     auto shape = [&](uint32_t S) {
@@ -1289,7 +1319,8 @@ int mlc_encode_embedding_q4_0(mlc_ctx* ctx, const void* table, size_t row_stride
 }
 
 static int encode_matvec(mlc_ctx* ctx, int qt, int in_mode, const void* weights, const void* in, const void* residual,
-                         size_t batch, size_t rows, size_t cols, size_t row_stride, size_t x_stride, void* out) {
+                         size_t batch, size_t rows, size_t cols, size_t row_stride, size_t x_stride, void* out,
+                         size_t pair_inner = 0) {
     if (!ctx) return MLC_ERR_INVALID_ARG;
     if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
     int st = check_matvec(ctx, qt, weights, in, out, batch, rows, cols, row_stride, x_stride);
@@ -1309,7 +1340,8 @@ static int encode_matvec(mlc_ctx* ctx, int qt, int in_mode, const void* weights,
     p.cols = static_cast<uint32_t>(cols);
     p.x_stride = static_cast<uint32_t>(x_stride);
     p.aligned16 = (row_stride % 16 == 0 && reinterpret_cast<uintptr_t>(weights) % 16 == 0) ? 1u : 0u;
-    const bool tcore = matvec_tc_enabled() && p.aligned16 && batch <= static_cast<size_t>(kTcN);
+    p.pair_inner = static_cast<uint32_t>(pair_inner);
+    const bool tcore = !pair_inner && matvec_tc_enabled() && p.aligned16 && batch <= static_cast<size_t>(kTcN);
 #define MLCB_MATVEC_DISPATCH(QT, IN) (tcore ? launch_matvec_tc<QT, IN>(ctx, p) : launch_matvec<QT, IN>(ctx, p))
     if (qt == kQ6_K) {
         if (in_mode == kInSiluMul) return MLCB_MATVEC_DISPATCH(kQ6_K, kInSiluMul);
@@ -1337,6 +1369,18 @@ int mlc_encode_matmul_quant_fused(mlc_ctx* ctx, int quant, const void* weights, 
     if (input_kind < kInPlain || input_kind > kInPacked)
         return ctx ? ctx->fail(MLC_ERR_INVALID_ARG, "unknown input kind") : MLC_ERR_INVALID_ARG;
     return encode_matvec(ctx, quant, input_kind, weights, in, residual, batch, rows, cols, row_stride, in_stride, out);
+}
+
+int mlc_encode_matmul_gate_up_silu_packed(mlc_ctx* ctx, int quant, const void* weights, const void* in, size_t in_stride,
+                                          int input_kind, size_t batch, size_t ffn_inner, size_t cols, size_t row_stride,
+                                          void* packed) {
+    if (quant != kQ4_0 && quant != kQ6_K) return ctx ? ctx->fail(MLC_ERR_INVALID_ARG, "unknown quantisation") : MLC_ERR_INVALID_ARG;
+    if (input_kind != kInPlain && input_kind != kInPacked)
+        return ctx ? ctx->fail(MLC_ERR_INVALID_ARG, "input kind must be 0 or 2") : MLC_ERR_INVALID_ARG;
+    if (ctx && (ffn_inner == 0 || ffn_inner % 4)) return ctx->fail(MLC_ERR_UNSUPPORTED, "ffn_inner must be a positive multiple of 4");
+    if (ctx && ffn_inner >= (size_t(1) << 30)) return ctx->fail(MLC_ERR_UNSUPPORTED, "dimension too large");
+    return encode_matvec(ctx, quant, input_kind, weights, in, nullptr, batch, 2 * ffn_inner, cols, row_stride, in_stride, packed,
+                         ffn_inner);
 }
 
 }  // extern "C"

@@ -218,6 +218,54 @@ def test_packed_activations_give_the_same_bits(executor, kind, batch, rows, cols
     assert torch.equal(want, got2)
 
 
+def _unpack_words(words):
+    """Operand words [batch, n] (int32; per pair of columns {hi0, hi1}, {lo0, lo1}) -> hi + lo as float64 [batch, n]."""
+    h = words.view(np.uint16).view(np.float16).reshape(words.shape[0], -1, 2, 2).astype(np.float64)   # [b, pair, hi|lo, 2]
+    return (h[:, :, 0, :] + h[:, :, 1, :]).reshape(words.shape[0], -1)
+
+
+@pytest.mark.parametrize("kind,batch,inner,hidden", [("q4_0", 32, 5632, 2048), ("q4_0", 5, 100, 64), ("q6_k", 7, 72, 256),
+                                                     ("q4_0", 16, 4100, 256)])
+def test_gate_up_projection_with_silu_epilogue(executor, oracle_mod, kind, batch, inner, hidden):
+    """gate | up mat-vec whose row tiles pair gate rows with their up rows and whose epilogue writes
+    SiLU(gate) * up as operand words: against the oracle's mat-vec + gate_up_split_silu_mul, and - fed to the
+    down projection as input_kind 2 - against the oracle's down projection + add."""
+    import torch
+    rng = np.random.default_rng(inner + hidden)
+    w, stride = _weights(kind, rng, 2 * inner, hidden)
+    x = (rng.standard_normal((batch, hidden)) * 0.5).astype(np.float32)
+    gu, absdot = _oracle_matvec(oracle_mod, kind, w, x, 2 * inner, hidden)
+    gu32 = gu.astype(np.float32)
+    _, _, mix = oracle_mod.gate_up_split_silu_mul(gu32, inner)
+    quant = 0 if kind == "q4_0" else 1
+    dw, dx = _dev(w), _dev(x)
+    words = torch.zeros((batch, inner), device="cuda", dtype=torch.int32)
+    _run(executor, lambda: executor.encodeMatMulGateUpSiluPacked(quant, dw, dx, hidden, 0, batch, inner, hidden, stride, words))
+    got = _unpack_words(words.cpu().numpy())
+    # d(silu(g) u) <= |u| 1.1 dg + |silu(g)| du, the sums' own bound as in test_quant_matvec, + 22-bit words + expf
+    g, u = gu[:, :inner].astype(np.float64), gu[:, inner:2 * inner].astype(np.float64)
+    dg, du = 2e-5 * absdot[:, :inner] + 1e-7, 2e-5 * absdot[:, inner:2 * inner] + 1e-7
+    silu = g / (1 + np.exp(-g))
+    bound = np.abs(u) * 1.1 * dg + np.abs(silu) * du + 2e-5 * np.abs(mix) + 1e-6
+    err = np.abs(got - mix)
+    assert (err <= bound).all(), f"max error {err.max():.3e}, worst excess {(err - bound).max():.3e}"
+    # fed to the down projection as operand words (input_kind 2), with the residual: the oracle's three separate ops
+    if inner % 32 == 0:
+        wd, stride_d = _weights("q4_0", rng, hidden, inner)
+        resid = rng.standard_normal((batch, hidden)).astype(np.float32)
+        down, absdot_d = _oracle_matvec(oracle_mod, "q4_0", wd, mix, hidden, inner)
+        want = oracle_mod.add(resid, down)
+        dwd, dres = _dev(wd), _dev(resid)
+        out = torch.full((batch, hidden), float("nan"), device="cuda")
+        _run(executor, lambda: executor.encodeMatMulQuantFused(0, dwd, words, inner, 2, dres, batch, hidden, inner, stride_d, out))
+        err = np.abs(out.cpu().numpy().astype(np.float64) - want)
+        assert (err <= 4e-5 * absdot_d + 1e-6 * (1 + np.abs(want))).all(), f"max error {err.max():.3e}"
+    # twice the same bits
+    words2 = torch.zeros_like(words)
+    _run(executor, lambda: executor.encodeMatMulGateUpSiluPacked(quant, dw, dx, hidden, 0, batch, inner, hidden, stride, words2))
+    assert torch.equal(words, words2)
+
+
 def test_layer_ops_argument_rules(executor):
     import torch
     x = torch.zeros((2, 64), device="cuda")
@@ -235,6 +283,8 @@ def test_layer_ops_argument_rules(executor):
     assert not executor.encodeMatMulQ4_0Batched(wq, x, 65, 128, 64, 48, out)      # batch above the limit
     assert not executor.encodeMatMulQ6KBatched(wq, x, 2, 128, 64, 48, out)        # not a whole super-block
     assert not executor.encodeGateUpSplitSiluMul(x, None, None, out, 2, 40, 64)   # row shorter than gate + up
+    assert not executor.encodeMatMulGateUpSiluPacked(0, wq, x, 64, 0, 2, 62, 64, 48, out)   # inner not a multiple of 4
+    assert not executor.encodeMatMulGateUpSiluPacked(0, wq, x, 64, 1, 2, 64, 64, 48, out)   # SiLU input makes no sense here
     assert executor.encodeAddBatched(x, x, out, 0)                                # nothing to do is not an error
     assert executor.flushForwardPassCB(), executor.last_error()
 
