@@ -114,46 +114,37 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, c
 
     if (ex.model_) {
         // The whole walker step on the device; logits [N, vocab] come back (batched_walker.cpp:461-475).
-        void* logits_dev = nullptr;
-        const double t_plan = walker_trace() ? now_us() : 0.0;
-        bool ok = mlc_pass_begin(ctx) == MLC_OK;
-        ok = ok && encode_model_pass(slots, plan, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos, &logits_dev);
-        const double t_enc = walker_trace() ? now_us() : 0.0;
-        ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
-        const double t_flush = walker_trace() ? now_us() : 0.0;
-        if (!ok || !logits_dev) return fail_all();
-        const size_t vocab = ex.model_->vocab_size;
         // A caller's buffer in page-locked memory takes the rows straight from the device; anything else goes
         // through this walker's page-locked landing area (a copy into pageable memory is several times slower).
+        const size_t vocab = ex.model_->vocab_size;
         bool direct = false;
         if (sink && sink->dst && sink->stride >= vocab) {
             cudaPointerAttributes attr{};
             direct = cudaPointerGetAttributes(&attr, sink->dst) == cudaSuccess && attr.type == cudaMemoryTypeHost;
             cudaGetLastError();   // a pointer the runtime does not know is not an error here
         }
-        if (direct) {
+        if (!direct && logits_pinned_floats_ < N * vocab) {
+            if (logits_pinned_) cudaFreeHost(logits_pinned_);
+            logits_pinned_ = nullptr;
+            logits_pinned_floats_ = 0;
             DeviceGuard guard(ctx->device);
-            if (cudaMemcpy2DAsync(sink->dst, sink->stride * sizeof(float), logits_dev, vocab * sizeof(float), vocab * sizeof(float), N,
-                                  cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
-                cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+            if (cudaHostAlloc(reinterpret_cast<void**>(&logits_pinned_), N * vocab * sizeof(float), cudaHostAllocDefault) !=
+                cudaSuccess)
                 return fail_all();
-        } else {
-            if (logits_pinned_floats_ < N * vocab) {
-                if (logits_pinned_) cudaFreeHost(logits_pinned_);
-                logits_pinned_ = nullptr;
-                logits_pinned_floats_ = 0;
-                DeviceGuard guard(ctx->device);
-                if (cudaHostAlloc(reinterpret_cast<void**>(&logits_pinned_), N * vocab * sizeof(float), cudaHostAllocDefault) !=
-                    cudaSuccess)
-                    return fail_all();
-                logits_pinned_floats_ = N * vocab;
-                ++ctx->allocations;
-            }
-            if (mlc_download(ctx, logits_dev, logits_pinned_, N * vocab * sizeof(float), 0) != MLC_OK) return fail_all();
-            if (sink && sink->dst && sink->stride >= vocab)
-                for (size_t r = 0; r < N; ++r)
-                    std::memcpy(sink->dst + r * sink->stride, logits_pinned_ + r * vocab, vocab * sizeof(float));
+            logits_pinned_floats_ = N * vocab;
+            ++ctx->allocations;
         }
+        const double t_plan = walker_trace() ? now_us() : 0.0;
+        bool ok = mlc_pass_begin(ctx) == MLC_OK;
+        ok = ok && encode_model_pass(slots, plan, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos,
+                                     direct ? sink->dst : logits_pinned_, direct ? sink->stride : vocab);
+        const double t_enc = walker_trace() ? now_us() : 0.0;
+        ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;   // the logits are on the host when this returns
+        const double t_flush = walker_trace() ? now_us() : 0.0;
+        if (!ok) return fail_all();
+        if (!direct && sink && sink->dst && sink->stride >= vocab)
+            for (size_t r = 0; r < N; ++r)
+                std::memcpy(sink->dst + r * sink->stride, logits_pinned_ + r * vocab, vocab * sizeof(float));
         const bool to_sink = sink && sink->dst && sink->stride >= vocab;
         out.per_request.reserve(N);
         for (size_t r = 0; r < N; ++r) {
@@ -165,7 +156,7 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, c
             out.per_request.push_back(std::move(p));
         }
         if (walker_trace())
-            std::fprintf(stderr, "[walker] tables+plan %.0f us | encode %.0f | flush %.0f | logits %.0f | total %.0f\n",
+            std::fprintf(stderr, "[walker] tables+plan %.0f us | encode %.0f | flush + logits %.0f | rows %.0f | total %.0f\n",
                          t_plan - t_start, t_enc - t_plan, t_flush - t_enc, now_us() - t_flush, now_us() - t_start);
         return out;
     }
@@ -256,7 +247,7 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                                       const std::vector<uint32_t>& page_ids, const std::vector<uint32_t>& slot_ids,
                                       const std::vector<uint32_t>& pt_flat, const std::vector<uint32_t>& pt_off,
                                       const std::vector<uint32_t>& seq_lens, const std::vector<uint32_t>& q_pos,
-                                      void** logits_dev) {
+                                      float* logits_host, size_t logits_stride) {
     PagedAttentionExecutor& ex = exec_;
     mlc_ctx* ctx = ex.ctx_;
     PagedKVStorage* storage = ex.storage_;
@@ -369,20 +360,42 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
     }
     NvtxRange head_range("mlc final norm + lm_head");
     const size_t head_stride = m.lm_head_quant == 1 ? hidden / 256 * 210 : row_h;
-    if (fused) {
-        ok = ok && mlc_encode_rms_norm_batched_packed(ctx, residual, m.output_norm, eps, N, hidden, nullptr, final_n) == MLC_OK &&
-             mlc_encode_matmul_quant_fused(ctx, m.lm_head_quant == 1 ? 1 : 0, m.lm_head, final_n, hidden, 2, nullptr, N, vocab,
-                                           hidden, head_stride, logits) == MLC_OK;
-    } else {
-        ok = ok && mlc_encode_rms_norm_batched(ctx, residual, m.output_norm, eps, N, hidden, final_n, nullptr) == MLC_OK;
-        if (ok) {
-            ok = m.lm_head_quant == 1
-                     ? mlc_encode_matmul_q6k_batched(ctx, m.lm_head, final_n, N, vocab, hidden, head_stride, logits) == MLC_OK
-                     : mlc_encode_matmul_q4_0_batched(ctx, m.lm_head, final_n, N, vocab, hidden, row_h, logits) == MLC_OK;
-        }
+    const int head_quant = m.lm_head_quant == 1 ? 1 : 0;
+    ok = ok && (fused ? mlc_encode_rms_norm_batched_packed(ctx, residual, m.output_norm, eps, N, hidden, nullptr, final_n)
+                      : mlc_encode_rms_norm_batched(ctx, residual, m.output_norm, eps, N, hidden, final_n, nullptr)) == MLC_OK;
+    if (!ok) return false;
+    // The lm_head runs as groups of vocabulary rows (one group in the reference's call order): a group's logits
+    // [N, rows of the group] start for the host - page-locked rows, on the copy-back stream - while the next
+    // group is computed, so all but the last group's share of the copy is off the step's critical path.
+    // mlc_pass_flush waits for the last copy.
+    const size_t groups = fused ? 4 : 1;
+    const size_t group_rows = ((vocab + groups - 1) / groups + 63) / 64 * 64;
+    DeviceGuard guard(ctx->device);
+    if (!ctx->d2h_stream && cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking) != cudaSuccess) return false;
+    while (ctx->pass_events.size() < groups + 1) {
+        cudaEvent_t e;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return false;
+        ctx->pass_events.push_back(e);
     }
-    *logits_dev = logits;
-    return ok;
+    size_t g = 0;
+    for (size_t r0 = 0; r0 < vocab; r0 += group_rows, ++g) {
+        const size_t nr = std::min(group_rows, vocab - r0);
+        float* out_g = static_cast<float*>(logits) + N * r0;
+        const uint8_t* w_g = static_cast<const uint8_t*>(m.lm_head) + r0 * head_stride;
+        const int st = fused ? mlc_encode_matmul_quant_fused(ctx, head_quant, w_g, final_n, hidden, 2, nullptr, N, nr, hidden,
+                                                             head_stride, out_g)
+                       : head_quant == 1 ? mlc_encode_matmul_q6k_batched(ctx, w_g, final_n, N, nr, hidden, head_stride, out_g)
+                                         : mlc_encode_matmul_q4_0_batched(ctx, w_g, final_n, N, nr, hidden, head_stride, out_g);
+        if (st != MLC_OK) return false;
+        if (cudaEventRecord(ctx->pass_events[g], ctx->stream) != cudaSuccess ||
+            cudaStreamWaitEvent(ctx->d2h_stream, ctx->pass_events[g], 0) != cudaSuccess ||
+            cudaMemcpy2DAsync(logits_host + r0, logits_stride * sizeof(float), out_g, nr * sizeof(float), nr * sizeof(float), N,
+                              cudaMemcpyDeviceToHost, ctx->d2h_stream) != cudaSuccess)
+            return false;
+    }
+    if (cudaEventRecord(ctx->pass_events[groups], ctx->d2h_stream) != cudaSuccess) return false;
+    ctx->host_pass_done = ctx->pass_events[groups];
+    return true;
 }
 
 

@@ -27,11 +27,12 @@ public:
     std::vector<float> prefill(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor);
 
 private:
-    // The layers of a pass with a model attached: encodes embedding .. lm_head onto the open pass.
+    // The layers of a pass with a model attached: encodes embedding .. lm_head onto the open pass and the copies of
+    // the logits [N, vocab] into page-locked host rows `logits_stride` floats apart.
     bool encode_model_pass(const std::vector<RequestSlot>& slots, mlc_attn_plan* plan, const std::vector<uint32_t>& page_ids,
                            const std::vector<uint32_t>& slot_ids, const std::vector<uint32_t>& pt_flat,
                            const std::vector<uint32_t>& pt_off, const std::vector<uint32_t>& seq_lens,
-                           const std::vector<uint32_t>& q_pos, void** logits_dev);
+                           const std::vector<uint32_t>& q_pos, float* logits_host, size_t logits_stride);
 
     PagedAttentionExecutor& exec_;
     std::vector<float> cos_host_, sin_host_;
