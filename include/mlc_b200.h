@@ -669,6 +669,40 @@ typedef struct mlc_model_desc {
     uint32_t n_layers;
 } mlc_model_desc;
 int mlc_executor_attach_model(mlc_executor* exec, const mlc_model_desc* model);
+/* ---- GGUF files (compiler/frontends/gguf_loader.{hpp,cpp}: GGUFLoader) -------------------------
+ * The container the reference loads its models from, versions 2 and 3: header, typed key / value
+ * metadata, tensor directory (sizes by ggml block format, offsets relative to the aligned end of the
+ * directory, general.alignment honoured), tensor bytes read through a read-only mapping, and the
+ * reference's byte-concatenation of every block's attn_q | attn_k | attn_v and ffn_gate | ffn_up
+ * (Q4_0) into the fused attn_qkv and ffn_gate_up the batched walker multiplies with
+ * (GGUFLoader::concatenateBlockWeights, gguf_loader.cpp:877-943). Version 1 files and damaged files
+ * the reference's recovery heuristics would read on through are rejected with a message.
+ * Functions that can fail take an optional `error` buffer for the message (always terminated).
+ *   mlc_gguf_open                     GGUFLoader(path) + load(); NULL on failure
+ *   mlc_gguf_concatenate_block_weights  number of tensors added, -1 on failure
+ *   mlc_gguf_describe                 everything but the tensor bytes as one JSON object
+ *                                     {version, n_tensors, n_kv, alignment, data_start,
+ *                                      quantization_version, kv: {key: {type, [elem_type,] value}},
+ *                                      tensors: {name: {shape, dtype, offset (absolute; -1 for a
+ *                                      concatenated tensor), n_bytes}}}; returns the bytes needed
+ *                                     including the terminator, copies at most `capacity`
+ *   mlc_gguf_tensor_data              GGUFLoader::loadTensorData: copies min(capacity, n_bytes) bytes
+ *                                     (dst may be NULL) and returns n_bytes, -1 on failure
+ *   mlc_executor_attach_gguf          reads the decoder out of the file - token_embd, per block
+ *                                     attn_norm, attn_qkv, attn_output, ffn_norm, ffn_gate_up, ffn_down,
+ *                                     output_norm, output (or the embedding table when the file ties
+ *                                     them), sizes and rotary / norm constants from the llama.* keys -
+ *                                     uploads the weights into one device allocation the executor owns
+ *                                     and attaches them like mlc_executor_attach_model. mlc_status. */
+typedef struct mlc_gguf mlc_gguf;
+mlc_gguf* mlc_gguf_open(const char* path, char* error, size_t error_capacity);
+void mlc_gguf_close(mlc_gguf* file);
+int mlc_gguf_concatenate_block_weights(mlc_gguf* file, char* error, size_t error_capacity);
+size_t mlc_gguf_describe(mlc_gguf* file, char* json, size_t capacity);
+int64_t mlc_gguf_tensor_data(mlc_gguf* file, const char* name, void* dst, size_t capacity, char* error,
+                             size_t error_capacity);
+int mlc_executor_attach_gguf(mlc_executor* exec, mlc_gguf* file, char* error, size_t error_capacity);
+
 /* No counterpart in the reference. Gives a request without pages a context of `tokens` tokens whose
  * K/V rows the caller has put (or will put) into the storage itself: reserves its pages
  * (RequestKVState::reserve) and sets its next position to `tokens`. For restoring a saved context and

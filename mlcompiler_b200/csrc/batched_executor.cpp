@@ -63,6 +63,7 @@ PagedAttentionExecutor::PagedAttentionExecutor(mlc_ctx* ctx, uint32_t num_heads,
 PagedAttentionExecutor::~PagedAttentionExecutor() {
     for (mlc_attn_plan* p : plans_)
         if (p) mlc_attn_plan_destroy(ctx_, p);
+    release_model_arena();
 }
 
 void PagedAttentionExecutor::attach_page_pool(PagePool* pool, uint32_t page_size_tokens) {

@@ -16,12 +16,17 @@
 #include <unordered_map>
 #include <vector>
 
+#include <string>
+
 #include "paged_kv.hpp"
 
 struct mlc_ctx;
 struct mlc_attn_plan;
 
 namespace mlcb {
+namespace gguf {
+class File;
+}
 namespace runtime {
 
 struct RequestSlot {
@@ -116,6 +121,10 @@ public:
     // [vocab_size] per request; a prompt is fed token by token through the decode path
     // (batched_executor.cpp:450-467). Returns false if the description does not fit the executor.
     bool attach_model(const ModelWeights& model);
+    // Reads the model out of a GGUF file (the tensors and metadata keys the reference's walker uses,
+    // batched_walker.cpp:183-190, 248-420; kernel_scheduler.cpp:251-258), uploads the weights into one device
+    // allocation owned by this executor and attaches them. On failure `error` says what is missing or unfit.
+    bool attach_gguf(gguf::File& file, std::string* error);
     bool has_model() const { return model_ != nullptr; }
     // Gives a request that has no pages yet a context of `tokens` tokens whose K/V rows the caller has put
     // (or will put) into the pools itself: pages are reserved and the next position is `tokens`. For
@@ -152,6 +161,8 @@ private:
     uint32_t H_, KVH_, D_, L_;
     std::unique_ptr<IQkvSource> source_;
     std::unique_ptr<ModelWeights> model_;
+    void* model_arena_ = nullptr;   // device memory of a model loaded by attach_gguf
+    void release_model_arena();
     std::unordered_map<uint32_t, PerRequest> requests_;
     PagePool* pool_ = nullptr;
     uint32_t page_size_tokens_ = 64;

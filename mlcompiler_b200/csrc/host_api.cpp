@@ -1,11 +1,14 @@
 // C ABI of the host-side objects: page pool, per-request page state, paged KV storage,
 // paged-attention executor and scheduler (declared in include/mlc_b200.h).
+#include <algorithm>
 #include <cstring>
+#include <string>
 #include <memory>
 #include <vector>
 
 #include "../../include/mlc_b200.h"
 #include "batched_executor.hpp"
+#include "gguf_file.hpp"
 #include "paged_kv.hpp"
 #include "scheduler.hpp"
 
@@ -57,6 +60,11 @@ private:
 struct mlc_executor {
     std::unique_ptr<IBatchedExecutor> exec;
     PagedAttentionExecutor* paged = nullptr;  // non-null when exec is the built-in one
+};
+
+struct mlc_gguf {
+    std::unique_ptr<mlcb::gguf::File> file;
+    std::string json;   // describe_json(), made on demand
 };
 
 struct mlc_scheduler {
@@ -192,6 +200,71 @@ int mlc_executor_attach_model(mlc_executor* e, const mlc_model_desc* d) {
     }
     return e->paged->attach_model(m) ? MLC_OK : MLC_ERR_INVALID_ARG;
 }
+// ---- GGUF ----------------------------------------------------------------------------
+static void copy_message(const std::string& what, char* error, size_t capacity) {
+    if (!error || !capacity) return;
+    const size_t n = std::min(what.size(), capacity - 1);
+    std::memcpy(error, what.data(), n);
+    error[n] = 0;
+}
+mlc_gguf* mlc_gguf_open(const char* path, char* error, size_t error_capacity) {
+    if (error && error_capacity) error[0] = 0;
+    if (!path) { copy_message("null path", error, error_capacity); return nullptr; }
+    try {
+        std::unique_ptr<mlc_gguf> g(new mlc_gguf);
+        g->file.reset(new mlcb::gguf::File(path));
+        return g.release();
+    } catch (const std::exception& e) {
+        copy_message(e.what(), error, error_capacity);
+        return nullptr;
+    }
+}
+void mlc_gguf_close(mlc_gguf* g) { delete g; }
+int mlc_gguf_concatenate_block_weights(mlc_gguf* g, char* error, size_t error_capacity) {
+    if (error && error_capacity) error[0] = 0;
+    if (!g) return -1;
+    try {
+        g->json.clear();
+        return static_cast<int>(g->file->concatenate_block_weights());
+    } catch (const std::exception& e) {
+        copy_message(e.what(), error, error_capacity);
+        return -1;
+    }
+}
+size_t mlc_gguf_describe(mlc_gguf* g, char* json, size_t capacity) {
+    if (!g) return 0;
+    if (g->json.empty()) g->json = g->file->describe_json();
+    if (json && capacity) {
+        const size_t n = std::min(g->json.size(), capacity - 1);
+        std::memcpy(json, g->json.data(), n);
+        json[n] = 0;
+    }
+    return g->json.size() + 1;
+}
+int64_t mlc_gguf_tensor_data(mlc_gguf* g, const char* name, void* dst, size_t capacity, char* error, size_t error_capacity) {
+    if (error && error_capacity) error[0] = 0;
+    if (!g || !name) return -1;
+    try {
+        const mlcb::gguf::TensorInfo* t = g->file->find_tensor(name);
+        if (!t) { copy_message(std::string("no tensor named ") + name, error, error_capacity); return -1; }
+        const uint8_t* p = g->file->data(*t);
+        if (dst) std::memcpy(dst, p, std::min<size_t>(capacity, t->n_bytes));
+        return static_cast<int64_t>(t->n_bytes);
+    } catch (const std::exception& e) {
+        copy_message(e.what(), error, error_capacity);
+        return -1;
+    }
+}
+int mlc_executor_attach_gguf(mlc_executor* e, mlc_gguf* g, char* error, size_t error_capacity) {
+    if (error && error_capacity) error[0] = 0;
+    if (!e || !e->paged || !g) return MLC_ERR_INVALID_ARG;
+    std::string what;
+    g->json.clear();   // attaching may add the concatenated tensors
+    if (e->paged->attach_gguf(*g->file, &what)) return MLC_OK;
+    copy_message(what, error, error_capacity);
+    return MLC_ERR_INVALID_ARG;
+}
+
 int mlc_executor_assume_context(mlc_executor* e, uint32_t request_id, size_t tokens) {
     if (!e || !e->paged) return MLC_ERR_INVALID_ARG;
     return e->paged->assume_context(request_id, tokens) ? MLC_OK : MLC_ERR_INVALID_ARG;

@@ -78,6 +78,12 @@ _PROTOTYPES = {
     "mlc_executor_set_call_order": (_i, [_vp, _i]),
     "mlc_executor_attach_model": (_i, [_vp, C.POINTER(ModelDescC)]),
     "mlc_executor_assume_context": (_i, [_vp, _u32, _sz]),
+    "mlc_gguf_open": (_vp, [C.c_char_p, C.c_char_p, _sz]),
+    "mlc_gguf_close": (None, [_vp]),
+    "mlc_gguf_concatenate_block_weights": (_i, [_vp, C.c_char_p, _sz]),
+    "mlc_gguf_describe": (_sz, [_vp, C.c_char_p, _sz]),
+    "mlc_gguf_tensor_data": (C.c_int64, [_vp, C.c_char_p, _vp, _sz, C.c_char_p, _sz]),
+    "mlc_executor_attach_gguf": (_i, [_vp, _vp, C.c_char_p, _sz]),
     "mlc_executor_run_decode": (_sz, [_vp, C.POINTER(RequestSlotC), _sz, C.POINTER(C.c_uint8), _fp, _sz]),
     "mlc_executor_run_prefill": (_sz, [_vp, _u32, _u64p, _sz, _fp, _sz]),
     "mlc_executor_release_request": (None, [_vp, _u32]),
@@ -221,6 +227,52 @@ class PagedKVStorage:
         return lib().mlc_kv_storage_page_bytes(self._h)
 
 
+class GgufFile:
+    """frontend::GGUFLoader (compiler/frontends/gguf_loader.hpp:60-139): open + load in the constructor (raises
+    RuntimeError with the loader's message), metadata and tensor directory through describe(), tensor bytes through
+    tensor_data(), concatenate_block_weights() as in the reference."""
+
+    def __init__(self, path):
+        err = C.create_string_buffer(512)
+        self._h = lib().mlc_gguf_open(str(path).encode(), err, len(err))
+        if not self._h:
+            raise RuntimeError(err.value.decode(errors="replace"))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().mlc_gguf_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def describe(self) -> dict:
+        import json
+        n = lib().mlc_gguf_describe(self._h, None, 0)
+        buf = C.create_string_buffer(n)
+        lib().mlc_gguf_describe(self._h, buf, n)
+        return json.loads(buf.value.decode("utf-8", errors="surrogateescape"))
+
+    def concatenate_block_weights(self) -> int:
+        err = C.create_string_buffer(512)
+        n = lib().mlc_gguf_concatenate_block_weights(self._h, err, len(err))
+        if n < 0:
+            raise RuntimeError(err.value.decode(errors="replace"))
+        return n
+
+    def tensor_data(self, name: str) -> np.ndarray:
+        err = C.create_string_buffer(512)
+        n = lib().mlc_gguf_tensor_data(self._h, name.encode(), None, 0, err, len(err))
+        if n < 0:
+            raise RuntimeError(err.value.decode(errors="replace"))
+        out = np.zeros(n, np.uint8)
+        lib().mlc_gguf_tensor_data(self._h, name.encode(), out.ctypes.data_as(_vp), n, err, len(err))
+        return out
+
+
 class _ExecutorBase:
     _h = None
 
@@ -279,6 +331,16 @@ class PagedAttentionExecutor(_ExecutorBase):
         ok = lib().mlc_executor_attach_model(self._h, C.byref(desc)) == 0
         if ok:
             self._logit_count = model.vocab_size
+        return ok
+
+    def attach_gguf(self, file: GgufFile) -> bool:
+        """The decoder of a GGUF file: weights uploaded into device memory the executor owns, then attached like
+        attach_model. The reason of a refusal is in self.attach_error."""
+        err = C.create_string_buffer(512)
+        ok = lib().mlc_executor_attach_gguf(self._h, file._h, err, len(err)) == 0
+        self.attach_error = err.value.decode(errors="replace")
+        if ok:
+            self._logit_count = file.describe()["tensors"]["token_embd.weight"]["shape"][1]
         return ok
 
     def _logits_rows(self, n, stride):

@@ -200,3 +200,85 @@ class SyntheticModel:
         import torch
         self.device = {k: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k, v in self.host.items()}
         return self
+
+    def write_gguf(self, path, split_fused=True, version=3, alignment=32, extra_kv=None):
+        """This model as a GGUF file with the keys and tensor names of a Llama checkpoint. split_fused stores
+        attn_q / attn_k / attn_v and ffn_gate / ffn_up apart, as real checkpoints do (a loader then rebuilds the fused
+        tensors by concatenation, compiler/frontends/gguf_loader.cpp:877-943)."""
+        h, D = self.hidden_size, self.head_dim
+        kv = [("general.architecture", "string", "llama"), ("general.name", "string", "synthetic"),
+              ("general.alignment", "u32", alignment), ("general.quantization_version", "u32", 2),
+              ("llama.block_count", "u32", self.n_layers), ("llama.embedding_length", "u32", h),
+              ("llama.feed_forward_length", "u32", self.ffn_inner), ("llama.attention.head_count", "u32", self.num_heads),
+              ("llama.attention.head_count_kv", "u32", self.kv_heads), ("llama.rope.dimension_count", "u32", self.rotary_dim),
+              ("llama.rope.freq_base", "f32", self.rope_base), ("llama.rope.freq_scale", "f32", self.rope_scale),
+              ("llama.attention.layer_norm_rms_epsilon", "f32", self.rms_epsilon)] + list(extra_kv or [])
+        tensors = []
+        q_rows, k_rows = self.num_heads * D, self.kv_heads * D
+        for name, a in self.host.items():
+            if a.dtype == np.float32:
+                tensors.append((name, [a.shape[0]], GGML_F32, a))
+                continue
+            rows = a.shape[0]
+            dtype = GGML_Q6_K if (name == "output.weight" and self.lm_head_quant == "q6_k") else GGML_Q4_0
+            cols = a.shape[1] // 210 * 256 if dtype == GGML_Q6_K else a.shape[1] // 18 * 32
+            if split_fused and name.endswith("attn_qkv.weight"):
+                pre = name[:-len("attn_qkv.weight")]
+                for part, r0, r1 in (("attn_q", 0, q_rows), ("attn_k", q_rows, q_rows + k_rows), ("attn_v", q_rows + k_rows, rows)):
+                    tensors.append((pre + part + ".weight", [cols, r1 - r0], dtype, a[r0:r1]))
+            elif split_fused and name.endswith("ffn_gate_up.weight"):
+                pre = name[:-len("ffn_gate_up.weight")]
+                tensors.append((pre + "ffn_gate.weight", [cols, rows // 2], dtype, a[:rows // 2]))
+                tensors.append((pre + "ffn_up.weight", [cols, rows // 2], dtype, a[rows // 2:]))
+            else:
+                tensors.append((name, [cols, rows], dtype, a))
+        write_gguf(path, kv, tensors, version=version, alignment=alignment)
+
+
+GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q6_K = 0, 1, 2, 14
+_GGUF_TYPES = {"u8": (0, "<B"), "i8": (1, "<b"), "u16": (2, "<H"), "i16": (3, "<h"), "u32": (4, "<I"), "i32": (5, "<i"),
+               "f32": (6, "<f"), "bool": (7, "<B"), "u64": (10, "<Q"), "i64": (11, "<q"), "f64": (12, "<d")}
+
+
+def _gguf_string(s) -> bytes:
+    import struct
+    b = s if isinstance(s, (bytes, bytearray)) else str(s).encode("utf-8")
+    return struct.pack("<Q", len(b)) + bytes(b)
+
+
+def _gguf_value(kind, value) -> bytes:
+    """kind: a scalar name of _GGUF_TYPES, "string", "raw", or ("array", element kind) with a list value."""
+    import struct
+    if isinstance(kind, tuple):
+        elem = kind[1]
+        code = 9 if isinstance(elem, tuple) else 8 if elem == "string" else 13 if elem == "raw" else _GGUF_TYPES[elem][0]
+        return struct.pack("<IQ", code, len(value)) + b"".join(_gguf_value(elem, v) for v in value)
+    if kind in ("string", "raw"):
+        return _gguf_string(value)
+    return struct.pack(_GGUF_TYPES[kind][1], value)
+
+
+def write_gguf(path, kv, tensors, version=3, alignment=32, tensor_padding=b"\x00"):
+    """A GGUF file (version 2 or 3 layout). kv: (key, kind, value) triples, kinds as in _gguf_value; tensors:
+    (name, shape fastest-first, ggml type, numpy array of the stored bytes) - stored in order, each aligned."""
+    import struct
+    out = bytearray(struct.pack("<IIQQ", 0x46554747, version, len(tensors), len(kv)))
+    for key, kind, value in kv:
+        code = 9 if isinstance(kind, tuple) else 8 if kind == "string" else 13 if kind == "raw" else _GGUF_TYPES[kind][0]
+        out += _gguf_string(key) + struct.pack("<I", code) + _gguf_value(kind, value)
+    offsets, cursor = [], 0
+    blobs = [np.ascontiguousarray(a).view(np.uint8).reshape(-1) for _, _, _, a in tensors]
+    for b in blobs:
+        offsets.append(cursor)
+        cursor = (cursor + b.nbytes + alignment - 1) // alignment * alignment
+    for (name, shape, dtype, _), off in zip(tensors, offsets):
+        out += _gguf_string(name) + struct.pack("<I", len(shape)) + b"".join(struct.pack("<Q", d) for d in shape)
+        out += struct.pack("<IQ", dtype, off)
+    out += tensor_padding * ((-len(out)) % alignment)
+    with open(path, "wb") as f:
+        f.write(out)
+        pos = 0
+        for b, off in zip(blobs, offsets):
+            f.write(tensor_padding * (off - pos))
+            f.write(b.tobytes())
+            pos = off + b.nbytes

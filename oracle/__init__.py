@@ -155,6 +155,10 @@ def ref():
         lib.ref_kvstate_release.argtypes = [_vp, _vp]
         _u8p = C.POINTER(C.c_uint8)
         lib.ref_elementwise_node.argtypes = [_i, _fp, _fp, _sz, _fp]
+        lib.ref_gguf_describe.restype = _sz
+        lib.ref_gguf_describe.argtypes = [C.c_char_p, _i, C.c_char_p, _sz]
+        lib.ref_gguf_tensor.restype = C.c_longlong
+        lib.ref_gguf_tensor.argtypes = [C.c_char_p, C.c_char_p, _i, C.c_void_p, _sz]
         for q in ("q4_0", "q6_k"):
             getattr(lib, f"ref_dequant_{q}").restype = None
             getattr(lib, f"ref_dequant_{q}").argtypes = [_u8p, _sz, _fp]
@@ -370,4 +374,34 @@ def matmul_quant_batched(kind: str, weights, x, rows: int, cols: int):
     out = np.zeros((x.shape[0], rows), np.float32)
     getattr(port(), f"orc_matmul_{kind}_batched")(w.ctypes.data_as(_u8p), _p(x, _fp), x.shape[0], rows, cols,
                                                   w.shape[1], _p(out, _fp))
+    return out
+
+
+def reference_gguf_describe(path, concatenate=False):
+    """What the reference's GGUFLoader (compiler/frontends/gguf_loader.cpp: load() 306-433, concatenateBlockWeights()
+    877-943) makes of a file, as the dict the product's mlc_gguf_describe gives (without alignment and data_start,
+    which the loader does not expose). Raises RuntimeError with the loader's message if it throws."""
+    import json
+    lib = ref()
+    assert lib is not None, "the reference library is not available here"
+    cap = 1 << 16
+    while True:
+        buf = C.create_string_buffer(cap)
+        n = lib.ref_gguf_describe(str(path).encode(), 1 if concatenate else 0, buf, cap)
+        if n == 0:
+            raise RuntimeError(buf.value.decode(errors="replace"))
+        if n <= cap:
+            return json.loads(buf.value.decode("utf-8", errors="surrogateescape"))
+        cap = n
+
+
+def reference_gguf_tensor(path, name, concatenate=False):
+    """GGUFLoader::loadTensorData (gguf_loader.cpp:844-875) as a uint8 array; None if the loader refuses."""
+    lib = ref()
+    assert lib is not None, "the reference library is not available here"
+    n = lib.ref_gguf_tensor(str(path).encode(), name.encode(), 1 if concatenate else 0, None, 0)
+    if n < 0:
+        return None
+    out = np.zeros(n, np.uint8)
+    lib.ref_gguf_tensor(str(path).encode(), name.encode(), 1 if concatenate else 0, out.ctypes.data_as(C.c_void_p), n)
     return out

@@ -18,6 +18,7 @@
 // (attention_cpu.cpp:272): the new K/V row is written at `pos` through the
 // reference's fp16 row writer, then every head attends over [0, pos].
 
+#include "frontends/gguf_loader.hpp"
 #include "runtime/attention_cpu.hpp"
 #include "runtime/execution_context.hpp"
 #include "runtime/execution_executor.hpp"
@@ -35,7 +36,9 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
 #include <fstream>
+#include <map>
 #include <memory>
 #include <string>
 #include <vector>
@@ -303,6 +306,156 @@ int ref_elementwise_node(int kind, const float* a, const float* b_or_weight, siz
         ::unlink(path.c_str());
         std::fprintf(stderr, "ref_elementwise_node: %s\n", e.what());
         return -3;
+    }
+}
+
+// ---- the reference's GGUF loader (compiler/frontends/gguf_loader.cpp), dumped in the product's format ----------
+namespace {
+using mlc::frontend::GGUFLoader;
+using mlc::frontend::GGUFValue;
+using mlc::frontend::GGUFValueType;
+
+const char* ref_type_name(GGUFValueType t) {
+    switch (t) {
+        case GGUFValueType::UINT8: return "UINT8";
+        case GGUFValueType::INT8: return "INT8";
+        case GGUFValueType::UINT16: return "UINT16";
+        case GGUFValueType::INT16: return "INT16";
+        case GGUFValueType::UINT32: return "UINT32";
+        case GGUFValueType::INT32: return "INT32";
+        case GGUFValueType::INT64: return "INT64";
+        case GGUFValueType::UINT64: return "UINT64";
+        case GGUFValueType::FLOAT32: return "FLOAT32";
+        case GGUFValueType::FLOAT64: return "FLOAT64";
+        case GGUFValueType::BOOL: return "BOOL";
+        case GGUFValueType::STRING: return "STRING";
+        case GGUFValueType::ARRAY: return "ARRAY";
+        case GGUFValueType::RAW: return "RAW";
+        default: return "?";
+    }
+}
+void ref_json_string(std::string& out, const std::string& s) {
+    out += '"';
+    for (unsigned char ch : s) {
+        if (ch == '"' || ch == '\\') { out += '\\'; out += static_cast<char>(ch); }
+        else if (ch < 0x20) { char b[8]; std::snprintf(b, sizeof(b), "\\u%04x", ch); out += b; }
+        else out += static_cast<char>(ch);
+    }
+    out += '"';
+}
+void ref_json_float(std::string& out, double f, bool single) {
+    if (f != f) { out += "\"nan\""; return; }
+    if (f - f != 0.0) { out += f > 0 ? "\"inf\"" : "\"-inf\""; return; }
+    char b[40];
+    std::snprintf(b, sizeof(b), single ? "%.9g" : "%.17g", f);
+    out += b;
+}
+void ref_json_value(std::string& out, const GGUFValue& v) {
+    switch (v.type) {
+        case GGUFValueType::UINT8: out += std::to_string(std::get<uint8_t>(v.data)); break;
+        case GGUFValueType::INT8: out += std::to_string(std::get<int8_t>(v.data)); break;
+        case GGUFValueType::UINT16: out += std::to_string(std::get<uint16_t>(v.data)); break;
+        case GGUFValueType::INT16: out += std::to_string(std::get<int16_t>(v.data)); break;
+        case GGUFValueType::UINT32: out += std::to_string(std::get<uint32_t>(v.data)); break;
+        case GGUFValueType::INT32: out += std::to_string(std::get<int32_t>(v.data)); break;
+        case GGUFValueType::UINT64: out += std::to_string(std::get<uint64_t>(v.data)); break;
+        case GGUFValueType::INT64: out += std::to_string(std::get<int64_t>(v.data)); break;
+        case GGUFValueType::FLOAT32: ref_json_float(out, std::get<float>(v.data), true); break;
+        case GGUFValueType::FLOAT64: ref_json_float(out, std::get<double>(v.data), false); break;
+        case GGUFValueType::BOOL: out += std::get<bool>(v.data) ? "true" : "false"; break;
+        case GGUFValueType::STRING: ref_json_string(out, std::get<std::string>(v.data)); break;
+        case GGUFValueType::RAW: {
+            out += '"';
+            for (uint8_t ch : std::get<std::vector<uint8_t>>(v.data)) { char b[4]; std::snprintf(b, sizeof(b), "%02x", ch); out += b; }
+            out += '"';
+            break;
+        }
+        case GGUFValueType::ARRAY: {
+            out += '[';
+            const auto& arr = std::get<std::vector<GGUFValue>>(v.data);
+            for (size_t i = 0; i < arr.size(); ++i) {
+                if (i) out += ',';
+                ref_json_value(out, arr[i]);
+            }
+            out += ']';
+            break;
+        }
+        default: out += "null";
+    }
+}
+}  // namespace
+
+// Returns the bytes needed (with terminator), 0 if the loader threw; its message then goes to `json`.
+size_t ref_gguf_describe(const char* path, int concatenate, char* json, size_t capacity) {
+    std::string out;
+    size_t ok = 1;
+    try {
+        GGUFLoader loader(path);
+        loader.load();
+        if (concatenate) loader.concatenateBlockWeights();
+        std::map<std::string, const GGUFValue*> kv;
+        for (const auto& e : loader.kvMetadata()) kv[e.first] = &e.second;
+        std::map<std::string, const mlc::frontend::GGUFTensorInfo*> tensors;
+        for (const auto& e : loader.tensors()) tensors[e.first] = &e.second;
+        out = "{\"version\":" + std::to_string(loader.header().version) + ",\"n_tensors\":" + std::to_string(loader.header().n_tensors) +
+              ",\"n_kv\":" + std::to_string(loader.header().n_kv) + ",\"quantization_version\":" + std::to_string(loader.quantizationVersion()) +
+              ",\"kv\":{";
+        bool first = true;
+        for (const auto& e : kv) {
+            if (!first) out += ',';
+            first = false;
+            ref_json_string(out, e.first);
+            out += std::string(":{\"type\":\"") + ref_type_name(e.second->type) + "\"";
+            if (e.second->type == GGUFValueType::ARRAY) {
+                const auto& arr = std::get<std::vector<GGUFValue>>(e.second->data);
+                // the loader keeps no element type for an empty array
+                out += std::string(",\"elem_type\":\"") + (arr.empty() ? "?" : ref_type_name(arr[0].type)) + "\"";
+            }
+            out += ",\"value\":";
+            ref_json_value(out, *e.second);
+            out += '}';
+        }
+        out += "},\"tensors\":{";
+        first = true;
+        for (const auto& e : tensors) {
+            if (!first) out += ',';
+            first = false;
+            ref_json_string(out, e.first);
+            out += ":{\"shape\":[";
+            for (size_t i = 0; i < e.second->shape.size(); ++i) {
+                if (i) out += ',';
+                out += std::to_string(e.second->shape[i]);
+            }
+            out += "],\"dtype\":" + std::to_string(e.second->dtype) + ",\"offset\":" +
+                   (e.second->offset == UINT64_MAX ? std::string("-1") : std::to_string(e.second->offset)) +
+                   ",\"n_bytes\":" + std::to_string(e.second->n_bytes) + "}";
+        }
+        out += "}}";
+    } catch (const std::exception& e) {
+        out = e.what();
+        ok = 0;
+    }
+    if (json && capacity) {
+        const size_t n = std::min(out.size(), capacity - 1);
+        std::memcpy(json, out.data(), n);
+        json[n] = 0;
+    }
+    return ok ? out.size() + 1 : 0;
+}
+
+// GGUFLoader::loadTensorData; returns n_bytes, -1 if the tensor is unknown or the loader threw.
+long long ref_gguf_tensor(const char* path, const char* name, int concatenate, unsigned char* dst, size_t capacity) {
+    try {
+        GGUFLoader loader(path);
+        loader.load();
+        if (concatenate) loader.concatenateBlockWeights();
+        auto it = loader.tensors().find(name);
+        if (it == loader.tensors().end()) return -1;
+        const std::vector<uint8_t> bytes = loader.loadTensorData(it->second);
+        if (dst) std::memcpy(dst, bytes.data(), std::min(capacity, bytes.size()));
+        return static_cast<long long>(bytes.size());
+    } catch (const std::exception&) {
+        return -1;
     }
 }
 

@@ -1,0 +1,111 @@
+"""GGUF files for the loader tests, written with mlcompiler_b200.synth.write_gguf from seeded data. Used by
+tests/test_gguf.py and by tests/golden/make_gguf_golden.py (which records what the reference's loader makes of them)."""
+import numpy as np
+
+from mlcompiler_b200 import synth
+
+# ggml type -> (weights per block, bytes per block), for sizing the stored bytes of a test tensor
+BLOCKS = {0: (1, 4), 1: (1, 2), 2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 9: (32, 36),
+          10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210), 15: (256, 292),
+          24: (1, 1), 25: (1, 2), 26: (1, 4), 30: (1, 2)}
+
+
+def stored_bytes(shape, dtype):
+    if not shape:
+        return 0
+    n = int(np.prod(shape, dtype=np.int64))
+    w, b = BLOCKS.get(dtype, (1, 4))        # an unknown type counts 4 bytes per element (gguf_loader.cpp:748-750)
+    return -(-n // w) * b
+
+
+def _tensor(rng, name, shape, dtype):
+    return (name, shape, dtype, rng.integers(0, 256, stored_bytes(shape, dtype), dtype=np.uint8))
+
+
+# name -> (version, alignment the file is laid out with, general.alignment as stored, its type)
+ZOO_CASES = {
+    "zoo_v3_a64": (3, 64, 64, "u32"),
+    "zoo_v2_a32": (2, 32, 32, "u32"),
+    "zoo_v3_a0": (3, 32, 0, "u32"),          # 0 means the default of 32
+    "zoo_v3_i64": (3, 128, 128, "i64"),
+    "zoo_v3_neg": (3, 32, -5, "i32"),        # a negative value is ignored
+}
+BLOCK_CASES = ("ok", "f16_k", "cols", "missing_v", "fused_present")
+
+
+def zoo(path, version=3, alignment=64, declared=None, alignment_kind="u32"):
+    """Every metadata type and most tensor types in one small file."""
+    rng = np.random.default_rng(20240607)
+    kv = [
+        ("general.architecture", "string", "llama"),
+        ("general.alignment", alignment_kind, alignment if declared is None else declared),
+        ("general.quantization_version", "u64", 3),
+        ("t.u8", "u8", 250), ("t.i8", "i8", -7), ("t.u16", "u16", 65000), ("t.i16", "i16", -1234),
+        ("t.u32", "u32", 4000000000), ("t.i32", "i32", -2000000000), ("t.u64", "u64", 2 ** 63 + 5), ("t.i64", "i64", -2 ** 62),
+        ("t.f32", "f32", 0.1), ("t.f64", "f64", 1.0 / 3.0), ("t.true", "bool", 1), ("t.false", "bool", 0),
+        ("t.string", "string", 'quote " backslash \\ tab \t newline \n café 日本'),
+        ("t.empty_string", "string", ""),
+        ("t.raw", "raw", bytes(range(0, 40, 3))),
+        ("t.arr_u32", ("array", "u32"), [1, 2, 3, 4000000000]),
+        ("t.arr_i16", ("array", "i16"), [-3, 0, 3]),
+        ("t.arr_f32", ("array", "f32"), [0.5, -1.25, 3.0e10]),
+        ("t.arr_str", ("array", "string"), ["<s>", "</s>", "", "▁the"]),
+        ("t.arr_bool", ("array", "bool"), [1, 0, 1]),
+        ("t.arr_nested", ("array", ("array", "u8")), [[1, 2], [], [3]]),
+        ("t.arr_empty", ("array", "f64"), []),
+        ("t.duplicate", "u32", 1), ("t.duplicate", "u32", 2),      # the later entry wins
+    ]
+    tensors = [
+        _tensor(rng, "f32.vec", [48], 0), _tensor(rng, "f16.mat", [16, 3], 1), _tensor(rng, "q4_0.mat", [64, 5], 2),
+        _tensor(rng, "q4_1.mat", [32, 2], 3), _tensor(rng, "q5_0.mat", [32, 3], 6), _tensor(rng, "q5_1.mat", [64, 1], 7),
+        _tensor(rng, "q8_0.mat", [32, 4], 8), _tensor(rng, "q8_1.mat", [32, 1], 9), _tensor(rng, "q2_k.mat", [256, 2], 10),
+        _tensor(rng, "q3_k.mat", [256, 1], 11), _tensor(rng, "q4_k.mat", [512, 1], 12), _tensor(rng, "q5_k.mat", [256, 1], 13),
+        _tensor(rng, "q6_k.mat", [256, 3], 14), _tensor(rng, "q8_k.mat", [256, 1], 15), _tensor(rng, "i8.vec", [7], 24),
+        _tensor(rng, "i16.vec", [5], 25), _tensor(rng, "i32.vec", [3], 26), _tensor(rng, "i64.as_unknown", [3], 27),
+        _tensor(rng, "f64.as_unknown", [2], 28), _tensor(rng, "bf16.vec", [9], 30), _tensor(rng, "type99", [5, 2], 99),
+        _tensor(rng, "ragged.q4_0", [40, 3], 2),           # 120 weights: 4 blocks
+        _tensor(rng, "rank3", [4, 3, 2], 0), _tensor(rng, "scalar.shape", [], 0),
+        _tensor(rng, "twice", [8], 0), _tensor(rng, "twice", [4, 4], 1),       # the later entry wins
+    ]
+    synth.write_gguf(path, kv, tensors, version=version, alignment=alignment, tensor_padding=b"\xAB")
+    return kv, tensors
+
+
+def blocks(path, case):
+    """Block weights for the concatenation rules (gguf_loader.cpp:877-943). case:
+    "ok": blocks 0, 2 and 10 complete; "f16_k": blk.0.attn_k is F16; "cols": blk.0.ffn_up has other columns;
+    "missing_v": blk.0 has no attn_v; "fused_present": blk.0.attn_qkv is already in the file."""
+    rng = np.random.default_rng(77)
+    cols = 64
+    t = []
+    for blk in (0, 2, 10):
+        pre = f"blk.{blk}."
+        for part, rows in (("attn_q", 8), ("attn_k", 4), ("attn_v", 4), ("ffn_gate", 6), ("ffn_up", 6)):
+            dtype, c = 2, cols
+            if blk == 0 and case == "f16_k" and part == "attn_k":
+                dtype = 1
+            if blk == 0 and case == "cols" and part == "ffn_up":
+                c = 32
+            if blk == 0 and case == "missing_v" and part == "attn_v":
+                continue
+            t.append(_tensor(rng, pre + part + ".weight", [c, rows], dtype))
+    if case == "fused_present":
+        t.append(_tensor(rng, "blk.0.attn_qkv.weight", [cols, 3], 2))
+    t.append(_tensor(rng, "blk.x.attn_q.weight", [cols, 2], 2))       # not a block index: ignored
+    synth.write_gguf(path, [("general.architecture", "string", "llama")], t)
+    return t
+
+
+def canonical(desc):
+    """A loader's description reduced to what both loaders report: no alignment / data_start (the reference does not
+    expose them), no element type for empty arrays (the reference keeps none)."""
+    out = {k: desc[k] for k in ("version", "n_tensors", "n_kv", "quantization_version")}
+    kv = {}
+    for key, v in desc["kv"].items():
+        v = dict(v)
+        if v["type"] == "ARRAY" and not v["value"]:
+            v.pop("elem_type", None)
+        kv[key] = v
+    out["kv"] = kv
+    out["tensors"] = desc["tensors"]
+    return out

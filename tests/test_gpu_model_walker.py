@@ -136,10 +136,13 @@ def test_model_decode_passes_match_the_oracle(executor, oracle_mod, name, shape,
             assert_logits_close(np.stack([o[2] for o in out]), want, f"step {step}")
         for rid in active:
             positions[rid] += 1
-    # launches of a pass: embedding + per layer 8 (fused) or 13 (the reference's ops one for one) + norm + lm_head;
-    # attention may add a merge launch per layer when the planner splits sequences over CTAs
+    # launches of a pass: embedding + per layer 8 (fused) or 13 (the reference's ops one for one) + norm + lm_head
+    # (fused: up to four groups of vocabulary rows, multiples of 64); attention may add a merge launch per layer
+    # when the planner splits sequences over CTAs
     per_layer = 13 if reference_order else 8
-    expect = 1 + layers * per_layer + 2
+    group_rows = -(-(-(-vocab // 4)) // 64) * 64
+    head_launches = 1 if reference_order else -(-vocab // group_rows)
+    expect = 1 + layers * per_layer + 1 + head_launches
     assert expect <= launches[-1] <= expect + layers, launches[-1]
     # the pools, at every (page, slot) a token was written to: layer 0's rows depend on embedding, norm,
     # mat-vec and rotary only; the last layer's on everything before it
