@@ -23,10 +23,15 @@ def _stack(executor, model, capacity=8):
     return pool, storage, ex
 
 
-@pytest.mark.parametrize("head,split,version,alignment", [("q6_k", True, 3, 32), ("q4_0", False, 2, 64)])
-def test_model_from_gguf_equals_model_from_pointers(executor, tmp_path, head, split, version, alignment):
-    model = synth.SyntheticModel(0xF11E, 2, 4, 2, 64, 512, 384, rotary_dim=32, lm_head_quant=head, rope_base=5000.0,
-                                 rms_epsilon=2e-5)
+@pytest.mark.parametrize("shape,head,split,version,alignment", [
+    ((2, 4, 2, 64, 512, 384), "q6_k", True, 3, 32),
+    ((2, 4, 2, 64, 512, 384), "q4_0", False, 2, 64),
+    ((1, 16, 4, 64, 1024, 40000), "q6_k", True, 3, 32),     # a 23 MB and a 34 MB tensor: several staging pieces each
+])
+def test_model_from_gguf_equals_model_from_pointers(executor, tmp_path, shape, head, split, version, alignment):
+    layers, H, KVH, D, inner, vocab = shape
+    model = synth.SyntheticModel(0xF11E, layers, H, KVH, D, inner, vocab, rotary_dim=32, lm_head_quant=head,
+                                 rope_base=5000.0, rms_epsilon=2e-5)
     path = tmp_path / "model.gguf"
     model.write_gguf(path, split_fused=split, version=version, alignment=alignment)
     _, sa, a = _stack(executor, model)
