@@ -154,11 +154,13 @@ std::vector<float> PagedAttentionExecutor::run_prefill(uint32_t request_id, cons
     // With paged storage the reference fills the pages token by token through the decode
     // path (batched_executor.cpp:450-467); that loop is kept for the reference call order.
     // The default feeds the whole chunk at once: scatter of its K/V rows, then chunked causal
-    // attention (tcgen05 kernel for head_dim 128 / 64-token pages).
+    // attention (tcgen05 kernel for head_dim 128 / 64-token pages); with a model attached, the whole step
+    // for 32 prompt tokens per pass.
     std::vector<float> last;
     if (tokens.empty()) return last;
     size_t cursor = known_position(request_id);
     if (order_ == CallOrder::Fused && storage_ && pool_ && !model_) return walker_->prefill(request_id, tokens, cursor);
+    if (order_ == CallOrder::Fused && storage_ && pool_ && model_) return walker_->prefill_model(request_id, tokens, cursor);
     for (uint64_t tok : tokens) {
         std::vector<RequestSlot> slot{{request_id, tok, cursor}};
         BatchedDecodeOutput out = run_decode(slot);

@@ -137,7 +137,7 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, c
         const double t_plan = walker_trace() ? now_us() : 0.0;
         bool ok = mlc_pass_begin(ctx) == MLC_OK;
         ok = ok && encode_model_pass(slots, plan, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos,
-                                     direct ? sink->dst : logits_pinned_, direct ? sink->stride : vocab);
+                                     direct ? sink->dst : logits_pinned_, direct ? sink->stride : vocab, 0);
         const double t_enc = walker_trace() ? now_us() : 0.0;
         ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;   // the logits are on the host when this returns
         const double t_flush = walker_trace() ? now_us() : 0.0;
@@ -247,7 +247,7 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                                       const std::vector<uint32_t>& page_ids, const std::vector<uint32_t>& slot_ids,
                                       const std::vector<uint32_t>& pt_flat, const std::vector<uint32_t>& pt_off,
                                       const std::vector<uint32_t>& seq_lens, const std::vector<uint32_t>& q_pos,
-                                      float* logits_host, size_t logits_stride) {
+                                      float* logits_host, size_t logits_stride, size_t head_first) {
     PagedAttentionExecutor& ex = exec_;
     mlc_ctx* ctx = ex.ctx_;
     PagedKVStorage* storage = ex.storage_;
@@ -361,9 +361,14 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
     NvtxRange head_range("mlc final norm + lm_head");
     const size_t head_stride = m.lm_head_quant == 1 ? hidden / 256 * 210 : row_h;
     const int head_quant = m.lm_head_quant == 1 ? 1 : 0;
-    ok = ok && (fused ? mlc_encode_rms_norm_batched_packed(ctx, residual, m.output_norm, eps, N, hidden, nullptr, final_n)
-                      : mlc_encode_rms_norm_batched(ctx, residual, m.output_norm, eps, N, hidden, final_n, nullptr)) == MLC_OK;
     if (!ok) return false;
+    // Only rows [head_first, N) get logits (a prompt chunk wants its last token's, or none at all)
+    if (head_first >= N) return true;
+    const size_t head_n = N - head_first;
+    const float* head_in = static_cast<const float*>(residual) + head_first * hidden;
+    if ((fused ? mlc_encode_rms_norm_batched_packed(ctx, head_in, m.output_norm, eps, head_n, hidden, nullptr, final_n)
+               : mlc_encode_rms_norm_batched(ctx, head_in, m.output_norm, eps, head_n, hidden, final_n, nullptr)) != MLC_OK)
+        return false;
     // The lm_head runs as groups of vocabulary rows (one group in the reference's call order): a group's logits
     // [N, rows of the group] start for the host - page-locked rows, on the copy-back stream - while the next
     // group is computed, so all but the last group's share of the copy is off the step's critical path.
@@ -380,16 +385,16 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
     size_t g = 0;
     for (size_t r0 = 0; r0 < vocab; r0 += group_rows, ++g) {
         const size_t nr = std::min(group_rows, vocab - r0);
-        float* out_g = static_cast<float*>(logits) + N * r0;
+        float* out_g = static_cast<float*>(logits) + head_n * r0;
         const uint8_t* w_g = static_cast<const uint8_t*>(m.lm_head) + r0 * head_stride;
-        const int st = fused ? mlc_encode_matmul_quant_fused(ctx, head_quant, w_g, final_n, hidden, 2, nullptr, N, nr, hidden,
+        const int st = fused ? mlc_encode_matmul_quant_fused(ctx, head_quant, w_g, final_n, hidden, 2, nullptr, head_n, nr, hidden,
                                                              head_stride, out_g)
-                       : head_quant == 1 ? mlc_encode_matmul_q6k_batched(ctx, w_g, final_n, N, nr, hidden, head_stride, out_g)
-                                         : mlc_encode_matmul_q4_0_batched(ctx, w_g, final_n, N, nr, hidden, head_stride, out_g);
+                       : head_quant == 1 ? mlc_encode_matmul_q6k_batched(ctx, w_g, final_n, head_n, nr, hidden, head_stride, out_g)
+                                         : mlc_encode_matmul_q4_0_batched(ctx, w_g, final_n, head_n, nr, hidden, head_stride, out_g);
         if (st != MLC_OK) return false;
         if (cudaEventRecord(ctx->pass_events[g], ctx->stream) != cudaSuccess ||
             cudaStreamWaitEvent(ctx->d2h_stream, ctx->pass_events[g], 0) != cudaSuccess ||
-            cudaMemcpy2DAsync(logits_host + r0, logits_stride * sizeof(float), out_g, nr * sizeof(float), nr * sizeof(float), N,
+            cudaMemcpy2DAsync(logits_host + r0, logits_stride * sizeof(float), out_g, nr * sizeof(float), nr * sizeof(float), head_n,
                               cudaMemcpyDeviceToHost, ctx->d2h_stream) != cudaSuccess)
             return false;
     }
@@ -398,6 +403,74 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
     return true;
 }
 
+
+std::vector<float> BatchedWalker::prefill_model(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor) {
+    PagedAttentionExecutor& ex = exec_;
+    mlc_ctx* ctx = ex.ctx_;
+    PagedKVStorage* storage = ex.storage_;
+    if (tokens.empty() || !storage || !ex.pool_ || !ex.model_) return {};
+    const uint32_t H = ex.H_, KVH = ex.KVH_, D = ex.D_, P = storage->page_size_tokens();
+    const size_t vocab = ex.model_->vocab_size, cap = storage->capacity_pages();
+    constexpr size_t kChunk = 32;   // tokens per pass: the mat-vec kernels' best batch
+
+    PagedAttentionExecutor::PerRequest& req = ex.ensure_request(request_id);
+    if (!req.page_state) {
+        req.page_state.reset(new RequestKVState());
+        req.page_state->request_id = request_id;
+        req.page_state->page_size_tokens = ex.page_size_tokens_;
+    }
+    if (logits_pinned_floats_ < vocab) {
+        if (logits_pinned_) cudaFreeHost(logits_pinned_);
+        logits_pinned_ = nullptr;
+        logits_pinned_floats_ = 0;
+        DeviceGuard guard(ctx->device);
+        if (cudaHostAlloc(reinterpret_cast<void**>(&logits_pinned_), vocab * sizeof(float), cudaHostAllocDefault) != cudaSuccess)
+            return {};
+        logits_pinned_floats_ = vocab;
+        ++ctx->allocations;
+    }
+    for (size_t done = 0; done < tokens.size(); done += kChunk) {
+        const size_t n = std::min(kChunk, tokens.size() - done);
+        // The chunk's tokens stand in the pass like n requests that share one page table: token i sees the
+        // context up to and including itself (its row and the rows of the chunk's earlier tokens are written
+        // before any attention of the layer runs). A pool that runs out fails the prefill; the pages taken so
+        // far stay with the request until it is released, as in the token loop.
+        std::vector<uint32_t> page_ids(n), slot_ids(n), seq_lens(n), q_pos(n), pt_off(n + 1, 0), pt_flat;
+        std::vector<RequestSlot> slots(n);
+        for (size_t i = 0; i < n; ++i) {
+            auto loc = req.page_state->extend_one_token(*ex.pool_);
+            if (!loc) return {};
+            page_ids[i] = loc->first;
+            slot_ids[i] = loc->second;
+            slots[i] = RequestSlot{request_id, tokens[done + i], cursor + done + i};
+        }
+        const std::vector<uint32_t>& table = req.page_state->page_table;
+        for (size_t i = 0; i < n; ++i) {
+            q_pos[i] = static_cast<uint32_t>(cursor + done + i);
+            seq_lens[i] = q_pos[i] + 1;
+            const size_t pages = (seq_lens[i] + P - 1) / P;
+            if (pages > table.size()) return {};   // the cursor does not continue the request's context
+            pt_off[i] = static_cast<uint32_t>(pt_flat.size());
+            pt_flat.insert(pt_flat.end(), table.begin(), table.begin() + pages);
+        }
+        pt_off[n] = static_cast<uint32_t>(pt_flat.size());
+        mlc_attn_plan*& slot = ex.plans_[ex.passes_++ & 1u];
+        const int st = slot ? mlc_attn_plan_update(ctx, slot, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
+                                                   q_pos.data(), page_ids.data(), slot_ids.data(), n)
+                            : mlc_attn_plan_create(ctx, pt_flat.data(), pt_flat.size(), pt_off.data(), seq_lens.data(),
+                                                   q_pos.data(), page_ids.data(), slot_ids.data(), n, H, KVH, D, P, 1, cap,
+                                                   &slot);
+        if (st != MLC_OK) return {};
+        const bool last = done + n == tokens.size();
+        bool ok = mlc_pass_begin(ctx) == MLC_OK;
+        ok = ok && encode_model_pass(slots, slot, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos, logits_pinned_, vocab,
+                                     last ? n - 1 : n);
+        ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
+        if (!ok) return {};
+    }
+    req.next_position = cursor + tokens.size();
+    return std::vector<float>(logits_pinned_, logits_pinned_ + vocab);
+}
 
 std::vector<float> BatchedWalker::prefill(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor) {
     PagedAttentionExecutor& ex = exec_;

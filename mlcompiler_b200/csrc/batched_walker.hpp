@@ -25,14 +25,18 @@ public:
     // attention output of the last layer, or {} on failure. The reference reaches the same
     // state with one decode pass per token (batched_executor.cpp:450-467).
     std::vector<float> prefill(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor);
+    // The same with a model attached: the prompt goes through the whole step 32 tokens per pass - a chunk's tokens
+    // stand in the batch like requests that share one page table - and only the last token's logits are computed
+    // and returned ({} on failure). The reference feeds a prompt one token per pass (batched_executor.cpp:450-467).
+    std::vector<float> prefill_model(uint32_t request_id, const std::vector<uint64_t>& tokens, size_t cursor);
 
 private:
     // The layers of a pass with a model attached: encodes embedding .. lm_head onto the open pass and the copies of
-    // the logits [N, vocab] into page-locked host rows `logits_stride` floats apart.
+    // the logits of rows [head_first, N) into page-locked host rows `logits_stride` floats apart.
     bool encode_model_pass(const std::vector<RequestSlot>& slots, mlc_attn_plan* plan, const std::vector<uint32_t>& page_ids,
                            const std::vector<uint32_t>& slot_ids, const std::vector<uint32_t>& pt_flat,
                            const std::vector<uint32_t>& pt_off, const std::vector<uint32_t>& seq_lens,
-                           const std::vector<uint32_t>& q_pos, float* logits_host, size_t logits_stride);
+                           const std::vector<uint32_t>& q_pos, float* logits_host, size_t logits_stride, size_t head_first);
 
     PagedAttentionExecutor& exec_;
     std::vector<float> cos_host_, sin_host_;

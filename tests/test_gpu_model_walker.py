@@ -158,22 +158,61 @@ def test_model_decode_passes_match_the_oracle(executor, oracle_mod, name, shape,
     storage.destroy()
 
 
-def test_model_prefill_is_token_by_token_and_scheduler_generates(executor, oracle_mod):
-    """run_prefill with a model feeds the prompt one token per pass (batched_executor.cpp:450-467); the
-    scheduler over the same executor generates greedy tokens that the oracle model reproduces."""
+@pytest.mark.parametrize("reference_order", [False, True], ids=["chunked", "token_by_token"])
+def test_model_prefill_matches_the_token_loop(executor, oracle_mod, reference_order):
+    """run_prefill with a model: the reference feeds the prompt one token per pass (batched_executor.cpp:450-467),
+    and so does the reference call order here; the default puts 32 prompt tokens into a pass. Either way the last
+    token's logits and the rows left in the pools are those of the oracle's token loop. A second call continues
+    the context."""
     model = synth.SyntheticModel(0xFEED, 2, 4, 2, 64, 256, 512)
     capacity = 8
     pool, storage, ex = make_stack(executor, model, capacity)
+    ex.set_call_order(reference_order)
     replay = OracleModel(oracle_mod, model, capacity)
-    prompt = [3, 141, 59, 26, 5]
+    rng = np.random.default_rng(3)
+    prompt = [int(t) for t in rng.integers(0, model.vocab_size, 70)]      # 32 + 32 + 6, over the 64-token page boundary
+    before = executor.launchCount()
     logits = ex.run_prefill(7, prompt)
+    launches = executor.launchCount() - before
     assert logits.size == model.vocab_size and ex.known_position(7) == len(prompt)
     table, total = ex.page_state(7)
+    assert total == len(prompt)
     for pos, tok in enumerate(prompt):
         want = replay.step([(7, tok, pos)], {7: (table, pos + 1)})
     assert_logits_close(logits[None], want, "prefill")
+    if not reference_order:
+        # three passes of embedding + 8 launches per layer, then the final norm and the lm_head's groups once
+        head = -(-model.vocab_size // (-(-(-(-model.vocab_size // 4)) // 64) * 64))
+        assert 3 * (1 + 2 * 8) + 1 + head <= launches <= 3 * (1 + 2 * 8 + 2) + 1 + head, launches
+    more = [int(t) for t in rng.integers(0, model.vocab_size, 9)]
+    logits = ex.run_prefill(7, more)
+    table, total = ex.page_state(7)
+    for i, tok in enumerate(more):
+        want = replay.step([(7, tok, len(prompt) + i)], {7: (table, len(prompt) + i + 1)})
+    assert_logits_close(logits[None], want, "second prefill call")
+    rows = [(table[pos // P], pos % P) for pos in range(total)]
+    pg, sl = np.array([r[0] for r in rows]), np.array([r[1] for r in rows])
+    for layer, tol in ((0, 3e-3), (1, 2e-2)):
+        k, v = _pools(executor, storage, model, layer, capacity)
+        for got, ref in ((k, replay.k[layer]), (v, replay.v[layer])):
+            g, w = got[pg, sl].astype(np.float32), ref[pg, sl].astype(np.float32)
+            assert np.abs(g - w).max() <= tol * max(1.0, float(np.sqrt((w ** 2).mean()))), f"layer {layer} pool rows"
+    # a decode pass continues from the prefilled context
+    out = ex.run_decode([(7, 11, total)])
+    want = replay.step([(7, 11, total)], {7: ex.page_state(7)})
+    assert out[0][1]
+    assert_logits_close(out[0][2][None], want, "decode after prefill")
     ex.release_request(7)
     assert pool.pages_in_use() == 0
+    ex.destroy()
+    storage.destroy()
+
+
+def test_scheduler_generates_the_oracles_tokens(executor, oracle_mod):
+    """The scheduler over the executor with a model generates greedy tokens that the oracle model reproduces."""
+    model = synth.SyntheticModel(0xFEED, 2, 4, 2, 64, 256, 512)
+    capacity = 8
+    pool, storage, ex = make_stack(executor, model, capacity)
 
     sched = Scheduler(ex, max_batch_size=4)
     prompts = {0: [9, 8, 7], 1: [100, 200, 300, 400]}
