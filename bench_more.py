@@ -382,7 +382,7 @@ class _RawHalf:
         self.__cuda_array_interface__ = {"shape": (n_halves,), "typestr": "<f2", "data": (int(ptr), False), "version": 3}
 
 
-def run_model(env, steps=40, warmup=5, batch=32, reference_order=False):
+def run_model(env, steps=40, warmup=5, batch=32, reference_order=False, from_gguf=False, prompt_tokens=1024):
     import time
     import torch
     from mlcompiler_b200 import synth
@@ -392,7 +392,7 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False):
     model = synth.SyntheticModel(0x11B, L, H, KVH, D, inner, vocab, lm_head_quant="q6_k")
     lens = synth.config_lengths(2)[:batch].astype(np.int64)
     total_steps = steps + max(warmup, 3)
-    capacity = int(sum((int(l) + total_steps + P - 1) // P for l in lens)) + 4
+    capacity = int(sum((int(l) + total_steps + P - 1) // P for l in lens)) + 4 + 2 * ((prompt_tokens + P - 1) // P + 1)
     pool = PagePool(capacity)
     storage = PagedKVStorage(ex, capacity, L, P, KVH, D, 2)
     assert storage.initialize()
@@ -407,7 +407,25 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False):
             for ptr in (storage.k_buffer(l), storage.v_buffer(l)):
                 torch.as_tensor(_RawHalf(ptr, n_halves), device=dev).normal_()
     stream.synchronize()
-    assert pex.attach_model(model)
+    load = None
+    if from_gguf:
+        # the same weights through a file: written as a GGUF checkpoint (q / k / v and gate / up apart), read back by the
+        # library's loader and streamed into device memory
+        import tempfile
+        from mlcompiler_b200.host import GgufFile
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, "model.gguf")
+            model.write_gguf(path)
+            size = os.path.getsize(path)
+            t0 = time.perf_counter()
+            f = GgufFile(path)
+            assert pex.attach_gguf(f), pex.attach_error
+            load = {"file_bytes": size, "seconds": time.perf_counter() - t0, "what": "mlc_gguf_open + mlc_executor_attach_gguf, "
+                    "file in the page cache"}
+            load["gbps"] = size / load["seconds"] / 1e9
+            f.close()
+    else:
+        assert pex.attach_model(model)
     for r in range(batch):
         assert pex.assume_context(r, int(lens[r]) - 1)
     pos = [int(l) - 1 for l in lens]
@@ -433,6 +451,20 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False):
         times.append(time.perf_counter() - t0)
     launches = ex.launchCount() - l0
     sec = env.reduce(float(np.mean(times)), "max")
+    # a prompt through run_prefill (32 tokens per pass in the fused order, one per pass in the reference's)
+    prefill = None
+    if prompt_tokens:
+        n_prompt = prompt_tokens if not reference_order else min(prompt_tokens, 64)
+        ptimes = []
+        for rep_i in range(2):
+            prompt = [int(t) for t in rng.integers(0, vocab, n_prompt)]
+            t0 = time.perf_counter()
+            lg = pex.run_prefill(batch + rep_i, prompt)
+            ptimes.append(time.perf_counter() - t0)
+            assert lg.size == vocab and np.isfinite(lg).all(), ex.last_error()
+        psec = env.reduce(float(min(ptimes)), "max")
+        prefill = {"prompt_tokens": n_prompt, "ms": psec * 1e3, "tokens_per_s": world * n_prompt / psec,
+                   "what": "run_prefill of one request from an empty context, wall clock, last token's logits on the host"}
     kv_bytes = float(sum(pos)) * 2 * KVH * D * 2 * L
     pex.destroy()
     storage.destroy()
@@ -447,7 +479,7 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False):
                    "logits on the host when it returns"},
         "ms_per_step_median_min_max": [float(np.median(times)) * 1e3, float(np.min(times)) * 1e3, float(np.max(times)) * 1e3],
         "bytes_per_step": {"weights": model.weight_bytes() - model.host["token_embd.weight"].nbytes, "kv": kv_bytes},
-        "gpu_launches": int(launches), "launches_per_step": launches / steps}
+        "gpu_launches": int(launches), "launches_per_step": launches / steps, "prefill": prefill, "model_load": load}
 
 
 def run_matvec(env, steps=200, warmup=10, rows=11264, cols=2048, quant="q4_0", batch=32):
@@ -503,6 +535,7 @@ def main():
     ap.add_argument("--exchange", choices=["fused", "peer", "nccl"], default="fused",
                     help="cfg3 on several GPUs: exchange fused into the attention kernel (default), the separate "
                          "peer-memory exchange kernel, or NCCL all-gather + combine")
+    ap.add_argument("--from-gguf", action="store_true", help="model: load the weights through a GGUF file and report the load")
     ap.add_argument("--reference-order", action="store_true",
                     help="model: the reference walker's 13 launches per layer instead of the fused 8")
     ap.add_argument("--rows", type=int, default=11264, help="matvec: weight rows")
@@ -532,7 +565,8 @@ def main():
     elif args.workload == "matvec":
         res = run_matvec(env, args.steps, args.warmup, args.rows, args.cols, args.quant, args.batch)
     elif args.workload == "model":
-        res = run_model(env, min(args.steps, 100), args.warmup, reference_order=args.reference_order)
+        res = run_model(env, min(args.steps, 100), args.warmup, reference_order=args.reference_order,
+                        from_gguf=args.from_gguf)
     else:
         res = run_cfg4(env, args.steps, args.warmup)
     if rank == 0:

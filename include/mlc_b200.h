@@ -648,8 +648,10 @@ mlc_executor* mlc_callback_executor_create(const mlc_executor_callbacks* callbac
  * With a model attached, mlc_executor_run_decode runs the whole walker step on the GPU and returns
  * vocab_size logits per request; in the fused call order (the default) a layer is 8 launches, in
  * the reference's call order (mlc_executor_set_call_order) the reference's 13, op for op. A prompt
- * is fed token by token through the decode path, as batched_executor.cpp:450-467 does. The
- * pointers must stay valid while the executor lives. */
+ * (mlc_executor_run_prefill) is fed token by token through the decode path in the reference's call
+ * order, as batched_executor.cpp:450-467 does, and 32 tokens per pass in the fused order; either
+ * way the logits returned are the last prompt token's. The pointers must stay valid while the
+ * executor lives. */
 typedef struct mlc_layer_weights {
     const void* attn_norm;
     const void* attn_qkv;      /* [(num_heads + 2 kv_heads) * head_dim] rows of hidden_size */

@@ -118,8 +118,9 @@ public:
     void set_call_order(CallOrder o) { order_ = o; }
     // With a model attached a decode pass is the whole walker step - embedding, every layer's norms,
     // mat-vecs, rotary, attention and residual adds, final norm and lm_head - and the logits are the model's
-    // [vocab_size] per request; a prompt is fed token by token through the decode path
-    // (batched_executor.cpp:450-467). Returns false if the description does not fit the executor.
+    // [vocab_size] per request; a prompt is fed token by token through the decode path in the reference's call
+    // order (batched_executor.cpp:450-467), 32 tokens per pass in the fused order. Returns false if the
+    // description does not fit the executor.
     bool attach_model(const ModelWeights& model);
     // Reads the model out of a GGUF file (the tensors and metadata keys the reference's walker uses,
     // batched_walker.cpp:183-190, 248-420; kernel_scheduler.cpp:251-258), uploads the weights into one device
