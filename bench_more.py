@@ -390,7 +390,7 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False, from_ggu
     ex, stream, dev, rank, world = env.ex, env.stream, env.dev, env.rank, env.world
     P, L, H, KVH, D, inner, vocab = 64, 22, 32, 4, 64, 5632, 32000
     model = synth.SyntheticModel(0x11B, L, H, KVH, D, inner, vocab, lm_head_quant="q6_k")
-    lens = synth.config_lengths(2)[:batch].astype(np.int64)
+    lens = np.resize(synth.config_lengths(2), batch).astype(np.int64)   # past 32 requests the lengths repeat
     total_steps = steps + max(warmup, 3)
     capacity = int(sum((int(l) + total_steps + P - 1) // P for l in lens)) + 4 + 2 * ((prompt_tokens + P - 1) // P + 1)
     pool = PagePool(capacity)
@@ -473,7 +473,7 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False, from_ggu
         "warmup": max(warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "dtype": "Q4_0 / Q6_K weights, f16 KV, f32 activations", "data": "synthetic",
         "config": {"workload": "model: 1.1B-shaped decoder (22 layers, hidden 2048, H32/KVH4/D64, FFN 5632, vocabulary "
-                               "32000), 32 requests, contexts U[512,2048], whole walker step through run_decode",
+                               f"32000), {batch} requests, contexts U[512,2048], whole walker step through run_decode",
                    "call_order": "reference" if reference_order else "fused",
                    "parallelism": f"replicas x{world}, {batch} requests each", "timed": "wall clock around run_decode, "
                    "logits on the host when it returns"},
@@ -541,7 +541,7 @@ def main():
     ap.add_argument("--rows", type=int, default=11264, help="matvec: weight rows")
     ap.add_argument("--cols", type=int, default=2048, help="matvec: weight columns")
     ap.add_argument("--quant", choices=["q4_0", "q6_k"], default="q4_0", help="matvec: weight format")
-    ap.add_argument("--batch", type=int, default=32, help="matvec: requests")
+    ap.add_argument("--batch", type=int, default=32, help="matvec, model: requests (model: at most 64)")
     ap.add_argument("--seq-len", type=int, default=None, help="cfg3: tokens per request instead of 32768")
     args = ap.parse_args()
 
@@ -565,7 +565,7 @@ def main():
     elif args.workload == "matvec":
         res = run_matvec(env, args.steps, args.warmup, args.rows, args.cols, args.quant, args.batch)
     elif args.workload == "model":
-        res = run_model(env, min(args.steps, 100), args.warmup, reference_order=args.reference_order,
+        res = run_model(env, min(args.steps, 100), args.warmup, batch=args.batch, reference_order=args.reference_order,
                         from_gguf=args.from_gguf)
     else:
         res = run_cfg4(env, args.steps, args.warmup)
