@@ -233,7 +233,11 @@ int mlc_gguf_concatenate_block_weights(mlc_gguf* g, char* error, size_t error_ca
 }
 size_t mlc_gguf_describe(mlc_gguf* g, char* json, size_t capacity) {
     if (!g) return 0;
-    if (g->json.empty()) g->json = g->file->describe_json();
+    try {
+        if (g->json.empty()) g->json = g->file->describe_json();
+    } catch (const std::exception&) {
+        return 0;   // out of memory while building the text
+    }
     if (json && capacity) {
         const size_t n = std::min(g->json.size(), capacity - 1);
         std::memcpy(json, g->json.data(), n);
