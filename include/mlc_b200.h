@@ -384,6 +384,18 @@ int mlc_encode_qkv_split_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan*
                                               void* q_out, int q_dtype, void* k_page_storage,
                                               void* v_page_storage, const void* cos_table,
                                               const void* sin_table, size_t qkv_rows, size_t rotary_dim);
+/* The fused Q | K | V projection and the step above in one launch: weights = (num_heads + 2 kv_heads) *
+ * head_dim rows of `cols` (quant, in, in_stride, input_kind, row_stride as in mlc_encode_matmul_quant_fused,
+ * input_kind 0 or 2); the kernel that has added up four adjacent rows of a request rotates them, rounds
+ * them to fp16 and writes Q to q_out [batch, num_heads * head_dim] (fp16) and K / V into the plan's
+ * (page, slot) of the request - bit for bit what mlc_encode_matmul_quant_fused followed by
+ * mlc_encode_qkv_split_rope_scatter_planned leaves there, without the fp32 [batch, qkv_rows] round trip and
+ * its launch. head_dim must be a multiple of 4, q_out 16-byte aligned. */
+int mlc_encode_matmul_qkv_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, int quant, const void* weights,
+                                               const void* in, size_t in_stride, int input_kind, size_t cols,
+                                               size_t row_stride, void* q_out, void* k_page_storage,
+                                               void* v_page_storage, const void* cos_table, const void* sin_table,
+                                               size_t rotary_dim);
 /* computeRotaryCoefficients (quantization.cpp:795-823) on the host: cos/sin of
  * position * freq_base^(-2i/rotary_dim) * freq_scale for i < rotary_dim / 2
  * (freq_base <= 0 -> 10000, freq_scale == 0 -> 1, as in the reference). */
@@ -646,7 +658,7 @@ mlc_executor* mlc_callback_executor_create(const mlc_executor_callbacks* callbac
  * Q4_0 rows, tightly packed; the lm_head is Q6_K (lm_head_quant = 1) or Q4_0 (0). hidden_size
  * must equal num_heads * head_dim and, like ffn_inner, be a multiple of 256.
  * With a model attached, mlc_executor_run_decode runs the whole walker step on the GPU and returns
- * vocab_size logits per request; in the fused call order (the default) a layer is 8 launches, in
+ * vocab_size logits per request; in the fused call order (the default) a layer is 7 launches, in
  * the reference's call order (mlc_executor_set_call_order) the reference's 13, op for op. A prompt
  * (mlc_executor_run_prefill) is fed token by token through the decode path in the reference's call
  * order, as batched_executor.cpp:450-467 does, and 32 tokens per pass in the fused order; either

@@ -72,6 +72,7 @@ _PROTOTYPES = {
     "mlc_encode_qkv_split_rope_cast": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz,
                                             _sz, _sz, _sz, _sz]),
     "mlc_encode_qkv_split_rope_scatter_planned": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _sz, _sz]),
+    "mlc_encode_matmul_qkv_rope_scatter_planned": (_i, [_vp, _vp, _i, _vp, _vp, _sz, _i, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _sz]),
     "mlc_encode_rms_norm_batched": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
     "mlc_encode_rms_norm_batched_packed": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
     "mlc_encode_add_batched": (_i, [_vp, _vp, _vp, _vp, _sz]),
@@ -514,6 +515,14 @@ class Executor:
         return self.status(self._lib.mlc_encode_qkv_split_rope_scatter_planned(
             self._h, plan.handle, _vp(_ptr(qkv_buf)), _vp(_ptr(q_out)), q_dtype, _vp(_ptr(k_storage)),
             _vp(_ptr(v_storage)), _vp(_ptr(cos_buf)), _vp(_ptr(sin_buf)), qkv_rows, rotary_dim))
+
+    def encodeMatMulQkvRopeScatterPlanned(self, plan, quant, weights_buf, in_buf, in_stride, input_kind, cols, row_stride,
+                                          q_out, k_storage, v_storage, cos_buf, sin_buf, rotary_dim) -> bool:
+        """The fused Q | K | V projection with split + rotate + cast + page write in its epilogue, one launch."""
+        return self.status(self._lib.mlc_encode_matmul_qkv_rope_scatter_planned(
+            self._h, plan.handle, quant, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), in_stride, int(input_kind), cols,
+            row_stride, _vp(_ptr(q_out)), _vp(_ptr(k_storage)), _vp(_ptr(v_storage)), _vp(_ptr(cos_buf)),
+            _vp(_ptr(sin_buf)), rotary_dim))
 
     def computeRotaryCoefficients(self, position, rotary_dim, freq_base=10000.0, freq_scale=1.0):
         """quantization.cpp:795-823: (cos, sin) float32 [rotary_dim // 2]."""

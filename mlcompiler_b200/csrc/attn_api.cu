@@ -1127,4 +1127,41 @@ int mlc_encode_qkv_split_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan*
     return launch_qkv_split_rope_cast(ctx, p);
 }
 
+int mlc_encode_matmul_qkv_rope_scatter_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, int quant, const void* weights,
+                                               const void* in, size_t in_stride, int input_kind, size_t cols,
+                                               size_t row_stride, void* q_out, void* k_page_storage,
+                                               void* v_page_storage, const void* cos_table, const void* sin_table,
+                                               size_t rotary_dim) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (!plan->d_page_ids) return ctx->fail(MLC_ERR_INVALID_ARG, "the plan was created without page_ids / slots_in_page");
+    if (!q_out || !k_page_storage || !v_page_storage) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    const PlanKey& k = plan->key;
+    const size_t qkv_rows = (k.H + 2 * k.KVH) * k.D;
+    // `in` stands in for the qkv buffer of the unfused form in the shared argument check (pointer and alignment only)
+    int st = check_qkv_rope_args(ctx, in, cos_table, sin_table, k.batch, k.H, k.KVH, k.D, qkv_rows, k.H * k.D, k.KVH * k.D,
+                                 k.KVH * k.D, rotary_dim);
+    if (st != MLC_OK) return st;
+    DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
+    QkvRopeParams p{};
+    p.q16 = static_cast<__half*>(q_out);
+    p.k_pool = static_cast<__half*>(k_page_storage);
+    p.v_pool = static_cast<__half*>(v_page_storage);
+    p.page_ids = plan->d_page_ids;
+    p.slots = plan->d_slots;
+    p.cos_t = static_cast<const float*>(cos_table);
+    p.sin_t = static_cast<const float*>(sin_table);
+    p.err = ctx->d_err;
+    p.batch = static_cast<uint32_t>(k.batch);
+    p.head_dim = static_cast<uint32_t>(k.D);
+    p.rotary_pairs = static_cast<uint32_t>(rotary_dim / 2);
+    p.qkv_rows = static_cast<uint32_t>(qkv_rows);
+    p.q_rows = static_cast<uint32_t>(k.H * k.D);
+    p.k_rows = p.v_rows = static_cast<uint32_t>(k.KVH * k.D);
+    p.page_tokens = static_cast<uint32_t>(k.P);
+    p.capacity = k.capacity ? static_cast<uint32_t>(k.capacity) : 0xFFFFFFFFu;
+    return encode_matvec_qkv_rope(ctx, quant, input_kind, weights, in, in_stride, cols, row_stride, p);
+}
+
 }  // extern "C"

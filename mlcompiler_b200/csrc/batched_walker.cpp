@@ -321,15 +321,21 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
         void* kp = storage->k_buffer(L);
         void* vp = storage->v_buffer(L);
         // fused order: the norms write the mat-vec's operand format directly (the mat-vec then converts nothing)
+        // fused order, head_dim a multiple of 4: the QKV projection rotates, casts and writes Q and the K / V page rows
+        // itself; otherwise the projection leaves fp32 rows for the split / rotary / page-write kernel
+        const bool qkv_epilogue = fused && D % 4 == 0;
         ok = fused ? mlc_encode_rms_norm_batched_packed(ctx, residual, w.attn_norm, eps, N, hidden, nullptr, norm_o) == MLC_OK &&
-                         mlc_encode_matmul_quant_fused(ctx, 0, w.attn_qkv, norm_o, hidden, 2, nullptr, N, qkv_rows, hidden, row_h,
-                                                       qkv) == MLC_OK
+                         (qkv_epilogue
+                              ? mlc_encode_matmul_qkv_rope_scatter_planned(ctx, plan, 0, w.attn_qkv, norm_o, hidden, 2, hidden, row_h,
+                                                                           q, kp, vp, cos_t, sin_t, m.rotary_dim)
+                              : mlc_encode_matmul_quant_fused(ctx, 0, w.attn_qkv, norm_o, hidden, 2, nullptr, N, qkv_rows, hidden,
+                                                              row_h, qkv)) == MLC_OK
                    : mlc_encode_rms_norm_batched(ctx, residual, w.attn_norm, eps, N, hidden, norm_o, nullptr) == MLC_OK &&
                          mlc_encode_matmul_q4_0_batched(ctx, w.attn_qkv, norm_o, N, qkv_rows, hidden, row_h, qkv) == MLC_OK;
         if (!ok) break;
         if (fused) {
-            ok = mlc_encode_qkv_split_rope_scatter_planned(ctx, plan, qkv, q, MLC_F16, kp, vp, cos_t, sin_t, qkv_rows,
-                                                           m.rotary_dim) == MLC_OK &&
+            ok = (qkv_epilogue || mlc_encode_qkv_split_rope_scatter_planned(ctx, plan, qkv, q, MLC_F16, kp, vp, cos_t, sin_t,
+                                                                            qkv_rows, m.rotary_dim) == MLC_OK) &&
                  mlc_encode_paged_flash_attention_planned(ctx, plan, q, kp, vp, attn_mix, scale, MLC_F16, MLC_F32) == MLC_OK &&
                  mlc_encode_matmul_quant_fused(ctx, 0, w.attn_output, attn_mix, hidden, 0, residual, N, hidden, hidden,
                                                row_h, resid1) == MLC_OK &&

@@ -25,6 +25,7 @@
 #include <vector>
 
 #include "ctx.hpp"
+#include "qkv_rope.hpp"
 #include "tcgen05_util.hpp"
 
 namespace mlcb {
@@ -240,6 +241,8 @@ struct MatVecParams {
     uint32_t slice_cols;     // columns per slice (a multiple of the block size)
     uint32_t chunk_cols;     // columns staged in shared memory at a time
     uint32_t w_pitch;        // bytes between weight rows in shared memory
+    uint32_t rope_mode;      // 1: the rows are a fused Q | K | V projection and the epilogue finishes them (see `rope`)
+    QkvRopeParams rope;      // where Q (fp16) and the K / V page rows go, the rotary tables, the pass's (page, slot) per request
     uint32_t pair_inner;     // 0, or: rows = gate rows [0, pair_inner) then up rows [pair_inner, 2 pair_inner); a row tile is
                              // half gate rows, half the up rows that go with them, and out gets SiLU(gate) * up as operand words
     uint32_t slices;         // CTAs per cluster
@@ -604,6 +607,45 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
             const uint32_t bn = i / rs4, lrow = slice * share + ((i - bn * rs4) << 2);
             if (bn >= p.batch || lrow >= kMvRows || row0 + lrow >= p.rows) continue;
             float4 sum = sum_tiles(bn, lrow);
+            if (p.rope_mode) {
+                // Rows row0 + lrow .. + 3 of request bn are two adjacent pairs of one head of Q, K or V: rotate
+                // (Q and K, inside the rotary dimensions), round to fp16, write Q to its buffer and K / V into the
+                // request's (page, slot) of the pools - the arithmetic of qkv_split_rope_cast_kernel, pair by pair.
+                const QkvRopeParams& q = p.rope;
+                const uint32_t col = row0 + lrow;
+                const bool is_q = col < q.q_rows, is_k = !is_q && col < q.q_rows + q.k_rows;
+                const uint32_t c = is_q ? col : (is_k ? col - q.q_rows : col - q.q_rows - q.k_rows);
+                float v[4] = {sum.x, sum.y, sum.z, sum.w};
+                if (is_q || is_k) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const uint32_t pair = ((c + 2 * j) % q.head_dim) >> 1;
+                        if (pair < q.rotary_pairs) {
+                            const float cs = q.cos_t[static_cast<size_t>(bn) * q.rotary_pairs + pair];
+                            const float sn = q.sin_t[static_cast<size_t>(bn) * q.rotary_pairs + pair];
+                            const float x0 = v[2 * j], x1 = v[2 * j + 1];
+                            v[2 * j] = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+                            v[2 * j + 1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+                        }
+                    }
+                }
+                const __half2 h01 = __floats2half2_rn(v[0], v[1]), h23 = __floats2half2_rn(v[2], v[3]);
+                const uint2 packed = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                if (is_q) {
+                    *reinterpret_cast<uint2*>(q.q16 + static_cast<size_t>(bn) * q.q_rows + c) = packed;
+                } else {
+                    const uint32_t page = q.page_ids[bn], slot = q.slots[bn];
+                    if (page >= q.capacity) {
+                        if (c == 0) atomicOr(q.err, MLC_DEVERR_BAD_PAGE);
+                    } else if (slot >= q.page_tokens) {
+                        if (c == 0) atomicOr(q.err, MLC_DEVERR_BAD_SLOT);
+                    } else {
+                        __half* pool = is_k ? q.k_pool : q.v_pool;
+                        *reinterpret_cast<uint2*>(pool + (static_cast<size_t>(page) * q.page_tokens + slot) * q.k_rows + c) = packed;
+                    }
+                }
+                continue;
+            }
             const size_t o = static_cast<size_t>(bn) * p.rows + row0 + lrow;
             if (vec_out) {
                 if (p.residual) {
@@ -1320,7 +1362,7 @@ int mlc_encode_embedding_q4_0(mlc_ctx* ctx, const void* table, size_t row_stride
 
 static int encode_matvec(mlc_ctx* ctx, int qt, int in_mode, const void* weights, const void* in, const void* residual,
                          size_t batch, size_t rows, size_t cols, size_t row_stride, size_t x_stride, void* out,
-                         size_t pair_inner = 0) {
+                         size_t pair_inner = 0, const QkvRopeParams* rope = nullptr) {
     if (!ctx) return MLC_ERR_INVALID_ARG;
     if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
     int st = check_matvec(ctx, qt, weights, in, out, batch, rows, cols, row_stride, x_stride);
@@ -1341,7 +1383,11 @@ static int encode_matvec(mlc_ctx* ctx, int qt, int in_mode, const void* weights,
     p.x_stride = static_cast<uint32_t>(x_stride);
     p.aligned16 = (row_stride % 16 == 0 && reinterpret_cast<uintptr_t>(weights) % 16 == 0) ? 1u : 0u;
     p.pair_inner = static_cast<uint32_t>(pair_inner);
-    const bool tcore = !pair_inner && matvec_tc_enabled() && p.aligned16 && batch <= static_cast<size_t>(kTcN);
+    if (rope) {
+        p.rope_mode = 1;
+        p.rope = *rope;
+    }
+    const bool tcore = !pair_inner && !rope && matvec_tc_enabled() && p.aligned16 && batch <= static_cast<size_t>(kTcN);
 #define MLCB_MATVEC_DISPATCH(QT, IN) (tcore ? launch_matvec_tc<QT, IN>(ctx, p) : launch_matvec<QT, IN>(ctx, p))
     if (qt == kQ6_K) {
         if (in_mode == kInSiluMul) return MLCB_MATVEC_DISPATCH(kQ6_K, kInSiluMul);
@@ -1384,3 +1430,20 @@ int mlc_encode_matmul_gate_up_silu_packed(mlc_ctx* ctx, int quant, const void* w
 }
 
 }  // extern "C"
+
+namespace mlcb {
+
+int encode_matvec_qkv_rope(mlc_ctx* ctx, int quant, int input_kind, const void* weights, const void* in, size_t in_stride,
+                           size_t cols, size_t row_stride, const QkvRopeParams& rope) {
+    if (quant != kQ4_0 && quant != kQ6_K) return ctx->fail(MLC_ERR_INVALID_ARG, "unknown quantisation");
+    if (input_kind != kInPlain && input_kind != kInPacked) return ctx->fail(MLC_ERR_INVALID_ARG, "input kind must be 0 or 2");
+    const size_t rows = static_cast<size_t>(rope.q_rows) + rope.k_rows + rope.v_rows;
+    if (rope.head_dim % 4 || reinterpret_cast<uintptr_t>(rope.q16) % 16 || reinterpret_cast<uintptr_t>(rope.k_pool) % 8 ||
+        reinterpret_cast<uintptr_t>(rope.v_pool) % 8)
+        return ctx->fail(MLC_ERR_UNSUPPORTED, "head_dim must be a multiple of 4, q 16-byte and the pools 8-byte aligned");
+    // `out` of the plain form is not written in this mode; q stands in for the pointer checks
+    return encode_matvec(ctx, quant, input_kind, weights, in, nullptr, rope.batch, rows, cols, row_stride, in_stride, rope.q16, 0,
+                         &rope);
+}
+
+}  // namespace mlcb

@@ -27,6 +27,11 @@ struct QkvRopeParams {
 };
 
 int launch_qkv_split_rope_cast(mlc_ctx* ctx, const QkvRopeParams& p);
+// The fused Q | K | V projection whose epilogue does what the kernel above does with its result (layer_ops.cu): q16,
+// k_pool, v_pool, page_ids, slots, the tables and the sizes of `rope` are used; its qkv, fp32 and unpaged fp16
+// outputs are not.
+int encode_matvec_qkv_rope(mlc_ctx* ctx, int quant, int input_kind, const void* weights, const void* in, size_t in_stride,
+                           size_t cols, size_t row_stride, const QkvRopeParams& rope);
 int check_qkv_rope_args(mlc_ctx* ctx, const void* qkv, const void* cos_t, const void* sin_t, size_t batch,
                         size_t num_heads, size_t kv_heads, size_t head_dim, size_t qkv_rows, size_t q_rows,
                         size_t k_rows, size_t v_rows, size_t rotary_dim);

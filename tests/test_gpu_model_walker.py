@@ -136,10 +136,11 @@ def test_model_decode_passes_match_the_oracle(executor, oracle_mod, name, shape,
             assert_logits_close(np.stack([o[2] for o in out]), want, f"step {step}")
         for rid in active:
             positions[rid] += 1
-    # launches of a pass: embedding + per layer 8 (fused) or 13 (the reference's ops one for one) + norm + lm_head
+    # launches of a pass: embedding + per layer 7 (fused: norm, QKV projection with rotary and page write, attention,
+    # output projection, norm, gate | up with SiLU, down) or 13 (the reference's ops one for one) + norm + lm_head
     # (fused: up to four groups of vocabulary rows, multiples of 64); attention may add a merge launch per layer
     # when the planner splits sequences over CTAs
-    per_layer = 13 if reference_order else 8
+    per_layer = 13 if reference_order else 7
     group_rows = -(-(-(-vocab // 4)) // 64) * 64
     head_launches = 1 if reference_order else -(-vocab // group_rows)
     expect = 1 + layers * per_layer + 1 + head_launches
@@ -181,9 +182,9 @@ def test_model_prefill_matches_the_token_loop(executor, oracle_mod, reference_or
         want = replay.step([(7, tok, pos)], {7: (table, pos + 1)})
     assert_logits_close(logits[None], want, "prefill")
     if not reference_order:
-        # three passes of embedding + 8 launches per layer, then the final norm and the lm_head's groups once
+        # three passes of embedding + 7 launches per layer, then the final norm and the lm_head's groups once
         head = -(-model.vocab_size // (-(-(-(-model.vocab_size // 4)) // 64) * 64))
-        assert 3 * (1 + 2 * 8) + 1 + head <= launches <= 3 * (1 + 2 * 8 + 2) + 1 + head, launches
+        assert 3 * (1 + 2 * 7) + 1 + head <= launches <= 3 * (1 + 2 * 7 + 2) + 1 + head, launches
     more = [int(t) for t in rng.integers(0, model.vocab_size, 9)]
     logits = ex.run_prefill(7, more)
     table, total = ex.page_state(7)

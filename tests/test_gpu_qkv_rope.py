@@ -104,6 +104,48 @@ def test_split_rope_scatter_writes_the_pages(ex, q_dtype):
     plan.destroy()
 
 
+@pytest.mark.parametrize("H,KVH,D,rd,hidden,lens", [
+    (32, 4, 64, 64, 2048, [700 + 31 * i for i in range(32)]),      # the 1.1B shape at 32 requests
+    (4, 2, 64, 32, 256, [1, 64, 65]),                              # partial rotation, a row short of a tile
+    (8, 2, 128, 128, 512, [5, 200, 129, 64, 1000]),
+])
+def test_projection_with_rope_epilogue_equals_projection_then_kernel(ex, H, KVH, D, rd, hidden, lens):
+    """mlc_encode_matmul_qkv_rope_scatter_planned against mlc_encode_matmul_quant_fused followed by
+    mlc_encode_qkv_split_rope_scatter_planned: the same sums, the same rotation - equal bits in Q and in both pools."""
+    import torch
+    from mlcompiler_b200 import synth
+    P = 64
+    case = make_case(91, lens, H=H, KVH=KVH, D=D)
+    batch = case.N
+    rng = np.random.default_rng(hidden)
+    qkv_rows = (H + 2 * KVH) * D
+    w = synth.random_q4_0(rng, qkv_rows, hidden)
+    x = (rng.standard_normal((batch, hidden)) * 2).astype(np.float32)
+    cos, sin = _tables(ex, case.q_pos, rd)
+    dev = torch.device("cuda:0")
+    dw, dx, d_cos, d_sin = (torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (w, x, cos, sin))
+    pools = [[torch.from_numpy(a.view(np.int16).copy()).to(dev) for a in (case.k_pool, case.v_pool)] for _ in range(2)]
+    q = [torch.zeros((batch, H * D), dtype=torch.float16, device=dev) for _ in range(2)]
+    qkv = torch.zeros((batch, qkv_rows), device=dev)
+    plan = ex.createPlan(case.pt_flat, case.pt_off, case.seq_lens, case.q_pos, batch, H, KVH, D, P, True,
+                         case.capacity, page_ids=case.page_ids, slots_in_page=case.slots)
+    stride = w.shape[1]
+    assert ex.beginForwardPassCB()
+    l0 = ex.launchCount()
+    assert ex.encodeMatMulQuantFused(0, dw, dx, hidden, 0, None, batch, qkv_rows, hidden, stride, qkv), ex.last_error()
+    assert ex.encodeQkvSplitRopeScatterPlanned(plan, qkv, q[0], capi.MLC_F16, pools[0][0], pools[0][1], d_cos, d_sin,
+                                               qkv_rows, rd), ex.last_error()
+    l1 = ex.launchCount()
+    assert ex.encodeMatMulQkvRopeScatterPlanned(plan, 0, dw, dx, hidden, 0, hidden, stride, q[1], pools[1][0], pools[1][1],
+                                                d_cos, d_sin, rd), ex.last_error()
+    assert (l1 - l0, ex.launchCount() - l1) == (2, 1)
+    assert ex.flushForwardPassCB(), ex.last_error()
+    assert torch.equal(q[0], q[1]) and bool(q[0].float().abs().sum() > 0)
+    assert torch.equal(pools[0][0], pools[1][0]) and torch.equal(pools[0][1], pools[1][1])
+    assert not np.array_equal(pools[1][0].cpu().numpy(), case.k_pool.view(np.int16))      # rows were written
+    plan.destroy()
+
+
 def test_split_rope_cast_argument_rules(ex):
     import torch
     dev = torch.device("cuda:0")
