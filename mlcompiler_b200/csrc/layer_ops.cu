@@ -290,7 +290,6 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     using F = QuantFormat<QT>;
     constexpr int kMvRows = ROWS;
     constexpr int MT = ROWS / 64;           // m-tiles per warp: they share the warp's activation fragments
-    constexpr int kHalves = 2;              // warps per m-tile group, each with its half of every chunk's columns
     constexpr int kRedPitch = ROWS + 4;     // floats per batch row of a partial tile: lanes t land 8 banks apart
     constexpr int kXRows = NT * 8;
     constexpr int kXArrays = IN == kInSiluMul ? 2 : 1;
@@ -555,7 +554,7 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
     // [s * ROWS / S, (s + 1) * ROWS / S) of all partial tiles, slice by slice and half by half, through
     // distributed shared memory - no round trip through L2, and the order is fixed, so results repeat bit for
     // bit. The second barrier keeps every CTA's tiles alive until their readers are done.
-    float* red = reinterpret_cast<float*>(smem);   // [kHalves][kXRows][kRedPitch], over the first stage
+    float* red = reinterpret_cast<float*>(smem);   // [2 column halves][kXRows][kRedPitch], over the first stage
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
