@@ -826,7 +826,7 @@ __global__ void __launch_bounds__(kTcThreads) quant_matvec_tc_kernel(const TcPar
     const uint32_t row0 = tile * kTcRows;
     const uint32_t c_begin = min(slice * p.slice_cols, p.cols), c_end = min(c_begin + p.slice_cols, p.cols);
     const uint32_t n_chunks = (c_end - c_begin + kTcChunk - 1) / kTcChunk;
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5;
 
     if (tid == 0) {
         for (int i = 0; i < kTcRawStages; ++i) {
