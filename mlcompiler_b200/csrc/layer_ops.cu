@@ -567,29 +567,56 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
             }
     if (S > 1) cluster_sync_publish(); else __syncthreads();
     const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
-    // rows [lrow, lrow + 4) of batch row bn, added up over the cluster's partial tiles in slice order
-    auto sum_tiles = [&](uint32_t bn, uint32_t lrow) -> float4 {
-        const uint32_t addr0 = red_base + (bn * kRedPitch + lrow) * 4;
-        const uint32_t addr1 = addr0 + kXRows * kRedPitch * 4;
-        float4 sum = ld_cluster_f4(addr0, 0);
-        for (uint32_t k = 0; k < S; ++k) {
-            if (k) {
-                const float4 v = ld_cluster_f4(addr0, k);
-                sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
+    // Rows [lrow, lrow + 4) of batch row bn, added up over the cluster's 2 S partial tiles (slice 0's two column
+    // halves, slice 1's, ...). T lanes share the work: lane j takes partials j, j + T, ... - requested four at a time
+    // before the first is used, so that a lane waits for one round trip through distributed shared memory per four
+    // partials and not for one per partial - and the lanes' sums meet in a butterfly. With T = 1 that is the plain
+    // sum in slice order; for a given launch shape T is fixed, so results repeat bit for bit.
+    auto sum_tiles = [&](bool valid, uint32_t bn, uint32_t lrow, uint32_t j, uint32_t T) -> float4 {
+        const uint32_t addr = red_base + (bn * kRedPitch + lrow) * 4;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        bool have = false;
+        if (valid) {
+            for (uint32_t q0 = j; q0 < 2 * S; q0 += 4 * T) {
+                float4 part[4];
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t q = q0 + u * T;
+                    if (q < 2 * S) part[u] = ld_cluster_f4(addr + (q & 1u) * (kXRows * kRedPitch * 4), q >> 1);
+                }
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    if (q0 + u * T >= 2 * S) continue;
+                    const float4 v = part[u];
+                    sum = have ? make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w)) : v;
+                    have = true;
+                }
             }
-            const float4 v = ld_cluster_f4(addr1, k);
-            sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
+        }
+        for (uint32_t off = T >> 1; off; off >>= 1) {   // every lane of the warp takes part
+            const float4 o = make_float4(__shfl_xor_sync(0xffffffffu, sum.x, off), __shfl_xor_sync(0xffffffffu, sum.y, off),
+                                         __shfl_xor_sync(0xffffffffu, sum.z, off), __shfl_xor_sync(0xffffffffu, sum.w, off));
+            sum = make_float4(__fadd_rn(sum.x, o.x), __fadd_rn(sum.y, o.y), __fadd_rn(sum.z, o.z), __fadd_rn(sum.w, o.w));
         }
         return sum;
+    };
+    // lanes per work item: as many (a power of two up to 8, at most one per partial) as leave every item a lane
+    auto lanes_per_item = [&](uint32_t items) {
+        uint32_t T = 1;
+        while (T < 8 && items * T * 2 <= kMvThreads && T * 2 <= 2 * S) T *= 2;
+        return T;
     };
     if (p.pair_inner) {
         // CTA s finishes gate rows [s * share, (s + 1) * share) of the tile and the up rows that go with them
         const uint32_t share = ((kPairHalf + S - 1) / S + 3u) & ~3u, rs4 = share >> 2;
-        for (uint32_t i = tid; i < kXRows * rs4; i += kMvThreads) {
+        const uint32_t items = kXRows * rs4, T = lanes_per_item(items);
+        for (uint32_t base = 0; base < items * T; base += kMvThreads) {
+            const uint32_t w = base + tid, i = w / T, j = w - i * T;
             const uint32_t bn = i / rs4, lrow = slice * share + ((i - bn * rs4) << 2);
             const uint32_t col = tile * kPairHalf + lrow;   // column of the [batch, pair_inner] output
-            if (bn >= p.batch || lrow >= kPairHalf || col >= p.pair_inner) continue;
-            const float4 gt = sum_tiles(bn, lrow), up = sum_tiles(bn, lrow + kPairHalf);
+            const bool valid = w < items * T && bn < p.batch && lrow < kPairHalf && col < p.pair_inner;
+            const float4 gt = sum_tiles(valid, bn, lrow, j, T), up = sum_tiles(valid, bn, lrow + kPairHalf, j, T);
+            if (!valid || j != 0) continue;
             const float4 r = make_float4(silu_mul(gt.x, up.x), silu_mul(gt.y, up.y), silu_mul(gt.z, up.z), silu_mul(gt.w, up.w));
             const __half2 h01 = __floats2half2_rn(r.x, r.y), h23 = __floats2half2_rn(r.z, r.w);
             const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
@@ -602,10 +629,13 @@ __global__ void __launch_bounds__(kMvThreads) quant_matvec_kernel(const MatVecPa
         const uint32_t share = ((kMvRows + S - 1) / S + 3u) & ~3u;   // rows this CTA adds up: a multiple of 4, the last CTA's may be short
         const uint32_t rs4 = share >> 2;                             // float4 per batch row in this CTA's share
         const bool vec_out = (p.rows & 3u) == 0;
-        for (uint32_t i = tid; i < kXRows * rs4; i += kMvThreads) {
+        const uint32_t items = kXRows * rs4, T = lanes_per_item(items);
+        for (uint32_t base = 0; base < items * T; base += kMvThreads) {
+            const uint32_t w = base + tid, i = w / T, j = w - i * T;
             const uint32_t bn = i / rs4, lrow = slice * share + ((i - bn * rs4) << 2);
-            if (bn >= p.batch || lrow >= kMvRows || row0 + lrow >= p.rows) continue;
-            float4 sum = sum_tiles(bn, lrow);
+            const bool valid = w < items * T && bn < p.batch && lrow < kMvRows && row0 + lrow < p.rows;
+            float4 sum = sum_tiles(valid, bn, lrow, j, T);
+            if (!valid || j != 0) continue;
             if (p.rope_mode) {
                 // Rows row0 + lrow .. + 3 of request bn are two adjacent pairs of one head of Q, K or V: rotate
                 // (Q and K, inside the rotary dimensions), round to fp16, write Q to its buffer and K / V into the
