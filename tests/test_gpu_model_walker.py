@@ -209,6 +209,34 @@ def test_model_prefill_matches_the_token_loop(executor, oracle_mod, reference_or
     storage.destroy()
 
 
+def test_benchmark_shapes_at_32_requests(executor, oracle_mod):
+    """Two layers of the benchmark's 1.1B shape (hidden 2048, H32 / KVH4 / D64, FFN 5632, vocabulary 32000, Q6_K head)
+    with 32 requests: the launch shapes the model benchmark runs - 128-row paired tiles in three column slices for
+    gate | up, the QKV projection's rotary epilogue over 40 row tiles, the lm_head in four groups of 8000 rows, a
+    32-token prompt chunk - against the oracle's token loop."""
+    model = synth.SyntheticModel(0xB16, 2, 32, 4, 64, 5632, 32000, lm_head_quant="q6_k")
+    capacity = 40
+    pool, storage, ex = make_stack(executor, model, capacity)
+    replay = OracleModel(oracle_mod, model, capacity)
+    rng = np.random.default_rng(21)
+    ids = list(range(32))
+    for step in range(2):
+        slots = [(rid, int(rng.integers(0, model.vocab_size)), step) for rid in ids]
+        out = ex.run_decode(slots)
+        assert [o[0] for o in out] == ids and all(o[1] for o in out), executor.last_error()
+        want = replay.step(slots, {rid: ex.page_state(rid) for rid in ids})
+        assert_logits_close(np.stack([o[2] for o in out]), want, f"step {step}")
+    # request 99: a prompt of 33 tokens = one full chunk and one token
+    prompt = [int(t) for t in rng.integers(0, model.vocab_size, 33)]
+    logits = ex.run_prefill(99, prompt)
+    table, total = ex.page_state(99)
+    for pos, tok in enumerate(prompt):
+        want = replay.step([(99, tok, pos)], {99: (table, pos + 1)})
+    assert_logits_close(logits[None], want, "prefill")
+    ex.destroy()
+    storage.destroy()
+
+
 def test_scheduler_generates_the_oracles_tokens(executor, oracle_mod):
     """The scheduler over the executor with a model generates greedy tokens that the oracle model reproduces."""
     model = synth.SyntheticModel(0xFEED, 2, 4, 2, 64, 256, 512)
