@@ -85,12 +85,38 @@ __global__ void __launch_bounds__(256) rms_norm_batched_kernel(const float* __re
                                                                float eps, uint32_t length, float* __restrict__ out,
                                                                __half* __restrict__ out16, uint32_t* __restrict__ packed) {
     __shared__ float part[8];
+    // Rows of up to 4096 columns stay in registers between the two passes, and their norm weights - which no
+    // kernel writes - are fetched before the wait for the kernel in front.
+    constexpr int kKeep = 4;
+    const bool vec = (length & 3) == 0;
+    const bool keep = vec && length <= 256u * 4u * kKeep && blockDim.x == 256;
+    float4 gk[kKeep], vk[kKeep];
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) {
+            const uint32_t i = (threadIdx.x + j * 256u) * 4u;
+            if (i < length) gk[j] = __ldg(reinterpret_cast<const float4*>(w + i));
+        }
+    }
     dependent_launch_gate();
     const float* x = in + static_cast<size_t>(blockIdx.x) * length;
     float* y = out ? out + static_cast<size_t>(blockIdx.x) * length : nullptr;
     float s = 0.0f;
-    const bool vec = (length & 3) == 0;
-    if (vec) {
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) {
+            const uint32_t i = (threadIdx.x + j * 256u) * 4u;
+            if (i < length) vk[j] = *reinterpret_cast<const float4*>(x + i);
+        }
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) {
+            const uint32_t i = (threadIdx.x + j * 256u) * 4u;
+            if (i < length) {
+                const float4 v = vk[j];
+                s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+            }
+        }
+    } else if (vec) {
         for (uint32_t i = threadIdx.x * 4; i < length; i += blockDim.x * 4) {
             const float4 v = *reinterpret_cast<const float4*>(x + i);
             s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
@@ -107,29 +133,35 @@ __global__ void __launch_bounds__(256) rms_norm_batched_kernel(const float* __re
     for (int i = 0; i < 8; ++i) tot += part[i];
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, static_cast<float>(length)), eps)));
     __half* y16 = out16 ? out16 + static_cast<size_t>(blockIdx.x) * length : nullptr;
-    if (vec) {
-        for (uint32_t i = threadIdx.x * 4; i < length; i += blockDim.x * 4) {
-            const float4 v = *reinterpret_cast<const float4*>(x + i);
-            const float4 g = *reinterpret_cast<const float4*>(w + i);
-            float4 r;
-            r.x = __fmul_rn(__fmul_rn(v.x, inv), g.x);
-            r.y = __fmul_rn(__fmul_rn(v.y, inv), g.y);
-            r.z = __fmul_rn(__fmul_rn(v.z, inv), g.z);
-            r.w = __fmul_rn(__fmul_rn(v.w, inv), g.w);
-            if (y) *reinterpret_cast<float4*>(y + i) = r;
-            if (packed) {   // the mat-vec kernel's operand format: {hi0, hi1}, {lo0, lo1} per pair of columns
-                const __half2 h01 = __floats2half2_rn(r.x, r.y), h23 = __floats2half2_rn(r.z, r.w);
-                const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-                const __half2 l01 = __floats2half2_rn(r.x - f01.x, r.y - f01.y), l23 = __floats2half2_rn(r.z - f23.x, r.w - f23.y);
-                *reinterpret_cast<uint4*>(packed + static_cast<size_t>(blockIdx.x) * length + i) =
-                    make_uint4(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&l01),
-                               *reinterpret_cast<const uint32_t*>(&h23), *reinterpret_cast<const uint32_t*>(&l23));
-            }
-            if (y16) {
-                *reinterpret_cast<__half2*>(y16 + i) = __floats2half2_rn(r.x, r.y);
-                *reinterpret_cast<__half2*>(y16 + i + 2) = __floats2half2_rn(r.z, r.w);
-            }
+    auto emit = [&](uint32_t i, const float4& v, const float4& g) {
+        float4 r;
+        r.x = __fmul_rn(__fmul_rn(v.x, inv), g.x);
+        r.y = __fmul_rn(__fmul_rn(v.y, inv), g.y);
+        r.z = __fmul_rn(__fmul_rn(v.z, inv), g.z);
+        r.w = __fmul_rn(__fmul_rn(v.w, inv), g.w);
+        if (y) *reinterpret_cast<float4*>(y + i) = r;
+        if (packed) {   // the mat-vec kernel's operand format: {hi0, hi1}, {lo0, lo1} per pair of columns
+            const __half2 h01 = __floats2half2_rn(r.x, r.y), h23 = __floats2half2_rn(r.z, r.w);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const __half2 l01 = __floats2half2_rn(r.x - f01.x, r.y - f01.y), l23 = __floats2half2_rn(r.z - f23.x, r.w - f23.y);
+            *reinterpret_cast<uint4*>(packed + static_cast<size_t>(blockIdx.x) * length + i) =
+                make_uint4(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&l01),
+                           *reinterpret_cast<const uint32_t*>(&h23), *reinterpret_cast<const uint32_t*>(&l23));
         }
+        if (y16) {
+            *reinterpret_cast<__half2*>(y16 + i) = __floats2half2_rn(r.x, r.y);
+            *reinterpret_cast<__half2*>(y16 + i + 2) = __floats2half2_rn(r.z, r.w);
+        }
+    };
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) {
+            const uint32_t i = (threadIdx.x + j * 256u) * 4u;
+            if (i < length) emit(i, vk[j], gk[j]);
+        }
+    } else if (vec) {
+        for (uint32_t i = threadIdx.x * 4; i < length; i += blockDim.x * 4)
+            emit(i, *reinterpret_cast<const float4*>(x + i), *reinterpret_cast<const float4*>(w + i));
     } else {
         for (uint32_t i = threadIdx.x; i < length; i += blockDim.x) {
             const float r = __fmul_rn(__fmul_rn(x[i], inv), w[i]);
