@@ -840,6 +840,27 @@ int mlc_encode_paged_flash_attention_planned(mlc_ctx* ctx, const mlc_attn_plan* 
     return launch_with_plan(ctx, a, *plan);
 }
 
+}  // extern "C"
+
+namespace mlcb {
+// mlc_encode_paged_flash_attention_planned for a caller that knows what the kernel in front wrote (see
+// AttnArgs::only_plan_rows_written): the walker's decode pass, whose QKV projection writes the newest token's rows.
+int encode_attention_planned_after_row_write(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q, const void* k_pages,
+                                             const void* v_pages, void* o, float scale, int q_dtype, int o_dtype) {
+    if (!ctx || !plan) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    DeviceGuard guard(ctx->device);
+    if (int ust = use_plan(ctx, plan); ust != MLC_OK) return ust;
+    AttnArgs a;
+    a.q = q; a.k_pages = k_pages; a.v_pages = v_pages; a.o = o;
+    a.scale = scale; a.q_dtype = q_dtype; a.o_dtype = o_dtype;
+    a.only_plan_rows_written = true;
+    return launch_with_plan(ctx, a, *plan);
+}
+}  // namespace mlcb
+
+extern "C" {
+
 int mlc_encode_paged_attention_partial_planned(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q,
                                                const void* k_pages, const void* v_pages,
                                                float* o_partial, float* ml_partial, float scale,

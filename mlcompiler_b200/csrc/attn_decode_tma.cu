@@ -186,6 +186,7 @@ struct DecodeParams {
     int step;           // 1: decode-step variant (fused row write, early start)
     int pdl;            // 1: launched with programmatic stream serialisation
     int early_fetch;    // 1: a decode step may fetch tiles of earlier steps' rows before griddepcontrol.wait
+    int fresh_rows;     // 1: not a decode step, but the kernel in front wrote only the rows the plan marks as fresh
     unsigned long long* trace;  // optional [cta][warp][8] %globaltimer stamps (MLC_B200_TRACE)
     // In-kernel merge: one arrival counter per (split segment, warp); null = a merge kernel follows.
     uint32_t* seg_counters;
@@ -488,7 +489,7 @@ __device__ __forceinline__ void decode_layer_body(const CUtensorMap& tmK, const 
     uint32_t next_issue = 0;  // next CTA-local tile to fetch
     const uint32_t window = n_tiles < stages ? n_tiles : stages;
     if (prm.pdl) {
-        if (prm.step && prm.early_fetch) {
+        if ((prm.step || prm.fresh_rows) && prm.early_fetch) {
             while (next_issue < window) {
                 const uint32_t e = tile_entry(next_issue);
                 if (e & kTileFreshBit) break;
@@ -2518,7 +2519,8 @@ int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePla
     // second has let its dependents go, while the first is still writing its new rows into pool A. Tiles
     // fetched before the wait must not come from a pool that one of the two launches before this one
     // writes, so in that case (passes of one or two layers) the early fetch is left out.
-    prm.early_fetch = (step && recently_written(ctx, a.k_pages, a.v_pages)) ? 0 : 1;
+    prm.fresh_rows = (!step && a.only_plan_rows_written && plan.step_fusable) ? 1 : 0;
+    prm.early_fetch = ((step || prm.fresh_rows) && recently_written(ctx, a.k_pages, a.v_pages)) ? 0 : 1;
     std::swap(ctx->recent_writes[0], ctx->recent_writes[1]);   // no allocation: the lists keep their storage
     ctx->recent_writes[1].few[0] = step ? a.k_pages : nullptr;
     ctx->recent_writes[1].few[1] = step ? a.v_pages : nullptr;

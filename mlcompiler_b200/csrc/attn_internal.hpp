@@ -25,6 +25,11 @@ struct AttnArgs {
     // the attention kernel itself (the pools are then written to, not only read).
     const void* k_new = nullptr;
     const void* v_new = nullptr;
+    // The kernel in front wrote nothing into the pools but the rows at the plan's (page, slot) per request - the
+    // newest token of every request (a step-fusable plan marks the tiles that hold them): every other tile may be
+    // fetched before the wait for that kernel, as in a decode step. Not for prompt chunks, whose rows land in tiles
+    // that other entries of the batch read.
+    bool only_plan_rows_written = false;
     // Caller-provided split-KV workspace (device memory) instead of the context's own;
     // when set, the launch makes no device or host allocation at all.
     void* ext_work = nullptr;
@@ -109,6 +114,8 @@ int launch_scatter_rows_device_tables(mlc_ctx* ctx, void* k_pool, void* v_pool, 
                                       const uint32_t* d_slots, size_t P, size_t KVH, size_t D,
                                       size_t batch, const void* k_src, const void* v_src, size_t capacity);
 int launch_attention_decode_tma(mlc_ctx* ctx, const AttnArgs& a, const DecodePlanView& plan);
+int encode_attention_planned_after_row_write(mlc_ctx* ctx, const mlc_attn_plan* plan, const void* q, const void* k_pages,
+                                             const void* v_pages, void* o, float scale, int q_dtype, int o_dtype);
 // Whole-pass launch: every layer's decode step (row write + attention) in one kernel. `shape` carries the
 // plan's shape, scale and dtypes. MLC_ERR_UNSUPPORTED (without an error text) when a layer's pointers do not
 // meet the TMA kernel's alignment rules: the caller then launches layer by layer.

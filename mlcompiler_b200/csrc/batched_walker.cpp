@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 #include <nvtx3/nvToolsExt.h>
 
+#include "attn_internal.hpp"
 #include "ctx.hpp"
 
 namespace mlcb {
@@ -137,7 +138,8 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, c
         const double t_plan = walker_trace() ? now_us() : 0.0;
         bool ok = mlc_pass_begin(ctx) == MLC_OK;
         ok = ok && encode_model_pass(slots, plan, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos,
-                                     direct ? sink->dst : logits_pinned_, direct ? sink->stride : vocab, 0);
+                                     direct ? sink->dst : logits_pinned_, direct ? sink->stride : vocab, 0,
+                                     true);   // a decode pass writes one row per request, at the plan's (page, slot)
         const double t_enc = walker_trace() ? now_us() : 0.0;
         ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;   // the logits are on the host when this returns
         const double t_flush = walker_trace() ? now_us() : 0.0;
@@ -247,7 +249,8 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                                       const std::vector<uint32_t>& page_ids, const std::vector<uint32_t>& slot_ids,
                                       const std::vector<uint32_t>& pt_flat, const std::vector<uint32_t>& pt_off,
                                       const std::vector<uint32_t>& seq_lens, const std::vector<uint32_t>& q_pos,
-                                      float* logits_host, size_t logits_stride, size_t head_first) {
+                                      float* logits_host, size_t logits_stride, size_t head_first,
+                                      bool rows_per_request_only) {
     PagedAttentionExecutor& ex = exec_;
     mlc_ctx* ctx = ex.ctx_;
     PagedKVStorage* storage = ex.storage_;
@@ -336,7 +339,9 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
         if (fused) {
             ok = (qkv_epilogue || mlc_encode_qkv_split_rope_scatter_planned(ctx, plan, qkv, q, MLC_F16, kp, vp, cos_t, sin_t,
                                                                             qkv_rows, m.rotary_dim) == MLC_OK) &&
-                 mlc_encode_paged_flash_attention_planned(ctx, plan, q, kp, vp, attn_mix, scale, MLC_F16, MLC_F32) == MLC_OK &&
+                 (rows_per_request_only
+                      ? encode_attention_planned_after_row_write(ctx, plan, q, kp, vp, attn_mix, scale, MLC_F16, MLC_F32)
+                      : mlc_encode_paged_flash_attention_planned(ctx, plan, q, kp, vp, attn_mix, scale, MLC_F16, MLC_F32)) == MLC_OK &&
                  mlc_encode_matmul_quant_fused(ctx, 0, w.attn_output, attn_mix, hidden, 0, residual, N, hidden, hidden,
                                                row_h, resid1) == MLC_OK &&
                  mlc_encode_rms_norm_batched_packed(ctx, resid1, w.ffn_norm, eps, N, hidden, nullptr, norm_o) == MLC_OK &&
@@ -470,7 +475,7 @@ std::vector<float> BatchedWalker::prefill_model(uint32_t request_id, const std::
         const bool last = done + n == tokens.size();
         bool ok = mlc_pass_begin(ctx) == MLC_OK;
         ok = ok && encode_model_pass(slots, slot, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos, logits_pinned_, vocab,
-                                     last ? n - 1 : n);
+                                     last ? n - 1 : n, false);   // a chunk's rows are context of the chunk's later tokens
         ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
         if (!ok) return {};
     }

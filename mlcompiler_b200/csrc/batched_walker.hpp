@@ -33,10 +33,13 @@ public:
 private:
     // The layers of a pass with a model attached: encodes embedding .. lm_head onto the open pass and the copies of
     // the logits of rows [head_first, N) into page-locked host rows `logits_stride` floats apart.
+    // rows_per_request_only: every entry of the batch is a request of its own (a decode pass), so the only rows a
+    // layer's QKV projection writes are the newest token's of each entry and attention may fetch everything else early.
     bool encode_model_pass(const std::vector<RequestSlot>& slots, mlc_attn_plan* plan, const std::vector<uint32_t>& page_ids,
                            const std::vector<uint32_t>& slot_ids, const std::vector<uint32_t>& pt_flat,
                            const std::vector<uint32_t>& pt_off, const std::vector<uint32_t>& seq_lens,
-                           const std::vector<uint32_t>& q_pos, float* logits_host, size_t logits_stride, size_t head_first);
+                           const std::vector<uint32_t>& q_pos, float* logits_host, size_t logits_stride, size_t head_first,
+                           bool rows_per_request_only);
 
     PagedAttentionExecutor& exec_;
     std::vector<float> cos_host_, sin_host_;
