@@ -717,6 +717,31 @@ int64_t mlc_gguf_tensor_data(mlc_gguf* file, const char* name, void* dst, size_t
                              size_t error_capacity);
 int mlc_executor_attach_gguf(mlc_executor* exec, mlc_gguf* file, char* error, size_t error_capacity);
 
+/* ---- Tokenizer (compiler/runtime/tokenizer.{hpp,cpp}: Tokenizer, as built without llama.cpp) -------
+ * Text <-> token ids from the vocabulary of a GGUF file (tokenizer.ggml.model / tokens / scores / merges /
+ * bos_token_id / eos_token_id / unk_token_id): best-score segmentation for "llama" / "spm" / "unigram"
+ * vocabularies, lowest-rank-first byte-pair merges for "gpt2" / "bpe" (and for a file with merges and no
+ * model key), longest-match when neither produced anything and no BOS was put in front; "<0xHH>" pieces
+ * are bytes. Same results as the reference's own code paths (tokenizer.cpp:153-244, 246-283, 327-423) on
+ * the same file and text; its optional llama.cpp path is not reproduced.
+ *   mlc_tokenizer_create        Tokenizer(loader); the file may be closed afterwards
+ *   mlc_tokenizer_info          returns valid(); vocabSize(), bosId(), eosId(), unkId() (UINT64_MAX = unset)
+ *   mlc_tokenizer_encode        encode(text, {add_bos, add_eos}): returns the number of ids, copies at
+ *                               most `capacity`
+ *   mlc_tokenizer_decode        decode(ids): returns the number of bytes, copies at most `capacity`
+ *                               (no terminator)
+ *   mlc_tokenizer_token_string  tokenString(id), same convention
+ *   mlc_tokenizer_token_flags   bit 0 isControlToken(id), bit 1 isEogToken(id) */
+typedef struct mlc_tokenizer mlc_tokenizer;
+mlc_tokenizer* mlc_tokenizer_create(mlc_gguf* file);
+void mlc_tokenizer_destroy(mlc_tokenizer* tokenizer);
+int mlc_tokenizer_info(const mlc_tokenizer* tokenizer, size_t* vocab_size, uint64_t* bos, uint64_t* eos, uint64_t* unk);
+size_t mlc_tokenizer_encode(const mlc_tokenizer* tokenizer, const char* text, size_t length, int add_bos, int add_eos,
+                            uint64_t* ids, size_t capacity);
+size_t mlc_tokenizer_decode(const mlc_tokenizer* tokenizer, const uint64_t* ids, size_t n, char* out, size_t capacity);
+size_t mlc_tokenizer_token_string(const mlc_tokenizer* tokenizer, uint64_t id, char* out, size_t capacity);
+int mlc_tokenizer_token_flags(const mlc_tokenizer* tokenizer, uint64_t id);
+
 /* No counterpart in the reference. Gives a request without pages a context of `tokens` tokens whose
  * K/V rows the caller has put (or will put) into the storage itself: reserves its pages
  * (RequestKVState::reserve) and sets its next position to `tokens`. For restoring a saved context and

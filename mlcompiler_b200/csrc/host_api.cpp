@@ -9,6 +9,7 @@
 #include "../../include/mlc_b200.h"
 #include "batched_executor.hpp"
 #include "gguf_file.hpp"
+#include "tokenizer.hpp"
 #include "paged_kv.hpp"
 #include "scheduler.hpp"
 
@@ -65,6 +66,11 @@ struct mlc_executor {
 struct mlc_gguf {
     std::unique_ptr<mlcb::gguf::File> file;
     std::string json;   // describe_json(), made on demand
+};
+
+struct mlc_tokenizer {
+    explicit mlc_tokenizer(const mlcb::gguf::File& f) : tok(f) {}
+    mlcb::text::Tokenizer tok;
 };
 
 struct mlc_scheduler {
@@ -267,6 +273,56 @@ int mlc_executor_attach_gguf(mlc_executor* e, mlc_gguf* g, char* error, size_t e
     if (e->paged->attach_gguf(*g->file, &what)) return MLC_OK;
     copy_message(what, error, error_capacity);
     return MLC_ERR_INVALID_ARG;
+}
+
+// ---- tokenizer -----------------------------------------------------------------------
+mlc_tokenizer* mlc_tokenizer_create(mlc_gguf* g) {
+    if (!g) return nullptr;
+    try {
+        return new mlc_tokenizer(*g->file);
+    } catch (const std::exception&) {
+        return nullptr;
+    }
+}
+void mlc_tokenizer_destroy(mlc_tokenizer* t) { delete t; }
+int mlc_tokenizer_info(const mlc_tokenizer* t, size_t* vocab_size, uint64_t* bos, uint64_t* eos, uint64_t* unk) {
+    if (!t) return 0;
+    if (vocab_size) *vocab_size = t->tok.vocab_size();
+    if (bos) *bos = t->tok.bos();
+    if (eos) *eos = t->tok.eos();
+    if (unk) *unk = t->tok.unk();
+    return t->tok.valid() ? 1 : 0;
+}
+size_t mlc_tokenizer_encode(const mlc_tokenizer* t, const char* text, size_t length, int add_bos, int add_eos, uint64_t* ids,
+                            size_t capacity) {
+    if (!t || (!text && length)) return 0;
+    try {
+        const std::vector<uint64_t> out = t->tok.encode(std::string(text ? text : "", length), add_bos != 0, add_eos != 0);
+        for (size_t i = 0; ids && i < out.size() && i < capacity; ++i) ids[i] = out[i];
+        return out.size();
+    } catch (const std::exception&) {
+        return 0;
+    }
+}
+size_t mlc_tokenizer_decode(const mlc_tokenizer* t, const uint64_t* ids, size_t n, char* out, size_t capacity) {
+    if (!t || (!ids && n)) return 0;
+    try {
+        const std::string s = t->tok.decode(ids, n);
+        if (out) std::memcpy(out, s.data(), std::min(capacity, s.size()));
+        return s.size();
+    } catch (const std::exception&) {
+        return 0;
+    }
+}
+size_t mlc_tokenizer_token_string(const mlc_tokenizer* t, uint64_t id, char* out, size_t capacity) {
+    if (!t) return 0;
+    const std::string s = t->tok.token_string(id);
+    if (out) std::memcpy(out, s.data(), std::min(capacity, s.size()));
+    return s.size();
+}
+int mlc_tokenizer_token_flags(const mlc_tokenizer* t, uint64_t id) {
+    if (!t) return 0;
+    return (t->tok.is_control(id) ? 1 : 0) | (t->tok.is_eog(id) ? 2 : 0);
 }
 
 int mlc_executor_assume_context(mlc_executor* e, uint32_t request_id, size_t tokens) {

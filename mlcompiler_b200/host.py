@@ -84,6 +84,13 @@ _PROTOTYPES = {
     "mlc_gguf_describe": (_sz, [_vp, C.c_char_p, _sz]),
     "mlc_gguf_tensor_data": (C.c_int64, [_vp, C.c_char_p, _vp, _sz, C.c_char_p, _sz]),
     "mlc_executor_attach_gguf": (_i, [_vp, _vp, C.c_char_p, _sz]),
+    "mlc_tokenizer_create": (_vp, [_vp]),
+    "mlc_tokenizer_destroy": (None, [_vp]),
+    "mlc_tokenizer_info": (_i, [_vp, _szp, _u64p, _u64p, _u64p]),
+    "mlc_tokenizer_encode": (_sz, [_vp, C.c_char_p, _sz, _i, _i, _u64p, _sz]),
+    "mlc_tokenizer_decode": (_sz, [_vp, _u64p, _sz, C.c_char_p, _sz]),
+    "mlc_tokenizer_token_string": (_sz, [_vp, _u64, C.c_char_p, _sz]),
+    "mlc_tokenizer_token_flags": (_i, [_vp, _u64]),
     "mlc_executor_run_decode": (_sz, [_vp, C.POINTER(RequestSlotC), _sz, C.POINTER(C.c_uint8), _fp, _sz]),
     "mlc_executor_run_prefill": (_sz, [_vp, _u32, _u64p, _sz, _fp, _sz]),
     "mlc_executor_release_request": (None, [_vp, _u32]),
@@ -271,6 +278,72 @@ class GgufFile:
         out = np.zeros(n, np.uint8)
         lib().mlc_gguf_tensor_data(self._h, name.encode(), out.ctypes.data_as(_vp), n, err, len(err))
         return out
+
+
+class Tokenizer:
+    """runtime::Tokenizer (compiler/runtime/tokenizer.hpp:22-77) over the vocabulary of a GgufFile. Text goes in and
+    comes out as bytes (str is encoded / decoded as UTF-8)."""
+    NONE = 2 ** 64 - 1
+
+    def __init__(self, file: GgufFile):
+        self._h = lib().mlc_tokenizer_create(file._h)
+        if not self._h:
+            raise RuntimeError("tokenizer could not be built")
+        n, b, e, u = C.c_size_t(), C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self._valid = bool(lib().mlc_tokenizer_info(self._h, C.byref(n), C.byref(b), C.byref(e), C.byref(u)))
+        self._vocab, self._bos, self._eos, self._unk = n.value, b.value, e.value, u.value
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                lib().mlc_tokenizer_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def valid(self) -> bool:
+        return self._valid
+
+    def vocabSize(self) -> int:
+        return self._vocab
+
+    def bosId(self) -> int:
+        return self._bos
+
+    def eosId(self) -> int:
+        return self._eos
+
+    def unkId(self) -> int:
+        return self._unk
+
+    def encode(self, text, add_bos: bool = True, add_eos: bool = False) -> list:
+        data = text.encode("utf-8") if isinstance(text, str) else bytes(text)
+        n = lib().mlc_tokenizer_encode(self._h, data, len(data), int(add_bos), int(add_eos), None, 0)
+        ids = (C.c_uint64 * max(n, 1))()
+        lib().mlc_tokenizer_encode(self._h, data, len(data), int(add_bos), int(add_eos), ids, n)
+        return [int(ids[i]) for i in range(n)]
+
+    def decode_bytes(self, ids) -> bytes:
+        arr = (C.c_uint64 * max(len(ids), 1))(*[int(i) for i in ids])
+        n = lib().mlc_tokenizer_decode(self._h, arr, len(ids), None, 0)
+        buf = C.create_string_buffer(max(n, 1))
+        lib().mlc_tokenizer_decode(self._h, arr, len(ids), buf, n)
+        return buf.raw[:n]
+
+    def decode(self, ids) -> str:
+        return self.decode_bytes(ids).decode("utf-8", errors="replace")
+
+    def tokenString(self, token_id: int) -> bytes:
+        n = lib().mlc_tokenizer_token_string(self._h, token_id, None, 0)
+        buf = C.create_string_buffer(max(n, 1))
+        lib().mlc_tokenizer_token_string(self._h, token_id, buf, n)
+        return buf.raw[:n]
+
+    def isControlToken(self, token_id: int) -> bool:
+        return bool(lib().mlc_tokenizer_token_flags(self._h, token_id) & 1)
+
+    def isEogToken(self, token_id: int) -> bool:
+        return bool(lib().mlc_tokenizer_token_flags(self._h, token_id) & 2)
 
 
 class _ExecutorBase:

@@ -159,6 +159,17 @@ def ref():
         lib.ref_gguf_describe.argtypes = [C.c_char_p, _i, C.c_char_p, _sz]
         lib.ref_gguf_tensor.restype = C.c_longlong
         lib.ref_gguf_tensor.argtypes = [C.c_char_p, C.c_char_p, _i, C.c_void_p, _sz]
+        lib.ref_tokenizer_create.restype = _vp
+        lib.ref_tokenizer_create.argtypes = [C.c_char_p]
+        lib.ref_tokenizer_destroy.argtypes = [_vp]
+        lib.ref_tokenizer_info.argtypes = [_vp, C.POINTER(C.c_ulonglong)]
+        lib.ref_tokenizer_encode.restype = _sz
+        lib.ref_tokenizer_encode.argtypes = [_vp, C.c_char_p, _sz, _i, _i, C.POINTER(C.c_ulonglong), _sz]
+        lib.ref_tokenizer_decode.restype = _sz
+        lib.ref_tokenizer_decode.argtypes = [_vp, C.POINTER(C.c_ulonglong), _sz, C.c_char_p, _sz]
+        lib.ref_tokenizer_token_string.restype = _sz
+        lib.ref_tokenizer_token_string.argtypes = [_vp, C.c_ulonglong, C.c_char_p, _sz]
+        lib.ref_tokenizer_flags.argtypes = [_vp, C.c_ulonglong]
         for q in ("q4_0", "q6_k"):
             getattr(lib, f"ref_dequant_{q}").restype = None
             getattr(lib, f"ref_dequant_{q}").argtypes = [_u8p, _sz, _fp]
@@ -405,3 +416,48 @@ def reference_gguf_tensor(path, name, concatenate=False):
     out = np.zeros(n, np.uint8)
     lib.ref_gguf_tensor(str(path).encode(), name.encode(), 1 if concatenate else 0, out.ctypes.data_as(C.c_void_p), n)
     return out
+
+
+class ReferenceTokenizer:
+    """The reference's runtime::Tokenizer (compiler/runtime/tokenizer.cpp, compiled without llama.cpp: its own BPE /
+    unigram / greedy code) over a GGUF file. Text is bytes in and out."""
+
+    def __init__(self, path):
+        lib = ref()
+        assert lib is not None, "the reference library is not available here"
+        self._lib = lib
+        self._h = lib.ref_tokenizer_create(str(path).encode())
+        assert self._h, "the reference could not load the file"
+        info = (C.c_ulonglong * 5)()
+        lib.ref_tokenizer_info(self._h, info)
+        self.valid, self.vocab_size, self.bos, self.eos, self.unk = bool(info[0]), *[int(v) for v in info[1:]]
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                self._lib.ref_tokenizer_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def encode(self, data: bytes, add_bos=True, add_eos=False):
+        n = self._lib.ref_tokenizer_encode(self._h, data, len(data), int(add_bos), int(add_eos), None, 0)
+        ids = (C.c_ulonglong * max(n, 1))()
+        self._lib.ref_tokenizer_encode(self._h, data, len(data), int(add_bos), int(add_eos), ids, n)
+        return [int(ids[i]) for i in range(n)]
+
+    def decode(self, ids) -> bytes:
+        arr = (C.c_ulonglong * max(len(ids), 1))(*[int(i) for i in ids])
+        n = self._lib.ref_tokenizer_decode(self._h, arr, len(ids), None, 0)
+        buf = C.create_string_buffer(max(n, 1))
+        self._lib.ref_tokenizer_decode(self._h, arr, len(ids), buf, n)
+        return buf.raw[:n]
+
+    def token_string(self, token_id) -> bytes:
+        n = self._lib.ref_tokenizer_token_string(self._h, token_id, None, 0)
+        buf = C.create_string_buffer(max(n, 1))
+        self._lib.ref_tokenizer_token_string(self._h, token_id, buf, n)
+        return buf.raw[:n]
+
+    def flags(self, token_id) -> int:
+        return int(self._lib.ref_tokenizer_flags(self._h, token_id))

@@ -27,6 +27,7 @@
 #include "runtime/quant_utils.hpp"
 #include "runtime/quantization.hpp"
 #include "runtime/session.hpp"
+#include "runtime/tokenizer.hpp"
 #include "runtime/float_convert.hpp"
 #include "runtime/paged_kv.hpp"
 #include "runtime/scheduler.hpp"
@@ -457,6 +458,58 @@ long long ref_gguf_tensor(const char* path, const char* name, int concatenate, u
     } catch (const std::exception&) {
         return -1;
     }
+}
+
+// ---- the reference's tokenizer (compiler/runtime/tokenizer.cpp, its own BPE / unigram / greedy code) ----------
+struct RefTokenizer {
+    std::unique_ptr<mlc::frontend::GGUFLoader> loader;
+    std::unique_ptr<mlc::runtime::Tokenizer> tok;
+};
+void* ref_tokenizer_create(const char* gguf_path) {
+    try {
+        auto t = std::make_unique<RefTokenizer>();
+        t->loader = std::make_unique<mlc::frontend::GGUFLoader>(gguf_path);
+        t->loader->load();
+        t->tok = std::make_unique<mlc::runtime::Tokenizer>(*t->loader);
+        return t.release();
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ref_tokenizer_create: %s\n", e.what());
+        return nullptr;
+    }
+}
+void ref_tokenizer_destroy(void* h) { delete static_cast<RefTokenizer*>(h); }
+// valid, vocabulary size, bos, eos, unk (UINT64_MAX when unset)
+void ref_tokenizer_info(void* h, unsigned long long* out5) {
+    const auto& t = *static_cast<RefTokenizer*>(h)->tok;
+    out5[0] = t.valid() ? 1 : 0;
+    out5[1] = t.vocabSize();
+    out5[2] = t.bosId();
+    out5[3] = t.eosId();
+    out5[4] = t.unkId();
+}
+size_t ref_tokenizer_encode(void* h, const char* text, size_t len, int add_bos, int add_eos, unsigned long long* ids,
+                            size_t capacity) {
+    mlc::runtime::TokenizerConfig cfg;
+    cfg.add_bos = add_bos != 0;
+    cfg.add_eos = add_eos != 0;
+    const auto out = static_cast<RefTokenizer*>(h)->tok->encode(std::string(text, len), cfg);
+    for (size_t i = 0; i < out.size() && i < capacity; ++i) ids[i] = out[i];
+    return out.size();
+}
+size_t ref_tokenizer_decode(void* h, const unsigned long long* ids, size_t n, char* out, size_t capacity) {
+    std::vector<uint64_t> v(ids, ids + n);
+    const std::string s = static_cast<RefTokenizer*>(h)->tok->decode(v);
+    if (out) std::memcpy(out, s.data(), std::min(capacity, s.size()));
+    return s.size();
+}
+size_t ref_tokenizer_token_string(void* h, unsigned long long id, char* out, size_t capacity) {
+    const std::string s = static_cast<RefTokenizer*>(h)->tok->tokenString(id);
+    if (out) std::memcpy(out, s.data(), std::min(capacity, s.size()));
+    return s.size();
+}
+int ref_tokenizer_flags(void* h, unsigned long long id) {
+    const auto& t = *static_cast<RefTokenizer*>(h)->tok;
+    return (t.isControlToken(id) ? 1 : 0) | (t.isEogToken(id) ? 2 : 0);
 }
 
 }  // extern "C"

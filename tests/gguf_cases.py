@@ -109,3 +109,84 @@ def canonical(desc):
     out["kv"] = kv
     out["tensors"] = desc["tensors"]
     return out
+
+
+# ---- vocabularies for the tokenizer tests ------------------------------------------------------------------------
+def _spm_vocab():
+    pieces = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)]
+    words = ["▁", "▁the", "▁a", "▁an", "the", "th", "he", "e", "▁hello", "hello", "hell", "lo", "l", "o", "h", "▁w", "or",
+             "ld", "▁world", "world", "▁wor", "a", "n", "an", "d", "▁and", "t", "s", "▁s", "er", "r", "▁", "▁▁", "é", "▁caf",
+             "c", "f", "af", "!", ",", ".", "▁.", "日本", "日", "本", "<|sys|>", "in", "g", "ing", "▁th", "w", "x"]
+    pieces += words
+    rng = np.random.default_rng(5)
+    scores = [-30.0, 0.0, 0.0] + [-20.0] * 256 + [float(-rng.uniform(1.0, 12.0)) - 0.5 * (8 - min(len(w), 8)) for w in words]
+    return pieces, scores
+
+
+def _bpe_vocab():
+    singles = [chr(c) for c in range(32, 127)] + ["Ġ", "é"]
+    merges = ["h e", "l l", "he ll", "hell o", "l o", "lo w", "e r", "low er", "t h", "th e", "w o", "wo r", "r l",
+              "wor l", "worl d", "a n", "an d", "i n", "in g", "no_space_entry", "e s", "es t", "n e", "ne w", "new est",
+              "h e"]           # a repeated merge keeps its last rank
+    merged = sorted({m.replace(" ", "") for m in merges if " " in m})
+    return ["<|endoftext|>"] + singles + merged, merges
+
+
+TOKENIZER_CASES = {
+    "spm": dict(model="llama", ids="u32"),
+    "spm_u64_ids": dict(model="spm", ids="u64"),
+    "spm_unk_zero": dict(model="llama", ids="u32", unk_score=0.0),          # an unknown byte costs nothing: it always wins
+    "spm_no_unk": dict(model="unigram", ids="u32", drop=("unk",)),
+    "spm_short_scores": dict(model="llama", ids="u32", short_scores=True),     # scores do not cover the vocabulary
+    "spm_f64_scores": dict(model="llama", ids="u32", f64_scores=True),
+    "bpe": dict(model="gpt2", ids="u32"),
+    "bpe_no_merges": dict(model="bpe", ids="u32", no_merges=True),
+    "no_model_merges": dict(model=None, ids="u32", base="bpe"),
+    "no_model_scores": dict(model=None, ids="u32", base="spm"),
+    "other_model": dict(model="wordpiece", ids="u32", base="spm"),
+    "bare": dict(model=None, ids=None, base="spm", no_scores=True),            # tokens only: longest match
+    "i32_ids": dict(model="llama", ids="i32"),                                 # ids of another integer type count as unset
+    "empty": dict(model="llama", ids="u32", no_tokens=True),
+}
+
+TOKENIZER_TEXTS = ["", "hello world", " hello world", "the hello and the world", "hello, world!", "café.", "日本 the",
+                   "lower newest and lowest", "thethethe", "xyz\x01\xff", "  a  an   the ", "<s>hello</s>", "world" * 40,
+                   "▁the▁world", "new\nline\ttab", "<|sys|> in going"]
+
+
+def text_bytes(text) -> bytes:
+    """The test texts as the bytes handed to the tokenizers: characters up to U+00FF written with \\x escapes are raw
+    bytes (so that invalid UTF-8 is covered), everything else UTF-8."""
+    return b"".join(bytes([ord(c)]) if ord(c) < 256 and not c.isalpha() and ord(c) > 127 or ord(c) < 32 else c.encode("utf-8") for c in text)
+
+
+def tokenizer_file(path, name):
+    spec = TOKENIZER_CASES[name]
+    base = spec.get("base", "bpe" if name.startswith("bpe") else "spm")
+    kv = [("general.architecture", "string", "llama")]
+    if spec["model"] is not None:
+        kv.append(("tokenizer.ggml.model", "string", spec["model"]))
+    if base == "spm":
+        pieces, scores = _spm_vocab()
+        merges = None
+        ids = {"bos": 1, "eos": 2, "unk": 0}
+    else:
+        pieces, merges = _bpe_vocab()
+        scores = None
+        ids = {"bos": 0, "eos": 0}
+    if not spec.get("no_tokens"):
+        kv.append(("tokenizer.ggml.tokens", ("array", "string"), pieces))
+    if scores is not None and not spec.get("no_scores"):
+        if "unk_score" in spec:
+            scores = [spec["unk_score"]] + scores[1:]
+        if spec.get("short_scores"):
+            scores = scores[:-3]
+        kv.append(("tokenizer.ggml.scores", ("array", "f64" if spec.get("f64_scores") else "f32"), scores))
+    if merges is not None and not spec.get("no_merges"):
+        kv.append(("tokenizer.ggml.merges", ("array", "string"), merges))
+    if spec["ids"]:
+        for key, value in ids.items():
+            if key not in spec.get("drop", ()):
+                kv.append((f"tokenizer.ggml.{key}_token_id", spec["ids"], value))
+    synth.write_gguf(path, kv, [])
+    return len(pieces)
