@@ -160,7 +160,8 @@ def text_bytes(text) -> bytes:
     return b"".join(bytes([ord(c)]) if ord(c) < 256 and not c.isalpha() and ord(c) > 127 or ord(c) < 32 else c.encode("utf-8") for c in text)
 
 
-def tokenizer_file(path, name):
+def tokenizer_kv(name):
+    """(metadata triples of the vocabulary case, number of pieces)"""
     spec = TOKENIZER_CASES[name]
     base = spec.get("base", "bpe" if name.startswith("bpe") else "spm")
     kv = [("general.architecture", "string", "llama")]
@@ -188,5 +189,10 @@ def tokenizer_file(path, name):
         for key, value in ids.items():
             if key not in spec.get("drop", ()):
                 kv.append((f"tokenizer.ggml.{key}_token_id", spec["ids"], value))
+    return kv, len(pieces)
+
+
+def tokenizer_file(path, name):
+    kv, n = tokenizer_kv(name)
     synth.write_gguf(path, kv, [])
-    return len(pieces)
+    return n

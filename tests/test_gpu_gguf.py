@@ -6,7 +6,8 @@ import numpy as np
 import pytest
 
 from mlcompiler_b200 import synth
-from mlcompiler_b200.host import GgufFile, PagePool, PagedAttentionExecutor, PagedKVStorage
+import gguf_cases
+from mlcompiler_b200.host import GgufFile, PagePool, PagedAttentionExecutor, PagedKVStorage, Scheduler, Tokenizer
 
 pytestmark = pytest.mark.gpu
 
@@ -88,3 +89,42 @@ def test_tied_embeddings_and_refusals(executor, tmp_path):
         x.destroy()
     for s in (sa, sb):
         s.destroy()
+
+
+def test_text_in_text_out_from_one_file(executor, tmp_path):
+    """What the reference's chat loop does with a checkpoint (tests/test_scheduler_e2e.cpp needs the TinyLlama file):
+    one GGUF file carries vocabulary and weights; the tokenizer turns a prompt into ids, the scheduler generates over
+    the executor that loaded the weights, the tokenizer turns the ids back into text. The weights are synthetic, so the
+    text means nothing - the ids must be those the same weights give when attached by pointer, run after run."""
+    kv, vocab = gguf_cases.tokenizer_kv("spm")
+    model = synth.SyntheticModel(0x7E47, 2, 4, 2, 64, 512, vocab, lm_head_quant="q6_k")
+    path = tmp_path / "chat.gguf"
+    model.write_gguf(path, extra_kv=[t for t in kv if t[0] != "general.architecture"])
+    f = GgufFile(path)
+    tok = Tokenizer(f)
+    assert tok.valid() and tok.vocabSize() == vocab
+    prompt = tok.encode("the hello and the world")
+    assert prompt[0] == tok.bosId() and tok.decode(prompt) == "the hello and the world"
+
+    def generate(attach):
+        _, storage, ex = _stack(executor, model)
+        attach(ex)
+        sched = Scheduler(ex, max_batch_size=2)
+        rids = [sched.add_request(prompt, max_new_tokens=12, eos_token_id=tok.eosId()),
+                sched.add_request(tok.encode("hello"), max_new_tokens=5, eos_token_id=tok.eosId())]
+        sched.run_until_idle()
+        done = {r["id"]: list(r["generated_tokens"]) for r in sched.drain_completed()}
+        ex.destroy()
+        storage.destroy()
+        return [done[r] for r in rids]
+
+    def from_file(ex):
+        assert ex.attach_gguf(f), ex.attach_error
+
+    def from_pointers(ex):
+        assert ex.attach_model(model.to_device())
+
+    a, b, c = generate(from_file), generate(from_pointers), generate(from_file)
+    assert a == b == c
+    assert all(1 <= len(g) <= n for g, n in zip(a, (12, 5))) and all(0 <= t < vocab for g in a for t in g)
+    assert isinstance(tok.decode(a[0]), str)
