@@ -541,7 +541,7 @@ def run_gpu_arm(args):
                 secondary[name] = {k: r[k] for k in r if k in ("metric", "value", "unit", "ms_per_step", "us_per_step", "scaling",
                                                                 "config", "roofline", "gpu_launches", "split_vs_one_gpu",
                                                                 "tokens_per_s", "error", "ms_per_step_median_min_max",
-                                                                "bytes_per_step", "launches_per_step", "prefill")}
+                                                                "bytes_per_step", "launches_per_step", "prefill", "served")}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

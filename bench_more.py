@@ -392,7 +392,9 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False, from_ggu
     model = synth.SyntheticModel(0x11B, L, H, KVH, D, inner, vocab, lm_head_quant="q6_k")
     lens = np.resize(synth.config_lengths(2), batch).astype(np.int64)   # past 32 requests the lengths repeat
     total_steps = steps + max(warmup, 3)
-    capacity = int(sum((int(l) + total_steps + P - 1) // P for l in lens)) + 4 + 2 * ((prompt_tokens + P - 1) // P + 1)
+    sched_prompt, sched_new = 128, 64
+    capacity = (int(sum((int(l) + total_steps + P - 1) // P for l in lens)) + 4 + 2 * ((prompt_tokens + P - 1) // P + 1) +
+                batch * ((sched_prompt + sched_new) // P + 2))
     pool = PagePool(capacity)
     storage = PagedKVStorage(ex, capacity, L, P, KVH, D, 2)
     assert storage.initialize()
@@ -466,6 +468,27 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False, from_ggu
         prefill = {"prompt_tokens": n_prompt, "ms": psec * 1e3, "tokens_per_s": world * n_prompt / psec,
                    "what": "run_prefill of one request from an empty context, wall clock, last token's logits on the host"}
     kv_bytes = float(sum(pos)) * 2 * KVH * D * 2 * L
+    # the same executor under the scheduler: `batch` requests of 128 prompt tokens, 64 new tokens each, greedy
+    # sampling (on the device), one request admitted per tick as in the reference's scheduler
+    served = None
+    if prompt_tokens and not reference_order:
+        from mlcompiler_b200.host import Scheduler
+        for r in range(batch + 2):
+            pex.release_request(r)
+        sched = Scheduler(pex, max_batch_size=batch)
+        for _ in range(batch):
+            sched.add_request([int(t) for t in rng.integers(0, vocab, sched_prompt)], max_new_tokens=sched_new, eos_token_id=-1)
+        t0 = time.perf_counter()
+        ticks = 0
+        while not sched.empty():
+            sched.tick()
+            ticks += 1
+        dt = env.reduce(time.perf_counter() - t0, "max")
+        made = sum(len(r["generated_tokens"]) for r in sched.drain_completed())
+        served = {"requests": batch, "prompt_tokens": sched_prompt, "new_tokens": sched_new, "ticks": ticks, "ms": dt * 1e3,
+                  "generated_tokens_per_s": world * made / dt,
+                  "what": "Scheduler.tick until idle: admission (one prompt per tick, 32 tokens per pass), batched decode "
+                          "passes with greedy sampling on the device"}
     pex.destroy()
     storage.destroy()
     return {
@@ -479,7 +502,7 @@ def run_model(env, steps=40, warmup=5, batch=32, reference_order=False, from_ggu
                    "logits on the host when it returns"},
         "ms_per_step_median_min_max": [float(np.median(times)) * 1e3, float(np.min(times)) * 1e3, float(np.max(times)) * 1e3],
         "bytes_per_step": {"weights": model.weight_bytes() - model.host["token_embd.weight"].nbytes, "kv": kv_bytes},
-        "gpu_launches": int(launches), "launches_per_step": launches / steps, "prefill": prefill, "model_load": load}
+        "gpu_launches": int(launches), "launches_per_step": launches / steps, "prefill": prefill, "served": served, "model_load": load}
 
 
 def run_matvec(env, steps=200, warmup=10, rows=11264, cols=2048, quant="q4_0", batch=32):

@@ -447,6 +447,11 @@ int mlc_encode_matmul_q6k_batched(mlc_ctx* ctx, const void* weights, const void*
  * MLC_DEVERR_BAD_TOKEN in the device error word. */
 int mlc_encode_embedding_q4_0(mlc_ctx* ctx, const void* table, size_t row_stride, const void* token_ids, size_t batch,
                               size_t cols, size_t vocab, void* out);
+/* Greedy sampling on the device (no counterpart in the reference, whose scheduler takes the argmax of the
+ * logits on the host, scheduler.cpp:101-118): out_ids[n] (uint32) = index of the first maximum of request n's
+ * vocab logits. group_rows = 0 or >= vocab: logits is a plain [batch, vocab] array; otherwise the walker's
+ * layout, groups of group_rows vocabulary rows, each group a [batch, rows of the group] array. */
+int mlc_encode_argmax_rows(mlc_ctx* ctx, const void* logits, size_t batch, size_t vocab, size_t group_rows, void* out_ids);
 /* The same mat-vec with its neighbours in the walker fused in (no counterpart in the reference).
  * input_kind 0: in = fp32 [batch, in_stride], as above.
  * input_kind 1: the input row n is SiLU(in[n, c]) * in[n, cols + c], computed on load (in = the

@@ -81,6 +81,7 @@ _PROTOTYPES = {
     "mlc_encode_matmul_q4_0_batched": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp]),
     "mlc_encode_matmul_q6k_batched": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp]),
     "mlc_encode_matmul_quant_fused": (_i, [_vp, _i, _vp, _vp, _sz, _i, _vp, _sz, _sz, _sz, _sz, _vp]),
+    "mlc_encode_argmax_rows": (_i, [_vp, _vp, _sz, _sz, _sz, _vp]),
     "mlc_encode_matmul_gate_up_silu_packed": (_i, [_vp, _i, _vp, _vp, _sz, _i, _sz, _sz, _sz, _sz, _vp]),
     "mlc_compute_rotary_coefficients": (_i, [_sz, _sz, _f, _f, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "mlc_exchange_create": (_i, [_vp, _i, _i, _sz, _sz, C.POINTER(_vp)]),
@@ -483,6 +484,11 @@ class Executor:
         return self.status(self._lib.mlc_encode_matmul_gate_up_silu_packed(
             self._h, quant, _vp(_ptr(weights_buf)), _vp(_ptr(in_buf)), in_stride, int(input_kind), batch, ffn_inner, cols,
             row_stride, _vp(_ptr(packed_buf))))
+
+    def encodeArgmaxRows(self, logits_buf, batch, vocab, group_rows, out_ids) -> bool:
+        """Index of the first maximum per request (uint32), logits plain [batch, vocab] or in the walker's groups."""
+        return self.status(self._lib.mlc_encode_argmax_rows(self._h, _vp(_ptr(logits_buf)), batch, vocab, group_rows,
+                                                            _vp(_ptr(out_ids))))
 
     def encodeAddBatched(self, a_buf, b_buf, out_buf, total_elements) -> bool:
         """metal_runtime.hpp:501-502."""

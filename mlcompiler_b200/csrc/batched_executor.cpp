@@ -135,6 +135,20 @@ BatchedDecodeOutput PagedAttentionExecutor::run_decode_into(const std::vector<Re
     return walker_->step(slots, &sink);
 }
 
+bool PagedAttentionExecutor::run_decode_greedy(const std::vector<RequestSlot>& slots, std::vector<uint64_t>& tokens) {
+    // only the whole model step in the fused order ends in logits on the device
+    if (slots.empty() || !storage_ || !pool_ || !model_ || order_ != CallOrder::Fused) return false;
+    tokens.clear();
+    const BatchedDecodeOutput out = walker_->step(slots, nullptr, &tokens);
+    if (tokens.size() != slots.size() || out.per_request.size() != slots.size()) {
+        tokens.assign(slots.size(), UINT64_MAX);   // the pass ran and failed (pool exhausted, bad token): every slot failed
+        return true;
+    }
+    for (size_t i = 0; i < slots.size(); ++i)
+        if (!out.per_request[i].success) tokens[i] = UINT64_MAX;
+    return true;
+}
+
 size_t PagedAttentionExecutor::logits_per_request() const {
     return model_ ? model_->vocab_size : static_cast<size_t>(H_) * D_;
 }

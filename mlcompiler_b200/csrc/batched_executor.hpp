@@ -48,6 +48,15 @@ class IBatchedExecutor {
 public:
     virtual ~IBatchedExecutor() = default;
     virtual BatchedDecodeOutput run_decode(const std::vector<RequestSlot>& slots) = 0;
+    // Optional (no counterpart in the reference, whose scheduler takes the argmax of the logits itself,
+    // scheduler.cpp:101-118): the same pass ending in greedy sampling inside the executor. On success tokens[i] is
+    // the index of the first maximum of slot i's logits and the function returns true; an executor that cannot do
+    // this returns false without having run anything, and the caller falls back to run_decode.
+    virtual bool run_decode_greedy(const std::vector<RequestSlot>& slots, std::vector<uint64_t>& tokens) {
+        (void)slots;
+        (void)tokens;
+        return false;
+    }
     virtual std::vector<float> run_prefill(uint32_t request_id, const std::vector<uint64_t>& tokens) = 0;
     virtual void release_request(uint32_t request_id) = 0;
 };
@@ -121,6 +130,7 @@ public:
     // [vocab_size] per request; a prompt is fed token by token through the decode path in the reference's call
     // order (batched_executor.cpp:450-467), 32 tokens per pass in the fused order. Returns false if the
     // description does not fit the executor.
+    bool run_decode_greedy(const std::vector<RequestSlot>& slots, std::vector<uint64_t>& tokens) override;
     bool attach_model(const ModelWeights& model);
     // Reads the model out of a GGUF file (the tensors and metadata keys the reference's walker uses,
     // batched_walker.cpp:183-190, 248-420; kernel_scheduler.cpp:251-258), uploads the weights into one device

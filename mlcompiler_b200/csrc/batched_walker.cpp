@@ -20,6 +20,7 @@ namespace runtime {
 
 BatchedWalker::~BatchedWalker() {
     if (logits_pinned_) cudaFreeHost(logits_pinned_);
+    if (tokens_pinned_) cudaFreeHost(tokens_pinned_);
 }
 
 // NVTX range for the lifetime of the object: a pass, and inside a model pass every layer, show up by name in a
@@ -44,7 +45,8 @@ static double now_us() {
     return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
-BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, const LogitsSink* sink) {
+BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, const LogitsSink* sink,
+                                        std::vector<uint64_t>* greedy) {
     BatchedDecodeOutput out;
     if (slots.empty()) return out;
     NvtxRange pass_range("mlc decode pass");
@@ -124,7 +126,18 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, c
             direct = cudaPointerGetAttributes(&attr, sink->dst) == cudaSuccess && attr.type == cudaMemoryTypeHost;
             cudaGetLastError();   // a pointer the runtime does not know is not an error here
         }
-        if (!direct && logits_pinned_floats_ < N * vocab) {
+        if (greedy && tokens_pinned_count_ < N) {
+            if (tokens_pinned_) cudaFreeHost(tokens_pinned_);
+            tokens_pinned_ = nullptr;
+            tokens_pinned_count_ = 0;
+            DeviceGuard guard(ctx->device);
+            if (cudaHostAlloc(reinterpret_cast<void**>(&tokens_pinned_), std::max<size_t>(N, 64) * sizeof(uint32_t),
+                              cudaHostAllocDefault) != cudaSuccess)
+                return fail_all();
+            tokens_pinned_count_ = std::max<size_t>(N, 64);
+            ++ctx->allocations;
+        }
+        if (!greedy && !direct && logits_pinned_floats_ < N * vocab) {
             if (logits_pinned_) cudaFreeHost(logits_pinned_);
             logits_pinned_ = nullptr;
             logits_pinned_floats_ = 0;
@@ -139,21 +152,25 @@ BatchedDecodeOutput BatchedWalker::step(const std::vector<RequestSlot>& slots, c
         bool ok = mlc_pass_begin(ctx) == MLC_OK;
         ok = ok && encode_model_pass(slots, plan, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos,
                                      direct ? sink->dst : logits_pinned_, direct ? sink->stride : vocab, 0,
-                                     true);   // a decode pass writes one row per request, at the plan's (page, slot)
+                                     true,   // a decode pass writes one row per request, at the plan's (page, slot)
+                                     greedy ? tokens_pinned_ : nullptr);
         const double t_enc = walker_trace() ? now_us() : 0.0;
         ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;   // the logits are on the host when this returns
         const double t_flush = walker_trace() ? now_us() : 0.0;
         if (!ok) return fail_all();
-        if (!direct && sink && sink->dst && sink->stride >= vocab)
+        if (greedy) {
+            greedy->assign(tokens_pinned_, tokens_pinned_ + N);
+        } else if (!direct && sink && sink->dst && sink->stride >= vocab) {
             for (size_t r = 0; r < N; ++r)
                 std::memcpy(sink->dst + r * sink->stride, logits_pinned_ + r * vocab, vocab * sizeof(float));
+        }
         const bool to_sink = sink && sink->dst && sink->stride >= vocab;
         out.per_request.reserve(N);
         for (size_t r = 0; r < N; ++r) {
             BatchedDecodeOutput::PerRequest p;
             p.request_id = slots[r].request_id;
             p.success = true;
-            if (!to_sink) p.logits.assign(logits_pinned_ + r * vocab, logits_pinned_ + (r + 1) * vocab);
+            if (!to_sink && !greedy) p.logits.assign(logits_pinned_ + r * vocab, logits_pinned_ + (r + 1) * vocab);
             reqs[r]->next_position = slots[r].sequence_position + 1;
             out.per_request.push_back(std::move(p));
         }
@@ -250,7 +267,7 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                                       const std::vector<uint32_t>& pt_flat, const std::vector<uint32_t>& pt_off,
                                       const std::vector<uint32_t>& seq_lens, const std::vector<uint32_t>& q_pos,
                                       float* logits_host, size_t logits_stride, size_t head_first,
-                                      bool rows_per_request_only) {
+                                      bool rows_per_request_only, uint32_t* greedy_host) {
     PagedAttentionExecutor& ex = exec_;
     mlc_ctx* ctx = ex.ctx_;
     PagedKVStorage* storage = ex.storage_;
@@ -403,11 +420,18 @@ bool BatchedWalker::encode_model_pass(const std::vector<RequestSlot>& slots, mlc
                        : head_quant == 1 ? mlc_encode_matmul_q6k_batched(ctx, w_g, final_n, head_n, nr, hidden, head_stride, out_g)
                                          : mlc_encode_matmul_q4_0_batched(ctx, w_g, final_n, head_n, nr, hidden, head_stride, out_g);
         if (st != MLC_OK) return false;
+        if (greedy_host) continue;   // the logits stay on the device
         if (cudaEventRecord(ctx->pass_events[g], ctx->stream) != cudaSuccess ||
             cudaStreamWaitEvent(ctx->d2h_stream, ctx->pass_events[g], 0) != cudaSuccess ||
             cudaMemcpy2DAsync(logits_host + r0, logits_stride * sizeof(float), out_g, nr * sizeof(float), nr * sizeof(float), head_n,
                               cudaMemcpyDeviceToHost, ctx->d2h_stream) != cudaSuccess)
             return false;
+    }
+    if (greedy_host) {
+        // greedy sampling on the device: one token id per request comes back instead of the logits
+        void* ids = scratch("w_argmax", head_n * sizeof(uint32_t));
+        return ids && mlc_encode_argmax_rows(ctx, logits, head_n, vocab, group_rows, ids) == MLC_OK &&
+               cudaMemcpyAsync(greedy_host, ids, head_n * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess;
     }
     if (cudaEventRecord(ctx->pass_events[groups], ctx->d2h_stream) != cudaSuccess) return false;
     ctx->host_pass_done = ctx->pass_events[groups];
@@ -475,7 +499,7 @@ std::vector<float> BatchedWalker::prefill_model(uint32_t request_id, const std::
         const bool last = done + n == tokens.size();
         bool ok = mlc_pass_begin(ctx) == MLC_OK;
         ok = ok && encode_model_pass(slots, slot, page_ids, slot_ids, pt_flat, pt_off, seq_lens, q_pos, logits_pinned_, vocab,
-                                     last ? n - 1 : n, false);   // a chunk's rows are context of the chunk's later tokens
+                                     last ? n - 1 : n, false, nullptr);   // a chunk's rows are context of the chunk's later tokens
         ok = (mlc_pass_flush(ctx) == MLC_OK) && ok;
         if (!ok) return {};
     }

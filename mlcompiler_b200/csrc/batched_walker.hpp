@@ -19,7 +19,10 @@ public:
         float* dst = nullptr;
         size_t stride = 0;
     };
-    BatchedDecodeOutput step(const std::vector<RequestSlot>& slots, const LogitsSink* sink = nullptr);
+    // greedy (model attached only): the pass ends with the argmax of every request's logits on the device and
+    // *greedy receives one token id per request; no logits come back.
+    BatchedDecodeOutput step(const std::vector<RequestSlot>& slots, const LogitsSink* sink = nullptr,
+                             std::vector<uint64_t>* greedy = nullptr);
     // All tokens of a prompt chunk in one pass per layer: the chunk's K/V rows are scattered,
     // then chunked causal attention runs over the request's pages. Returns the last token's
     // attention output of the last layer, or {} on failure. The reference reaches the same
@@ -39,13 +42,15 @@ private:
                            const std::vector<uint32_t>& slot_ids, const std::vector<uint32_t>& pt_flat,
                            const std::vector<uint32_t>& pt_off, const std::vector<uint32_t>& seq_lens,
                            const std::vector<uint32_t>& q_pos, float* logits_host, size_t logits_stride, size_t head_first,
-                           bool rows_per_request_only);
+                           bool rows_per_request_only, uint32_t* greedy_host);
 
     PagedAttentionExecutor& exec_;
     std::vector<float> cos_host_, sin_host_;
     std::vector<uint32_t> tok_host_;
     float* logits_pinned_ = nullptr;   // page-locked landing area of the logits download, grown on demand
     size_t logits_pinned_floats_ = 0;
+    uint32_t* tokens_pinned_ = nullptr;   // page-locked landing area of the greedy token ids
+    size_t tokens_pinned_count_ = 0;
     // host staging, reused across passes
     std::vector<float> q_host_;
     std::vector<uint16_t> k_host_, v_host_;

@@ -210,6 +210,45 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
     if (i < n) out[i] = silu_mul(gate[i], up[i]);
 }
 
+// Index of the first maximum of every request's logits, one CTA per request. The logits lie as the walker's lm_head
+// leaves them: groups of `group_rows` vocabulary rows, each group a [batch, rows of the group] array (group_rows >=
+// vocab: one plain [batch, vocab] array). A thread looks at indices tid, tid + 256, ... in rising order and keeps the
+// first maximum it sees; between threads the larger value wins and, among equals, the lower index - what a host
+// loop `if (x[i] > x[best]) best = i` returns for finite values.
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, uint32_t batch, uint32_t vocab,
+                                                          uint32_t group_rows, uint32_t* __restrict__ out) {
+    __shared__ float s_val[8];
+    __shared__ uint32_t s_idx[8];
+    dependent_launch_gate();
+    const uint32_t n = blockIdx.x;
+    float best = -INFINITY;
+    uint32_t best_i = 0xFFFFFFFFu;
+    for (uint32_t r0 = 0; r0 < vocab; r0 += group_rows) {
+        const uint32_t nr = min(group_rows, vocab - r0);
+        const float* row = logits + static_cast<size_t>(batch) * r0 + static_cast<size_t>(n) * nr;
+        for (uint32_t c = threadIdx.x; c < nr; c += blockDim.x) {
+            const float v = row[c];
+            if (v > best || best_i == 0xFFFFFFFFu) { best = v; best_i = r0 + c; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t i = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (i != 0xFFFFFFFFu && (best_i == 0xFFFFFFFFu || v > best || (v == best && i < best_i))) { best = v; best_i = i; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) {
+            const float v = s_val[w];
+            const uint32_t i = s_idx[w];
+            if (i != 0xFFFFFFFFu && (best_i == 0xFFFFFFFFu || v > best || (v == best && i < best_i))) { best = v; best_i = i; }
+        }
+        out[n] = best_i;
+    }
+}
+
 __device__ __forceinline__ float half_bits_to_float(uint32_t bits) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(bits)));
 }
@@ -1399,6 +1438,21 @@ int mlc_encode_gate_up_split_silu_mul(mlc_ctx* ctx, const void* gate_up, void* g
                                        static_cast<const float*>(gate_up), static_cast<float*>(gate), static_cast<float*>(up),
                                        static_cast<float*>(out), static_cast<uint32_t>(batch), static_cast<uint32_t>(ffn_inner),
                                        static_cast<uint32_t>(ffn_gate_up_rows)));
+    ++ctx->launches;
+    return MLC_OK;
+}
+
+int mlc_encode_argmax_rows(mlc_ctx* ctx, const void* logits, size_t batch, size_t vocab, size_t group_rows, void* out_ids) {
+    if (!ctx) return MLC_ERR_INVALID_ARG;
+    if (!ctx->pass_open) return ctx->fail(MLC_ERR_NO_OPEN_PASS, "encode without an open pass");
+    if (!logits || !out_ids) return ctx->fail(MLC_ERR_INVALID_ARG, "null buffer");
+    if (batch == 0 || vocab == 0) return ctx->fail(MLC_ERR_INVALID_ARG, "zero dimension");
+    if (batch >= (1u << 31) || vocab >= (size_t(1) << 32)) return ctx->fail(MLC_ERR_UNSUPPORTED, "dimension too large");
+    if (group_rows == 0 || group_rows > vocab) group_rows = vocab;
+    DeviceGuard guard(ctx->device);
+    MLCB_CUDA(ctx, launch_layer_kernel(ctx, argmax_rows_kernel, static_cast<unsigned>(batch), 256, 0, 1,
+                                       static_cast<const float*>(logits), static_cast<uint32_t>(batch), static_cast<uint32_t>(vocab),
+                                       static_cast<uint32_t>(group_rows), static_cast<uint32_t*>(out_ids)));
     ++ctx->launches;
     return MLC_OK;
 }

@@ -110,6 +110,24 @@ void Scheduler::decode_active() {
         who.push_back(&req);
     }
     if (slots.empty()) return;
+    // an executor that samples greedily itself hands back token ids instead of logits
+    std::vector<uint64_t> sampled;
+    if (executor_->run_decode_greedy(slots, sampled)) {
+        ++stats_.total_decode_steps;
+        if (sampled.size() != slots.size()) {
+            for (Request* req : who) fail(*req, "decode output size mismatch");
+            return;
+        }
+        for (size_t i = 0; i < who.size(); ++i) {
+            if (sampled[i] == UINT64_MAX) {
+                fail(*who[i], "decode failed");
+                continue;
+            }
+            ++who[i]->position;
+            accept_token(*who[i], sampled[i]);
+        }
+        return;
+    }
     const BatchedDecodeOutput out = executor_->run_decode(slots);
     ++stats_.total_decode_steps;
     if (out.per_request.size() != slots.size()) {

@@ -266,6 +266,29 @@ def test_gate_up_projection_with_silu_epilogue(executor, oracle_mod, kind, batch
     assert torch.equal(words, words2)
 
 
+@pytest.mark.parametrize("batch,vocab,group_rows", [(32, 32000, 8000), (3, 1000, 0), (5, 321, 128), (1, 7, 64), (64, 4099, 1088)])
+def test_argmax_rows(executor, batch, vocab, group_rows):
+    """Greedy sampling on the device: the first maximum of every request's logits, from a plain [batch, vocab] array
+    or from the walker's layout (groups of vocabulary rows, each a [batch, rows of the group] array)."""
+    import torch
+    rng = np.random.default_rng(vocab)
+    logits = rng.standard_normal((batch, vocab)).astype(np.float32)
+    logits[0, 5 % vocab] = logits[0, vocab - 1] = 9.0           # a tie: the lower index wins
+    if batch > 1:
+        logits[1, :] = -3.5                                     # all equal: index 0
+    if batch > 2:
+        logits[2, vocab - 1] = 50.0                             # the last column
+    want = logits.argmax(axis=1).astype(np.uint32)
+    if group_rows and group_rows < vocab:
+        laid = np.concatenate([logits[:, r0:r0 + group_rows].reshape(-1) for r0 in range(0, vocab, group_rows)])
+    else:
+        laid = logits.reshape(-1)
+    d = _dev(laid)
+    out = torch.full((batch,), 0x7FFFFFFF, device="cuda", dtype=torch.int32)
+    _run(executor, lambda: executor.encodeArgmaxRows(d, batch, vocab, group_rows, out))
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want)
+
+
 def test_layer_ops_argument_rules(executor):
     import torch
     x = torch.zeros((2, 64), device="cuda")
