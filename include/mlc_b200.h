@@ -767,6 +767,11 @@ int mlc_executor_set_call_order(mlc_executor* exec, int reference_order);
  * device when `logits` is page-locked host memory (cudaHostAlloc / cudaHostRegister / pin_memory). */
 size_t mlc_executor_run_decode(mlc_executor* exec, const mlc_request_slot* slots, size_t n, uint8_t* success,
                                float* logits, size_t logits_stride);
+/* The same pass ending in greedy sampling on the device (model attached, fused call order): tokens[i] =
+ * index of the first maximum of slot i's logits, UINT64_MAX for a slot that failed; 128 bytes cross the bus
+ * instead of batch * vocab_size floats. Returns n, or 0 when the executor cannot do it (nothing has run
+ * then: use mlc_executor_run_decode). The scheduler uses this path by itself. */
+size_t mlc_executor_run_decode_greedy(mlc_executor* exec, const mlc_request_slot* slots, size_t n, uint64_t* tokens);
 /* run_prefill: returns the number of logits (0 = failed). */
 size_t mlc_executor_run_prefill(mlc_executor* exec, uint32_t request_id, const uint64_t* tokens, size_t n,
                                 float* logits, size_t capacity);

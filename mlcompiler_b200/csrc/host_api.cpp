@@ -352,6 +352,16 @@ size_t mlc_executor_run_decode(mlc_executor* e, const mlc_request_slot* slots, s
     }
     return out.per_request.size();
 }
+size_t mlc_executor_run_decode_greedy(mlc_executor* e, const mlc_request_slot* slots, size_t n, uint64_t* tokens) {
+    if (!e || (!slots && n) || (!tokens && n)) return 0;
+    std::vector<RequestSlot> in(n);
+    for (size_t i = 0; i < n; ++i)
+        in[i] = {slots[i].request_id, slots[i].input_token, static_cast<size_t>(slots[i].sequence_position)};
+    std::vector<uint64_t> out;
+    if (!e->exec->run_decode_greedy(in, out) || out.size() != n) return 0;
+    std::memcpy(tokens, out.data(), n * sizeof(uint64_t));
+    return n;
+}
 size_t mlc_executor_run_prefill(mlc_executor* e, uint32_t request_id, const uint64_t* tokens, size_t n,
                                 float* logits, size_t capacity) {
     if (!e) return 0;

@@ -92,6 +92,7 @@ _PROTOTYPES = {
     "mlc_tokenizer_token_string": (_sz, [_vp, _u64, C.c_char_p, _sz]),
     "mlc_tokenizer_token_flags": (_i, [_vp, _u64]),
     "mlc_executor_run_decode": (_sz, [_vp, C.POINTER(RequestSlotC), _sz, C.POINTER(C.c_uint8), _fp, _sz]),
+    "mlc_executor_run_decode_greedy": (_sz, [_vp, C.POINTER(RequestSlotC), _sz, _u64p]),
     "mlc_executor_run_prefill": (_sz, [_vp, _u32, _u64p, _sz, _fp, _sz]),
     "mlc_executor_release_request": (None, [_vp, _u32]),
     "mlc_executor_live_request_count": (_sz, [_vp]),
@@ -441,6 +442,16 @@ class PagedAttentionExecutor(_ExecutorBase):
         logits = self._logits_rows(max(n, 1), stride)          # rows are returned as views of this one array
         got = lib().mlc_executor_run_decode(self._h, arr, n, success, logits.ctypes.data_as(_fp), stride)
         return [(slots[i][0], bool(success[i]), logits[i] if success[i] else None) for i in range(got)]
+
+    def run_decode_greedy(self, slots):
+        """slots as in run_decode -> [token id or None (failed slot)], or None when the executor has no model attached
+        (or runs the reference's call order): the argmax of every request's logits, taken on the device."""
+        n = len(slots)
+        arr = (RequestSlotC * max(n, 1))(*[RequestSlotC(*s) for s in slots])
+        toks = (C.c_uint64 * max(n, 1))()
+        if lib().mlc_executor_run_decode_greedy(self._h, arr, n, toks) != n or n == 0:
+            return None
+        return [None if int(t) == 2 ** 64 - 1 else int(t) for t in toks[:n]]
 
     def run_prefill(self, request_id, tokens):
         toks = (C.c_uint64 * max(len(tokens), 1))(*tokens)

@@ -237,6 +237,30 @@ def test_benchmark_shapes_at_32_requests(executor, oracle_mod):
     storage.destroy()
 
 
+def test_greedy_decode_on_the_device_equals_argmax_of_the_logits(executor):
+    """run_decode_greedy against run_decode + numpy argmax on two executors fed the same slots."""
+    model = synth.SyntheticModel(0xA46, 2, 4, 2, 64, 256, 515)          # a vocabulary that is no multiple of 4
+    _, sa, a = make_stack(executor, model, 8)
+    _, sb, b = make_stack(executor, model, 8)
+    rng = np.random.default_rng(1)
+    pos = {3: 0, 4: 0, 9: 0}
+    for step in range(6):
+        slots = [(rid, int(rng.integers(0, model.vocab_size)), pos[rid]) for rid in pos]
+        want = [int(np.argmax(o[2])) for o in a.run_decode(slots)]
+        got = b.run_decode_greedy(slots)
+        assert got == want, f"step {step}"
+        for rid in pos:
+            pos[rid] += 1
+    b.set_call_order(True)
+    assert b.run_decode_greedy([(3, 1, pos[3])]) is None          # the reference's call order returns logits only
+    bare = PagedAttentionExecutor(executor, 4, 2, 64, 2, 0)
+    assert bare.run_decode_greedy([(1, 1, 0)]) is None            # no model attached
+    for x in (a, b, bare):
+        x.destroy()
+    for s_ in (sa, sb):
+        s_.destroy()
+
+
 def test_scheduler_generates_the_oracles_tokens(executor, oracle_mod):
     """The scheduler over the executor with a model generates greedy tokens that the oracle model reproduces."""
     model = synth.SyntheticModel(0xFEED, 2, 4, 2, 64, 256, 512)
