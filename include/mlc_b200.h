@@ -689,13 +689,16 @@ typedef struct mlc_model_desc {
 } mlc_model_desc;
 int mlc_executor_attach_model(mlc_executor* exec, const mlc_model_desc* model);
 /* ---- GGUF files (compiler/frontends/gguf_loader.{hpp,cpp}: GGUFLoader) -------------------------
- * The container the reference loads its models from, versions 2 and 3: header, typed key / value
+ * The container the reference loads its models from, versions 1 to 3: header, typed key / value
  * metadata, tensor directory (sizes by ggml block format, offsets relative to the aligned end of the
  * directory, general.alignment honoured), tensor bytes read through a read-only mapping, and the
  * reference's byte-concatenation of every block's attn_q | attn_k | attn_v and ffn_gate | ffn_up
  * (Q4_0) into the fused attn_qkv and ffn_gate_up the batched walker multiplies with
- * (GGUFLoader::concatenateBlockWeights, gguf_loader.cpp:877-943). Version 1 files and damaged files
- * the reference's recovery heuristics would read on through are rejected with a message.
+ * (GGUFLoader::concatenateBlockWeights, gguf_loader.cpp:877-943). Version 1 is read as the reference
+ * reads it (and its tests write it): 32-bit tensor dimensions, optionally behind a 64-bit repeat of the
+ * rank, offsets that are file positions. A key longer than 1 MiB is dropped with its value
+ * (gguf_loader.cpp:553-607); damaged files the reference's other recovery heuristics would read on
+ * through are rejected with a message.
  * Functions that can fail take an optional `error` buffer for the message (always terminated).
  *   mlc_gguf_open                     GGUFLoader(path) + load(); NULL on failure
  *   mlc_gguf_concatenate_block_weights  number of tensors added, -1 on failure

@@ -39,6 +39,17 @@ struct Cursor {
         pos += n;
         return s;
     }
+    // A key or a tensor name: one of more than 1 MiB is taken for damage - its bytes are passed over and the entry
+    // it names is dropped (gguf_loader.cpp:187-243 with enforce_soft_limit, 553-554, 590-607).
+    std::string name(const char* what, bool* damaged) {
+        const uint64_t n = get<uint64_t>(what);
+        if (n > end - pos) fail(std::string("string longer than the rest of the file: ") + what);
+        *damaged = n > (uint64_t(1) << 20);
+        std::string s;
+        if (!*damaged) s.assign(reinterpret_cast<const char*>(base + pos), static_cast<size_t>(n));
+        pos += n;
+        return s;
+    }
 };
 
 Value parse_value(Cursor& c, uint32_t type, int depth) {
@@ -189,14 +200,16 @@ File::File(const std::string& path) : path_(path) {
         Cursor c{map_, 0, size_};
         if (c.get<uint32_t>("magic") != kMagic) fail("Invalid GGUF magic");
         version_ = c.get<uint32_t>("version");
-        if (version_ != 2 && version_ != 3) fail("Unsupported GGUF version: " + std::to_string(version_));
+        if (version_ < 1 || version_ > 3) fail("Unsupported GGUF version: " + std::to_string(version_));
         n_tensors_ = c.get<uint64_t>("tensor count");
         n_kv_ = c.get<uint64_t>("metadata count");
         for (uint64_t i = 0; i < n_kv_; ++i) {
-            std::string key = c.str("metadata key");
+            bool damaged = false;
+            std::string key = c.name("metadata key", &damaged);
             const uint32_t type = c.get<uint32_t>("metadata value type");
             if (type > kRaw) fail("Invalid value type " + std::to_string(type));
-            kv_[key] = parse_value(c, type, 0);
+            Value v = parse_value(c, type, 0);
+            if (!damaged) kv_[key] = std::move(v);
         }
         if (const Value* q = find_kv("general.quantization_version"))
             if (q->type == kU32 || q->type == kU64) quant_version_ = static_cast<uint32_t>(q->u);
@@ -208,19 +221,36 @@ File::File(const std::string& path) : path_(path) {
         }
         for (uint64_t i = 0; i < n_tensors_; ++i) {
             TensorInfo t;
-            t.name = c.str("tensor name");
+            bool damaged = false;
+            t.name = c.name("tensor name", &damaged);
+            if (damaged) t.name = "<CORRUPT_STRING>";   // the reference keeps such an entry under this name
             const uint32_t n_dims = c.get<uint32_t>("tensor rank");
             if (n_dims > 16) fail("tensor '" + t.name + "' has " + std::to_string(n_dims) + " dimensions");
-            for (uint32_t d = 0; d < n_dims; ++d) t.shape.push_back(c.get<uint64_t>("tensor dimension"));
+            if (version_ == 1) {
+                // version 1 as the reference reads it (gguf_loader.cpp:781-807): 32-bit dimensions, optionally behind
+                // a 64-bit repeat of the rank
+                if (n_dims > 0 && c.end - c.pos >= 8) {
+                    uint64_t again;
+                    std::memcpy(&again, c.base + c.pos, 8);
+                    if (again == n_dims) c.pos += 8;
+                }
+                for (uint32_t d = 0; d < n_dims; ++d) t.shape.push_back(c.get<uint32_t>("tensor dimension"));
+            } else {
+                for (uint32_t d = 0; d < n_dims; ++d) t.shape.push_back(c.get<uint64_t>("tensor dimension"));
+            }
             t.dtype = c.get<uint32_t>("tensor type");
             t.offset = c.get<uint64_t>("tensor offset");
             t.n_bytes = tensor_bytes(t.shape, t.dtype);
             tensors_[t.name] = std::move(t);   // a repeated name keeps its last entry
         }
-        data_start_ = (c.pos + alignment_ - 1) / alignment_ * alignment_;
-        for (auto& kv : tensors_)
-            if (__builtin_add_overflow(kv.second.offset, data_start_, &kv.second.offset))
-                fail("tensor '" + kv.first + "': offset overflows");
+        if (version_ == 1) {
+            data_start_ = c.pos;   // version 1: offsets are positions in the file, nothing is padded
+        } else {
+            data_start_ = (c.pos + alignment_ - 1) / alignment_ * alignment_;
+            for (auto& kv : tensors_)
+                if (__builtin_add_overflow(kv.second.offset, data_start_, &kv.second.offset))
+                    fail("tensor '" + kv.first + "': offset overflows");
+        }
     } catch (...) {
         if (map_) ::munmap(const_cast<uint8_t*>(map_), size_);
         if (fd_ >= 0) ::close(fd_);

@@ -1,4 +1,4 @@
-// GGUF container (versions 2 and 3): header, key/value metadata, tensor directory, tensor bytes.
+// GGUF container (versions 1 to 3): header, key/value metadata, tensor directory, tensor bytes.
 // Host-only; the file is mapped read-only and tensor bytes are handed out as pointers into the mapping.
 //
 // Follows what compiler/frontends/gguf_loader.cpp makes of a file (load(): 306-433, parseValue: 463-533,
@@ -12,8 +12,13 @@
 //   * a name that occurs twice keeps its last entry;
 //   * per block, attn_q | attn_k | attn_v and ffn_gate | ffn_up (all Q4_0, 2-D, equal column counts) are
 //     byte-concatenated into attn_qkv and ffn_gate_up, the tensors the batched walker reads.
-// Not taken over: version 1 files and the reference's recovery heuristics for damaged files (32-bit string
-// lengths, skipping to the next 32-byte boundary after a bad entry); such files are rejected with a message.
+//   * version 1 as the reference reads (and its tests write) it: 64-bit counts and string lengths like the later
+//     versions, 32-bit tensor dimensions optionally behind a 64-bit repeat of the rank, tensor offsets that are
+//     positions in the file, no padding;
+//   * a key or tensor name longer than 1 MiB is taken for damage: a key's entry is dropped, its value still read.
+// Not taken over: the reference's other recovery heuristics for damaged files (32-bit string lengths, skipping to
+// the next 32-byte boundary after an entry that failed to parse, a truncated tensor directory read as far as it
+// goes); such files are rejected with a message.
 #pragma once
 
 #include <cstdint>

@@ -196,3 +196,54 @@ def tokenizer_file(path, name):
     kv, n = tokenizer_kv(name)
     synth.write_gguf(path, kv, [])
     return n
+
+
+# ---- version-1 files laid out like the fixtures of the reference's own loader tests ----------------------------------
+def _s(b):
+    import struct
+    b = b if isinstance(b, bytes) else b.encode()
+    return struct.pack("<Q", len(b)) + b
+
+
+def v1_file(path, case):
+    """case "mock": tests/test_gguf_loader.cpp:20-86 (one string key, two tensors whose 32-bit dimensions follow a 64-bit
+    repeat of the rank, absolute offsets 256 and 400); "plain_dims": the same without the repeat; "corrupt_key":
+    :248-282 (a key of 1 MiB + 16 bytes is dropped, its value read, the next entry kept); "values": every value type
+    as tests/test_gguf_values.cpp writes them, a raw blob (:275-285) and nested arrays (:325-358) among them;
+    "overflow": :284-308 (three dimensions of 2^32 - 1)."""
+    import struct
+    head = lambda n_tensors, n_kv: struct.pack("<IIQQ", 0x46554747, 1, n_tensors, n_kv)
+    if case in ("mock", "plain_dims"):
+        rep = (lambda n: struct.pack("<Q", n)) if case == "mock" else (lambda n: b"")
+        out = head(2, 1) + _s("test.key") + struct.pack("<I", 8) + _s("test.value")
+        out += _s("tensor1") + struct.pack("<I", 2) + rep(2) + struct.pack("<II", 3, 4) + struct.pack("<IQ", 0, 256)
+        out += _s("tensor2") + struct.pack("<I", 1) + rep(1) + struct.pack("<I", 10) + struct.pack("<IQ", 2, 400)
+        out = out.ljust(256, b"\0") + np.full(12, 1.5, np.float32).tobytes()
+        out = out.ljust(400, b"\0") + np.full(10, 0x3C00, np.uint16).tobytes()
+    elif case == "corrupt_key":
+        n = (1 << 20) + 16
+        out = head(0, 2) + struct.pack("<Q", n) + b"A" * n + struct.pack("<IB", 0, 7)
+        out += _s("valid.key") + struct.pack("<I", 8) + _s("ok")
+    elif case == "values":
+        kv = [("u8", 0, struct.pack("<B", 200)), ("i8", 1, struct.pack("<b", -5)), ("u16", 2, struct.pack("<H", 60000)),
+              ("i16", 3, struct.pack("<h", -300)), ("u32", 4, struct.pack("<I", 123456789)), ("i32", 5, struct.pack("<i", -7)),
+              ("f32", 6, struct.pack("<f", 3.25)), ("flag", 7, b"\x01"), ("str", 8, _s("hello")),
+              ("ints", 9, struct.pack("<IQ", 5, 3) + struct.pack("<iii", 1, -2, 3)),
+              ("strs", 9, struct.pack("<IQ", 8, 2) + _s("a") + _s("bc")),
+              ("u64", 10, struct.pack("<Q", 2 ** 40)), ("i64", 11, struct.pack("<q", -2 ** 40)), ("f64", 12, struct.pack("<d", 0.1)),
+              ("blob", 13, _s(bytes([1, 2, 3, 250]))),
+              ("nested", 9, struct.pack("<IQ", 9, 2) + struct.pack("<IQ", 4, 2) + struct.pack("<II", 7, 8) +
+               struct.pack("<IQ", 4, 1) + struct.pack("<I", 9))]
+        out = head(1, len(kv)) + b"".join(_s(k) + struct.pack("<I", t) + v for k, t, v in kv)
+        out += _s("t") + struct.pack("<I", 1) + struct.pack("<Q", 1) + struct.pack("<I", 4) + struct.pack("<IQ", 0, 1024)
+        out = out.ljust(1024, b"\0") + np.arange(4, dtype=np.float32).tobytes()
+    elif case == "overflow":
+        out = head(1, 0) + _s("huge.tensor") + struct.pack("<I", 3) + struct.pack("<Q", 3) + struct.pack("<III", *[2 ** 32 - 1] * 3)
+        out += struct.pack("<IQ", 0, 0)
+    else:
+        raise ValueError(case)
+    with open(path, "wb") as f:
+        f.write(out)
+
+
+V1_CASES = ("mock", "plain_dims", "corrupt_key", "values")

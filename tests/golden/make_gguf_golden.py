@@ -35,6 +35,10 @@ def main():
             path = tmp / (name + ".gguf")
             gguf_cases.zoo(path, version, alignment, declared, kind)
             out[name] = record(path, False)
+        for case in gguf_cases.V1_CASES:
+            path = tmp / ("v1_" + case + ".gguf")
+            gguf_cases.v1_file(path, case)
+            out["v1_" + case] = record(path, False)
         for case in gguf_cases.BLOCK_CASES:
             path = tmp / (case + ".gguf")
             gguf_cases.blocks(path, case)

@@ -22,6 +22,9 @@ def _write_case(name, tmp_path):
     if name in gguf_cases.ZOO_CASES:
         gguf_cases.zoo(path, *gguf_cases.ZOO_CASES[name])
         return path, False
+    if name.startswith("v1_"):
+        gguf_cases.v1_file(path, name[len("v1_"):])
+        return path, False
     gguf_cases.blocks(path, name[len("blocks_"):])
     return path, True
 
@@ -112,7 +115,8 @@ def _string(s):
 @pytest.mark.parametrize("blob,message", [
     (_header(magic=0x46554746), "Invalid GGUF magic"),
     (_header(version=7), "Unsupported GGUF version: 7"),
-    (_header(version=1), "Unsupported GGUF version: 1"),          # the reference reads version 1; this loader does not
+    (_header(version=0), "Unsupported GGUF version: 0"),
+    (_header(version=4), "Unsupported GGUF version: 4"),
     (_header()[:10], "unexpected end of file"),
     (_header(n_kv=1) + _string(b"k") + struct.pack("<I", 99), "Invalid value type 99"),
     (_header(n_kv=1) + _string(b"k") + struct.pack("<IIQ", 9, 99, 0), "Invalid value type 99"),
@@ -129,6 +133,24 @@ def test_refusals(tmp_path, blob, message):
         GgufFile(path)
 
 
+def test_version_1_fixture_of_the_reference_tests(tmp_path):
+    """tests/test_gguf_loader.cpp:108-178 on the file of :20-86: header, the one key, both tensors, their bytes."""
+    path = tmp_path / "mock.gguf"
+    gguf_cases.v1_file(path, "mock")
+    f = GgufFile(path)
+    d = f.describe()
+    assert (d["version"], d["n_tensors"], d["n_kv"]) == (1, 2, 1)
+    assert d["kv"] == {"test.key": {"type": "STRING", "value": "test.value"}}
+    assert d["tensors"]["tensor1"] == {"shape": [3, 4], "dtype": 0, "offset": 256, "n_bytes": 48}
+    assert d["tensors"]["tensor2"]["shape"] == [10] and d["tensors"]["tensor2"]["offset"] == 400
+    assert np.array_equal(f.tensor_data("tensor1").view(np.float32), np.full(12, 1.5, np.float32))
+    gguf_cases.v1_file(tmp_path / "over.gguf", "overflow")
+    with pytest.raises(RuntimeError, match="Overflow while calculating"):
+        GgufFile(tmp_path / "over.gguf")
+    gguf_cases.v1_file(tmp_path / "ck.gguf", "corrupt_key")
+    assert GgufFile(tmp_path / "ck.gguf").describe()["kv"] == {"valid.key": {"type": "STRING", "value": "ok"}}
+
+
 def test_refusal_details(tmp_path, oracle_mod):
     with pytest.raises(RuntimeError, match="Failed to open GGUF file"):
         GgufFile(tmp_path / "absent.gguf")
@@ -142,6 +164,9 @@ def test_refusal_details(tmp_path, oracle_mod):
     if oracle_mod.ref() is not None:
         assert oracle_mod.reference_gguf_tensor(path, "t") is None
         # the messages the two loaders share
+        gguf_cases.v1_file(tmp_path / "over.gguf", "overflow")
+        with pytest.raises(RuntimeError, match="Overflow while calculating"):
+            oracle_mod.reference_gguf_describe(tmp_path / "over.gguf")
         for blob, message in ((_header(magic=1), "Invalid GGUF magic"), (_header(version=7), "Unsupported GGUF version: 7")):
             bad = tmp_path / "bad.gguf"
             bad.write_bytes(blob)
