@@ -147,6 +147,8 @@ TOKENIZER_CASES = {
     "bare": dict(model=None, ids=None, base="spm", no_scores=True),            # tokens only: longest match
     "i32_ids": dict(model="llama", ids="i32"),                                 # ids of another integer type count as unset
     "empty": dict(model="llama", ids="u32", no_tokens=True),
+    # the vocabulary of the reference's own tokenizer test (tests/test_runtime.cpp:3377-3441): version 1, no model key
+    "reference_test": dict(model=None, ids="u32", fixture=True),
 }
 
 TOKENIZER_TEXTS = ["", "hello world", " hello world", "the hello and the world", "hello, world!", "café.", "日本 the",
@@ -163,6 +165,14 @@ def text_bytes(text) -> bytes:
 def tokenizer_kv(name):
     """(metadata triples of the vocabulary case, number of pieces)"""
     spec = TOKENIZER_CASES[name]
+    if spec.get("fixture"):
+        toks = ["<s>", "<eos>", "<unk>", "h", "e", "l", "o", " ", "w", "r", "d", "he", "hel", "hell", "hello", "wo", "wor",
+                "worl", "world"]
+        scores = [0.0, 0.0, -10.0] + [-1.0] * 8 + [1.0, 2.0, 3.0, 4.0] * 2
+        merges = ["h e", "he l", "hel l", "hell o", "  w", "wo r", "wor l", "worl d", "hello  "]
+        return [("tokenizer.ggml.tokens", ("array", "string"), toks), ("tokenizer.ggml.bos_token_id", "u32", 0),
+                ("tokenizer.ggml.eos_token_id", "u32", 1), ("tokenizer.ggml.unk_token_id", "u32", 2),
+                ("tokenizer.ggml.scores", ("array", "f32"), scores), ("tokenizer.ggml.merges", ("array", "string"), merges)], len(toks)
     base = spec.get("base", "bpe" if name.startswith("bpe") else "spm")
     kv = [("general.architecture", "string", "llama")]
     if spec["model"] is not None:
@@ -194,7 +204,7 @@ def tokenizer_kv(name):
 
 def tokenizer_file(path, name):
     kv, n = tokenizer_kv(name)
-    synth.write_gguf(path, kv, [])
+    synth.write_gguf(path, kv, [], version=1 if TOKENIZER_CASES[name].get("fixture") else 3)
     return n
 
 

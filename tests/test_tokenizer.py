@@ -68,6 +68,18 @@ def test_live_differential_against_the_reference(oracle_mod, tmp_path):
         assert t.decode_bytes(everything) == ref.decode(everything)
 
 
+def test_vocabulary_of_the_reference_test(tmp_path):
+    """The vocabulary of tests/test_runtime.cpp:3377-3441. That test expects <s>, hello, " ", world, <eos> = [0, 14, 7, 18, 1]
+    for "hello world" - what the llama.cpp path gives. The reference's own merge code, the behaviour restated here
+    (and recorded in the golden file from the reference built without llama.cpp), applies the merge "  w" first, gets
+    " w", which is no piece of the vocabulary, and answers [0, 14, 2, 6, 9, 5, 10, 1]; its decode does not treat "<eos>" as
+    special."""
+    _, _, t = _product(tmp_path, "reference_test")
+    assert t.valid() and t.encode("hello world", add_bos=True, add_eos=True) == [0, 14, 2, 6, 9, 5, 10, 1]
+    assert t.decode([0, 14, 7, 18, 1]) == "hello world<eos>"
+    assert t.encode("hello", add_bos=False) == [14]
+
+
 def test_round_trips_and_text_interface(tmp_path):
     _, _, t = _product(tmp_path, "spm")
     ids = t.encode("the hello and the world", add_bos=True)
